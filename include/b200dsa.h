@@ -1,0 +1,115 @@
+/* b200dsa — C ABI of the B200 (sm_100a) sparse-attention selection kernels.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream (as void*),
+ * launches asynchronously on that stream, allocates nothing and never synchronises.
+ * Return value: 0 on success, a negative B200DSA_E* code when the arguments are rejected
+ * (nothing is launched in that case).  Kernels that contain bounded waits or index checks
+ * report through a caller-owned int32 `status` word in device memory (0 = ok,
+ * 1 = a wait gave up, 2 = an out-of-range index was skipped); the caller zeroes it once
+ * and may read it whenever convenient.
+ *
+ * "Reference" citations name files of the TransArch repository whose behaviour the entry
+ * point reproduces (path relative to its root).
+ */
+#ifndef B200DSA_H_
+#define B200DSA_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200DSA_OK 0
+#define B200DSA_EINVAL (-1)      /* bad size / null pointer / unsupported combination */
+#define B200DSA_EALIGN (-2)      /* pointer or stride not aligned as documented */
+#define B200DSA_ECUDA (-3)       /* a CUDA runtime / driver call failed (see b200dsa_last_error) */
+#define B200DSA_EUNSUPPORTED (-4)
+
+/* Library / device introspection. */
+int b200dsa_abi_version(void);
+const char* b200dsa_last_error(void);
+
+/* ---------------------------------------------------------------------------------------
+ * Row-wise top-k selection over fp32 scores.
+ *
+ * Replaces the torch.topk + "-1 where not finite" step of
+ *   OpenDSA/opendsa/ops/topk_select.py:66-71
+ * and the torch.topk + gather + mask sequences of
+ *   MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/indexers.py:499-518, :566-568.
+ *
+ * Row r looks at columns [col_begin[r], col_end[r]) (defaults 0 and n_cols; clamped to
+ * [0, n_cols]).  -inf and NaN are never selected; +inf only when keep_pos_inf != 0.  The k
+ * largest remaining scores are chosen; equal scores are resolved towards the lowest
+ * output position, so the selected SET is deterministic.  Output rows are written in
+ * descending score order (ties: ascending position) and padded with -1 (values: -inf).
+ *
+ * Output position of column c in row r:
+ *   pos_map   != NULL : pos_map[r*pos_map_stride + c]
+ *   page_table!= NULL : page_table[r*page_table_stride + c/page_size]*page_size + c%page_size
+ *   otherwise         : c
+ * plus row_pos_offset[r] when that pointer is given.
+ *
+ * Limits: 1 <= k <= 8192.  scores rows need 4-byte alignment only.
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_topk_select(const float* scores, int64_t row_stride, int32_t n_rows, int32_t n_cols,
+                        const int32_t* col_begin, const int32_t* col_end, int32_t k,
+                        int32_t keep_pos_inf,
+                        const int32_t* pos_map, int64_t pos_map_stride,
+                        const int32_t* page_table, int64_t page_table_stride, int32_t page_size,
+                        const int32_t* row_pos_offset,
+                        int32_t* out_idx, float* out_val, int64_t out_stride,
+                        void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Decode indexer logits over the paged FP8 key cache (tcgen05 FP8 contraction).
+ *
+ *   logits[r, c] = out_scale * k_scale[c] * sum_h weights[r,h] * relu(<q[r,h,:], k_fp8[c,:]>)
+ *   for c < context_lens[r]; -inf for context_lens[r] <= c < roundup(context_lens[r], 128)
+ *   (clipped to max_cols); columns beyond that are left untouched.
+ *
+ * Replaces MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/misa_ops.py:56-199
+ * (paged_mqa_sparse_head_return_logits + interface) and the whole-cache dequantisation at
+ * :360-378; same role as the DeepGEMM fp8_paged_mqa_logits call at
+ * MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/indexers.py:182-191.
+ *
+ *   q_fp8        [n_rows, 64, 128] e4m3 (row r = request r/next_n, draft token r%next_n)
+ *   weights      [n_rows, 64] fp32, with q scale, softmax scale and head scale folded in
+ *                (MISA_preprint/.../misa_deepseek_v2.py:289-292)
+ *   cache        [num_pages, page_size*(128+4)] bytes: page_size*128 e4m3 then page_size fp32
+ *                scales (layout read at misa_ops.py:360-372); page_size in {32, 64, 128}
+ *   context_lens [n_rows] int32, keys visible to row r
+ *   block_table  [n_rows/next_n, block_table_stride] int32 page ids
+ * Page ids outside [0, num_pages) are skipped and reported through status (2).
+ * q, weights and cache must be 16-byte aligned.
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* weights, const void* cache,
+                                     int32_t num_pages, int32_t page_size, const int32_t* context_lens,
+                                     const int32_t* block_table, int64_t block_table_stride,
+                                     int32_t n_rows, int32_t next_n, int32_t max_cols, float out_scale,
+                                     float* logits, int64_t logits_stride, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Token logits inside per-row lists of 128-key blocks, bf16 keys (tcgen05 bf16 contraction).
+ * HISA stage 2 / block-sparse re-scoring.
+ *
+ *   column c of row r is key position block_list[r, c/128]*128 + c%128;
+ *   logits[r, c] = out_scale * sum_h weights[r,h]*relu(<q[r,h,:], keys[pos,:]>) when
+ *   c < row_cols[r] and pos_lo[r] <= pos < pos_hi[r] (bounds optional), else -inf.
+ *
+ * Replaces MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/block_ops.py:756-937
+ * (block_sparse_mqa_attn_return_logits and its interface).
+ *   q_bf16 [n_rows, 64, 128], keys_bf16 [n_keys, 128] (both 16-byte aligned),
+ *   row_cols [n_rows] = 128 * (number of listed blocks), block ids in [0, ceil(n_keys/128)).
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const float* weights, const void* keys_bf16,
+                                          int32_t n_keys, const int32_t* block_list,
+                                          int64_t block_list_stride, const int32_t* row_cols,
+                                          const int32_t* pos_lo, const int32_t* pos_hi, int32_t n_rows,
+                                          int32_t max_cols, float out_scale, float* logits,
+                                          int64_t logits_stride, int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200DSA_H_ */

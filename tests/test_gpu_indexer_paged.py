@@ -1,0 +1,90 @@
+"""tcgen05 paged FP8 indexer and bf16 block-list indexer against the oracle."""
+import pytest
+import torch
+
+from oracle import dsa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+FP8_RTOL = 1e-2   # stated tolerance for FP8 scores (relative, see oracle.rel_err)
+BF16_RTOL = 2e-3  # stated tolerance for bf16 scores
+
+
+def make_paged_case(seed, ctxs, P, extra_pages=3):
+    g = torch.Generator().manual_seed(seed)
+    ks = [torch.randn(c, 128, generator=g) for c in ctxs]
+    qs = [O.quant_fp8_rows(k) for k in ks]
+    n_pages = sum((c + P - 1) // P for c in ctxs) + extra_pages
+    cache, table = O.pack_paged_fp8_cache([a for a, _ in qs], [b for _, b in qs], P, n_pages, g)
+    B = len(ctxs)
+    q = torch.randn(B, 64, 128, generator=g)
+    w = torch.randn(B, 64, generator=g) / 8
+    q_fp8, wf = O.quant_q_fold_weights(q, w, 128 ** -0.5)
+    return q_fp8, wf, cache, table, torch.tensor(ctxs, dtype=torch.int32)
+
+
+@pytest.mark.parametrize("P", [64, 32, 128])
+@pytest.mark.parametrize("ctxs", [[130, 64, 1, 257, 4096], [8192, 5000, 12345]])
+def test_paged_fp8_logits(ctxs, P):
+    from transarch_b200 import _lib, kernels as K
+    q_fp8, wf, cache, table, lens = make_paged_case(len(ctxs) * 7 + P, ctxs, P)
+    max_cols = table.shape[1] * P
+    ref = O.paged_indexer_logits(q_fp8.float(), cache, wf, lens, table, P, max_cols, 1.0)
+    out = K.indexer_paged_fp8_logits(q_fp8.cuda(), wf.cuda(), cache.cuda(), P, lens.cuda(), table.cuda())
+    assert _lib.read_status(out.device) == 0
+    out = out.cpu()
+    assert torch.equal(torch.isfinite(out), torch.isfinite(ref))
+    # fp8 x fp8 products are exact in fp32; only the summation order differs
+    assert O.rel_err(out, ref) < 1e-4
+    assert O.rel_err(out, ref) < FP8_RTOL
+
+
+def test_paged_fp8_zero_context_and_next_n():
+    from transarch_b200 import _lib, kernels as K
+    P = 64
+    q_fp8, wf, cache, table, lens = make_paged_case(99, [300, 200], P)
+    # next_n = 2: rows (b, n) share request b's table; draft token n sees ctx-1+n keys
+    q2 = q_fp8.repeat_interleave(2, 0).contiguous()
+    w2 = wf.repeat_interleave(2, 0).contiguous()
+    lens2 = torch.tensor([299, 300, 0, 200], dtype=torch.int32)
+    out = K.indexer_paged_fp8_logits(q2.cuda(), w2.cuda(), cache.cuda(), P, lens2.cuda(), table.cuda(),
+                                     next_n=2).cpu()
+    ref = O.paged_indexer_logits(q_fp8.float(), cache, wf, lens, table, P, out.shape[1], 1.0)
+    assert O.rel_err(out[1], ref[0]) < 1e-4 and O.rel_err(out[3], ref[1]) < 1e-4
+    assert torch.isinf(out[0, 299:]).all() and O.rel_err(out[0, :299], ref[0, :299]) < 1e-4
+    assert torch.isinf(out[2]).all()
+    assert _lib.read_status(torch.device("cuda", 0)) == 0
+
+
+def test_blocklist_bf16_logits():
+    from transarch_b200 import _lib, kernels as K
+    g = torch.Generator().manual_seed(8)
+    T, S, m = 9, 128 * 37 + 50, 12
+    q = torch.randn(T, 64, 128, generator=g).bfloat16()
+    k = torch.randn(S, 128, generator=g).bfloat16()
+    w = torch.randn(T, 64, generator=g) / 8
+    nb = (S + 127) // 128
+    lists = torch.stack([torch.randperm(nb, generator=g)[:m] for _ in range(T)]).to(torch.int32)
+    nblk = torch.randint(1, m + 1, (T,), generator=g)
+    nblk[0] = m
+    lists[0, 3] = nb - 1                       # tail block: rows beyond S must come out masked
+    for t in range(T):
+        lists[t, nblk[t]:] = -1
+    row_cols = (nblk * 128).to(torch.int32)
+    ke = torch.randint(S // 2, S + 1, (T,), generator=g, dtype=torch.int32)
+    ke[0] = S
+    ks = torch.randint(0, S // 4, (T,), generator=g, dtype=torch.int32)
+    out = K.indexer_blocklist_bf16_logits(q.cuda(), w.cuda(), k.cuda(), lists.cuda(), row_cols.cuda(),
+                                          pos_lo=ks.cuda(), pos_hi=ke.cuda(), out_scale=128 ** -0.5)
+    assert _lib.read_status(out.device) == 0
+    out = out.cpu()
+    full = O.indexer_scores(q, k, w, 128 ** -0.5)
+    ref = torch.full_like(out, float("-inf"))
+    for t in range(T):
+        for j in range(int(nblk[t])):
+            b = int(lists[t, j])
+            pos = torch.arange(b * 128, (b + 1) * 128)
+            ok = (pos >= ks[t]) & (pos < ke[t]) & (pos < S)
+            ref[t, j * 128:(j + 1) * 128][ok] = full[t, pos[ok]]
+    assert torch.equal(torch.isfinite(out), torch.isfinite(ref))
+    assert O.rel_err(out, ref) < BF16_RTOL

@@ -1,0 +1,123 @@
+"""Top-k kernel against torch.topk / the oracle.  Bit-exact as sets; with distinct scores
+also as ordered lists."""
+import pytest
+import torch
+
+from oracle import dsa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref_sets(scores_cpu, k, lo=None, hi=None):
+    """Oracle top-k made tie-deterministic: descending score, equal scores by ascending
+    position (a stable sort), -1 where the pick is not finite."""
+    n_rows, n_cols = scores_cpu.shape
+    lo = torch.zeros(n_rows, dtype=torch.int64) if lo is None else lo.long()
+    hi = torch.full((n_rows,), n_cols, dtype=torch.int64) if hi is None else hi.long()
+    masked = O.mask_interval(scores_cpu, lo, hi)
+    vals, order = torch.sort(masked, dim=1, descending=True, stable=True)
+    k_eff = min(k, n_cols)
+    out = torch.full((n_rows, k), -1, dtype=torch.int32)
+    out[:, :k_eff] = torch.where(torch.isfinite(vals[:, :k_eff]), order[:, :k_eff].to(torch.int32),
+                                 torch.full((n_rows, k_eff), -1, dtype=torch.int32))
+    # same set as the reference's torch.topk (ties aside)
+    assert O.set_recall(out, O.topk_rows(masked, k)) > 0.9999
+    return out
+
+
+@pytest.mark.parametrize("n_rows,n_cols,k", [(7, 100, 16), (5, 4096, 2048), (3, 8192, 2048),
+                                            (4, 8193, 2048), (2, 131072, 2048), (3, 40000, 512),
+                                            (2, 65536, 8192), (9, 33, 64), (1, 1, 1)])
+def test_topk_matches_torch(n_rows, n_cols, k):
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(n_cols + k)
+    s = torch.randn(n_rows, n_cols, generator=g)
+    ref = _ref_sets(s, k)
+    idx, val = K.topk_select(s.cuda(), k, return_values=True)
+    idx = idx.cpu(); val = val.cpu()
+    assert torch.equal(idx, ref)         # randn fp32: distinct values -> same order too
+    k_eff = min(k, n_cols)
+    assert torch.equal(val[:, :k_eff], torch.gather(s, 1, ref[:, :k_eff].long()))
+    assert (idx[:, k_eff:] == -1).all()
+
+
+def test_topk_ranges_ragged_and_empty():
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(3)
+    n_rows, n_cols, k = 12, 20000, 2048
+    s = torch.randn(n_rows, n_cols, generator=g)
+    lo = torch.randint(0, 5000, (n_rows,), generator=g, dtype=torch.int32)
+    hi = torch.randint(5000, n_cols + 1, (n_rows,), generator=g, dtype=torch.int32)
+    hi[0] = lo[0]                      # empty row
+    hi[1] = lo[1] + 5                  # fewer than k
+    hi[2] = lo[2] + 2048               # exactly k
+    ref = _ref_sets(s, k, lo, hi)
+    idx = K.topk_select(s.cuda(), k, col_begin=lo.cuda(), col_end=hi.cuda()).cpu()
+    assert torch.equal(idx, ref)
+    assert (idx[0] == -1).all() and (idx[1, 5:] == -1).all() and (idx[2] >= 0).all()
+
+
+def test_topk_masked_entries_and_inf():
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(4)
+    s = torch.randn(6, 8192, generator=g)
+    s[:, ::3] = float("-inf")
+    s[0, 5] = float("nan")
+    s[1, 7] = float("inf")
+    idx = K.topk_select(s.cuda(), 4096).cpu()
+    for r in range(6):
+        row = s[r].clone()
+        row[torch.isnan(row) | torch.isinf(row)] = float("-inf")
+        n_valid = int(torch.isfinite(row).sum())
+        exp = torch.sort(row, descending=True, stable=True).indices[:min(4096, n_valid)]
+        assert torch.equal(idx[r, :exp.numel()].long(), exp)
+        assert (idx[r, exp.numel():] == -1).all()
+    # +inf kept on request, and it sorts first
+    idx2 = K.topk_select(s.cuda(), 16, keep_pos_inf=True).cpu()
+    assert idx2[1, 0] == 7
+
+
+def test_topk_massive_ties_take_lowest_positions():
+    from transarch_b200 import kernels as K
+    # all equal: must select positions 0..k-1 (fallback radix over position bits)
+    s = torch.zeros(2, 50000)
+    idx = K.topk_select(s.cuda(), 2048).cpu()
+    assert torch.equal(idx[0], torch.arange(2048, dtype=torch.int32))
+    # two-valued: all the 1.0s (sparse) then the lowest-position 0.0s
+    s = torch.zeros(1, 30000)
+    ones = torch.arange(0, 30000, 37)
+    s[0, ones] = 1.0
+    idx = K.topk_select(s.cuda(), 2048).cpu()[0]
+    n1 = ones.numel()
+    assert torch.equal(idx[:n1].long(), ones)
+    rest = [i for i in range(3000) if i % 37 != 0][: 2048 - n1]
+    assert idx[n1:].tolist() == rest
+
+
+def test_topk_position_maps():
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(5)
+    n_rows, nblk, P, k = 5, 6, 128, 200
+    s = torch.randn(n_rows, nblk * P, generator=g)
+    table = torch.stack([torch.randperm(40, generator=g)[:nblk] for _ in range(n_rows)]).to(torch.int32)
+    off = torch.tensor([0, -3, 10, 0, 7], dtype=torch.int32)
+    idx = K.topk_select(s.cuda(), k, page_table=table.cuda(), page_size=P, row_pos_offset=off.cuda()).cpu()
+    cols = torch.topk(s, k, dim=1).indices
+    exp = torch.gather(table.long(), 1, cols // P) * P + cols % P + off.view(-1, 1)
+    assert torch.equal(idx.long(), exp)
+    pm = torch.randint(0, 1 << 20, s.shape, generator=g, dtype=torch.int32)
+    idx = K.topk_select(s.cuda(), k, pos_map=pm.cuda()).cpu()
+    assert torch.equal(idx, torch.gather(pm, 1, cols))
+
+
+def test_topk_deterministic_twice():
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(6)
+    s = (torch.randn(8, 100000, generator=g) * 4).round() / 4     # many ties
+    a = K.topk_select(s.cuda(), 2048)
+    b = K.topk_select(s.cuda(), 2048)
+    assert torch.equal(a, b)
+    # set check against a stable CPU sort: descending value, ascending position
+    for r in range(8):
+        order = sorted(range(100000), key=lambda i: (-float(s[r, i]), i))[:2048]
+        assert a[r].cpu().tolist() == order

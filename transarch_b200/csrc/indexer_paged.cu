@@ -1,0 +1,508 @@
+// Lightning-indexer token logits over a block table, one tcgen05 contraction per 128 keys.
+//
+//   logit[r, c] = out_scale * key_scale(c) * sum_h w[r,h] * relu( <q[r,h,:], key(c)> )
+//
+// Two key sources share the kernel:
+//   FP8 paged cache (decode): pages of P tokens, P*128 e4m3 bytes followed by P fp32 scales;
+//     row r walks its block-table row, column c is the logical key index.
+//   bf16 flat keys addressed by a per-row list of 128-key blocks (HISA stage 2): column c is
+//     (list slot, offset); its position is list[slot]*128 + offset, masked to [pos_lo, pos_hi).
+//
+// Orientation: the 128 keys of a tile are the UMMA M dimension (one TMEM lane per key), the
+// 64 index heads are N, d=128 is K.  Per-head scores exist only in TMEM and registers: each
+// epilogue thread owns one key and reduces the 64 heads locally.
+//
+// Roles (192 threads): warp 0 lane 0 issues TMA loads into an mbarrier ring, warp 1 lane 0
+// issues the MMAs into a double-buffered TMEM accumulator, warps 2-5 run the epilogue.  The
+// grid is persistent: the list of all (row, tile) pairs is split evenly over the CTAs, so
+// ragged context lengths stay balanced.  Every wait is bounded; on a timeout the CTA raises
+// the status word, drains its loads, frees TMEM and returns.
+#include "b200dsa_common.cuh"
+
+namespace b200dsa {
+
+constexpr int kTileKeys = 128;
+constexpr int kHeads = 64;
+constexpr int kDim = 128;
+constexpr int kMaxRows = 1024;  // rows per launch (host loops beyond that)
+constexpr int kThreads = 192;
+
+template <bool kFp8>
+struct PagedCfg {
+  static constexpr int kElem = kFp8 ? 1 : 2;
+  static constexpr int kStageBytes = kTileKeys * kDim * kElem;  // 16 KB / 32 KB
+  static constexpr int kQBytes = kHeads * kDim * kElem;         // 8 KB / 16 KB
+  static constexpr int kStages = kFp8 ? 8 : 5;
+  static constexpr int kKSteps = kFp8 ? 4 : 8;                  // MMAs per tile (32 B of K each)
+  static constexpr int kSmemBytes = kStages * kStageBytes + 2 * kQBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct PagedIndexerParams {
+  const uint8_t* cache;         // fp8 mode: base of the paged cache (for the scales)
+  int64_t page_bytes;           // fp8 mode: P*(128+4)
+  int32_t page_size;            // fp8 mode: P (32, 64 or 128); bf16 mode: 128
+  int32_t num_pages;            // valid page / block ids are [0, num_pages)
+  const float* weights;         // [n_rows, 64]
+  const int32_t* row_cols;      // [n_rows] number of columns of each row
+  const int32_t* table;         // block table / block list
+  int64_t table_stride;
+  int32_t table_row_div;        // table row of row r is r / table_row_div (next_n > 1 shares tables)
+  const int32_t* pos_lo;        // bf16 mode, nullable: keep only pos_lo[r] <= position < pos_hi[r]
+  const int32_t* pos_hi;
+  int32_t n_rows;
+  float out_scale;
+  float* logits;                // [n_rows, logits_stride]
+  int64_t logits_stride;
+  int32_t logits_cols;          // columns that may be written per row
+  int32_t* status;
+};
+
+template <bool kFp8>
+__global__ void __launch_bounds__(kThreads, 1)
+indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
+                     const PagedIndexerParams p) {
+  using Cfg = PagedCfg<kFp8>;
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ int s_prefix[kMaxRows + 1];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_dyn + (smem_base - smem_u32(smem_dyn));
+  uint8_t* stage_mem = smem_al;
+  uint8_t* q_mem = smem_al + Cfg::kStages * Cfg::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(q_mem + 2 * Cfg::kQBytes);
+  uint64_t* full = bars;                       // [kStages]
+  uint64_t* empty = bars + Cfg::kStages;       // [kStages]
+  uint64_t* q_full = empty + Cfg::kStages;     // [2]
+  uint64_t* q_empty = q_full + 2;              // [2]
+  uint64_t* acc_full = q_empty + 2;            // [2]
+  uint64_t* acc_empty = acc_full + 2;          // [2]
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // tiles per row -> exclusive prefix (rows <= kMaxRows)
+  if (tid == 0) s_abort = 0;
+  for (int r = tid; r < p.n_rows; r += kThreads) {
+    int c = p.row_cols[r];
+    c = max(0, min(c, p.logits_cols));
+    s_prefix[r + 1] = (c + kTileKeys - 1) / kTileKeys;
+  }
+  if (tid == 0) s_prefix[0] = 0;
+  __syncthreads();
+  if (tid == 0) {
+    int acc = 0;
+    for (int r = 0; r < p.n_rows; ++r) {
+      acc += s_prefix[r + 1];
+      s_prefix[r + 1] = acc;
+    }
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_empty[s], 128);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&s_tmem_base, 128);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  const uint32_t tmem_base = s_tmem_base;
+  const int total_tiles = s_prefix[p.n_rows];
+  const int g0 = static_cast<int>((static_cast<int64_t>(total_tiles) * blockIdx.x) / gridDim.x);
+  const int g1 = static_cast<int>((static_cast<int64_t>(total_tiles) * (blockIdx.x + 1)) / gridDim.x);
+  volatile int* abort_flag = &s_abort;
+
+  // first row of this CTA's range
+  int row0 = 0;
+  if (g0 < g1) {
+    int lo = 0, hi = p.n_rows;  // find row with prefix[row] <= g0 < prefix[row+1]
+    while (hi - lo > 1) {
+      int mid = (lo + hi) >> 1;
+      if (s_prefix[mid] <= g0) lo = mid; else hi = mid;
+    }
+    row0 = lo;
+  }
+
+  int issued = 0;  // producer: loads issued (for the drain on abort)
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_k);
+      tma_prefetch_desc(&tmap_q);
+      int row = row0, prev_row = -1;
+      int it = 0, qit = 0;
+      for (int g = g0; g < g1; ++g) {
+        while (g >= s_prefix[row + 1]) ++row;
+        const int t = g - s_prefix[row];
+        if (row != prev_row) {
+          const int qs = qit & 1;
+          if (!mbar_wait(&q_empty[qs], ((qit >> 1) & 1) ^ 1, abort_flag)) break;
+          mbar_arrive_expect_tx(&q_full[qs], Cfg::kQBytes);
+          if constexpr (kFp8) {
+            tma_load_2d(q_mem + qs * Cfg::kQBytes, &tmap_q, &q_full[qs], 0, row * kHeads);
+          } else {
+            tma_load_2d(q_mem + qs * Cfg::kQBytes, &tmap_q, &q_full[qs], 0, row * kHeads);
+            tma_load_2d(q_mem + qs * Cfg::kQBytes + Cfg::kQBytes / 2, &tmap_q, &q_full[qs], 64, row * kHeads);
+          }
+          ++qit;
+          prev_row = row;
+        }
+        const int s = it % Cfg::kStages;
+        if (!mbar_wait(&empty[s], ((it / Cfg::kStages) & 1) ^ 1, abort_flag)) break;
+        uint8_t* dst = stage_mem + s * Cfg::kStageBytes;
+        const int32_t* trow = p.table + static_cast<int64_t>(row / p.table_row_div) * p.table_stride;
+        int cols = max(0, min(p.row_cols[row], p.logits_cols));
+        const int key0 = t * kTileKeys;
+        const int nkeys = min(kTileKeys, cols - key0);
+        if constexpr (kFp8) {
+          const int P = p.page_size;
+          const int npages = (nkeys + P - 1) / P;
+          int pg[4];
+          int nvalid = 0;
+          for (int j = 0; j < npages; ++j) {
+            pg[j] = trow[key0 / P + j];
+            if (pg[j] >= 0 && pg[j] < p.num_pages) ++nvalid; else pg[j] = -1;
+          }
+          mbar_arrive_expect_tx(&full[s], nvalid * P * kDim);
+          for (int j = 0; j < npages; ++j)
+            if (pg[j] >= 0) tma_load_3d(dst + j * P * kDim, &tmap_k, &full[s], 0, 0, pg[j]);
+          if (nvalid != npages) atomicMax(p.status, kDevBadIndex);
+        } else {
+          const int blk = trow[t];
+          if (blk >= 0 && blk < p.num_pages) {
+            mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
+            tma_load_2d(dst, &tmap_k, &full[s], 0, blk * kTileKeys);
+            tma_load_2d(dst + Cfg::kStageBytes / 2, &tmap_k, &full[s], 64, blk * kTileKeys);
+          } else {
+            mbar_arrive_expect_tx(&full[s], 0);
+            atomicMax(p.status, kDevBadIndex);
+          }
+        }
+        ++it;
+      }
+      issued = it;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = kFp8 ? make_idesc(kFmtE4M3, kFmtE4M3, 128, kHeads)
+                                      : make_idesc(kFmtBF16, kFmtBF16, 128, kHeads);
+      int row = row0, prev_row = -1;
+      int it = 0, qit = 0, ait = 0, qs = 0;
+      for (int g = g0; g < g1; ++g) {
+        while (g >= s_prefix[row + 1]) ++row;
+        if (row != prev_row) {
+          if (prev_row >= 0) tc_commit(&q_empty[qs]);  // q slot free once the old row's MMAs retire
+          qs = qit & 1;
+          if (!mbar_wait(&q_full[qs], (qit >> 1) & 1, abort_flag)) break;
+          ++qit;
+          prev_row = row;
+        }
+        const int s = it % Cfg::kStages;
+        if (!mbar_wait(&full[s], (it / Cfg::kStages) & 1, abort_flag)) break;
+        const int as = ait & 1;
+        if (!mbar_wait(&acc_empty[as], ((ait >> 1) & 1) ^ 1, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
+        const uint32_t b_addr = smem_base + Cfg::kStages * Cfg::kStageBytes + qs * Cfg::kQBytes;
+        const uint32_t d_tmem = tmem_base + as * kHeads;
+#pragma unroll
+        for (int kk = 0; kk < Cfg::kKSteps; ++kk) {
+          uint32_t a_off, b_off;
+          if constexpr (kFp8) {
+            a_off = kk * 32;
+            b_off = kk * 32;
+          } else {
+            a_off = (kk >> 2) * (Cfg::kStageBytes / 2) + (kk & 3) * 32;
+            b_off = (kk >> 2) * (Cfg::kQBytes / 2) + (kk & 3) * 32;
+          }
+          const uint64_t a_desc = make_desc_k_sw128(a_addr + a_off);
+          const uint64_t b_desc = make_desc_k_sw128(b_addr + b_off);
+          if constexpr (kFp8) mma_f8f6f4_ss(d_tmem, a_desc, b_desc, idesc, kk > 0);
+          else mma_f16_ss(d_tmem, a_desc, b_desc, idesc, kk > 0);
+        }
+        tc_commit(&empty[s]);
+        tc_commit(&acc_full[as]);
+        ++it;
+        ++ait;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int lane_base = (warp & 3) * 32;  // TMEM lanes this warp may read
+    float w[kHeads];
+    int row = row0, prev_row = -1;
+    int ait = 0;
+    int cols = 0, lo = 0, hi = 0x7fffffff;
+    const int32_t* trow = p.table;
+    for (int g = g0; g < g1; ++g) {
+      while (g >= s_prefix[row + 1]) ++row;
+      const int t = g - s_prefix[row];
+      if (row != prev_row) {
+        const float4* wr = reinterpret_cast<const float4*>(p.weights + static_cast<int64_t>(row) * kHeads);
+#pragma unroll
+        for (int j = 0; j < kHeads / 4; ++j) {
+          float4 x = __ldg(wr + j);
+          w[4 * j + 0] = x.x; w[4 * j + 1] = x.y; w[4 * j + 2] = x.z; w[4 * j + 3] = x.w;
+        }
+        cols = max(0, min(p.row_cols[row], p.logits_cols));
+        trow = p.table + static_cast<int64_t>(row / p.table_row_div) * p.table_stride;
+        if (p.pos_lo) { lo = p.pos_lo[row]; hi = p.pos_hi[row]; }
+        prev_row = row;
+      }
+      const int key = t * kTileKeys + lane_base + lane;  // column of this thread
+      // scale / mask inputs fetched before the accumulator is ready
+      float kscale = 1.0f;
+      bool keep = key < cols;
+      if constexpr (kFp8) {
+        if (keep) {
+          const int P = p.page_size;
+          const int pg = trow[key / P];
+          if (pg >= 0 && pg < p.num_pages) {
+            const float* sc = reinterpret_cast<const float*>(p.cache + static_cast<int64_t>(pg) * p.page_bytes +
+                                                             static_cast<int64_t>(P) * kDim);
+            kscale = __ldg(sc + (key % P));
+          } else {
+            keep = false;
+          }
+        }
+      } else {
+        if (keep) {
+          const int blk = trow[t];
+          const int pos = blk * kTileKeys + lane_base + lane;
+          keep = (blk >= 0 && blk < p.num_pages) && pos >= lo && pos < hi;
+        }
+      }
+      const int as = ait & 1;
+      const bool ready = mbar_wait(&acc_full[as], (ait >> 1) & 1, abort_flag);
+      if (!__all_sync(0xffffffffu, ready)) break;  // warp-uniform: tcgen05.ld needs the whole warp
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + as * kHeads;
+      uint32_t v0[32], v1[32];
+      tmem_ld_32x32(taddr, v0);
+      tmem_ld_32x32(taddr + 32, v1);
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&acc_empty[as]);
+      float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        acc0 = fmaf(fmaxf(__uint_as_float(v0[j]), 0.f), w[j], acc0);
+        acc1 = fmaf(fmaxf(__uint_as_float(v1[j]), 0.f), w[32 + j], acc1);
+      }
+      const int tile_cols = min(p.logits_cols, (t + 1) * kTileKeys);
+      if (key < tile_cols) {
+        const float out = keep ? (acc0 + acc1) * kscale * p.out_scale : -INFINITY;
+        p.logits[static_cast<int64_t>(row) * p.logits_stride + key] = out;
+      }
+      ++ait;
+    }
+  }
+
+  // ---------------------------------------------------------------------- common tail
+  if (s_abort && warp == 0 && lane == 0) {
+    // give loads already in flight a bounded chance to land before shared memory is released
+    const int n = min(issued, Cfg::kStages);
+    for (int j = 0; j < n; ++j) {
+      const int it = issued - 1 - j;
+      const int s = it % Cfg::kStages;
+      const uint64_t t0 = global_timer_ns();
+      while (!mbar_test(&full[s], (it / Cfg::kStages) & 1)) {
+        if (global_timer_ns() - t0 > 2000000ull) break;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, 128);
+  if (tid == 0 && s_abort) atomicMax(p.status, kDevWaitTimeout);
+}
+
+void set_last_error(const char* msg);
+
+static int encode_map(CUtensorMap* m, CUtensorMapDataType dt, uint32_t rank, const void* base, const cuuint64_t* dims,
+                      const cuuint64_t* strides, const cuuint32_t* box) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (!enc) return B200DSA_ECUDA;
+  cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
+  CUresult r = enc(m, dt, rank, const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled rejected the tensor layout");
+    return B200DSA_ECUDA;
+  }
+  return B200DSA_OK;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n) return n;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  if (n <= 0) n = 148;
+  return n;
+}
+
+template <bool kFp8>
+static int launch_paged(const CUtensorMap& mk, const CUtensorMap& mq, PagedIndexerParams p, int64_t est_tiles,
+                        cudaStream_t stream) {
+  using Cfg = PagedCfg<kFp8>;
+  cudaError_t e = cudaFuncSetAttribute(indexer_paged_kernel<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg::kSmemBytes);
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  int grid = sm_count();
+  if (est_tiles > 0 && est_tiles < grid) grid = static_cast<int>(est_tiles);
+  indexer_paged_kernel<kFp8><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(mk, mq, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  return B200DSA_OK;
+}
+
+}  // namespace b200dsa
+
+using namespace b200dsa;
+
+extern "C" int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* weights, const void* cache,
+                                                int32_t num_pages, int32_t page_size, const int32_t* context_lens,
+                                                const int32_t* block_table, int64_t block_table_stride,
+                                                int32_t n_rows, int32_t next_n, int32_t max_cols, float out_scale,
+                                                float* logits, int64_t logits_stride, int32_t* status, void* stream) {
+  if (n_rows == 0) return B200DSA_OK;
+  if (!q_fp8 || !weights || !cache || !context_lens || !block_table || !logits || !status || n_rows < 0 ||
+      next_n < 1 || num_pages < 1 || max_cols < 0 || logits_stride < max_cols) {
+    set_last_error("b200dsa_indexer_paged_fp8_logits: bad argument");
+    return B200DSA_EINVAL;
+  }
+  if (page_size != 32 && page_size != 64 && page_size != 128) {
+    set_last_error("b200dsa_indexer_paged_fp8_logits: page_size must be 32, 64 or 128");
+    return B200DSA_EUNSUPPORTED;
+  }
+  if ((reinterpret_cast<uintptr_t>(q_fp8) & 15) || (reinterpret_cast<uintptr_t>(cache) & 15) ||
+      (reinterpret_cast<uintptr_t>(weights) & 15)) {
+    set_last_error("b200dsa_indexer_paged_fp8_logits: q, weights and cache must be 16-byte aligned");
+    return B200DSA_EALIGN;
+  }
+  const int64_t page_bytes = static_cast<int64_t>(page_size) * (kDim + 4);
+  CUtensorMap mk, mq;
+  {
+    cuuint64_t dims[3] = {kDim, static_cast<cuuint64_t>(page_size), static_cast<cuuint64_t>(num_pages)};
+    cuuint64_t strides[2] = {kDim, static_cast<cuuint64_t>(page_bytes)};
+    cuuint32_t box[3] = {kDim, static_cast<cuuint32_t>(page_size), 1};
+    int rc = encode_map(&mk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, cache, dims, strides, box);
+    if (rc) return rc;
+  }
+  for (int r0 = 0; r0 < n_rows; r0 += kMaxRows) {
+    const int nr = n_rows - r0 < kMaxRows ? n_rows - r0 : kMaxRows;
+    // chunk boundaries must not split the next_n rows of one request
+    if (r0 % next_n != 0) {
+      set_last_error("b200dsa_indexer_paged_fp8_logits: next_n must divide 1024 when n_rows > 1024");
+      return B200DSA_EUNSUPPORTED;
+    }
+    const uint8_t* qbase = static_cast<const uint8_t*>(q_fp8) + static_cast<int64_t>(r0) * kHeads * kDim;
+    cuuint64_t dims[2] = {kDim, static_cast<cuuint64_t>(nr) * kHeads};
+    cuuint64_t strides[1] = {kDim};
+    cuuint32_t box[2] = {kDim, kHeads};
+    int rc = encode_map(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, qbase, dims, strides, box);
+    if (rc) return rc;
+    PagedIndexerParams p{};
+    p.cache = static_cast<const uint8_t*>(cache);
+    p.page_bytes = page_bytes;
+    p.page_size = page_size;
+    p.num_pages = num_pages;
+    p.weights = weights + static_cast<int64_t>(r0) * kHeads;
+    p.row_cols = context_lens + r0;
+    p.table = block_table + static_cast<int64_t>(r0 / next_n) * block_table_stride;
+    p.table_stride = block_table_stride;
+    p.table_row_div = next_n;
+    p.pos_lo = nullptr;
+    p.pos_hi = nullptr;
+    p.n_rows = nr;
+    p.out_scale = out_scale;
+    p.logits = logits + static_cast<int64_t>(r0) * logits_stride;
+    p.logits_stride = logits_stride;
+    p.logits_cols = max_cols;
+    p.status = status;
+    rc = launch_paged<true>(mk, mq, p, 0, static_cast<cudaStream_t>(stream));
+    if (rc) return rc;
+  }
+  return B200DSA_OK;
+}
+
+extern "C" int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const float* weights, const void* keys_bf16,
+                                                     int32_t n_keys, const int32_t* block_list,
+                                                     int64_t block_list_stride, const int32_t* row_cols,
+                                                     const int32_t* pos_lo, const int32_t* pos_hi, int32_t n_rows,
+                                                     int32_t max_cols, float out_scale, float* logits,
+                                                     int64_t logits_stride, int32_t* status, void* stream) {
+  if (n_rows == 0) return B200DSA_OK;
+  if (!q_bf16 || !weights || !keys_bf16 || !block_list || !row_cols || !logits || !status || n_rows < 0 ||
+      n_keys < 1 || max_cols < 0 || logits_stride < max_cols || ((pos_lo == nullptr) != (pos_hi == nullptr))) {
+    set_last_error("b200dsa_indexer_blocklist_bf16_logits: bad argument");
+    return B200DSA_EINVAL;
+  }
+  if ((reinterpret_cast<uintptr_t>(q_bf16) & 15) || (reinterpret_cast<uintptr_t>(keys_bf16) & 15) ||
+      (reinterpret_cast<uintptr_t>(weights) & 15)) {
+    set_last_error("b200dsa_indexer_blocklist_bf16_logits: q, weights and keys must be 16-byte aligned");
+    return B200DSA_EALIGN;
+  }
+  CUtensorMap mk, mq;
+  {
+    cuuint64_t dims[2] = {kDim, static_cast<cuuint64_t>(n_keys)};
+    cuuint64_t strides[1] = {kDim * 2};
+    cuuint32_t box[2] = {64, kTileKeys};
+    int rc = encode_map(&mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, keys_bf16, dims, strides, box);
+    if (rc) return rc;
+  }
+  const int n_blocks = (n_keys + kTileKeys - 1) / kTileKeys;
+  for (int r0 = 0; r0 < n_rows; r0 += kMaxRows) {
+    const int nr = n_rows - r0 < kMaxRows ? n_rows - r0 : kMaxRows;
+    const uint8_t* qbase = static_cast<const uint8_t*>(q_bf16) + static_cast<int64_t>(r0) * kHeads * kDim * 2;
+    cuuint64_t dims[2] = {kDim, static_cast<cuuint64_t>(nr) * kHeads};
+    cuuint64_t strides[1] = {kDim * 2};
+    cuuint32_t box[2] = {64, kHeads};
+    int rc = encode_map(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, qbase, dims, strides, box);
+    if (rc) return rc;
+    PagedIndexerParams p{};
+    p.cache = nullptr;
+    p.page_bytes = 0;
+    p.page_size = kTileKeys;
+    p.num_pages = n_blocks;
+    p.weights = weights + static_cast<int64_t>(r0) * kHeads;
+    p.row_cols = row_cols + r0;
+    p.table = block_list + static_cast<int64_t>(r0) * block_list_stride;
+    p.table_stride = block_list_stride;
+    p.table_row_div = 1;
+    p.pos_lo = pos_lo ? pos_lo + r0 : nullptr;
+    p.pos_hi = pos_hi ? pos_hi + r0 : nullptr;
+    p.n_rows = nr;
+    p.out_scale = out_scale;
+    p.logits = logits + static_cast<int64_t>(r0) * logits_stride;
+    p.logits_stride = logits_stride;
+    p.logits_cols = max_cols;
+    p.status = status;
+    rc = launch_paged<false>(mk, mq, p, 0, static_cast<cudaStream_t>(stream));
+    if (rc) return rc;
+  }
+  return B200DSA_OK;
+}

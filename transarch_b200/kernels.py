@@ -1,0 +1,115 @@
+"""Thin tensor-level wrappers over the C ABI (one function per entry point).
+
+They validate dtype / device / contiguity, allocate outputs with torch and launch on the
+current stream.  Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import check, ptr, require_cuda, status_word, stream_ptr
+
+NEG_INF = float("-inf")
+
+
+def _i32(t: Optional[torch.Tensor], name: str) -> Optional[torch.Tensor]:
+    if t is None:
+        return None
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise _lib.B200DSAError(f"{name} must be a contiguous int32 tensor")
+    return t
+
+
+def topk_select(scores: torch.Tensor, k: int, *, col_begin: Optional[torch.Tensor] = None,
+                col_end: Optional[torch.Tensor] = None, keep_pos_inf: bool = False,
+                pos_map: Optional[torch.Tensor] = None, page_table: Optional[torch.Tensor] = None,
+                page_size: int = 0, row_pos_offset: Optional[torch.Tensor] = None,
+                return_values: bool = False, out: Optional[torch.Tensor] = None):
+    """Row-wise top-k positions (int32, descending score, -1 padded); see b200dsa_topk_select."""
+    require_cuda(scores, col_begin, col_end, pos_map, page_table, row_pos_offset)
+    if scores.dtype != torch.float32 or scores.dim() != 2 or scores.stride(1) != 1:
+        raise _lib.B200DSAError("scores must be a 2-D fp32 tensor with unit column stride")
+    n_rows, n_cols = scores.shape
+    if out is None:
+        out = torch.empty(n_rows, k, dtype=torch.int32, device=scores.device)
+    elif out.dtype != torch.int32 or out.stride(1) != 1 or out.shape[0] < n_rows or out.shape[1] < k:
+        raise _lib.B200DSAError("out must be int32 [>=n_rows, >=k] with unit column stride")
+    vals = torch.empty(n_rows, out.stride(0), dtype=torch.float32, device=scores.device) if return_values else None
+    lib = _lib.load()
+    rc = lib.b200dsa_topk_select(
+        ptr(scores), scores.stride(0), n_rows, n_cols,
+        ptr(_i32(col_begin, "col_begin")), ptr(_i32(col_end, "col_end")), k, int(keep_pos_inf),
+        ptr(_i32(pos_map, "pos_map")), pos_map.stride(0) if pos_map is not None else 0,
+        ptr(_i32(page_table, "page_table")), page_table.stride(0) if page_table is not None else 0, page_size,
+        ptr(_i32(row_pos_offset, "row_pos_offset")),
+        ptr(out), ptr(vals), out.stride(0), stream_ptr())
+    check(rc, "b200dsa_topk_select")
+    if return_values:
+        return out[:n_rows, :k], vals[:, :k]
+    return out[:n_rows, :k]
+
+
+def indexer_paged_fp8_logits(q_fp8: torch.Tensor, weights: torch.Tensor, cache: torch.Tensor, page_size: int,
+                             context_lens: torch.Tensor, block_table: torch.Tensor, *, next_n: int = 1,
+                             max_cols: Optional[int] = None, out_scale: float = 1.0,
+                             out: Optional[torch.Tensor] = None, fill: bool = True) -> torch.Tensor:
+    """Decode logits [n_rows, max_cols] fp32 over the paged FP8 cache; see
+    b200dsa_indexer_paged_fp8_logits.  fill=True pre-fills a fresh output with -inf so that
+    columns beyond each context are -inf as in the reference; pass out= to reuse a buffer."""
+    require_cuda(q_fp8, weights, cache, context_lens, block_table)
+    if q_fp8.dtype != torch.float8_e4m3fn or not q_fp8.is_contiguous() or q_fp8.shape[-2:] != (64, 128):
+        raise _lib.B200DSAError("q_fp8 must be contiguous float8_e4m3fn [..., 64, 128]")
+    n_rows = q_fp8.numel() // (64 * 128)
+    if weights.dtype != torch.float32 or not weights.is_contiguous() or weights.numel() != n_rows * 64:
+        raise _lib.B200DSAError("weights must be contiguous fp32 [n_rows, 64]")
+    if cache.dtype != torch.uint8 or not cache.is_contiguous():
+        raise _lib.B200DSAError("cache must be a contiguous uint8 tensor")
+    page_bytes = page_size * 132
+    if cache.numel() % page_bytes:
+        raise _lib.B200DSAError("cache size is not a multiple of page_size*(128+4)")
+    num_pages = cache.numel() // page_bytes
+    _i32(context_lens, "context_lens"); _i32(block_table, "block_table")
+    if context_lens.numel() != n_rows:
+        raise _lib.B200DSAError("context_lens must have one entry per row")
+    if max_cols is None:
+        max_cols = block_table.shape[-1] * page_size
+    if out is None:
+        out = (torch.full if fill else torch.empty)(
+            (n_rows, max_cols), *((NEG_INF,) if fill else ()), dtype=torch.float32, device=q_fp8.device)
+    lib = _lib.load()
+    rc = lib.b200dsa_indexer_paged_fp8_logits(
+        ptr(q_fp8), ptr(weights), ptr(cache), num_pages, page_size, ptr(context_lens),
+        ptr(block_table), block_table.stride(0), n_rows, next_n, max_cols, out_scale,
+        ptr(out), out.stride(0), ptr(status_word(q_fp8.device)), stream_ptr())
+    check(rc, "b200dsa_indexer_paged_fp8_logits")
+    return out
+
+
+def indexer_blocklist_bf16_logits(q: torch.Tensor, weights: torch.Tensor, keys: torch.Tensor,
+                                  block_list: torch.Tensor, row_cols: torch.Tensor, *,
+                                  pos_lo: Optional[torch.Tensor] = None, pos_hi: Optional[torch.Tensor] = None,
+                                  out_scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Token logits [n_rows, 128*list_len] inside per-row lists of 128-key blocks; see
+    b200dsa_indexer_blocklist_bf16_logits."""
+    require_cuda(q, weights, keys, block_list, row_cols, pos_lo, pos_hi)
+    if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.shape[-2:] != (64, 128):
+        raise _lib.B200DSAError("q must be contiguous bf16 [n_rows, 64, 128]")
+    if keys.dtype != torch.bfloat16 or not keys.is_contiguous() or keys.shape[-1] != 128:
+        raise _lib.B200DSAError("keys must be contiguous bf16 [n_keys, 128]")
+    n_rows = q.shape[0]
+    if weights.dtype != torch.float32 or not weights.is_contiguous() or weights.numel() != n_rows * 64:
+        raise _lib.B200DSAError("weights must be contiguous fp32 [n_rows, 64]")
+    _i32(block_list, "block_list"); _i32(row_cols, "row_cols")
+    max_cols = block_list.shape[1] * 128
+    if out is None:
+        out = torch.full((n_rows, max_cols), NEG_INF, dtype=torch.float32, device=q.device)
+    lib = _lib.load()
+    rc = lib.b200dsa_indexer_blocklist_bf16_logits(
+        ptr(q), ptr(weights), ptr(keys), keys.shape[0], ptr(block_list), block_list.stride(0),
+        ptr(row_cols), ptr(_i32(pos_lo, "pos_lo")), ptr(_i32(pos_hi, "pos_hi")), n_rows, max_cols, out_scale,
+        ptr(out), out.stride(0), ptr(status_word(q.device)), stream_ptr())
+    check(rc, "b200dsa_indexer_blocklist_bf16_logits")
+    return out
