@@ -41,8 +41,10 @@ const char* b200dsa_last_error(void);
  * Row r looks at columns [col_begin[r], col_end[r]) (defaults 0 and n_cols; clamped to
  * [0, n_cols]).  -inf and NaN are never selected; +inf only when keep_pos_inf != 0.  The k
  * largest remaining scores are chosen; equal scores are resolved towards the lowest
- * output position, so the selected SET is deterministic.  Output rows are written in
- * descending score order (ties: ascending position) and padded with -1 (values: -inf).
+ * output position, so the selected SET is deterministic.  With sorted != 0 a row is written
+ * in descending score order (ties: ascending position), as torch.topk(sorted=True) would;
+ * with sorted == 0 the winners come in no particular order (torch.topk(sorted=False), which
+ * the reference uses at misa_ops.py:402,710).  Rows are padded with -1 (values: -inf).
  *
  * Output position of column c in row r:
  *   pos_map   != NULL : pos_map[r*pos_map_stride + c]
@@ -54,7 +56,7 @@ const char* b200dsa_last_error(void);
  * ------------------------------------------------------------------------------------- */
 int b200dsa_topk_select(const float* scores, int64_t row_stride, int32_t n_rows, int32_t n_cols,
                         const int32_t* col_begin, const int32_t* col_end, int32_t k,
-                        int32_t keep_pos_inf,
+                        int32_t keep_pos_inf, int32_t sorted,
                         const int32_t* pos_map, int64_t pos_map_stride,
                         const int32_t* page_table, int64_t page_table_stride, int32_t page_size,
                         const int32_t* row_pos_offset,

@@ -121,3 +121,13 @@ def test_topk_deterministic_twice():
     for r in range(8):
         order = sorted(range(100000), key=lambda i: (-float(s[r, i]), i))[:2048]
         assert a[r].cpu().tolist() == order
+
+
+@pytest.mark.parametrize("n_cols,k", [(131072, 2048), (5000, 2048), (70000, 8192)])
+def test_topk_unsorted_same_set(n_cols, k):
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(n_cols)
+    s = torch.randn(3, n_cols, generator=g)
+    ref = _ref_sets(s, k)
+    idx = K.topk_select(s.cuda(), k, sorted=False).cpu()
+    assert torch.equal(torch.sort(idx, dim=1).values, torch.sort(ref, dim=1).values)

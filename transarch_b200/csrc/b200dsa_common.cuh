@@ -55,20 +55,22 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Wait limit for every spin in this library: about one second of wall time.
-constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
+// Wait limit for every spin in this library: 2^31 SM clock cycles, about one second.
+constexpr long long kWaitLimitCycles = 1ll << 31;
 
 // Bounded wait.  Returns false when it gave up or when another role already raised
 // *abort_flag (a shared-memory int); in both cases the caller unwinds to the common tail.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_test(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  long long t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if (mbar_test(bar, parity)) return true;
-    if ((++spins & 0x3ff) == 0) {
+    if ((++spins & 0xff) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitCycles) {
         *abort_flag = 1;
         return false;
       }
@@ -93,6 +95,14 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uin
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
+}
+
+// Untiled bulk copy global -> shared; both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 
 // ---------------------------------------------------------------------------------------

@@ -34,7 +34,13 @@ struct PagedCfg {
   static constexpr int kQBytes = kHeads * kDim * kElem;         // 8 KB / 16 KB
   static constexpr int kStages = kFp8 ? 8 : 5;
   static constexpr int kKSteps = kFp8 ? 4 : 8;                  // MMAs per tile (32 B of K each)
-  static constexpr int kSmemBytes = kStages * kStageBytes + 2 * kQBytes + 1024 /*align*/ + 256 /*barriers*/;
+  // Per-tile key scales travel through their own ring.  A slot is reused kScaleSlots tiles
+  // later; by then the MMA of tile (it + 2) has retired, which needed the epilogue of tile
+  // `it` to release its accumulator, and the epilogue reads the scale before that release.
+  static constexpr int kScaleSlots = kStages + 2;
+  static constexpr int kScaleBytes = kFp8 ? kScaleSlots * kTileKeys * 4 : 0;
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + 2 * kQBytes + kScaleBytes + 1024 /*align*/ + 512 /*barriers*/;
 };
 
 struct PagedIndexerParams {
@@ -46,6 +52,7 @@ struct PagedIndexerParams {
   const int32_t* row_cols;      // [n_rows] number of columns of each row
   const int32_t* table;         // block table / block list
   int64_t table_stride;
+  int32_t table_cols;           // entries that may be read per table row
   int32_t table_row_div;        // table row of row r is r / table_row_div (next_n > 1 shares tables)
   const int32_t* pos_lo;        // bf16 mode, nullable: keep only pos_lo[r] <= position < pos_hi[r]
   const int32_t* pos_hi;
@@ -71,13 +78,15 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
   uint8_t* smem_al = smem_dyn + (smem_base - smem_u32(smem_dyn));
   uint8_t* stage_mem = smem_al;
   uint8_t* q_mem = smem_al + Cfg::kStages * Cfg::kStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(q_mem + 2 * Cfg::kQBytes);
+  float* sc_mem = reinterpret_cast<float*>(q_mem + 2 * Cfg::kQBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(q_mem + 2 * Cfg::kQBytes + Cfg::kScaleBytes);
   uint64_t* full = bars;                       // [kStages]
   uint64_t* empty = bars + Cfg::kStages;       // [kStages]
   uint64_t* q_full = empty + Cfg::kStages;     // [2]
   uint64_t* q_empty = q_full + 2;              // [2]
   uint64_t* acc_full = q_empty + 2;            // [2]
   uint64_t* acc_empty = acc_full + 2;          // [2]
+  uint64_t* sc_full = acc_empty + 2;           // [kScaleSlots]
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -108,6 +117,7 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], 128);
     }
+    for (int s = 0; s < Cfg::kScaleSlots; ++s) mbar_init(&sc_full[s], 1);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -139,49 +149,85 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // The whole warp walks the tile list with identical (uniform) values in every lane; the
+    // lanes fetch 32 table entries at a time and one elected lane issues the copies.
+    if (elect_one()) {
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_q);
-      int row = row0, prev_row = -1;
-      int it = 0, qit = 0;
-      for (int g = g0; g < g1; ++g) {
-        while (g >= s_prefix[row + 1]) ++row;
-        const int t = g - s_prefix[row];
-        if (row != prev_row) {
-          const int qs = qit & 1;
-          if (!mbar_wait(&q_empty[qs], ((qit >> 1) & 1) ^ 1, abort_flag)) break;
+    }
+    int row = row0, prev_row = -1;
+    int it = 0, qit = 0;
+    int tbl_base = -1, tbl_entry = -1, tbl_len = 0, cols = 0;
+    const int32_t* trow = p.table;
+    const int P = kFp8 ? p.page_size : kTileKeys;
+    const int p_shift = 31 - __clz(P);  // P is a power of two
+    for (int g = g0; g < g1; ++g) {
+      while (g >= s_prefix[row + 1]) ++row;
+      const int t = g - s_prefix[row];
+      if (row != prev_row) {
+        const int qs = qit & 1;
+        const bool okq = mbar_wait(&q_empty[qs], ((qit >> 1) & 1) ^ 1, abort_flag);
+        if (!__all_sync(0xffffffffu, okq)) break;
+        if (elect_one()) {
           mbar_arrive_expect_tx(&q_full[qs], Cfg::kQBytes);
-          if constexpr (kFp8) {
-            tma_load_2d(q_mem + qs * Cfg::kQBytes, &tmap_q, &q_full[qs], 0, row * kHeads);
-          } else {
-            tma_load_2d(q_mem + qs * Cfg::kQBytes, &tmap_q, &q_full[qs], 0, row * kHeads);
+          tma_load_2d(q_mem + qs * Cfg::kQBytes, &tmap_q, &q_full[qs], 0, row * kHeads);
+          if constexpr (!kFp8)
             tma_load_2d(q_mem + qs * Cfg::kQBytes + Cfg::kQBytes / 2, &tmap_q, &q_full[qs], 64, row * kHeads);
-          }
-          ++qit;
-          prev_row = row;
         }
-        const int s = it % Cfg::kStages;
-        if (!mbar_wait(&empty[s], ((it / Cfg::kStages) & 1) ^ 1, abort_flag)) break;
-        uint8_t* dst = stage_mem + s * Cfg::kStageBytes;
-        const int32_t* trow = p.table + static_cast<int64_t>(row / p.table_row_div) * p.table_stride;
-        int cols = max(0, min(p.row_cols[row], p.logits_cols));
-        const int key0 = t * kTileKeys;
-        const int nkeys = min(kTileKeys, cols - key0);
-        if constexpr (kFp8) {
-          const int P = p.page_size;
-          const int npages = (nkeys + P - 1) / P;
-          int pg[4];
-          int nvalid = 0;
-          for (int j = 0; j < npages; ++j) {
-            pg[j] = trow[key0 / P + j];
-            if (pg[j] >= 0 && pg[j] < p.num_pages) ++nvalid; else pg[j] = -1;
+        ++qit;
+        prev_row = row;
+        cols = max(0, min(p.row_cols[row], p.logits_cols));
+        trow = p.table + static_cast<int64_t>(row / p.table_row_div) * p.table_stride;
+        tbl_len = min(p.table_cols, (cols + P - 1) >> p_shift);
+        tbl_base = -1;
+      }
+      const int s = it % Cfg::kStages;
+      const bool oke = mbar_wait(&empty[s], ((it / Cfg::kStages) & 1) ^ 1, abort_flag);
+      if (!__all_sync(0xffffffffu, oke)) break;
+      uint8_t* dst = stage_mem + s * Cfg::kStageBytes;
+      const int key0 = t * kTileKeys;
+      const int nkeys = min(kTileKeys, cols - key0);
+      const int first = key0 >> p_shift;
+      const int npages = (nkeys + P - 1) >> p_shift;
+      if (tbl_base < 0 || first < tbl_base || first + npages > tbl_base + 32) {
+        tbl_base = first;
+        const int e = tbl_base + lane;
+        tbl_entry = (e < tbl_len) ? trow[e] : -1;
+      }
+      if constexpr (kFp8) {
+        int pg[4];  // statically indexed below so that it stays in registers
+        int nvalid = 0;
+        float* sc = sc_mem + (it % Cfg::kScaleSlots) * kTileKeys;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          pg[j] = -1;
+          if (j < npages) {
+            const int e = __shfl_sync(0xffffffffu, tbl_entry, (first + j - tbl_base) & 31);
+            if (e >= 0 && e < p.num_pages) {
+              pg[j] = e;
+              ++nvalid;
+            } else {
+              for (int i = lane; i < P; i += 32) sc[j * P + i] = -1.0f;  // marks the keys as masked
+            }
           }
+        }
+        __syncwarp();
+        if (elect_one()) {
+          uint64_t* scb = &sc_full[it % Cfg::kScaleSlots];
+          mbar_arrive_expect_tx(scb, nvalid * P * 4);
           mbar_arrive_expect_tx(&full[s], nvalid * P * kDim);
-          for (int j = 0; j < npages; ++j)
-            if (pg[j] >= 0) tma_load_3d(dst + j * P * kDim, &tmap_k, &full[s], 0, 0, pg[j]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (pg[j] < 0) continue;
+            tma_load_3d(dst + j * P * kDim, &tmap_k, &full[s], 0, 0, pg[j]);
+            bulk_load_1d(sc + j * P, p.cache + static_cast<int64_t>(pg[j]) * p.page_bytes + static_cast<int64_t>(P) * kDim,
+                         P * 4, scb);
+          }
           if (nvalid != npages) atomicMax(p.status, kDevBadIndex);
-        } else {
-          const int blk = trow[t];
+        }
+      } else {
+        const int blk = __shfl_sync(0xffffffffu, tbl_entry, (first - tbl_base) & 31);
+        if (elect_one()) {
           if (blk >= 0 && blk < p.num_pages) {
             mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
             tma_load_2d(dst, &tmap_k, &full[s], 0, blk * kTileKeys);
@@ -191,31 +237,34 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
             atomicMax(p.status, kDevBadIndex);
           }
         }
-        ++it;
       }
-      issued = it;
+      ++it;
     }
+    issued = it;
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = kFp8 ? make_idesc(kFmtE4M3, kFmtE4M3, 128, kHeads)
-                                      : make_idesc(kFmtBF16, kFmtBF16, 128, kHeads);
-      int row = row0, prev_row = -1;
-      int it = 0, qit = 0, ait = 0, qs = 0;
-      for (int g = g0; g < g1; ++g) {
-        while (g >= s_prefix[row + 1]) ++row;
-        if (row != prev_row) {
-          if (prev_row >= 0) tc_commit(&q_empty[qs]);  // q slot free once the old row's MMAs retire
-          qs = qit & 1;
-          if (!mbar_wait(&q_full[qs], (qit >> 1) & 1, abort_flag)) break;
-          ++qit;
-          prev_row = row;
-        }
-        const int s = it % Cfg::kStages;
-        if (!mbar_wait(&full[s], (it / Cfg::kStages) & 1, abort_flag)) break;
-        const int as = ait & 1;
-        if (!mbar_wait(&acc_empty[as], ((ait >> 1) & 1) ^ 1, abort_flag)) break;
-        tc_fence_after();
+    // Whole warp in the loop; one elected lane issues the MMAs and their commits.
+    constexpr uint32_t idesc = kFp8 ? make_idesc(kFmtE4M3, kFmtE4M3, 128, kHeads)
+                                    : make_idesc(kFmtBF16, kFmtBF16, 128, kHeads);
+    int row = row0, prev_row = -1;
+    int it = 0, qit = 0, ait = 0, qs = 0;
+    for (int g = g0; g < g1; ++g) {
+      while (g >= s_prefix[row + 1]) ++row;
+      if (row != prev_row) {
+        qs = qit & 1;
+        const bool okq = mbar_wait(&q_full[qs], (qit >> 1) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, okq)) break;
+        ++qit;
+        prev_row = row;
+      }
+      const bool last_of_row = (g + 1 == g1) || (g + 1 >= s_prefix[row + 1]);
+      const int s = it % Cfg::kStages;
+      const int as = ait & 1;
+      const bool okf = mbar_wait(&full[s], (it / Cfg::kStages) & 1, abort_flag) &&
+                       mbar_wait(&acc_empty[as], ((ait >> 1) & 1) ^ 1, abort_flag);
+      if (!__all_sync(0xffffffffu, okf)) break;
+      tc_fence_after();
+      if (elect_one()) {
         const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
         const uint32_t b_addr = smem_base + Cfg::kStages * Cfg::kStageBytes + qs * Cfg::kQBytes;
         const uint32_t d_tmem = tmem_base + as * kHeads;
@@ -236,9 +285,11 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
         }
         tc_commit(&empty[s]);
         tc_commit(&acc_full[as]);
-        ++it;
-        ++ait;
+        if (last_of_row) tc_commit(&q_empty[qs]);  // q slot free once this row's MMAs retire
       }
+      __syncwarp();
+      ++it;
+      ++ait;
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
@@ -264,21 +315,14 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
         prev_row = row;
       }
       const int key = t * kTileKeys + lane_base + lane;  // column of this thread
-      // scale / mask inputs fetched before the accumulator is ready
       float kscale = 1.0f;
       bool keep = key < cols;
       if constexpr (kFp8) {
-        if (keep) {
-          const int P = p.page_size;
-          const int pg = trow[key / P];
-          if (pg >= 0 && pg < p.num_pages) {
-            const float* sc = reinterpret_cast<const float*>(p.cache + static_cast<int64_t>(pg) * p.page_bytes +
-                                                             static_cast<int64_t>(P) * kDim);
-            kscale = __ldg(sc + (key % P));
-          } else {
-            keep = false;
-          }
-        }
+        const int slot = ait % Cfg::kScaleSlots;
+        const bool sc_ready = mbar_wait(&sc_full[slot], (ait / Cfg::kScaleSlots) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, sc_ready)) break;
+        kscale = sc_mem[slot * kTileKeys + lane_base + lane];
+        keep = keep && (kscale >= 0.0f);
       } else {
         if (keep) {
           const int blk = trow[t];
@@ -319,9 +363,9 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
     for (int j = 0; j < n; ++j) {
       const int it = issued - 1 - j;
       const int s = it % Cfg::kStages;
-      const uint64_t t0 = global_timer_ns();
+      const long long t0 = clock64();
       while (!mbar_test(&full[s], (it / Cfg::kStages) & 1)) {
-        if (global_timer_ns() - t0 > 2000000ull) break;
+        if (clock64() - t0 > (1ll << 22)) break;
       }
     }
   }
@@ -434,6 +478,7 @@ extern "C" int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* 
     p.row_cols = context_lens + r0;
     p.table = block_table + static_cast<int64_t>(r0 / next_n) * block_table_stride;
     p.table_stride = block_table_stride;
+    p.table_cols = static_cast<int32_t>(block_table_stride);
     p.table_row_div = next_n;
     p.pos_lo = nullptr;
     p.pos_hi = nullptr;
@@ -492,6 +537,7 @@ extern "C" int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const f
     p.row_cols = row_cols + r0;
     p.table = block_list + static_cast<int64_t>(r0) * block_list_stride;
     p.table_stride = block_list_stride;
+    p.table_cols = static_cast<int32_t>(block_list_stride);
     p.table_row_div = 1;
     p.pos_lo = pos_lo ? pos_lo + r0 : nullptr;
     p.pos_hi = pos_hi ? pos_hi + r0 : nullptr;

@@ -10,19 +10,22 @@
 //      with a 6-sigma margin, at least k row elements lie at or above it;
 //   2. one streaming pass appends every element at or above that bin to a shared-memory
 //      candidate list (warp-aggregated append);
-//   3. the candidates are bitonic-sorted in shared memory and the first k are written.
+//   3. an exact most-significant-digit radix select (12/12/8-bit digits over the 64-bit
+//      composite) runs on the candidates in shared memory; the undecided bin, once small,
+//      is bitonic-sorted to pick the last few winners.
 // Rows that fit the candidate list entirely skip step 1.
-// Exact fallback (any distribution, massive ties): most-significant-digit radix select over
-// the 64-bit composite, re-reading the row per digit until the undecided bin fits the list.
+// Exact fallback (any distribution, massive ties): the same radix select with the row in
+// global memory as its source, re-reading it once per digit.
+// The k winners are optionally bitonic-sorted (descending score, ascending position).
 #include "b200dsa_common.cuh"
 
 namespace b200dsa {
 
 constexpr int kHistBins = 4096;
 constexpr int kCandCap = 8192;   // candidate list entries (64 KB)
-constexpr int kEqCap = 4096;     // undecided-bin list of the fallback (32 KB)
+constexpr int kEqCap = 1024;     // undecided-bin list (8 KB)
 constexpr int kSampleChunk = 128;
-constexpr int kSampleMax = 8192;
+constexpr int kSampleMax = 16384;
 
 struct TopkParams {
   const float* scores;
@@ -41,6 +44,7 @@ struct TopkParams {
   int32_t* out_idx;
   float* out_val;
   int64_t out_stride;
+  int32_t sorted;
 };
 
 __device__ __forceinline__ bool score_valid(float v, int keep_pos_inf) {
@@ -90,6 +94,49 @@ __device__ __forceinline__ void list_append(uint64_t* list, int* counter, int ca
   if (active) {
     int slot = base + __popc(act & ((1u << lane) - 1));
     if (slot < cap) list[slot] = key;
+  }
+}
+
+// Stream row elements [begin, begin+n) through f(value, column, in_range) with many loads in
+// flight per thread.  Every thread calls f the same number of times (f may use warp votes).
+// The 16-byte path needs src 16-byte aligned.
+template <class F>
+__device__ __forceinline__ void stream_row(const float* __restrict__ src, int begin, int n, bool vec_ok, F&& f) {
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  if (vec_ok) {
+    const int a0 = begin & ~3;
+    const int n4 = (begin + n - a0 + 3) >> 2;
+    const float4* src4 = reinterpret_cast<const float4*>(src + a0);
+    for (int base = 0; base < n4; base += nthr * 4) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i4 = base + u * nthr + tid;
+        v[u] = (i4 < n4) ? __ldg(src4 + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = a0 + 4 * (base + u * nthr + tid);
+        f(v[u].x, c + 0, c + 0 >= begin && c + 0 < begin + n);
+        f(v[u].y, c + 1, c + 1 >= begin && c + 1 < begin + n);
+        f(v[u].z, c + 2, c + 2 >= begin && c + 2 < begin + n);
+        f(v[u].w, c + 3, c + 3 >= begin && c + 3 < begin + n);
+      }
+    }
+  } else {
+    for (int base = 0; base < n; base += nthr * 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = base + u * nthr + tid;
+        v[u] = (i < n) ? __ldg(src + begin + i) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = base + u * nthr + tid;
+        f(v[u], begin + i, i < n);
+      }
+    }
   }
 }
 
@@ -156,12 +203,60 @@ __device__ void find_threshold_bin(const uint32_t* hist, int nbins, int need, in
   }
 }
 
+struct SelectResult {
+  bool take_all;     // fewer valid keys than wanted: every valid key wins
+  uint64_t full;     // decided leading bits of the threshold composite
+  int full_bits;
+  int need_eq;       // winners still to be taken from the keys whose leading bits equal `full`
+};
+
+// Most-significant-digit radix select.  for_each(need_pos, f) must call f(key, active) the same
+// number of times on every thread of a warp; keys are 64-bit composites (position bits may be
+// zero while need_pos is false).
+template <class ForEach>
+__device__ SelectResult radix_select(ForEach&& for_each, int need, uint32_t* hist, int* s_res) {
+  SelectResult r{false, 0, 0, 0};
+  uint64_t prefix = 0;
+  int prefix_bits = 0;
+  for (int level = 0; level < 6; ++level) {
+    const int digit_bits = (level % 3 == 2) ? 8 : 12;
+    const int shift = 64 - prefix_bits - digit_bits;
+    const bool need_pos = (prefix_bits + digit_bits) > 32;
+    for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for_each(need_pos, [&](uint64_t key, bool active) {
+      const bool ok = active && (prefix_bits == 0 || (key >> (64 - prefix_bits)) == prefix);
+      const uint32_t bin = static_cast<uint32_t>(key >> shift) & ((1u << digit_bits) - 1);
+      hist_add(hist, bin, ok);
+    });
+    __syncthreads();
+    find_threshold_bin(hist, kHistBins, need, s_res);
+    __syncthreads();
+    const int d = s_res[0];
+    if (d < 0) {  // level 0 only
+      r.take_all = true;
+      return r;
+    }
+    const int above = s_res[1];
+    const int in_bin = s_res[2];
+    r.full = (prefix << digit_bits) | static_cast<uint64_t>(d);
+    r.full_bits = prefix_bits + digit_bits;
+    r.need_eq = need - above;
+    if (in_bin <= kEqCap || level == 5) return r;
+    prefix = r.full;
+    prefix_bits = r.full_bits;
+    need = r.need_eq;
+  }
+  return r;
+}
+
 __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p, int k_pow2) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw);
   uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + kHistBins * sizeof(uint32_t));
   uint64_t* eq = cand + kCandCap;
-  __shared__ int s_cnt, s_eq_cnt, s_res[3];
+  uint64_t* sel = eq + kEqCap;  // k_pow2 entries
+  __shared__ int s_cnt, s_eq_cnt, s_sel_cnt, s_res[3];
 
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
@@ -172,6 +267,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   end = min(end, p.n_cols);
   const int n = end - begin;
   const float* src = p.scores + row * p.row_stride;
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.scores) & 15) == 0) && ((p.row_stride & 3) == 0);
   int32_t* out_idx = p.out_idx + row * p.out_stride;
   float* out_val = p.out_val ? p.out_val + row * p.out_stride : nullptr;
   const int k = p.k;
@@ -187,36 +283,44 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   if (tid == 0) {
     s_cnt = 0;
     s_eq_cnt = 0;
+    s_sel_cnt = 0;
   }
   __syncthreads();
-  bool done = false;
-  int n_final = 0;  // entries in cand to be sorted
 
-  // ------------------------------------------------------------------ fast paths
+  // ------------------------------------------------------------------ candidate collection
   uint32_t bin_floor = 0;
   bool try_fast = true;
   if (n > kCandCap) {
-    // sample histogram
     for (int i = tid; i < kHistBins; i += nthr) hist[i] = 0;
     __syncthreads();
-    const int n_chunks = kSampleMax / kSampleChunk;  // 64
-    const int m = n_chunks * kSampleChunk;
-    const int64_t step = n / n_chunks;               // >= 128 since n > 8192
-    for (int i = tid; i < m; i += nthr) {
-      int c = i / kSampleChunk;
-      int col = begin + static_cast<int>(c * step) + (i - c * kSampleChunk);
-      float v = src[col];
-      bool ok = score_valid(v, p.keep_pos_inf);
-      hist_add(hist, float_to_ordered(v) >> 20, ok);
+    // rows up to kSampleMax are histogrammed completely (exact threshold bin); longer rows
+    // through contiguous chunks spread evenly over the row
+    const bool exact = n <= kSampleMax;
+    const int m = exact ? n : kSampleMax;
+    const int64_t step = exact ? kSampleChunk : n / (kSampleMax / kSampleChunk);
+    for (int base = 0; base < m; base += nthr * 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = base + u * nthr + tid;
+        const int c = i / kSampleChunk;
+        v[u] = (i < m) ? __ldg(src + begin + static_cast<int>(c * step) + (i - c * kSampleChunk)) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = base + u * nthr + tid;
+        const bool ok = (i < m) && score_valid(v[u], p.keep_pos_inf);
+        hist_add(hist, float_to_ordered(v[u]) >> 20, ok);
+      }
     }
     __syncthreads();
-    // elements wanted at or above the bin: k + 6 sigma of the scaled-up sample count
+    // elements wanted at or above the bin: k, plus 6 sigma of the scaled-up sample count
     const float ratio = static_cast<float>(n) / static_cast<float>(m);
-    const float want_full = k + 6.0f * sqrtf(2.0f * k * ratio) + 32.0f;
+    const float want_full = exact ? static_cast<float>(k) : k + 6.0f * sqrtf(2.0f * k * ratio) + 32.0f;
     if (want_full > 0.8f * kCandCap) {
       try_fast = false;
     } else {
-      int want_sample = static_cast<int>(ceilf(want_full / ratio));
+      const int want_sample = static_cast<int>(ceilf(want_full / ratio));
       find_threshold_bin(hist, kHistBins, want_sample, s_res);
       __syncthreads();
       if (s_res[0] < 0) try_fast = false;  // sample too sparse (many invalid entries)
@@ -225,132 +329,95 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     __syncthreads();
   }
 
+  bool from_smem = false;
+  int cnt = 0;
   if (try_fast) {
-    // streaming collect of everything at or above bin_floor
-    const int n_round = (n + 31) & ~31;
-    for (int i = tid; i < n_round; i += nthr) {
+    stream_row(src, begin, n, vec_ok, [&](float v, int col, bool in_range) {
       bool take = false;
       uint64_t key = 0;
-      if (i < n) {
-        float v = src[begin + i];
-        if (score_valid(v, p.keep_pos_inf) && (float_to_ordered(v) >> 20) >= bin_floor) {
-          take = true;
-          key = make_composite(v, out_position(p, row, begin + i));
-        }
+      if (in_range && score_valid(v, p.keep_pos_inf) && (float_to_ordered(v) >> 20) >= bin_floor) {
+        take = true;
+        key = make_composite(v, out_position(p, row, col));
       }
       list_append(cand, &s_cnt, kCandCap, key, take);
-    }
+    });
     __syncthreads();
-    const int cnt = s_cnt;
-    if (cnt <= kCandCap && (cnt >= k || n <= kCandCap)) {
-      done = true;
-      n_final = cnt;
-    }
-    __syncthreads();
+    cnt = s_cnt;
+    from_smem = cnt <= kCandCap && (cnt >= k || n <= kCandCap);
   }
 
-  // ------------------------------------------------------------------ exact fallback
-  if (!done) {
-    uint64_t prefix = 0;
-    int prefix_bits = 0;
-    int need = k;
-    int digit_bits = 12;
-    uint64_t full = 0;
-    int full_bits = 0;
-    int need_eq = 0;
-    bool take_all = false;
-    for (int level = 0; level < 6; ++level) {
-      digit_bits = (level % 3 == 2) ? 8 : 12;
-      const int shift = 64 - prefix_bits - digit_bits;
-      const bool need_pos = (prefix_bits + digit_bits) > 32;
-      for (int i = tid; i < kHistBins; i += nthr) hist[i] = 0;
-      __syncthreads();
-      const int n_round = (n + 31) & ~31;
-      for (int i = tid; i < n_round; i += nthr) {
-        bool ok = false;
-        uint32_t bin = 0;
-        if (i < n) {
-          float v = src[begin + i];
-          if (score_valid(v, p.keep_pos_inf)) {
-            uint64_t key = need_pos ? make_composite(v, out_position(p, row, begin + i))
-                                    : (static_cast<uint64_t>(float_to_ordered(v)) << 32);
-            if (prefix_bits == 0 || (key >> (64 - prefix_bits)) == prefix) {
-              ok = true;
-              bin = static_cast<uint32_t>(key >> shift) & ((1u << digit_bits) - 1);
-            }
-          }
-        }
-        hist_add(hist, bin, ok);
-      }
-      __syncthreads();
-      find_threshold_bin(hist, kHistBins, need, s_res);
-      __syncthreads();
-      const int d = s_res[0];
-      if (d < 0) {  // fewer valid elements than k: everything valid is selected (level 0 only)
-        take_all = true;
-        break;
-      }
-      const int above = s_res[1];
-      const int in_bin = s_res[2];
-      full = (prefix << digit_bits) | static_cast<uint64_t>(d);
-      full_bits = prefix_bits + digit_bits;
-      need_eq = need - above;
-      if (in_bin <= kEqCap || level == 5) break;
-      prefix = full;
-      prefix_bits = full_bits;
-      need = need_eq;
-      __syncthreads();
+  // ------------------------------------------------------------------ exact selection
+  auto each_cand = [&](bool /*need_pos*/, auto&& f) {
+    for (int base = 0; base < cnt; base += nthr) {
+      const int i = base + tid;
+      const bool active = i < cnt;
+      f(active ? cand[i] : 0ull, active);
     }
-    if (tid == 0) {
-      s_cnt = 0;
-      s_eq_cnt = 0;
-    }
-    __syncthreads();
-    const int n_round = (n + 31) & ~31;
-    for (int i = tid; i < n_round; i += nthr) {
-      bool direct = false, tie = false;
+  };
+  auto each_row = [&](bool need_pos, auto&& f) {
+    stream_row(src, begin, n, vec_ok, [&](float v, int col, bool in_range) {
+      const bool active = in_range && score_valid(v, p.keep_pos_inf);
       uint64_t key = 0;
-      if (i < n) {
-        float v = src[begin + i];
-        if (score_valid(v, p.keep_pos_inf)) {
-          key = make_composite(v, out_position(p, row, begin + i));
-          if (take_all) {
-            direct = true;
-          } else {
-            uint64_t top = key >> (64 - full_bits);
-            direct = top > full;
-            tie = top == full;
-          }
+      if (active)
+        key = need_pos ? make_composite(v, out_position(p, row, col))
+                       : (static_cast<uint64_t>(float_to_ordered(v)) << 32);
+      f(key, active);
+    });
+  };
+  auto emit = [&](const SelectResult& r) {
+    return [&, r](uint64_t key, bool active) {
+      bool direct = false, tie = false;
+      if (active) {
+        if (r.take_all) {
+          direct = true;
+        } else {
+          const uint64_t top = key >> (64 - r.full_bits);
+          direct = top > r.full;
+          tie = top == r.full;
         }
       }
-      list_append(cand, &s_cnt, kCandCap, key, direct);
+      list_append(sel, &s_sel_cnt, k_pow2, key, direct);
       list_append(eq, &s_eq_cnt, kEqCap, key, tie);
+    };
+  };
+
+  SelectResult r;
+  if (from_smem) {
+    if (cnt <= k) {
+      r = SelectResult{true, 0, 0, 0};
+    } else {
+      r = radix_select(each_cand, k, hist, s_res);
     }
-    __syncthreads();
-    int n_direct = s_cnt;
-    if (!take_all) {
-      int n_eq = min(s_eq_cnt, kEqCap);
-      int n_eq_pow2 = 32;
-      while (n_eq_pow2 < n_eq) n_eq_pow2 <<= 1;
-      for (int i = n_eq + tid; i < n_eq_pow2; i += nthr) eq[i] = 0;
-      bitonic_sort_desc(eq, n_eq_pow2);
-      int take = min(need_eq, n_eq);
-      for (int i = tid; i < take; i += nthr) cand[n_direct + i] = eq[i];
-      n_direct += take;
-    }
-    n_final = n_direct;
+    each_cand(true, emit(r));
+  } else {
+    r = radix_select(each_row, k, hist, s_res);
+    each_row(true, emit(r));
+  }
+  __syncthreads();
+  int n_sel = min(s_sel_cnt, k_pow2);
+  if (!r.take_all) {
+    const int n_eq = min(s_eq_cnt, kEqCap);
+    int n_eq_pow2 = 32;
+    while (n_eq_pow2 < n_eq) n_eq_pow2 <<= 1;
+    for (int i = n_eq + tid; i < n_eq_pow2; i += nthr) eq[i] = 0;
+    bitonic_sort_desc(eq, n_eq_pow2);
+    const int take = min(min(r.need_eq, n_eq), k_pow2 - n_sel);
+    for (int i = tid; i < take; i += nthr) sel[n_sel + i] = eq[i];
+    n_sel += take;
     __syncthreads();
   }
 
-  // ------------------------------------------------------------------ sort + write
-  int n_pow2 = 32;
-  while (n_pow2 < n_final) n_pow2 <<= 1;
-  for (int i = n_final + tid; i < n_pow2; i += nthr) cand[i] = 0;
-  bitonic_sort_desc(cand, n_pow2);
-  const int n_out = min(n_final, k);
+  // ------------------------------------------------------------------ order + write
+  if (p.sorted) {
+    int n_pow2 = 32;
+    while (n_pow2 < n_sel) n_pow2 <<= 1;
+    for (int i = n_sel + tid; i < n_pow2; i += nthr) sel[i] = 0;
+    bitonic_sort_desc(sel, n_pow2);
+  }
+  const int n_out = min(n_sel, k);
   for (int j = tid; j < k; j += nthr) {
     if (j < n_out) {
-      uint64_t key = cand[j];
+      const uint64_t key = sel[j];
       out_idx[j] = static_cast<int32_t>(~static_cast<uint32_t>(key & 0xffffffffu));
       if (out_val) out_val[j] = ordered_to_float(static_cast<uint32_t>(key >> 32));
     } else {
@@ -358,7 +425,6 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
       if (out_val) out_val[j] = -INFINITY;
     }
   }
-  (void)k_pow2;
 }
 
 void set_last_error(const char* msg);
@@ -369,10 +435,10 @@ using namespace b200dsa;
 
 extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int32_t n_rows, int32_t n_cols,
                                    const int32_t* col_begin, const int32_t* col_end, int32_t k,
-                                   int32_t keep_pos_inf, const int32_t* pos_map, int64_t pos_map_stride,
-                                   const int32_t* page_table, int64_t page_table_stride, int32_t page_size,
-                                   const int32_t* row_pos_offset, int32_t* out_idx, float* out_val,
-                                   int64_t out_stride, void* stream) {
+                                   int32_t keep_pos_inf, int32_t sorted, const int32_t* pos_map,
+                                   int64_t pos_map_stride, const int32_t* page_table, int64_t page_table_stride,
+                                   int32_t page_size, const int32_t* row_pos_offset, int32_t* out_idx,
+                                   float* out_val, int64_t out_stride, void* stream) {
   if (n_rows == 0) return B200DSA_OK;
   if (!scores || !out_idx || n_rows < 0 || n_cols < 0 || k < 1 || k > kCandCap || out_stride < k ||
       row_stride < n_cols) {
@@ -384,17 +450,18 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
     return B200DSA_EINVAL;
   }
   TopkParams p{scores, row_stride, n_rows, n_cols, col_begin, col_end, k, keep_pos_inf, pos_map, pos_map_stride,
-               page_table, page_table_stride, page_size, row_pos_offset, out_idx, out_val, out_stride};
-  const size_t smem = kHistBins * sizeof(uint32_t) + (kCandCap + kEqCap) * sizeof(uint64_t);
+               page_table, page_table_stride, page_size, row_pos_offset, out_idx, out_val, out_stride, sorted};
+  int k_pow2 = 32;
+  while (k_pow2 < k) k_pow2 <<= 1;
+  const size_t smem = kHistBins * sizeof(uint32_t) + (kCandCap + kEqCap + k_pow2) * sizeof(uint64_t);
   cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem));
+                                       static_cast<int>(kHistBins * sizeof(uint32_t) +
+                                                        (2 * kCandCap + kEqCap) * sizeof(uint64_t)));
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;
   }
   const int threads = n_cols > 16384 ? 1024 : 512;
-  int k_pow2 = 32;
-  while (k_pow2 < k) k_pow2 <<= 1;
   topk_select_kernel<<<n_rows, threads, smem, static_cast<cudaStream_t>(stream)>>>(p, k_pow2);
   e = cudaGetLastError();
   if (e != cudaSuccess) {

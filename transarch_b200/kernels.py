@@ -27,8 +27,9 @@ def topk_select(scores: torch.Tensor, k: int, *, col_begin: Optional[torch.Tenso
                 col_end: Optional[torch.Tensor] = None, keep_pos_inf: bool = False,
                 pos_map: Optional[torch.Tensor] = None, page_table: Optional[torch.Tensor] = None,
                 page_size: int = 0, row_pos_offset: Optional[torch.Tensor] = None,
-                return_values: bool = False, out: Optional[torch.Tensor] = None):
-    """Row-wise top-k positions (int32, descending score, -1 padded); see b200dsa_topk_select."""
+                sorted: bool = True, return_values: bool = False, out: Optional[torch.Tensor] = None):
+    """Row-wise top-k positions (int32, -1 padded; descending score when sorted); see
+    b200dsa_topk_select."""
     require_cuda(scores, col_begin, col_end, pos_map, page_table, row_pos_offset)
     if scores.dtype != torch.float32 or scores.dim() != 2 or scores.stride(1) != 1:
         raise _lib.B200DSAError("scores must be a 2-D fp32 tensor with unit column stride")
@@ -41,7 +42,7 @@ def topk_select(scores: torch.Tensor, k: int, *, col_begin: Optional[torch.Tenso
     lib = _lib.load()
     rc = lib.b200dsa_topk_select(
         ptr(scores), scores.stride(0), n_rows, n_cols,
-        ptr(_i32(col_begin, "col_begin")), ptr(_i32(col_end, "col_end")), k, int(keep_pos_inf),
+        ptr(_i32(col_begin, "col_begin")), ptr(_i32(col_end, "col_end")), k, int(keep_pos_inf), int(sorted),
         ptr(_i32(pos_map, "pos_map")), pos_map.stride(0) if pos_map is not None else 0,
         ptr(_i32(page_table, "page_table")), page_table.stride(0) if page_table is not None else 0, page_size,
         ptr(_i32(row_pos_offset, "row_pos_offset")),
