@@ -32,7 +32,8 @@ struct PagedCfg {
   static constexpr int kElem = kFp8 ? 1 : 2;
   static constexpr int kStageBytes = kTileKeys * kDim * kElem;  // 16 KB / 32 KB
   static constexpr int kQBytes = kHeads * kDim * kElem;         // 8 KB / 16 KB
-  static constexpr int kStages = kFp8 ? 8 : 5;
+  static constexpr int kStages = kFp8 ? 5 : 5;
+  static constexpr int kCtasPerSm = kFp8 ? 2 : 1;
   static constexpr int kKSteps = kFp8 ? 4 : 8;                  // MMAs per tile (32 B of K each)
   // Per-tile key scales travel through their own ring.  A slot is reused kScaleSlots tiles
   // later; by then the MMA of tile (it + 2) has retired, which needed the epilogue of tile
@@ -65,7 +66,7 @@ struct PagedIndexerParams {
 };
 
 template <bool kFp8>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, PagedCfg<kFp8>::kCtasPerSm)
 indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
                      const PagedIndexerParams p) {
   using Cfg = PagedCfg<kFp8>;
@@ -412,7 +413,7 @@ static int launch_paged(const CUtensorMap& mk, const CUtensorMap& mq, PagedIndex
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;
   }
-  int grid = sm_count();
+  int grid = sm_count() * Cfg::kCtasPerSm;
   if (est_tiles > 0 && est_tiles < grid) grid = static_cast<int>(est_tiles);
   indexer_paged_kernel<kFp8><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(mk, mq, p);
   e = cudaGetLastError();
