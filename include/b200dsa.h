@@ -111,6 +111,29 @@ int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const float* weigh
                                           int32_t max_cols, float out_scale, float* logits,
                                           int64_t logits_stride, int32_t* status, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Sparse MLA attention over selected keys in the absorbed latent space (tcgen05), one query
+ * token per item; emits the latent-space context and the log-sum-exp so that partial results
+ * over disjoint key sets can be merged.
+ *
+ *   valid(j) = idx_j >= 0 and idx_j <= q_pos[item] and pos_lo <= idx_j < pos_hi
+ *   s[h,j]   = sm_scale * <q[item,h,:], kv[kv_row_base[item] + idx_j - pos_lo, :]>
+ *   ctx[item,h,:] = sum_j softmax_j(s)[h,j] * kv[row_j, 0:512]     (0 when no key is valid)
+ *   lse[item,h]   = log sum_j exp(s[h,j])                           (-inf when no key is valid)
+ *
+ * Reproduces OpenDSA/opendsa/ops/sparse_mla.py:39-43 with the validity rule of :90, i.e.
+ * _attend_absorbed_chunk before its W_UV up-projection (:44).
+ *   q_bf16 [n_items, n_heads, 576], kv_bf16 [kv_rows, 576] (512 value dims then 64 rope dims),
+ *   indices [n_items, idx_stride] int32, kv_row_base / q_pos optional (0 / no bound),
+ *   ctx [n_items, n_heads, 512] fp32, lse [n_items, n_heads] fp32.  1 <= n_heads <= 128.
+ * Rows outside [0, kv_rows) are skipped and reported through status (2).
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16, int64_t kv_rows,
+                              const int64_t* kv_row_base, const int32_t* indices, int64_t idx_stride,
+                              int32_t n_idx, const int32_t* q_pos, int32_t pos_lo, int32_t pos_hi,
+                              int32_t n_items, int32_t n_heads, float sm_scale, float* ctx, float* lse,
+                              int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,97 @@
+"""tcgen05 sparse MLA decode kernel against the oracle (and, through it, the reference's
+sparse_attend_absorbed_chunked golden outputs)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import dsa_oracle as O
+from tests.golden.make_golden import ATTEND_CASES, golden_inputs_attend
+
+pytestmark = pytest.mark.gpu
+
+ATTN_RTOL = 2e-2   # stated tolerance for bf16 attention output
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _check(ctx, lse, ref_ctx, ref_lse):
+    assert torch.isfinite(ctx).all()
+    err = (ctx - ref_ctx).abs().max() / ref_ctx.abs().max().clamp_min(1e-6)
+    assert err < ATTN_RTOL, f"ctx err {err}"
+    fin = torch.isfinite(ref_lse)
+    assert torch.equal(torch.isfinite(lse), fin)
+    assert (lse[fin] - ref_lse[fin]).abs().max() < 2e-2
+
+
+def test_golden_mla_shape_matches_reference_output():
+    """Same seeded inputs as the stored reference run (rounded to bf16 for the kernel)."""
+    from transarch_b200 import _lib, kernels as K
+    name, seed, L, H, Dl, d_c, Kk = ATTEND_CASES[1]
+    q, lat, W_UV, idx = golden_inputs_attend(seed, L, H, Dl, d_c, Kk)
+    g = np.load(os.path.join(GOLD, name + ".npz"))
+    qpos = torch.arange(L, dtype=torch.int32)
+    ctx, lse = K.sparse_mla_decode(q.bfloat16().cuda(), lat.bfloat16().cuda(), idx.cuda(), Dl ** -0.5,
+                                   q_pos=qpos.cuda())
+    assert _lib.read_status(ctx.device) == 0
+    ref = torch.from_numpy(g["ctx"])
+    err = (ctx.cpu() - ref).abs().max() / ref.abs().max()
+    assert err < ATTN_RTOL
+    assert (ctx.cpu()[3] == 0).all() and torch.isinf(lse.cpu()[3]).all()    # fully masked row
+
+
+@pytest.mark.parametrize("n_items,H,n_idx,ctx_len", [(3, 128, 2048, 5000), (2, 16, 64, 300), (4, 128, 100, 4000),
+                                                      (1, 128, 33, 50)])
+def test_decode_vs_oracle(n_items, H, n_idx, ctx_len):
+    from transarch_b200 import _lib, kernels as K
+    g = torch.Generator().manual_seed(n_idx + H)
+    q = torch.randn(n_items, H, 576, generator=g).bfloat16()
+    kv = (0.5 * torch.randn(n_items * ctx_len, 576, generator=g)).bfloat16()
+    base = torch.arange(n_items, dtype=torch.int64) * ctx_len
+    idx = torch.stack([torch.randperm(ctx_len, generator=g)[:n_idx] for _ in range(n_items)]).to(torch.int32)
+    idx[:, ::7] = -1
+    qpos = torch.full((n_items,), ctx_len - 1, dtype=torch.int32)
+    qpos[0] = ctx_len // 2                                  # masks about half of item 0's picks
+    scale = 192 ** -0.5
+    ctx, lse = K.sparse_mla_decode(q.cuda(), kv.cuda(), idx.cuda(), scale, kv_row_base=base.cuda(),
+                                   q_pos=qpos.cuda())
+    assert _lib.read_status(ctx.device) == 0
+    for b in range(n_items):
+        rc, rl = O.sparse_attend_latent(q[b:b + 1], kv[b * ctx_len:(b + 1) * ctx_len], idx[b:b + 1],
+                                        d_c=512, sm_scale=scale, q_pos=qpos[b:b + 1])
+        _check(ctx[b:b + 1].cpu(), lse[b:b + 1].cpu(), rc, rl)
+
+
+def test_shard_partials_merge_to_full():
+    """Two position shards attended separately and merged by log-sum-exp equal the full result."""
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(77)
+    n, H, n_idx, ctx_len = 2, 128, 512, 3000
+    q = torch.randn(n, H, 576, generator=g).bfloat16()
+    kv = (0.5 * torch.randn(ctx_len, 576, generator=g)).bfloat16()
+    idx = torch.stack([torch.randperm(ctx_len, generator=g)[:n_idx] for _ in range(n)]).to(torch.int32)
+    scale = 192 ** -0.5
+    full_ctx, full_lse = O.sparse_attend_latent(q, kv, idx, d_c=512, sm_scale=scale,
+                                                q_pos=torch.full((n,), ctx_len - 1))
+    parts, lses = [], []
+    for lo, hi in [(0, 1400), (1400, ctx_len)]:
+        c, l = K.sparse_mla_decode(q.cuda(), kv[lo:hi].contiguous().cuda(), idx.cuda(), scale,
+                                   pos_lo=lo, pos_hi=hi)
+        parts.append(c.cpu()); lses.append(l.cpu())
+    out, lse = O.lse_combine(parts, lses)
+    _check(out, lse, full_ctx, full_lse)
+
+
+def test_large_scores_trigger_rescale():
+    """Keys ordered so that the running maximum keeps growing: exercises the O rescale path."""
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(78)
+    H, n_idx = 128, 256
+    q = torch.randn(1, H, 576, generator=g).bfloat16()
+    kv = torch.randn(n_idx, 576, generator=g)
+    kv = (kv * torch.linspace(0.2, 6.0, n_idx).view(-1, 1)).bfloat16()   # later keys: far larger scores
+    idx = torch.arange(n_idx, dtype=torch.int32).view(1, -1)
+    scale = 0.3
+    ctx, lse = K.sparse_mla_decode(q.cuda(), kv.cuda(), idx.cuda(), scale)
+    rc, rl = O.sparse_attend_latent(q, kv, idx, d_c=512, sm_scale=scale, q_pos=torch.tensor([n_idx]))
+    _check(ctx.cpu(), lse.cpu(), rc, rl)

@@ -26,6 +26,8 @@ SIGNATURES = {
                                          _vp, _i64, _vp, _vp],
     "b200dsa_indexer_blocklist_bf16_logits": [_vp, _vp, _vp, _i32, _vp, _i64, _vp, _vp, _vp, _i32, _i32, _f32,
                                               _vp, _i64, _vp, _vp],
+    "b200dsa_sparse_mla_decode": [_vp, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _i32, _i32, _i32, _i32, _f32,
+                                  _vp, _vp, _vp, _vp],
 }
 
 _lib: Optional[C.CDLL] = None
@@ -85,5 +87,9 @@ def status_word(device: torch.device) -> torch.Tensor:
 
 
 def read_status(device: torch.device) -> int:
-    """Synchronising read of the status word (tests and debugging only)."""
-    return int(status_word(device).item())
+    """Synchronising read-and-clear of the status word (tests and debugging only)."""
+    w = status_word(device)
+    v = int(w.item())
+    if v:
+        w.zero_()
+    return v

@@ -1,0 +1,438 @@
+// Sparse MLA attention in the absorbed latent space, one query token per work item.
+//
+//   s[h, j]  = sm_scale * <q[h, 0:576], kv[idx_j, 0:576]>          (j over the selected keys)
+//   p        = softmax_j(s)  over valid j
+//   ctx[h,:] = sum_j p[h, j] * kv[idx_j, 0:512]                    (latent-space context)
+//   lse[h]   = log sum_j exp(s[h, j])
+//
+// Work split: CTA (item, half) computes all heads of one item for value dims
+// [256*half, 256*half+256).  Heads are the UMMA M dimension (one TMEM lane and one softmax
+// thread per head, so row max / row sum are thread-local), 32 gathered keys are N of the
+// score MMA and K of the value MMA.  The 576-wide rows are gathered with 16-byte cp.async
+// into the 128-byte-swizzled K-major layout the score MMA reads; the same bytes serve,
+// read MN-major, as the value operand.  Q (128 x 576 bf16) stays in shared memory.
+//
+// TMEM: O accumulator 256 columns + two 32-column score buffers.
+// Roles (288 threads): warps 0-3 gather, warps 4-7 softmax (warp w owns TMEM lanes
+// 32*(w%4)..), warp 8 issues MMAs.  All waits are bounded.
+#include <cuda_bf16.h>
+
+#include "b200dsa_common.cuh"
+
+namespace b200dsa {
+
+constexpr int kMlaHeadsTile = 128;
+constexpr int kMlaD = 576;          // latent width (512 value dims + 64 rope dims)
+constexpr int kMlaDv = 512;
+constexpr int kMlaDvHalf = 256;
+constexpr int kMlaChunks = 9;       // 576 / 64 elements (128-byte chunks)
+constexpr int kMlaTile = 32;        // keys per tile
+constexpr int kMlaStages = 2;
+constexpr int kMlaThreads = 288;
+constexpr int kMlaQBytes = kMlaHeadsTile * kMlaD * 2;            // 147456
+constexpr int kMlaChunkBytesQ = kMlaHeadsTile * 128;             // 16384 per 64-wide chunk
+constexpr int kMlaStageBytes = kMlaTile * kMlaD * 2;             // 36864
+constexpr int kMlaChunkBytesK = kMlaTile * 128;                  // 4096
+constexpr int kMlaPBytes = kMlaHeadsTile * kMlaTile * 2;         // 8192
+constexpr int kMlaSmemBytes = kMlaQBytes + kMlaStages * kMlaStageBytes + kMlaPBytes + 1024 + 256;
+constexpr uint32_t kMlaTmemCols = 512;
+constexpr uint32_t kMlaTmemO = 0;
+constexpr uint32_t kMlaTmemS = 256;  // two buffers: 256, 288
+
+struct MlaParams {
+  const __nv_bfloat16* kv;     // [kv_rows, 576]
+  int64_t kv_rows;
+  const int64_t* kv_row_base;  // nullable [n_items]: row of position 0 of the item's sequence
+  const int32_t* indices;      // [n_items, idx_stride] key positions, -1 = none
+  int64_t idx_stride;
+  int32_t n_idx;
+  const int32_t* q_pos;        // nullable [n_items]: keys beyond this position are masked
+  int32_t pos_lo, pos_hi;      // only positions in [pos_lo, pos_hi) are attended (shard ownership)
+  int32_t n_items, n_heads;
+  float scale_log2;            // sm_scale * log2(e)
+  float* ctx;                  // [n_items, n_heads, 512] fp32
+  float* lse;                  // [n_items, n_heads] fp32 (natural log)
+  int32_t* status;
+};
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+  const uint32_t sz = valid ? 16u : 0u;  // 0 -> the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_mbar_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// K-major operand without swizzle: core matrices of 8 rows x 16 bytes stored contiguously
+// (128 bytes); lbo = byte step between core matrices along K, sbo = along M/N.
+__device__ __forceinline__ uint64_t make_desc_k_noswz(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(lbo >> 4) << 16;
+  d |= static_cast<uint64_t>(sbo >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+// MN-major operand, 128-byte swizzle: atoms of 8 K-rows x 64 MN-elements (1024 bytes);
+// lbo = byte step between atoms along MN, sbo = byte step between atoms along K.
+__device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(lbo >> 4) << 16;
+  d |= static_cast<uint64_t>(sbo >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+__global__ void __launch_bounds__(kMlaThreads, 1)
+sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaParams p) {
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  __shared__ uint32_t s_mask[kMlaStages];  // one validity bit per key of the stage, byte w from gather warp w
+
+  const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_dyn + (smem_base - smem_u32(smem_dyn));
+  const uint32_t q_addr = smem_base;
+  const uint32_t kv_addr = smem_base + kMlaQBytes;
+  const uint32_t p_addr = kv_addr + kMlaStages * kMlaStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + kMlaQBytes + kMlaStages * kMlaStageBytes + kMlaPBytes);
+  uint64_t* q_full = bars;          // [1]
+  uint64_t* kv_full = bars + 1;     // [2] 128 gather threads
+  uint64_t* kv_empty = bars + 3;    // [2] value MMA retired
+  uint64_t* s_full = bars + 5;      // [2] score MMA retired
+  uint64_t* s_empty = bars + 7;     // [2] 128 softmax threads have read the scores
+  uint64_t* p_full = bars + 9;      // [1] 128 softmax threads wrote P
+  uint64_t* pv_done = bars + 10;    // [1] value MMA retired (P buffer free, O stable)
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int item = blockIdx.x >> 1;
+  const int half = blockIdx.x & 1;
+  const int n_tiles = (p.n_idx + kMlaTile - 1) / kMlaTile;
+  volatile int* abort_flag = &s_abort;
+
+  if (tid == 0) {
+    s_abort = 0;
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 128);
+      mbar_init(&kv_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(&s_tmem_base, kMlaTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  const int qpos = p.q_pos ? p.q_pos[item] : 0x7fffffff;
+  const int64_t row_base = (p.kv_row_base ? p.kv_row_base[item] : 0) - p.pos_lo;
+
+  if (warp < 4) {
+    // ------------------------------------------------------------------ gather producers
+    const int r = tid >> 2;        // key row of the tile
+    const int sub = tid & 3;
+    const int32_t* idx_row = p.indices + static_cast<int64_t>(item) * p.idx_stride;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int s = t & 1;
+      const bool ok = mbar_wait(&kv_empty[s], ((t >> 1) & 1) ^ 1, abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      const int j = t * kMlaTile + r;
+      const int idx = (j < p.n_idx) ? __ldg(idx_row + j) : -1;
+      bool valid = idx >= 0 && idx <= qpos && idx >= p.pos_lo && idx < p.pos_hi;
+      const int64_t grow = row_base + idx;
+      if (valid && (grow < 0 || grow >= p.kv_rows)) {
+        valid = false;
+        atomicMax(p.status, kDevBadIndex);
+      }
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(p.kv) + (valid ? grow : 0) * (kMlaD * 2);
+      const uint32_t dst_row = kv_addr + s * kMlaStageBytes + r * 128;
+#pragma unroll
+      for (int u = 0; u < 18; ++u) {
+        const int c16 = sub + 4 * u;           // 16-byte chunk of the 1152-byte row
+        const int c = c16 >> 3, w = c16 & 7;   // 128-byte chunk, position inside it
+        cp_async_16(dst_row + c * kMlaChunkBytesK + ((w ^ (r & 7)) << 4), src + c16 * 16, valid);
+      }
+      const unsigned b = __ballot_sync(0xffffffffu, valid && sub == 0);
+      if (lane == 0) {
+        uint32_t m8 = 0;
+#pragma unroll
+        for (int rr = 0; rr < 8; ++rr) m8 |= ((b >> (4 * rr)) & 1u) << rr;
+        reinterpret_cast<volatile uint8_t*>(&s_mask[s])[warp] = static_cast<uint8_t>(m8);
+      }
+      __threadfence_block();
+      __syncwarp();
+      // the barrier receives this thread's arrival once all its copies above have landed
+      cp_async_mbar_arrive(&kv_full[s]);
+    }
+    cp_async_wait_all();
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ softmax, one head per thread
+    const int head = (warp & 3) * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    float m_ref = -INFINITY, l = 0.f;
+    bool aborted = false;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int sb = t & 1;
+      bool ok = mbar_wait(&s_full[sb], (t >> 1) & 1, abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) { aborted = true; break; }
+      tc_fence_after();
+      uint32_t v[32];
+      tmem_ld_32x32(tmem_base + lane_addr + kMlaTmemS + sb * kMlaTile, v);
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&s_empty[sb]);
+      const uint32_t mask = s_mask[sb];
+      float x[32];
+      float mt = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        x[j] = ((mask >> j) & 1u) ? __uint_as_float(v[j]) * p.scale_log2 : -INFINITY;
+        mt = fmaxf(mt, x[j]);
+      }
+      bool waited_pv = false;
+      // lazy rescale: only when the running maximum grows by more than 2^8
+      const bool grow = mt > m_ref + 8.0f;
+      if (__any_sync(0xffffffffu, grow) && t > 0) {
+        ok = mbar_wait(pv_done, (t - 1) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) { aborted = true; break; }
+        waited_pv = true;
+        tc_fence_after();
+        const float f = grow ? ((m_ref == -INFINITY) ? 0.f : exp2f(m_ref - mt)) : 1.0f;
+#pragma unroll 1
+        for (int c = 0; c < kMlaDvHalf / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_base + lane_addr + kMlaTmemO + c * 32, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * f);
+          tmem_st_32x32(tmem_base + lane_addr + kMlaTmemO + c * 32, o);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        l *= f;
+      }
+      if (grow) m_ref = mt;
+      uint32_t pk[16];
+      float lsum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const float p0 = (x[j] == -INFINITY) ? 0.f : exp2f(x[j] - m_ref);
+        const float p1 = (x[j + 1] == -INFINITY) ? 0.f : exp2f(x[j + 1] - m_ref);
+        lsum += p0 + p1;
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+        pk[j >> 1] = *reinterpret_cast<uint32_t*>(&h2);
+      }
+      l += lsum;
+      if (t > 0 && !waited_pv) {
+        ok = mbar_wait(pv_done, (t - 1) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) { aborted = true; break; }
+      }
+      // P row (32 bf16) as 4 core-matrix rows of 16 bytes: (head/8)*512 + c*128 + (head%8)*16
+      const uint32_t prow = p_addr + (head >> 3) * 512 + (head & 7) * 16;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + c * 128), "r"(pk[4 * c]),
+                     "r"(pk[4 * c + 1]), "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3])
+                     : "memory");
+      }
+      fence_proxy_async();
+      mbar_arrive(p_full);
+    }
+    // ---- output
+    float* ctx_row = p.ctx + (static_cast<int64_t>(item) * p.n_heads + head) * kMlaDv + half * kMlaDvHalf;
+    const bool write = head < p.n_heads;
+    if (n_tiles == 0 || aborted) {
+      if (write && !aborted) {
+        for (int j = 0; j < kMlaDvHalf; j += 4) *reinterpret_cast<float4*>(ctx_row + j) = make_float4(0, 0, 0, 0);
+        if (half == 0) p.lse[static_cast<int64_t>(item) * p.n_heads + head] = -INFINITY;
+      }
+    } else {
+      const bool ok = mbar_wait(pv_done, (n_tiles - 1) & 1, abort_flag);
+      if (__all_sync(0xffffffffu, ok)) {
+        tc_fence_after();
+        const float inv = (l > 0.f) ? 1.0f / l : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < kMlaDvHalf / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_base + lane_addr + kMlaTmemO + c * 32, o);
+          tc_wait_ld();
+          if (write) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              *reinterpret_cast<float4*>(ctx_row + c * 32 + j) =
+                  make_float4(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv,
+                              __uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+            }
+          }
+        }
+        tc_fence_before();
+        if (write && half == 0)
+          p.lse[static_cast<int64_t>(item) * p.n_heads + head] =
+              (l > 0.f) ? (m_ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ MMA issuer (warp 8)
+    constexpr uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, 128, kMlaTile);
+    constexpr uint32_t idesc_pv = make_idesc(kFmtBF16, kFmtBF16, 128, kMlaDvHalf, 0, 1);
+    if (elect_one()) {
+      tma_prefetch_desc(&tmap_q);
+      mbar_arrive_expect_tx(q_full, kMlaQBytes);
+      for (int c = 0; c < kMlaChunks; ++c)
+        tma_load_2d(smem_al + c * kMlaChunkBytesQ, &tmap_q, q_full, c * 64, item * p.n_heads);
+    }
+    __syncwarp();
+    bool ok = mbar_wait(q_full, 0, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    auto issue_scores = [&](int t) -> bool {
+      const int s = t & 1;
+      bool w = mbar_wait(&kv_full[s], (t >> 1) & 1, abort_flag) &&
+               mbar_wait(&s_empty[s], ((t >> 1) & 1) ^ 1, abort_flag);
+      if (!__all_sync(0xffffffffu, w)) return false;
+      fence_proxy_async();  // gathered rows were written through the generic proxy
+      tc_fence_after();
+      if (elect_one()) {
+        const uint32_t d = tmem_base + kMlaTmemS + s * kMlaTile;
+#pragma unroll 1
+        for (int c = 0; c < kMlaChunks; ++c) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t a = make_desc_k_sw128(q_addr + c * kMlaChunkBytesQ + kk * 32);
+            const uint64_t b = make_desc_k_sw128(kv_addr + s * kMlaStageBytes + c * kMlaChunkBytesK + kk * 32);
+            mma_f16_ss(d, a, b, idesc_s, (c | kk) != 0);
+          }
+        }
+        tc_commit(&s_full[s]);
+      }
+      __syncwarp();
+      return true;
+    };
+    if (ok && n_tiles > 0) ok = issue_scores(0);
+    for (int t = 0; ok && t < n_tiles; ++t) {
+      if (t + 1 < n_tiles) {
+        ok = issue_scores(t + 1);
+        if (!ok) break;
+      }
+      const int s = t & 1;
+      const bool w = mbar_wait(p_full, t & 1, abort_flag);
+      if (!__all_sync(0xffffffffu, w)) break;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint32_t d = tmem_base + kMlaTmemO;
+        const uint32_t v_addr = kv_addr + s * kMlaStageBytes + (4 * half) * kMlaChunkBytesK;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {  // 16 keys per MMA
+          const uint64_t a = make_desc_k_noswz(p_addr + j * 256, 128, 512);
+          const uint64_t b = make_desc_mn_sw128(v_addr + j * 2048, kMlaChunkBytesK, 1024);
+          mma_f16_ss(d, a, b, idesc_pv, (t | j) != 0);
+        }
+        tc_commit(&kv_empty[s]);
+        tc_commit(pv_done);
+      }
+      __syncwarp();
+    }
+  }
+
+  // ---------------------------------------------------------------------- common tail
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 8) tmem_dealloc(tmem_base, kMlaTmemCols);
+  if (tid == 0 && s_abort) atomicMax(p.status, kDevWaitTimeout);
+}
+
+void set_last_error(const char* msg);
+
+}  // namespace b200dsa
+
+using namespace b200dsa;
+
+extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16, int64_t kv_rows,
+                                         const int64_t* kv_row_base, const int32_t* indices, int64_t idx_stride,
+                                         int32_t n_idx, const int32_t* q_pos, int32_t pos_lo, int32_t pos_hi,
+                                         int32_t n_items, int32_t n_heads, float sm_scale, float* ctx, float* lse,
+                                         int32_t* status, void* stream) {
+  if (n_items == 0) return B200DSA_OK;
+  if (!q_bf16 || !kv_bf16 || !indices || !ctx || !lse || !status || n_items < 0 || n_heads < 1 ||
+      n_heads > kMlaHeadsTile || n_idx < 0 || idx_stride < n_idx || kv_rows < 1 || pos_hi < pos_lo) {
+    set_last_error("b200dsa_sparse_mla_decode: bad argument (1 <= n_heads <= 128, idx_stride >= n_idx)");
+    return B200DSA_EINVAL;
+  }
+  if ((reinterpret_cast<uintptr_t>(q_bf16) & 15) || (reinterpret_cast<uintptr_t>(kv_bf16) & 15) ||
+      (reinterpret_cast<uintptr_t>(ctx) & 15)) {
+    set_last_error("b200dsa_sparse_mla_decode: q, kv and ctx must be 16-byte aligned");
+    return B200DSA_EALIGN;
+  }
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (!enc) return B200DSA_ECUDA;
+  CUtensorMap mq;
+  {
+    cuuint64_t dims[2] = {kMlaD, static_cast<cuuint64_t>(n_items) * n_heads};
+    cuuint64_t strides[1] = {kMlaD * 2};
+    cuuint32_t box[2] = {64, kMlaHeadsTile};
+    cuuint32_t es[2] = {1, 1};
+    CUresult r = enc(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(q_bf16), dims, strides, box, es,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_last_error("b200dsa_sparse_mla_decode: cuTensorMapEncodeTiled rejected the q layout");
+      return B200DSA_ECUDA;
+    }
+  }
+  cudaError_t e = cudaFuncSetAttribute(sparse_mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kMlaSmemBytes);
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  MlaParams p{};
+  p.kv = static_cast<const __nv_bfloat16*>(kv_bf16);
+  p.kv_rows = kv_rows;
+  p.kv_row_base = kv_row_base;
+  p.indices = indices;
+  p.idx_stride = idx_stride;
+  p.n_idx = n_idx;
+  p.q_pos = q_pos;
+  p.pos_lo = pos_lo;
+  p.pos_hi = pos_hi;
+  p.n_items = n_items;
+  p.n_heads = n_heads;
+  p.scale_log2 = sm_scale * 1.4426950408889634f;
+  p.ctx = ctx;
+  p.lse = lse;
+  p.status = status;
+  sparse_mla_decode_kernel<<<n_items * 2, kMlaThreads, kMlaSmemBytes, static_cast<cudaStream_t>(stream)>>>(mq, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  return B200DSA_OK;
+}

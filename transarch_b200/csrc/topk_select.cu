@@ -73,13 +73,9 @@ __device__ __forceinline__ uint64_t make_composite(float v, int32_t pos) {
   return (static_cast<uint64_t>(float_to_ordered(v)) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(pos));
 }
 
-// warp-aggregated histogram increment
+// histogram increment (shared-memory atomic without a return value)
 __device__ __forceinline__ void hist_add(uint32_t* hist, uint32_t bin, bool active) {
-  unsigned act = __ballot_sync(0xffffffffu, active);
-  if (!active) return;
-  unsigned peers = __match_any_sync(act, bin);
-  int leader = __ffs(peers) - 1;
-  if ((threadIdx.x & 31) == leader) atomicAdd(&hist[bin], __popc(peers));
+  if (active) atomicAdd(&hist[bin], 1u);
 }
 
 // warp-aggregated append; entries beyond cap are counted but not stored
@@ -160,47 +156,66 @@ __device__ void bitonic_sort_desc(uint64_t* a, int n) {
   __syncthreads();
 }
 
-// Warp 0: find the highest bin d such that (#elements in bins >= d) >= need.
-// Writes res[0]=d (or -1 when the whole histogram holds fewer than need), res[1]=count in
-// bins above d, res[2]=hist[d].
-__device__ void find_threshold_bin(const uint32_t* hist, int nbins, int need, int* res) {
-  if (threadIdx.x >= 32) return;
-  const int lane = threadIdx.x;
-  const int per = nbins / 32;
-  // lane 0 owns the highest bins
-  const int hi = nbins - lane * per;  // exclusive
-  uint32_t mine = 0;
-  for (int b = hi - 1; b >= hi - per; --b) mine += hist[b];
-  uint32_t incl = mine;  // inclusive prefix over lanes (= suffix over bins)
-  for (int o = 1; o < 32; o <<= 1) {
-    uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += v;
+// Find the highest bin d such that (#elements in bins >= d) >= need.  All threads call it
+// (it contains block barriers).  Writes res[0]=d (or -1 when the whole histogram holds fewer
+// than need), res[1]=count in bins above d, res[2]=hist[d].  Segment s (128 bins) covers bins
+// [4096-128(s+1), 4096-128s): segment 0 is the highest.
+__device__ void find_threshold_bin(const uint32_t* hist, int need, int* res, uint32_t* seg_sum) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int sgm = warp; sgm < 32; sgm += nwarps) {
+    const uint4 v = reinterpret_cast<const uint4*>(hist + kHistBins - 128 * (sgm + 1))[lane];
+    uint32_t t = v.x + v.y + v.z + v.w;
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) seg_sum[sgm] = t;
   }
-  uint32_t excl = incl - mine;
-  bool owner = (excl < static_cast<uint32_t>(need)) && (incl >= static_cast<uint32_t>(need));
-  unsigned who = __ballot_sync(0xffffffffu, owner);
-  const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-  if (who == 0) {
-    if (lane == 0) {
-      res[0] = -1;
-      res[1] = static_cast<int>(total);
-      res[2] = 0;
+  __syncthreads();
+  if (warp == 0) {
+    const uint32_t mine = seg_sum[lane];
+    uint32_t incl = mine;
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
     }
-    return;
-  }
-  if (owner) {
-    uint32_t above = excl;
-    for (int b = hi - 1; b >= hi - per; --b) {
-      uint32_t h = hist[b];
-      if (above + h >= static_cast<uint32_t>(need)) {
-        res[0] = b;
-        res[1] = static_cast<int>(above);
-        res[2] = static_cast<int>(h);
-        break;
+    const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+    const bool owner = (incl - mine < static_cast<uint32_t>(need)) && (incl >= static_cast<uint32_t>(need));
+    const unsigned who = __ballot_sync(0xffffffffu, owner);
+    if (who == 0) {
+      if (lane == 0) {
+        res[0] = -1;
+        res[1] = static_cast<int>(total);
+        res[2] = 0;
       }
-      above += h;
+    } else {
+      const int sgm = __ffs(who) - 1;
+      const uint32_t above_seg = __shfl_sync(0xffffffffu, incl - mine, sgm);
+      // lane l takes bins base+4l..base+4l+3; higher lanes hold higher bins
+      const int base = kHistBins - 128 * (sgm + 1);
+      const uint4 v = reinterpret_cast<const uint4*>(hist + base)[lane];
+      const uint32_t t = v.x + v.y + v.z + v.w;
+      uint32_t suf = t;  // inclusive suffix over lanes (lane 31 first)
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t u = __shfl_down_sync(0xffffffffu, suf, o);
+        if (lane + o < 32) suf += u;
+      }
+      const uint32_t above_lane = above_seg + suf - t;  // elements in bins above this lane's four
+      const bool own = (above_lane < static_cast<uint32_t>(need)) && (above_lane + t >= static_cast<uint32_t>(need));
+      if (own) {
+        uint32_t above = above_lane;
+        const uint32_t h[4] = {v.w, v.z, v.y, v.x};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (above + h[j] >= static_cast<uint32_t>(need)) {
+            res[0] = base + 4 * lane + 3 - j;
+            res[1] = static_cast<int>(above);
+            res[2] = static_cast<int>(h[j]);
+            break;
+          }
+          above += h[j];
+        }
+      }
     }
   }
+  __syncthreads();
 }
 
 struct SelectResult {
@@ -214,7 +229,7 @@ struct SelectResult {
 // number of times on every thread of a warp; keys are 64-bit composites (position bits may be
 // zero while need_pos is false).
 template <class ForEach>
-__device__ SelectResult radix_select(ForEach&& for_each, int need, uint32_t* hist, int* s_res) {
+__device__ SelectResult radix_select(ForEach&& for_each, int need, uint32_t* hist, int* s_res, uint32_t* s_seg) {
   SelectResult r{false, 0, 0, 0};
   uint64_t prefix = 0;
   int prefix_bits = 0;
@@ -230,8 +245,7 @@ __device__ SelectResult radix_select(ForEach&& for_each, int need, uint32_t* his
       hist_add(hist, bin, ok);
     });
     __syncthreads();
-    find_threshold_bin(hist, kHistBins, need, s_res);
-    __syncthreads();
+    find_threshold_bin(hist, need, s_res, s_seg);
     const int d = s_res[0];
     if (d < 0) {  // level 0 only
       r.take_all = true;
@@ -256,7 +270,8 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + kHistBins * sizeof(uint32_t));
   uint64_t* eq = cand + kCandCap;
   uint64_t* sel = eq + kEqCap;  // k_pow2 entries
-  __shared__ int s_cnt, s_eq_cnt, s_sel_cnt, s_res[3];
+  __shared__ int s_eq_cnt, s_sel_cnt, s_res[3], s_warp_cnt[32], s_overflow;
+  __shared__ uint32_t s_seg[32];
 
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
@@ -281,7 +296,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   }
 
   if (tid == 0) {
-    s_cnt = 0;
+    s_overflow = 0;
     s_eq_cnt = 0;
     s_sel_cnt = 0;
   }
@@ -321,36 +336,46 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
       try_fast = false;
     } else {
       const int want_sample = static_cast<int>(ceilf(want_full / ratio));
-      find_threshold_bin(hist, kHistBins, want_sample, s_res);
-      __syncthreads();
+      find_threshold_bin(hist, want_sample, s_res, s_seg);
       if (s_res[0] < 0) try_fast = false;  // sample too sparse (many invalid entries)
       else bin_floor = static_cast<uint32_t>(s_res[0]);
     }
     __syncthreads();
   }
 
+  // Each warp compacts its takes into its own segment of the candidate list with votes
+  // only (no atomics); a full segment raises the overflow flag and the row falls back.
   bool from_smem = false;
-  int cnt = 0;
+  const int warp_id = tid >> 5, lane_id = tid & 31, n_warps = nthr >> 5;
+  const int seg_cap = kCandCap / n_warps;
+  uint64_t* my_seg = cand + warp_id * seg_cap;
+  int cnt = 0;  // total candidates
   if (try_fast) {
+    int wcnt = 0;  // warp-uniform
     stream_row(src, begin, n, vec_ok, [&](float v, int col, bool in_range) {
-      bool take = false;
-      uint64_t key = 0;
-      if (in_range && score_valid(v, p.keep_pos_inf) && (float_to_ordered(v) >> 20) >= bin_floor) {
-        take = true;
-        key = make_composite(v, out_position(p, row, col));
+      const bool take = in_range && score_valid(v, p.keep_pos_inf) && (float_to_ordered(v) >> 20) >= bin_floor;
+      const unsigned act = __ballot_sync(0xffffffffu, take);
+      if (take) {
+        const int slot = wcnt + __popc(act & ((1u << lane_id) - 1));
+        if (slot < seg_cap) my_seg[slot] = make_composite(v, out_position(p, row, col));
       }
-      list_append(cand, &s_cnt, kCandCap, key, take);
+      wcnt += __popc(act);
     });
+    if (lane_id == 0) {
+      s_warp_cnt[warp_id] = min(wcnt, seg_cap);
+      if (wcnt > seg_cap) s_overflow = 1;
+    }
     __syncthreads();
-    cnt = s_cnt;
-    from_smem = cnt <= kCandCap && (cnt >= k || n <= kCandCap);
+    for (int w = 0; w < n_warps; ++w) cnt += s_warp_cnt[w];
+    from_smem = (s_overflow == 0) && (cnt >= k || n <= kCandCap);
   }
 
   // ------------------------------------------------------------------ exact selection
   auto each_cand = [&](bool /*need_pos*/, auto&& f) {
-    for (int base = 0; base < cnt; base += nthr) {
+    for (int base = 0; base < kCandCap; base += nthr) {
       const int i = base + tid;
-      const bool active = i < cnt;
+      const int w = i / seg_cap;
+      const bool active = (i - w * seg_cap) < s_warp_cnt[w];
       f(active ? cand[i] : 0ull, active);
     }
   };
@@ -386,11 +411,11 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     if (cnt <= k) {
       r = SelectResult{true, 0, 0, 0};
     } else {
-      r = radix_select(each_cand, k, hist, s_res);
+      r = radix_select(each_cand, k, hist, s_res, s_seg);
     }
     each_cand(true, emit(r));
   } else {
-    r = radix_select(each_row, k, hist, s_res);
+    r = radix_select(each_row, k, hist, s_res, s_seg);
     each_row(true, emit(r));
   }
   __syncthreads();

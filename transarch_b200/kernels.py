@@ -114,3 +114,33 @@ def indexer_blocklist_bf16_logits(q: torch.Tensor, weights: torch.Tensor, keys: 
         ptr(out), out.stride(0), ptr(status_word(q.device)), stream_ptr())
     check(rc, "b200dsa_indexer_blocklist_bf16_logits")
     return out
+
+
+def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: float, *,
+                      kv_row_base: Optional[torch.Tensor] = None, q_pos: Optional[torch.Tensor] = None,
+                      pos_lo: int = 0, pos_hi: int = 2 ** 31 - 1,
+                      ctx: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None
+                      ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Latent-space sparse attention: (ctx [n, H, 512] fp32, lse [n, H] fp32); see
+    b200dsa_sparse_mla_decode."""
+    require_cuda(q, kv, indices, kv_row_base, q_pos)
+    if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.dim() != 3 or q.shape[2] != 576:
+        raise _lib.B200DSAError("q must be contiguous bf16 [n_items, n_heads, 576]")
+    if kv.dtype != torch.bfloat16 or not kv.is_contiguous() or kv.dim() != 2 or kv.shape[1] != 576:
+        raise _lib.B200DSAError("kv must be contiguous bf16 [rows, 576]")
+    if indices.dtype != torch.int32 or indices.dim() != 2 or indices.stride(1) != 1 or indices.shape[0] != q.shape[0]:
+        raise _lib.B200DSAError("indices must be int32 [n_items, n_idx] with unit column stride")
+    if kv_row_base is not None and (kv_row_base.dtype != torch.int64 or not kv_row_base.is_contiguous()):
+        raise _lib.B200DSAError("kv_row_base must be contiguous int64")
+    _i32(q_pos, "q_pos")
+    n, H, _ = q.shape
+    if ctx is None:
+        ctx = torch.empty(n, H, 512, dtype=torch.float32, device=q.device)
+    if lse is None:
+        lse = torch.empty(n, H, dtype=torch.float32, device=q.device)
+    lib = _lib.load()
+    rc = lib.b200dsa_sparse_mla_decode(
+        ptr(q), ptr(kv), kv.shape[0], ptr(kv_row_base), ptr(indices), indices.stride(0), indices.shape[1],
+        ptr(q_pos), pos_lo, pos_hi, n, H, sm_scale, ptr(ctx), ptr(lse), ptr(status_word(q.device)), stream_ptr())
+    check(rc, "b200dsa_sparse_mla_decode")
+    return ctx, lse
