@@ -52,6 +52,11 @@ const char* b200dsa_last_error(void);
  *   otherwise         : c
  * plus row_pos_offset[r] when that pointer is given.
  *
+ * Segmented rows (seg_cols > 0): column c of a row is stored at offset
+ * (c / seg_cols) * seg_stride + c % seg_cols from the row start, in scores and in pos_map
+ * alike.  This reads the [n_ranks, n_rows, seg] layout an all-gather of per-shard candidates
+ * produces without a transpose (row_stride = distance between rows inside one segment).
+ *
  * Limits: 1 <= k <= 8192.  scores rows need 4-byte alignment only.
  * ------------------------------------------------------------------------------------- */
 int b200dsa_topk_select(const float* scores, int64_t row_stride, int32_t n_rows, int32_t n_cols,
@@ -60,6 +65,7 @@ int b200dsa_topk_select(const float* scores, int64_t row_stride, int32_t n_rows,
                         const int32_t* pos_map, int64_t pos_map_stride,
                         const int32_t* page_table, int64_t page_table_stride, int32_t page_size,
                         const int32_t* row_pos_offset,
+                        int32_t seg_cols, int64_t seg_stride,
                         int32_t* out_idx, float* out_val, int64_t out_stride,
                         void* stream);
 
@@ -133,6 +139,40 @@ int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16, int64_t k
                               int32_t n_idx, const int32_t* q_pos, int32_t pos_lo, int32_t pos_hi,
                               int32_t n_items, int32_t n_heads, float sm_scale, float* ctx, float* lse,
                               int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Merge attention partials computed over disjoint key sets (key shards of several GPUs, or
+ * splits on one GPU):  out = sum_r exp(lse_r - m) ctx_r / sum_r exp(lse_r - m),
+ * lse_out = m + log(sum_r exp(lse_r - m)),  m = max_r lse_r.  No counterpart call in the
+ * reference (its inference path is single-GPU); the nearest analogue is the context-parallel
+ * key gather at OpenDSA/opendsa/modeling/dsa_attention.py:650-669.
+ *   ctx_parts [n_parts, n_rows, 512] fp32, lse_parts [n_parts, n_rows] fp32,
+ *   ctx_out [n_rows, 512] fp32, lse_out [n_rows] fp32 (optional).  n_parts <= 64.
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_lse_combine(const float* ctx_parts, const float* lse_parts, int32_t n_parts, int64_t n_rows,
+                        float* ctx_out, float* lse_out, void* stream);
+
+/* All-reduce form of the merge above, for partials that live on different GPUs.  After a MAX
+ * all-reduce of lse gives lse_max, prescale writes 516-float wire rows
+ * (ctx*exp(lse-lse_max) [512], exp(lse-lse_max), 3 zero pads); the caller SUM-all-reduces
+ * (or reduce-scatters) the wire buffer; finalize divides by the summed weight and writes
+ * lse_out = lse_max + log(weight sum).  wire is [n_rows, 516] fp32, 16-byte aligned. */
+int b200dsa_lse_prescale(const float* ctx, const float* lse, const float* lse_max, int64_t n_rows,
+                         float* wire, void* stream);
+int b200dsa_lse_finalize(const float* wire, const float* lse_max, int64_t n_rows, float* ctx_out,
+                         float* lse_out, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * FP8 quantisation of the index queries with the scale folded into the head weights:
+ *   scale = max(amax|q[t,h,:]|, 1e-4)/448, q_fp8 = e4m3(q/scale), weights = w * scale * fold.
+ * Replaces MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/misa_deepseek_v2.py:279-292
+ * (per_token_group_quant_fp8 over the 128-wide head + weight folding; fold carries
+ * softmax_scale * n_head**-0.5 there).
+ *   q_bf16 [n_rows, 128] (n_rows = tokens*heads), w [n_rows] fp32,
+ *   q_fp8 [n_rows, 128] e4m3 out, weights [n_rows] fp32 out.
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_quant_q_fold_weights(const void* q_bf16, const float* w, int64_t n_rows, float fold,
+                                 void* q_fp8, float* weights, void* stream);
 
 #ifdef __cplusplus
 }

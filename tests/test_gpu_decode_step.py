@@ -1,0 +1,94 @@
+"""Whole decode step (quantise q -> indexer -> top-k -> sparse MLA) against the oracle, and
+the key-sharded flow emulated on one GPU (two shards run one after the other, the all-gather
+replaced by a copy) against the unsharded result."""
+import pytest
+import torch
+
+from oracle import dsa_oracle as O
+from tests.decode_cases import make_global_problem, oracle_decode, shard_state
+
+pytestmark = pytest.mark.gpu
+IDX_SCALE, ATT_SCALE = 128 ** -0.5, 192 ** -0.5
+
+
+def _cuda(prob):
+    return prob["q_idx"].cuda(), prob["w"].cuda(), prob["q_lat"].cuda()
+
+
+@pytest.mark.parametrize("ctxs,topk", [([3000, 8192, 700, 5555], 512), ([20000, 9000], 2048)])
+def test_single_gpu_step_matches_oracle(ctxs, topk):
+    from transarch_b200 import _lib
+    from transarch_b200.decode import SparseDecodeStep
+    prob = make_global_problem(41, ctxs)
+    st = shard_state(prob, 0, 1, max(ctxs), "cuda")
+    step = SparseDecodeStep(len(ctxs), st["table"].shape[1] * 64, topk=topk, sorted_topk=True)
+    q_idx, w, q_lat = _cuda(prob)
+    idx, ctx, lse = step.run(q_idx, w, q_lat, st["cache"], st["lens"], st["table"], st["kv"], st["base"])
+    assert _lib.read_status(ctx.device) == 0
+    ref_idx, scores, ref_ctx, ref_lse = oracle_decode(prob, topk, IDX_SCALE, ATT_SCALE)
+    idx = idx.cpu()
+    assert O.set_recall(idx, ref_idx) >= 0.999
+    total, bad = O.near_tie_audit(idx, ref_idx, torch.cat([torch.nn.functional.pad(s, (0, max(ctxs) - s.shape[1]),
+                                  value=float("-inf")) for s in scores]), rtol=1e-3)
+    assert bad == 0, f"{bad} of {total} disagreements are not near-ties"
+    # attention compared on the kernel's own selection (removes tie effects)
+    for b in range(len(ctxs)):
+        c, l = O.sparse_attend_latent(prob["q_lat"][b:b + 1], prob["kv"][b], idx[b:b + 1], d_c=512,
+                                      sm_scale=ATT_SCALE, q_pos=torch.tensor([ctxs[b] - 1]))
+        err = (ctx[b].cpu() - c[0]).abs().max() / c.abs().max()
+        assert err < 2e-2
+        assert (lse[b].cpu() - l[0]).abs().max() < 2e-2
+    err = (ctx.cpu() - ref_ctx).abs().max() / ref_ctx.abs().max()
+    assert err < 2e-2
+
+
+def test_two_shards_equal_unsharded():
+    from transarch_b200 import kernels as K
+    from transarch_b200.decode import ShardInfo, SparseDecodeStep
+    ctxs, topk, shard_len = [6000, 8192, 2500], 1024, 4096
+    prob = make_global_problem(42, ctxs)
+    q_idx, w, q_lat = _cuda(prob)
+    full = shard_state(prob, 0, 1, max(ctxs), "cuda")
+    one = SparseDecodeStep(3, full["table"].shape[1] * 64, topk=topk, sorted_topk=True)
+    idx1, ctx1, lse1 = one.run(q_idx, w, q_lat, full["cache"], full["lens"], full["table"], full["kv"], full["base"])
+    idx1, ctx1, lse1 = idx1.clone(), ctx1.clone(), lse1.clone()
+
+    steps, states = [], []
+    for r in range(2):
+        st = shard_state(prob, r, 2, shard_len, "cuda")
+        sp = SparseDecodeStep(3, shard_len, topk=topk, sorted_topk=True,
+                              shard=ShardInfo(rank=r, world_size=2, shard_len=shard_len))
+        sp.select(q_idx, w, st["cache"], st["local"], st["table"])
+        steps.append(sp); states.append(st)
+    gathered = torch.stack([s.cand for s in steps])            # what the all-gather delivers
+    parts, lses = [], []
+    for r, sp in enumerate(steps):
+        sp.cand_all.copy_(gathered)
+        flat = sp.cand_all.view(-1)
+        K.topk_select(flat[topk:].view(torch.float32).view(1, -1), topk, sorted=True, pos_map=flat.view(1, -1),
+                      out=sp.merged, n_cols=2 * topk, row_stride=2 * topk, seg_cols=topk,
+                      seg_stride=3 * 2 * topk, n_rows=3, pos_map_stride=2 * topk)
+        assert torch.equal(sp.merged, idx1), "merged shard candidates differ from the unsharded top-k"
+        torch.sub(states[r]["lens"], 1, out=sp.q_pos)
+        c, l = sp.attend(q_lat, states[r]["kv"], states[r]["base"], sp.merged, sp.q_pos)
+        parts.append(c.clone()); lses.append(l.clone())
+    ctx2, lse2 = K.lse_combine(torch.stack(parts), torch.stack(lses))
+    assert (ctx2 - ctx1).abs().max() / ctx1.abs().max() < 2e-3
+    assert (lse2 - lse1).abs().max() < 2e-3
+    # all-reduce form: prescale with the max, sum, finalize
+    m = torch.maximum(lses[0], lses[1])
+    wire = sum(K.lse_prescale(parts[r], lses[r], m, torch.empty(3 * 128, K.WIRE_ROW, device="cuda")) for r in range(2))
+    ctx3, lse3 = K.lse_finalize(wire.contiguous(), m, torch.empty_like(ctx1), torch.empty_like(lse1))
+    assert (ctx3 - ctx2).abs().max() < 1e-5 and (lse3 - lse2).abs().max() < 1e-5
+
+
+def test_quant_fold_matches_oracle_bitwise():
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(37, 64, 128, generator=g).bfloat16()
+    q[3, 5] = 0                                                  # all-zero head: scale floor
+    w = torch.randn(37, 64, generator=g) / 8
+    q_fp8, wf = K.quant_q_fold_weights(q.cuda(), w.cuda(), IDX_SCALE)
+    rq, rw = O.quant_q_fold_weights(q.float(), w, IDX_SCALE)
+    assert torch.equal(q_fp8.cpu().view(torch.uint8), rq.view(torch.uint8))
+    assert torch.allclose(wf.cpu(), rw, rtol=1e-6, atol=0)

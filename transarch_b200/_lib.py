@@ -21,13 +21,17 @@ SIGNATURES = {
     "b200dsa_abi_version": [],
     "b200dsa_last_error": [],
     "b200dsa_topk_select": [_vp, _i64, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _i32, _vp,
-                            _vp, _vp, _i64, _vp],
+                            _i32, _i64, _vp, _vp, _i64, _vp],
     "b200dsa_indexer_paged_fp8_logits": [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _i32, _i32, _i32, _f32,
                                          _vp, _i64, _vp, _vp],
     "b200dsa_indexer_blocklist_bf16_logits": [_vp, _vp, _vp, _i32, _vp, _i64, _vp, _vp, _vp, _i32, _i32, _f32,
                                               _vp, _i64, _vp, _vp],
     "b200dsa_sparse_mla_decode": [_vp, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _i32, _i32, _i32, _i32, _f32,
                                   _vp, _vp, _vp, _vp],
+    "b200dsa_lse_combine": [_vp, _vp, _i32, _i64, _vp, _vp, _vp],
+    "b200dsa_lse_prescale": [_vp, _vp, _vp, _i64, _vp, _vp],
+    "b200dsa_lse_finalize": [_vp, _vp, _i64, _vp, _vp, _vp],
+    "b200dsa_quant_q_fold_weights": [_vp, _vp, _i64, _f32, _vp, _vp, _vp],
 }
 
 _lib: Optional[C.CDLL] = None

@@ -1,0 +1,62 @@
+// Index-query quantisation with the scale folded into the head weights:
+//   scale[t,h] = max(amax_d |q[t,h,d]|, 1e-4) / 448;  q_fp8 = e4m3(q / scale)  (round to nearest even)
+//   weights[t,h] = w[t,h] * scale[t,h] * fold
+// so that  sum_h weights * relu(<q_fp8, k_fp8>) * k_scale  equals the unquantised score up to
+// FP8 rounding.  One warp per (t, h) row of 128 values, four per lane.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "b200dsa_common.cuh"
+
+namespace b200dsa {
+
+__global__ void __launch_bounds__(256) quant_q_fold_kernel(const __nv_bfloat16* __restrict__ q,
+                                                           const float* __restrict__ w, int64_t n_rows, float fold,
+                                                           uint8_t* __restrict__ q_fp8, float* __restrict__ weights) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const int lane = threadIdx.x & 31;
+  const uint2 raw = __ldg(reinterpret_cast<const uint2*>(q + row * 128) + lane);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  float x[4] = {__low2float(a), __high2float(a), __low2float(b), __high2float(b)};
+  float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float scale = __fdiv_rn(fmaxf(amax, 1e-4f), 448.0f);
+  uint32_t packed = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float y = fminf(fmaxf(__fdiv_rn(x[j], scale), -448.0f), 448.0f);
+    packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3)) << (8 * j);
+  }
+  reinterpret_cast<uint32_t*>(q_fp8 + row * 128)[lane] = packed;
+  if (lane == 0) weights[row] = __ldg(w + row) * scale * fold;
+}
+
+void set_last_error(const char* msg);
+
+}  // namespace b200dsa
+
+using namespace b200dsa;
+
+extern "C" int b200dsa_quant_q_fold_weights(const void* q_bf16, const float* w, int64_t n_rows, float fold,
+                                            void* q_fp8, float* weights, void* stream) {
+  if (n_rows == 0) return B200DSA_OK;
+  if (!q_bf16 || !w || !q_fp8 || !weights || n_rows < 0) {
+    set_last_error("b200dsa_quant_q_fold_weights: bad argument");
+    return B200DSA_EINVAL;
+  }
+  if ((reinterpret_cast<uintptr_t>(q_bf16) & 7) || (reinterpret_cast<uintptr_t>(q_fp8) & 3)) {
+    set_last_error("b200dsa_quant_q_fold_weights: q must be 8-byte and q_fp8 4-byte aligned");
+    return B200DSA_EALIGN;
+  }
+  const unsigned grid = static_cast<unsigned>((n_rows + 7) / 8);
+  quant_q_fold_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(q_bf16), w, n_rows, fold, static_cast<uint8_t*>(q_fp8), weights);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  return B200DSA_OK;
+}

@@ -45,6 +45,8 @@ struct TopkParams {
   float* out_val;
   int64_t out_stride;
   int32_t sorted;
+  int32_t seg_cols;     // > 0: column c lives at (c / seg_cols) * seg_stride + c % seg_cols of its row
+  int64_t seg_stride;
 };
 
 __device__ __forceinline__ bool score_valid(float v, int keep_pos_inf) {
@@ -55,10 +57,16 @@ __device__ __forceinline__ bool score_valid(float v, int keep_pos_inf) {
   return true;
 }
 
+__device__ __forceinline__ int64_t col_offset(const TopkParams& p, int col) {
+  if (p.seg_cols <= 0) return col;
+  const int r = col / p.seg_cols;
+  return r * p.seg_stride + (col - r * p.seg_cols);
+}
+
 __device__ __forceinline__ int32_t out_position(const TopkParams& p, int row, int col) {
   int32_t pos;
   if (p.pos_map) {
-    pos = p.pos_map[row * p.pos_map_stride + col];
+    pos = p.pos_map[row * p.pos_map_stride + col_offset(p, col)];
   } else if (p.page_table) {
     int pg = col / p.page_size;
     pos = p.page_table[row * p.page_table_stride + pg] * p.page_size + (col - pg * p.page_size);
@@ -96,8 +104,8 @@ __device__ __forceinline__ void list_append(uint64_t* list, int* counter, int ca
 // Stream row elements [begin, begin+n) through f(value, column, in_range) with many loads in
 // flight per thread.  Every thread calls f the same number of times (f may use warp votes).
 // The 16-byte path needs src 16-byte aligned.
-template <class F>
-__device__ __forceinline__ void stream_row(const float* __restrict__ src, int begin, int n, bool vec_ok, F&& f) {
+template <class F, class Off>
+__device__ __forceinline__ void stream_row(const float* __restrict__ src, int begin, int n, bool vec_ok, Off&& off, F&& f) {
   const int tid = threadIdx.x, nthr = blockDim.x;
   if (vec_ok) {
     const int a0 = begin & ~3;
@@ -125,7 +133,7 @@ __device__ __forceinline__ void stream_row(const float* __restrict__ src, int be
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const int i = base + u * nthr + tid;
-        v[u] = (i < n) ? __ldg(src + begin + i) : 0.f;
+        v[u] = (i < n) ? __ldg(src + off(begin + i)) : 0.f;
       }
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
@@ -282,7 +290,8 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   end = min(end, p.n_cols);
   const int n = end - begin;
   const float* src = p.scores + row * p.row_stride;
-  const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.scores) & 15) == 0) && ((p.row_stride & 3) == 0);
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.scores) & 15) == 0) && ((p.row_stride & 3) == 0) && p.seg_cols <= 0;
+  auto coff = [&](int col) { return col_offset(p, col); };
   int32_t* out_idx = p.out_idx + row * p.out_stride;
   float* out_val = p.out_val ? p.out_val + row * p.out_stride : nullptr;
   const int k = p.k;
@@ -319,7 +328,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
       for (int u = 0; u < 8; ++u) {
         const int i = base + u * nthr + tid;
         const int c = i / kSampleChunk;
-        v[u] = (i < m) ? __ldg(src + begin + static_cast<int>(c * step) + (i - c * kSampleChunk)) : 0.f;
+        v[u] = (i < m) ? __ldg(src + coff(begin + static_cast<int>(c * step) + (i - c * kSampleChunk))) : 0.f;
       }
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
@@ -352,7 +361,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   int cnt = 0;  // total candidates
   if (try_fast) {
     int wcnt = 0;  // warp-uniform
-    stream_row(src, begin, n, vec_ok, [&](float v, int col, bool in_range) {
+    stream_row(src, begin, n, vec_ok, coff, [&](float v, int col, bool in_range) {
       const bool take = in_range && score_valid(v, p.keep_pos_inf) && (float_to_ordered(v) >> 20) >= bin_floor;
       const unsigned act = __ballot_sync(0xffffffffu, take);
       if (take) {
@@ -380,7 +389,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     }
   };
   auto each_row = [&](bool need_pos, auto&& f) {
-    stream_row(src, begin, n, vec_ok, [&](float v, int col, bool in_range) {
+    stream_row(src, begin, n, vec_ok, coff, [&](float v, int col, bool in_range) {
       const bool active = in_range && score_valid(v, p.keep_pos_inf);
       uint64_t key = 0;
       if (active)
@@ -462,11 +471,12 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
                                    const int32_t* col_begin, const int32_t* col_end, int32_t k,
                                    int32_t keep_pos_inf, int32_t sorted, const int32_t* pos_map,
                                    int64_t pos_map_stride, const int32_t* page_table, int64_t page_table_stride,
-                                   int32_t page_size, const int32_t* row_pos_offset, int32_t* out_idx,
-                                   float* out_val, int64_t out_stride, void* stream) {
+                                   int32_t page_size, const int32_t* row_pos_offset, int32_t seg_cols,
+                                   int64_t seg_stride, int32_t* out_idx, float* out_val, int64_t out_stride,
+                                   void* stream) {
   if (n_rows == 0) return B200DSA_OK;
   if (!scores || !out_idx || n_rows < 0 || n_cols < 0 || k < 1 || k > kCandCap || out_stride < k ||
-      row_stride < n_cols) {
+      (seg_cols <= 0 && row_stride < n_cols) || seg_cols < 0) {
     set_last_error("b200dsa_topk_select: bad argument (need 1<=k<=8192, out_stride>=k, row_stride>=n_cols)");
     return B200DSA_EINVAL;
   }
@@ -475,7 +485,8 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
     return B200DSA_EINVAL;
   }
   TopkParams p{scores, row_stride, n_rows, n_cols, col_begin, col_end, k, keep_pos_inf, pos_map, pos_map_stride,
-               page_table, page_table_stride, page_size, row_pos_offset, out_idx, out_val, out_stride, sorted};
+               page_table, page_table_stride, page_size, row_pos_offset, out_idx, out_val, out_stride, sorted,
+               seg_cols, seg_stride};
   int k_pow2 = 32;
   while (k_pow2 < k) k_pow2 <<= 1;
   const size_t smem = kHistBins * sizeof(uint32_t) + (kCandCap + kEqCap + k_pow2) * sizeof(uint64_t);

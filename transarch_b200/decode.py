@@ -1,0 +1,150 @@
+"""Sparse decode step: indexer logits -> top-k -> (key-sharded merge) -> sparse MLA attention
+-> (log-sum-exp combine).
+
+Single GPU: three launches on pre-allocated buffers, nothing is allocated per step.
+
+Key-sharded over N ranks of one box (keys of every request split into N contiguous position
+ranges; rank r owns [r*shard_len, (r+1)*shard_len)): every rank scores and selects inside
+its own range, the per-rank candidate lists (global position, score) are all-gathered,
+every rank selects the same global top-k from the N*k candidates (the union of the shard
+top-k contains the global top-k; ties resolve towards the lowest global position on every
+rank alike), attends the selected keys it owns, and the partial (context, lse) pairs are
+merged: MAX all-reduce of lse, pre-scale, SUM all-reduce of the 516-wide wire rows, divide.
+The query-side inputs are replicated.  The reference has no such path; the idea of local
+queries against position-indexed keys follows OpenDSA's context-parallel forward
+(OpenDSA/opendsa/modeling/dsa_attention.py:620-684).
+
+`backend` is the module providing the kernel wrappers (transarch_b200.kernels by default).
+Host-logic tests on CPU ranks pass a stand-in with the same function names.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class ShardInfo:
+    rank: int = 0
+    world_size: int = 1
+    shard_len: int = 0          # positions per rank (0 = unsharded)
+    group: Optional[object] = None
+
+    @property
+    def pos_lo(self) -> int:
+        return self.rank * self.shard_len if self.world_size > 1 else 0
+
+    @property
+    def pos_hi(self) -> int:
+        return (self.rank + 1) * self.shard_len if self.world_size > 1 else 2 ** 31 - 1
+
+
+def local_context_lens(context_lens: torch.Tensor, shard: ShardInfo) -> torch.Tensor:
+    """Keys of each request that fall into this rank's position range."""
+    if shard.world_size == 1:
+        return context_lens
+    return (context_lens - shard.pos_lo).clamp(min=0, max=shard.shard_len).to(torch.int32)
+
+
+class SparseDecodeStep:
+    """Pre-allocated decode step for a fixed batch size.
+
+    Per-step inputs (device tensors):
+      q_idx   bf16 [B, 64, 128]   index queries        w      fp32 [B, 64] head weights
+      q_lat   bf16 [B, H, 576]    absorbed MLA queries
+    Persistent state (device tensors owned by the caller):
+      k_cache uint8 paged FP8 index-key cache (this rank's pages), block_table int32 [B, pages]
+      context_lens int32 [B] (global lengths), kv bf16 [rows, 576] latent cache (this rank's rows),
+      kv_row_base int64 [B] row of each request's first local position.
+    """
+
+    def __init__(self, batch: int, max_local_ctx: int, *, page_size: int = 64, topk: int = 2048,
+                 n_heads: int = 128, index_scale: float = 128 ** -0.5, attn_scale: float = 192 ** -0.5,
+                 device: Optional[torch.device] = None, shard: Optional[ShardInfo] = None, backend=None,
+                 sorted_topk: bool = False):
+        if backend is None:
+            from . import kernels as backend  # the CUDA kernels; fails loudly without the library
+        self.K = backend
+        self.B, self.topk, self.H, self.P = batch, topk, n_heads, page_size
+        self.index_scale, self.attn_scale = index_scale, attn_scale
+        self.shard = shard or ShardInfo()
+        self.sorted_topk = sorted_topk
+        dev = device if device is not None else torch.device("cuda")
+        self.dev = dev
+        f32, i32 = torch.float32, torch.int32
+        n = self.shard.world_size
+        self.max_cols = max_local_ctx
+        self.logits = torch.empty(batch, max_local_ctx, dtype=f32, device=dev)
+        self.q_fp8 = torch.empty(batch, 64, 128, dtype=torch.float8_e4m3fn, device=dev)
+        self.weights = torch.empty(batch, 64, dtype=f32, device=dev)
+        # candidate wire layout: [B, 2k] int32 = k global positions then k score bit patterns
+        self.cand = torch.empty(batch, 2 * topk, dtype=i32, device=dev)
+        self.pos_offset = torch.full((batch,), self.shard.pos_lo, dtype=i32, device=dev)
+        self.ctx = torch.empty(batch, n_heads, 512, dtype=f32, device=dev)
+        self.lse = torch.empty(batch, n_heads, dtype=f32, device=dev)
+        self.q_pos = torch.empty(batch, dtype=i32, device=dev)
+        if n > 1:
+            self.cand_all = torch.empty(n, batch, 2 * topk, dtype=i32, device=dev)
+            self.merged = torch.empty(batch, topk, dtype=i32, device=dev)
+            self.lse_max = torch.empty(batch, n_heads, dtype=f32, device=dev)
+            self.wire = torch.empty(batch * n_heads, backend.WIRE_ROW, dtype=f32, device=dev)
+            self.ctx_out = torch.empty(batch, n_heads, 512, dtype=f32, device=dev)
+            self.lse_out = torch.empty(batch, n_heads, dtype=f32, device=dev)
+
+    # ------------------------------------------------------------------ stages
+    def select(self, q_idx, w, k_cache, context_lens_local, block_table) -> torch.Tensor:
+        """Indexer + top-k on this rank's keys; returns int32 [B, k] global positions."""
+        K = self.K
+        K.quant_q_fold_weights(q_idx, w, self.index_scale, q_fp8=self.q_fp8, weights=self.weights)
+        K.indexer_paged_fp8_logits(self.q_fp8, self.weights, k_cache, self.P, context_lens_local, block_table,
+                                   max_cols=self.max_cols, out=self.logits)
+        idx = self.cand[:, : self.topk]
+        val = self.cand[:, self.topk:].view(torch.float32)
+        K.topk_select(self.logits, self.topk, col_end=context_lens_local, sorted=self.sorted_topk,
+                      row_pos_offset=self.pos_offset if self.shard.world_size > 1 else None,
+                      out=idx, out_values=val)
+        return idx
+
+    def merge_candidates(self) -> torch.Tensor:
+        """All-gather the per-rank candidates and select the global top-k (identical on every rank)."""
+        n, k = self.shard.world_size, self.topk
+        dist.all_gather_into_tensor(self.cand_all.view(-1), self.cand.view(-1), group=self.shard.group)
+        flat = self.cand_all.view(-1)
+        scores = flat[k:].view(torch.float32)        # segment r, row b starts at r*B*2k + b*2k + k
+        pos = flat                                   # positions start at r*B*2k + b*2k
+        self.K.topk_select(scores.view(1, -1), k, sorted=self.sorted_topk, pos_map=pos.view(1, -1),
+                           out=self.merged, n_cols=n * k, row_stride=2 * k, seg_cols=k,
+                           seg_stride=self.B * 2 * k, n_rows=self.B, pos_map_stride=2 * k)
+        return self.merged
+
+    def attend(self, q_lat, kv, kv_row_base, indices, q_pos) -> Tuple[torch.Tensor, torch.Tensor]:
+        return self.K.sparse_mla_decode(q_lat, kv, indices, self.attn_scale, kv_row_base=kv_row_base, q_pos=q_pos,
+                                        pos_lo=self.shard.pos_lo, pos_hi=self.shard.pos_hi,
+                                        ctx=self.ctx, lse=self.lse)
+
+    def combine(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Merge the per-rank (ctx, lse) partials; every rank ends with the full result."""
+        K, g = self.K, self.shard.group
+        self.lse_max.copy_(self.lse)
+        dist.all_reduce(self.lse_max, op=dist.ReduceOp.MAX, group=g)
+        K.lse_prescale(self.ctx, self.lse, self.lse_max, self.wire)
+        dist.all_reduce(self.wire, op=dist.ReduceOp.SUM, group=g)
+        return K.lse_finalize(self.wire, self.lse_max, self.ctx_out, self.lse_out)
+
+    # ------------------------------------------------------------------ whole step
+    def run(self, q_idx, w, q_lat, k_cache, context_lens, block_table, kv, kv_row_base,
+            context_lens_local: Optional[torch.Tensor] = None):
+        """Returns (indices int32 [B,k] global positions, ctx fp32 [B,H,512], lse fp32 [B,H])."""
+        if context_lens_local is None:
+            context_lens_local = local_context_lens(context_lens, self.shard)
+        idx = self.select(q_idx, w, k_cache, context_lens_local, block_table)
+        if self.shard.world_size > 1:
+            idx = self.merge_candidates()
+        torch.sub(context_lens, 1, out=self.q_pos)
+        ctx, lse = self.attend(q_lat, kv, kv_row_base, idx, self.q_pos)
+        if self.shard.world_size > 1:
+            ctx, lse = self.combine()
+        return idx, ctx, lse

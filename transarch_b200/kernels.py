@@ -27,29 +27,39 @@ def topk_select(scores: torch.Tensor, k: int, *, col_begin: Optional[torch.Tenso
                 col_end: Optional[torch.Tensor] = None, keep_pos_inf: bool = False,
                 pos_map: Optional[torch.Tensor] = None, page_table: Optional[torch.Tensor] = None,
                 page_size: int = 0, row_pos_offset: Optional[torch.Tensor] = None,
-                sorted: bool = True, return_values: bool = False, out: Optional[torch.Tensor] = None):
+                sorted: bool = True, return_values: bool = False, out: Optional[torch.Tensor] = None,
+                out_values: Optional[torch.Tensor] = None, seg_cols: int = 0, seg_stride: int = 0,
+                n_cols: Optional[int] = None, row_stride: Optional[int] = None,
+                n_rows: Optional[int] = None, pos_map_stride: Optional[int] = None):
     """Row-wise top-k positions (int32, -1 padded; descending score when sorted); see
     b200dsa_topk_select."""
     require_cuda(scores, col_begin, col_end, pos_map, page_table, row_pos_offset)
     if scores.dtype != torch.float32 or scores.dim() != 2 or scores.stride(1) != 1:
         raise _lib.B200DSAError("scores must be a 2-D fp32 tensor with unit column stride")
-    n_rows, n_cols = scores.shape
+    n_rows = scores.shape[0] if n_rows is None else n_rows
+    n_cols = scores.shape[1] if n_cols is None else n_cols
+    row_stride = scores.stride(0) if row_stride is None else row_stride
     if out is None:
         out = torch.empty(n_rows, k, dtype=torch.int32, device=scores.device)
     elif out.dtype != torch.int32 or out.stride(1) != 1 or out.shape[0] < n_rows or out.shape[1] < k:
         raise _lib.B200DSAError("out must be int32 [>=n_rows, >=k] with unit column stride")
-    vals = torch.empty(n_rows, out.stride(0), dtype=torch.float32, device=scores.device) if return_values else None
+    vals = out_values
+    if vals is None and return_values:
+        vals = torch.empty(n_rows, out.stride(0), dtype=torch.float32, device=scores.device)
+    if vals is not None and (vals.dtype != torch.float32 or vals.stride(0) != out.stride(0)):
+        raise _lib.B200DSAError("out_values must be fp32 with the row stride of out")
     lib = _lib.load()
     rc = lib.b200dsa_topk_select(
-        ptr(scores), scores.stride(0), n_rows, n_cols,
+        ptr(scores), row_stride, n_rows, n_cols,
         ptr(_i32(col_begin, "col_begin")), ptr(_i32(col_end, "col_end")), k, int(keep_pos_inf), int(sorted),
-        ptr(_i32(pos_map, "pos_map")), pos_map.stride(0) if pos_map is not None else 0,
+        ptr(_i32(pos_map, "pos_map")),
+        (pos_map_stride if pos_map_stride is not None else pos_map.stride(0)) if pos_map is not None else 0,
         ptr(_i32(page_table, "page_table")), page_table.stride(0) if page_table is not None else 0, page_size,
-        ptr(_i32(row_pos_offset, "row_pos_offset")),
+        ptr(_i32(row_pos_offset, "row_pos_offset")), seg_cols, seg_stride,
         ptr(out), ptr(vals), out.stride(0), stream_ptr())
     check(rc, "b200dsa_topk_select")
-    if return_values:
-        return out[:n_rows, :k], vals[:, :k]
+    if return_values or out_values is not None:
+        return out[:n_rows, :k], vals[:n_rows, :k]
     return out[:n_rows, :k]
 
 
@@ -144,3 +154,68 @@ def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, 
         ptr(q_pos), pos_lo, pos_hi, n, H, sm_scale, ptr(ctx), ptr(lse), ptr(status_word(q.device)), stream_ptr())
     check(rc, "b200dsa_sparse_mla_decode")
     return ctx, lse
+
+
+def lse_combine(ctx_parts: torch.Tensor, lse_parts: torch.Tensor, *, ctx_out: Optional[torch.Tensor] = None,
+                lse_out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Merge partials [R, ..., 512] / [R, ...] over R disjoint key sets; see b200dsa_lse_combine."""
+    require_cuda(ctx_parts, lse_parts)
+    if ctx_parts.dtype != torch.float32 or lse_parts.dtype != torch.float32 or \
+            not ctx_parts.is_contiguous() or not lse_parts.is_contiguous() or ctx_parts.shape[-1] != 512:
+        raise _lib.B200DSAError("partials must be contiguous fp32 [R, ..., 512] and [R, ...]")
+    R = ctx_parts.shape[0]
+    n_rows = lse_parts[0].numel()
+    if ctx_out is None:
+        ctx_out = torch.empty(ctx_parts.shape[1:], dtype=torch.float32, device=ctx_parts.device)
+    if lse_out is None:
+        lse_out = torch.empty(lse_parts.shape[1:], dtype=torch.float32, device=ctx_parts.device)
+    rc = _lib.load().b200dsa_lse_combine(ptr(ctx_parts), ptr(lse_parts), R, n_rows, ptr(ctx_out), ptr(lse_out),
+                                         stream_ptr())
+    check(rc, "b200dsa_lse_combine")
+    return ctx_out, lse_out
+
+
+def quant_q_fold_weights(q: torch.Tensor, w: torch.Tensor, fold: float, *, q_fp8: Optional[torch.Tensor] = None,
+                         weights: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(q_fp8 [..., H, 128] e4m3, weights [..., H] fp32) with the per-(token, head) scale folded
+    into the weights; see b200dsa_quant_q_fold_weights."""
+    require_cuda(q, w)
+    if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.shape[-1] != 128:
+        raise _lib.B200DSAError("q must be contiguous bf16 [..., 128]")
+    n_rows = q.numel() // 128
+    if w.dtype != torch.float32 or not w.is_contiguous() or w.numel() != n_rows:
+        raise _lib.B200DSAError("w must be contiguous fp32 with one entry per (token, head)")
+    if q_fp8 is None:
+        q_fp8 = torch.empty(q.shape, dtype=torch.float8_e4m3fn, device=q.device)
+    if weights is None:
+        weights = torch.empty(w.shape, dtype=torch.float32, device=q.device)
+    rc = _lib.load().b200dsa_quant_q_fold_weights(ptr(q), ptr(w), n_rows, fold, ptr(q_fp8), ptr(weights),
+                                                  stream_ptr())
+    check(rc, "b200dsa_quant_q_fold_weights")
+    return q_fp8, weights
+
+
+WIRE_ROW = 516  # floats per (item, head) row of the all-reduce wire buffer
+
+
+def lse_prescale(ctx: torch.Tensor, lse: torch.Tensor, lse_max: torch.Tensor, wire: torch.Tensor) -> torch.Tensor:
+    """wire[row] = (ctx*exp(lse-lse_max), exp(lse-lse_max), 0, 0, 0); see b200dsa_lse_prescale."""
+    require_cuda(ctx, lse, lse_max, wire)
+    n_rows = lse.numel()
+    for t_, nm in ((ctx, "ctx"), (lse, "lse"), (lse_max, "lse_max"), (wire, "wire")):
+        if t_.dtype != torch.float32 or not t_.is_contiguous():
+            raise _lib.B200DSAError(f"{nm} must be contiguous fp32")
+    if ctx.numel() != n_rows * 512 or wire.numel() != n_rows * WIRE_ROW:
+        raise _lib.B200DSAError("ctx must hold 512 and wire 516 floats per row")
+    check(_lib.load().b200dsa_lse_prescale(ptr(ctx), ptr(lse), ptr(lse_max), n_rows, ptr(wire), stream_ptr()),
+          "b200dsa_lse_prescale")
+    return wire
+
+
+def lse_finalize(wire: torch.Tensor, lse_max: torch.Tensor, ctx_out: torch.Tensor, lse_out: torch.Tensor):
+    """Divide the summed wire rows by the summed weight; see b200dsa_lse_finalize."""
+    require_cuda(wire, lse_max, ctx_out, lse_out)
+    n_rows = lse_max.numel()
+    check(_lib.load().b200dsa_lse_finalize(ptr(wire), ptr(lse_max), n_rows, ptr(ctx_out), ptr(lse_out),
+                                            stream_ptr()), "b200dsa_lse_finalize")
+    return ctx_out, lse_out
