@@ -1,0 +1,321 @@
+"""Benchmark of the sparse decode step (indexer -> top-k -> sparse MLA attention).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload: batch 64 requests at context 131072, one query token each, 64 index heads (d=128)
+over an FP8 paged index-key cache, top-2048 selection, sparse MLA attention over 576-wide bf16
+latent rows with 128 heads.  With N > 1 (launched by torch.distributed.run) the key range is
+sharded over the ranks; total work is fixed ("strong" scaling).  One JSON line is printed by
+rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BATCH = 64
+CONTEXT = 131072
+HEADS = 128
+TOPK = 2048
+PAGE = 64
+INDEX_SCALE = 128 ** -0.5
+ATTN_SCALE = 192 ** -0.5
+# DRAM bytes (read + write) per scored key of the indexer kernel, from the ncu capture summarised
+# in profiles/indexer_paged_fp8_ncu.md (traffic grows in proportion to the number of keys).
+DRAM_BYTES_PER_KEY = 138.3
+METRIC = "sparse_mla_decode_tokens_per_s"
+WORKLOAD = ("sparse MLA decode, key-sharded: batch 64, context 131072, 64 index heads d=128, FP8 paged "
+            "index keys (page 64) with per-token scale, top-2048, 128 heads over 576-wide bf16 latent KV")
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows = []
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                mhz.append(float(r[0])); mx = float(r[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def cpu_port_tokens_per_s(n_requests: int, context: int, threads: int):
+    """Times the CPU oracle (a port of the reference's PyTorch ops) on n_requests requests of
+    the benchmark's shape.  Returns (tokens/s, seconds)."""
+    from oracle import dsa_oracle as O
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(4)
+    k = torch.randn(context, 128, generator=g)
+    kq, sc = O.quant_fp8_rows(k)
+    kd = kq.float() * sc.unsqueeze(-1)
+    kv = (0.5 * torch.randn(context, 576, generator=g)).bfloat16().float()
+    q = torch.randn(n_requests, 64, 128, generator=g)
+    w = torch.randn(n_requests, 64, generator=g) / 8
+    q_lat = torch.randn(n_requests, HEADS, 576, generator=g)
+    t0 = time.perf_counter()
+    for b in range(n_requests):
+        q_fp8, wf = O.quant_q_fold_weights(q[b:b + 1], w[b:b + 1], INDEX_SCALE)
+        s = O.indexer_scores(q_fp8.float(), kd, wf, 1.0)
+        idx = O.topk_rows(s, TOPK)
+        O.sparse_attend_latent(q_lat[b:b + 1], kv, idx, d_c=512, sm_scale=ATTN_SCALE,
+                               q_pos=torch.tensor([context - 1]))
+    dt = time.perf_counter() - t0
+    return n_requests / dt, dt
+
+
+def run_reference(args, rank: int):
+    """Reference arm: the reference's own implementation of this path is PyTorch on the host
+    cores; it cannot travel to the GPU box, so its CPU port (the oracle) is timed here."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    _, dt4 = cpu_port_tokens_per_s(4, CONTEXT, threads)              # calibrate: about 2 s per step
+    n_req = max(4, min(256, int(2.0 / max(dt4 / 4, 1e-4))))
+    for _ in range(min(args.warmup, 2)):
+        cpu_port_tokens_per_s(n_req, CONTEXT, threads)
+    args.steps = min(args.steps, 20)                                  # keep the whole arm within a few minutes
+    vals, secs = [], 0.0
+    for _ in range(args.steps):
+        v, dt = cpu_port_tokens_per_s(n_req, CONTEXT, threads)
+        vals.append(v); secs += dt
+    value = sum(vals) / len(vals)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * secs / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"{n_req} of 64 requests per step at context {CONTEXT}, all stages"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch.distributed as dist
+    from transarch_b200 import _lib
+    from transarch_b200.decode import ShardInfo, SparseDecodeStep
+    from transarch_b200.workloads import make_decode_queries, make_decode_state
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    B, ctx = args.batch, args.context
+    assert ctx % (world * PAGE) == 0
+    shard_len = ctx // world
+    shard = ShardInfo(rank=rank, world_size=world, shard_len=shard_len, group=group)
+    state = make_decode_state(B, ctx, page_size=PAGE, seed=4, rank=rank, world_size=world, shard_len=shard_len,
+                              device=dev)
+    step = SparseDecodeStep(B, shard_len, page_size=PAGE, topk=TOPK, n_heads=HEADS, index_scale=INDEX_SCALE,
+                            attn_scale=ATTN_SCALE, device=dev, shard=shard)
+    n_sets = 4  # rotating query sets so consecutive steps differ
+    dev_q = [make_decode_queries(B, HEADS, seed=100 + i, device=dev) for i in range(n_sets)]
+    host_q = [make_decode_queries(B, HEADS, seed=100 + i, pinned=True) for i in range(n_sets)]
+    stage_q = [torch.empty_like(t, device=dev) for t in dev_q[0]]
+    host_idx = torch.empty(B, TOPK, dtype=torch.int32).pin_memory()
+    host_ctx = torch.empty(B, HEADS, 512, dtype=torch.float32).pin_memory()
+
+    def run_device(i):
+        q_idx, w, q_lat = dev_q[i % n_sets]
+        return step.run(q_idx, w, q_lat, state.k_cache, state.context_lens, state.block_table, state.kv,
+                        state.kv_row_base, state.context_lens_local)
+
+    def run_e2e(i):
+        for dst, src in zip(stage_q, host_q[i % n_sets]):
+            dst.copy_(src, non_blocking=True)
+        idx, c, _ = step.run(stage_q[0], stage_q[1], stage_q[2], state.k_cache, state.context_lens,
+                             state.block_table, state.kv, state.kv_row_base, state.context_lens_local)
+        host_idx.copy_(idx, non_blocking=True)
+        host_ctx.copy_(c, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, stage_events=None):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        sync_all()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for i in range(max(args.warmup, 3)):
+        run_device(i)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    total_ms = timed(run_device, args.steps)
+    if rank == 0 and len(sampler.rows) < 3:      # very short timed region: sample a repeat of it as well
+        timed(run_device, max(args.steps, 500))
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = total_ms / args.steps
+    value = B * args.steps / (total_ms * 1e-3)
+
+    # per-stage device times inside a second timed region (events around each launch)
+    stage_ms = {"quant+indexer": 0.0, "topk": 0.0, "attention+merge": 0.0}
+    sync_all()
+    for i in range(args.steps):
+        q_idx, w, q_lat = dev_q[i % n_sets]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        ev[0].record()
+        K = step.K
+        K.quant_q_fold_weights(q_idx, w, step.index_scale, q_fp8=step.q_fp8, weights=step.weights)
+        ev_i0 = torch.cuda.Event(enable_timing=True); ev_i0.record()
+        K.indexer_paged_fp8_logits(step.q_fp8, step.weights, state.k_cache, PAGE, state.context_lens_local,
+                                   state.block_table, max_cols=step.max_cols, out=step.logits)
+        ev[1].record()
+        K.topk_select(step.logits, TOPK, col_end=state.context_lens_local, sorted=False,
+                      out=step.cand[:, :TOPK], out_values=step.cand[:, TOPK:].view(torch.float32),
+                      row_pos_offset=step.pos_offset if world > 1 else None)
+        ev[2].record()
+        idx = step.merge_candidates() if world > 1 else step.cand[:, :TOPK]
+        torch.sub(state.context_lens, 1, out=step.q_pos)
+        step.attend(q_lat, state.kv, state.kv_row_base, idx, step.q_pos)
+        if world > 1:
+            step.combine()
+        ev[3].record()
+        torch.cuda.synchronize()
+        stage_ms["quant+indexer"] += ev[0].elapsed_time(ev[1])
+        stage_ms["topk"] += ev[1].elapsed_time(ev[2])
+        stage_ms["attention+merge"] += ev[2].elapsed_time(ev[3])
+        stage_ms.setdefault("indexer", 0.0)
+        stage_ms["indexer"] += ev_i0.elapsed_time(ev[1])
+    for k_ in stage_ms:
+        stage_ms[k_] /= args.steps
+
+    for i in range(3):
+        run_e2e(i)
+    e2e_ms = timed(run_e2e, args.steps)
+    e2e_value = B * args.steps / (e2e_ms * 1e-3)
+    status = _lib.read_status(dev)
+
+    if rank == 0:
+        peaks, peak_kind = measured_peaks()
+        idx_bytes = B * shard_len * (128 + 4)  # fp8 key + fp32 scale per key, read once
+        achieved = idx_bytes / (stage_ms["indexer"] * 1e-3) / 1e9
+        h2d = sum(t.numel() * t.element_size() for t in host_q[0])
+        d2h = host_idx.numel() * 4 + host_ctx.numel() * 4
+        launches = 4 if world == 1 else 7
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp8(e4m3) index scores / bf16 attention, fp32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD if (B, ctx) == (BATCH, CONTEXT) else f"batch {B}, context {ctx} (non-default)",
+                       "parallelism": f"key-sharded x{world}",
+                       "l2": "inputs larger than L2 (index-key cache %.2f GB per GPU, 4 rotating query sets)"
+                             % (idx_bytes / 1e9)},
+            "indexer_topk_us_per_step": 1e3 * (stage_ms["quant+indexer"] + stage_ms["topk"]),
+            "stage_us": {k_: round(1e3 * v, 2) for k_, v in stage_ms.items()},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches * args.steps,
+            "roofline": {"kernel": "indexer_paged_kernel<fp8>", "bound": "hbm", "achieved": achieved,
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                         "peak_source": peak_kind, "traffic": None},
+            "clocks": clocks, "status_word": status,
+        }
+        line["roofline"]["traffic"] = DRAM_BYTES_PER_KEY * B * shard_len
+        if world == 1 and not args.skip_cpu_baseline:
+            threads = os.cpu_count() or 1
+            _, dt4 = cpu_port_tokens_per_s(4, ctx, threads)          # calibrate: about 10 s of CPU work
+            n_req = max(4, min(1024, int(10.0 / max(dt4 / 4, 1e-4))))
+            v, dt = cpu_port_tokens_per_s(n_req, ctx, threads)
+            line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                    "sample": f"{n_req} requests of the {B}-request batch shape at context {ctx}, "
+                                              f"all stages (quantise, score, top-k, attention), {dt:.1f} s"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
