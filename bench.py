@@ -234,7 +234,7 @@ def main():
     if rank == 0:
         sampler.start()
     total_ms = timed(run_device, args.steps)
-    if rank == 0 and len(sampler.rows) < 3:      # very short timed region: sample a repeat of it as well
+    if total_ms < 150.0:                         # very short timed region: sample a longer repeat as well
         timed(run_device, max(args.steps, 500))
     clocks = sampler.stop() if rank == 0 else None
     ms_per_step = total_ms / args.steps

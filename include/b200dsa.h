@@ -174,6 +174,49 @@ int b200dsa_lse_finalize(const float* wire, const float* lse_max, int64_t n_rows
 int b200dsa_quant_q_fold_weights(const void* q_bf16, const float* w, int64_t n_rows, float fold,
                                  void* q_fp8, float* weights, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Block mean pooling of index keys: pooled[j] = mean(keys[j*block : min((j+1)*block, n)]),
+ * fp32 accumulation, the tail block divided by its true length.
+ * Replaces MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/block_ops.py:685-754
+ * (block_mean_pooling + interface; output cast back to bf16 as at :752) and, for the paged
+ * FP8 cache, :381-486 (paged_mean_pooling: fp32 [n_requests, max_pool_blocks, 128], blocks
+ * beyond a request's context are zero).  Either output pointer of the bf16 variant may be NULL.
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_block_mean_pool_bf16(const void* keys_bf16, int32_t n_keys, int32_t block, void* out_bf16,
+                                 float* out_f32, void* stream);
+int b200dsa_paged_mean_pool_fp8(const void* cache, int32_t num_pages, int32_t page_size,
+                                const int32_t* context_lens, const int32_t* block_table,
+                                int64_t block_table_stride, int32_t n_requests, int32_t block,
+                                int32_t max_pool_blocks, float* out, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * MISA head routers.  Each writes head_idx [n_tokens, n_keep] int32 (descending router score,
+ * ties to the lowest head) and weights_out [n_tokens, 64] fp32 that is zero on dropped heads,
+ * so the 64-head indexer entry points apply the gating through their weight operand.
+ *
+ *  qnorm      : largest ||q[t,h,:]||_2; kept heads keep w[t,h].  Reference:
+ *               MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/misa_deepseek_v2.py:254-266
+ *               with the weight gather of misa_ops.py:703-705.
+ *  block_score: largest sum over pooled key blocks j in [blk_lo[t], blk_hi[t]) of
+ *               |w[t,h]*relu(<q[t,h,:], pooled[set(t), j, :]>)|; kept heads keep w[t,h].
+ *               Reference: block_ops.py:488-573 (prefill) and :11-98 (decode), consumed at
+ *               misa_ops.py:694-705 and :380-388.  pooled_keys is fp32 [n_sets, pooled_set_stride/128, 128];
+ *               pooled_set (optional) maps a token to its set (decode: the request).
+ *  linear     : logits = x[t,:] @ W_r (bf16 inputs, fp32 accumulate), top-n heads, weights =
+ *               softmax over the kept logits.  No counterpart in the reference (the router the
+ *               benchmark configuration describes); logits_out optional.
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_router_qnorm_topk(const void* q_bf16, const float* w, int32_t n_tokens, int32_t n_keep,
+                              float* weights_out, int32_t* head_idx, void* stream);
+int b200dsa_router_block_score_topk(const void* q_bf16, const float* w, const float* pooled_keys,
+                                    int64_t pooled_set_stride, const int32_t* pooled_set,
+                                    const int32_t* blk_lo, const int32_t* blk_hi, int32_t n_tokens,
+                                    int32_t n_keep, float* weights_out, int32_t* head_idx,
+                                    float* scores_out, void* stream);
+int b200dsa_router_linear_topk_softmax(const void* x_bf16, const void* w_r_bf16, int32_t n_tokens,
+                                       int32_t hidden, int32_t n_keep, float* weights_out,
+                                       int32_t* head_idx, float* logits_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

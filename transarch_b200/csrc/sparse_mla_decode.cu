@@ -5,39 +5,45 @@
 //   ctx[h,:] = sum_j p[h, j] * kv[idx_j, 0:512]                    (latent-space context)
 //   lse[h]   = log sum_j exp(s[h, j])
 //
-// Work split: CTA (item, half) computes all heads of one item for value dims
-// [256*half, 256*half+256).  Heads are the UMMA M dimension (one TMEM lane and one softmax
-// thread per head, so row max / row sum are thread-local), 32 gathered keys are N of the
-// score MMA and K of the value MMA.  The 576-wide rows are gathered with 16-byte cp.async
-// into the 128-byte-swizzled K-major layout the score MMA reads; the same bytes serve,
-// read MN-major, as the value operand.  Q (128 x 576 bf16) stays in shared memory.
+// Work split: CTA (item, hh) computes heads [64*hh, 64*hh+64) of one item over all selected
+// keys.  Heads are the UMMA M dimension (M = 64: an accumulator row m lives in TMEM lane
+// 32*(m/16) + m%16, i.e. the lower half of each 32-lane sub-partition), 64 gathered keys are
+// N of the score MMA and K of the value MMA.  The O accumulator (64 x 512) fills all 512
+// columns on the lower half-lanes; the two score buffers sit on the upper half-lanes
+// (lane offset 16) of columns 0..127, so both fit at once.  The 576-wide rows are gathered
+// with 16-byte cp.async into the 128-byte-swizzled K-major layout the score MMA reads; the
+// same bytes serve, read MN-major, as the value operand.  Q (64 x 576 bf16) stays in shared
+// memory.  Softmax: lane 16+i of warp 4+w owns head row 16w+i (row max / sum are
+// thread-local); lane i of the same warp owns that row of O.
 //
-// TMEM: O accumulator 256 columns + two 32-column score buffers.
-// Roles (288 threads): warps 0-3 gather, warps 4-7 softmax (warp w owns TMEM lanes
-// 32*(w%4)..), warp 8 issues MMAs.  All waits are bounded.
+// Roles (288 threads): warps 0-3 gather, warps 4-7 softmax, warp 8 issues MMAs.  All waits
+// are bounded.
 #include <cuda_bf16.h>
 
 #include "b200dsa_common.cuh"
 
 namespace b200dsa {
 
-constexpr int kMlaHeadsTile = 128;
+constexpr int kMlaHeadsTile = 64;    // heads per CTA (UMMA M)
+constexpr int kMlaMaxHeads = 128;
 constexpr int kMlaD = 576;          // latent width (512 value dims + 64 rope dims)
 constexpr int kMlaDv = 512;
-constexpr int kMlaDvHalf = 256;
 constexpr int kMlaChunks = 9;       // 576 / 64 elements (128-byte chunks)
-constexpr int kMlaTile = 32;        // keys per tile
-constexpr int kMlaStages = 2;
 constexpr int kMlaThreads = 288;
-constexpr int kMlaQBytes = kMlaHeadsTile * kMlaD * 2;            // 147456
-constexpr int kMlaChunkBytesQ = kMlaHeadsTile * 128;             // 16384 per 64-wide chunk
-constexpr int kMlaStageBytes = kMlaTile * kMlaD * 2;             // 36864
-constexpr int kMlaChunkBytesK = kMlaTile * 128;                  // 4096
-constexpr int kMlaPBytes = kMlaHeadsTile * kMlaTile * 2;         // 8192
+constexpr int kMlaQBytes = kMlaHeadsTile * kMlaD * 2;            // 73728
+constexpr int kMlaChunkBytesQ = kMlaHeadsTile * 128;             // 8192 per 64-wide chunk
+// keys per tile and gather pipeline depth: smaller tiles allow more row gathers in flight
+constexpr int kMlaTile = 32;
+constexpr int kMlaStages = 4;
+constexpr int kMlaStageBytes = kMlaTile * kMlaD * 2;
+constexpr int kMlaChunkBytesK = kMlaTile * 128;
+constexpr int kMlaPBytes = kMlaHeadsTile * kMlaTile * 2;
 constexpr int kMlaSmemBytes = kMlaQBytes + kMlaStages * kMlaStageBytes + kMlaPBytes + 1024 + 256;
+constexpr int kMlaTpr = 128 / kMlaTile;                          // gather threads per key row
+static_assert(kMlaTile == 32 || kMlaTile == 64, "tile must be 32 or 64 keys");
 constexpr uint32_t kMlaTmemCols = 512;
-constexpr uint32_t kMlaTmemO = 0;
-constexpr uint32_t kMlaTmemS = 256;  // two buffers: 256, 288
+constexpr uint32_t kMlaTmemO = 0;                 // lanes 0-15 of every sub-partition, columns 0..511
+constexpr uint32_t kMlaTmemS = (16u << 16);       // lanes 16-31 of every sub-partition, columns 0..127
 
 struct MlaParams {
   const __nv_bfloat16* kv;     // [kv_rows, 576]
@@ -105,7 +111,11 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
   extern __shared__ uint8_t smem_dyn[];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
-  __shared__ uint32_t s_mask[kMlaStages];  // one validity bit per key of the stage, byte w from gather warp w
+  __shared__ uint32_t s_mask[kMlaStages][2];  // validity bit per key of the stage
+
+  const int item = blockIdx.x >> 1;
+  const int hh = blockIdx.x & 1;
+  if (hh * kMlaHeadsTile >= p.n_heads) return;  // nothing to do for this head half (whole CTA)
 
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_dyn + (smem_base - smem_u32(smem_dyn));
@@ -113,28 +123,28 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
   const uint32_t kv_addr = smem_base + kMlaQBytes;
   const uint32_t p_addr = kv_addr + kMlaStages * kMlaStageBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + kMlaQBytes + kMlaStages * kMlaStageBytes + kMlaPBytes);
-  uint64_t* q_full = bars;          // [1]
-  uint64_t* kv_full = bars + 1;     // [2] 128 gather threads
-  uint64_t* kv_empty = bars + 3;    // [2] value MMA retired
-  uint64_t* s_full = bars + 5;      // [2] score MMA retired
-  uint64_t* s_empty = bars + 7;     // [2] 128 softmax threads have read the scores
-  uint64_t* p_full = bars + 9;      // [1] 128 softmax threads wrote P
-  uint64_t* pv_done = bars + 10;    // [1] value MMA retired (P buffer free, O stable)
+  uint64_t* q_full = bars;                       // [1]
+  uint64_t* s_full = bars + 1;                   // [2] score MMA retired
+  uint64_t* s_empty = bars + 3;                  // [2] 128 softmax-warp threads have read the scores
+  uint64_t* p_full = bars + 5;                   // [1] 128 softmax-warp threads: P written
+  uint64_t* pv_done = bars + 6;                  // [1] value MMA retired (P buffer free, O stable)
+  uint64_t* kv_full = bars + 7;                  // [stages] 128 gather threads (arrivals of their copies)
+  uint64_t* kv_empty = bars + 7 + kMlaStages;    // [stages] value MMA retired
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int item = blockIdx.x >> 1;
-  const int half = blockIdx.x & 1;
   const int n_tiles = (p.n_idx + kMlaTile - 1) / kMlaTile;
   volatile int* abort_flag = &s_abort;
 
   if (tid == 0) {
     s_abort = 0;
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kMlaStages; ++s) {
       mbar_init(&kv_full[s], 128);
       mbar_init(&kv_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
       mbar_init(&s_empty[s], 128);
     }
@@ -156,12 +166,12 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
 
   if (warp < 4) {
     // ------------------------------------------------------------------ gather producers
-    const int r = tid >> 2;        // key row of the tile
-    const int sub = tid & 3;
+    const int r = tid / kMlaTpr;   // key row of the tile
+    const int sub = tid % kMlaTpr;
     const int32_t* idx_row = p.indices + static_cast<int64_t>(item) * p.idx_stride;
     for (int t = 0; t < n_tiles; ++t) {
-      const int s = t & 1;
-      const bool ok = mbar_wait(&kv_empty[s], ((t >> 1) & 1) ^ 1, abort_flag);
+      const int s = t % kMlaStages;
+      const bool ok = mbar_wait(&kv_empty[s], ((t / kMlaStages) & 1) ^ 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) break;
       const int j = t * kMlaTile + r;
       const int idx = (j < p.n_idx) ? __ldg(idx_row + j) : -1;
@@ -174,17 +184,18 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
       const uint8_t* src = reinterpret_cast<const uint8_t*>(p.kv) + (valid ? grow : 0) * (kMlaD * 2);
       const uint32_t dst_row = kv_addr + s * kMlaStageBytes + r * 128;
 #pragma unroll
-      for (int u = 0; u < 18; ++u) {
-        const int c16 = sub + 4 * u;           // 16-byte chunk of the 1152-byte row
+      for (int u = 0; u < 72 / kMlaTpr; ++u) {
+        const int c16 = sub + kMlaTpr * u;     // 16-byte chunk of the 1152-byte row
         const int c = c16 >> 3, w = c16 & 7;   // 128-byte chunk, position inside it
         cp_async_16(dst_row + c * kMlaChunkBytesK + ((w ^ (r & 7)) << 4), src + c16 * 16, valid);
       }
       const unsigned b = __ballot_sync(0xffffffffu, valid && sub == 0);
       if (lane == 0) {
-        uint32_t m8 = 0;
+        uint32_t mw = 0;  // one bit per row this warp gathers
 #pragma unroll
-        for (int rr = 0; rr < 8; ++rr) m8 |= ((b >> (4 * rr)) & 1u) << rr;
-        reinterpret_cast<volatile uint8_t*>(&s_mask[s])[warp] = static_cast<uint8_t>(m8);
+        for (int rr = 0; rr < 32 / kMlaTpr; ++rr) mw |= ((b >> (kMlaTpr * rr)) & 1u) << rr;
+        if constexpr (kMlaTpr == 2) reinterpret_cast<volatile uint16_t*>(&s_mask[s][0])[warp] = static_cast<uint16_t>(mw);
+        else reinterpret_cast<volatile uint8_t*>(&s_mask[s][0])[warp] = static_cast<uint8_t>(mw);
       }
       __threadfence_block();
       __syncwarp();
@@ -193,9 +204,12 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
     }
     cp_async_wait_all();
   } else if (warp < 8) {
-    // ------------------------------------------------------------------ softmax, one head per thread
-    const int head = (warp & 3) * 32 + lane;
-    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    // ------------------------------------------------------------------ softmax
+    // lanes 16..31: score row `row`; lanes 0..15: the same row of O (partner lane = lane ^ 16)
+    const int wq = warp & 3;
+    const int row = wq * 16 + (lane & 15);          // head row inside this CTA's 64
+    const bool is_s = lane >= 16;
+    const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;  // sub-partition base lane
     float m_ref = -INFINITY, l = 0.f;
     bool aborted = false;
     for (int t = 0; t < n_tiles; ++t) {
@@ -203,83 +217,114 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
       bool ok = mbar_wait(&s_full[sb], (t >> 1) & 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) { aborted = true; break; }
       tc_fence_after();
-      uint32_t v[32];
-      tmem_ld_32x32(tmem_base + lane_addr + kMlaTmemS + sb * kMlaTile, v);
+      const int ks = t % kMlaStages;
+      uint32_t v0[32], v1[32];
+      tmem_ld_32x32(tmem_base + lane_addr + sb * kMlaTile, v0);       // lanes 16-31 receive the score rows
+      if constexpr (kMlaTile == 64) {
+        tmem_ld_32x32(tmem_base + lane_addr + sb * kMlaTile + 32, v1);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v1[j] = 0;
+      }
       tc_wait_ld();
       tc_fence_before();
       mbar_arrive(&s_empty[sb]);
-      const uint32_t mask = s_mask[sb];
-      float x[32];
+      const uint32_t mask0 = s_mask[ks][0], mask1 = (kMlaTile == 64) ? s_mask[ks][1] : 0u;
       float mt = -INFINITY;
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
-        x[j] = ((mask >> j) & 1u) ? __uint_as_float(v[j]) * p.scale_log2 : -INFINITY;
-        mt = fmaxf(mt, x[j]);
+        const float a = ((mask0 >> j) & 1u) ? __uint_as_float(v0[j]) * p.scale_log2 : -INFINITY;
+        const float b2 = ((mask1 >> j) & 1u) ? __uint_as_float(v1[j]) * p.scale_log2 : -INFINITY;
+        v0[j] = __float_as_uint(a);
+        v1[j] = __float_as_uint(b2);
+        mt = fmaxf(mt, fmaxf(a, b2));
       }
+      if (!is_s) mt = -INFINITY;
       bool waited_pv = false;
       // lazy rescale: only when the running maximum grows by more than 2^8
-      const bool grow = mt > m_ref + 8.0f;
+      const bool grow = is_s && (mt > m_ref + 8.0f);
       if (__any_sync(0xffffffffu, grow) && t > 0) {
         ok = mbar_wait(pv_done, (t - 1) & 1, abort_flag);
         if (!__all_sync(0xffffffffu, ok)) { aborted = true; break; }
         waited_pv = true;
+        if (t + 1 < n_tiles) {
+          // the write-back below also touches the upper half-lanes of columns 0..127, where the
+          // next tile's scores may still be landing: let that MMA finish first
+          ok = mbar_wait(&s_full[(t + 1) & 1], ((t + 1) >> 1) & 1, abort_flag);
+          if (!__all_sync(0xffffffffu, ok)) { aborted = true; break; }
+        }
         tc_fence_after();
-        const float f = grow ? ((m_ref == -INFINITY) ? 0.f : exp2f(m_ref - mt)) : 1.0f;
+        float f = grow ? ((m_ref == -INFINITY) ? 0.f : exp2f(m_ref - mt)) : 1.0f;
+        if (is_s) l *= f;
+        f = __shfl_xor_sync(0xffffffffu, f, 16);   // O-row lanes take the factor of their partner
 #pragma unroll 1
-        for (int c = 0; c < kMlaDvHalf / 32; ++c) {
+        for (int c = 0; c < kMlaDv / 32; ++c) {
           uint32_t o[32];
           tmem_ld_32x32(tmem_base + lane_addr + kMlaTmemO + c * 32, o);
           tc_wait_ld();
+          if (!is_s) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * f);
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * f);
+          }
+          // upper lanes write back what they read (score buffers and unused cells)
           tmem_st_32x32(tmem_base + lane_addr + kMlaTmemO + c * 32, o);
         }
         tc_wait_st();
         tc_fence_before();
-        l *= f;
       }
       if (grow) m_ref = mt;
-      uint32_t pk[16];
+      uint32_t pk[32];
       float lsum = 0.f;
 #pragma unroll
       for (int j = 0; j < 32; j += 2) {
-        const float p0 = (x[j] == -INFINITY) ? 0.f : exp2f(x[j] - m_ref);
-        const float p1 = (x[j + 1] == -INFINITY) ? 0.f : exp2f(x[j + 1] - m_ref);
-        lsum += p0 + p1;
-        __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-        pk[j >> 1] = *reinterpret_cast<uint32_t*>(&h2);
+        const float a0 = __uint_as_float(v0[j]), a1 = __uint_as_float(v0[j + 1]);
+        const float b0 = __uint_as_float(v1[j]), b1 = __uint_as_float(v1[j + 1]);
+        const float p0 = (a0 == -INFINITY) ? 0.f : exp2f(a0 - m_ref);
+        const float p1 = (a1 == -INFINITY) ? 0.f : exp2f(a1 - m_ref);
+        const float p2 = (b0 == -INFINITY) ? 0.f : exp2f(b0 - m_ref);
+        const float p3 = (b1 == -INFINITY) ? 0.f : exp2f(b1 - m_ref);
+        lsum += (p0 + p1) + (p2 + p3);
+        __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1);
+        __nv_bfloat162 h23 = __floats2bfloat162_rn(p2, p3);
+        pk[j >> 1] = *reinterpret_cast<uint32_t*>(&h01);
+        pk[16 + (j >> 1)] = *reinterpret_cast<uint32_t*>(&h23);
       }
-      l += lsum;
+      if (is_s) l += lsum;
       if (t > 0 && !waited_pv) {
         ok = mbar_wait(pv_done, (t - 1) & 1, abort_flag);
         if (!__all_sync(0xffffffffu, ok)) { aborted = true; break; }
       }
-      // P row (32 bf16) as 4 core-matrix rows of 16 bytes: (head/8)*512 + c*128 + (head%8)*16
-      const uint32_t prow = p_addr + (head >> 3) * 512 + (head & 7) * 16;
+      if (is_s) {
+        // P row (tile bf16) as core-matrix rows of 16 bytes: (row/8)*(tile/8*128) + c*128 + (row%8)*16
+        const uint32_t prow = p_addr + (row >> 3) * (kMlaTile / 8 * 128) + (row & 7) * 16;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + c * 128), "r"(pk[4 * c]),
-                     "r"(pk[4 * c + 1]), "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3])
-                     : "memory");
+        for (int c = 0; c < kMlaTile / 8; ++c) {
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + c * 128), "r"(pk[4 * c]),
+                       "r"(pk[4 * c + 1]), "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3])
+                       : "memory");
+        }
       }
       fence_proxy_async();
       mbar_arrive(p_full);
     }
-    // ---- output
-    float* ctx_row = p.ctx + (static_cast<int64_t>(item) * p.n_heads + head) * kMlaDv + half * kMlaDvHalf;
-    const bool write = head < p.n_heads;
+    // ---- output: lanes 0..15 own the O rows; l and m_ref come from the partner lane
+    const float l_o = __shfl_xor_sync(0xffffffffu, l, 16);
+    const float m_o = __shfl_xor_sync(0xffffffffu, m_ref, 16);
+    const int head = hh * kMlaHeadsTile + row;
+    float* ctx_row = p.ctx + (static_cast<int64_t>(item) * p.n_heads + head) * kMlaDv;
+    const bool write = !is_s && head < p.n_heads;
     if (n_tiles == 0 || aborted) {
       if (write && !aborted) {
-        for (int j = 0; j < kMlaDvHalf; j += 4) *reinterpret_cast<float4*>(ctx_row + j) = make_float4(0, 0, 0, 0);
-        if (half == 0) p.lse[static_cast<int64_t>(item) * p.n_heads + head] = -INFINITY;
+        for (int j = 0; j < kMlaDv; j += 4) *reinterpret_cast<float4*>(ctx_row + j) = make_float4(0, 0, 0, 0);
+        p.lse[static_cast<int64_t>(item) * p.n_heads + head] = -INFINITY;
       }
     } else {
       const bool ok = mbar_wait(pv_done, (n_tiles - 1) & 1, abort_flag);
       if (__all_sync(0xffffffffu, ok)) {
         tc_fence_after();
-        const float inv = (l > 0.f) ? 1.0f / l : 0.f;
+        const float inv = (l_o > 0.f) ? 1.0f / l_o : 0.f;
 #pragma unroll 1
-        for (int c = 0; c < kMlaDvHalf / 32; ++c) {
+        for (int c = 0; c < kMlaDv / 32; ++c) {
           uint32_t o[32];
           tmem_ld_32x32(tmem_base + lane_addr + kMlaTmemO + c * 32, o);
           tc_wait_ld();
@@ -293,43 +338,45 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
           }
         }
         tc_fence_before();
-        if (write && half == 0)
+        if (write)
           p.lse[static_cast<int64_t>(item) * p.n_heads + head] =
-              (l > 0.f) ? (m_ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
+              (l_o > 0.f) ? (m_o + log2f(l_o)) * 0.6931471805599453f : -INFINITY;
       }
     }
   } else {
     // ------------------------------------------------------------------ MMA issuer (warp 8)
-    constexpr uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, 128, kMlaTile);
-    constexpr uint32_t idesc_pv = make_idesc(kFmtBF16, kFmtBF16, 128, kMlaDvHalf, 0, 1);
+    constexpr uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, kMlaHeadsTile, kMlaTile);
+    constexpr uint32_t idesc_pv = make_idesc(kFmtBF16, kFmtBF16, kMlaHeadsTile, 256, 0, 1);
     if (elect_one()) {
       tma_prefetch_desc(&tmap_q);
       mbar_arrive_expect_tx(q_full, kMlaQBytes);
       for (int c = 0; c < kMlaChunks; ++c)
-        tma_load_2d(smem_al + c * kMlaChunkBytesQ, &tmap_q, q_full, c * 64, item * p.n_heads);
+        tma_load_2d(smem_al + c * kMlaChunkBytesQ, &tmap_q, q_full, c * 64, item * p.n_heads + hh * kMlaHeadsTile);
     }
     __syncwarp();
     bool ok = mbar_wait(q_full, 0, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
     auto issue_scores = [&](int t) -> bool {
-      const int s = t & 1;
-      bool w = mbar_wait(&kv_full[s], (t >> 1) & 1, abort_flag) &&
-               mbar_wait(&s_empty[s], ((t >> 1) & 1) ^ 1, abort_flag);
+      const int s = t % kMlaStages, sb = t & 1;
+      bool w = mbar_wait(&kv_full[s], (t / kMlaStages) & 1, abort_flag) &&
+               mbar_wait(&s_empty[sb], ((t >> 1) & 1) ^ 1, abort_flag);
       if (!__all_sync(0xffffffffu, w)) return false;
       fence_proxy_async();  // gathered rows were written through the generic proxy
       tc_fence_after();
       if (elect_one()) {
-        const uint32_t d = tmem_base + kMlaTmemS + s * kMlaTile;
-#pragma unroll 1
+        const uint32_t d = tmem_base + kMlaTmemS + sb * kMlaTile;
+        // descriptors differ only in the 16-byte-granular start address: one add per operand
+        const uint64_t a0 = make_desc_k_sw128(q_addr);
+        const uint64_t b0 = make_desc_k_sw128(kv_addr + s * kMlaStageBytes);
+#pragma unroll
         for (int c = 0; c < kMlaChunks; ++c) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t a = make_desc_k_sw128(q_addr + c * kMlaChunkBytesQ + kk * 32);
-            const uint64_t b = make_desc_k_sw128(kv_addr + s * kMlaStageBytes + c * kMlaChunkBytesK + kk * 32);
-            mma_f16_ss(d, a, b, idesc_s, (c | kk) != 0);
+            mma_f16_ss(d, a0 + ((c * kMlaChunkBytesQ + kk * 32) >> 4), b0 + ((c * kMlaChunkBytesK + kk * 32) >> 4),
+                       idesc_s, (c | kk) != 0);
           }
         }
-        tc_commit(&s_full[s]);
+        tc_commit(&s_full[sb]);
       }
       __syncwarp();
       return true;
@@ -340,18 +387,20 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
         ok = issue_scores(t + 1);
         if (!ok) break;
       }
-      const int s = t & 1;
+      const int s = t % kMlaStages;
       const bool w = mbar_wait(p_full, t & 1, abort_flag);
       if (!__all_sync(0xffffffffu, w)) break;
       tc_fence_after();
       if (elect_one()) {
-        const uint32_t d = tmem_base + kMlaTmemO;
-        const uint32_t v_addr = kv_addr + s * kMlaStageBytes + (4 * half) * kMlaChunkBytesK;
+        const uint64_t pa0 = make_desc_k_noswz(p_addr, 128, kMlaTile / 8 * 128);
+        const uint64_t vb0 = make_desc_mn_sw128(kv_addr + s * kMlaStageBytes, kMlaChunkBytesK, 1024);
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {  // 16 keys per MMA
-          const uint64_t a = make_desc_k_noswz(p_addr + j * 256, 128, 512);
-          const uint64_t b = make_desc_mn_sw128(v_addr + j * 2048, kMlaChunkBytesK, 1024);
-          mma_f16_ss(d, a, b, idesc_pv, (t | j) != 0);
+        for (int j = 0; j < kMlaTile / 16; ++j) {  // 16 keys per MMA
+#pragma unroll
+          for (int nh = 0; nh < 2; ++nh) {        // value dims [256*nh, 256*nh+256)
+            mma_f16_ss(tmem_base + kMlaTmemO + nh * 256, pa0 + ((j * 256) >> 4),
+                       vb0 + (((4 * nh) * kMlaChunkBytesK + j * 2048) >> 4), idesc_pv, (t | j) != 0);
+          }
         }
         tc_commit(&kv_empty[s]);
         tc_commit(pv_done);
@@ -381,7 +430,7 @@ extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16
                                          int32_t* status, void* stream) {
   if (n_items == 0) return B200DSA_OK;
   if (!q_bf16 || !kv_bf16 || !indices || !ctx || !lse || !status || n_items < 0 || n_heads < 1 ||
-      n_heads > kMlaHeadsTile || n_idx < 0 || idx_stride < n_idx || kv_rows < 1 || pos_hi < pos_lo) {
+      n_heads > kMlaMaxHeads || n_idx < 0 || idx_stride < n_idx || kv_rows < 1 || pos_hi < pos_lo) {
     set_last_error("b200dsa_sparse_mla_decode: bad argument (1 <= n_heads <= 128, idx_stride >= n_idx)");
     return B200DSA_EINVAL;
   }
@@ -396,7 +445,7 @@ extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16
   {
     cuuint64_t dims[2] = {kMlaD, static_cast<cuuint64_t>(n_items) * n_heads};
     cuuint64_t strides[1] = {kMlaD * 2};
-    cuuint32_t box[2] = {64, kMlaHeadsTile};
+    cuuint32_t box[2] = {64, kMlaHeadsTile};  // 64 elements x 64 head rows
     cuuint32_t es[2] = {1, 1};
     CUresult r = enc(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(q_bf16), dims, strides, box, es,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,

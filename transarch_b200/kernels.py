@@ -219,3 +219,82 @@ def lse_finalize(wire: torch.Tensor, lse_max: torch.Tensor, ctx_out: torch.Tenso
     check(_lib.load().b200dsa_lse_finalize(ptr(wire), ptr(lse_max), n_rows, ptr(ctx_out), ptr(lse_out),
                                             stream_ptr()), "b200dsa_lse_finalize")
     return ctx_out, lse_out
+
+
+def block_mean_pool(keys: torch.Tensor, block: int, *, want_f32: bool = False):
+    """Pooled keys bf16 [ceil(n/block), 128] (and fp32 copy when want_f32); see
+    b200dsa_block_mean_pool_bf16."""
+    require_cuda(keys)
+    if keys.dtype != torch.bfloat16 or not keys.is_contiguous() or keys.dim() != 2 or keys.shape[1] != 128:
+        raise _lib.B200DSAError("keys must be contiguous bf16 [n, 128]")
+    nb = (keys.shape[0] + block - 1) // block
+    out = torch.empty(nb, 128, dtype=torch.bfloat16, device=keys.device)
+    out32 = torch.empty(nb, 128, dtype=torch.float32, device=keys.device) if want_f32 else None
+    check(_lib.load().b200dsa_block_mean_pool_bf16(ptr(keys), keys.shape[0], block, ptr(out), ptr(out32),
+                                                  stream_ptr()), "b200dsa_block_mean_pool_bf16")
+    return (out, out32) if want_f32 else out
+
+
+def paged_mean_pool_fp8(cache: torch.Tensor, page_size: int, context_lens: torch.Tensor,
+                        block_table: torch.Tensor, block: int, max_pool_blocks: int) -> torch.Tensor:
+    """fp32 [n_requests, max_pool_blocks, 128] block means over the paged FP8 cache."""
+    require_cuda(cache, context_lens, block_table)
+    _i32(context_lens, "context_lens"); _i32(block_table, "block_table")
+    num_pages = cache.numel() // (page_size * 132)
+    B = context_lens.numel()
+    out = torch.empty(B, max_pool_blocks, 128, dtype=torch.float32, device=cache.device)
+    check(_lib.load().b200dsa_paged_mean_pool_fp8(ptr(cache), num_pages, page_size, ptr(context_lens),
+                                                 ptr(block_table), block_table.stride(0), B, block, max_pool_blocks,
+                                                 ptr(out), ptr(status_word(cache.device)), stream_ptr()),
+          "b200dsa_paged_mean_pool_fp8")
+    return out
+
+
+def _router_out(n_tokens: int, n_keep: int, device):
+    return (torch.empty(n_tokens, 64, dtype=torch.float32, device=device),
+            torch.empty(n_tokens, n_keep, dtype=torch.int32, device=device))
+
+
+def router_qnorm_topk(q: torch.Tensor, w: torch.Tensor, n_keep: int):
+    """(weights [T,64] zero on dropped heads, head_idx int32 [T,n_keep]); see b200dsa_router_qnorm_topk."""
+    require_cuda(q, w)
+    if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.shape[-2:] != (64, 128):
+        raise _lib.B200DSAError("q must be contiguous bf16 [T, 64, 128]")
+    T = q.numel() // (64 * 128)
+    wo, hi = _router_out(T, n_keep, q.device)
+    check(_lib.load().b200dsa_router_qnorm_topk(ptr(q), ptr(w.contiguous()), T, n_keep, ptr(wo), ptr(hi),
+                                                stream_ptr()), "b200dsa_router_qnorm_topk")
+    return wo, hi
+
+
+def router_block_score_topk(q: torch.Tensor, w: torch.Tensor, pooled: torch.Tensor, blk_lo: torch.Tensor,
+                            blk_hi: torch.Tensor, n_keep: int, *, pooled_set: Optional[torch.Tensor] = None,
+                            return_scores: bool = False):
+    """Block-score router; pooled fp32 [n_blocks,128] or [n_sets,n_blocks,128]."""
+    require_cuda(q, w, pooled, blk_lo, blk_hi, pooled_set)
+    if pooled.dtype != torch.float32 or not pooled.is_contiguous():
+        raise _lib.B200DSAError("pooled keys must be contiguous fp32")
+    T = q.numel() // (64 * 128)
+    set_stride = pooled.shape[-2] * 128 if pooled.dim() == 3 else 0
+    wo, hi = _router_out(T, n_keep, q.device)
+    sc = torch.empty(T, 64, dtype=torch.float32, device=q.device) if return_scores else None
+    check(_lib.load().b200dsa_router_block_score_topk(
+        ptr(q), ptr(w.contiguous()), ptr(pooled), set_stride, ptr(_i32(pooled_set, "pooled_set")),
+        ptr(_i32(blk_lo, "blk_lo")), ptr(_i32(blk_hi, "blk_hi")), T, n_keep, ptr(wo), ptr(hi), ptr(sc),
+        stream_ptr()), "b200dsa_router_block_score_topk")
+    return (wo, hi, sc) if return_scores else (wo, hi)
+
+
+def router_linear_topk_softmax(x: torch.Tensor, w_r: torch.Tensor, n_keep: int, *, return_logits: bool = False):
+    """Linear router: top-n of x @ W_r with softmax weights over the kept heads."""
+    require_cuda(x, w_r)
+    if x.dtype != torch.bfloat16 or w_r.dtype != torch.bfloat16 or not x.is_contiguous() or \
+            not w_r.is_contiguous() or w_r.shape != (x.shape[1], 64):
+        raise _lib.B200DSAError("x must be bf16 [T, hidden] and W_r bf16 [hidden, 64], both contiguous")
+    T, hidden = x.shape
+    wo, hi = _router_out(T, n_keep, x.device)
+    lg = torch.empty(T, 64, dtype=torch.float32, device=x.device) if return_logits else None
+    check(_lib.load().b200dsa_router_linear_topk_softmax(ptr(x), ptr(w_r), T, hidden, n_keep, ptr(wo), ptr(hi),
+                                                        ptr(lg), stream_ptr()),
+          "b200dsa_router_linear_topk_softmax")
+    return (wo, hi, lg) if return_logits else (wo, hi)
