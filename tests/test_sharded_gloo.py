@@ -1,0 +1,82 @@
+"""Key-sharded decode step on two CPU ranks (gloo): the host logic of SparseDecodeStep — shard
+ranges, candidate wire layout, all-gather + segmented merge, log-sum-exp all-reduce — must give
+every rank the unsharded oracle result.  Kernels are replaced by the oracle-backed stand-in."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from tests.decode_cases import make_global_problem, oracle_decode, shard_state
+
+CTXS, TOPK, SHARD = [700, 1024, 130], 128, 512
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
+
+
+def _worker(rank, world, port, fail_rank, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from tests import cpu_backend
+        from transarch_b200.decode import ShardInfo, SparseDecodeStep, local_context_lens
+        torch.set_num_threads(2)
+        prob = make_global_problem(51, CTXS, H=8)
+        st = shard_state(prob, rank, world, SHARD, "cpu")
+        shard = ShardInfo(rank=rank, world_size=world, shard_len=SHARD)
+        assert torch.equal(local_context_lens(st["lens"], shard), st["local"])
+        step = SparseDecodeStep(len(CTXS), SHARD, topk=TOPK, n_heads=8, device=torch.device("cpu"), shard=shard,
+                                backend=cpu_backend, sorted_topk=True)
+        idx, ctx, lse = step.run(prob["q_idx"], prob["w"], prob["q_lat"], st["cache"], st["lens"], st["table"],
+                                 st["kv"], st["base"])
+        ref_idx, _, ref_ctx, ref_lse = oracle_decode(prob, TOPK, 128 ** -0.5, 192 ** -0.5)
+        ok = torch.equal(idx, ref_idx) and torch.allclose(ctx, ref_ctx, rtol=1e-4, atol=1e-5) and \
+            torch.allclose(lse, ref_lse, rtol=1e-4, atol=1e-5)
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_sharded_step_matches_unsharded():
+    port = _free_port()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(2, port, -1, ret), nprocs=2, join=True)
+    assert ret.get(0) is True and ret.get(1) is True
+
+
+def _absent_worker(rank, world, port, ret):
+    """Rank 1 never joins the candidate exchange: rank 0 must get an error from the collective
+    (short process-group timeout), not hang."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    try:
+        if rank == 1:
+            ret[1] = "left"
+            return                      # leaves between steps, nothing in flight
+        t = torch.zeros(4)
+        try:
+            dist.all_reduce(t)
+            ret[0] = "no error"
+        except Exception as e:          # noqa: BLE001
+            ret[0] = "error"
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:               # noqa: BLE001
+            pass
+
+
+def test_missing_rank_is_reported_not_hung():
+    port = _free_port()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_absent_worker, args=(2, port, ret), nprocs=2, join=True)
+    assert ret.get(0) == "error" and ret.get(1) == "left"

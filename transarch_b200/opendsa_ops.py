@@ -1,0 +1,153 @@
+"""Drop-in replacements for OpenDSA's selection ops, same names and argument meaning:
+
+    indexer_select_topk            OpenDSA/opendsa/ops/topk_select.py:30-72
+    sparse_attend_absorbed_chunked OpenDSA/opendsa/ops/sparse_mla.py:51-103
+    prepare_ks_ke / prepare_ks_ke_cp  OpenDSA/opendsa/ops/flashkl_warmup.py:41-56, :235-248
+
+Both ops are forward-only (the reference's selection is under torch.no_grad; the sparse
+training backward stays with the reference).  Tensors must live on a CUDA device; there is no
+CPU path.  `patch_opendsa()` rebinds the names the reference imported at module load
+(OpenDSA/opendsa/modeling/dsa_attention.py:31-38).
+
+Numerics: scores are computed from bf16-rounded q and k with fp32 accumulation on tcgen05
+tensor cores (the reference computes in the dtype it is given); attention runs in bf16 with
+fp32 softmax and accumulation.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import kernels as K
+from ._lib import B200DSAError
+
+_BLOCK = 128
+_MAX_LOGIT_BYTES = 1 << 30   # scratch bound for one query chunk of token logits
+
+
+def prepare_ks_ke(cu_seqlens: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per packed query the causal interval [ks, ke): ks = start of its document,
+    ke = its own position + 1.  Device-side (no host synchronisation beyond the total length)."""
+    cu = cu_seqlens.to(torch.int64)
+    total = int(cu[-1]) if cu.numel() else 0
+    t = torch.arange(total, dtype=torch.int64, device=cu.device)
+    doc = torch.searchsorted(cu, t, right=True) - 1
+    return cu[doc], t + 1
+
+
+def prepare_ks_ke_cp(cu_full: torch.Tensor, q_global_pos: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Intervals for local queries that sit at global positions (context parallel / decode)."""
+    cu = cu_full.to(torch.int64)
+    p = q_global_pos.to(torch.int64)
+    d = (torch.searchsorted(cu, p, right=True) - 1).clamp(0, cu.numel() - 2)
+    return cu[d], p + 1
+
+
+def _pad_heads(q: torch.Tensor, w: torch.Tensor):
+    """The kernels score exactly 64 index heads; fewer heads are padded with zero weight."""
+    H = q.shape[1]
+    if H == 64:
+        return q.contiguous(), w.contiguous()
+    if H > 64:
+        raise B200DSAError("at most 64 index heads are supported")
+    qp = q.new_zeros(q.shape[0], 64, q.shape[2])
+    qp[:, :H] = q
+    wp = w.new_zeros(w.shape[0], 64)
+    wp[:, :H] = w
+    return qp, wp
+
+
+def identity_block_lists(ks: torch.Tensor, ke: torch.Tensor, n_keys: int):
+    """Per row the list of 128-key blocks covering [ks, ke): (block_list int32 [T, max_blocks]
+    padded with -1, row_cols int32 [T])."""
+    nb_total = (n_keys + _BLOCK - 1) // _BLOCK
+    b0 = (ks // _BLOCK).to(torch.int32)
+    b1 = ((ke + _BLOCK - 1) // _BLOCK).to(torch.int32)
+    nblk = (b1 - b0).clamp(min=0)
+    j = torch.arange(nb_total, dtype=torch.int32, device=ks.device).view(1, -1)
+    bl = torch.where(j < nblk.view(-1, 1), b0.view(-1, 1) + j, torch.full_like(j, -1))
+    return bl.contiguous(), (nblk * _BLOCK).to(torch.int32)
+
+
+def indexer_logits_flat(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, ks: torch.Tensor, ke: torch.Tensor,
+                        sm_scale: float):
+    """Token logits of every row over the blocks covering its interval:
+    (logits fp32 [T, max_blocks*128] with -inf outside [ks,ke), block_list, row_cols)."""
+    bl, row_cols = identity_block_lists(ks, ke, k.shape[0])
+    logits = K.indexer_blocklist_bf16_logits(q, w, k, bl, row_cols, pos_lo=ks.to(torch.int32).contiguous(),
+                                             pos_hi=ke.to(torch.int32).contiguous(), out_scale=sm_scale)
+    return logits, bl, row_cols
+
+
+@torch.no_grad()
+def indexer_select_topk(index_q, index_k, index_w, cu_seqlens, topk, *, sm_scale_index: Optional[float] = None,
+                        q_chunk: int = 4096, q_global_pos=None) -> torch.Tensor:
+    """Per-query top-k causal key positions by the lightning-indexer score
+    I[t,j] = sm_scale * sum_h w[t,h] * relu(<q[t,h], k[j]>); int32 [Lq, topk], absolute
+    positions in descending score order, -1 where fewer than topk keys are visible."""
+    if not index_q.is_cuda:
+        raise B200DSAError("indexer_select_topk needs CUDA tensors (no CPU path)")
+    Lq, H, d = index_q.shape
+    if d != 128:
+        raise B200DSAError("index head dim must be 128")
+    sf = sm_scale_index if sm_scale_index is not None else d ** -0.5
+    if q_global_pos is None:
+        ks, ke = prepare_ks_ke(cu_seqlens)
+    else:
+        ks, ke = prepare_ks_ke_cp(cu_seqlens, q_global_pos)
+    q, w = _pad_heads(index_q.to(torch.bfloat16), index_w.to(torch.float32))
+    k = index_k.to(torch.bfloat16).contiguous()
+    Lk = k.shape[0]
+    out = torch.full((Lq, topk), -1, dtype=torch.int32, device=index_q.device)
+    if Lq == 0 or Lk == 0:
+        return out
+    cols = ((Lk + _BLOCK - 1) // _BLOCK) * _BLOCK
+    rows_per = max(1, min(q_chunk, _MAX_LOGIT_BYTES // (cols * 4)))
+    k_eff = min(topk, 8192)
+    if topk > 8192:
+        raise B200DSAError("topk above 8192 is not supported")
+    for t0 in range(0, Lq, rows_per):
+        t1 = min(t0 + rows_per, Lq)
+        logits, bl, row_cols = indexer_logits_flat(q[t0:t1], k, w[t0:t1], ks[t0:t1], ke[t0:t1], sf)
+        K.topk_select(logits, k_eff, col_end=row_cols, page_table=bl, page_size=_BLOCK, sorted=True, out=out[t0:t1])
+    return out
+
+
+@torch.no_grad()
+def sparse_attend_latent(q_lat, latent, indices, *, sm_scale: float, q_pos: Optional[torch.Tensor] = None):
+    """Latent-space context and log-sum-exp: (ctx fp32 [L,H,512], lse fp32 [L,H])."""
+    if q_lat.shape[-1] != 576 or latent.shape[-1] != 576:
+        raise B200DSAError("latent width must be 576 (512 value dims + 64 rope dims)")
+    return K.sparse_mla_decode(q_lat.to(torch.bfloat16).contiguous(), latent.to(torch.bfloat16).contiguous(),
+                               indices.to(torch.int32).contiguous(), sm_scale,
+                               q_pos=None if q_pos is None else q_pos.to(torch.int32).contiguous())
+
+
+def sparse_attend_absorbed_chunked(q_lat, latent, W_UV, indices, *, d_c: int, sm_scale: float, cu_seqlens=None,
+                                   q_chunk: int = 512, checkpoint: bool = True, q_global_pos=None) -> torch.Tensor:
+    """Sparse MLA attention in the absorbed latent space followed by the W_UV up-projection;
+    [Lq, H, Dv].  q_chunk and checkpoint are accepted for signature compatibility and ignored
+    (nothing of size [chunk, K, 576] is ever materialised).  Forward only."""
+    if torch.is_grad_enabled() and (q_lat.requires_grad or latent.requires_grad or W_UV.requires_grad):
+        raise B200DSAError("sparse_attend_absorbed_chunked is forward-only; run the reference op for training")
+    if d_c != 512:
+        raise B200DSAError("d_c must be 512")
+    L = q_lat.shape[0]
+    if q_global_pos is not None:
+        q_pos = q_global_pos
+    elif cu_seqlens is not None:
+        q_pos = prepare_ks_ke(cu_seqlens)[1] - 1
+    else:
+        q_pos = torch.arange(L, device=q_lat.device)
+    ctx, _ = sparse_attend_latent(q_lat, latent, indices, sm_scale=sm_scale, q_pos=q_pos)
+    return torch.einsum("thl,hvl->thv", ctx.to(W_UV.dtype), W_UV)
+
+
+def patch_opendsa() -> None:
+    """Rebind the reference's names to these implementations (the OpenDSA package must be importable)."""
+    import opendsa.modeling.dsa_attention as att
+    import opendsa.ops as ops
+    for mod in (att, ops):
+        mod.indexer_select_topk = indexer_select_topk
+        mod.sparse_attend_absorbed_chunked = sparse_attend_absorbed_chunked
