@@ -88,13 +88,17 @@ int b200dsa_topk_select(const float* scores, int64_t row_stride, int32_t n_rows,
  *                scales (layout read at misa_ops.py:360-372); page_size in {32, 64, 128}
  *   context_lens [n_rows] int32, keys visible to row r
  *   block_table  [n_rows/next_n, block_table_stride] int32 page ids
+ *   row_table    optional int32 [n_rows]: block-table row of each logits row (prefill chunks,
+ *                where a request contributes a varying number of query rows); when given it
+ *                replaces the row/next_n rule
  * Page ids outside [0, num_pages) are skipped and reported through status (2).
  * q, weights and cache must be 16-byte aligned.
  * ------------------------------------------------------------------------------------- */
 int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* weights, const void* cache,
                                      int32_t num_pages, int32_t page_size, const int32_t* context_lens,
                                      const int32_t* block_table, int64_t block_table_stride,
-                                     int32_t n_rows, int32_t next_n, int32_t max_cols, float out_scale,
+                                     const int32_t* row_table, int32_t n_rows, int32_t next_n,
+                                     int32_t max_cols, float out_scale,
                                      float* logits, int64_t logits_stride, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
@@ -216,6 +220,18 @@ int b200dsa_router_block_score_topk(const void* q_bf16, const float* w, const fl
 int b200dsa_router_linear_topk_softmax(const void* x_bf16, const void* w_r_bf16, int32_t n_tokens,
                                        int32_t hidden, int32_t n_keep, float* weights_out,
                                        int32_t* head_idx, float* logits_out, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Insert new index keys into the paged FP8 cache: per-token e4m3 quantisation
+ * (scale = max(amax,1e-4)/448) written to slot_mapping[t] = page*page_size + offset
+ * (negative = skip).  Stands in for the third-party vLLM op the reference calls at
+ * MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/indexers.py:454-460
+ * (ops.indexer_k_quant_and_cache), producing the page layout read at misa_ops.py:360-372.
+ *   k_bf16 [n_tokens, 128], slot_mapping int64 [n_tokens], cache [num_pages, page_size*132].
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_indexer_k_quant_and_cache(const void* k_bf16, const int64_t* slot_mapping, int64_t n_tokens,
+                                      void* cache, int64_t num_pages, int32_t page_size, int32_t* status,
+                                      void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,182 @@
+"""MISA routers, routed two-stage logits and the vLLM-style hook against the oracle."""
+import pytest
+import torch
+
+from oracle import dsa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _paged(seed, ctxs, P=64):
+    g = torch.Generator().manual_seed(seed)
+    ks = [torch.randn(c, 128, generator=g) for c in ctxs]
+    qs = [O.quant_fp8_rows(k) for k in ks]
+    n_pages = sum((c + P - 1) // P for c in ctxs) + 3
+    cache, table = O.pack_paged_fp8_cache([a for a, _ in qs], [b for _, b in qs], P, n_pages, g)
+    return g, qs, cache, table
+
+
+def test_routers_match_oracle():
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(30)
+    T = 19
+    q = torch.randn(T, 64, 128, generator=g).bfloat16()
+    w = torch.randn(T, 64, generator=g) / 8
+    # q-norm
+    wo, hi = K.router_qnorm_topk(q.cuda(), w.cuda(), 8)
+    ref = O.qnorm_head_topk(q, 8)
+    assert torch.equal(torch.sort(hi.cpu().long(), 1).values, torch.sort(ref, 1).values)
+    assert torch.equal(wo.cpu(), torch.zeros(T, 64).scatter_(1, ref, torch.gather(w, 1, ref)))
+    # block score
+    kblk = torch.randn(37, 128, generator=g)
+    lo = torch.randint(0, 5, (T,), generator=g, dtype=torch.int32)
+    hi_b = torch.randint(6, 38, (T,), generator=g, dtype=torch.int32)
+    wo, hidx, sc = K.router_block_score_topk(q.cuda(), w.cuda(), kblk.cuda(), lo.cuda(), hi_b.cuda(), 8,
+                                             return_scores=True)
+    ref_sc = O.misa_block_head_scores(q, kblk, w, lo.long(), hi_b.long())
+    assert torch.allclose(sc.cpu(), ref_sc, rtol=2e-4, atol=1e-5)
+    ref_idx = torch.topk(ref_sc, 8, dim=-1).indices
+    assert torch.equal(torch.sort(hidx.cpu().long(), 1).values, torch.sort(ref_idx, 1).values)
+    # linear router (no reference code; oracle restatement)
+    x = torch.randn(T, 7168, generator=g).bfloat16()
+    W = (torch.randn(7168, 64, generator=g) * 7168 ** -0.5).bfloat16()
+    wo, hidx, lg = K.router_linear_topk_softmax(x.cuda(), W.cuda(), 8, return_logits=True)
+    ridx, rw, rlog = O.linear_router_topk_softmax(x, W, 8)
+    assert torch.allclose(lg.cpu(), rlog, rtol=1e-3, atol=1e-3)
+    assert torch.equal(torch.sort(hidx.cpu().long(), 1).values, torch.sort(ridx, 1).values)
+    dense = torch.zeros(T, 64).scatter_(1, ridx, rw)
+    assert torch.allclose(wo.cpu(), dense, rtol=2e-3, atol=1e-4)
+    assert torch.allclose(wo.cpu().sum(1), torch.ones(T), atol=1e-5)
+
+
+def test_pooling_matches_oracle():
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(31)
+    k = torch.randn(1000, 128, generator=g).bfloat16()
+    p16, p32 = K.block_mean_pool(k.cuda(), 128, want_f32=True)
+    ref = O.block_mean_pool(k.float(), 128)
+    assert torch.allclose(p32.cpu(), ref, rtol=1e-5, atol=1e-6)
+    assert (p16.cpu().float() - ref).abs().max() < 4e-3
+    _, qs, cache, table = _paged(32, [300, 64, 1000])
+    lens = torch.tensor([300, 64, 1000], dtype=torch.int32)
+    pooled = K.paged_mean_pool_fp8(cache.cuda(), 64, lens.cuda(), table.cuda(), 128, 8).cpu()
+    for b, c in enumerate([300, 64, 1000]):
+        kd = qs[b][0].float() * qs[b][1].unsqueeze(-1)
+        ref = O.block_mean_pool(kd, 128)
+        assert torch.allclose(pooled[b, :ref.shape[0]], ref, rtol=1e-5, atol=1e-6)
+        assert (pooled[b, ref.shape[0]:] == 0).all()
+
+
+@pytest.mark.parametrize("use_qnorm", [True, False])
+def test_misa_mqa_logits_prefill(use_qnorm):
+    from transarch_b200 import misa as M
+    g = torch.Generator().manual_seed(33)
+    Mq, N, s1 = 24, 3000, 512
+    k = torch.randn(N, 128, generator=g)
+    kq, sc = O.quant_fp8_rows(k)
+    q = torch.randn(Mq, 64, 128, generator=g)
+    w = torch.randn(Mq, 64, generator=g) / 8
+    q_fp8, wf = O.quant_q_fold_weights(q, w, 128 ** -0.5, 64 ** -0.5)
+    ke = torch.arange(N - Mq, N, dtype=torch.int32) + 1
+    ks = torch.zeros(Mq, dtype=torch.int32)
+    hidx = O.qnorm_head_topk(q, 8) if use_qnorm else None
+    logits, cand = M.misa_mqa_logits(q_fp8.cuda(), (kq.cuda(), sc.cuda()), wf.cuda(),
+                                     None if hidx is None else hidx.cuda(), ks.cuda(), ke.cuda(), use_qnorm, 8, s1,
+                                     k_block_size=128)
+    kb = (kq.float() * sc.unsqueeze(-1)).bfloat16().float()
+    qf = q_fp8.float()
+    if not use_qnorm:
+        pooled = O.block_mean_pool(kb.bfloat16(), 128).float()
+        hs = O.misa_block_head_scores(qf, pooled, wf, ks.long() // 128, (ke.long() + 127) // 128)
+        hidx = torch.topk(hs, 8, dim=-1).indices
+    ref_logits, ref_cand = O.misa_mqa_logits(qf, kb, wf, hidx, ks.long(), ke.long(), s1)
+    assert O.set_recall(cand.cpu(), ref_cand) >= 0.995
+    full = O.mask_interval(O.indexer_scores(qf, kb, wf, 1.0), ks.long(), ke.long())
+    got = torch.gather(full, 1, cand.cpu().clamp(min=0).long())
+    ok = cand.cpu() >= 0
+    assert O.rel_err(logits.cpu()[ok], got[ok]) < 2e-3
+
+
+def test_misa_page_logits_and_hook_decode_prefill():
+    from transarch_b200 import _lib, misa as M, vllm_hook as V
+    ctxs = [700, 1500, 130]
+    g, qs, cache, table = _paged(34, ctxs)
+    B = len(ctxs)
+    q = torch.randn(B, 64, 128, generator=g)
+    w = torch.randn(B, 64, generator=g) / 8
+    q_fp8, wf = O.quant_q_fold_weights(q, w, 128 ** -0.5, 64 ** -0.5)
+    lens = torch.tensor(ctxs, dtype=torch.int32)
+    cache4 = cache.view(cache.shape[0], 64, 1, 132).cuda()
+    hidx = O.qnorm_head_topk(q, 8)
+    logits, cand = M.misa_page_mqa_logits(q_fp8.view(B, 1, 64, 128).cuda(), cache4, wf.cuda(), hidx.cuda(),
+                                          lens.cuda(), table.cuda(), 1536, 8, True, 256)
+    final = M.misa_final_topk(logits, cand, 64).cpu()
+    for b, c in enumerate(ctxs):
+        kd = qs[b][0].float() * qs[b][1].unsqueeze(-1)
+        q8, w8 = O.gather_heads(q_fp8[b:b + 1].float(), wf[b:b + 1], hidx[b:b + 1])
+        s1 = O.indexer_scores(q8, kd, w8, 1.0)
+        c1 = torch.topk(s1, min(256, c), dim=-1).indices
+        full = O.indexer_scores(q_fp8[b:b + 1].float(), kd, wf[b:b + 1], 1.0)
+        ref = c1[0][torch.topk(full[0][c1[0]], min(64, c1.shape[1])).indices]
+        got = final[b][final[b] >= 0]
+        assert len(set(got.tolist()) & set(ref.tolist())) >= 0.98 * ref.numel()
+
+    # ---- hook, decode step: new key appended, then selection over the cache
+    P = 64
+    buf = torch.full((8, 64), 7, dtype=torch.int32, device="cuda")
+    new_k = torch.randn(B, 128, generator=g).bfloat16()
+    slots = torch.tensor([int(table[b, c // P]) * P + c % P for b, c in enumerate(ctxs)], dtype=torch.int64)
+    cache_dev = cache.clone().view(cache.shape[0], 64, 1, 132).cuda()
+    md = V.IndexerMetadata(slot_mapping=slots.cuda(), num_decodes=B, num_decode_tokens=B,
+                           decode=V.DecodeMetadata(seq_lens=(lens + 1).cuda(), block_table=table.cuda()))
+    op = V.BaselineSparseAttnIndexer(cache_dev, 128, None, 64, 128, 1536, 4096, buf)
+    out = op.forward_cuda(torch.empty(B, 16, device="cuda"), q_fp8.cuda(), new_k.cuda(), wf.cuda(),
+                          attn_metadata=md)
+    assert out is buf and _lib.read_status(buf.device) == 0
+    nkq, nsc = O.quant_fp8_rows(new_k.float())
+    for b, c in enumerate(ctxs):
+        kd = torch.cat([qs[b][0].float() * qs[b][1].unsqueeze(-1), (nkq[b].float() * nsc[b]).view(1, -1)])
+        ref = O.topk_rows(O.indexer_scores(q_fp8[b:b + 1].float(), kd, wf[b:b + 1], 1.0), 64)
+        assert O.set_recall(buf[b:b + 1].cpu(), ref) >= 0.98
+    assert (buf[B:] == 7).all()                                # rows of other tokens untouched
+
+    # ---- hook, prefill chunk with two requests (MISA, q-norm heads)
+    ctx2 = [200, 333]
+    T = sum(ctx2)
+    g2, qs2, cache2, table2 = _paged(35, [0, 0])                 # empty cache, keys arrive through the hook
+    n_pages = 12
+    cache2 = torch.zeros(n_pages, 64 * 132, dtype=torch.uint8)
+    table2 = torch.tensor([[0, 1, 2, 3, -1, -1], [4, 5, 6, 7, 8, 9]], dtype=torch.int32)
+    kf = torch.randn(T, 128, generator=g2).bfloat16()
+    qf = torch.randn(T, 64, 128, generator=g2)
+    wq = torch.randn(T, 64, generator=g2) / 8
+    q8, w8 = O.quant_q_fold_weights(qf, wq, 128 ** -0.5, 64 ** -0.5)
+    slot, ks, ke = [], [], []
+    for r, c in enumerate(ctx2):
+        off = sum(ctx2[:r])
+        for i in range(c):
+            slot.append(int(table2[r, i // 64]) * 64 + i % 64)
+            ks.append(off); ke.append(off + i + 1)
+    chunk = V.PrefillChunk(0, T, table2.cuda(), torch.tensor([0, 200, 533], dtype=torch.int32).cuda(),
+                           torch.tensor(ks, dtype=torch.int32).cuda(), torch.tensor(ke, dtype=torch.int32).cuda(), T)
+    md = V.IndexerMetadata(slot_mapping=torch.tensor(slot).cuda(), num_prefills=2,
+                           prefill=V.PrefillMetadata([chunk]))
+    buf2 = torch.zeros(T, 32, dtype=torch.int32, device="cuda")
+    hq = O.qnorm_head_topk(qf, 8)
+    op2 = V.MiSASparseAttnIndexer(cache2.view(n_pages, 64, 1, 132).cuda(), 128, None, 8, 8, True, 128, 128, 32, 128,
+                                  384, 4096, buf2)
+    op2.forward_cuda(torch.empty(T, 16, device="cuda"), q8.cuda(), kf.cuda(), w8.cuda(), hq.cuda(), attn_metadata=md)
+    kq_all, sc_all = O.quant_fp8_rows(kf.float())
+    kd_all = kq_all.float() * sc_all.unsqueeze(-1)
+    res = buf2.cpu()
+    for t in [0, 5, 150, 199, 200, 260, 532]:
+        r = 0 if t < 200 else 1
+        off = 0 if r == 0 else 200
+        kd = kd_all[off: ke[t]]
+        qh, wh = O.gather_heads(q8[t:t + 1].float(), w8[t:t + 1], hq[t:t + 1])
+        c1 = torch.topk(O.indexer_scores(qh, kd, wh, 1.0), min(128, kd.shape[0]), dim=-1).indices[0]
+        full = O.indexer_scores(q8[t:t + 1].float(), kd, w8[t:t + 1], 1.0)[0]
+        ref = c1[torch.topk(full[c1], min(32, c1.numel())).indices]
+        got = res[t][res[t] >= 0]
+        assert got.numel() == ref.numel()
+        assert len(set(got.tolist()) & set(ref.tolist())) >= 0.95 * ref.numel(), t

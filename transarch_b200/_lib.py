@@ -22,7 +22,7 @@ SIGNATURES = {
     "b200dsa_last_error": [],
     "b200dsa_topk_select": [_vp, _i64, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _i32, _vp,
                             _i32, _i64, _vp, _vp, _i64, _vp],
-    "b200dsa_indexer_paged_fp8_logits": [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _i32, _i32, _i32, _f32,
+    "b200dsa_indexer_paged_fp8_logits": [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _f32,
                                          _vp, _i64, _vp, _vp],
     "b200dsa_indexer_blocklist_bf16_logits": [_vp, _vp, _vp, _i32, _vp, _i64, _vp, _vp, _vp, _i32, _i32, _f32,
                                               _vp, _i64, _vp, _vp],
@@ -37,6 +37,7 @@ SIGNATURES = {
     "b200dsa_router_qnorm_topk": [_vp, _vp, _i32, _i32, _vp, _vp, _vp],
     "b200dsa_router_block_score_topk": [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp],
     "b200dsa_router_linear_topk_softmax": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp],
+    "b200dsa_indexer_k_quant_and_cache": [_vp, _vp, _i64, _vp, _i64, _i32, _vp, _vp],
 }
 
 _lib: Optional[C.CDLL] = None

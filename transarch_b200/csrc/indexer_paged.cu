@@ -55,6 +55,7 @@ struct PagedIndexerParams {
   int64_t table_stride;
   int32_t table_cols;           // entries that may be read per table row
   int32_t table_row_div;        // table row of row r is r / table_row_div (next_n > 1 shares tables)
+  const int32_t* row_table;     // nullable: explicit table row per row (overrides the division)
   const int32_t* pos_lo;        // bf16 mode, nullable: keep only pos_lo[r] <= position < pos_hi[r]
   const int32_t* pos_hi;
   int32_t n_rows;
@@ -178,7 +179,7 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
         ++qit;
         prev_row = row;
         cols = max(0, min(p.row_cols[row], p.logits_cols));
-        trow = p.table + static_cast<int64_t>(row / p.table_row_div) * p.table_stride;
+        trow = p.table + static_cast<int64_t>(p.row_table ? p.row_table[row] : row / p.table_row_div) * p.table_stride;
         tbl_len = min(p.table_cols, (cols + P - 1) >> p_shift);
         tbl_base = -1;
       }
@@ -311,7 +312,7 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
           w[4 * j + 0] = x.x; w[4 * j + 1] = x.y; w[4 * j + 2] = x.z; w[4 * j + 3] = x.w;
         }
         cols = max(0, min(p.row_cols[row], p.logits_cols));
-        trow = p.table + static_cast<int64_t>(row / p.table_row_div) * p.table_stride;
+        trow = p.table + static_cast<int64_t>(p.row_table ? p.row_table[row] : row / p.table_row_div) * p.table_stride;
         if (p.pos_lo) { lo = p.pos_lo[row]; hi = p.pos_hi[row]; }
         prev_row = row;
       }
@@ -431,7 +432,8 @@ using namespace b200dsa;
 extern "C" int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* weights, const void* cache,
                                                 int32_t num_pages, int32_t page_size, const int32_t* context_lens,
                                                 const int32_t* block_table, int64_t block_table_stride,
-                                                int32_t n_rows, int32_t next_n, int32_t max_cols, float out_scale,
+                                                const int32_t* row_table, int32_t n_rows, int32_t next_n,
+                                                int32_t max_cols, float out_scale,
                                                 float* logits, int64_t logits_stride, int32_t* status, void* stream) {
   if (n_rows == 0) return B200DSA_OK;
   if (!q_fp8 || !weights || !cache || !context_lens || !block_table || !logits || !status || n_rows < 0 ||
@@ -460,7 +462,7 @@ extern "C" int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* 
   for (int r0 = 0; r0 < n_rows; r0 += kMaxRows) {
     const int nr = n_rows - r0 < kMaxRows ? n_rows - r0 : kMaxRows;
     // chunk boundaries must not split the next_n rows of one request
-    if (r0 % next_n != 0) {
+    if (!row_table && r0 % next_n != 0) {
       set_last_error("b200dsa_indexer_paged_fp8_logits: next_n must divide 1024 when n_rows > 1024");
       return B200DSA_EUNSUPPORTED;
     }
@@ -477,7 +479,8 @@ extern "C" int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* 
     p.num_pages = num_pages;
     p.weights = weights + static_cast<int64_t>(r0) * kHeads;
     p.row_cols = context_lens + r0;
-    p.table = block_table + static_cast<int64_t>(r0 / next_n) * block_table_stride;
+    p.table = row_table ? block_table : block_table + static_cast<int64_t>(r0 / next_n) * block_table_stride;
+    p.row_table = row_table ? row_table + r0 : nullptr;
     p.table_stride = block_table_stride;
     p.table_cols = static_cast<int32_t>(block_table_stride);
     p.table_row_div = next_n;

@@ -66,7 +66,8 @@ def topk_select(scores: torch.Tensor, k: int, *, col_begin: Optional[torch.Tenso
 def indexer_paged_fp8_logits(q_fp8: torch.Tensor, weights: torch.Tensor, cache: torch.Tensor, page_size: int,
                              context_lens: torch.Tensor, block_table: torch.Tensor, *, next_n: int = 1,
                              max_cols: Optional[int] = None, out_scale: float = 1.0,
-                             out: Optional[torch.Tensor] = None, fill: bool = True) -> torch.Tensor:
+                             out: Optional[torch.Tensor] = None, fill: bool = True,
+                             row_table: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Decode logits [n_rows, max_cols] fp32 over the paged FP8 cache; see
     b200dsa_indexer_paged_fp8_logits.  fill=True pre-fills a fresh output with -inf so that
     columns beyond each context are -inf as in the reference; pass out= to reuse a buffer."""
@@ -93,7 +94,8 @@ def indexer_paged_fp8_logits(q_fp8: torch.Tensor, weights: torch.Tensor, cache: 
     lib = _lib.load()
     rc = lib.b200dsa_indexer_paged_fp8_logits(
         ptr(q_fp8), ptr(weights), ptr(cache), num_pages, page_size, ptr(context_lens),
-        ptr(block_table), block_table.stride(0), n_rows, next_n, max_cols, out_scale,
+        ptr(block_table), block_table.stride(0), ptr(_i32(row_table, "row_table")), n_rows, next_n, max_cols,
+        out_scale,
         ptr(out), out.stride(0), ptr(status_word(q_fp8.device)), stream_ptr())
     check(rc, "b200dsa_indexer_paged_fp8_logits")
     return out
@@ -298,3 +300,21 @@ def router_linear_topk_softmax(x: torch.Tensor, w_r: torch.Tensor, n_keep: int, 
                                                         ptr(lg), stream_ptr()),
           "b200dsa_router_linear_topk_softmax")
     return (wo, hi, lg) if return_logits else (wo, hi)
+
+
+def indexer_k_quant_and_cache(k: torch.Tensor, cache: torch.Tensor, slot_mapping: torch.Tensor,
+                              page_size: int) -> None:
+    """Quantise new index keys and write them into their cache slots; see
+    b200dsa_indexer_k_quant_and_cache."""
+    require_cuda(k, cache, slot_mapping)
+    if k.dtype != torch.bfloat16 or not k.is_contiguous() or k.shape[-1] != 128:
+        raise _lib.B200DSAError("k must be contiguous bf16 [n, 128]")
+    if slot_mapping.dtype != torch.int64 or not slot_mapping.is_contiguous():
+        raise _lib.B200DSAError("slot_mapping must be contiguous int64")
+    if cache.dtype != torch.uint8 or not cache.is_contiguous():
+        raise _lib.B200DSAError("cache must be a contiguous uint8 tensor")
+    n = slot_mapping.numel()
+    num_pages = cache.numel() // (page_size * 132)
+    check(_lib.load().b200dsa_indexer_k_quant_and_cache(ptr(k), ptr(slot_mapping), n, ptr(cache), num_pages,
+                                                        page_size, ptr(status_word(k.device)), stream_ptr()),
+          "b200dsa_indexer_k_quant_and_cache")
