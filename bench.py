@@ -159,6 +159,7 @@ def main():
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -170,7 +171,7 @@ def main():
 
     import torch.distributed as dist
     from transarch_b200 import _lib
-    from transarch_b200.decode import ShardInfo, SparseDecodeStep
+    from transarch_b200.decode import GraphedDecodeStep, ShardInfo, SparseDecodeStep
     from transarch_b200.workloads import make_decode_queries, make_decode_state
 
     torch.cuda.set_device(local_rank)
@@ -194,16 +195,34 @@ def main():
     host_idx = torch.empty(B, TOPK, dtype=torch.int32).pin_memory()
     host_ctx = torch.empty(B, HEADS, 512, dtype=torch.float32).pin_memory()
 
-    def run_device(i):
+    def run_eager(i):
         q_idx, w, q_lat = dev_q[i % n_sets]
         return step.run(q_idx, w, q_lat, state.k_cache, state.context_lens, state.block_table, state.kv,
                         state.kv_row_base, state.context_lens_local)
 
+    for i in range(2):
+        run_eager(i)                      # lazy initialisation (NCCL communicators, function attributes)
+    torch.cuda.synchronize()
+    graphed = None
+    if not args.no_graph:
+        graphed = GraphedDecodeStep(step, state.k_cache, state.context_lens, state.block_table, state.kv,
+                                    state.kv_row_base, state.context_lens_local).capture()
+
+    def run_device(i):
+        # inputs already resident in HBM: a device-to-device copy into the graph's static buffers
+        if graphed is None:
+            return run_eager(i)
+        return graphed.replay(*dev_q[i % n_sets])
+
     def run_e2e(i):
-        for dst, src in zip(stage_q, host_q[i % n_sets]):
-            dst.copy_(src, non_blocking=True)
-        idx, c, _ = step.run(stage_q[0], stage_q[1], stage_q[2], state.k_cache, state.context_lens,
-                             state.block_table, state.kv, state.kv_row_base, state.context_lens_local)
+        # the public call with HOST buffers: pinned inputs in, indices and context out
+        if graphed is None:
+            for dst, src in zip(stage_q, host_q[i % n_sets]):
+                dst.copy_(src, non_blocking=True)
+            idx, c, _ = step.run(stage_q[0], stage_q[1], stage_q[2], state.k_cache, state.context_lens,
+                                 state.block_table, state.kv, state.kv_row_base, state.context_lens_local)
+        else:
+            idx, c, _ = graphed.replay(*host_q[i % n_sets])
         host_idx.copy_(idx, non_blocking=True)
         host_ctx.copy_(c, non_blocking=True)
         torch.cuda.current_stream().synchronize()
@@ -253,9 +272,9 @@ def main():
         K.indexer_paged_fp8_logits(step.q_fp8, step.weights, state.k_cache, PAGE, state.context_lens_local,
                                    state.block_table, max_cols=step.max_cols, out=step.logits)
         ev[1].record()
-        K.topk_select(step.logits, TOPK, col_end=state.context_lens_local, sorted=False,
-                      out=step.cand[:, :TOPK], out_values=step.cand[:, TOPK:].view(torch.float32),
-                      row_pos_offset=step.pos_offset if world > 1 else None)
+        K.topk_select_split(step.logits, TOPK, step.topk_scratch, col_end=state.context_lens_local, sorted=False,
+                            out=step.cand[:, :TOPK], out_values=step.cand[:, TOPK:].view(torch.float32),
+                            row_pos_offset=step.pos_offset if world > 1 else None)
         ev[2].record()
         idx = step.merge_candidates() if world > 1 else step.cand[:, :TOPK]
         torch.sub(state.context_lens, 1, out=step.q_pos)
@@ -284,14 +303,14 @@ def main():
         achieved = idx_bytes / (stage_ms["indexer"] * 1e-3) / 1e9
         h2d = sum(t.numel() * t.element_size() for t in host_q[0])
         d2h = host_idx.numel() * 4 + host_ctx.numel() * 4
-        launches = 4 if world == 1 else 7
+        launches = 5 if world == 1 else 8
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8(e4m3) index scores / bf16 attention, fp32 accumulate",
             "data": "synthetic",
             "config": {"workload": WORKLOAD if (B, ctx) == (BATCH, CONTEXT) else f"batch {B}, context {ctx} (non-default)",
-                       "parallelism": f"key-sharded x{world}",
+                       "parallelism": f"key-sharded x{world}", "launch": "eager" if graphed is None else "cuda-graph replay",
                        "l2": "inputs larger than L2 (index-key cache %.2f GB per GPU, 4 rotating query sets)"
                              % (idx_bytes / 1e9)},
             "indexer_topk_us_per_step": 1e3 * (stage_ms["quant+indexer"] + stage_ms["topk"]),

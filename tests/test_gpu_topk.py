@@ -131,3 +131,35 @@ def test_topk_unsorted_same_set(n_cols, k):
     ref = _ref_sets(s, k)
     idx = K.topk_select(s.cuda(), k, sorted=False).cpu()
     assert torch.equal(torch.sort(idx, dim=1).values, torch.sort(ref, dim=1).values)
+
+
+@pytest.mark.parametrize("n_rows,n_cols,k,splits", [(5, 131072, 2048, 4), (3, 40000, 512, 3), (64, 32768, 2048, 0),
+                                                    (2, 100003, 2048, 7)])
+def test_topk_split_equals_single(n_rows, n_cols, k, splits):
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(n_cols * 3 + k)
+    s = torch.randn(n_rows, n_cols, generator=g).cuda()
+    hi = torch.randint(n_cols // 2, n_cols + 1, (n_rows,), generator=g, dtype=torch.int32)
+    hi[0] = 100                                   # a short row: the second kernel selects on its own
+    if n_rows > 2:
+        hi[2] = 0                                 # an empty row
+    off = torch.arange(n_rows, dtype=torch.int32) * 1000
+    scratch = K.topk_scratch(n_rows, s.device)
+    ref, ref_v = K.topk_select(s, k, col_end=hi.cuda(), row_pos_offset=off.cuda(), return_values=True)
+    for _ in range(2):                            # twice: the scratch counters must be re-armed
+        out, val = K.topk_select_split(s, k, scratch, col_end=hi.cuda(), row_pos_offset=off.cuda(), splits=splits,
+                                       out_values=torch.empty(n_rows, k, device="cuda"))
+        assert torch.equal(out, ref) and torch.equal(val, ref_v)
+        assert (scratch[1] == 0).all()
+    uns = K.topk_select_split(s, k, scratch, col_end=hi.cuda(), row_pos_offset=off.cuda(), sorted=False)
+    assert torch.equal(torch.sort(uns, 1).values, torch.sort(ref, 1).values)
+
+
+def test_topk_split_ties_fall_back():
+    from transarch_b200 import kernels as K
+    s = torch.zeros(3, 60000, device="cuda")
+    s[1] = (torch.arange(60000, device="cuda") % 7).float()
+    scratch = K.topk_scratch(3, s.device)
+    out = K.topk_select_split(s, 2048, scratch, splits=4)
+    assert torch.equal(out, K.topk_select(s, 2048))
+    assert torch.equal(out[0].cpu(), torch.arange(2048, dtype=torch.int32))

@@ -47,6 +47,9 @@ struct TopkParams {
   int32_t sorted;
   int32_t seg_cols;     // > 0: column c lives at (c / seg_cols) * seg_stride + c % seg_cols of its row
   int64_t seg_stride;
+  // split mode: candidates pre-collected by topk_collect_kernel into global scratch
+  uint64_t* pre_cand;   // [n_rows, kCandCap]
+  int32_t* pre_count;   // [n_rows]; > kCandCap means "no usable list, select from the row itself"
 };
 
 __device__ __forceinline__ bool score_valid(float v, int keep_pos_inf) {
@@ -226,6 +229,70 @@ __device__ void find_threshold_bin(const uint32_t* hist, int need, int* res, uin
   __syncthreads();
 }
 
+// Sample the row into the 4096-bin histogram and choose the bin floor: with a 6-sigma margin at
+// least k elements of the row lie at or above it.  Returns false when the fast path does not
+// apply (margin too wide for the candidate list, or a sample with too few valid scores).  All
+// threads of the CTA call it.  Rows up to kSampleMax are histogrammed completely (exact bin).
+//
+// Shared-memory atomics on the few bins around the mode of the scores serialise badly, and those
+// bins are irrelevant for a top-k: a first pass over 1024 samples finds a bin well below the
+// wanted quantile (4x the wanted tail mass), and the main pass only counts scores at or above it.
+template <class Off>
+__device__ bool sample_bin_floor(const TopkParams& p, const float* __restrict__ src, int begin, int n, int k,
+                                 Off&& coff, uint32_t* hist, int* s_res, uint32_t* s_seg, uint32_t* bin_floor) {
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const bool exact = n <= kSampleMax;
+  const int m = exact ? n : kSampleMax;
+  const int n_chunks = kSampleMax / kSampleChunk;  // 128
+  const int64_t step = exact ? kSampleChunk : n / n_chunks;
+  const float ratio = static_cast<float>(n) / static_cast<float>(m);
+  const float want_full = exact ? static_cast<float>(k) : k + 6.0f * sqrtf(2.0f * k * ratio) + 32.0f;
+  if (want_full > 0.8f * kCandCap) return false;
+  const int want_sample = static_cast<int>(ceilf(want_full / ratio));
+
+  // pass 1: 8 samples from the head of every chunk
+  for (int i = tid; i < kHistBins; i += nthr) hist[i] = 0;
+  __syncthreads();
+  const int m1 = min(m, n_chunks * 8);
+  for (int i = tid; i < ((m1 + 31) & ~31); i += nthr) {
+    const int c = i >> 3;
+    const int col = exact ? i : begin * 0 + static_cast<int>(c * step) + (i & 7);
+    float v = 0.f;
+    if (i < m1) v = __ldg(src + coff(begin + col));
+    hist_add(hist, float_to_ordered(v) >> 20, (i < m1) && score_valid(v, p.keep_pos_inf));
+  }
+  __syncthreads();
+  const int want1 = min(m1, 4 * static_cast<int>(ceilf(static_cast<float>(want_sample) * m1 / m)) + 8);
+  find_threshold_bin(hist, want1, s_res, s_seg);
+  const uint32_t bin_lo = s_res[0] < 0 ? 0u : static_cast<uint32_t>(s_res[0]);
+  __syncthreads();
+
+  // pass 2: the full sample, counting only scores at or above bin_lo
+  for (int i = tid; i < kHistBins; i += nthr) hist[i] = 0;
+  __syncthreads();
+  for (int base = 0; base < m; base += nthr * 8) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + u * nthr + tid;
+      const int c = i / kSampleChunk;
+      v[u] = (i < m) ? __ldg(src + coff(begin + static_cast<int>(c * step) + (i - c * kSampleChunk))) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + u * nthr + tid;
+      const uint32_t bin = float_to_ordered(v[u]) >> 20;
+      hist_add(hist, bin, (i < m) && bin >= bin_lo && score_valid(v[u], p.keep_pos_inf));
+    }
+  }
+  __syncthreads();
+  find_threshold_bin(hist, want_sample, s_res, s_seg);
+  const bool ok = s_res[0] >= 0;   // fewer counted samples than wanted: bin_lo was too high, or too few valid scores
+  if (ok) *bin_floor = static_cast<uint32_t>(s_res[0]);
+  __syncthreads();
+  return ok;
+}
+
 struct SelectResult {
   bool take_all;     // fewer valid keys than wanted: every valid key wins
   uint64_t full;     // decided leading bits of the threshold composite
@@ -312,53 +379,33 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   __syncthreads();
 
   // ------------------------------------------------------------------ candidate collection
-  uint32_t bin_floor = 0;
-  bool try_fast = true;
-  if (n > kCandCap) {
-    for (int i = tid; i < kHistBins; i += nthr) hist[i] = 0;
-    __syncthreads();
-    // rows up to kSampleMax are histogrammed completely (exact threshold bin); longer rows
-    // through contiguous chunks spread evenly over the row
-    const bool exact = n <= kSampleMax;
-    const int m = exact ? n : kSampleMax;
-    const int64_t step = exact ? kSampleChunk : n / (kSampleMax / kSampleChunk);
-    for (int base = 0; base < m; base += nthr * 8) {
-      float v[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int i = base + u * nthr + tid;
-        const int c = i / kSampleChunk;
-        v[u] = (i < m) ? __ldg(src + coff(begin + static_cast<int>(c * step) + (i - c * kSampleChunk))) : 0.f;
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int i = base + u * nthr + tid;
-        const bool ok = (i < m) && score_valid(v[u], p.keep_pos_inf);
-        hist_add(hist, float_to_ordered(v[u]) >> 20, ok);
-      }
-    }
-    __syncthreads();
-    // elements wanted at or above the bin: k, plus 6 sigma of the scaled-up sample count
-    const float ratio = static_cast<float>(n) / static_cast<float>(m);
-    const float want_full = exact ? static_cast<float>(k) : k + 6.0f * sqrtf(2.0f * k * ratio) + 32.0f;
-    if (want_full > 0.8f * kCandCap) {
-      try_fast = false;
-    } else {
-      const int want_sample = static_cast<int>(ceilf(want_full / ratio));
-      find_threshold_bin(hist, want_sample, s_res, s_seg);
-      if (s_res[0] < 0) try_fast = false;  // sample too sparse (many invalid entries)
-      else bin_floor = static_cast<uint32_t>(s_res[0]);
-    }
-    __syncthreads();
-  }
-
-  // Each warp compacts its takes into its own segment of the candidate list with votes
-  // only (no atomics); a full segment raises the overflow flag and the row falls back.
-  bool from_smem = false;
   const int warp_id = tid >> 5, lane_id = tid & 31, n_warps = nthr >> 5;
   const int seg_cap = kCandCap / n_warps;
   uint64_t* my_seg = cand + warp_id * seg_cap;
+  bool from_smem = false;
   int cnt = 0;  // total candidates
+  bool have_pre = false;
+  if (p.pre_cand) {
+    // split mode: the candidates of this row were collected by topk_collect_kernel
+    const int c = p.pre_count[row];
+    __syncthreads();
+    if (tid == 0) p.pre_count[row] = 0;  // re-arm the counter for the next call
+    if (c >= k && c <= kCandCap) {
+      const uint64_t* g = p.pre_cand + static_cast<int64_t>(row) * kCandCap;
+      for (int i = tid; i < c; i += nthr) cand[i] = g[i];
+      if (tid < n_warps) s_warp_cnt[tid] = max(0, min(seg_cap, c - tid * seg_cap));
+      __syncthreads();
+      have_pre = true;
+      from_smem = true;
+      cnt = c;
+    }
+  }
+  uint32_t bin_floor = 0;
+  bool try_fast = !have_pre;
+  if (try_fast && n > kCandCap) try_fast = sample_bin_floor(p, src, begin, n, k, coff, hist, s_res, s_seg, &bin_floor);
+
+  // Each warp compacts its takes into its own segment of the candidate list with votes
+  // only (no atomics); a full segment raises the overflow flag and the row falls back.
   if (try_fast) {
     int wcnt = 0;  // warp-uniform
     stream_row(src, begin, n, vec_ok, coff, [&](float v, int col, bool in_range) {
@@ -461,6 +508,73 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   }
 }
 
+
+// Split mode, first kernel: CTA (split, row) samples the whole row (every split of a row arrives
+// at the same bin floor), streams its slice of the row and appends the candidates to the row's
+// list in global scratch.  A count above kCandCap tells the second kernel that no usable list
+// exists for the row.
+__global__ void __launch_bounds__(512, 2) topk_collect_kernel(const TopkParams p, int splits) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw);
+  uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + kHistBins * sizeof(uint32_t));
+  __shared__ int s_res[3], s_warp_cnt[32], s_overflow, s_base;
+  __shared__ uint32_t s_seg[32];
+
+  const int row = blockIdx.y, split = blockIdx.x;
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  int begin = p.col_begin ? p.col_begin[row] : 0;
+  int end = p.col_end ? p.col_end[row] : p.n_cols;
+  begin = max(begin, 0);
+  end = min(end, p.n_cols);
+  const int n = end - begin;
+  if (n <= 0) return;
+  const float* src = p.scores + row * p.row_stride;
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.scores) & 15) == 0) && ((p.row_stride & 3) == 0);
+  auto coff = [](int col) { return col; };
+  if (tid == 0) s_overflow = 0;
+  uint32_t bin_floor = 0;
+  bool ok = n > kCandCap;  // short rows are cheaper in the second kernel alone
+  if (ok) ok = sample_bin_floor(p, src, begin, n, p.k, coff, hist, s_res, s_seg, &bin_floor);
+  if (!ok) {
+    if (split == 0 && tid == 0) atomicAdd(&p.pre_count[row], kCandCap + 1);
+    return;
+  }
+  const int slice = (((n + splits - 1) / splits) + 3) & ~3;
+  const int my_begin = begin + split * slice;
+  const int my_n = min(slice, end - my_begin);
+  const int warp_id = tid >> 5, lane_id = tid & 31, n_warps = nthr >> 5;
+  const int seg_cap = kCandCap / n_warps;
+  uint64_t* my_seg = cand + warp_id * seg_cap;
+  int wcnt = 0;
+  if (my_n > 0) {
+    stream_row(src, my_begin, my_n, vec_ok, coff, [&](float v, int col, bool in_range) {
+      const bool take = in_range && score_valid(v, p.keep_pos_inf) && (float_to_ordered(v) >> 20) >= bin_floor;
+      const unsigned act = __ballot_sync(0xffffffffu, take);
+      if (take) {
+        const int slot = wcnt + __popc(act & ((1u << lane_id) - 1));
+        if (slot < seg_cap) my_seg[slot] = make_composite(v, out_position(p, row, col));
+      }
+      wcnt += __popc(act);
+    });
+  }
+  if (lane_id == 0) {
+    s_warp_cnt[warp_id] = min(wcnt, seg_cap);
+    if (wcnt > seg_cap) s_overflow = 1;
+  }
+  __syncthreads();
+  int total = 0, my_off = 0;
+  for (int w = 0; w < n_warps; ++w) {
+    if (w == warp_id) my_off = total;
+    total += s_warp_cnt[w];
+  }
+  if (tid == 0) s_base = atomicAdd(&p.pre_count[row], s_overflow ? kCandCap + 1 : total);
+  __syncthreads();
+  const int base = s_base;
+  if (s_overflow || base + total > kCandCap) return;  // the count already marks the list unusable
+  uint64_t* g = p.pre_cand + static_cast<int64_t>(row) * kCandCap + base + my_off;
+  for (int i = lane_id; i < s_warp_cnt[warp_id]; i += 32) g[i] = my_seg[i];
+}
+
 void set_last_error(const char* msg);
 
 }  // namespace b200dsa
@@ -499,6 +613,48 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
   }
   const int threads = n_cols > 16384 ? 1024 : 512;
   topk_select_kernel<<<n_rows, threads, smem, static_cast<cudaStream_t>(stream)>>>(p, k_pow2);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  return B200DSA_OK;
+}
+
+extern "C" int b200dsa_topk_select_split(const float* scores, int64_t row_stride, int32_t n_rows, int32_t n_cols,
+                                         const int32_t* col_begin, const int32_t* col_end, int32_t k,
+                                         int32_t keep_pos_inf, int32_t sorted, const int32_t* row_pos_offset,
+                                         int32_t splits, void* scratch_cand, int32_t* scratch_count,
+                                         int32_t* out_idx, float* out_val, int64_t out_stride, void* stream) {
+  if (n_rows == 0) return B200DSA_OK;
+  if (!scores || !out_idx || !scratch_cand || !scratch_count || n_rows < 0 || n_cols < 0 || k < 1 ||
+      k > kCandCap || out_stride < k || row_stride < n_cols || splits < 1 || splits > 64) {
+    set_last_error("b200dsa_topk_select_split: bad argument (1<=k<=8192, 1<=splits<=64, scratch required)");
+    return B200DSA_EINVAL;
+  }
+  if (reinterpret_cast<uintptr_t>(scratch_cand) & 7) {
+    set_last_error("b200dsa_topk_select_split: scratch_cand must be 8-byte aligned");
+    return B200DSA_EALIGN;
+  }
+  TopkParams p{scores, row_stride, n_rows, n_cols, col_begin, col_end, k, keep_pos_inf, nullptr, 0, nullptr, 0, 0,
+               row_pos_offset, out_idx, out_val, out_stride, sorted, 0, 0,
+               static_cast<uint64_t*>(scratch_cand), scratch_count};
+  int k_pow2 = 32;
+  while (k_pow2 < k) k_pow2 <<= 1;
+  const size_t smem_a = kHistBins * sizeof(uint32_t) + kCandCap * sizeof(uint64_t);
+  const size_t smem_b = kHistBins * sizeof(uint32_t) + (kCandCap + kEqCap + k_pow2) * sizeof(uint64_t);
+  cudaError_t e = cudaFuncSetAttribute(topk_collect_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem_a));
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kHistBins * sizeof(uint32_t) + (2 * kCandCap + kEqCap) * sizeof(uint64_t)));
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  topk_collect_kernel<<<dim3(splits, n_rows), 512, smem_a, st>>>(p, splits);
+  topk_select_kernel<<<n_rows, 1024, smem_b, st>>>(p, k_pow2);
   e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));

@@ -86,6 +86,10 @@ class SparseDecodeStep:
         self.ctx = torch.empty(batch, n_heads, 512, dtype=f32, device=dev)
         self.lse = torch.empty(batch, n_heads, dtype=f32, device=dev)
         self.q_pos = torch.empty(batch, dtype=i32, device=dev)
+        # few long rows: spread the top-k of every row over several CTAs (global scratch, allocated once)
+        self.topk_scratch = None
+        if hasattr(backend, "topk_scratch") and batch <= 148 and max_local_ctx >= 32768:
+            self.topk_scratch = backend.topk_scratch(batch, dev)
         if n > 1:
             self.cand_all = torch.empty(n, batch, 2 * topk, dtype=i32, device=dev)
             self.merged = torch.empty(batch, topk, dtype=i32, device=dev)
@@ -103,9 +107,13 @@ class SparseDecodeStep:
                                    max_cols=self.max_cols, out=self.logits)
         idx = self.cand[:, : self.topk]
         val = self.cand[:, self.topk:].view(torch.float32)
-        K.topk_select(self.logits, self.topk, col_end=context_lens_local, sorted=self.sorted_topk,
-                      row_pos_offset=self.pos_offset if self.shard.world_size > 1 else None,
-                      out=idx, out_values=val)
+        offset = self.pos_offset if self.shard.world_size > 1 else None
+        if self.topk_scratch is not None:
+            K.topk_select_split(self.logits, self.topk, self.topk_scratch, col_end=context_lens_local,
+                                sorted=self.sorted_topk, row_pos_offset=offset, out=idx, out_values=val)
+        else:
+            K.topk_select(self.logits, self.topk, col_end=context_lens_local, sorted=self.sorted_topk,
+                          row_pos_offset=offset, out=idx, out_values=val)
         return idx
 
     def merge_candidates(self) -> torch.Tensor:
@@ -148,3 +156,49 @@ class SparseDecodeStep:
         if self.shard.world_size > 1:
             ctx, lse = self.combine()
         return idx, ctx, lse
+
+
+class GraphedDecodeStep:
+    """The whole step captured once into a CUDA graph and replayed: per-step host work drops to
+    one graph launch (the kernels' host calls, tensor-map encodes and NCCL enqueues are recorded
+    at capture time).  Inputs are copied into static buffers before each replay; outputs are the
+    step's own pre-allocated buffers.  Capture after at least one eager run (so that lazy
+    initialisation, e.g. NCCL communicators, is done) and never while another capture is active."""
+
+    def __init__(self, step: SparseDecodeStep, k_cache, context_lens, block_table, kv, kv_row_base,
+                 context_lens_local=None):
+        self.step = step
+        dev = step.dev
+        B, H = step.B, step.H
+        self.q_idx = torch.empty(B, 64, 128, dtype=torch.bfloat16, device=dev)
+        self.w = torch.empty(B, 64, dtype=torch.float32, device=dev)
+        self.q_lat = torch.empty(B, H, 576, dtype=torch.bfloat16, device=dev)
+        self._state = (k_cache, context_lens, block_table, kv, kv_row_base, context_lens_local)
+        self.graph = None
+        self.out = None
+
+    def capture(self):
+        k_cache, context_lens, block_table, kv, kv_row_base, local = self._state
+        if local is None:
+            local = local_context_lens(context_lens, self.step.shard)
+            self._state = (k_cache, context_lens, block_table, kv, kv_row_base, local)
+        side = torch.cuda.Stream(device=self.step.dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):            # warm-up on the capture stream
+            self.step.run(self.q_idx, self.w, self.q_lat, k_cache, context_lens, block_table, kv, kv_row_base, local)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.out = self.step.run(self.q_idx, self.w, self.q_lat, k_cache, context_lens, block_table, kv,
+                                     kv_row_base, local)
+        return self
+
+    def replay(self, q_idx=None, w=None, q_lat=None):
+        """Copy the given inputs (device or pinned host tensors) into the static buffers and replay."""
+        if q_idx is not None:
+            self.q_idx.copy_(q_idx, non_blocking=True)
+            self.w.copy_(w, non_blocking=True)
+            self.q_lat.copy_(q_lat, non_blocking=True)
+        self.graph.replay()
+        return self.out

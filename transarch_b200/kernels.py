@@ -63,6 +63,45 @@ def topk_select(scores: torch.Tensor, k: int, *, col_begin: Optional[torch.Tenso
     return out[:n_rows, :k]
 
 
+CAND_CAP = 8192  # candidate list entries per row of the split top-k scratch
+
+
+def topk_scratch(n_rows: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Zeroed scratch for topk_select_split: (candidates uint64-as-int64 [n_rows, 8192], counters int32 [n_rows])."""
+    return (torch.zeros(n_rows, CAND_CAP, dtype=torch.int64, device=device),
+            torch.zeros(n_rows, dtype=torch.int32, device=device))
+
+
+def topk_select_split(scores: torch.Tensor, k: int, scratch: Tuple[torch.Tensor, torch.Tensor], *,
+                      col_begin: Optional[torch.Tensor] = None, col_end: Optional[torch.Tensor] = None,
+                      keep_pos_inf: bool = False, row_pos_offset: Optional[torch.Tensor] = None,
+                      sorted: bool = True, splits: int = 0, out: Optional[torch.Tensor] = None,
+                      out_values: Optional[torch.Tensor] = None):
+    """Top-k for few long rows, several CTAs per row; see b200dsa_topk_select_split.  `scratch`
+    comes from topk_scratch() and may be reused by later calls on the same stream."""
+    require_cuda(scores, col_begin, col_end, row_pos_offset, *scratch)
+    if scores.dtype != torch.float32 or scores.dim() != 2 or scores.stride(1) != 1:
+        raise _lib.B200DSAError("scores must be a 2-D fp32 tensor with unit column stride")
+    n_rows, n_cols = scores.shape
+    cand, count = scratch
+    if cand.numel() < n_rows * CAND_CAP or count.numel() < n_rows:
+        raise _lib.B200DSAError("scratch is too small for this many rows")
+    if splits <= 0:
+        splits = max(1, min(16, (2 * 148) // max(1, n_rows)))
+    if out is None:
+        out = torch.empty(n_rows, k, dtype=torch.int32, device=scores.device)
+    if out_values is not None and (out_values.dtype != torch.float32 or out_values.stride(0) != out.stride(0)):
+        raise _lib.B200DSAError("out_values must be fp32 with the row stride of out")
+    rc = _lib.load().b200dsa_topk_select_split(
+        ptr(scores), scores.stride(0), n_rows, n_cols, ptr(_i32(col_begin, "col_begin")),
+        ptr(_i32(col_end, "col_end")), k, int(keep_pos_inf), int(sorted), ptr(_i32(row_pos_offset, "row_pos_offset")),
+        splits, ptr(cand), ptr(count), ptr(out), ptr(out_values), out.stride(0), stream_ptr())
+    check(rc, "b200dsa_topk_select_split")
+    if out_values is not None:
+        return out[:n_rows, :k], out_values[:n_rows, :k]
+    return out[:n_rows, :k]
+
+
 def indexer_paged_fp8_logits(q_fp8: torch.Tensor, weights: torch.Tensor, cache: torch.Tensor, page_size: int,
                              context_lens: torch.Tensor, block_table: torch.Tensor, *, next_n: int = 1,
                              max_cols: Optional[int] = None, out_scale: float = 1.0,
