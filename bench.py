@@ -333,7 +333,17 @@ def main():
                                               f"all stages (quantise, score, top-k, attention), {dt:.1f} s"}
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # A captured graph that holds NCCL kernels keeps the communicator busy: tearing the process
+        # group down while it exists never returns.  Release the graph first; then leave without
+        # running the communicator's destructor at all (every rank has printed and synchronised).
+        if graphed is not None:
+            graphed.graph.reset()
+            graphed = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
