@@ -149,11 +149,13 @@ int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const float* weigh
  *   q_bf16 [n_items, n_heads, 576], kv_bf16 [kv_rows, 576] (512 value dims then 64 rope dims),
  *   indices [n_items, idx_stride] int32, kv_row_base / q_pos optional (0 / no bound),
  *   ctx [n_items, n_heads, 512] fp32, lse [n_items, n_heads] fp32.  1 <= n_heads <= 128.
- * Rows outside [0, kv_rows) are skipped and reported through status (2).
+ * n_idx_item (optional int32 [n_items]) limits item i to its first n_idx_item[i] indices
+ * (compacted shard lists).  Rows outside [0, kv_rows) are skipped and reported through status (2).
  * ------------------------------------------------------------------------------------- */
 int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16, int64_t kv_rows,
                               const int64_t* kv_row_base, const int32_t* indices, int64_t idx_stride,
-                              int32_t n_idx, const int32_t* q_pos, int32_t pos_lo, int32_t pos_hi,
+                              int32_t n_idx, const int32_t* n_idx_item, const int32_t* q_pos,
+                              int32_t pos_lo, int32_t pos_hi,
                               int32_t n_items, int32_t n_heads, float sm_scale, float* ctx, float* lse,
                               int32_t* status, void* stream);
 
@@ -168,6 +170,13 @@ int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16, int64_t k
  * ------------------------------------------------------------------------------------- */
 int b200dsa_lse_combine(const float* ctx_parts, const float* lse_parts, int32_t n_parts, int64_t n_rows,
                         float* ctx_out, float* lse_out, void* stream);
+
+/* Shard ownership compaction: per row, the positions inside [pos_lo, pos_hi) are moved to the
+ * front of out (relative order kept), the rest of the row is -1, count[row] = how many.  Lets a
+ * rank attend only the selected keys it owns.  out must not alias indices. */
+int b200dsa_compact_owned(const int32_t* indices, int64_t idx_stride, int32_t n_rows, int32_t n_idx,
+                          int32_t pos_lo, int32_t pos_hi, int32_t* out, int64_t out_stride,
+                          int32_t* count, void* stream);
 
 /* All-reduce form of the merge above, for partials that live on different GPUs.  After a MAX
  * all-reduce of lse gives lse_max, prescale writes 516-float wire rows

@@ -65,7 +65,7 @@ def sorted_by(vals, pos):
 
 
 def sparse_mla_decode(q, kv, indices, sm_scale, *, kv_row_base=None, q_pos=None, pos_lo=0, pos_hi=2 ** 31 - 1,
-                      ctx=None, lse=None):
+                      n_idx_item=None, ctx=None, lse=None):
     n = q.shape[0]
     for b in range(n):
         idx = indices[b].long()

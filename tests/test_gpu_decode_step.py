@@ -92,3 +92,15 @@ def test_quant_fold_matches_oracle_bitwise():
     rq, rw = O.quant_q_fold_weights(q.float(), w, IDX_SCALE)
     assert torch.equal(q_fp8.cpu().view(torch.uint8), rq.view(torch.uint8))
     assert torch.allclose(wf.cpu(), rw, rtol=1e-6, atol=0)
+
+
+def test_compact_owned():
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(12)
+    idx = torch.randint(-1, 5000, (7, 2048), generator=g, dtype=torch.int32)
+    out = torch.empty_like(idx).cuda(); cnt = torch.empty(7, dtype=torch.int32, device="cuda")
+    K.compact_owned(idx.cuda(), 1000, 2500, out, cnt)
+    for r in range(7):
+        own = idx[r][(idx[r] >= 1000) & (idx[r] < 2500)]
+        assert int(cnt[r]) == own.numel()
+        assert torch.equal(out[r, :own.numel()].cpu(), own) and (out[r, own.numel():] == -1).all()

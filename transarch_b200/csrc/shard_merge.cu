@@ -73,6 +73,41 @@ __global__ void __launch_bounds__(128) lse_finalize_kernel(const float* __restri
   if (tid == 0 && lse_out) lse_out[row] = den > 0.f ? __ldg(lse_max + row) + logf(den) : -INFINITY;
 }
 
+// Per row: move the positions that fall into [pos_lo, pos_hi) to the front (order kept), fill the
+// rest with -1 and report how many there are.  One CTA of 256 threads per row.
+__global__ void __launch_bounds__(256) compact_owned_kernel(const int32_t* __restrict__ idx, int64_t idx_stride, int n_idx,
+                                                            int pos_lo, int pos_hi, int32_t* __restrict__ out,
+                                                            int64_t out_stride, int32_t* __restrict__ count) {
+  __shared__ int s_warp[8];
+  __shared__ int s_base;
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int32_t* src = idx + row * idx_stride;
+  int32_t* dst = out + row * out_stride;
+  if (tid == 0) s_base = 0;
+  __syncthreads();
+  for (int j0 = 0; j0 < n_idx; j0 += 256) {
+    const int j = j0 + tid;
+    const int v = (j < n_idx) ? src[j] : -1;
+    const bool own = v >= pos_lo && v < pos_hi;
+    const unsigned m = __ballot_sync(0xffffffffu, own);
+    if (lane == 0) s_warp[warp] = __popc(m);
+    __syncthreads();
+    int off = s_base;
+    for (int w = 0; w < warp; ++w) off += s_warp[w];
+    if (own) dst[off + __popc(m & ((1u << lane) - 1))] = v;
+    __syncthreads();
+    if (tid == 0) {
+      int t = 0;
+      for (int w = 0; w < 8; ++w) t += s_warp[w];
+      s_base += t;
+    }
+    __syncthreads();
+  }
+  const int total = s_base;
+  for (int j = total + tid; j < n_idx; j += 256) dst[j] = -1;
+  if (tid == 0) count[row] = total;
+}
+
 void set_last_error(const char* msg);
 
 }  // namespace b200dsa
@@ -128,6 +163,25 @@ extern "C" int b200dsa_lse_finalize(const float* wire, const float* lse_max, int
   }
   lse_finalize_kernel<<<static_cast<unsigned>(n_rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(wire, lse_max,
                                                                                                     ctx_out, lse_out);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  return B200DSA_OK;
+}
+
+extern "C" int b200dsa_compact_owned(const int32_t* indices, int64_t idx_stride, int32_t n_rows, int32_t n_idx,
+                                     int32_t pos_lo, int32_t pos_hi, int32_t* out, int64_t out_stride,
+                                     int32_t* count, void* stream) {
+  if (n_rows == 0) return B200DSA_OK;
+  if (!indices || !out || !count || n_rows < 0 || n_idx < 0 || idx_stride < n_idx || out_stride < n_idx ||
+      indices == out) {
+    set_last_error("b200dsa_compact_owned: bad argument (out must not alias indices)");
+    return B200DSA_EINVAL;
+  }
+  compact_owned_kernel<<<n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(indices, idx_stride, n_idx, pos_lo,
+                                                                             pos_hi, out, out_stride, count);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));

@@ -52,6 +52,7 @@ struct MlaParams {
   const int32_t* indices;      // [n_items, idx_stride] key positions, -1 = none
   int64_t idx_stride;
   int32_t n_idx;
+  const int32_t* n_idx_item;   // nullable [n_items]: only the first n_idx_item[i] indices of item i are looked at
   const int32_t* q_pos;        // nullable [n_items]: keys beyond this position are masked
   int32_t pos_lo, pos_hi;      // only positions in [pos_lo, pos_hi) are attended (shard ownership)
   int32_t n_items, n_heads;
@@ -134,7 +135,8 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int n_tiles = (p.n_idx + kMlaTile - 1) / kMlaTile;
+  const int n_idx = p.n_idx_item ? max(0, min(p.n_idx, p.n_idx_item[blockIdx.x >> 1])) : p.n_idx;
+  const int n_tiles = (n_idx + kMlaTile - 1) / kMlaTile;
   volatile int* abort_flag = &s_abort;
 
   if (tid == 0) {
@@ -174,7 +176,7 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
       const bool ok = mbar_wait(&kv_empty[s], ((t / kMlaStages) & 1) ^ 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) break;
       const int j = t * kMlaTile + r;
-      const int idx = (j < p.n_idx) ? __ldg(idx_row + j) : -1;
+      const int idx = (j < n_idx) ? __ldg(idx_row + j) : -1;
       bool valid = idx >= 0 && idx <= qpos && idx >= p.pos_lo && idx < p.pos_hi;
       const int64_t grow = row_base + idx;
       if (valid && (grow < 0 || grow >= p.kv_rows)) {
@@ -425,7 +427,8 @@ using namespace b200dsa;
 
 extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16, int64_t kv_rows,
                                          const int64_t* kv_row_base, const int32_t* indices, int64_t idx_stride,
-                                         int32_t n_idx, const int32_t* q_pos, int32_t pos_lo, int32_t pos_hi,
+                                         int32_t n_idx, const int32_t* n_idx_item, const int32_t* q_pos,
+                                         int32_t pos_lo, int32_t pos_hi,
                                          int32_t n_items, int32_t n_heads, float sm_scale, float* ctx, float* lse,
                                          int32_t* status, void* stream) {
   if (n_items == 0) return B200DSA_OK;
@@ -468,6 +471,7 @@ extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16
   p.indices = indices;
   p.idx_stride = idx_stride;
   p.n_idx = n_idx;
+  p.n_idx_item = n_idx_item;
   p.q_pos = q_pos;
   p.pos_lo = pos_lo;
   p.pos_hi = pos_hi;

@@ -93,6 +93,8 @@ class SparseDecodeStep:
         if n > 1:
             self.cand_all = torch.empty(n, batch, 2 * topk, dtype=i32, device=dev)
             self.merged = torch.empty(batch, topk, dtype=i32, device=dev)
+            self.owned = torch.empty(batch, topk, dtype=i32, device=dev)
+            self.owned_count = torch.empty(batch, dtype=i32, device=dev)
             self.lse_max = torch.empty(batch, n_heads, dtype=f32, device=dev)
             self.wire = torch.empty(batch * n_heads, backend.WIRE_ROW, dtype=f32, device=dev)
             self.ctx_out = torch.empty(batch, n_heads, 512, dtype=f32, device=dev)
@@ -129,8 +131,14 @@ class SparseDecodeStep:
         return self.merged
 
     def attend(self, q_lat, kv, kv_row_base, indices, q_pos) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Attention over the selected keys this rank owns (all of them when unsharded)."""
+        count = None
+        if self.shard.world_size > 1 and hasattr(self.K, "compact_owned"):
+            # only about 1/N of the selection lives here: compact it so the kernel walks just those
+            indices, count = self.K.compact_owned(indices, self.shard.pos_lo, self.shard.pos_hi, self.owned,
+                                                  self.owned_count)
         return self.K.sparse_mla_decode(q_lat, kv, indices, self.attn_scale, kv_row_base=kv_row_base, q_pos=q_pos,
-                                        pos_lo=self.shard.pos_lo, pos_hi=self.shard.pos_hi,
+                                        pos_lo=self.shard.pos_lo, pos_hi=self.shard.pos_hi, n_idx_item=count,
                                         ctx=self.ctx, lse=self.lse)
 
     def combine(self) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -169,7 +169,7 @@ def indexer_blocklist_bf16_logits(q: torch.Tensor, weights: torch.Tensor, keys: 
 
 def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: float, *,
                       kv_row_base: Optional[torch.Tensor] = None, q_pos: Optional[torch.Tensor] = None,
-                      pos_lo: int = 0, pos_hi: int = 2 ** 31 - 1,
+                      pos_lo: int = 0, pos_hi: int = 2 ** 31 - 1, n_idx_item: Optional[torch.Tensor] = None,
                       ctx: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None
                       ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Latent-space sparse attention: (ctx [n, H, 512] fp32, lse [n, H] fp32); see
@@ -192,7 +192,7 @@ def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, 
     lib = _lib.load()
     rc = lib.b200dsa_sparse_mla_decode(
         ptr(q), ptr(kv), kv.shape[0], ptr(kv_row_base), ptr(indices), indices.stride(0), indices.shape[1],
-        ptr(q_pos), pos_lo, pos_hi, n, H, sm_scale, ptr(ctx), ptr(lse), ptr(status_word(q.device)), stream_ptr())
+        ptr(_i32(n_idx_item, "n_idx_item")), ptr(q_pos), pos_lo, pos_hi, n, H, sm_scale, ptr(ctx), ptr(lse), ptr(status_word(q.device)), stream_ptr())
     check(rc, "b200dsa_sparse_mla_decode")
     return ctx, lse
 
@@ -357,3 +357,13 @@ def indexer_k_quant_and_cache(k: torch.Tensor, cache: torch.Tensor, slot_mapping
     check(_lib.load().b200dsa_indexer_k_quant_and_cache(ptr(k), ptr(slot_mapping), n, ptr(cache), num_pages,
                                                         page_size, ptr(status_word(k.device)), stream_ptr()),
           "b200dsa_indexer_k_quant_and_cache")
+
+
+def compact_owned(indices: torch.Tensor, pos_lo: int, pos_hi: int, out: torch.Tensor, count: torch.Tensor):
+    """Positions inside [pos_lo, pos_hi) first, -1 after, count per row; see b200dsa_compact_owned."""
+    require_cuda(indices, out, count)
+    n_rows, n_idx = indices.shape
+    check(_lib.load().b200dsa_compact_owned(ptr(indices), indices.stride(0), n_rows, n_idx, pos_lo, pos_hi, ptr(out),
+                                            out.stride(0), ptr(_i32(count, "count")), stream_ptr()),
+          "b200dsa_compact_owned")
+    return out, count
