@@ -72,9 +72,9 @@ int b200dsa_topk_select(const float* scores, int64_t row_stride, int32_t n_rows,
 /* Same selection for few, long rows (decode: tens of rows of 10^5 scores), spread over the
  * whole GPU: `splits` CTAs per row collect the candidates of their slice into global scratch,
  * then one CTA per row finishes the exact selection.  Identity positions (+ row_pos_offset)
- * only.  Scratch: scratch_cand = n_rows*8192 uint64 (8-byte aligned), scratch_count = n_rows
- * int32 that must be ZERO before the first call; the library leaves it zero again after every
- * call.  Calls that share scratch must not overlap on the GPU.  Results equal
+ * only.  Scratch: scratch_cand = n_rows*8192 uint64 (8-byte aligned), scratch_count = 2*n_rows
+ * int32 whose first n_rows entries must be ZERO before the first call; the library leaves them
+ * zero again after every call.  Calls that share scratch must not overlap on the GPU.  Results equal
  * b200dsa_topk_select's (same set; same order when sorted != 0). */
 int b200dsa_topk_select_split(const float* scores, int64_t row_stride, int32_t n_rows, int32_t n_cols,
                               const int32_t* col_begin, const int32_t* col_end, int32_t k,

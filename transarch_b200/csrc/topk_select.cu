@@ -25,7 +25,7 @@ constexpr int kHistBins = 4096;
 constexpr int kCandCap = 8192;   // candidate list entries (64 KB)
 constexpr int kEqCap = 1024;     // undecided-bin list (8 KB)
 constexpr int kSampleChunk = 128;
-constexpr int kSampleMax = 16384;
+constexpr int kSampleMax = 8192;
 
 struct TopkParams {
   const float* scores;
@@ -428,6 +428,14 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
 
   // ------------------------------------------------------------------ exact selection
   auto each_cand = [&](bool /*need_pos*/, auto&& f) {
+    if (have_pre) {  // contiguous list
+      for (int base = 0; base < cnt; base += nthr) {
+        const int i = base + tid;
+        const bool active = i < cnt;
+        f(active ? cand[i] : 0ull, active);
+      }
+      return;
+    }
     for (int base = 0; base < kCandCap; base += nthr) {
       const int i = base + tid;
       const int w = i / seg_cap;
@@ -509,70 +517,93 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
 }
 
 
-// Split mode, first kernel: CTA (split, row) samples the whole row (every split of a row arrives
-// at the same bin floor), streams its slice of the row and appends the candidates to the row's
-// list in global scratch.  A count above kCandCap tells the second kernel that no usable list
-// exists for the row.
-__global__ void __launch_bounds__(512, 2) topk_collect_kernel(const TopkParams p, int splits) {
+// Split mode.  Kernel 1 (one CTA per row) samples the row and stores the bin floor (or -1 when
+// the fast path does not apply: short rows, rows dominated by ties or invalid scores).
+__global__ void __launch_bounds__(1024, 1) topk_floor_kernel(const TopkParams p, int32_t* __restrict__ floor_out) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw);
-  uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + kHistBins * sizeof(uint32_t));
-  __shared__ int s_res[3], s_warp_cnt[32], s_overflow, s_base;
+  __shared__ int s_res[3];
   __shared__ uint32_t s_seg[32];
+  const int row = blockIdx.x;
+  int begin = p.col_begin ? p.col_begin[row] : 0;
+  int end = p.col_end ? p.col_end[row] : p.n_cols;
+  begin = max(begin, 0);
+  end = min(end, p.n_cols);
+  const int n = end - begin;
+  const float* src = p.scores + row * p.row_stride;
+  auto coff = [](int col) { return col; };
+  uint32_t bin_floor = 0;
+  bool ok = n > kCandCap;  // short rows are cheaper in the last kernel alone
+  if (ok) ok = sample_bin_floor(p, src, begin, n, p.k, coff, hist, s_res, s_seg, &bin_floor);
+  if (threadIdx.x == 0) floor_out[row] = ok ? static_cast<int32_t>(bin_floor) : -1;
+}
+
+// Kernel 2: CTA (split, row) streams its slice of the row; every thread keeps the scores at or
+// above the floor in a private list (interleaved in shared memory, no votes, no atomics); the
+// lists are then compacted into the row's candidate list in global scratch.  A count above
+// kCandCap tells the last kernel that no usable list exists for the row.
+constexpr int kCollectThreads = 512;
+constexpr int kCollectSlots = kCandCap / kCollectThreads;  // 16 private entries per thread
+
+__global__ void __launch_bounds__(kCollectThreads, 2)
+topk_collect_kernel(const TopkParams p, int splits, const int32_t* __restrict__ floor_in) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw);  // [slot][thread]
+  __shared__ int s_warp_tot[kCollectThreads / 32], s_base, s_overflow;
 
   const int row = blockIdx.y, split = blockIdx.x;
-  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int begin = p.col_begin ? p.col_begin[row] : 0;
   int end = p.col_end ? p.col_end[row] : p.n_cols;
   begin = max(begin, 0);
   end = min(end, p.n_cols);
   const int n = end - begin;
   if (n <= 0) return;
-  const float* src = p.scores + row * p.row_stride;
-  const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.scores) & 15) == 0) && ((p.row_stride & 3) == 0);
-  auto coff = [](int col) { return col; };
-  if (tid == 0) s_overflow = 0;
-  uint32_t bin_floor = 0;
-  bool ok = n > kCandCap;  // short rows are cheaper in the second kernel alone
-  if (ok) ok = sample_bin_floor(p, src, begin, n, p.k, coff, hist, s_res, s_seg, &bin_floor);
-  if (!ok) {
+  const int fl = floor_in[row];
+  if (fl < 0) {
     if (split == 0 && tid == 0) atomicAdd(&p.pre_count[row], kCandCap + 1);
     return;
   }
+  const float* src = p.scores + row * p.row_stride;
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.scores) & 15) == 0) && ((p.row_stride & 3) == 0);
+  auto coff = [](int col) { return col; };
+  // smallest float of the floor bin; comparing floats directly is equivalent to comparing bins
+  const float thr = fmaxf(ordered_to_float(static_cast<uint32_t>(fl) << 20), -3.402823466e38f);
+  const float vmax = p.keep_pos_inf ? INFINITY : 3.402823466e38f;
+  if (tid == 0) s_overflow = 0;
   const int slice = (((n + splits - 1) / splits) + 3) & ~3;
   const int my_begin = begin + split * slice;
   const int my_n = min(slice, end - my_begin);
-  const int warp_id = tid >> 5, lane_id = tid & 31, n_warps = nthr >> 5;
-  const int seg_cap = kCandCap / n_warps;
-  uint64_t* my_seg = cand + warp_id * seg_cap;
-  int wcnt = 0;
+  int cnt = 0;
   if (my_n > 0) {
     stream_row(src, my_begin, my_n, vec_ok, coff, [&](float v, int col, bool in_range) {
-      const bool take = in_range && score_valid(v, p.keep_pos_inf) && (float_to_ordered(v) >> 20) >= bin_floor;
-      const unsigned act = __ballot_sync(0xffffffffu, take);
-      if (take) {
-        const int slot = wcnt + __popc(act & ((1u << lane_id) - 1));
-        if (slot < seg_cap) my_seg[slot] = make_composite(v, out_position(p, row, col));
+      if (in_range && v >= thr && v <= vmax) {
+        if (cnt < kCollectSlots) cand[cnt * kCollectThreads + tid] = make_composite(v, out_position(p, row, col));
+        ++cnt;
       }
-      wcnt += __popc(act);
     });
   }
-  if (lane_id == 0) {
-    s_warp_cnt[warp_id] = min(wcnt, seg_cap);
-    if (wcnt > seg_cap) s_overflow = 1;
+  if (cnt > kCollectSlots) s_overflow = 1;
+  cnt = min(cnt, kCollectSlots);
+  // block-wide exclusive scan of the private counts
+  int incl = cnt;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
   }
+  if (lane == 31) s_warp_tot[warp] = incl;
   __syncthreads();
-  int total = 0, my_off = 0;
-  for (int w = 0; w < n_warps; ++w) {
-    if (w == warp_id) my_off = total;
-    total += s_warp_cnt[w];
+  int warp_off = 0, total = 0;
+  for (int w = 0; w < kCollectThreads / 32; ++w) {
+    if (w == warp) warp_off = total;
+    total += s_warp_tot[w];
   }
   if (tid == 0) s_base = atomicAdd(&p.pre_count[row], s_overflow ? kCandCap + 1 : total);
   __syncthreads();
   const int base = s_base;
   if (s_overflow || base + total > kCandCap) return;  // the count already marks the list unusable
-  uint64_t* g = p.pre_cand + static_cast<int64_t>(row) * kCandCap + base + my_off;
-  for (int i = lane_id; i < s_warp_cnt[warp_id]; i += 32) g[i] = my_seg[i];
+  uint64_t* g = p.pre_cand + static_cast<int64_t>(row) * kCandCap + base + warp_off + (incl - cnt);
+  for (int j = 0; j < cnt; ++j) g[j] = cand[j * kCollectThreads + tid];
 }
 
 void set_last_error(const char* msg);
@@ -641,7 +672,8 @@ extern "C" int b200dsa_topk_select_split(const float* scores, int64_t row_stride
                static_cast<uint64_t*>(scratch_cand), scratch_count};
   int k_pow2 = 32;
   while (k_pow2 < k) k_pow2 <<= 1;
-  const size_t smem_a = kHistBins * sizeof(uint32_t) + kCandCap * sizeof(uint64_t);
+  const size_t smem_f = kHistBins * sizeof(uint32_t);
+  const size_t smem_a = kCandCap * sizeof(uint64_t);
   const size_t smem_b = kHistBins * sizeof(uint32_t) + (kCandCap + kEqCap + k_pow2) * sizeof(uint64_t);
   cudaError_t e = cudaFuncSetAttribute(topk_collect_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem_a));
@@ -653,7 +685,9 @@ extern "C" int b200dsa_topk_select_split(const float* scores, int64_t row_stride
     return B200DSA_ECUDA;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  topk_collect_kernel<<<dim3(splits, n_rows), 512, smem_a, st>>>(p, splits);
+  int32_t* floor_bin = scratch_count + n_rows;  // second half of the int32 scratch
+  topk_floor_kernel<<<n_rows, 1024, smem_f, st>>>(p, floor_bin);
+  topk_collect_kernel<<<dim3(splits, n_rows), kCollectThreads, smem_a, st>>>(p, splits, floor_bin);
   topk_select_kernel<<<n_rows, 1024, smem_b, st>>>(p, k_pow2);
   e = cudaGetLastError();
   if (e != cudaSuccess) {

@@ -67,9 +67,10 @@ CAND_CAP = 8192  # candidate list entries per row of the split top-k scratch
 
 
 def topk_scratch(n_rows: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Zeroed scratch for topk_select_split: (candidates uint64-as-int64 [n_rows, 8192], counters int32 [n_rows])."""
+    """Zeroed scratch for topk_select_split: (candidates uint64-as-int64 [n_rows, 8192], int32 [2*n_rows]:
+    per-row counters then per-row bin floors)."""
     return (torch.zeros(n_rows, CAND_CAP, dtype=torch.int64, device=device),
-            torch.zeros(n_rows, dtype=torch.int32, device=device))
+            torch.zeros(2 * n_rows, dtype=torch.int32, device=device))
 
 
 def topk_select_split(scores: torch.Tensor, k: int, scratch: Tuple[torch.Tensor, torch.Tensor], *,
@@ -84,7 +85,7 @@ def topk_select_split(scores: torch.Tensor, k: int, scratch: Tuple[torch.Tensor,
         raise _lib.B200DSAError("scores must be a 2-D fp32 tensor with unit column stride")
     n_rows, n_cols = scores.shape
     cand, count = scratch
-    if cand.numel() < n_rows * CAND_CAP or count.numel() < n_rows:
+    if cand.numel() < n_rows * CAND_CAP or count.numel() < 2 * n_rows:
         raise _lib.B200DSAError("scratch is too small for this many rows")
     if splits <= 0:
         splits = max(1, min(16, (2 * 148) // max(1, n_rows)))
