@@ -82,6 +82,25 @@ int b200dsa_topk_select_split(const float* scores, int64_t row_stride, int32_t n
                               int32_t splits, void* scratch_cand, int32_t* scratch_count,
                               int32_t* out_idx, float* out_val, int64_t out_stride, void* stream);
 
+/* b200dsa_topk_select_split for hosts that cannot provide scratch memory.  It has no counterpart
+ * in the reference.  Some callers have no way to allocate on the device when they call us: an
+ * inference server that gave almost the whole GPU to its own pool at start-up leaves no room
+ * for a plug-in's cudaMalloc, and a bare C host may own neither workspace nor allocator.  Here
+ * the candidate lists and counters sit in a 4 MiB array built into the library (present on every
+ * GPU that loads it, until the process ends), so the call allocates nothing.
+ *   - at most 64 rows; more is rejected with B200DSA_EINVAL and a message naming the limit;
+ *   - the first call on a device looks up the array's device address; make that first call
+ *     outside of any stream capture;
+ *   - the array is shared by all calls on a device and keeps the previous call's contents (the
+ *     counters are cleared at the start of each call, on `stream`); two calls that overlap on
+ *     the GPU, from whatever streams or threads, corrupt each other;
+ *   - same arguments and results as b200dsa_topk_select_split otherwise. */
+int b200dsa_topk_select_split_static(const float* scores, int64_t row_stride, int32_t n_rows, int32_t n_cols,
+                                     const int32_t* col_begin, const int32_t* col_end, int32_t k,
+                                     int32_t keep_pos_inf, int32_t sorted, const int32_t* row_pos_offset,
+                                     int32_t splits, int32_t* out_idx, float* out_val, int64_t out_stride,
+                                     void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Decode indexer logits over the paged FP8 key cache (tcgen05 FP8 contraction).
  *

@@ -696,3 +696,75 @@ extern "C" int b200dsa_topk_select_split(const float* scores, int64_t row_stride
   }
   return B200DSA_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Split top-k without caller-provided scratch.
+//
+// Some hosts of this library cannot obtain device memory at call time: a serving engine that
+// handed nearly all of the GPU to its own memory pool at start-up (a later cudaMalloc from a
+// plug-in can simply fail there), or a plain C caller that owns no workspace and no allocator.
+// For them the candidate lists and counters live in a fixed array inside the library image.
+// The price: every device that loads the library carries the 4 MB until the process exits, the
+// row count is capped, and all calls share the one array.
+// ---------------------------------------------------------------------------------------------
+namespace b200dsa {
+
+constexpr int kStaticMaxRows = 64;
+constexpr size_t kStaticCandBytes = static_cast<size_t>(kStaticMaxRows) * kCandCap * sizeof(uint64_t);  // 4 MiB
+constexpr size_t kStaticIntBytes = 2 * kStaticMaxRows * sizeof(int32_t);
+
+// candidate lists first, then 2*rows int32 (per-row counters, per-row bin floors)
+static __device__ __align__(256) unsigned char g_topk_static_scratch[kStaticCandBytes + kStaticIntBytes];
+
+}  // namespace b200dsa
+
+#include <mutex>
+
+extern "C" int b200dsa_topk_select_split_static(const float* scores, int64_t row_stride, int32_t n_rows,
+                                                int32_t n_cols, const int32_t* col_begin, const int32_t* col_end,
+                                                int32_t k, int32_t keep_pos_inf, int32_t sorted,
+                                                const int32_t* row_pos_offset, int32_t splits, int32_t* out_idx,
+                                                float* out_val, int64_t out_stride, void* stream) {
+  if (n_rows == 0) return B200DSA_OK;
+  if (n_rows < 0 || n_rows > kStaticMaxRows) {
+    set_last_error("b200dsa_topk_select_split_static: n_rows exceeds the built-in scratch (at most 64 rows); "
+                   "use b200dsa_topk_select_split with caller-provided scratch for larger batches");
+    return B200DSA_EINVAL;
+  }
+  // The array's name is only a host-side handle; the device address has to be asked for, once
+  // per device, while that device is current.
+  constexpr int kMaxDevices = 64;
+  static void* dev_ptr[kMaxDevices] = {nullptr};
+  static std::mutex mu;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_last_error("b200dsa_topk_select_split_static: cannot identify the current device");
+    return B200DSA_ECUDA;
+  }
+  void* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!dev_ptr[dev]) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_topk_static_scratch);
+      if (e != cudaSuccess || !p) {
+        set_last_error("b200dsa_topk_select_split_static: cudaGetSymbolAddress failed for the built-in scratch");
+        return B200DSA_ECUDA;
+      }
+      dev_ptr[dev] = p;
+    }
+    base = dev_ptr[dev];
+  }
+  unsigned char* bytes = static_cast<unsigned char*>(base);
+  int32_t* counters = reinterpret_cast<int32_t*>(bytes + kStaticCandBytes);
+  // The array keeps whatever the previous call (possibly of another shape, possibly cut short)
+  // left behind; the per-row counters are the only part that must start at zero.
+  e = cudaMemsetAsync(counters, 0, kStaticIntBytes, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  return b200dsa_topk_select_split(scores, row_stride, n_rows, n_cols, col_begin, col_end, k, keep_pos_inf, sorted,
+                                   row_pos_offset, splits, bytes, counters, out_idx, out_val, out_stride, stream);
+}

@@ -103,6 +103,32 @@ def topk_select_split(scores: torch.Tensor, k: int, scratch: Tuple[torch.Tensor,
     return out[:n_rows, :k]
 
 
+STATIC_TOPK_MAX_ROWS = 64
+
+
+def topk_select_split_static(scores: torch.Tensor, k: int, *, col_begin: Optional[torch.Tensor] = None,
+                             col_end: Optional[torch.Tensor] = None, keep_pos_inf: bool = False,
+                             row_pos_offset: Optional[torch.Tensor] = None, sorted: bool = True, splits: int = 0,
+                             out: torch.Tensor = None, out_values: Optional[torch.Tensor] = None):
+    """topk_select_split on the library's built-in scratch (at most 64 rows): for callers that
+    have no device memory to lend.  `out` (int32 [n_rows, >=k]) must be supplied, so that this
+    wrapper, like the entry point under it, allocates nothing.  One call at a time per device."""
+    require_cuda(scores, col_begin, col_end, row_pos_offset, out, out_values)
+    if scores.dtype != torch.float32 or scores.dim() != 2 or scores.stride(1) != 1:
+        raise _lib.B200DSAError("scores must be a 2-D fp32 tensor with unit column stride")
+    if out is None or out.dtype != torch.int32 or out.stride(1) != 1 or out.shape[1] < k:
+        raise _lib.B200DSAError("out must be a preallocated int32 [n_rows, >=k] tensor")
+    n_rows, n_cols = scores.shape
+    if splits <= 0:
+        splits = max(1, min(16, (2 * 148) // max(1, n_rows)))
+    rc = _lib.load().b200dsa_topk_select_split_static(
+        ptr(scores), scores.stride(0), n_rows, n_cols, ptr(_i32(col_begin, "col_begin")),
+        ptr(_i32(col_end, "col_end")), k, int(keep_pos_inf), int(sorted), ptr(_i32(row_pos_offset, "row_pos_offset")),
+        splits, ptr(out), ptr(out_values), out.stride(0), stream_ptr())
+    check(rc, "b200dsa_topk_select_split_static")
+    return out[:n_rows, :k]
+
+
 def indexer_paged_fp8_logits(q_fp8: torch.Tensor, weights: torch.Tensor, cache: torch.Tensor, page_size: int,
                              context_lens: torch.Tensor, block_table: torch.Tensor, *, next_n: int = 1,
                              max_cols: Optional[int] = None, out_scale: float = 1.0,
