@@ -191,9 +191,6 @@ def main():
     n_sets = 4  # rotating query sets so consecutive steps differ
     dev_q = [make_decode_queries(B, HEADS, seed=100 + i, device=dev) for i in range(n_sets)]
     host_q = [make_decode_queries(B, HEADS, seed=100 + i, pinned=True) for i in range(n_sets)]
-    stage_q = [torch.empty_like(t, device=dev) for t in dev_q[0]]
-    host_idx = torch.empty(B, TOPK, dtype=torch.int32).pin_memory()
-    host_ctx = torch.empty(B, HEADS, 512, dtype=torch.float32).pin_memory()
 
     def run_eager(i):
         q_idx, w, q_lat = dev_q[i % n_sets]
@@ -214,18 +211,48 @@ def main():
             return run_eager(i)
         return graphed.replay(*dev_q[i % n_sets])
 
+    # End to end with HOST buffers, as a serving loop would run it: three streams and two slots, so the
+    # pinned-host -> device copy of step i+1 and the device -> host copy of step i-1 overlap the
+    # kernels of step i.  Every step's inputs cross PCIe and every step's result reaches the host.
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    slots = 2
+    in_dev = [[torch.empty_like(x, device=dev) for x in dev_q[0]] for _ in range(slots)]
+    out_dev = [(torch.empty(B, TOPK, dtype=torch.int32, device=dev),
+                torch.empty(B, HEADS, 512, dtype=torch.float32, device=dev)) for _ in range(slots)]
+    out_host = [(torch.empty(B, TOPK, dtype=torch.int32).pin_memory(),
+                 torch.empty(B, HEADS, 512, dtype=torch.float32).pin_memory()) for _ in range(slots)]
+    ev_in = [torch.cuda.Event() for _ in range(slots)]
+    ev_done = [torch.cuda.Event() for _ in range(slots)]
+    ev_out = [torch.cuda.Event() for _ in range(slots)]
+    ev_in_free = [torch.cuda.Event() for _ in range(slots)]
+    e2e_started = [False] * slots
+
     def run_e2e(i):
-        # the public call with HOST buffers: pinned inputs in, indices and context out
-        if graphed is None:
-            for dst, src in zip(stage_q, host_q[i % n_sets]):
+        sl = i % slots
+        main = torch.cuda.current_stream()
+        if e2e_started[sl]:
+            ev_out[sl].synchronize()                     # result of step i-2 is on the host
+            s_in.wait_event(ev_in_free[sl])
+        with torch.cuda.stream(s_in):
+            for dst, src in zip(in_dev[sl], host_q[i % n_sets]):
                 dst.copy_(src, non_blocking=True)
-            idx, c, _ = step.run(stage_q[0], stage_q[1], stage_q[2], state.k_cache, state.context_lens,
+            ev_in[sl].record(s_in)
+        main.wait_event(ev_in[sl])
+        if graphed is None:
+            idx, c, _ = step.run(in_dev[sl][0], in_dev[sl][1], in_dev[sl][2], state.k_cache, state.context_lens,
                                  state.block_table, state.kv, state.kv_row_base, state.context_lens_local)
         else:
-            idx, c, _ = graphed.replay(*host_q[i % n_sets])
-        host_idx.copy_(idx, non_blocking=True)
-        host_ctx.copy_(c, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+            idx, c, _ = graphed.replay(*in_dev[sl])
+        ev_in_free[sl].record(main)
+        out_dev[sl][0].copy_(idx, non_blocking=True)
+        out_dev[sl][1].copy_(c, non_blocking=True)
+        ev_done[sl].record(main)
+        s_out.wait_event(ev_done[sl])
+        with torch.cuda.stream(s_out):
+            out_host[sl][0].copy_(out_dev[sl][0], non_blocking=True)
+            out_host[sl][1].copy_(out_dev[sl][1], non_blocking=True)
+            ev_out[sl].record(s_out)
+        e2e_started[sl] = True
 
     def sync_all():
         if world > 1:
@@ -302,7 +329,7 @@ def main():
         idx_bytes = B * shard_len * (128 + 4)  # fp8 key + fp32 scale per key, read once
         achieved = idx_bytes / (stage_ms["indexer"] * 1e-3) / 1e9
         h2d = sum(t.numel() * t.element_size() for t in host_q[0])
-        d2h = host_idx.numel() * 4 + host_ctx.numel() * 4
+        d2h = out_host[0][0].numel() * 4 + out_host[0][1].numel() * 4
         launches = 5 if world == 1 else 8
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
