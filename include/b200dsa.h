@@ -207,6 +207,13 @@ int b200dsa_lse_prescale(const float* ctx, const float* lse, const float* lse_ma
 int b200dsa_lse_finalize(const float* wire, const float* lse_max, int64_t n_rows, float* ctx_out,
                          float* lse_out, void* stream);
 
+/* Compact form for bf16 results: lse_all [n_parts, n_rows] holds every rank's lse (all-gathered,
+ * 4 bytes per row and rank); the rank writes out = bf16(ctx * exp(lse_me - m) / sum_r exp(lse_r - m))
+ * and lse_out = m + log(sum); one SUM all-reduce of the bf16 [n_rows, 512] rows then gives the
+ * merged context on every rank (half the bytes of the fp32 wire, no finalize pass). */
+int b200dsa_lse_prescale_norm(const float* ctx, const float* lse_all, int32_t n_parts, int32_t my_part,
+                              int64_t n_rows, void* out_bf16, float* lse_out, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * FP8 quantisation of the index queries with the scale folded into the head weights:
  *   scale = max(amax|q[t,h,:]|, 1e-4)/448, q_fp8 = e4m3(q/scale), weights = w * scale * fold.

@@ -94,3 +94,14 @@ def lse_finalize(wire, lse_max, ctx_out, lse_out):
     ctx_out[den == 0] = 0
     lse_out.copy_(torch.where(den > 0, lse_max + torch.log(den), torch.full_like(den, NEG_INF)))
     return ctx_out, lse_out
+
+
+def lse_prescale_norm(ctx, lse_all, my_part, out_bf16, lse_out):
+    m = lse_all.max(0).values
+    ms = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
+    w = torch.where(torch.isfinite(lse_all), torch.exp(lse_all - ms), torch.zeros_like(lse_all))
+    den = w.sum(0)
+    share = torch.where(den > 0, w[my_part] / den.clamp_min(1e-38), torch.zeros_like(den))
+    out_bf16.copy_((ctx * share.unsqueeze(-1)).to(torch.bfloat16))
+    lse_out.copy_(torch.where(den > 0, ms + torch.log(den), torch.full_like(den, NEG_INF)))
+    return out_bf16, lse_out

@@ -104,3 +104,25 @@ def test_compact_owned():
         own = idx[r][(idx[r] >= 1000) & (idx[r] < 2500)]
         assert int(cnt[r]) == own.numel()
         assert torch.equal(out[r, :own.numel()].cpu(), own) and (out[r, own.numel():] == -1).all()
+
+
+def test_prescale_norm_equals_combine():
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(13)
+    R, n, H = 4, 3, 16
+    parts = torch.randn(R, n, H, 512, generator=g).cuda()
+    lses = torch.randn(R, n, H, generator=g).cuda() * 3
+    lses[2, 1] = float("-inf")                       # an empty partial
+    lses[:, 2, 5] = float("-inf")                    # a row empty on every rank
+    ref_ctx, ref_lse = K.lse_combine(parts, lses)
+    acc = torch.zeros(n, H, 512, device="cuda")
+    for r in range(R):
+        out = torch.empty(n, H, 512, dtype=torch.bfloat16, device="cuda")
+        lse_out = torch.empty(n, H, device="cuda")
+        K.lse_prescale_norm(parts[r].contiguous(), lses, r, out, lse_out)
+        acc += out.float()
+        assert torch.equal(torch.isfinite(lse_out), torch.isfinite(ref_lse))
+        fin = torch.isfinite(ref_lse)
+        assert (lse_out[fin] - ref_lse[fin]).abs().max() < 1e-5
+    assert (acc - ref_ctx).abs().max() < 2e-2 * ref_ctx.abs().max()
+    assert (acc[2, 5] == 0).all()

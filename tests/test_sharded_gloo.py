@@ -18,7 +18,7 @@ def _free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
 
 
-def _worker(rank, world, port, fail_rank, ret):
+def _worker(rank, world, port, wire, ret):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -31,22 +31,24 @@ def _worker(rank, world, port, fail_rank, ret):
         shard = ShardInfo(rank=rank, world_size=world, shard_len=SHARD)
         assert torch.equal(local_context_lens(st["lens"], shard), st["local"])
         step = SparseDecodeStep(len(CTXS), SHARD, topk=TOPK, n_heads=8, device=torch.device("cpu"), shard=shard,
-                                backend=cpu_backend, sorted_topk=True)
+                                backend=cpu_backend, sorted_topk=True, wire=wire)
         idx, ctx, lse = step.run(prob["q_idx"], prob["w"], prob["q_lat"], st["cache"], st["lens"], st["table"],
                                  st["kv"], st["base"])
         ref_idx, _, ref_ctx, ref_lse = oracle_decode(prob, TOPK, 128 ** -0.5, 192 ** -0.5)
-        ok = torch.equal(idx, ref_idx) and torch.allclose(ctx, ref_ctx, rtol=1e-4, atol=1e-5) and \
+        tol = dict(rtol=1e-4, atol=1e-5) if wire == "fp32" else dict(rtol=2e-2, atol=2e-3)   # bf16 wire
+        ok = torch.equal(idx, ref_idx) and torch.allclose(ctx.float(), ref_ctx, **tol) and \
             torch.allclose(lse, ref_lse, rtol=1e-4, atol=1e-5)
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
 
 
-def test_two_rank_sharded_step_matches_unsharded():
+@pytest.mark.parametrize("wire", ["fp32", "bf16"])
+def test_two_rank_sharded_step_matches_unsharded(wire):
     port = _free_port()
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(2, port, -1, ret), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, wire, ret), nprocs=2, join=True)
     assert ret.get(0) is True and ret.get(1) is True
 
 

@@ -3,6 +3,8 @@
 //   m = max_r lse_r;  w_r = exp(lse_r - m);  out = sum_r w_r * ctx_r / sum_r w_r;
 //   lse_out = m + log(sum_r w_r).  Rows whose every partial is empty (lse = -inf) give 0 / -inf.
 // One CTA of 128 threads per (item, head) row; each thread owns 4 of the 512 value dims.
+#include <cuda_bf16.h>
+
 #include "b200dsa_common.cuh"
 
 namespace b200dsa {
@@ -108,6 +110,40 @@ __global__ void __launch_bounds__(256) compact_owned_kernel(const int32_t* __res
   if (tid == 0) count[row] = total;
 }
 
+// Compact wire form: with every rank's lse gathered first (tiny), a rank knows the common
+// maximum and the exact denominator, so it contributes its normalised share
+//   out = bf16( ctx * exp(lse_me - m) / sum_r exp(lse_r - m) )
+// and a single SUM all-reduce of the bf16 rows yields the merged context directly.
+__global__ void __launch_bounds__(128) lse_prescale_norm_kernel(const float* __restrict__ ctx,
+                                                                const float* __restrict__ lse_all, int n_parts,
+                                                                int my_part, int64_t n_rows,
+                                                                __nv_bfloat16* __restrict__ out,
+                                                                float* __restrict__ lse_out) {
+  const int64_t row = blockIdx.x;
+  const int tid = threadIdx.x;
+  float m = -INFINITY;
+  for (int r = 0; r < n_parts; ++r) m = fmaxf(m, __ldg(lse_all + r * n_rows + row));
+  float den = 0.f, mine = 0.f;
+  if (m != -INFINITY) {
+    for (int r = 0; r < n_parts; ++r) {
+      const float l = __ldg(lse_all + r * n_rows + row);
+      const float w = (l == -INFINITY) ? 0.f : expf(l - m);
+      den += w;
+      if (r == my_part) mine = w;
+    }
+  }
+  const float w = den > 0.f ? mine / den : 0.f;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (w != 0.f) v = __ldg(reinterpret_cast<const float4*>(ctx + row * kCombineDv) + tid);
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x * w, v.y * w);
+  __nv_bfloat162 b = __floats2bfloat162_rn(v.z * w, v.w * w);
+  uint2 packed;
+  packed.x = *reinterpret_cast<uint32_t*>(&a);
+  packed.y = *reinterpret_cast<uint32_t*>(&b);
+  reinterpret_cast<uint2*>(out + row * kCombineDv)[tid] = packed;
+  if (tid == 0 && lse_out) lse_out[row] = den > 0.f ? m + logf(den) : -INFINITY;
+}
+
 void set_last_error(const char* msg);
 
 }  // namespace b200dsa
@@ -182,6 +218,25 @@ extern "C" int b200dsa_compact_owned(const int32_t* indices, int64_t idx_stride,
   }
   compact_owned_kernel<<<n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(indices, idx_stride, n_idx, pos_lo,
                                                                              pos_hi, out, out_stride, count);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  return B200DSA_OK;
+}
+
+extern "C" int b200dsa_lse_prescale_norm(const float* ctx, const float* lse_all, int32_t n_parts, int32_t my_part,
+                                         int64_t n_rows, void* out_bf16, float* lse_out, void* stream) {
+  if (n_rows == 0) return B200DSA_OK;
+  if (!ctx || !lse_all || !out_bf16 || n_parts < 1 || n_parts > kCombineMaxParts || my_part < 0 ||
+      my_part >= n_parts || n_rows < 0 || (reinterpret_cast<uintptr_t>(ctx) & 15) ||
+      (reinterpret_cast<uintptr_t>(out_bf16) & 7)) {
+    set_last_error("b200dsa_lse_prescale_norm: bad argument (1 <= n_parts <= 64, 0 <= my_part < n_parts, aligned buffers)");
+    return B200DSA_EINVAL;
+  }
+  lse_prescale_norm_kernel<<<static_cast<unsigned>(n_rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      ctx, lse_all, n_parts, my_part, n_rows, static_cast<__nv_bfloat16*>(out_bf16), lse_out);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));

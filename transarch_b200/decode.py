@@ -9,7 +9,9 @@ its own range, the per-rank candidate lists (global position, score) are all-gat
 every rank selects the same global top-k from the N*k candidates (the union of the shard
 top-k contains the global top-k; ties resolve towards the lowest global position on every
 rank alike), attends the selected keys it owns, and the partial (context, lse) pairs are
-merged: MAX all-reduce of lse, pre-scale, SUM all-reduce of the 516-wide wire rows, divide.
+merged: all-gather of lse (4 B per row), normalised bf16 shares, one SUM all-reduce of the bf16
+rows (or, with wire="fp32": MAX all-reduce of lse, pre-scale, SUM all-reduce of 516-wide fp32
+rows, divide).
 The query-side inputs are replicated.  The reference has no such path; the idea of local
 queries against position-indexed keys follows OpenDSA's context-parallel forward
 (OpenDSA/opendsa/modeling/dsa_attention.py:620-684).
@@ -64,7 +66,7 @@ class SparseDecodeStep:
     def __init__(self, batch: int, max_local_ctx: int, *, page_size: int = 64, topk: int = 2048,
                  n_heads: int = 128, index_scale: float = 128 ** -0.5, attn_scale: float = 192 ** -0.5,
                  device: Optional[torch.device] = None, shard: Optional[ShardInfo] = None, backend=None,
-                 sorted_topk: bool = False):
+                 sorted_topk: bool = False, wire: str = "bf16"):
         if backend is None:
             from . import kernels as backend  # the CUDA kernels; fails loudly without the library
         self.K = backend
@@ -72,6 +74,7 @@ class SparseDecodeStep:
         self.index_scale, self.attn_scale = index_scale, attn_scale
         self.shard = shard or ShardInfo()
         self.sorted_topk = sorted_topk
+        self.wire = wire if hasattr(backend, "lse_prescale_norm") else "fp32"
         dev = device if device is not None else torch.device("cuda")
         self.dev = dev
         f32, i32 = torch.float32, torch.int32
@@ -99,6 +102,8 @@ class SparseDecodeStep:
             self.wire = torch.empty(batch * n_heads, backend.WIRE_ROW, dtype=f32, device=dev)
             self.ctx_out = torch.empty(batch, n_heads, 512, dtype=f32, device=dev)
             self.lse_out = torch.empty(batch, n_heads, dtype=f32, device=dev)
+            self.lse_all = torch.empty(n, batch, n_heads, dtype=f32, device=dev)
+            self.ctx_bf16 = torch.empty(batch, n_heads, 512, dtype=torch.bfloat16, device=dev)
 
     # ------------------------------------------------------------------ stages
     def select(self, q_idx, w, k_cache, context_lens_local, block_table) -> torch.Tensor:
@@ -144,6 +149,14 @@ class SparseDecodeStep:
     def combine(self) -> Tuple[torch.Tensor, torch.Tensor]:
         """Merge the per-rank (ctx, lse) partials; every rank ends with the full result."""
         K, g = self.K, self.shard.group
+        if self.wire == "bf16":
+            # gather the lse of every rank (4 B per row and rank): each rank then knows the common
+            # maximum and the exact denominator and sends its normalised bf16 share; the summed
+            # rows are the result
+            dist.all_gather_into_tensor(self.lse_all.view(-1), self.lse.view(-1), group=g)
+            K.lse_prescale_norm(self.ctx, self.lse_all, self.shard.rank, self.ctx_bf16, self.lse_out)
+            dist.all_reduce(self.ctx_bf16, op=dist.ReduceOp.SUM, group=g)
+            return self.ctx_bf16, self.lse_out
         self.lse_max.copy_(self.lse)
         dist.all_reduce(self.lse_max, op=dist.ReduceOp.MAX, group=g)
         K.lse_prescale(self.ctx, self.lse, self.lse_max, self.wire)

@@ -394,3 +394,17 @@ def compact_owned(indices: torch.Tensor, pos_lo: int, pos_hi: int, out: torch.Te
                                             out.stride(0), ptr(_i32(count, "count")), stream_ptr()),
           "b200dsa_compact_owned")
     return out, count
+
+
+def lse_prescale_norm(ctx: torch.Tensor, lse_all: torch.Tensor, my_part: int, out_bf16: torch.Tensor,
+                      lse_out: torch.Tensor):
+    """This rank's normalised bf16 share of the merged context; see b200dsa_lse_prescale_norm."""
+    require_cuda(ctx, lse_all, out_bf16, lse_out)
+    n_parts = lse_all.shape[0]
+    n_rows = lse_all[0].numel()
+    if ctx.dtype != torch.float32 or lse_all.dtype != torch.float32 or out_bf16.dtype != torch.bfloat16 or \
+            not (ctx.is_contiguous() and lse_all.is_contiguous() and out_bf16.is_contiguous()):
+        raise _lib.B200DSAError("ctx / lse_all must be contiguous fp32 and out_bf16 contiguous bf16")
+    check(_lib.load().b200dsa_lse_prescale_norm(ptr(ctx), ptr(lse_all), n_parts, my_part, n_rows, ptr(out_bf16),
+                                                ptr(lse_out), stream_ptr()), "b200dsa_lse_prescale_norm")
+    return out_bf16, lse_out
