@@ -303,16 +303,22 @@ def main():
                             out=step.cand[:, :TOPK], out_values=step.cand[:, TOPK:].view(torch.float32),
                             row_pos_offset=step.pos_offset if world > 1 else None)
         ev[2].record()
+        sub = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
         idx = step.merge_candidates() if world > 1 else step.cand[:, :TOPK]
+        sub[0].record()
         torch.sub(state.context_lens, 1, out=step.q_pos)
         step.attend(q_lat, state.kv, state.kv_row_base, idx, step.q_pos)
+        sub[1].record()
         if world > 1:
             step.combine()
+        sub[2].record()
         ev[3].record()
         torch.cuda.synchronize()
         stage_ms["quant+indexer"] += ev[0].elapsed_time(ev[1])
         stage_ms["topk"] += ev[1].elapsed_time(ev[2])
         stage_ms["attention+merge"] += ev[2].elapsed_time(ev[3])
+        for nm, a, b_ in (("gather+merge", ev[2], sub[0]), ("attention", sub[0], sub[1]), ("combine", sub[1], sub[2])):
+            stage_ms[nm] = stage_ms.get(nm, 0.0) + a.elapsed_time(b_)
         stage_ms.setdefault("indexer", 0.0)
         stage_ms["indexer"] += ev_i0.elapsed_time(ev[1])
     for k_ in stage_ms:
