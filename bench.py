@@ -143,7 +143,7 @@ def run_reference(args, rank: int):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
-                         "sample": f"{n_req} of 64 requests per step at context {CONTEXT}, all stages"},
+                         "sample": f"{n_req} requests of the batch's shape per step at context {CONTEXT}, all stages"},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
