@@ -38,14 +38,17 @@ constexpr int kMlaStages = 4;
 constexpr int kMlaStageBytes = kMlaTile * kMlaD * 2;
 constexpr int kMlaChunkBytesK = kMlaTile * 128;
 constexpr int kMlaPBytes = kMlaHeadsTile * kMlaTile * 2;
-constexpr int kMlaSmemBytes = kMlaQBytes + kMlaStages * kMlaStageBytes + kMlaPBytes + 1024 + 256;
+constexpr int kMlaSmemBytes = kMlaStages * kMlaStageBytes + kMlaPBytes + 1024 + 256;
 constexpr int kMlaTpr = 128 / kMlaTile;                          // gather threads per key row
 static_assert(kMlaTile == 32 || kMlaTile == 64, "tile must be 32 or 64 keys");
 constexpr uint32_t kMlaTmemCols = 512;
 constexpr uint32_t kMlaTmemO = 0;                 // lanes 0-15 of every sub-partition, columns 0..511
 constexpr uint32_t kMlaTmemS = (16u << 16);       // lanes 16-31 of every sub-partition, columns 0..127
+constexpr uint32_t kMlaTmemQ = (16u << 16) + 128; // Q as the A operand: upper half-lanes, columns 128..415
+                                                  // (64 rows x 576 bf16, two per 32-bit cell)
 
 struct MlaParams {
+  const __nv_bfloat16* q;      // [n_items, n_heads, 576]
   const __nv_bfloat16* kv;     // [kv_rows, 576]
   int64_t kv_rows;
   const int64_t* kv_row_base;  // nullable [n_items]: row of position 0 of the item's sequence
@@ -85,6 +88,23 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand is read from tensor memory (same lanes as D).
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {   // 2^x, ex2.approx: 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // K-major operand without swizzle: core matrices of 8 rows x 16 bytes stored contiguously
 // (128 bytes); lbo = byte step between core matrices along K, sbo = along M/N.
 __device__ __forceinline__ uint64_t make_desc_k_noswz(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
@@ -120,10 +140,9 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
 
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_dyn + (smem_base - smem_u32(smem_dyn));
-  const uint32_t q_addr = smem_base;
-  const uint32_t kv_addr = smem_base + kMlaQBytes;
+  const uint32_t kv_addr = smem_base;
   const uint32_t p_addr = kv_addr + kMlaStages * kMlaStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + kMlaQBytes + kMlaStages * kMlaStageBytes + kMlaPBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + kMlaStages * kMlaStageBytes + kMlaPBytes);
   uint64_t* q_full = bars;                       // [1]
   uint64_t* s_full = bars + 1;                   // [2] score MMA retired
   uint64_t* s_empty = bars + 3;                  // [2] 128 softmax-warp threads have read the scores
@@ -141,7 +160,7 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
 
   if (tid == 0) {
     s_abort = 0;
-    mbar_init(q_full, 1);
+    mbar_init(q_full, 128);   // the softmax threads, once Q sits in TMEM
     for (int s = 0; s < kMlaStages; ++s) {
       mbar_init(&kv_full[s], 128);
       mbar_init(&kv_empty[s], 1);
@@ -168,37 +187,47 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
 
   if (warp < 4) {
     // ------------------------------------------------------------------ gather producers
-    const int r = tid / kMlaTpr;   // key row of the tile
-    const int sub = tid % kMlaTpr;
+    // Warp w gathers rows 8w..8w+7 of every 32-key tile.  A row (1152 B) is copied by the whole
+    // warp in three instructions (32 + 32 + 8 lanes x 16 B), so that one instruction touches at
+    // most four consecutive 128-byte lines; lanes 0..7 hold the row indices, fetched one tile ahead.
     const int32_t* idx_row = p.indices + static_cast<int64_t>(item) * p.idx_stride;
+    const int r0 = warp * 8;
+    auto load_idx = [&](int t) {
+      const int j = t * kMlaTile + r0 + lane;
+      return (lane < 8 && j < n_idx) ? __ldg(idx_row + j) : -1;
+    };
+    int idx_next = load_idx(0);
     for (int t = 0; t < n_tiles; ++t) {
       const int s = t % kMlaStages;
-      const bool ok = mbar_wait(&kv_empty[s], ((t / kMlaStages) & 1) ^ 1, abort_flag);
-      if (!__all_sync(0xffffffffu, ok)) break;
-      const int j = t * kMlaTile + r;
-      const int idx = (j < n_idx) ? __ldg(idx_row + j) : -1;
+      const int idx = idx_next;
+      if (t + 1 < n_tiles) idx_next = load_idx(t + 1);
       bool valid = idx >= 0 && idx <= qpos && idx >= p.pos_lo && idx < p.pos_hi;
       const int64_t grow = row_base + idx;
       if (valid && (grow < 0 || grow >= p.kv_rows)) {
         valid = false;
         atomicMax(p.status, kDevBadIndex);
       }
-      const uint8_t* src = reinterpret_cast<const uint8_t*>(p.kv) + (valid ? grow : 0) * (kMlaD * 2);
-      const uint32_t dst_row = kv_addr + s * kMlaStageBytes + r * 128;
+      const bool ok = mbar_wait(&kv_empty[s], ((t / kMlaStages) & 1) ^ 1, abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      const unsigned vmask = __ballot_sync(0xffffffffu, valid) & 0xffu;
+      const uint32_t stage_addr = kv_addr + s * kMlaStageBytes;
 #pragma unroll
-      for (int u = 0; u < 72 / kMlaTpr; ++u) {
-        const int c16 = sub + kMlaTpr * u;     // 16-byte chunk of the 1152-byte row
-        const int c = c16 >> 3, w = c16 & 7;   // 128-byte chunk, position inside it
-        cp_async_16(dst_row + c * kMlaChunkBytesK + ((w ^ (r & 7)) << 4), src + c16 * 16, valid);
-      }
-      const unsigned b = __ballot_sync(0xffffffffu, valid && sub == 0);
-      if (lane == 0) {
-        uint32_t mw = 0;  // one bit per row this warp gathers
+      for (int rr = 0; rr < 8; ++rr) {
+        const int64_t g = __shfl_sync(0xffffffffu, grow, rr);
+        const bool v = (vmask >> rr) & 1u;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.kv) + (v ? g : 0) * (kMlaD * 2);
+        const int r = r0 + rr;
+        const uint32_t dst_row = stage_addr + r * 128;
 #pragma unroll
-        for (int rr = 0; rr < 32 / kMlaTpr; ++rr) mw |= ((b >> (kMlaTpr * rr)) & 1u) << rr;
-        if constexpr (kMlaTpr == 2) reinterpret_cast<volatile uint16_t*>(&s_mask[s][0])[warp] = static_cast<uint16_t>(mw);
-        else reinterpret_cast<volatile uint8_t*>(&s_mask[s][0])[warp] = static_cast<uint8_t>(mw);
+        for (int u = 0; u < 3; ++u) {
+          const int c16 = lane + 32 * u;          // 16-byte chunk of the 1152-byte row
+          if (c16 < 72) {
+            const int c = c16 >> 3, w8 = c16 & 7;  // 128-byte chunk, position inside it
+            cp_async_16(dst_row + c * kMlaChunkBytesK + ((w8 ^ (r & 7)) << 4), src + c16 * 16, v);
+          }
+        }
       }
+      if (lane == 0) reinterpret_cast<volatile uint8_t*>(&s_mask[s][0])[warp] = static_cast<uint8_t>(vmask);
       __threadfence_block();
       __syncwarp();
       // the barrier receives this thread's arrival once all its copies above have landed
@@ -214,33 +243,53 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
     const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;  // sub-partition base lane
     float m_ref = -INFINITY, l = 0.f;
     bool aborted = false;
+    {
+      // Q -> TMEM once: lane 16+i of this warp stores head row 16*wq+i into the upper half-lanes
+      // (two bf16 per 32-bit cell, 288 cells per row).  The lower half-lanes of these columns
+      // belong to O, which nothing has written yet.
+      const int qhead = hh * kMlaHeadsTile + row;
+      const bool have = is_s && qhead < p.n_heads;
+      const uint4* qrow = reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(item) * p.n_heads + (have ? qhead : 0)) * kMlaD);
+#pragma unroll 1
+      for (int c = 0; c < kMlaD / 64; ++c) {
+        uint32_t qv[32];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint4 x = make_uint4(0u, 0u, 0u, 0u);
+          if (have) x = __ldg(qrow + c * 8 + j);
+          qv[4 * j] = x.x; qv[4 * j + 1] = x.y; qv[4 * j + 2] = x.z; qv[4 * j + 3] = x.w;
+        }
+        tmem_st_32x32(tmem_base + lane_addr + 128 + c * 32, qv);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(q_full);
+    }
     for (int t = 0; t < n_tiles; ++t) {
       const int sb = t & 1;
       bool ok = mbar_wait(&s_full[sb], (t >> 1) & 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) { aborted = true; break; }
       tc_fence_after();
       const int ks = t % kMlaStages;
-      uint32_t v0[32], v1[32];
+      uint32_t v0[32];
       tmem_ld_32x32(tmem_base + lane_addr + sb * kMlaTile, v0);       // lanes 16-31 receive the score rows
-      if constexpr (kMlaTile == 64) {
-        tmem_ld_32x32(tmem_base + lane_addr + sb * kMlaTile + 32, v1);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v1[j] = 0;
-      }
       tc_wait_ld();
       tc_fence_before();
       mbar_arrive(&s_empty[sb]);
-      const uint32_t mask0 = s_mask[ks][0], mask1 = (kMlaTile == 64) ? s_mask[ks][1] : 0u;
-      float mt = -INFINITY;
+      const uint32_t mask0 = s_mask[ks][0];
+      float mt = -INFINITY;   // tile maximum of the raw scores, scaled once below (the scale is positive)
+      if (mask0 == 0xffffffffu) {   // common case: every key of the tile is valid
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float a = ((mask0 >> j) & 1u) ? __uint_as_float(v0[j]) * p.scale_log2 : -INFINITY;
-        const float b2 = ((mask1 >> j) & 1u) ? __uint_as_float(v1[j]) * p.scale_log2 : -INFINITY;
-        v0[j] = __float_as_uint(a);
-        v1[j] = __float_as_uint(b2);
-        mt = fmaxf(mt, fmaxf(a, b2));
+        for (int j = 0; j < 32; ++j) mt = fmaxf(mt, __uint_as_float(v0[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float a = ((mask0 >> j) & 1u) ? __uint_as_float(v0[j]) : -INFINITY;
+          v0[j] = __float_as_uint(a);
+          mt = fmaxf(mt, a);
+        }
       }
+      mt *= p.scale_log2;
       if (!is_s) mt = -INFINITY;
       bool waited_pv = false;
       // lazy rescale: only when the running maximum grows by more than 2^8
@@ -275,21 +324,17 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
         tc_fence_before();
       }
       if (grow) m_ref = mt;
-      uint32_t pk[32];
+      uint32_t pk[16];
       float lsum = 0.f;
+      // p = 2^(s*scale - m_ref) as one FMA and one ex2; masked scores are -inf and give exactly 0
+      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
 #pragma unroll
       for (int j = 0; j < 32; j += 2) {
-        const float a0 = __uint_as_float(v0[j]), a1 = __uint_as_float(v0[j + 1]);
-        const float b0 = __uint_as_float(v1[j]), b1 = __uint_as_float(v1[j + 1]);
-        const float p0 = (a0 == -INFINITY) ? 0.f : exp2f(a0 - m_ref);
-        const float p1 = (a1 == -INFINITY) ? 0.f : exp2f(a1 - m_ref);
-        const float p2 = (b0 == -INFINITY) ? 0.f : exp2f(b0 - m_ref);
-        const float p3 = (b1 == -INFINITY) ? 0.f : exp2f(b1 - m_ref);
-        lsum += (p0 + p1) + (p2 + p3);
+        const float p0 = fast_exp2(fmaf(__uint_as_float(v0[j]), p.scale_log2, neg_m));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(v0[j + 1]), p.scale_log2, neg_m));
+        lsum += p0 + p1;
         __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1);
-        __nv_bfloat162 h23 = __floats2bfloat162_rn(p2, p3);
         pk[j >> 1] = *reinterpret_cast<uint32_t*>(&h01);
-        pk[16 + (j >> 1)] = *reinterpret_cast<uint32_t*>(&h23);
       }
       if (is_s) l += lsum;
       if (t > 0 && !waited_pv) {
@@ -349,13 +394,6 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
     // ------------------------------------------------------------------ MMA issuer (warp 8)
     constexpr uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, kMlaHeadsTile, kMlaTile);
     constexpr uint32_t idesc_pv = make_idesc(kFmtBF16, kFmtBF16, kMlaHeadsTile, 256, 0, 1);
-    if (elect_one()) {
-      tma_prefetch_desc(&tmap_q);
-      mbar_arrive_expect_tx(q_full, kMlaQBytes);
-      for (int c = 0; c < kMlaChunks; ++c)
-        tma_load_2d(smem_al + c * kMlaChunkBytesQ, &tmap_q, q_full, c * 64, item * p.n_heads + hh * kMlaHeadsTile);
-    }
-    __syncwarp();
     bool ok = mbar_wait(q_full, 0, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
     auto issue_scores = [&](int t) -> bool {
@@ -368,13 +406,12 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
       if (elect_one()) {
         const uint32_t d = tmem_base + kMlaTmemS + sb * kMlaTile;
         // descriptors differ only in the 16-byte-granular start address: one add per operand
-        const uint64_t a0 = make_desc_k_sw128(q_addr);
         const uint64_t b0 = make_desc_k_sw128(kv_addr + s * kMlaStageBytes);
 #pragma unroll
         for (int c = 0; c < kMlaChunks; ++c) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            mma_f16_ss(d, a0 + ((c * kMlaChunkBytesQ + kk * 32) >> 4), b0 + ((c * kMlaChunkBytesK + kk * 32) >> 4),
+            mma_f16_ts(d, tmem_base + kMlaTmemQ + c * 32 + kk * 8, b0 + ((c * kMlaChunkBytesK + kk * 32) >> 4),
                        idesc_s, (c | kk) != 0);
           }
         }
@@ -465,6 +502,7 @@ extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16
     return B200DSA_ECUDA;
   }
   MlaParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q_bf16);
   p.kv = static_cast<const __nv_bfloat16*>(kv_bf16);
   p.kv_rows = kv_rows;
   p.kv_row_base = kv_row_base;
