@@ -33,8 +33,8 @@ constexpr int kMlaThreads = 288;
 constexpr int kMlaQBytes = kMlaHeadsTile * kMlaD * 2;            // 73728
 constexpr int kMlaChunkBytesQ = kMlaHeadsTile * 128;             // 8192 per 64-wide chunk
 // keys per tile and gather pipeline depth: smaller tiles allow more row gathers in flight
-constexpr int kMlaTile = 32;
-constexpr int kMlaStages = 4;
+constexpr int kMlaTile = 64;
+constexpr int kMlaStages = 3;
 constexpr int kMlaStageBytes = kMlaTile * kMlaD * 2;
 constexpr int kMlaChunkBytesK = kMlaTile * 128;
 constexpr int kMlaPBytes = kMlaHeadsTile * kMlaTile * 2;
@@ -191,10 +191,11 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
     // warp in three instructions (32 + 32 + 8 lanes x 16 B), so that one instruction touches at
     // most four consecutive 128-byte lines; lanes 0..7 hold the row indices, fetched one tile ahead.
     const int32_t* idx_row = p.indices + static_cast<int64_t>(item) * p.idx_stride;
-    const int r0 = warp * 8;
+    constexpr int kRowsPerWarp = kMlaTile / 4;   // 8 or 16
+    const int r0 = warp * kRowsPerWarp;
     auto load_idx = [&](int t) {
       const int j = t * kMlaTile + r0 + lane;
-      return (lane < 8 && j < n_idx) ? __ldg(idx_row + j) : -1;
+      return (lane < kRowsPerWarp && j < n_idx) ? __ldg(idx_row + j) : -1;
     };
     int idx_next = load_idx(0);
     for (int t = 0; t < n_tiles; ++t) {
@@ -209,10 +210,10 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
       }
       const bool ok = mbar_wait(&kv_empty[s], ((t / kMlaStages) & 1) ^ 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) break;
-      const unsigned vmask = __ballot_sync(0xffffffffu, valid) & 0xffu;
+      const unsigned vmask = __ballot_sync(0xffffffffu, valid) & ((1u << kRowsPerWarp) - 1u);
       const uint32_t stage_addr = kv_addr + s * kMlaStageBytes;
 #pragma unroll
-      for (int rr = 0; rr < 8; ++rr) {
+      for (int rr = 0; rr < kRowsPerWarp; ++rr) {
         const int64_t g = __shfl_sync(0xffffffffu, grow, rr);
         const bool v = (vmask >> rr) & 1u;
         const uint8_t* src = reinterpret_cast<const uint8_t*>(p.kv) + (v ? g : 0) * (kMlaD * 2);
@@ -227,7 +228,10 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
           }
         }
       }
-      if (lane == 0) reinterpret_cast<volatile uint8_t*>(&s_mask[s][0])[warp] = static_cast<uint8_t>(vmask);
+      if (lane == 0) {
+        if constexpr (kRowsPerWarp == 8) reinterpret_cast<volatile uint8_t*>(&s_mask[s][0])[warp] = static_cast<uint8_t>(vmask);
+        else reinterpret_cast<volatile uint16_t*>(&s_mask[s][0])[warp] = static_cast<uint16_t>(vmask);
+      }
       __threadfence_block();
       __syncwarp();
       // the barrier receives this thread's arrival once all its copies above have landed
@@ -271,22 +275,28 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
       if (!__all_sync(0xffffffffu, ok)) { aborted = true; break; }
       tc_fence_after();
       const int ks = t % kMlaStages;
-      uint32_t v0[32];
-      tmem_ld_32x32(tmem_base + lane_addr + sb * kMlaTile, v0);       // lanes 16-31 receive the score rows
+      constexpr int kNV = kMlaTile / 32;   // 32-column groups per tile
+      uint32_t v[kNV][32];
+#pragma unroll
+      for (int h = 0; h < kNV; ++h)
+        tmem_ld_32x32(tmem_base + lane_addr + sb * kMlaTile + 32 * h, v[h]);   // lanes 16-31: score rows
       tc_wait_ld();
       tc_fence_before();
       mbar_arrive(&s_empty[sb]);
-      const uint32_t mask0 = s_mask[ks][0];
       float mt = -INFINITY;   // tile maximum of the raw scores, scaled once below (the scale is positive)
-      if (mask0 == 0xffffffffu) {   // common case: every key of the tile is valid
 #pragma unroll
-        for (int j = 0; j < 32; ++j) mt = fmaxf(mt, __uint_as_float(v0[j]));
-      } else {
+      for (int h = 0; h < kNV; ++h) {
+        const uint32_t mk = s_mask[ks][h];
+        if (mk == 0xffffffffu) {   // common case: all 32 keys of the group are valid
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float a = ((mask0 >> j) & 1u) ? __uint_as_float(v0[j]) : -INFINITY;
-          v0[j] = __float_as_uint(a);
-          mt = fmaxf(mt, a);
+          for (int j = 0; j < 32; ++j) mt = fmaxf(mt, __uint_as_float(v[h][j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float a = ((mk >> j) & 1u) ? __uint_as_float(v[h][j]) : -INFINITY;
+            v[h][j] = __float_as_uint(a);
+            mt = fmaxf(mt, a);
+          }
         }
       }
       mt *= p.scale_log2;
@@ -324,17 +334,20 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
         tc_fence_before();
       }
       if (grow) m_ref = mt;
-      uint32_t pk[16];
+      uint32_t pk[kMlaTile / 2];
       float lsum = 0.f;
       // p = 2^(s*scale - m_ref) as one FMA and one ex2; masked scores are -inf and give exactly 0
       const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(v0[j]), p.scale_log2, neg_m));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(v0[j + 1]), p.scale_log2, neg_m));
-        lsum += p0 + p1;
-        __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1);
-        pk[j >> 1] = *reinterpret_cast<uint32_t*>(&h01);
+      for (int h = 0; h < kNV; ++h) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(v[h][j]), p.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(v[h][j + 1]), p.scale_log2, neg_m));
+          lsum += p0 + p1;
+          __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1);
+          pk[16 * h + (j >> 1)] = *reinterpret_cast<uint32_t*>(&h01);
+        }
       }
       if (is_s) l += lsum;
       if (t > 0 && !waited_pv) {
