@@ -31,9 +31,10 @@ TOPK = 2048
 PAGE = 64
 INDEX_SCALE = 128 ** -0.5
 ATTN_SCALE = 192 ** -0.5
-# DRAM bytes (read + write) per scored key of the indexer kernel, from the ncu capture summarised
-# in profiles/indexer_paged_fp8_ncu.md (traffic grows in proportion to the number of keys).
-DRAM_BYTES_PER_KEY = 138.3
+# DRAM bytes (read + write) per scored key of the indexer kernel, from an ncu capture of that kernel
+# on a smaller case (dram__bytes_read + dram__bytes_write over the keys scored; traffic grows in
+# proportion to the number of keys).
+DRAM_BYTES_PER_KEY = 137.8
 METRIC = "sparse_mla_decode_tokens_per_s"
 WORKLOAD = ("sparse MLA decode, key-sharded: batch 64, context 131072, 64 index heads d=128, FP8 paged "
             "index keys (page 64) with per-token scale, top-2048, 128 heads over 576-wide bf16 latent KV")

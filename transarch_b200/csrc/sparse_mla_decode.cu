@@ -6,18 +6,21 @@
 //   lse[h]   = log sum_j exp(s[h, j])
 //
 // Work split: CTA (item, hh) computes heads [64*hh, 64*hh+64) of one item over all selected
-// keys.  Heads are the UMMA M dimension (M = 64: an accumulator row m lives in TMEM lane
+// keys.  Heads are the UMMA M dimension (M = 64: accumulator row m lives in TMEM lane
 // 32*(m/16) + m%16, i.e. the lower half of each 32-lane sub-partition), 64 gathered keys are
-// N of the score MMA and K of the value MMA.  The O accumulator (64 x 512) fills all 512
-// columns on the lower half-lanes; the two score buffers sit on the upper half-lanes
-// (lane offset 16) of columns 0..127, so both fit at once.  The 576-wide rows are gathered
-// with 16-byte cp.async into the 128-byte-swizzled K-major layout the score MMA reads; the
-// same bytes serve, read MN-major, as the value operand.  Q (64 x 576 bf16) stays in shared
-// memory.  Softmax: lane 16+i of warp 4+w owns head row 16w+i (row max / sum are
-// thread-local); lane i of the same warp owns that row of O.
+// N of the score MMA and K of the value MMA.  TMEM plan (512 columns):
+//   lower half-lanes, columns 0..511 : O accumulator (64 x 512 fp32)
+//   upper half-lanes, columns 0..127 : two score buffers (64 x 64 fp32 each)
+//   upper half-lanes, columns 128..415: Q (64 x 576 bf16, two per cell), the A operand of the
+//                                        score MMA, stored once by the softmax threads
+// The 576-wide rows are gathered with 16-byte cp.async into the 128-byte-swizzled K-major layout
+// the score MMA reads; the same bytes serve, read MN-major, as the value operand.  Softmax:
+// lane 16+i of warp 4+w owns head row 16w+i (row max / sum are thread-local); lane i of the
+// same warp owns that row of O.
 //
-// Roles (288 threads): warps 0-3 gather, warps 4-7 softmax, warp 8 issues MMAs.  All waits
-// are bounded.
+// Roles (320 threads): warps 0-3 gather (warp w owns 16 rows of every tile, one row per three
+// instructions), warps 4-7 softmax, warp 8 issues the score MMAs, warp 9 the value MMAs.
+// All waits are bounded.
 #include <cuda_bf16.h>
 
 #include "b200dsa_common.cuh"
@@ -29,9 +32,7 @@ constexpr int kMlaMaxHeads = 128;
 constexpr int kMlaD = 576;          // latent width (512 value dims + 64 rope dims)
 constexpr int kMlaDv = 512;
 constexpr int kMlaChunks = 9;       // 576 / 64 elements (128-byte chunks)
-constexpr int kMlaThreads = 288;
-constexpr int kMlaQBytes = kMlaHeadsTile * kMlaD * 2;            // 73728
-constexpr int kMlaChunkBytesQ = kMlaHeadsTile * 128;             // 8192 per 64-wide chunk
+constexpr int kMlaThreads = 320;
 // keys per tile and gather pipeline depth: smaller tiles allow more row gathers in flight
 constexpr int kMlaTile = 64;
 constexpr int kMlaStages = 3;
@@ -39,7 +40,6 @@ constexpr int kMlaStageBytes = kMlaTile * kMlaD * 2;
 constexpr int kMlaChunkBytesK = kMlaTile * 128;
 constexpr int kMlaPBytes = kMlaHeadsTile * kMlaTile * 2;
 constexpr int kMlaSmemBytes = kMlaStages * kMlaStageBytes + kMlaPBytes + 1024 + 256;
-constexpr int kMlaTpr = 128 / kMlaTile;                          // gather threads per key row
 static_assert(kMlaTile == 32 || kMlaTile == 64, "tile must be 32 or 64 keys");
 constexpr uint32_t kMlaTmemCols = 512;
 constexpr uint32_t kMlaTmemO = 0;                 // lanes 0-15 of every sub-partition, columns 0..511
@@ -128,7 +128,7 @@ __device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr, uint3
 }
 
 __global__ void __launch_bounds__(kMlaThreads, 1)
-sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaParams p) {
+sparse_mla_decode_kernel(const MlaParams p) {
   extern __shared__ uint8_t smem_dyn[];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
@@ -281,8 +281,6 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
       for (int h = 0; h < kNV; ++h)
         tmem_ld_32x32(tmem_base + lane_addr + sb * kMlaTile + 32 * h, v[h]);   // lanes 16-31: score rows
       tc_wait_ld();
-      tc_fence_before();
-      mbar_arrive(&s_empty[sb]);
       float mt = -INFINITY;   // tile maximum of the raw scores, scaled once below (the scale is positive)
 #pragma unroll
       for (int h = 0; h < kNV; ++h) {
@@ -333,6 +331,10 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
         tc_wait_st();
         tc_fence_before();
       }
+      // Only now may the score issuer overwrite this buffer (two tiles ahead): the write-back of a
+      // rescale above also touches the score cells.
+      tc_fence_before();
+      mbar_arrive(&s_empty[sb]);
       if (grow) m_ref = mt;
       uint32_t pk[kMlaTile / 2];
       float lsum = 0.f;
@@ -403,17 +405,18 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
               (l_o > 0.f) ? (m_o + log2f(l_o)) * 0.6931471805599453f : -INFINITY;
       }
     }
-  } else {
-    // ------------------------------------------------------------------ MMA issuer (warp 8)
+  } else if (warp == 8) {
+    // ------------------------------------------------------------------ score MMA issuer (warp 8)
+    // Scores and values are issued by different warps so that neither waits for the other's
+    // barriers: the tensor pipe sees S(t+1), S(t+2) ... interleaved with PV(t) as they become ready.
     constexpr uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, kMlaHeadsTile, kMlaTile);
-    constexpr uint32_t idesc_pv = make_idesc(kFmtBF16, kFmtBF16, kMlaHeadsTile, 256, 0, 1);
     bool ok = mbar_wait(q_full, 0, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
-    auto issue_scores = [&](int t) -> bool {
+    for (int t = 0; ok && t < n_tiles; ++t) {
       const int s = t % kMlaStages, sb = t & 1;
-      bool w = mbar_wait(&kv_full[s], (t / kMlaStages) & 1, abort_flag) &&
-               mbar_wait(&s_empty[sb], ((t >> 1) & 1) ^ 1, abort_flag);
-      if (!__all_sync(0xffffffffu, w)) return false;
+      const bool w = mbar_wait(&kv_full[s], (t / kMlaStages) & 1, abort_flag) &&
+                     mbar_wait(&s_empty[sb], ((t >> 1) & 1) ^ 1, abort_flag);
+      if (!__all_sync(0xffffffffu, w)) break;
       fence_proxy_async();  // gathered rows were written through the generic proxy
       tc_fence_after();
       if (elect_one()) {
@@ -431,17 +434,16 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const MlaPa
         tc_commit(&s_full[sb]);
       }
       __syncwarp();
-      return true;
-    };
-    if (ok && n_tiles > 0) ok = issue_scores(0);
-    for (int t = 0; ok && t < n_tiles; ++t) {
-      if (t + 1 < n_tiles) {
-        ok = issue_scores(t + 1);
-        if (!ok) break;
-      }
+    }
+  } else {
+    // ------------------------------------------------------------------ value MMA issuer (warp 9)
+    constexpr uint32_t idesc_pv = make_idesc(kFmtBF16, kFmtBF16, kMlaHeadsTile, 256, 0, 1);
+    for (int t = 0; t < n_tiles; ++t) {
       const int s = t % kMlaStages;
-      const bool w = mbar_wait(p_full, t & 1, abort_flag);
+      const bool w = mbar_wait(p_full, t & 1, abort_flag) &&
+                     mbar_wait(&kv_full[s], (t / kMlaStages) & 1, abort_flag);  // long complete; orders the V reads
       if (!__all_sync(0xffffffffu, w)) break;
+      fence_proxy_async();
       tc_fence_after();
       if (elect_one()) {
         const uint64_t pa0 = make_desc_k_noswz(p_addr, 128, kMlaTile / 8 * 128);
@@ -492,22 +494,6 @@ extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16
     set_last_error("b200dsa_sparse_mla_decode: q, kv and ctx must be 16-byte aligned");
     return B200DSA_EALIGN;
   }
-  PFN_encodeTiled enc = get_encode_tiled();
-  if (!enc) return B200DSA_ECUDA;
-  CUtensorMap mq;
-  {
-    cuuint64_t dims[2] = {kMlaD, static_cast<cuuint64_t>(n_items) * n_heads};
-    cuuint64_t strides[1] = {kMlaD * 2};
-    cuuint32_t box[2] = {64, kMlaHeadsTile};  // 64 elements x 64 head rows
-    cuuint32_t es[2] = {1, 1};
-    CUresult r = enc(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(q_bf16), dims, strides, box, es,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-      set_last_error("b200dsa_sparse_mla_decode: cuTensorMapEncodeTiled rejected the q layout");
-      return B200DSA_ECUDA;
-    }
-  }
   cudaError_t e = cudaFuncSetAttribute(sparse_mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kMlaSmemBytes);
   if (e != cudaSuccess) {
@@ -532,7 +518,7 @@ extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16
   p.ctx = ctx;
   p.lse = lse;
   p.status = status;
-  sparse_mla_decode_kernel<<<n_items * 2, kMlaThreads, kMlaSmemBytes, static_cast<cudaStream_t>(stream)>>>(mq, p);
+  sparse_mla_decode_kernel<<<n_items * 2, kMlaThreads, kMlaSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
