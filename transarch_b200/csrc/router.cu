@@ -51,29 +51,58 @@ __global__ void __launch_bounds__(256) router_linear_kernel(const __nv_bfloat16*
                                                             float* __restrict__ weights_out,
                                                             int32_t* __restrict__ head_idx,
                                                             float* __restrict__ logits_out) {
-  __shared__ float part[4][kRouterHeads];
+  // Thread (grp, h8): rows grp, grp+32, ... of W_r, heads 8*h8 .. 8*h8+7 (one 16-byte load per row),
+  // four rows in flight; x is staged in shared memory once.
+  extern __shared__ __nv_bfloat16 xs[];
+  __shared__ float part[32][kRouterHeads + 1];
   __shared__ float logit[kRouterHeads];
   __shared__ int sel[kRouterHeads], keep[kRouterHeads];
-  const int t = blockIdx.x, h = threadIdx.x & 63, g = threadIdx.x >> 6;
+  const int t = blockIdx.x, tid = threadIdx.x, h8 = tid & 7, grp = tid >> 3;
   const __nv_bfloat16* xr = x + static_cast<int64_t>(t) * hidden;
-  float acc0 = 0.f, acc1 = 0.f;
-  int i = g;
-  for (; i + 4 < hidden; i += 8) {
-    acc0 = fmaf(__bfloat162float(xr[i]), __bfloat162float(w_r[static_cast<int64_t>(i) * 64 + h]), acc0);
-    acc1 = fmaf(__bfloat162float(xr[i + 4]), __bfloat162float(w_r[static_cast<int64_t>(i + 4) * 64 + h]), acc1);
-  }
-  for (; i < hidden; i += 4)
-    acc0 = fmaf(__bfloat162float(xr[i]), __bfloat162float(w_r[static_cast<int64_t>(i) * 64 + h]), acc0);
-  part[g][h] = acc0 + acc1;
+  for (int i = tid; i < hidden; i += 256) xs[i] = xr[i];
   __syncthreads();
-  if (threadIdx.x < 64) {
-    logit[h] = (part[0][h] + part[1][h]) + (part[2][h] + part[3][h]);
-    if (logits_out) logits_out[static_cast<int64_t>(t) * 64 + h] = logit[h];
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const uint4* wv = reinterpret_cast<const uint4*>(w_r) + h8;   // row i: 8 uint4 (64 bf16)
+  int i = grp;
+  for (; i + 96 < hidden; i += 128) {
+    uint4 r[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) r[u] = __ldg(wv + static_cast<int64_t>(i + 32 * u) * 8);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float xv = __bfloat162float(xs[i + 32 * u]);
+      const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&r[u]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] = fmaf(xv, __low2float(w2[j]), acc[2 * j]);
+        acc[2 * j + 1] = fmaf(xv, __high2float(w2[j]), acc[2 * j + 1]);
+      }
+    }
+  }
+  for (; i < hidden; i += 32) {
+    const uint4 r = __ldg(wv + static_cast<int64_t>(i) * 8);
+    const float xv = __bfloat162float(xs[i]);
+    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      acc[2 * j] = fmaf(xv, __low2float(w2[j]), acc[2 * j]);
+      acc[2 * j + 1] = fmaf(xv, __high2float(w2[j]), acc[2 * j + 1]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) part[grp][8 * h8 + j] = acc[j];
+  __syncthreads();
+  if (tid < 64) {
+    float sum = 0.f;
+    for (int g = 0; g < 32; ++g) sum += part[g][tid];
+    logit[tid] = sum;
+    if (logits_out) logits_out[static_cast<int64_t>(t) * 64 + tid] = sum;
   }
   __syncthreads();
   select_top_heads(logit, n_keep, sel, keep);
   __syncthreads();
-  if (threadIdx.x < 64) {
+  if (tid < 64) {
+    const int h = tid;
     // softmax over the kept logits (sel[0] holds the largest)
     const float mx = logit[sel[0]];
     float den = 0.f;
@@ -186,7 +215,11 @@ extern "C" int b200dsa_router_linear_topk_softmax(const void* x_bf16, const void
     set_last_error("b200dsa_router_linear_topk_softmax: bad argument (1 <= n_keep <= 64)");
     return B200DSA_EINVAL;
   }
-  router_linear_kernel<<<n_tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  if (hidden > 24576 || (reinterpret_cast<uintptr_t>(w_r_bf16) & 15)) {
+    set_last_error("b200dsa_router_linear_topk_softmax: hidden must be <= 24576 and W_r 16-byte aligned");
+    return B200DSA_EINVAL;
+  }
+  router_linear_kernel<<<n_tokens, 256, static_cast<size_t>(hidden) * 2, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x_bf16), static_cast<const __nv_bfloat16*>(w_r_bf16), hidden, n_keep,
       weights_out, head_idx, logits_out);
   return finish_launch();
