@@ -167,7 +167,8 @@ int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const float* weigh
  * _attend_absorbed_chunk before its W_UV up-projection (:44).
  *   q_bf16 [n_items, n_heads, 576], kv_bf16 [kv_rows, 576] (512 value dims then 64 rope dims),
  *   indices [n_items, idx_stride] int32, kv_row_base / q_pos optional (0 / no bound),
- *   ctx [n_items, n_heads, 512] fp32, lse [n_items, n_heads] fp32.  1 <= n_heads <= 128.
+ *   ctx [n_items, n_heads, 512] fp32, or bf16 (the dtype the reference returns, sparse_mla.py:44-47)
+ *   when ctx_bf16 != 0; lse [n_items, n_heads] fp32.  1 <= n_heads <= 128.
  * n_idx_item (optional int32 [n_items]) limits item i to its first n_idx_item[i] indices
  * (compacted shard lists).  Rows outside [0, kv_rows) are skipped and reported through status (2).
  * ------------------------------------------------------------------------------------- */
@@ -175,8 +176,8 @@ int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16, int64_t k
                               const int64_t* kv_row_base, const int32_t* indices, int64_t idx_stride,
                               int32_t n_idx, const int32_t* n_idx_item, const int32_t* q_pos,
                               int32_t pos_lo, int32_t pos_hi,
-                              int32_t n_items, int32_t n_heads, float sm_scale, float* ctx, float* lse,
-                              int32_t* status, void* stream);
+                              int32_t n_items, int32_t n_heads, float sm_scale, void* ctx, int32_t ctx_bf16,
+                              float* lse, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Merge attention partials computed over disjoint key sets (key shards of several GPUs, or

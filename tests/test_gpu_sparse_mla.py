@@ -60,6 +60,11 @@ def test_decode_vs_oracle(n_items, H, n_idx, ctx_len):
         rc, rl = O.sparse_attend_latent(q[b:b + 1], kv[b * ctx_len:(b + 1) * ctx_len], idx[b:b + 1],
                                         d_c=512, sm_scale=scale, q_pos=qpos[b:b + 1])
         _check(ctx[b:b + 1].cpu(), lse[b:b + 1].cpu(), rc, rl)
+    # bf16 result buffer (the dtype the reference op returns): the fp32 result rounded once
+    out16 = torch.empty(n_items, H, 512, dtype=torch.bfloat16, device="cuda")
+    ctx16, lse16 = K.sparse_mla_decode(q.cuda(), kv.cuda(), idx.cuda(), scale, kv_row_base=base.cuda(),
+                                       q_pos=qpos.cuda(), ctx=out16)
+    assert ctx16.dtype == torch.bfloat16 and torch.equal(ctx16, ctx.bfloat16()) and torch.equal(lse16, lse)
 
 
 def test_shard_partials_merge_to_full():

@@ -36,7 +36,8 @@ def _worker(rank, world, port, wire, ret):
                                  st["kv"], st["base"])
         ref_idx, _, ref_ctx, ref_lse = oracle_decode(prob, TOPK, 128 ** -0.5, 192 ** -0.5)
         tol = dict(rtol=1e-4, atol=1e-5) if wire == "fp32" else dict(rtol=2e-2, atol=2e-3)   # bf16 wire
-        ok = torch.equal(idx, ref_idx) and torch.allclose(ctx.float(), ref_ctx, **tol) and \
+        want = torch.bfloat16 if wire == "bf16" else torch.float32       # the wire that was asked for ran
+        ok = ctx.dtype == want and torch.equal(idx, ref_idx) and torch.allclose(ctx.float(), ref_ctx, **tol) and \
             torch.allclose(lse, ref_lse, rtol=1e-4, atol=1e-5)
         ret[rank] = bool(ok)
     finally:

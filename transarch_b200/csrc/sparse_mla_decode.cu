@@ -47,6 +47,11 @@ constexpr uint32_t kMlaTmemS = (16u << 16);       // lanes 16-31 of every sub-pa
 constexpr uint32_t kMlaTmemQ = (16u << 16) + 128; // Q as the A operand: upper half-lanes, columns 128..415
                                                   // (64 rows x 576 bf16, two per 32-bit cell)
 
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
 struct MlaParams {
   const __nv_bfloat16* q;      // [n_items, n_heads, 576]
   const __nv_bfloat16* kv;     // [kv_rows, 576]
@@ -60,7 +65,8 @@ struct MlaParams {
   int32_t pos_lo, pos_hi;      // only positions in [pos_lo, pos_hi) are attended (shard ownership)
   int32_t n_items, n_heads;
   float scale_log2;            // sm_scale * log2(e)
-  float* ctx;                  // [n_items, n_heads, 512] fp32
+  void* ctx;                   // [n_items, n_heads, 512] fp32, or bf16 when ctx_bf16 != 0
+  int ctx_bf16;
   float* lse;                  // [n_items, n_heads] fp32 (natural log)
   int32_t* status;
 };
@@ -373,11 +379,17 @@ sparse_mla_decode_kernel(const MlaParams p) {
     const float l_o = __shfl_xor_sync(0xffffffffu, l, 16);
     const float m_o = __shfl_xor_sync(0xffffffffu, m_ref, 16);
     const int head = hh * kMlaHeadsTile + row;
-    float* ctx_row = p.ctx + (static_cast<int64_t>(item) * p.n_heads + head) * kMlaDv;
+    const int64_t ctx_off = (static_cast<int64_t>(item) * p.n_heads + head) * kMlaDv;
+    float* ctx_row = static_cast<float*>(p.ctx) + ctx_off;
+    __nv_bfloat16* ctx_row_h = static_cast<__nv_bfloat16*>(p.ctx) + ctx_off;
     const bool write = !is_s && head < p.n_heads;
     if (n_tiles == 0 || aborted) {
       if (write && !aborted) {
-        for (int j = 0; j < kMlaDv; j += 4) *reinterpret_cast<float4*>(ctx_row + j) = make_float4(0, 0, 0, 0);
+        if (p.ctx_bf16) {
+          for (int j = 0; j < kMlaDv; j += 8) *reinterpret_cast<uint4*>(ctx_row_h + j) = make_uint4(0, 0, 0, 0);
+        } else {
+          for (int j = 0; j < kMlaDv; j += 4) *reinterpret_cast<float4*>(ctx_row + j) = make_float4(0, 0, 0, 0);
+        }
         p.lse[static_cast<int64_t>(item) * p.n_heads + head] = -INFINITY;
       }
     } else {
@@ -390,7 +402,17 @@ sparse_mla_decode_kernel(const MlaParams p) {
           uint32_t o[32];
           tmem_ld_32x32(tmem_base + lane_addr + kMlaTmemO + c * 32, o);
           tc_wait_ld();
-          if (write) {
+          if (write && p.ctx_bf16) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
+              v.y = pack_bf16x2(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+              v.z = pack_bf16x2(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
+              v.w = pack_bf16x2(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
+              *reinterpret_cast<uint4*>(ctx_row_h + c * 32 + j) = v;
+            }
+          } else if (write) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               *reinterpret_cast<float4*>(ctx_row + c * 32 + j) =
@@ -481,8 +503,8 @@ extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16
                                          const int64_t* kv_row_base, const int32_t* indices, int64_t idx_stride,
                                          int32_t n_idx, const int32_t* n_idx_item, const int32_t* q_pos,
                                          int32_t pos_lo, int32_t pos_hi,
-                                         int32_t n_items, int32_t n_heads, float sm_scale, float* ctx, float* lse,
-                                         int32_t* status, void* stream) {
+                                         int32_t n_items, int32_t n_heads, float sm_scale, void* ctx, int32_t ctx_bf16,
+                                         float* lse, int32_t* status, void* stream) {
   if (n_items == 0) return B200DSA_OK;
   if (!q_bf16 || !kv_bf16 || !indices || !ctx || !lse || !status || n_items < 0 || n_heads < 1 ||
       n_heads > kMlaMaxHeads || n_idx < 0 || idx_stride < n_idx || kv_rows < 1 || pos_hi < pos_lo) {
@@ -516,6 +538,7 @@ extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16
   p.n_heads = n_heads;
   p.scale_log2 = sm_scale * 1.4426950408889634f;
   p.ctx = ctx;
+  p.ctx_bf16 = ctx_bf16;
   p.lse = lse;
   p.status = status;
   sparse_mla_decode_kernel<<<n_items * 2, kMlaThreads, kMlaSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);

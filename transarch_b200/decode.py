@@ -66,7 +66,7 @@ class SparseDecodeStep:
     def __init__(self, batch: int, max_local_ctx: int, *, page_size: int = 64, topk: int = 2048,
                  n_heads: int = 128, index_scale: float = 128 ** -0.5, attn_scale: float = 192 ** -0.5,
                  device: Optional[torch.device] = None, shard: Optional[ShardInfo] = None, backend=None,
-                 sorted_topk: bool = False, wire: str = "bf16"):
+                 sorted_topk: bool = False, wire: str = "bf16", ctx_dtype: torch.dtype = torch.float32):
         if backend is None:
             from . import kernels as backend  # the CUDA kernels; fails loudly without the library
         self.K = backend
@@ -74,7 +74,9 @@ class SparseDecodeStep:
         self.index_scale, self.attn_scale = index_scale, attn_scale
         self.shard = shard or ShardInfo()
         self.sorted_topk = sorted_topk
-        self.wire = wire if hasattr(backend, "lse_prescale_norm") else "fp32"
+        if wire not in ("bf16", "fp32"):
+            raise ValueError("wire must be 'bf16' or 'fp32'")
+        self.wire_mode = wire if hasattr(backend, "lse_prescale_norm") else "fp32"
         dev = device if device is not None else torch.device("cuda")
         self.dev = dev
         f32, i32 = torch.float32, torch.int32
@@ -86,7 +88,9 @@ class SparseDecodeStep:
         # candidate wire layout: [B, 2k] int32 = k global positions then k score bit patterns
         self.cand = torch.empty(batch, 2 * topk, dtype=i32, device=dev)
         self.pos_offset = torch.full((batch,), self.shard.pos_lo, dtype=i32, device=dev)
-        self.ctx = torch.empty(batch, n_heads, 512, dtype=f32, device=dev)
+        # unsharded: the kernel writes the result in ctx_dtype (bf16 is what the reference op returns);
+        # sharded: fp32 partials, merged by combine()
+        self.ctx = torch.empty(batch, n_heads, 512, dtype=ctx_dtype if n == 1 else f32, device=dev)
         self.lse = torch.empty(batch, n_heads, dtype=f32, device=dev)
         self.q_pos = torch.empty(batch, dtype=i32, device=dev)
         # few long rows: spread the top-k of every row over several CTAs (global scratch, allocated once)
@@ -99,11 +103,13 @@ class SparseDecodeStep:
             self.owned = torch.empty(batch, topk, dtype=i32, device=dev)
             self.owned_count = torch.empty(batch, dtype=i32, device=dev)
             self.lse_max = torch.empty(batch, n_heads, dtype=f32, device=dev)
-            self.wire = torch.empty(batch * n_heads, backend.WIRE_ROW, dtype=f32, device=dev)
-            self.ctx_out = torch.empty(batch, n_heads, 512, dtype=f32, device=dev)
             self.lse_out = torch.empty(batch, n_heads, dtype=f32, device=dev)
-            self.lse_all = torch.empty(n, batch, n_heads, dtype=f32, device=dev)
-            self.ctx_bf16 = torch.empty(batch, n_heads, 512, dtype=torch.bfloat16, device=dev)
+            if self.wire_mode == "bf16":
+                self.lse_all = torch.empty(n, batch, n_heads, dtype=f32, device=dev)
+                self.ctx_bf16 = torch.empty(batch, n_heads, 512, dtype=torch.bfloat16, device=dev)
+            else:
+                self.wire_rows = torch.empty(batch * n_heads, backend.WIRE_ROW, dtype=f32, device=dev)
+                self.ctx_out = torch.empty(batch, n_heads, 512, dtype=f32, device=dev)
 
     # ------------------------------------------------------------------ stages
     def select(self, q_idx, w, k_cache, context_lens_local, block_table) -> torch.Tensor:
@@ -149,7 +155,7 @@ class SparseDecodeStep:
     def combine(self) -> Tuple[torch.Tensor, torch.Tensor]:
         """Merge the per-rank (ctx, lse) partials; every rank ends with the full result."""
         K, g = self.K, self.shard.group
-        if self.wire == "bf16":
+        if self.wire_mode == "bf16":
             # gather the lse of every rank (4 B per row and rank): each rank then knows the common
             # maximum and the exact denominator and sends its normalised bf16 share; the summed
             # rows are the result
@@ -159,14 +165,15 @@ class SparseDecodeStep:
             return self.ctx_bf16, self.lse_out
         self.lse_max.copy_(self.lse)
         dist.all_reduce(self.lse_max, op=dist.ReduceOp.MAX, group=g)
-        K.lse_prescale(self.ctx, self.lse, self.lse_max, self.wire)
-        dist.all_reduce(self.wire, op=dist.ReduceOp.SUM, group=g)
-        return K.lse_finalize(self.wire, self.lse_max, self.ctx_out, self.lse_out)
+        K.lse_prescale(self.ctx, self.lse, self.lse_max, self.wire_rows)
+        dist.all_reduce(self.wire_rows, op=dist.ReduceOp.SUM, group=g)
+        return K.lse_finalize(self.wire_rows, self.lse_max, self.ctx_out, self.lse_out)
 
     # ------------------------------------------------------------------ whole step
     def run(self, q_idx, w, q_lat, k_cache, context_lens, block_table, kv, kv_row_base,
             context_lens_local: Optional[torch.Tensor] = None):
-        """Returns (indices int32 [B,k] global positions, ctx fp32 [B,H,512], lse fp32 [B,H])."""
+        """Returns (indices int32 [B,k] global positions, ctx [B,H,512], lse fp32 [B,H]); ctx is
+        ctx_dtype when unsharded, bf16 / fp32 after a sharded combine with the bf16 / fp32 wire."""
         if context_lens_local is None:
             context_lens_local = local_context_lens(context_lens, self.shard)
         idx = self.select(q_idx, w, k_cache, context_lens_local, block_table)

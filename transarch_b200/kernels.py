@@ -199,8 +199,8 @@ def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, 
                       pos_lo: int = 0, pos_hi: int = 2 ** 31 - 1, n_idx_item: Optional[torch.Tensor] = None,
                       ctx: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None
                       ) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Latent-space sparse attention: (ctx [n, H, 512] fp32, lse [n, H] fp32); see
-    b200dsa_sparse_mla_decode."""
+    """Latent-space sparse attention: (ctx [n, H, 512], lse [n, H] fp32); see
+    b200dsa_sparse_mla_decode.  ctx is fp32 unless a bf16 buffer is passed in."""
     require_cuda(q, kv, indices, kv_row_base, q_pos)
     if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.dim() != 3 or q.shape[2] != 576:
         raise _lib.B200DSAError("q must be contiguous bf16 [n_items, n_heads, 576]")
@@ -216,10 +216,13 @@ def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, 
         ctx = torch.empty(n, H, 512, dtype=torch.float32, device=q.device)
     if lse is None:
         lse = torch.empty(n, H, dtype=torch.float32, device=q.device)
+    if ctx.dtype not in (torch.float32, torch.bfloat16) or not ctx.is_contiguous() or ctx.shape != (n, H, 512):
+        raise _lib.B200DSAError("ctx must be contiguous fp32 or bf16 [n_items, n_heads, 512]")
     lib = _lib.load()
     rc = lib.b200dsa_sparse_mla_decode(
         ptr(q), ptr(kv), kv.shape[0], ptr(kv_row_base), ptr(indices), indices.stride(0), indices.shape[1],
-        ptr(_i32(n_idx_item, "n_idx_item")), ptr(q_pos), pos_lo, pos_hi, n, H, sm_scale, ptr(ctx), ptr(lse), ptr(status_word(q.device)), stream_ptr())
+        ptr(_i32(n_idx_item, "n_idx_item")), ptr(q_pos), pos_lo, pos_hi, n, H, sm_scale, ptr(ctx),
+        int(ctx.dtype == torch.bfloat16), ptr(lse), ptr(status_word(q.device)), stream_ptr())
     check(rc, "b200dsa_sparse_mla_decode")
     return ctx, lse
 
