@@ -125,13 +125,19 @@ int b200dsa_topk_select_split_static(const float* scores, int64_t row_stride, in
  *                replaces the row/next_n rule
  * Page ids outside [0, num_pages) are skipped and reported through status (2).
  * q, weights and cache must be 16-byte aligned.
+ * head_mask / logits_gated (both or neither): when given, logits_gated[r, c] (same stride as
+ * logits) receives the same sum restricted to the heads whose bit is set in head_mask[r]
+ * (bit h = head h).  This is MISA's routed stage-1 score (zero weight on the dropped heads,
+ * misa_ops.py:703-705) produced in the same pass over the cache as the all-head score that the
+ * reference computes in a second pass (misa_ops.py:396-411).
  * ------------------------------------------------------------------------------------- */
 int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* weights, const void* cache,
                                      int32_t num_pages, int32_t page_size, const int32_t* context_lens,
                                      const int32_t* block_table, int64_t block_table_stride,
                                      const int32_t* row_table, int32_t n_rows, int32_t next_n,
                                      int32_t max_cols, float out_scale,
-                                     float* logits, int64_t logits_stride, int32_t* status, void* stream);
+                                     float* logits, int64_t logits_stride, const uint64_t* head_mask,
+                                     float* logits_gated, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Token logits inside per-row lists of 128-key blocks, bf16 keys (tcgen05 bf16 contraction).
@@ -145,13 +151,15 @@ int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* weights, co
  * (block_sparse_mqa_attn_return_logits and its interface).
  *   q_bf16 [n_rows, 64, 128], keys_bf16 [n_keys, 128] (both 16-byte aligned),
  *   row_cols [n_rows] = 128 * (number of listed blocks), block ids in [0, ceil(n_keys/128)).
+ * head_mask / logits_gated: as for b200dsa_indexer_paged_fp8_logits.
  * ------------------------------------------------------------------------------------- */
 int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const float* weights, const void* keys_bf16,
                                           int32_t n_keys, const int32_t* block_list,
                                           int64_t block_list_stride, const int32_t* row_cols,
                                           const int32_t* pos_lo, const int32_t* pos_hi, int32_t n_rows,
                                           int32_t max_cols, float out_scale, float* logits,
-                                          int64_t logits_stride, int32_t* status, void* stream);
+                                          int64_t logits_stride, const uint64_t* head_mask,
+                                          float* logits_gated, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Sparse MLA attention over selected keys in the absorbed latent space (tcgen05), one query

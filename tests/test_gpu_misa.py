@@ -180,3 +180,47 @@ def test_misa_page_logits_and_hook_decode_prefill():
         got = res[t][res[t] >= 0]
         assert got.numel() == ref.numel()
         assert len(set(got.tolist()) & set(ref.tolist())) >= 0.95 * ref.numel(), t
+
+
+def test_single_pass_gated_and_full_scores():
+    """The one-pass (all heads, routed heads) pair equals two separate passes bit for bit: a pass
+    with the original weights, and a pass with zero weights on the dropped heads."""
+    from transarch_b200 import _lib, kernels as K
+    from transarch_b200.misa import gate_weights_by_heads
+    from transarch_b200.opendsa_ops import identity_block_lists
+    ctxs = [700, 64, 2049, 1]
+    g, qs, cache, table = _paged(11, ctxs)
+    B = len(ctxs)
+    q = torch.randn(B, 64, 128, generator=g)
+    w = torch.randn(B, 64, generator=g) / 8
+    heads = torch.stack([torch.randperm(64, generator=g)[:8] for _ in range(B)]).to(torch.int32)
+    heads[0, 0], heads[1, 0] = 63, 0                                   # both ends of the mask word
+    q8, wf = K.quant_q_fold_weights(q.cuda().bfloat16(), w.cuda(), 128 ** -0.5)
+    lens = torch.tensor(ctxs, dtype=torch.int32).cuda()
+    mask = K.head_mask_from_indices(heads.cuda())
+    for b in range(B):
+        want = sum(1 << int(h) for h in set(heads[b].tolist()))
+        assert (int(mask[b]) & (2 ** 64 - 1)) == want
+    kw = dict(max_cols=2112)
+    full, gated = K.indexer_paged_fp8_logits(q8, wf, cache.cuda(), 64, lens, table.cuda(), head_mask=mask, **kw)
+    full_ref = K.indexer_paged_fp8_logits(q8, wf, cache.cuda(), 64, lens, table.cuda(), **kw)
+    gated_ref = K.indexer_paged_fp8_logits(q8, gate_weights_by_heads(wf, heads.cuda()), cache.cuda(), 64, lens,
+                                           table.cuda(), **kw)
+    assert torch.equal(full, full_ref) and torch.equal(gated, gated_ref)
+    assert not torch.equal(full[:, :1], gated[:, :1])
+    # bf16 block-list form
+    N = 1000
+    k = torch.randn(N, 128, generator=g).bfloat16().cuda()
+    T = 5
+    qb = torch.randn(T, 64, 128, generator=g).bfloat16().cuda()
+    wb = (torch.randn(T, 64, generator=g) / 8).cuda()
+    hb = torch.stack([torch.randperm(64, generator=g)[:8] for _ in range(T)]).to(torch.int32).cuda()
+    ks = torch.zeros(T, dtype=torch.int32).cuda()
+    ke = torch.tensor([1000, 300, 129, 128, 1], dtype=torch.int32).cuda()
+    bl, row_cols = identity_block_lists(ks.long(), ke.long(), N)
+    f2, g2 = K.indexer_blocklist_bf16_logits(qb, wb, k, bl, row_cols, pos_lo=ks, pos_hi=ke,
+                                             head_mask=K.head_mask_from_indices(hb))
+    f2_ref = K.indexer_blocklist_bf16_logits(qb, wb, k, bl, row_cols, pos_lo=ks, pos_hi=ke)
+    g2_ref = K.indexer_blocklist_bf16_logits(qb, gate_weights_by_heads(wb, hb), k, bl, row_cols, pos_lo=ks, pos_hi=ke)
+    assert torch.equal(f2, f2_ref) and torch.equal(g2, g2_ref)
+    assert _lib.read_status(full.device) == 0

@@ -63,6 +63,8 @@ struct PagedIndexerParams {
   float* logits;                // [n_rows, logits_stride]
   int64_t logits_stride;
   int32_t logits_cols;          // columns that may be written per row
+  const uint64_t* head_mask;    // nullable [n_rows]: bit h set = head h counts towards logits_gated
+  float* logits_gated;          // nullable [n_rows, logits_stride]: the same sum over the masked heads only
   int32_t* status;
 };
 
@@ -300,6 +302,8 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
     int row = row0, prev_row = -1;
     int ait = 0;
     int cols = 0, lo = 0, hi = 0x7fffffff;
+    uint32_t hm0 = 0, hm1 = 0;
+    const bool dual = p.logits_gated != nullptr;
     const int32_t* trow = p.table;
     for (int g = g0; g < g1; ++g) {
       while (g >= s_prefix[row + 1]) ++row;
@@ -314,6 +318,11 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
         cols = max(0, min(p.row_cols[row], p.logits_cols));
         trow = p.table + static_cast<int64_t>(p.row_table ? p.row_table[row] : row / p.table_row_div) * p.table_stride;
         if (p.pos_lo) { lo = p.pos_lo[row]; hi = p.pos_hi[row]; }
+        if (dual) {
+          const uint64_t hm = p.head_mask[row];
+          hm0 = static_cast<uint32_t>(hm);
+          hm1 = static_cast<uint32_t>(hm >> 32);
+        }
         prev_row = row;
       }
       const int key = t * kTileKeys + lane_base + lane;  // column of this thread
@@ -344,12 +353,28 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       tc_fence_before();
       mbar_arrive(&acc_empty[as]);
       float acc0 = 0.f, acc1 = 0.f;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        acc0 = fmaf(fmaxf(__uint_as_float(v0[j]), 0.f), w[j], acc0);
-        acc1 = fmaf(fmaxf(__uint_as_float(v1[j]), 0.f), w[32 + j], acc1);
-      }
       const int tile_cols = min(p.logits_cols, (t + 1) * kTileKeys);
+      if (dual) {
+        // one pass, two sums: all heads, and the routed heads only (a zero weight elsewhere)
+        float gat0 = 0.f, gat1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float r0 = fmaxf(__uint_as_float(v0[j]), 0.f), r1 = fmaxf(__uint_as_float(v1[j]), 0.f);
+          acc0 = fmaf(r0, w[j], acc0);
+          acc1 = fmaf(r1, w[32 + j], acc1);
+          gat0 = fmaf(r0, ((hm0 >> j) & 1u) ? w[j] : 0.f, gat0);
+          gat1 = fmaf(r1, ((hm1 >> j) & 1u) ? w[32 + j] : 0.f, gat1);
+        }
+        if (key < tile_cols)
+          p.logits_gated[static_cast<int64_t>(row) * p.logits_stride + key] =
+              keep ? (gat0 + gat1) * kscale * p.out_scale : -INFINITY;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          acc0 = fmaf(fmaxf(__uint_as_float(v0[j]), 0.f), w[j], acc0);
+          acc1 = fmaf(fmaxf(__uint_as_float(v1[j]), 0.f), w[32 + j], acc1);
+        }
+      }
       if (key < tile_cols) {
         const float out = keep ? (acc0 + acc1) * kscale * p.out_scale : -INFINITY;
         p.logits[static_cast<int64_t>(row) * p.logits_stride + key] = out;
@@ -434,10 +459,12 @@ extern "C" int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* 
                                                 const int32_t* block_table, int64_t block_table_stride,
                                                 const int32_t* row_table, int32_t n_rows, int32_t next_n,
                                                 int32_t max_cols, float out_scale,
-                                                float* logits, int64_t logits_stride, int32_t* status, void* stream) {
+                                                float* logits, int64_t logits_stride, const uint64_t* head_mask,
+                                                float* logits_gated, int32_t* status, void* stream) {
   if (n_rows == 0) return B200DSA_OK;
   if (!q_fp8 || !weights || !cache || !context_lens || !block_table || !logits || !status || n_rows < 0 ||
-      next_n < 1 || num_pages < 1 || max_cols < 0 || logits_stride < max_cols) {
+      next_n < 1 || num_pages < 1 || max_cols < 0 || logits_stride < max_cols ||
+      ((head_mask == nullptr) != (logits_gated == nullptr))) {
     set_last_error("b200dsa_indexer_paged_fp8_logits: bad argument");
     return B200DSA_EINVAL;
   }
@@ -491,6 +518,8 @@ extern "C" int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* 
     p.logits = logits + static_cast<int64_t>(r0) * logits_stride;
     p.logits_stride = logits_stride;
     p.logits_cols = max_cols;
+    p.head_mask = head_mask ? head_mask + r0 : nullptr;
+    p.logits_gated = logits_gated ? logits_gated + static_cast<int64_t>(r0) * logits_stride : nullptr;
     p.status = status;
     rc = launch_paged<true>(mk, mq, p, 0, static_cast<cudaStream_t>(stream));
     if (rc) return rc;
@@ -503,10 +532,12 @@ extern "C" int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const f
                                                      int64_t block_list_stride, const int32_t* row_cols,
                                                      const int32_t* pos_lo, const int32_t* pos_hi, int32_t n_rows,
                                                      int32_t max_cols, float out_scale, float* logits,
-                                                     int64_t logits_stride, int32_t* status, void* stream) {
+                                                     int64_t logits_stride, const uint64_t* head_mask,
+                                                     float* logits_gated, int32_t* status, void* stream) {
   if (n_rows == 0) return B200DSA_OK;
   if (!q_bf16 || !weights || !keys_bf16 || !block_list || !row_cols || !logits || !status || n_rows < 0 ||
-      n_keys < 1 || max_cols < 0 || logits_stride < max_cols || ((pos_lo == nullptr) != (pos_hi == nullptr))) {
+      n_keys < 1 || max_cols < 0 || logits_stride < max_cols || ((pos_lo == nullptr) != (pos_hi == nullptr)) ||
+      ((head_mask == nullptr) != (logits_gated == nullptr))) {
     set_last_error("b200dsa_indexer_blocklist_bf16_logits: bad argument");
     return B200DSA_EINVAL;
   }
@@ -550,6 +581,8 @@ extern "C" int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const f
     p.logits = logits + static_cast<int64_t>(r0) * logits_stride;
     p.logits_stride = logits_stride;
     p.logits_cols = max_cols;
+    p.head_mask = head_mask ? head_mask + r0 : nullptr;
+    p.logits_gated = logits_gated ? logits_gated + static_cast<int64_t>(r0) * logits_stride : nullptr;
     p.status = status;
     rc = launch_paged<false>(mk, mq, p, 0, static_cast<cudaStream_t>(stream));
     if (rc) return rc;

@@ -67,9 +67,9 @@ CAND_CAP = 8192  # candidate list entries per row of the split top-k scratch
 
 
 def topk_scratch(n_rows: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Zeroed scratch for topk_select_split: (candidates uint64-as-int64 [n_rows, 8192], int32 [2*n_rows]:
-    per-row counters then per-row bin floors)."""
-    return (torch.zeros(n_rows, CAND_CAP, dtype=torch.int64, device=device),
+    """Scratch for topk_select_split: (candidates uint64-as-int64 [n_rows, 8192], zeroed int32 [2*n_rows]:
+    per-row counters then per-row bin floors).  Only the counters have to start at zero."""
+    return (torch.empty(n_rows, CAND_CAP, dtype=torch.int64, device=device),
             torch.zeros(2 * n_rows, dtype=torch.int32, device=device))
 
 
@@ -133,11 +133,14 @@ def indexer_paged_fp8_logits(q_fp8: torch.Tensor, weights: torch.Tensor, cache: 
                              context_lens: torch.Tensor, block_table: torch.Tensor, *, next_n: int = 1,
                              max_cols: Optional[int] = None, out_scale: float = 1.0,
                              out: Optional[torch.Tensor] = None, fill: bool = True,
-                             row_table: Optional[torch.Tensor] = None) -> torch.Tensor:
+                             row_table: Optional[torch.Tensor] = None, head_mask: Optional[torch.Tensor] = None,
+                             out_gated: Optional[torch.Tensor] = None):
     """Decode logits [n_rows, max_cols] fp32 over the paged FP8 cache; see
     b200dsa_indexer_paged_fp8_logits.  fill=True pre-fills a fresh output with -inf so that
-    columns beyond each context are -inf as in the reference; pass out= to reuse a buffer."""
-    require_cuda(q_fp8, weights, cache, context_lens, block_table)
+    columns beyond each context are -inf as in the reference; pass out= to reuse a buffer.
+    With head_mask (int64 [n_rows], bit h = head h) the same pass also produces the sum over the
+    masked heads only, and the call returns (logits, gated logits)."""
+    require_cuda(q_fp8, weights, cache, context_lens, block_table, head_mask, out_gated)
     if q_fp8.dtype != torch.float8_e4m3fn or not q_fp8.is_contiguous() or q_fp8.shape[-2:] != (64, 128):
         raise _lib.B200DSAError("q_fp8 must be contiguous float8_e4m3fn [..., 64, 128]")
     n_rows = q_fp8.numel() // (64 * 128)
@@ -157,23 +160,48 @@ def indexer_paged_fp8_logits(q_fp8: torch.Tensor, weights: torch.Tensor, cache: 
     if out is None:
         out = (torch.full if fill else torch.empty)(
             (n_rows, max_cols), *((NEG_INF,) if fill else ()), dtype=torch.float32, device=q_fp8.device)
+    out_gated = _gated_output(head_mask, out_gated, out, n_rows, fill)
     lib = _lib.load()
     rc = lib.b200dsa_indexer_paged_fp8_logits(
         ptr(q_fp8), ptr(weights), ptr(cache), num_pages, page_size, ptr(context_lens),
         ptr(block_table), block_table.stride(0), ptr(_i32(row_table, "row_table")), n_rows, next_n, max_cols,
         out_scale,
-        ptr(out), out.stride(0), ptr(status_word(q_fp8.device)), stream_ptr())
+        ptr(out), out.stride(0), ptr(head_mask), ptr(out_gated), ptr(status_word(q_fp8.device)), stream_ptr())
     check(rc, "b200dsa_indexer_paged_fp8_logits")
-    return out
+    return out if head_mask is None else (out, out_gated)
+
+
+def _gated_output(head_mask, out_gated, out, n_rows, fill=True):
+    if head_mask is None:
+        if out_gated is not None:
+            raise _lib.B200DSAError("out_gated needs head_mask")
+        return None
+    if head_mask.dtype != torch.int64 or not head_mask.is_contiguous() or head_mask.numel() != n_rows:
+        raise _lib.B200DSAError("head_mask must be contiguous int64 [n_rows]")
+    if out_gated is None:
+        out_gated = torch.full_like(out, NEG_INF) if fill else torch.empty_like(out)
+    if out_gated.dtype != torch.float32 or out_gated.shape != out.shape or out_gated.stride() != out.stride():
+        raise _lib.B200DSAError("out_gated must have the shape and strides of the logits")
+    return out_gated
+
+
+def head_mask_from_indices(head_idx: torch.Tensor) -> torch.Tensor:
+    """int64 [n_rows] bit masks (bit h = head h) from kept-head indices [n_rows, n_keep]."""
+    keep = torch.zeros(head_idx.shape[0], 64, dtype=torch.bool, device=head_idx.device)
+    keep.scatter_(1, head_idx.long(), True)
+    bits = torch.bitwise_left_shift(keep.long(), torch.arange(64, device=head_idx.device))
+    return bits.sum(dim=1)                      # distinct bits: the wrap-around of bit 63 is the bit pattern
 
 
 def indexer_blocklist_bf16_logits(q: torch.Tensor, weights: torch.Tensor, keys: torch.Tensor,
                                   block_list: torch.Tensor, row_cols: torch.Tensor, *,
                                   pos_lo: Optional[torch.Tensor] = None, pos_hi: Optional[torch.Tensor] = None,
-                                  out_scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                                  out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
+                                  head_mask: Optional[torch.Tensor] = None,
+                                  out_gated: Optional[torch.Tensor] = None):
     """Token logits [n_rows, 128*list_len] inside per-row lists of 128-key blocks; see
-    b200dsa_indexer_blocklist_bf16_logits."""
-    require_cuda(q, weights, keys, block_list, row_cols, pos_lo, pos_hi)
+    b200dsa_indexer_blocklist_bf16_logits.  head_mask: as for indexer_paged_fp8_logits."""
+    require_cuda(q, weights, keys, block_list, row_cols, pos_lo, pos_hi, head_mask, out_gated)
     if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.shape[-2:] != (64, 128):
         raise _lib.B200DSAError("q must be contiguous bf16 [n_rows, 64, 128]")
     if keys.dtype != torch.bfloat16 or not keys.is_contiguous() or keys.shape[-1] != 128:
@@ -185,13 +213,14 @@ def indexer_blocklist_bf16_logits(q: torch.Tensor, weights: torch.Tensor, keys: 
     max_cols = block_list.shape[1] * 128
     if out is None:
         out = torch.full((n_rows, max_cols), NEG_INF, dtype=torch.float32, device=q.device)
+    out_gated = _gated_output(head_mask, out_gated, out, n_rows)
     lib = _lib.load()
     rc = lib.b200dsa_indexer_blocklist_bf16_logits(
         ptr(q), ptr(weights), ptr(keys), keys.shape[0], ptr(block_list), block_list.stride(0),
         ptr(row_cols), ptr(_i32(pos_lo, "pos_lo")), ptr(_i32(pos_hi, "pos_hi")), n_rows, max_cols, out_scale,
-        ptr(out), out.stride(0), ptr(status_word(q.device)), stream_ptr())
+        ptr(out), out.stride(0), ptr(head_mask), ptr(out_gated), ptr(status_word(q.device)), stream_ptr())
     check(rc, "b200dsa_indexer_blocklist_bf16_logits")
-    return out
+    return out if head_mask is None else (out, out_gated)
 
 
 def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: float, *,

@@ -6,10 +6,11 @@ Same names, arguments and tuple returns as the reference's orchestration functio
     misa_mqa_logits       MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/misa_ops.py:653-713
     misa_page_mqa_logits  MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/misa_ops.py:344-413
 
-Head gating is applied through the weight operand of the 64-head tensor-core kernels (a zero
-weight removes a head from the sum exactly), so one kernel serves the routed and the dense
-pass.  The decode path reads the FP8 cache in place (the reference dequantises the whole
-cache to bf16 first, misa_ops.py:360-378).  Weights stay fp32 (the reference rounds them to
+Head gating is a zero weight on the dropped heads (it removes a head from the sum exactly).
+The 64-head tensor-core kernels take the kept heads as a bit mask and write, in ONE pass over
+the keys, both the routed stage-1 score and the all-head score that the reference computes in
+a second pass over the candidates; stage 2 is then a gather.  The decode path reads the FP8
+cache in place (the reference dequantises the whole cache to bf16 first, misa_ops.py:360-378).  Weights stay fp32 (the reference rounds them to
 bf16 at :690); scores therefore follow the fp32-weight oracle.
 
 Routers: q-norm (misa_deepseek_v2.py:254-266), block-score (block_ops.py:11-98, :488-573) and a
@@ -73,19 +74,19 @@ def misa_mqa_logits(q: torch.Tensor, kv: Tuple[torch.Tensor, torch.Tensor], weig
     if use_qnorm:
         if q_head_topk_indices is None:
             raise B200DSAError("use_qnorm needs q_head_topk_indices")
-        w_gate = gate_weights_by_heads(w, q_head_topk_indices[:, :topk_heads])
+        head_idx = q_head_topk_indices[:, :topk_heads]
     else:
         if k_block_size is None:
             raise B200DSAError("k_block_size must be provided for the block-score router")
         _, pooled = K.block_mean_pool(k, k_block_size, want_f32=True)
         pooled = pooled.to(torch.bfloat16).float().contiguous()            # the reference pools to bf16
-        w_gate, _ = K.router_block_score_topk(qb, w, pooled, (ks // k_block_size).contiguous(),
-                                              ((ke + k_block_size - 1) // k_block_size).contiguous(), topk_heads)
+        _, head_idx = K.router_block_score_topk(qb, w, pooled, (ks // k_block_size).contiguous(),
+                                                ((ke + k_block_size - 1) // k_block_size).contiguous(), topk_heads)
     bl, row_cols = identity_block_lists(ks.long(), ke.long(), N)
     s1 = min(stage1_topk, N)
-    stage1 = K.indexer_blocklist_bf16_logits(qb, w_gate, k, bl, row_cols, pos_lo=ks, pos_hi=ke)
+    full, stage1 = K.indexer_blocklist_bf16_logits(qb, w, k, bl, row_cols, pos_lo=ks, pos_hi=ke,
+                                                   head_mask=K.head_mask_from_indices(head_idx))
     cand = K.topk_select(stage1, s1, col_end=row_cols, page_table=bl, page_size=128, sorted=False)
-    full = K.indexer_blocklist_bf16_logits(qb, w, k, bl, row_cols, pos_lo=ks, pos_hi=ke, out=stage1)
     # candidate positions -> columns of `full` (column = position - 128*first block of the row)
     col0 = ((ks // 128) * 128).view(-1, 1)
     cols = (cand - col0).clamp(min=0).long()
@@ -118,7 +119,7 @@ def misa_page_mqa_logits(q_fp8: torch.Tensor, kv_cache_fp8: torch.Tensor, weight
     if use_qnorm:
         if q_head_topk_indices is None:
             raise B200DSAError("use_qnorm needs q_head_topk_indices")
-        w_gate = gate_weights_by_heads(w, q_head_topk_indices.reshape(rows, -1)[:, :decode_topk_heads])
+        head_idx = q_head_topk_indices.reshape(rows, -1)[:, :decode_topk_heads]
     else:
         if k_block_size is None:
             raise B200DSAError("k_block_size must be provided for the block-score router")
@@ -127,15 +128,15 @@ def misa_page_mqa_logits(q_fp8: torch.Tensor, kv_cache_fp8: torch.Tensor, weight
         n_pool = ((row_ctx + k_block_size - 1) // k_block_size).to(torch.int32).contiguous()
         req = torch.arange(rows, device=ctx.device, dtype=torch.int32) // next_n
         qb = q_fp8.to(torch.bfloat16).reshape(rows, 64, 128).contiguous()
-        w_gate, _ = K.router_block_score_topk(qb, w, pooled, torch.zeros_like(n_pool), n_pool, decode_topk_heads,
-                                              pooled_set=req.contiguous())
+        _, head_idx = K.router_block_score_topk(qb, w, pooled, torch.zeros_like(n_pool), n_pool, decode_topk_heads,
+                                                pooled_set=req.contiguous())
     q2 = q_fp8.reshape(rows, 64, 128).contiguous()
     s1 = min(stage1_topk, max_model_len)
-    stage1 = K.indexer_paged_fp8_logits(q2, w_gate, cache, page_size, row_ctx, tables, next_n=next_n,
-                                        max_cols=max_model_len)
+    # columns beyond a row's context are never read below (col_end / valid candidates only): no fill
+    full, stage1 = K.indexer_paged_fp8_logits(q2, w, cache, page_size, row_ctx, tables, next_n=next_n,
+                                              max_cols=max_model_len, fill=False,
+                                              head_mask=K.head_mask_from_indices(head_idx))
     cand = K.topk_select(stage1, s1, col_end=row_ctx, sorted=False)
-    full = K.indexer_paged_fp8_logits(q2, w, cache, page_size, row_ctx, tables, next_n=next_n,
-                                      max_cols=max_model_len, out=stage1)
     logits = torch.gather(full, 1, cand.clamp(min=0).long())
     logits = torch.where(cand >= 0, logits, torch.full_like(logits, float("-inf")))
     return logits, cand
@@ -160,5 +161,10 @@ def misa_linear_router_decode(x: torch.Tensor, w_r: torch.Tensor, q_fp8: torch.T
     weights = (gate * q_scale_fold).contiguous()
     logits = K.indexer_paged_fp8_logits(q_fp8, weights, cache, page_size, context_lens, block_table,
                                         max_cols=max_cols, fill=False)
-    idx = K.topk_select(logits, topk, col_end=context_lens, sorted=True)
+    if logits.shape[0] <= 148 and logits.shape[1] >= 32768 and topk <= 4096:
+        # few long rows: several CTAs per row
+        idx = K.topk_select_split(logits, topk, K.topk_scratch(logits.shape[0], logits.device),
+                                  col_end=context_lens, sorted=True)
+    else:
+        idx = K.topk_select(logits, topk, col_end=context_lens, sorted=True)
     return idx, head_idx

@@ -226,7 +226,10 @@ class BaselineSparseAttnIndexer(MiSASparseAttnIndexer):
 
 def register() -> None:
     """Register the hook as a torch custom op named like the reference's
-    (indexers.py:607-613: mutates topk_indices_buffer, with a fake implementation for tracing)."""
+    (indexers.py:607-613: mutates topk_indices_buffer, with a fake implementation for tracing).
+    Calling it again is a no-op."""
+    if getattr(register, "_lib", None) is not None:
+        return
     lib = torch.library.Library("b200dsa", "FRAGMENT")
     lib.define("misa_sparse_attn_indexer(Tensor hidden_states, str k_cache_prefix, Tensor kv_cache, Tensor q_fp8, "
                "Tensor k, Tensor weights, Tensor? q_head_topk_indices, int quant_block_size, str? scale_fmt, "
