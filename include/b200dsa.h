@@ -199,6 +199,39 @@ int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16, int64_t k
 int b200dsa_lse_combine(const float* ctx_parts, const float* lse_parts, int32_t n_parts, int64_t n_rows,
                         float* ctx_out, float* lse_out, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * The same merge across the GPUs of one node in ONE kernel over NVLink peer memory (replaces
+ * the all-gather of lse + all-reduce of the scaled partials).  No counterpart in the reference
+ * (its context-parallel path gathers keys instead, OpenDSA/opendsa/modeling/dsa_attention.py:650-669).
+ *
+ * Every rank owns an exchange buffer of identical layout, mapped into every rank's address space
+ * (b200dsa_peer_alloc / b200dsa_peer_open); bufs is a HOST array of the `world` device pointers
+ * as seen from the calling process (bufs[rank] = its own buffer).  Byte offsets inside a buffer:
+ *   off_ctx      bf16 [n_rows, 512]  this rank's normalised partial (written before the call)
+ *   off_lse      fp32 [n_rows]       its log-sum-exp (-inf for an empty partial)
+ *   off_out      bf16 [n_rows, 512]  merged result, complete on every rank when the kernel ends
+ *   off_lse_out  fp32 [n_rows]
+ *   off_flags    256 bytes of flags, zero before the first call and never touched by the host
+ * state: two int32 of LOCAL device memory, zero before the first call (the step counter lives
+ * there, so a captured launch can be replayed).  All ranks must make the same sequence of calls.
+ * Waits for peers are bounded (about half a second): on expiry *status gets 1 and the call
+ * completes with an unusable result instead of hanging.  no_sync != 0 skips the flag exchange:
+ * ranks emulated one after another on a single GPU (tests); ranks that wait for each other
+ * must run on different GPUs.  1 <= world <= 8.
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_peer_lse_combine(void* const* bufs, int32_t rank, int32_t world, int64_t n_rows,
+                             int64_t off_ctx, int64_t off_lse, int64_t off_out, int64_t off_lse_out,
+                             int64_t off_flags, int32_t* state, int32_t no_sync, int32_t* status,
+                             void* stream);
+
+/* Exchange buffers.  peer_alloc: zeroed device allocation on the current device plus the 64-byte
+ * CUDA IPC handle another process passes to peer_open (with ITS device current) to map it;
+ * peer_close unmaps, peer_free releases the allocation in the owning process. */
+int b200dsa_peer_alloc(int64_t bytes, void** ptr, unsigned char* handle64);
+int b200dsa_peer_open(const unsigned char* handle64, void** ptr);
+int b200dsa_peer_close(void* ptr);
+int b200dsa_peer_free(void* ptr);
+
 /* Shard ownership compaction: per row, the positions inside [pos_lo, pos_hi) are moved to the
  * front of out (relative order kept), the rest of the row is -1, count[row] = how many.  Lets a
  * rank attend only the selected keys it owns.  out must not alias indices. */

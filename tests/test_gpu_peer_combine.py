@@ -1,0 +1,116 @@
+"""The one-kernel peer-memory merge of attention partials.
+
+On one GPU the ranks are emulated one after another without the flag exchange (kernels that wait
+for each other must not share a GPU); with two or more GPUs the real exchange runs as one process
+per GPU."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _partials(world, n_rows, seed):
+    g = torch.Generator().manual_seed(seed)
+    ctx = torch.randn(world, n_rows, 512, generator=g).bfloat16()
+    lse = 3.0 * torch.randn(world, n_rows, generator=g)
+    lse[0, 1] = float("-inf")                      # one empty partial
+    lse[:, 2] = float("-inf")                      # a row that is empty on every rank
+    if world > 1:
+        lse[1, 3] = 40.0                           # one rank dominates
+    return ctx, lse
+
+
+def _expected(ctx, lse):
+    m = lse.max(dim=0).values
+    w = torch.where(torch.isinf(lse), torch.zeros_like(lse), torch.exp(lse - torch.where(torch.isinf(m), torch.zeros_like(m), m)))
+    den = w.sum(0)
+    out = (w.unsqueeze(-1) * ctx.float()).sum(0) / den.clamp_min(1e-38).unsqueeze(-1)
+    out = torch.where(den.unsqueeze(-1) > 0, out, torch.zeros_like(out))
+    lse_out = torch.where(den > 0, m + torch.log(den.clamp_min(1e-38)), torch.full_like(m, float("-inf")))
+    return out, lse_out
+
+
+@pytest.mark.parametrize("world,n_rows", [(4, 1000), (2, 8192), (8, 37), (1, 64)])
+def test_emulated_ranks_one_after_another(world, n_rows):
+    from transarch_b200 import _lib
+    from transarch_b200.peer import PeerLseCombine
+    dev = torch.device("cuda")
+    pc = PeerLseCombine(n_rows, dev, emulate_world=world)
+    try:
+        for step in range(2):                                   # the step counter advances by itself
+            ctx, lse = _partials(world, n_rows, 7 + step)
+            for r in range(world):
+                c, l, o, lo = pc.views_of(r)
+                c.copy_(ctx[r]); l.copy_(lse[r]); o.fill_(7.0); lo.fill_(7.0)
+            for r in range(world):
+                pc.run(rank=r, no_sync=True)
+            torch.cuda.synchronize()
+            want, want_lse = _expected(ctx, lse)
+            for r in range(world):
+                _, _, o, lo = pc.views_of(r)
+                assert torch.allclose(o.float().cpu(), want, rtol=1e-2, atol=1e-2)
+                assert torch.allclose(lo.cpu(), want_lse, rtol=1e-5, atol=1e-5)
+                assert (o[2] == 0).all()
+            assert [int(s[0]) for s in pc.state] == [step + 1] * world
+        assert _lib.read_status(dev) == 0
+    finally:
+        pc.close()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, ret):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from transarch_b200 import _lib
+        from transarch_b200.peer import PeerLseCombine
+        n_rows = 8192
+        pc = PeerLseCombine(n_rows, dev)
+        ok = True
+        for step in range(3):
+            ctx, lse = _partials(world, n_rows, 21 + step)
+            pc.ctx.copy_(ctx[rank]); pc.lse.copy_(lse[rank])
+            out, lse_out = pc.run()
+            torch.cuda.synchronize()
+            want, want_lse = _expected(ctx, lse)
+            ok = ok and torch.allclose(out.float().cpu(), want, rtol=1e-2, atol=1e-2) and \
+                torch.allclose(lse_out.cpu(), want_lse, rtol=1e-5, atol=1e-5)
+        ok = ok and _lib.read_status(dev) == 0
+        dist.barrier()
+        pc.close()
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpus_exchange_over_peer_memory():
+    import torch.multiprocessing as mp
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=180)
+    stuck = [p for p in procs if p.is_alive()]
+    for p in stuck:
+        p.kill()
+    assert not stuck, "a rank did not finish"
+    assert ret.get(0) is True and ret.get(1) is True

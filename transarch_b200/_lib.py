@@ -34,6 +34,11 @@ SIGNATURES = {
     "b200dsa_sparse_mla_decode": [_vp, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _f32,
                                   _vp, _i32, _vp, _vp, _vp],
     "b200dsa_lse_combine": [_vp, _vp, _i32, _i64, _vp, _vp, _vp],
+    "b200dsa_peer_lse_combine": [_vp, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _i32, _vp, _vp],
+    "b200dsa_peer_alloc": [_i64, _vp, _vp],
+    "b200dsa_peer_open": [_vp, _vp],
+    "b200dsa_peer_close": [_vp],
+    "b200dsa_peer_free": [_vp],
     "b200dsa_lse_prescale": [_vp, _vp, _vp, _i64, _vp, _vp],
     "b200dsa_lse_finalize": [_vp, _vp, _i64, _vp, _vp, _vp],
     "b200dsa_lse_prescale_norm": [_vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp],

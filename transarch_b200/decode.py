@@ -66,7 +66,8 @@ class SparseDecodeStep:
     def __init__(self, batch: int, max_local_ctx: int, *, page_size: int = 64, topk: int = 2048,
                  n_heads: int = 128, index_scale: float = 128 ** -0.5, attn_scale: float = 192 ** -0.5,
                  device: Optional[torch.device] = None, shard: Optional[ShardInfo] = None, backend=None,
-                 sorted_topk: bool = False, wire: str = "bf16", ctx_dtype: torch.dtype = torch.float32):
+                 sorted_topk: bool = False, wire: str = "bf16", ctx_dtype: torch.dtype = torch.float32,
+                 combine: str = "auto"):
         if backend is None:
             from . import kernels as backend  # the CUDA kernels; fails loudly without the library
         self.K = backend
@@ -77,6 +78,8 @@ class SparseDecodeStep:
         if wire not in ("bf16", "fp32"):
             raise ValueError("wire must be 'bf16' or 'fp32'")
         self.wire_mode = wire if hasattr(backend, "lse_prescale_norm") else "fp32"
+        if combine not in ("auto", "peer", "nccl"):
+            raise ValueError("combine must be 'auto', 'peer' or 'nccl'")
         dev = device if device is not None else torch.device("cuda")
         self.dev = dev
         f32, i32 = torch.float32, torch.int32
@@ -97,6 +100,16 @@ class SparseDecodeStep:
         self.topk_scratch = None
         if hasattr(backend, "topk_scratch") and batch <= 148 and max_local_ctx >= 32768:
             self.topk_scratch = backend.topk_scratch(batch, dev)
+        self.peer = None
+        if combine == "peer" and not (n > 1 and dist.is_initialized()):
+            raise ValueError("combine='peer' needs an initialised process group of more than one rank")
+        if n > 1 and combine != "nccl" and dev.type == "cuda" and dist.is_initialized() and \
+                getattr(backend, "__name__", "").endswith(".kernels"):
+            self.peer = self._open_peer_combine(batch * n_heads, dev, combine == "peer")
+        if self.peer is not None:
+            # attention writes its normalised bf16 partial straight into the exchange buffer
+            self.ctx = self.peer.ctx.view(batch, n_heads, 512)
+            self.lse = self.peer.lse.view(batch, n_heads)
         if n > 1:
             self.cand_all = torch.empty(n, batch, 2 * topk, dtype=i32, device=dev)
             self.merged = torch.empty(batch, topk, dtype=i32, device=dev)
@@ -104,12 +117,35 @@ class SparseDecodeStep:
             self.owned_count = torch.empty(batch, dtype=i32, device=dev)
             self.lse_max = torch.empty(batch, n_heads, dtype=f32, device=dev)
             self.lse_out = torch.empty(batch, n_heads, dtype=f32, device=dev)
-            if self.wire_mode == "bf16":
+            if self.peer is not None:
+                pass
+            elif self.wire_mode == "bf16":
                 self.lse_all = torch.empty(n, batch, n_heads, dtype=f32, device=dev)
                 self.ctx_bf16 = torch.empty(batch, n_heads, 512, dtype=torch.bfloat16, device=dev)
             else:
                 self.wire_rows = torch.empty(batch * n_heads, backend.WIRE_ROW, dtype=f32, device=dev)
                 self.ctx_out = torch.empty(batch, n_heads, 512, dtype=f32, device=dev)
+
+    def _open_peer_combine(self, n_rows: int, dev, required: bool):
+        """Map the exchange buffers of all ranks (they must share a node).  Every rank learns
+        whether all succeeded, so that the group takes the same path."""
+        from .peer import PeerLseCombine
+        peer, err = None, None
+        try:
+            peer = PeerLseCombine(n_rows, dev, self.shard.group)
+        except Exception as e:                                   # noqa: BLE001 - reported below
+            err = e
+        ok = torch.tensor([0 if peer is None else 1], dtype=torch.int32, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.shard.group)
+        if int(ok.item()) == 1:
+            return peer
+        if peer is not None:
+            peer.close()
+        if required:
+            raise RuntimeError(f"peer-memory combine is not available on every rank: {err}")
+        import warnings
+        warnings.warn(f"peer-memory combine unavailable ({err}); merging through NCCL")
+        return None
 
     # ------------------------------------------------------------------ stages
     def select(self, q_idx, w, k_cache, context_lens_local, block_table) -> torch.Tensor:
@@ -155,6 +191,11 @@ class SparseDecodeStep:
     def combine(self) -> Tuple[torch.Tensor, torch.Tensor]:
         """Merge the per-rank (ctx, lse) partials; every rank ends with the full result."""
         K, g = self.K, self.shard.group
+        if self.peer is not None:
+            # one kernel: flags, peer loads of all partials of the rows this rank owns, merged rows
+            # stored to every rank
+            out, lse_out = self.peer.run()
+            return out.view(self.B, self.H, 512), lse_out.view(self.B, self.H)
         if self.wire_mode == "bf16":
             # gather the lse of every rank (4 B per row and rank): each rank then knows the common
             # maximum and the exact denominator and sends its normalised bf16 share; the summed

@@ -1,0 +1,135 @@
+"""Exchange buffers shared by the GPUs of one node, and the one-kernel attention-partial merge
+that runs over them (NVLink peer loads and stores instead of NCCL calls).
+
+Each rank allocates one buffer of a common layout; the 64-byte CUDA IPC handles travel through
+the process group once at start-up and every rank maps every peer's buffer.  After that the data
+path makes no library call: kernels read and write peer memory directly.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .kernels import check, ptr, status_word, stream_ptr
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class _Span:
+    """Device memory owned elsewhere, exposed to torch through the CUDA array interface."""
+
+    def __init__(self, address: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (address, False),
+                                         "version": 3, "strides": None}
+
+
+class PeerBuffers:
+    """One zeroed device buffer of `nbytes` per rank, mapped into every rank of `group`.
+
+    local            uint8 tensor over this rank's buffer
+    addresses[r]     device address of rank r's buffer in THIS process
+    With emulate_world=n (single process, tests) the n buffers are n local allocations.
+    """
+
+    def __init__(self, nbytes: int, device: torch.device, group=None, emulate_world: Optional[int] = None):
+        lib = _lib.load()
+        self.device = torch.device(device)
+        self.nbytes = _align(nbytes)
+        self._owned: List[int] = []
+        self._opened: List[int] = []
+        with torch.cuda.device(self.device):
+            if emulate_world is not None:
+                self.rank, self.world = 0, emulate_world
+                self.addresses = [self._alloc(lib)[0] for _ in range(emulate_world)]
+            else:
+                self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+                mine, handle = self._alloc(lib)
+                # the handles are 64 opaque bytes: gather them as a tensor on the group's own backend
+                h = torch.tensor(list(handle), dtype=torch.uint8, device=self.device)
+                gathered = torch.empty(self.world, 64, dtype=torch.uint8, device=self.device)
+                dist.all_gather_into_tensor(gathered.view(-1), h, group=group)
+                gathered = gathered.cpu()
+                self.addresses = []
+                for r in range(self.world):
+                    if r == self.rank:
+                        self.addresses.append(mine)
+                        continue
+                    raw = (ctypes.c_ubyte * 64)(*gathered[r].tolist())
+                    out = ctypes.c_void_p()
+                    check(lib.b200dsa_peer_open(raw, ctypes.byref(out)), "b200dsa_peer_open")
+                    self._opened.append(out.value)
+                    self.addresses.append(out.value)
+                dist.barrier(group=group)
+        self.views = [torch.as_tensor(_Span(a, self.nbytes), device=self.device) for a in self.addresses]
+        self.local = self.views[self.rank]
+        self._addr_array = (ctypes.c_void_p * self.world)(*self.addresses)
+
+    def _alloc(self, lib):
+        out = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        check(lib.b200dsa_peer_alloc(self.nbytes, ctypes.byref(out), handle), "b200dsa_peer_alloc")
+        self._owned.append(out.value)
+        return out.value, bytes(handle)
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's own (call on every rank, after a barrier)."""
+        lib = _lib.load()
+        self.views, self.local = [], None
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for a in self._opened:
+                lib.b200dsa_peer_close(ctypes.c_void_p(a))
+            for a in self._owned:
+                lib.b200dsa_peer_free(ctypes.c_void_p(a))
+        self._opened, self._owned = [], []
+
+
+class PeerLseCombine:
+    """Merge of key-sharded attention partials in one kernel over peer memory; see
+    b200dsa_peer_lse_combine.  The attention kernel writes straight into `ctx` / `lse` (views of
+    this rank's exchange buffer); after run() `out` / `lse_out` hold the merged result on every rank."""
+
+    def __init__(self, n_rows: int, device: torch.device, group=None, emulate_world: Optional[int] = None):
+        self.n_rows = n_rows
+        self.off_ctx = 0
+        self.off_lse = _align(n_rows * 512 * 2)
+        self.off_out = self.off_lse + _align(n_rows * 4)
+        self.off_lse_out = self.off_out + _align(n_rows * 512 * 2)
+        self.off_flags = self.off_lse_out + _align(n_rows * 4)
+        self.buffers = PeerBuffers(self.off_flags + 256, device, group, emulate_world)
+        self.rank, self.world = self.buffers.rank, self.buffers.world
+        self.state = [torch.zeros(2, dtype=torch.int32, device=device) for _ in range(emulate_world or 1)]
+        v = self.views_of(self.rank)
+        self.ctx, self.lse, self.out, self.lse_out = v
+
+    def views_of(self, r: int):
+        """(ctx bf16 [n,512], lse fp32 [n], out bf16 [n,512], lse_out fp32 [n]) inside rank r's buffer."""
+        b, n = self.buffers.views[r], self.n_rows
+        return (b[self.off_ctx:self.off_ctx + n * 1024].view(torch.bfloat16).view(n, 512),
+                b[self.off_lse:self.off_lse + n * 4].view(torch.float32),
+                b[self.off_out:self.off_out + n * 1024].view(torch.bfloat16).view(n, 512),
+                b[self.off_lse_out:self.off_lse_out + n * 4].view(torch.float32))
+
+    def run(self, rank: Optional[int] = None, no_sync: bool = False):
+        """Launch on the current stream.  `rank` / no_sync are for single-GPU emulation only: there the
+        ranks run one after another and must not wait for each other."""
+        r = self.rank if rank is None else rank
+        if self.buffers.world > 1 and rank is not None and not no_sync:
+            raise _lib.B200DSAError("emulated ranks on one GPU must run with no_sync")
+        state = self.state[r if len(self.state) > 1 else 0]
+        rc = _lib.load().b200dsa_peer_lse_combine(
+            self.buffers._addr_array, r, self.world, self.n_rows, self.off_ctx, self.off_lse, self.off_out,
+            self.off_lse_out, self.off_flags, ptr(state), int(no_sync), ptr(status_word(self.buffers.device)),
+            stream_ptr())
+        check(rc, "b200dsa_peer_lse_combine")
+        return self.out, self.lse_out
+
+    def close(self) -> None:
+        self.ctx = self.lse = self.out = self.lse_out = None
+        self.buffers.close()
