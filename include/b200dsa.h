@@ -56,6 +56,10 @@ const char* b200dsa_last_error(void);
  * (c / seg_cols) * seg_stride + c % seg_cols from the row start, in scores and in pos_map
  * alike.  This reads the [n_ranks, n_rows, seg] layout an all-gather of per-shard candidates
  * produces without a transpose (row_stride = distance between rows inside one segment).
+ * seg_offsets (optional HOST array, one entry per segment, at most 8): segment r starts
+ * seg_offsets[r] elements from `scores` (and from `pos_map`) instead of r * seg_stride.  The
+ * segments may then be separate buffers, for example the candidate buffers of peer GPUs mapped
+ * into this process, read in place over NVLink (after b200dsa_peer_barrier).
  *
  * Limits: 1 <= k <= 8192.  scores rows need 4-byte alignment only.
  * ------------------------------------------------------------------------------------- */
@@ -65,7 +69,7 @@ int b200dsa_topk_select(const float* scores, int64_t row_stride, int32_t n_rows,
                         const int32_t* pos_map, int64_t pos_map_stride,
                         const int32_t* page_table, int64_t page_table_stride, int32_t page_size,
                         const int32_t* row_pos_offset,
-                        int32_t seg_cols, int64_t seg_stride,
+                        int32_t seg_cols, int64_t seg_stride, const int64_t* seg_offsets,
                         int32_t* out_idx, float* out_val, int64_t out_stride,
                         void* stream);
 
@@ -223,6 +227,14 @@ int b200dsa_peer_lse_combine(void* const* bufs, int32_t rank, int32_t world, int
                              int64_t off_ctx, int64_t off_lse, int64_t off_out, int64_t off_lse_out,
                              int64_t off_flags, int32_t* state, int32_t no_sync, int32_t* status,
                              void* stream);
+
+/* Node-wide barrier on the stream: one small kernel writes this rank's step number into every
+ * peer's flag word `slot*8 + rank` (uint32 words at off_flags; slots 0 and 2 belong to
+ * b200dsa_peer_lse_combine, use 1 or 3..7) and waits, bounded, until all peers' words reached the same
+ * step.  state: one int32 of local device memory per slot user, zero before the first call.  What
+ * the peers wrote to their own buffers before their barrier call is readable afterwards. */
+int b200dsa_peer_barrier(void* const* bufs, int32_t rank, int32_t world, int64_t off_flags, int32_t slot,
+                         int32_t* state, int32_t* status, void* stream);
 
 /* Exchange buffers.  peer_alloc: zeroed device allocation on the current device plus the 64-byte
  * CUDA IPC handle another process passes to peer_open (with ITS device current) to map it;

@@ -28,6 +28,6 @@ def test_library_builds_and_exports_header_symbols():
 def test_argument_validation_rejects_without_launching():
     lib = _lib.load()
     # k out of range -> EINVAL before any CUDA call
-    rc = lib.b200dsa_topk_select(1, 8, 1, 8, None, None, 0, 0, 1, None, 0, None, 0, 0, None, 0, 0, 1, None, 8, None)
+    rc = lib.b200dsa_topk_select(1, 8, 1, 8, None, None, 0, 0, 1, None, 0, None, 0, 0, None, 0, 0, None, 1, None, 8, None)
     assert rc == -1
     assert b"topk_select" in lib.b200dsa_last_error()

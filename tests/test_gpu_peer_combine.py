@@ -66,6 +66,39 @@ def _free_port():
         return s.getsockname()[1]
 
 
+def _sharded_step_agrees(rank, world, dev):
+    """The whole key-sharded step with the exchanges in peer memory against the same step through
+    NCCL: identical selection, same context up to bf16 rounding."""
+    from transarch_b200 import _lib
+    from transarch_b200.decode import ShardInfo, SparseDecodeStep
+    from transarch_b200.workloads import make_decode_queries, make_decode_state
+    B, ctx_len, topk = 8, 16384, 2048
+    shard_len = ctx_len // world
+    shard = ShardInfo(rank=rank, world_size=world, shard_len=shard_len)
+    st = make_decode_state(B, ctx_len, page_size=64, seed=5, rank=rank, world_size=world, shard_len=shard_len,
+                           device=dev)
+    res = {}
+    for mode in ("peer", "nccl"):
+        step = SparseDecodeStep(B, shard_len, topk=topk, device=dev, shard=shard, sorted_topk=True, combine=mode)
+        assert (step.peer is not None) == (mode == "peer")
+        for i in range(2):                                        # twice: flags and step counters advance
+            q_idx, w, q_lat = make_decode_queries(B, 128, seed=40 + i, device=dev)
+            idx, c, lse = step.run(q_idx, w, q_lat, st.k_cache, st.context_lens, st.block_table, st.kv,
+                                   st.kv_row_base, st.context_lens_local)
+            torch.cuda.synchronize()
+            res[mode, i] = (idx.clone(), c.float().clone(), lse.clone())
+        if step.peer is not None:
+            import torch.distributed as dist
+            dist.barrier()
+            step.peer.close()
+    ok = _lib.read_status(dev) == 0
+    for i in range(2):
+        a, b = res["peer", i], res["nccl", i]
+        ok = ok and torch.equal(a[0], b[0]) and torch.allclose(a[1], b[1], rtol=2e-2, atol=2e-2) and \
+            torch.allclose(a[2], b[2], rtol=1e-4, atol=1e-4)
+    return ok
+
+
 def _rank_main(rank, world, port, ret):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -91,6 +124,7 @@ def _rank_main(rank, world, port, ret):
         ok = ok and _lib.read_status(dev) == 0
         dist.barrier()
         pc.close()
+        ok = ok and _sharded_step_agrees(rank, world, dev)
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()

@@ -163,3 +163,28 @@ def test_topk_split_ties_fall_back():
     out = K.topk_select_split(s, 2048, scratch, splits=4)
     assert torch.equal(out, K.topk_select(s, 2048))
     assert torch.equal(out[0].cpu(), torch.arange(2048, dtype=torch.int32))
+
+
+def test_segments_in_separate_buffers():
+    """seg_offsets: the segments of a row live in unrelated allocations (as the candidate buffers of
+    peer GPUs do); the result equals the top-k of the concatenated rows."""
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(5)
+    rows, k, n_seg = 6, 256, 3
+    bufs = []
+    for r in range(n_seg):
+        pos = torch.stack([torch.randperm(10000, generator=g)[:k] + 10000 * r for _ in range(rows)]).to(torch.int32)
+        sc = torch.randn(rows, k, generator=g)
+        sc[0, :5] = float("-inf")
+        bufs.append(torch.cat([pos, sc.view(torch.int32)], dim=1).cuda().contiguous())   # [rows, 2k]: pos | score bits
+    base = bufs[0].data_ptr()
+    offs = [(b.data_ptr() - base) // 4 for b in bufs]
+    flat = bufs[0].view(-1)
+    out = torch.empty(rows, k, dtype=torch.int32, device="cuda")
+    K.topk_select(flat[k:].view(torch.float32).view(1, -1), k, sorted=True, pos_map=flat.view(1, -1), out=out,
+                  n_cols=n_seg * k, row_stride=2 * k, seg_cols=k, seg_offsets=offs, n_rows=rows, pos_map_stride=2 * k)
+    all_pos = torch.cat([b[:, :k] for b in bufs], dim=1).cpu()
+    all_sc = torch.cat([b[:, k:].view(torch.float32) for b in bufs], dim=1).cpu()
+    for r in range(rows):
+        order = sorted(range(n_seg * k), key=lambda c: (-float(all_sc[r, c]), int(all_pos[r, c])))[:k]
+        assert out[r].cpu().tolist() == [int(all_pos[r, c]) for c in order]

@@ -21,7 +21,7 @@ SIGNATURES = {
     "b200dsa_abi_version": [],
     "b200dsa_last_error": [],
     "b200dsa_topk_select": [_vp, _i64, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _i32, _vp,
-                            _i32, _i64, _vp, _vp, _i64, _vp],
+                            _i32, _i64, _vp, _vp, _vp, _i64, _vp],
     "b200dsa_topk_select_split": [_vp, _i64, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _i32, _vp, _vp,
                                   _vp, _vp, _i64, _vp],
     "b200dsa_topk_select_split_static": [_vp, _i64, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _i32,
@@ -35,6 +35,7 @@ SIGNATURES = {
                                   _vp, _i32, _vp, _vp, _vp],
     "b200dsa_lse_combine": [_vp, _vp, _i32, _i64, _vp, _vp, _vp],
     "b200dsa_peer_lse_combine": [_vp, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _i32, _vp, _vp],
+    "b200dsa_peer_barrier": [_vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp],
     "b200dsa_peer_alloc": [_i64, _vp, _vp],
     "b200dsa_peer_open": [_vp, _vp],
     "b200dsa_peer_close": [_vp],

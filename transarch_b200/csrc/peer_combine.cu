@@ -173,6 +173,20 @@ __global__ void __launch_bounds__(256) peer_lse_combine_kernel(const PeerCombine
   }
 }
 
+// Node-wide barrier as a kernel of its own: flag word slot*8 + r of a buffer is written by rank r.
+__global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerCombineParams p, int slot) {
+  const int tid = threadIdx.x;
+  const uint32_t step = static_cast<uint32_t>(*reinterpret_cast<volatile int32_t*>(p.state)) + 1u;
+  __syncwarp();
+  if (tid < p.world) {
+    st_release_sys(reinterpret_cast<uint32_t*>(p.buf[tid] + p.off_flags) + slot * 8 + p.rank, step);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.buf[p.rank] + p.off_flags) + slot * 8 + tid;
+    if (!wait_step(mine, step)) atomicMax(p.status, kDevWaitTimeout);
+  }
+  __syncwarp();
+  if (tid == 0) p.state[0] = static_cast<int32_t>(step);
+}
+
 void set_last_error(const char* msg);
 
 }  // namespace b200dsa
@@ -213,6 +227,35 @@ extern "C" int b200dsa_peer_lse_combine(void* const* bufs, int32_t rank, int32_t
   if (grid < 1) grid = 1;
   if (grid > 148) grid = 148;          // every block must be resident: the last one waits for peers
   peer_lse_combine_kernel<<<static_cast<int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  return B200DSA_OK;
+}
+
+extern "C" int b200dsa_peer_barrier(void* const* bufs, int32_t rank, int32_t world, int64_t off_flags, int32_t slot,
+                                    int32_t* state, int32_t* status, void* stream) {
+  if (!bufs || !state || !status || world < 1 || world > kPeerMaxRanks || rank < 0 || rank >= world ||
+      off_flags < 0 || (off_flags & 15) || slot < 0 || slot > 7 || slot == 0 || slot == 2) {
+    set_last_error("b200dsa_peer_barrier: bad argument (1 <= world <= 8, slot 1 or 3..7)");
+    return B200DSA_EINVAL;
+  }
+  PeerCombineParams p{};
+  for (int r = 0; r < world; ++r) {
+    if (!bufs[r]) {
+      set_last_error("b200dsa_peer_barrier: every rank's buffer must be mapped");
+      return B200DSA_EINVAL;
+    }
+    p.buf[r] = static_cast<unsigned char*>(bufs[r]);
+  }
+  p.rank = rank;
+  p.world = world;
+  p.off_flags = off_flags;
+  p.state = state;
+  p.status = status;
+  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p, slot);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));

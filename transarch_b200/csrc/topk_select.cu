@@ -50,6 +50,10 @@ struct TopkParams {
   // split mode: candidates pre-collected by topk_collect_kernel into global scratch
   uint64_t* pre_cand;   // [n_rows, kCandCap]
   int32_t* pre_count;   // [n_rows]; > kCandCap means "no usable list, select from the row itself"
+  // segmented rows whose segments are separate buffers (peer GPUs): element offset of segment r
+  // from `scores` / `pos_map` instead of r * seg_stride
+  int32_t seg_off_n;
+  int64_t seg_off[8];
 };
 
 __device__ __forceinline__ bool score_valid(float v, int keep_pos_inf) {
@@ -63,7 +67,7 @@ __device__ __forceinline__ bool score_valid(float v, int keep_pos_inf) {
 __device__ __forceinline__ int64_t col_offset(const TopkParams& p, int col) {
   if (p.seg_cols <= 0) return col;
   const int r = col / p.seg_cols;
-  return r * p.seg_stride + (col - r * p.seg_cols);
+  return (p.seg_off_n > 0 ? p.seg_off[r] : r * p.seg_stride) + (col - r * p.seg_cols);
 }
 
 __device__ __forceinline__ int32_t out_position(const TopkParams& p, int row, int col) {
@@ -617,8 +621,8 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
                                    int32_t keep_pos_inf, int32_t sorted, const int32_t* pos_map,
                                    int64_t pos_map_stride, const int32_t* page_table, int64_t page_table_stride,
                                    int32_t page_size, const int32_t* row_pos_offset, int32_t seg_cols,
-                                   int64_t seg_stride, int32_t* out_idx, float* out_val, int64_t out_stride,
-                                   void* stream) {
+                                   int64_t seg_stride, const int64_t* seg_offsets, int32_t* out_idx,
+                                   float* out_val, int64_t out_stride, void* stream) {
   if (n_rows == 0) return B200DSA_OK;
   if (!scores || !out_idx || n_rows < 0 || n_cols < 0 || k < 1 || k > kCandCap || out_stride < k ||
       (seg_cols <= 0 && row_stride < n_cols) || seg_cols < 0) {
@@ -632,6 +636,15 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
   TopkParams p{scores, row_stride, n_rows, n_cols, col_begin, col_end, k, keep_pos_inf, pos_map, pos_map_stride,
                page_table, page_table_stride, page_size, row_pos_offset, out_idx, out_val, out_stride, sorted,
                seg_cols, seg_stride};
+  if (seg_offsets) {
+    const int n_seg = seg_cols > 0 ? (n_cols + seg_cols - 1) / seg_cols : 0;
+    if (n_seg < 1 || n_seg > 8) {
+      set_last_error("b200dsa_topk_select: seg_offsets needs seg_cols > 0 and at most 8 segments");
+      return B200DSA_EINVAL;
+    }
+    p.seg_off_n = n_seg;
+    for (int r = 0; r < n_seg; ++r) p.seg_off[r] = seg_offsets[r];
+  }
   int k_pow2 = 32;
   while (k_pow2 < k) k_pow2 <<= 1;
   const size_t smem = kHistBins * sizeof(uint32_t) + (kCandCap + kEqCap + k_pow2) * sizeof(uint64_t);

@@ -105,11 +105,14 @@ class SparseDecodeStep:
             raise ValueError("combine='peer' needs an initialised process group of more than one rank")
         if n > 1 and combine != "nccl" and dev.type == "cuda" and dist.is_initialized() and \
                 getattr(backend, "__name__", "").endswith(".kernels"):
-            self.peer = self._open_peer_combine(batch * n_heads, dev, combine == "peer")
+            self.peer = self._open_peer_combine(batch * n_heads, dev, combine == "peer", batch * 2 * topk * 4)
         if self.peer is not None:
-            # attention writes its normalised bf16 partial straight into the exchange buffer
+            # attention writes its normalised bf16 partial straight into the exchange buffer, the local
+            # top-k its (position, score) candidates: peers read both in place over NVLink
             self.ctx = self.peer.ctx.view(batch, n_heads, 512)
             self.lse = self.peer.lse.view(batch, n_heads)
+            self.cand = self.peer.extra_of(self.peer.rank).view(i32).view(batch, 2 * topk)
+            self.seg_offsets = self.peer.element_offsets(4)
         if n > 1:
             self.cand_all = torch.empty(n, batch, 2 * topk, dtype=i32, device=dev)
             self.merged = torch.empty(batch, topk, dtype=i32, device=dev)
@@ -126,13 +129,13 @@ class SparseDecodeStep:
                 self.wire_rows = torch.empty(batch * n_heads, backend.WIRE_ROW, dtype=f32, device=dev)
                 self.ctx_out = torch.empty(batch, n_heads, 512, dtype=f32, device=dev)
 
-    def _open_peer_combine(self, n_rows: int, dev, required: bool):
+    def _open_peer_combine(self, n_rows: int, dev, required: bool, extra_bytes: int):
         """Map the exchange buffers of all ranks (they must share a node).  Every rank learns
         whether all succeeded, so that the group takes the same path."""
         from .peer import PeerLseCombine
         peer, err = None, None
         try:
-            peer = PeerLseCombine(n_rows, dev, self.shard.group)
+            peer = PeerLseCombine(n_rows, dev, self.shard.group, extra_bytes=extra_bytes)
         except Exception as e:                                   # noqa: BLE001 - reported below
             err = e
         ok = torch.tensor([0 if peer is None else 1], dtype=torch.int32, device=dev)
@@ -168,6 +171,14 @@ class SparseDecodeStep:
     def merge_candidates(self) -> torch.Tensor:
         """All-gather the per-rank candidates and select the global top-k (identical on every rank)."""
         n, k = self.shard.world_size, self.topk
+        if self.peer is not None:
+            # no gather: after a node-wide barrier the merge reads every rank's candidates where they lie
+            self.peer.barrier(slot=1)
+            flat = self.cand.view(-1)
+            self.K.topk_select(flat[k:].view(torch.float32).view(1, -1), k, sorted=self.sorted_topk,
+                               pos_map=flat.view(1, -1), out=self.merged, n_cols=n * k, row_stride=2 * k,
+                               seg_cols=k, seg_offsets=self.seg_offsets, n_rows=self.B, pos_map_stride=2 * k)
+            return self.merged
         dist.all_gather_into_tensor(self.cand_all.view(-1), self.cand.view(-1), group=self.shard.group)
         flat = self.cand_all.view(-1)
         scores = flat[k:].view(torch.float32)        # segment r, row b starts at r*B*2k + b*2k + k

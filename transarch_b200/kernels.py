@@ -5,7 +5,8 @@ current stream.  Nothing here computes on the CPU.
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+import ctypes
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -30,9 +31,11 @@ def topk_select(scores: torch.Tensor, k: int, *, col_begin: Optional[torch.Tenso
                 sorted: bool = True, return_values: bool = False, out: Optional[torch.Tensor] = None,
                 out_values: Optional[torch.Tensor] = None, seg_cols: int = 0, seg_stride: int = 0,
                 n_cols: Optional[int] = None, row_stride: Optional[int] = None,
-                n_rows: Optional[int] = None, pos_map_stride: Optional[int] = None):
+                n_rows: Optional[int] = None, pos_map_stride: Optional[int] = None,
+                seg_offsets: Optional[Sequence[int]] = None):
     """Row-wise top-k positions (int32, -1 padded; descending score when sorted); see
-    b200dsa_topk_select."""
+    b200dsa_topk_select.  seg_offsets: element offsets of the segments from scores / pos_map
+    (segments in separate, possibly peer-GPU, buffers)."""
     require_cuda(scores, col_begin, col_end, pos_map, page_table, row_pos_offset)
     if scores.dtype != torch.float32 or scores.dim() != 2 or scores.stride(1) != 1:
         raise _lib.B200DSAError("scores must be a 2-D fp32 tensor with unit column stride")
@@ -48,6 +51,7 @@ def topk_select(scores: torch.Tensor, k: int, *, col_begin: Optional[torch.Tenso
         vals = torch.empty(n_rows, out.stride(0), dtype=torch.float32, device=scores.device)
     if vals is not None and (vals.dtype != torch.float32 or vals.stride(0) != out.stride(0)):
         raise _lib.B200DSAError("out_values must be fp32 with the row stride of out")
+    seg_arr = (ctypes.c_int64 * len(seg_offsets))(*seg_offsets) if seg_offsets is not None else None
     lib = _lib.load()
     rc = lib.b200dsa_topk_select(
         ptr(scores), row_stride, n_rows, n_cols,
@@ -55,7 +59,7 @@ def topk_select(scores: torch.Tensor, k: int, *, col_begin: Optional[torch.Tenso
         ptr(_i32(pos_map, "pos_map")),
         (pos_map_stride if pos_map_stride is not None else pos_map.stride(0)) if pos_map is not None else 0,
         ptr(_i32(page_table, "page_table")), page_table.stride(0) if page_table is not None else 0, page_size,
-        ptr(_i32(row_pos_offset, "row_pos_offset")), seg_cols, seg_stride,
+        ptr(_i32(row_pos_offset, "row_pos_offset")), seg_cols, seg_stride, seg_arr,
         ptr(out), ptr(vals), out.stride(0), stream_ptr())
     check(rc, "b200dsa_topk_select")
     if return_values or out_values is not None:

@@ -95,14 +95,19 @@ class PeerLseCombine:
     b200dsa_peer_lse_combine.  The attention kernel writes straight into `ctx` / `lse` (views of
     this rank's exchange buffer); after run() `out` / `lse_out` hold the merged result on every rank."""
 
-    def __init__(self, n_rows: int, device: torch.device, group=None, emulate_world: Optional[int] = None):
+    def __init__(self, n_rows: int, device: torch.device, group=None, emulate_world: Optional[int] = None,
+                 extra_bytes: int = 0):
+        """extra_bytes: room after the flags for other data the ranks read from each other (`extra`)."""
         self.n_rows = n_rows
         self.off_ctx = 0
         self.off_lse = _align(n_rows * 512 * 2)
         self.off_out = self.off_lse + _align(n_rows * 4)
         self.off_lse_out = self.off_out + _align(n_rows * 512 * 2)
         self.off_flags = self.off_lse_out + _align(n_rows * 4)
-        self.buffers = PeerBuffers(self.off_flags + 256, device, group, emulate_world)
+        self.off_extra = self.off_flags + 256
+        self.extra_bytes = extra_bytes
+        self.buffers = PeerBuffers(self.off_extra + extra_bytes, device, group, emulate_world)
+        self.barrier_state = torch.zeros(8, dtype=torch.int32, device=device)
         self.rank, self.world = self.buffers.rank, self.buffers.world
         self.state = [torch.zeros(2, dtype=torch.int32, device=device) for _ in range(emulate_world or 1)]
         v = self.views_of(self.rank)
@@ -115,6 +120,23 @@ class PeerLseCombine:
                 b[self.off_lse:self.off_lse + n * 4].view(torch.float32),
                 b[self.off_out:self.off_out + n * 1024].view(torch.bfloat16).view(n, 512),
                 b[self.off_lse_out:self.off_lse_out + n * 4].view(torch.float32))
+
+    def extra_of(self, r: int) -> torch.Tensor:
+        """uint8 view of the extra area of rank r's buffer."""
+        return self.buffers.views[r][self.off_extra:self.off_extra + self.extra_bytes]
+
+    def element_offsets(self, itemsize: int = 4) -> List[int]:
+        """Offset of every rank's buffer from this rank's, in elements of `itemsize` bytes."""
+        base = self.buffers.addresses[self.rank]
+        return [(a - base) // itemsize for a in self.buffers.addresses]
+
+    def barrier(self, slot: int = 1) -> None:
+        """Node-wide barrier on the current stream (b200dsa_peer_barrier): what the peers wrote into
+        their buffers before their call can be read from this rank afterwards."""
+        rc = _lib.load().b200dsa_peer_barrier(
+            self.buffers._addr_array, self.rank, self.world, self.off_flags, slot,
+            ptr(self.barrier_state[slot:slot + 1]), ptr(status_word(self.buffers.device)), stream_ptr())
+        check(rc, "b200dsa_peer_barrier")
 
     def run(self, rank: Optional[int] = None, no_sync: bool = False):
         """Launch on the current stream.  `rank` / no_sync are for single-GPU emulation only: there the
