@@ -356,14 +356,22 @@ def main():
         achieved = idx_bytes / (indexer_ms * 1e-3) / 1e9
         h2d = sum(t.numel() * t.element_size() for t in host_q[0])
         d2h = sum(t.numel() * t.element_size() for t in out_host[0])
-        launches = 5 if world == 1 else 8
+        # our kernels per step: q quantisation, indexer, top-k (3 in the split form), attention; sharded:
+        # + merge top-k, compaction and either barrier + peer combine or the bf16 share kernel (NCCL's
+        # own kernels are not counted)
+        launches = 2 + (3 if step.topk_scratch is not None else 1) + 1
+        if world > 1:
+            launches += 2 + (2 if step.peer is not None else 1)
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8(e4m3) index scores / bf16 attention, fp32 accumulate",
             "data": "synthetic",
             "config": {"workload": WORKLOAD if (B, ctx) == (BATCH, CONTEXT) else f"batch {B}, context {ctx} (non-default)",
-                       "parallelism": f"key-sharded x{world}", "launch": "eager" if graphed is None else "cuda-graph replay",
+                       "parallelism": f"key-sharded x{world}",
+                       "exchange": "none" if world == 1 else ("peer memory (NVLink loads/stores in our kernels)"
+                                                              if step.peer is not None else "NCCL"),
+                       "launch": "eager" if graphed is None else "cuda-graph replay",
                        "l2": "inputs larger than L2 (index-key cache %.2f GB per GPU, 4 rotating query sets)"
                              % (idx_bytes / 1e9)},
             "indexer_topk_us_per_step": 1e3 * (stage_ms["quant+indexer"] + stage_ms["topk"]),
