@@ -198,6 +198,9 @@ def main():
         return step.run(q_idx, w, q_lat, state.k_cache, state.context_lens, state.block_table, state.kv,
                         state.kv_row_base, state.context_lens_local)
 
+    if world > 1:
+        dist.barrier()                    # ranks build their state at different speeds; the kernels' waits
+        torch.cuda.synchronize()          # for peers are bounded to about a second
     for i in range(2):
         res = run_eager(i)                # lazy initialisation (NCCL communicators, function attributes)
     ctx_dtype = res[1].dtype              # bf16, the dtype the reference op returns
@@ -344,6 +347,18 @@ def main():
         indexer_ms = float(tt.item())
     stage_ms["indexer_back_to_back"] = indexer_ms
 
+    # what the host link gives by itself: the step's input copy alone, back to back (explains e2e when
+    # the copies, not the kernels, bound the pipelined loop)
+    sync_all()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for _ in range(20):
+        for dst, src in zip(in_dev[0], host_q[0]):
+            dst.copy_(src, non_blocking=True)
+    c1.record()
+    torch.cuda.synchronize()
+    h2d_only_ms = c0.elapsed_time(c1) / 20
+
     for i in range(3):
         run_e2e(i)
     e2e_ms = timed(run_e2e, args.steps)
@@ -376,7 +391,9 @@ def main():
                              % (idx_bytes / 1e9)},
             "indexer_topk_us_per_step": 1e3 * (stage_ms["quant+indexer"] + stage_ms["topk"]),
             "stage_us": {k_: round(1e3 * v, 2) for k_, v in stage_ms.items()},
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / args.steps, "h2d_copy_alone_ms": h2d_only_ms,
+                    "h2d_copy_alone_gbs": h2d / (h2d_only_ms * 1e-3) / 1e9},
             "gpu_launches": launches * args.steps,
             "roofline": {"kernel": "indexer_paged_kernel<fp8>", "bound": "hbm", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],

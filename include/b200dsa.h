@@ -218,7 +218,7 @@ int b200dsa_lse_combine(const float* ctx_parts, const float* lse_parts, int32_t 
  *   off_flags    256 bytes of flags, zero before the first call and never touched by the host
  * state: two int32 of LOCAL device memory, zero before the first call (the step counter lives
  * there, so a captured launch can be replayed).  All ranks must make the same sequence of calls.
- * Waits for peers are bounded (about half a second): on expiry *status gets 1 and the call
+ * Waits for peers are bounded (about a second): on expiry *status gets 1 and the call
  * completes with an unusable result instead of hanging.  no_sync != 0 skips the flag exchange:
  * ranks emulated one after another on a single GPU (tests); ranks that wait for each other
  * must run on different GPUs.  1 <= world <= 8.

@@ -26,7 +26,7 @@ namespace b200dsa {
 
 constexpr int kPeerMaxRanks = 8;
 constexpr int kPeerDv = 512;
-constexpr long long kPeerWaitCycles = 1ll << 30;   // about half a second
+constexpr long long kPeerWaitCycles = 1ll << 31;   // about a second
 constexpr int kPeerDoneSlot = 16;                  // flags: ready[0..7], done[16..23] (uint32 words)
 
 struct PeerCombineParams {

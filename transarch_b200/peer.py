@@ -35,6 +35,11 @@ class PeerBuffers:
     local            uint8 tensor over this rank's buffer
     addresses[r]     device address of rank r's buffer in THIS process
     With emulate_world=n (single process, tests) the n buffers are n local allocations.
+
+    The constructor is collective (one all-gather of the handles).  It raises on every rank when an
+    allocation failed anywhere, and on the ranks that could not map a peer; the group must agree on
+    the outcome (as SparseDecodeStep does with an all-reduce) before any rank launches a kernel on
+    the buffers, and must synchronise (host barrier) before close().
     """
 
     def __init__(self, nbytes: int, device: torch.device, group=None, emulate_world: Optional[int] = None):
@@ -49,23 +54,38 @@ class PeerBuffers:
                 self.addresses = [self._alloc(lib)[0] for _ in range(emulate_world)]
             else:
                 self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-                mine, handle = self._alloc(lib)
-                # the handles are 64 opaque bytes: gather them as a tensor on the group's own backend
-                h = torch.tensor(list(handle), dtype=torch.uint8, device=self.device)
-                gathered = torch.empty(self.world, 64, dtype=torch.uint8, device=self.device)
+                # Every rank takes part in the one collective below whether or not its allocation
+                # worked (first byte = valid), so that a local failure cannot leave the others waiting.
+                mine, handle, err = None, bytes(64), None
+                try:
+                    mine, handle = self._alloc(lib)
+                except _lib.B200DSAError as e:
+                    err = e
+                h = torch.tensor([0 if mine is None else 1] + list(handle), dtype=torch.uint8, device=self.device)
+                gathered = torch.empty(self.world, 65, dtype=torch.uint8, device=self.device)
                 dist.all_gather_into_tensor(gathered.view(-1), h, group=group)
                 gathered = gathered.cpu()
+                if not bool(gathered[:, 0].all()):
+                    self.close()
+                    raise _lib.B200DSAError(f"exchange buffer allocation failed on a rank of the group ({err})")
                 self.addresses = []
-                for r in range(self.world):
-                    if r == self.rank:
-                        self.addresses.append(mine)
-                        continue
-                    raw = (ctypes.c_ubyte * 64)(*gathered[r].tolist())
-                    out = ctypes.c_void_p()
-                    check(lib.b200dsa_peer_open(raw, ctypes.byref(out)), "b200dsa_peer_open")
-                    self._opened.append(out.value)
-                    self.addresses.append(out.value)
-                dist.barrier(group=group)
+                try:
+                    for r in range(self.world):
+                        if r == self.rank:
+                            self.addresses.append(mine)
+                            continue
+                        raw = (ctypes.c_ubyte * 64)(*gathered[r, 1:].tolist())
+                        out = ctypes.c_void_p()
+                        check(lib.b200dsa_peer_open(raw, ctypes.byref(out)), "b200dsa_peer_open")
+                        self._opened.append(out.value)
+                        self.addresses.append(out.value)
+                except _lib.B200DSAError:
+                    # ranks on another node, or IPC not permitted: unmap what was mapped; the buffer of
+                    # this rank stays allocated until close(), peers may still have it mapped
+                    for a in self._opened:
+                        lib.b200dsa_peer_close(ctypes.c_void_p(a))
+                    self._opened = []
+                    raise
         self.views = [torch.as_tensor(_Span(a, self.nbytes), device=self.device) for a in self.addresses]
         self.local = self.views[self.rank]
         self._addr_array = (ctypes.c_void_p * self.world)(*self.addresses)
@@ -81,6 +101,7 @@ class PeerBuffers:
         """Unmap the peers' buffers and free this rank's own (call on every rank, after a barrier)."""
         lib = _lib.load()
         self.views, self.local = [], None
+        self.addresses = []
         with torch.cuda.device(self.device):
             torch.cuda.synchronize()
             for a in self._opened:
