@@ -156,6 +156,8 @@ int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* weights, co
  *   q_bf16 [n_rows, 64, 128], keys_bf16 [n_keys, 128] (both 16-byte aligned),
  *   row_cols [n_rows] = 128 * (number of listed blocks), block ids in [0, ceil(n_keys/128)).
  * head_mask / logits_gated: as for b200dsa_indexer_paged_fp8_logits.
+ * block_list may be NULL when pos_lo / pos_hi are given: row r then covers the consecutive
+ * blocks pos_lo[r]/128, pos_lo[r]/128 + 1, ... (flat causal prefill needs no list).
  * ------------------------------------------------------------------------------------- */
 int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const float* weights, const void* keys_bf16,
                                           int32_t n_keys, const int32_t* block_list,

@@ -161,7 +161,7 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
     }
     int row = row0, prev_row = -1;
     int it = 0, qit = 0;
-    int tbl_base = -1, tbl_entry = -1, tbl_len = 0, cols = 0;
+    int tbl_base = -1, tbl_entry = -1, tbl_len = 0, cols = 0, ident0 = 0;
     const int32_t* trow = p.table;
     const int P = kFp8 ? p.page_size : kTileKeys;
     const int p_shift = 31 - __clz(P);  // P is a power of two
@@ -181,7 +181,11 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
         ++qit;
         prev_row = row;
         cols = max(0, min(p.row_cols[row], p.logits_cols));
-        trow = p.table + static_cast<int64_t>(p.row_table ? p.row_table[row] : row / p.table_row_div) * p.table_stride;
+        if (p.table) {
+          trow = p.table + static_cast<int64_t>(p.row_table ? p.row_table[row] : row / p.table_row_div) * p.table_stride;
+        } else {
+          ident0 = p.pos_lo[row] >> 7;    // no list: consecutive blocks from the one holding pos_lo
+        }
         tbl_len = min(p.table_cols, (cols + P - 1) >> p_shift);
         tbl_base = -1;
       }
@@ -196,7 +200,7 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       if (tbl_base < 0 || first < tbl_base || first + npages > tbl_base + 32) {
         tbl_base = first;
         const int e = tbl_base + lane;
-        tbl_entry = (e < tbl_len) ? trow[e] : -1;
+        tbl_entry = (e < tbl_len) ? (p.table ? trow[e] : ident0 + e) : -1;
       }
       if constexpr (kFp8) {
         int pg[4];  // statically indexed below so that it stays in registers
@@ -316,7 +320,8 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
           w[4 * j + 0] = x.x; w[4 * j + 1] = x.y; w[4 * j + 2] = x.z; w[4 * j + 3] = x.w;
         }
         cols = max(0, min(p.row_cols[row], p.logits_cols));
-        trow = p.table + static_cast<int64_t>(p.row_table ? p.row_table[row] : row / p.table_row_div) * p.table_stride;
+        if (p.table)
+          trow = p.table + static_cast<int64_t>(p.row_table ? p.row_table[row] : row / p.table_row_div) * p.table_stride;
         if (p.pos_lo) { lo = p.pos_lo[row]; hi = p.pos_hi[row]; }
         if (dual) {
           const uint64_t hm = p.head_mask[row];
@@ -336,7 +341,7 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
         keep = keep && (kscale >= 0.0f);
       } else {
         if (keep) {
-          const int blk = trow[t];
+          const int blk = p.table ? trow[t] : (lo >> 7) + t;
           const int pos = blk * kTileKeys + lane_base + lane;
           keep = (blk >= 0 && blk < p.num_pages) && pos >= lo && pos < hi;
         }
@@ -535,7 +540,7 @@ extern "C" int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const f
                                                      int64_t logits_stride, const uint64_t* head_mask,
                                                      float* logits_gated, int32_t* status, void* stream) {
   if (n_rows == 0) return B200DSA_OK;
-  if (!q_bf16 || !weights || !keys_bf16 || !block_list || !row_cols || !logits || !status || n_rows < 0 ||
+  if (!q_bf16 || !weights || !keys_bf16 || (!block_list && !pos_lo) || !row_cols || !logits || !status || n_rows < 0 ||
       n_keys < 1 || max_cols < 0 || logits_stride < max_cols || ((pos_lo == nullptr) != (pos_hi == nullptr)) ||
       ((head_mask == nullptr) != (logits_gated == nullptr))) {
     set_last_error("b200dsa_indexer_blocklist_bf16_logits: bad argument");
@@ -570,9 +575,9 @@ extern "C" int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const f
     p.num_pages = n_blocks;
     p.weights = weights + static_cast<int64_t>(r0) * kHeads;
     p.row_cols = row_cols + r0;
-    p.table = block_list + static_cast<int64_t>(r0) * block_list_stride;
+    p.table = block_list ? block_list + static_cast<int64_t>(r0) * block_list_stride : nullptr;
     p.table_stride = block_list_stride;
-    p.table_cols = static_cast<int32_t>(block_list_stride);
+    p.table_cols = block_list ? static_cast<int32_t>(block_list_stride) : 0x7fffffff;
     p.table_row_div = 1;
     p.pos_lo = pos_lo ? pos_lo + r0 : nullptr;
     p.pos_hi = pos_hi ? pos_hi + r0 : nullptr;

@@ -151,11 +151,17 @@ __device__ __forceinline__ void stream_row(const float* __restrict__ src, int be
   }
 }
 
-// In-place descending bitonic sort of n (power of two) keys in shared memory.
+// In-place descending bitonic sort of n (power of two, >= 64) keys in shared memory.  Pair index t
+// is handled by thread t % blockDim, so a warp works on contiguous 64-key chunks and keeps the same
+// chunks in every stage: stages whose stride is at most 32 exchange keys inside a chunk only and need
+// a warp barrier, not a block barrier (51 of the 66 stages of a 2048-key sort).
 __device__ void bitonic_sort_desc(uint64_t* a, int n) {
+  bool prev_wide = true;  // keys were written by other warps before the sort
   for (int size = 2; size <= n; size <<= 1) {
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      __syncthreads();
+      const bool wide = stride > 32;
+      if (wide || prev_wide) __syncthreads(); else __syncwarp();
+      prev_wide = wide;
       for (int t = threadIdx.x; t < (n >> 1); t += blockDim.x) {
         int lo = 2 * t - (t & (stride - 1));
         int hi = lo + stride;

@@ -202,9 +202,11 @@ def indexer_blocklist_bf16_logits(q: torch.Tensor, weights: torch.Tensor, keys: 
                                   pos_lo: Optional[torch.Tensor] = None, pos_hi: Optional[torch.Tensor] = None,
                                   out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
                                   head_mask: Optional[torch.Tensor] = None,
-                                  out_gated: Optional[torch.Tensor] = None):
+                                  out_gated: Optional[torch.Tensor] = None, max_cols: Optional[int] = None):
     """Token logits [n_rows, 128*list_len] inside per-row lists of 128-key blocks; see
-    b200dsa_indexer_blocklist_bf16_logits.  head_mask: as for indexer_paged_fp8_logits."""
+    b200dsa_indexer_blocklist_bf16_logits.  head_mask: as for indexer_paged_fp8_logits.
+    block_list=None: row r covers consecutive blocks starting at the one that holds pos_lo[r]
+    (pos_lo / pos_hi and max_cols, a multiple of 128, are then required)."""
     require_cuda(q, weights, keys, block_list, row_cols, pos_lo, pos_hi, head_mask, out_gated)
     if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.shape[-2:] != (64, 128):
         raise _lib.B200DSAError("q must be contiguous bf16 [n_rows, 64, 128]")
@@ -214,13 +216,19 @@ def indexer_blocklist_bf16_logits(q: torch.Tensor, weights: torch.Tensor, keys: 
     if weights.dtype != torch.float32 or not weights.is_contiguous() or weights.numel() != n_rows * 64:
         raise _lib.B200DSAError("weights must be contiguous fp32 [n_rows, 64]")
     _i32(block_list, "block_list"); _i32(row_cols, "row_cols")
-    max_cols = block_list.shape[1] * 128
+    if block_list is None:
+        if pos_lo is None or pos_hi is None or (max_cols is None and out is None):
+            raise _lib.B200DSAError("without a block list pos_lo, pos_hi and max_cols are required")
+        max_cols = out.shape[1] if max_cols is None else max_cols
+    else:
+        max_cols = block_list.shape[1] * 128
     if out is None:
         out = torch.full((n_rows, max_cols), NEG_INF, dtype=torch.float32, device=q.device)
     out_gated = _gated_output(head_mask, out_gated, out, n_rows)
     lib = _lib.load()
     rc = lib.b200dsa_indexer_blocklist_bf16_logits(
-        ptr(q), ptr(weights), ptr(keys), keys.shape[0], ptr(block_list), block_list.stride(0),
+        ptr(q), ptr(weights), ptr(keys), keys.shape[0], ptr(block_list),
+        block_list.stride(0) if block_list is not None else 0,
         ptr(row_cols), ptr(_i32(pos_lo, "pos_lo")), ptr(_i32(pos_hi, "pos_hi")), n_rows, max_cols, out_scale,
         ptr(out), out.stride(0), ptr(head_mask), ptr(out_gated), ptr(status_word(q.device)), stream_ptr())
     check(rc, "b200dsa_indexer_blocklist_bf16_logits")

@@ -26,11 +26,13 @@ _BLOCK = 128
 _MAX_LOGIT_BYTES = 1 << 30   # scratch bound for one query chunk of token logits
 
 
-def prepare_ks_ke(cu_seqlens: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+def prepare_ks_ke(cu_seqlens: torch.Tensor, total: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Per packed query the causal interval [ks, ke): ks = start of its document,
-    ke = its own position + 1.  Device-side (no host synchronisation beyond the total length)."""
+    ke = its own position + 1.  Device-side; `total` (the number of packed tokens, cu_seqlens[-1])
+    saves the one host synchronisation that reading it costs."""
     cu = cu_seqlens.to(torch.int64)
-    total = int(cu[-1]) if cu.numel() else 0
+    if total is None:
+        total = int(cu[-1]) if cu.numel() else 0
     t = torch.arange(total, dtype=torch.int64, device=cu.device)
     doc = torch.searchsorted(cu, t, right=True) - 1
     return cu[doc], t + 1
@@ -72,12 +74,18 @@ def identity_block_lists(ks: torch.Tensor, ke: torch.Tensor, n_keys: int):
 
 def indexer_logits_flat(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, ks: torch.Tensor, ke: torch.Tensor,
                         sm_scale: float):
-    """Token logits of every row over the blocks covering its interval:
-    (logits fp32 [T, max_blocks*128] with -inf outside [ks,ke), block_list, row_cols)."""
-    bl, row_cols = identity_block_lists(ks, ke, k.shape[0])
-    logits = K.indexer_blocklist_bf16_logits(q, w, k, bl, row_cols, pos_lo=ks.to(torch.int32).contiguous(),
-                                             pos_hi=ke.to(torch.int32).contiguous(), out_scale=sm_scale)
-    return logits, bl, row_cols
+    """Token logits of every row over the 128-key blocks covering its interval [ks, ke):
+    (logits fp32 [T, cols] with -inf outside the interval, col0 int32 [T] = position of column 0 of
+    each row, row_cols int32 [T]).  No block list is built: the kernel walks consecutive blocks."""
+    lo = ks.to(torch.int32).contiguous()
+    hi = ke.to(torch.int32).contiguous()
+    col0 = (lo >> 7) << 7
+    row_cols = (((hi + (_BLOCK - 1)) >> 7) << 7) - col0
+    row_cols.clamp_(min=0)
+    cols = ((k.shape[0] + _BLOCK - 1) // _BLOCK) * _BLOCK
+    logits = K.indexer_blocklist_bf16_logits(q, w, k, None, row_cols, pos_lo=lo, pos_hi=hi, out_scale=sm_scale,
+                                             max_cols=cols)
+    return logits, col0, row_cols
 
 
 @torch.no_grad()
@@ -93,7 +101,7 @@ def indexer_select_topk(index_q, index_k, index_w, cu_seqlens, topk, *, sm_scale
         raise B200DSAError("index head dim must be 128")
     sf = sm_scale_index if sm_scale_index is not None else d ** -0.5
     if q_global_pos is None:
-        ks, ke = prepare_ks_ke(cu_seqlens)
+        ks, ke = prepare_ks_ke(cu_seqlens, total=Lq)
     else:
         ks, ke = prepare_ks_ke_cp(cu_seqlens, q_global_pos)
     q, w = _pad_heads(index_q.to(torch.bfloat16), index_w.to(torch.float32))
@@ -109,8 +117,8 @@ def indexer_select_topk(index_q, index_k, index_w, cu_seqlens, topk, *, sm_scale
         raise B200DSAError("topk above 8192 is not supported")
     for t0 in range(0, Lq, rows_per):
         t1 = min(t0 + rows_per, Lq)
-        logits, bl, row_cols = indexer_logits_flat(q[t0:t1], k, w[t0:t1], ks[t0:t1], ke[t0:t1], sf)
-        K.topk_select(logits, k_eff, col_end=row_cols, page_table=bl, page_size=_BLOCK, sorted=True, out=out[t0:t1])
+        logits, col0, row_cols = indexer_logits_flat(q[t0:t1], k, w[t0:t1], ks[t0:t1], ke[t0:t1], sf)
+        K.topk_select(logits, k_eff, col_end=row_cols, row_pos_offset=col0, sorted=True, out=out[t0:t1])
     return out
 
 
