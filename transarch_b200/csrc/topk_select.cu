@@ -498,8 +498,28 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     const int n_eq = min(s_eq_cnt, kEqCap);
     int n_eq_pow2 = 32;
     while (n_eq_pow2 < n_eq) n_eq_pow2 <<= 1;
-    for (int i = n_eq + tid; i < n_eq_pow2; i += nthr) eq[i] = 0;
-    bitonic_sort_desc(eq, n_eq_pow2);
+    if (n_eq <= 32) {
+      // the usual case (a handful of undecided keys): one warp sorts them in registers
+      if (tid < 32) {
+        uint64_t key = tid < n_eq ? eq[tid] : 0ull;
+#pragma unroll
+        for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+          for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            const uint64_t other = __shfl_xor_sync(0xffffffffu, key, stride);
+            const bool upper = (tid & stride) != 0;           // holds the later slot of the pair
+            const bool desc = (tid & size) == 0;
+            const bool want_max = (upper != desc);             // descending run: earlier slot keeps the larger key
+            key = (want_max == (key > other)) ? key : other;
+          }
+        }
+        eq[tid] = key;
+      }
+      __syncthreads();
+    } else {
+      for (int i = n_eq + tid; i < n_eq_pow2; i += nthr) eq[i] = 0;
+      bitonic_sort_desc(eq, n_eq_pow2);
+    }
     const int take = min(min(r.need_eq, n_eq), k_pow2 - n_sel);
     for (int i = tid; i < take; i += nthr) sel[n_sel + i] = eq[i];
     n_sel += take;
