@@ -34,7 +34,7 @@ ATTN_SCALE = 192 ** -0.5
 # DRAM bytes (read + write) per scored key of the indexer kernel, from an ncu capture of that kernel
 # on a smaller case (dram__bytes_read + dram__bytes_write over the keys scored; traffic grows in
 # proportion to the number of keys).
-DRAM_BYTES_PER_KEY = 137.8
+DRAM_BYTES_PER_KEY = 137.3
 METRIC = "sparse_mla_decode_tokens_per_s"
 WORKLOAD = ("sparse MLA decode, key-sharded: batch 64, context 131072, 64 index heads d=128, FP8 paged "
             "index keys (page 64) with per-token scale, top-2048, 128 heads over 576-wide bf16 latent KV")
