@@ -311,8 +311,7 @@ def main():
         sub = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
         idx = step.merge_candidates() if world > 1 else step.cand[:, :TOPK]
         sub[0].record()
-        torch.sub(state.context_lens, 1, out=step.q_pos)
-        step.attend(q_lat, state.kv, state.kv_row_base, idx, step.q_pos)
+        step.attend(q_lat, state.kv, state.kv_row_base, idx, state.context_lens, q_pos_bias=-1)
         sub[1].record()
         if world > 1:
             step.combine()

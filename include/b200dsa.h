@@ -172,7 +172,8 @@ int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const float* weigh
  * token per item; emits the latent-space context and the log-sum-exp so that partial results
  * over disjoint key sets can be merged.
  *
- *   valid(j) = idx_j >= 0 and idx_j <= q_pos[item] and pos_lo <= idx_j < pos_hi
+ *   valid(j) = idx_j >= 0 and idx_j <= q_pos[item] + q_pos_bias and pos_lo <= idx_j < pos_hi
+ *              (q_pos_bias = -1 lets a caller pass context lengths as q_pos)
  *   s[h,j]   = sm_scale * <q[item,h,:], kv[kv_row_base[item] + idx_j - pos_lo, :]>
  *   ctx[item,h,:] = sum_j softmax_j(s)[h,j] * kv[row_j, 0:512]     (0 when no key is valid)
  *   lse[item,h]   = log sum_j exp(s[h,j])                           (-inf when no key is valid)
@@ -189,7 +190,7 @@ int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const float* weigh
 int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16, int64_t kv_rows,
                               const int64_t* kv_row_base, const int32_t* indices, int64_t idx_stride,
                               int32_t n_idx, const int32_t* n_idx_item, const int32_t* q_pos,
-                              int32_t pos_lo, int32_t pos_hi,
+                              int32_t q_pos_bias, int32_t pos_lo, int32_t pos_hi,
                               int32_t n_items, int32_t n_heads, float sm_scale, void* ctx, int32_t ctx_bf16,
                               float* lse, int32_t* status, void* stream);
 

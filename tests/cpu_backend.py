@@ -65,13 +65,13 @@ def sorted_by(vals, pos):
 
 
 def sparse_mla_decode(q, kv, indices, sm_scale, *, kv_row_base=None, q_pos=None, pos_lo=0, pos_hi=2 ** 31 - 1,
-                      n_idx_item=None, ctx=None, lse=None):
+                      n_idx_item=None, ctx=None, lse=None, q_pos_bias=0):
     n = q.shape[0]
     for b in range(n):
         idx = indices[b].long()
         keep = (idx >= pos_lo) & (idx < pos_hi) & (idx >= 0)
         if q_pos is not None:
-            keep &= idx <= int(q_pos[b])
+            keep &= idx <= int(q_pos[b]) + q_pos_bias
         rows = (idx - pos_lo + (int(kv_row_base[b]) if kv_row_base is not None else 0))
         local = torch.where(keep, rows, torch.full_like(rows, -1)).to(torch.int32).view(1, -1)
         c, l = O.sparse_attend_latent(q[b:b + 1], kv, local, d_c=512, sm_scale=sm_scale,

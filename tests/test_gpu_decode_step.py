@@ -126,3 +126,55 @@ def test_prescale_norm_equals_combine():
         assert (lse_out[fin] - ref_lse[fin]).abs().max() < 1e-5
     assert (acc - ref_ctx).abs().max() < 2e-2 * ref_ctx.abs().max()
     assert (acc[2, 5] == 0).all()
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_many_shards_through_peer_buffers_emulated(world):
+    """The peer-memory data path with 4 and 8 shards on one GPU: every shard's candidates and
+    partials live in their own exchange buffer, the merge reads them through per-segment offsets and
+    the one-kernel combine runs rank after rank without the flag exchange.  Result: the unsharded one."""
+    from transarch_b200 import _lib
+    from transarch_b200.decode import ShardInfo, SparseDecodeStep
+    from transarch_b200.peer import PeerLseCombine
+    shard_len, topk, H = 1024, 512, 128
+    ctxs = [world * shard_len, world * shard_len - 700, 3 * shard_len + 5]
+    B = len(ctxs)
+    prob = make_global_problem(43, ctxs)
+    q_idx, w, q_lat = _cuda(prob)
+    full = shard_state(prob, 0, 1, max(ctxs), "cuda")
+    one = SparseDecodeStep(B, full["table"].shape[1] * 64, topk=topk, sorted_topk=True)
+    idx1, ctx1, lse1 = [t.clone() for t in one.run(q_idx, w, q_lat, full["cache"], full["lens"], full["table"],
+                                                     full["kv"], full["base"])]
+    dev = torch.device("cuda")
+    pc = PeerLseCombine(B * H, dev, emulate_world=world, extra_bytes=B * 2 * topk * 4)
+    try:
+        steps, states = [], []
+        for r in range(world):
+            st = shard_state(prob, r, world, shard_len, "cuda")
+            sp = SparseDecodeStep(B, shard_len, topk=topk, sorted_topk=True,
+                                  shard=ShardInfo(rank=r, world_size=world, shard_len=shard_len))
+            c, l, _, _ = pc.views_of(r)                   # what SparseDecodeStep does with a real group
+            sp.ctx, sp.lse = c.view(B, H, 512), l.view(B, H)
+            sp.cand = pc.extra_of(r).view(torch.int32).view(B, 2 * topk)
+            sp.select(q_idx, w, st["cache"], st["local"], st["table"])
+            steps.append(sp); states.append(st)
+        base = pc.buffers.addresses
+        for r, sp in enumerate(steps):
+            flat = sp.cand.view(-1)
+            sp.K.topk_select(flat[topk:].view(torch.float32).view(1, -1), topk, sorted=True, pos_map=flat.view(1, -1),
+                             out=sp.merged, n_cols=world * topk, row_stride=2 * topk, seg_cols=topk,
+                             seg_offsets=[(a - base[r]) // 4 for a in base], n_rows=B, pos_map_stride=2 * topk)
+            assert torch.equal(sp.merged, idx1), "merged shard candidates differ from the unsharded top-k"
+            torch.sub(states[r]["lens"], 1, out=sp.q_pos)
+            sp.attend(q_lat, states[r]["kv"], states[r]["base"], sp.merged, sp.q_pos)
+        for r in range(world):
+            pc.run(rank=r, no_sync=True)
+        torch.cuda.synchronize()
+        assert _lib.read_status(dev) == 0
+        for r in range(world):
+            _, _, out, lse_out = pc.views_of(r)
+            err = (out.float().view(B, H, 512) - ctx1.float()).abs().max() / ctx1.float().abs().max()
+            assert err < 2e-2
+            assert (lse_out.view(B, H) - lse1).abs().max() < 1e-3
+    finally:
+        pc.close()

@@ -61,7 +61,8 @@ struct MlaParams {
   int64_t idx_stride;
   int32_t n_idx;
   const int32_t* n_idx_item;   // nullable [n_items]: only the first n_idx_item[i] indices of item i are looked at
-  const int32_t* q_pos;        // nullable [n_items]: keys beyond this position are masked
+  const int32_t* q_pos;        // nullable [n_items]: keys beyond q_pos[item] + q_pos_bias are masked
+  int q_pos_bias;
   int32_t pos_lo, pos_hi;      // only positions in [pos_lo, pos_hi) are attended (shard ownership)
   int32_t n_items, n_heads;
   float scale_log2;            // sm_scale * log2(e)
@@ -188,7 +189,7 @@ sparse_mla_decode_kernel(const MlaParams p) {
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
 
-  const int qpos = p.q_pos ? p.q_pos[item] : 0x7fffffff;
+  const int qpos = p.q_pos ? p.q_pos[item] + p.q_pos_bias : 0x7fffffff;
   const int64_t row_base = (p.kv_row_base ? p.kv_row_base[item] : 0) - p.pos_lo;
 
   if (warp < 4) {
@@ -502,7 +503,7 @@ using namespace b200dsa;
 extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16, int64_t kv_rows,
                                          const int64_t* kv_row_base, const int32_t* indices, int64_t idx_stride,
                                          int32_t n_idx, const int32_t* n_idx_item, const int32_t* q_pos,
-                                         int32_t pos_lo, int32_t pos_hi,
+                                         int32_t q_pos_bias, int32_t pos_lo, int32_t pos_hi,
                                          int32_t n_items, int32_t n_heads, float sm_scale, void* ctx, int32_t ctx_bf16,
                                          float* lse, int32_t* status, void* stream) {
   if (n_items == 0) return B200DSA_OK;
@@ -532,6 +533,7 @@ extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16
   p.n_idx = n_idx;
   p.n_idx_item = n_idx_item;
   p.q_pos = q_pos;
+  p.q_pos_bias = q_pos_bias;
   p.pos_lo = pos_lo;
   p.pos_hi = pos_hi;
   p.n_items = n_items;

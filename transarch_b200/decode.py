@@ -188,8 +188,9 @@ class SparseDecodeStep:
                            seg_stride=self.B * 2 * k, n_rows=self.B, pos_map_stride=2 * k)
         return self.merged
 
-    def attend(self, q_lat, kv, kv_row_base, indices, q_pos) -> Tuple[torch.Tensor, torch.Tensor]:
-        """Attention over the selected keys this rank owns (all of them when unsharded)."""
+    def attend(self, q_lat, kv, kv_row_base, indices, q_pos, q_pos_bias: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Attention over the selected keys this rank owns (all of them when unsharded).  Keys beyond
+        q_pos + q_pos_bias are masked (context lengths with a bias of -1 save a subtraction kernel)."""
         count = None
         if self.shard.world_size > 1 and hasattr(self.K, "compact_owned"):
             # only about 1/N of the selection lives here: compact it so the kernel walks just those
@@ -197,7 +198,7 @@ class SparseDecodeStep:
                                                   self.owned_count)
         return self.K.sparse_mla_decode(q_lat, kv, indices, self.attn_scale, kv_row_base=kv_row_base, q_pos=q_pos,
                                         pos_lo=self.shard.pos_lo, pos_hi=self.shard.pos_hi, n_idx_item=count,
-                                        ctx=self.ctx, lse=self.lse)
+                                        ctx=self.ctx, lse=self.lse, q_pos_bias=q_pos_bias)
 
     def combine(self) -> Tuple[torch.Tensor, torch.Tensor]:
         """Merge the per-rank (ctx, lse) partials; every rank ends with the full result."""
@@ -231,8 +232,7 @@ class SparseDecodeStep:
         idx = self.select(q_idx, w, k_cache, context_lens_local, block_table)
         if self.shard.world_size > 1:
             idx = self.merge_candidates()
-        torch.sub(context_lens, 1, out=self.q_pos)
-        ctx, lse = self.attend(q_lat, kv, kv_row_base, idx, self.q_pos)
+        ctx, lse = self.attend(q_lat, kv, kv_row_base, idx, context_lens, q_pos_bias=-1)
         if self.shard.world_size > 1:
             ctx, lse = self.combine()
         return idx, ctx, lse

@@ -238,10 +238,11 @@ def indexer_blocklist_bf16_logits(q: torch.Tensor, weights: torch.Tensor, keys: 
 def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: float, *,
                       kv_row_base: Optional[torch.Tensor] = None, q_pos: Optional[torch.Tensor] = None,
                       pos_lo: int = 0, pos_hi: int = 2 ** 31 - 1, n_idx_item: Optional[torch.Tensor] = None,
-                      ctx: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None
-                      ) -> Tuple[torch.Tensor, torch.Tensor]:
+                      ctx: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
+                      q_pos_bias: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
     """Latent-space sparse attention: (ctx [n, H, 512], lse [n, H] fp32); see
-    b200dsa_sparse_mla_decode.  ctx is fp32 unless a bf16 buffer is passed in."""
+    b200dsa_sparse_mla_decode.  ctx is fp32 unless a bf16 buffer is passed in; q_pos_bias is added to
+    q_pos (-1: q_pos holds context lengths)."""
     require_cuda(q, kv, indices, kv_row_base, q_pos)
     if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.dim() != 3 or q.shape[2] != 576:
         raise _lib.B200DSAError("q must be contiguous bf16 [n_items, n_heads, 576]")
@@ -262,7 +263,7 @@ def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, 
     lib = _lib.load()
     rc = lib.b200dsa_sparse_mla_decode(
         ptr(q), ptr(kv), kv.shape[0], ptr(kv_row_base), ptr(indices), indices.stride(0), indices.shape[1],
-        ptr(_i32(n_idx_item, "n_idx_item")), ptr(q_pos), pos_lo, pos_hi, n, H, sm_scale, ptr(ctx),
+        ptr(_i32(n_idx_item, "n_idx_item")), ptr(q_pos), q_pos_bias, pos_lo, pos_hi, n, H, sm_scale, ptr(ctx),
         int(ctx.dtype == torch.bfloat16), ptr(lse), ptr(status_word(q.device)), stream_ptr())
     check(rc, "b200dsa_sparse_mla_decode")
     return ctx, lse
