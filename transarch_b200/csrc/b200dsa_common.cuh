@@ -211,6 +211,37 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---------------------------------------------------------------------------------------
+// Programmatic dependent launch.  Kernels of one step are launched with the attribute that lets
+// the next kernel of the stream become resident while the current one drains; a kernel says when
+// that may start (launch_dependents, at its top) and must not touch global memory that an
+// earlier kernel of the stream produces or still reads before pdl_wait_prior() returns, which
+// happens once every earlier kernel has completed and flushed.  Without the launch attribute
+// both instructions do nothing.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_prior() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool pdl_enabled();   // runtime.cu: off unless the environment says B200DSA_PDL=1 (measured gain on the
+                      // graph-replayed decode step: 0.7 %)
+
+// Launch `kernel` so that it may overlap the tail of the previous kernel of `stream` (see above).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Order-preserving map fp32 -> u32 (larger float <=> larger unsigned).
 __device__ __forceinline__ uint32_t float_to_ordered(float f) {
   uint32_t u = __float_as_uint(f);

@@ -73,6 +73,8 @@ __global__ void __launch_bounds__(kThreads, PagedCfg<kFp8>::kCtasPerSm)
 indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
                      const PagedIndexerParams p) {
   using Cfg = PagedCfg<kFp8>;
+  pdl_launch_dependents();
+  pdl_wait_prior();
   extern __shared__ uint8_t smem_dyn[];
   __shared__ int s_prefix[kMaxRows + 1];
   __shared__ uint32_t s_tmem_base;
@@ -446,8 +448,8 @@ static int launch_paged(const CUtensorMap& mk, const CUtensorMap& mq, PagedIndex
   }
   int grid = sm_count() * Cfg::kCtasPerSm;
   if (est_tiles > 0 && est_tiles < grid) grid = static_cast<int>(est_tiles);
-  indexer_paged_kernel<kFp8><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(mk, mq, p);
-  e = cudaGetLastError();
+  e = launch_chained(indexer_paged_kernel<kFp8>, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, mk, mq, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;

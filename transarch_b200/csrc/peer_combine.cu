@@ -91,6 +91,9 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float* a) {
 }
 
 __global__ void __launch_bounds__(256) peer_lse_combine_kernel(const PeerCombineParams p) {
+  // nothing may be signalled to the peers before the kernels that produced this rank's partial are done
+  pdl_launch_dependents();
+  pdl_wait_prior();
   __shared__ int s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t step = static_cast<uint32_t>(*reinterpret_cast<volatile int32_t*>(p.state)) + 1u;
@@ -175,6 +178,8 @@ __global__ void __launch_bounds__(256) peer_lse_combine_kernel(const PeerCombine
 
 // Node-wide barrier as a kernel of its own: flag word slot*8 + r of a buffer is written by rank r.
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerCombineParams p, int slot) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
   const int tid = threadIdx.x;
   const uint32_t step = static_cast<uint32_t>(*reinterpret_cast<volatile int32_t*>(p.state)) + 1u;
   __syncwarp();
@@ -226,8 +231,9 @@ extern "C" int b200dsa_peer_lse_combine(void* const* bufs, int32_t rank, int32_t
   int64_t grid = (per + 7) / 8;
   if (grid < 1) grid = 1;
   if (grid > 148) grid = 148;          // every block must be resident: the last one waits for peers
-  peer_lse_combine_kernel<<<static_cast<int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  const cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_chained(peer_lse_combine_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0,
+                                 static_cast<cudaStream_t>(stream), p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;
@@ -255,8 +261,9 @@ extern "C" int b200dsa_peer_barrier(void* const* bufs, int32_t rank, int32_t wor
   p.off_flags = off_flags;
   p.state = state;
   p.status = status;
-  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p, slot);
-  const cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_chained(peer_barrier_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), p,
+                                 static_cast<int>(slot));
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;

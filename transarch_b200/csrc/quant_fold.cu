@@ -13,6 +13,8 @@ namespace b200dsa {
 __global__ void __launch_bounds__(256) quant_q_fold_kernel(const __nv_bfloat16* __restrict__ q,
                                                            const float* __restrict__ w, int64_t n_rows, float fold,
                                                            uint8_t* __restrict__ q_fp8, float* __restrict__ weights) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
   const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (row >= n_rows) return;
   const int lane = threadIdx.x & 31;
@@ -51,9 +53,9 @@ extern "C" int b200dsa_quant_q_fold_weights(const void* q_bf16, const float* w, 
     return B200DSA_EALIGN;
   }
   const unsigned grid = static_cast<unsigned>((n_rows + 7) / 8);
-  quant_q_fold_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  cudaError_t e_launch = launch_chained(quant_q_fold_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16*>(q_bf16), w, n_rows, fold, static_cast<uint8_t*>(q_fp8), weights);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = e_launch != cudaSuccess ? e_launch : cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;

@@ -1,5 +1,6 @@
 // Host-side runtime shared by every entry point: last-error text, ABI version, and the
 // driver entry point used to encode TMA tensor maps.
+#include <stdlib.h>
 #include <string.h>
 
 #include "b200dsa_common.cuh"
@@ -25,6 +26,15 @@ PFN_encodeTiled get_encode_tiled() {
   }
   fn = reinterpret_cast<PFN_encodeTiled>(ptr);
   return fn;
+}
+
+bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("B200DSA_PDL");
+    on = (e && e[0] == '1') ? 1 : 0;
+  }
+  return on != 0;
 }
 
 }  // namespace b200dsa

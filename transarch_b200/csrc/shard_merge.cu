@@ -80,6 +80,8 @@ __global__ void __launch_bounds__(128) lse_finalize_kernel(const float* __restri
 __global__ void __launch_bounds__(256) compact_owned_kernel(const int32_t* __restrict__ idx, int64_t idx_stride, int n_idx,
                                                             int pos_lo, int pos_hi, int32_t* __restrict__ out,
                                                             int64_t out_stride, int32_t* __restrict__ count) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
   __shared__ int s_warp[8];
   __shared__ int s_base;
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -216,9 +218,9 @@ extern "C" int b200dsa_compact_owned(const int32_t* indices, int64_t idx_stride,
     set_last_error("b200dsa_compact_owned: bad argument (out must not alias indices)");
     return B200DSA_EINVAL;
   }
-  compact_owned_kernel<<<n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(indices, idx_stride, n_idx, pos_lo,
-                                                                             pos_hi, out, out_stride, count);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_chained(compact_owned_kernel, dim3(n_rows), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                                 indices, idx_stride, n_idx, pos_lo, pos_hi, out, out_stride, count);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;

@@ -136,6 +136,8 @@ __device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr, uint3
 
 __global__ void __launch_bounds__(kMlaThreads, 1)
 sparse_mla_decode_kernel(const MlaParams p) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
   extern __shared__ uint8_t smem_dyn[];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
@@ -543,8 +545,9 @@ extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16
   p.ctx_bf16 = ctx_bf16;
   p.lse = lse;
   p.status = status;
-  sparse_mla_decode_kernel<<<n_items * 2, kMlaThreads, kMlaSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
-  e = cudaGetLastError();
+  e = launch_chained(sparse_mla_decode_kernel, dim3(n_items * 2), dim3(kMlaThreads), kMlaSmemBytes,
+                     static_cast<cudaStream_t>(stream), p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;

@@ -350,6 +350,8 @@ __device__ SelectResult radix_select(ForEach&& for_each, int need, uint32_t* his
 }
 
 __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p, int k_pow2) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
   extern __shared__ __align__(16) uint8_t smem_raw[];
   uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw);
   uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + kHistBins * sizeof(uint32_t));
@@ -550,6 +552,8 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
 // Split mode.  Kernel 1 (one CTA per row) samples the row and stores the bin floor (or -1 when
 // the fast path does not apply: short rows, rows dominated by ties or invalid scores).
 __global__ void __launch_bounds__(1024, 1) topk_floor_kernel(const TopkParams p, int32_t* __restrict__ floor_out) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
   extern __shared__ __align__(16) uint8_t smem_raw[];
   uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw);
   __shared__ int s_res[3];
@@ -577,6 +581,8 @@ constexpr int kCollectSlots = kCandCap / kCollectThreads;  // 16 private entries
 
 __global__ void __launch_bounds__(kCollectThreads, 2)
 topk_collect_kernel(const TopkParams p, int splits, const int32_t* __restrict__ floor_in) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
   extern __shared__ __align__(16) uint8_t smem_raw[];
   uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw);  // [slot][thread]
   __shared__ int s_warp_tot[kCollectThreads / 32], s_base, s_overflow;
@@ -682,8 +688,8 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
     return B200DSA_ECUDA;
   }
   const int threads = n_cols > 16384 ? 1024 : 512;
-  topk_select_kernel<<<n_rows, threads, smem, static_cast<cudaStream_t>(stream)>>>(p, k_pow2);
-  e = cudaGetLastError();
+  e = launch_chained(topk_select_kernel, dim3(n_rows), dim3(threads), smem, static_cast<cudaStream_t>(stream), p, k_pow2);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;
@@ -725,10 +731,12 @@ extern "C" int b200dsa_topk_select_split(const float* scores, int64_t row_stride
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int32_t* floor_bin = scratch_count + n_rows;  // second half of the int32 scratch
-  topk_floor_kernel<<<n_rows, 1024, smem_f, st>>>(p, floor_bin);
-  topk_collect_kernel<<<dim3(splits, n_rows), kCollectThreads, smem_a, st>>>(p, splits, floor_bin);
-  topk_select_kernel<<<n_rows, 1024, smem_b, st>>>(p, k_pow2);
-  e = cudaGetLastError();
+  e = launch_chained(topk_floor_kernel, dim3(n_rows), dim3(1024), smem_f, st, p, floor_bin);
+  if (e == cudaSuccess)
+    e = launch_chained(topk_collect_kernel, dim3(splits, n_rows), dim3(kCollectThreads), smem_a, st, p, splits,
+                       static_cast<const int32_t*>(floor_bin));
+  if (e == cudaSuccess) e = launch_chained(topk_select_kernel, dim3(n_rows), dim3(1024), smem_b, st, p, k_pow2);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;
