@@ -216,11 +216,11 @@ def main():
             return run_eager(i)
         return graphed.replay(*dev_q[i % n_sets])
 
-    # End to end with HOST buffers, as a serving loop would run it: three streams and two slots, so the
+    # End to end with HOST buffers, as a serving loop would run it: three streams and four slots, so the
     # pinned-host -> device copy of step i+1 and the device -> host copy of step i-1 overlap the
     # kernels of step i.  Every step's inputs cross PCIe and every step's result reaches the host.
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-    slots = 2
+    slots = 4
     in_dev = [[torch.empty_like(x, device=dev) for x in dev_q[0]] for _ in range(slots)]
     out_dev = [(torch.empty(B, TOPK, dtype=torch.int32, device=dev),
                 torch.empty(B, HEADS, 512, dtype=ctx_dtype, device=dev)) for _ in range(slots)]
