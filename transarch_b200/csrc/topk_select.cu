@@ -349,13 +349,13 @@ __device__ SelectResult radix_select(ForEach&& for_each, int need, uint32_t* his
   return r;
 }
 
-__global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p, int k_pow2) {
+__global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p, int k_pow2, int cand_cap) {
   pdl_launch_dependents();
   pdl_wait_prior();
   extern __shared__ __align__(16) uint8_t smem_raw[];
   uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw);
   uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + kHistBins * sizeof(uint32_t));
-  uint64_t* eq = cand + kCandCap;
+  uint64_t* eq = cand + cand_cap;   // cand_cap <= kCandCap: rows that fit entirely get a smaller list
   uint64_t* sel = eq + kEqCap;  // k_pow2 entries
   __shared__ int s_eq_cnt, s_sel_cnt, s_res[3], s_warp_cnt[32], s_overflow;
   __shared__ uint32_t s_seg[32];
@@ -392,7 +392,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
 
   // ------------------------------------------------------------------ candidate collection
   const int warp_id = tid >> 5, lane_id = tid & 31, n_warps = nthr >> 5;
-  const int seg_cap = kCandCap / n_warps;
+  const int seg_cap = cand_cap / n_warps;
   uint64_t* my_seg = cand + warp_id * seg_cap;
   bool from_smem = false;
   int cnt = 0;  // total candidates
@@ -414,7 +414,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   }
   uint32_t bin_floor = 0;
   bool try_fast = !have_pre;
-  if (try_fast && n > kCandCap) try_fast = sample_bin_floor(p, src, begin, n, k, coff, hist, s_res, s_seg, &bin_floor);
+  if (try_fast && n > cand_cap) try_fast = sample_bin_floor(p, src, begin, n, k, coff, hist, s_res, s_seg, &bin_floor);
 
   // Each warp compacts its takes into its own segment of the candidate list with votes
   // only (no atomics); a full segment raises the overflow flag and the row falls back.
@@ -435,7 +435,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     }
     __syncthreads();
     for (int w = 0; w < n_warps; ++w) cnt += s_warp_cnt[w];
-    from_smem = (s_overflow == 0) && (cnt >= k || n <= kCandCap);
+    from_smem = (s_overflow == 0) && (cnt >= k || n <= cand_cap);
   }
 
   // ------------------------------------------------------------------ exact selection
@@ -448,7 +448,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
       }
       return;
     }
-    for (int base = 0; base < kCandCap; base += nthr) {
+    for (int base = 0; base < cand_cap; base += nthr) {
       const int i = base + tid;
       const int w = i / seg_cap;
       const bool active = (i - w * seg_cap) < s_warp_cnt[w];
@@ -679,7 +679,14 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
   }
   int k_pow2 = 32;
   while (k_pow2 < k) k_pow2 <<= 1;
-  const size_t smem = kHistBins * sizeof(uint32_t) + (kCandCap + kEqCap + k_pow2) * sizeof(uint64_t);
+  // rows that fit the candidate list entirely need no larger list than the row: smaller CTAs, more of
+  // them per SM (many short rows: block top-m, causal prefill)
+  int cand_cap = kCandCap;
+  if (n_cols <= kCandCap) {
+    cand_cap = 1024;
+    while (cand_cap < n_cols) cand_cap <<= 1;
+  }
+  const size_t smem = kHistBins * sizeof(uint32_t) + (static_cast<size_t>(cand_cap) + kEqCap + k_pow2) * sizeof(uint64_t);
   cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(kHistBins * sizeof(uint32_t) +
                                                         (2 * kCandCap + kEqCap) * sizeof(uint64_t)));
@@ -687,8 +694,9 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;
   }
-  const int threads = n_cols > 16384 ? 1024 : 512;
-  e = launch_chained(topk_select_kernel, dim3(n_rows), dim3(threads), smem, static_cast<cudaStream_t>(stream), p, k_pow2);
+  const int threads = n_cols > 16384 ? 1024 : (n_cols > 2048 ? 512 : 256);
+  e = launch_chained(topk_select_kernel, dim3(n_rows), dim3(threads), smem, static_cast<cudaStream_t>(stream), p, k_pow2,
+                     cand_cap);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
@@ -735,7 +743,8 @@ extern "C" int b200dsa_topk_select_split(const float* scores, int64_t row_stride
   if (e == cudaSuccess)
     e = launch_chained(topk_collect_kernel, dim3(splits, n_rows), dim3(kCollectThreads), smem_a, st, p, splits,
                        static_cast<const int32_t*>(floor_bin));
-  if (e == cudaSuccess) e = launch_chained(topk_select_kernel, dim3(n_rows), dim3(1024), smem_b, st, p, k_pow2);
+  if (e == cudaSuccess) e = launch_chained(topk_select_kernel, dim3(n_rows), dim3(1024), smem_b, st, p, k_pow2,
+                                             static_cast<int>(kCandCap));
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));

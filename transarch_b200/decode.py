@@ -98,7 +98,7 @@ class SparseDecodeStep:
         self.q_pos = torch.empty(batch, dtype=i32, device=dev)
         # few long rows: spread the top-k of every row over several CTAs (global scratch, allocated once)
         self.topk_scratch = None
-        if hasattr(backend, "topk_scratch") and batch <= 148 and max_local_ctx >= 32768:
+        if hasattr(backend, "topk_scratch") and batch <= 148 and max_local_ctx >= 16384:
             self.topk_scratch = backend.topk_scratch(batch, dev)
         self.peer = None
         if combine == "peer" and not (n > 1 and dist.is_initialized()):

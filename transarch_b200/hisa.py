@@ -50,13 +50,16 @@ def hisa_block_topk(q: torch.Tensor, k_pooled: torch.Tensor, w: torch.Tensor, ks
     bke = ((ke + P - 1) // P).to(torch.int32).clamp(max=nb).contiguous()
     logits = K.indexer_blocklist_bf16_logits(q, w, k_pooled, lists, row_cols, pos_lo=bks, pos_hi=bke,
                                              out_scale=sm_scale)
-    rows = torch.arange(T, device=dev)
-    has = bke > bks
-    inf = torch.tensor(float("inf"), device=dev)
+    # force-keep by a +inf score; rows without any valid block keep what they have (no host
+    # synchronisation: a scatter of either +inf or the value already there)
+    has = (bke > bks).view(-1, 1)
+    inf = torch.full((T, 1), float("inf"), device=dev)
     if cfg.keep_last_block:
-        logits[rows[has], (bke[has] - 1).long()] = inf
+        col = (bke - 1).clamp(min=0).long().view(-1, 1)
+        logits.scatter_(1, col, torch.where(has, inf, logits.gather(1, col)))
     if cfg.keep_first_block:
-        logits[rows[has], bks[has].long()] = inf
+        col = bks.clamp(max=logits.shape[1] - 1).long().view(-1, 1)
+        logits.scatter_(1, col, torch.where(has, inf, logits.gather(1, col)))
     return K.topk_select(logits, cfg.hisa_block_topk, keep_pos_inf=True, sorted=True)
 
 
