@@ -177,6 +177,75 @@ __device__ void bitonic_sort_desc(uint64_t* a, int n) {
   __syncthreads();
 }
 
+// The same sort with the keys in registers: thread t holds keys [E*t, E*t + E).  Strides below E
+// are compare-exchanges inside the thread, strides below 32*E go through warp shuffles, and only the
+// widest strides pass through shared memory (10 of the 66 stages of a 2048-key sort with 512
+// threads).  n must equal E * blockDim.x.
+template <int E>
+__device__ void bitonic_sort_desc_reg(uint64_t* a, int n) {
+  const int base = threadIdx.x * E;
+  uint64_t v[E];
+  __syncthreads();
+#pragma unroll
+  for (int e = 0; e < E; ++e) v[e] = a[base + e];
+  for (int size = 2; size <= n; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      if (stride >= 32 * E) {
+        __syncthreads();
+#pragma unroll
+        for (int e = 0; e < E; ++e) a[base + e] = v[e];
+        __syncthreads();
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const int idx = base + e;
+          const uint64_t other = a[idx ^ stride];
+          const bool want_max = ((idx & stride) != 0) != ((idx & size) == 0);
+          v[e] = (want_max == (v[e] > other)) ? v[e] : other;
+        }
+      } else if (stride >= E) {
+        const int lane_mask = stride / E;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const int idx = base + e;
+          const uint64_t other = __shfl_xor_sync(0xffffffffu, v[e], lane_mask);
+          const bool want_max = ((idx & stride) != 0) != ((idx & size) == 0);
+          v[e] = (want_max == (v[e] > other)) ? v[e] : other;
+        }
+      } else {
+#pragma unroll
+        for (int s = E >> 1; s > 0; s >>= 1) {
+          if (stride == s) {
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+              if ((e & s) == 0) {
+                const bool desc = ((base + e) & size) == 0;
+                const uint64_t x = v[e], y = v[e + s];
+                if ((x < y) == desc) {
+                  v[e] = y;
+                  v[e + s] = x;
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int e = 0; e < E; ++e) a[base + e] = v[e];
+  __syncthreads();
+}
+
+// Sort dispatcher: registers when the key count is 2, 4 or 8 times the thread count.
+__device__ void sort_desc(uint64_t* a, int n) {
+  const int per = n / static_cast<int>(blockDim.x);
+  if (per * static_cast<int>(blockDim.x) == n && per == 2) bitonic_sort_desc_reg<2>(a, n);
+  else if (per * static_cast<int>(blockDim.x) == n && per == 4) bitonic_sort_desc_reg<4>(a, n);
+  else if (per * static_cast<int>(blockDim.x) == n && per == 8) bitonic_sort_desc_reg<8>(a, n);
+  else bitonic_sort_desc(a, n);
+}
+
 // Find the highest bin d such that (#elements in bins >= d) >= need.  All threads call it
 // (it contains block barriers).  Writes res[0]=d (or -1 when the whole histogram holds fewer
 // than need), res[1]=count in bins above d, res[2]=hist[d].  Segment s (128 bins) covers bins
@@ -533,7 +602,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     int n_pow2 = 32;
     while (n_pow2 < n_sel) n_pow2 <<= 1;
     for (int i = n_sel + tid; i < n_pow2; i += nthr) sel[i] = 0;
-    bitonic_sort_desc(sel, n_pow2);
+    sort_desc(sel, n_pow2);
   }
   const int n_out = min(n_sel, k);
   for (int j = tid; j < k; j += nthr) {
