@@ -403,8 +403,8 @@ def main():
         line["roofline"]["traffic"] = DRAM_BYTES_PER_KEY * B * shard_len
         if world == 1 and not args.skip_cpu_baseline:
             threads = os.cpu_count() or 1
-            _, dt4 = cpu_port_tokens_per_s(4, ctx, threads)          # calibrate: about 10 s of CPU work
-            n_req = max(4, min(1024, int(10.0 / max(dt4 / 4, 1e-4))))
+            _, dt4 = cpu_port_tokens_per_s(4, ctx, threads)          # calibrate: about 15 s of CPU work
+            n_req = max(4, min(2048, int(15.0 / max(dt4 / 4, 1e-4))))
             v, dt = cpu_port_tokens_per_s(n_req, ctx, threads)
             line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
                                     "sample": f"{n_req} requests of the {B}-request batch shape at context {ctx}, "
