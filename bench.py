@@ -328,6 +328,35 @@ def main():
     for k_ in stage_ms:
         stage_ms[k_] /= args.steps
 
+    # Selection alone (q quantisation + indexer + top-k), replayed from its own CUDA graph: the
+    # "indexer + top-k per step" figure without the host's launch gaps of the eager stage split above.
+    select_us = None
+    if graphed is not None:
+        sel_q, sel_w, _ = dev_q[0]
+        s_cap = torch.cuda.Stream(device=dev)
+        s_cap.wait_stream(torch.cuda.current_stream())
+        sel_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(s_cap):
+            with torch.cuda.graph(sel_graph, stream=s_cap):
+                step.select(sel_q, sel_w, state.k_cache, state.context_lens_local, state.block_table)
+        torch.cuda.current_stream().wait_stream(s_cap)
+        for _ in range(3):
+            sel_graph.replay()
+        sync_all()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(args.steps):
+            sel_graph.replay()
+        g1.record()
+        torch.cuda.synchronize()
+        select_ms = g0.elapsed_time(g1) / args.steps
+        if world > 1:
+            ts = torch.tensor([select_ms], device=dev)
+            dist.all_reduce(ts, op=dist.ReduceOp.MAX)
+            select_ms = float(ts.item())
+        select_us = 1e3 * select_ms
+        sel_graph.reset()
+
     # The dominant kernel by itself: back-to-back launches on the current stream between two events
     # (the per-stage times above include the host-side gaps of eager launches; these do not).
     reps = max(20, min(200, args.steps))
@@ -388,7 +417,11 @@ def main():
                        "launch": "eager" if graphed is None else "cuda-graph replay",
                        "l2": "inputs larger than L2 (index-key cache %.2f GB per GPU, 4 rotating query sets)"
                              % (idx_bytes / 1e9)},
-            "indexer_topk_us_per_step": 1e3 * (stage_ms["quant+indexer"] + stage_ms["topk"]),
+            "indexer_topk_us_per_step": select_us if select_us is not None
+            else 1e3 * (stage_ms["quant+indexer"] + stage_ms["topk"]),
+            # bytes the selection must move: keys + scales read, logits written once and read once
+            "indexer_topk_hbm_frac": (None if select_us is None else
+                                      (B * shard_len * (132 + 8)) / (select_us * 1e-6) / 1e9 / peaks["hbm_gbs"]),
             "stage_us": {k_: round(1e3 * v, 2) for k_, v in stage_ms.items()},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps, "h2d_copy_alone_ms": h2d_only_ms,
