@@ -239,6 +239,14 @@ int b200dsa_peer_lse_combine(void* const* bufs, int32_t rank, int32_t world, int
 int b200dsa_peer_barrier(void* const* bufs, int32_t rank, int32_t world, int64_t off_flags, int32_t slot,
                          int32_t* state, int32_t* status, void* stream);
 
+/* The same barrier followed, in the same kernel, by an all-gather: nbytes at off_src of every
+ * rank's buffer are copied into dst[r * nbytes ...] of LOCAL memory (16-byte peer loads, coalesced).
+ * state: two int32 of local device memory, zero before the first call.  Sizes and offsets are
+ * multiples of 16.  Replaces the NCCL all-gather of the per-shard top-k candidates. */
+int b200dsa_peer_gather(void* const* bufs, int32_t rank, int32_t world, int64_t off_src, int64_t nbytes,
+                        void* dst, int64_t off_flags, int32_t slot, int32_t* state, int32_t* status,
+                        void* stream);
+
 /* Exchange buffers.  peer_alloc: zeroed device allocation on the current device plus the 64-byte
  * CUDA IPC handle another process passes to peer_open (with ITS device current) to map it;
  * peer_close unmaps, peer_free releases the allocation in the owning process. */

@@ -192,6 +192,52 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerCombineParam
   if (tid == 0) p.state[0] = static_cast<int32_t>(step);
 }
 
+// Barrier + all-gather in one kernel: after the flag exchange every block copies its share of every
+// rank's `nbytes` at `off_src` into the local buffer dst[r * nbytes ...] with 16-byte loads, four in
+// flight per thread (element-wise peer loads of a consumer kernel would pay NVLink latency per element).
+// state: [0] launches completed, [1] blocks finished in this launch.
+__global__ void __launch_bounds__(256) peer_gather_kernel(const PeerCombineParams p, int slot, int64_t off_src,
+                                                          int64_t nbytes, unsigned char* __restrict__ dst) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
+  __shared__ int s_last;
+  const int tid = threadIdx.x;
+  const uint32_t step = static_cast<uint32_t>(*reinterpret_cast<volatile int32_t*>(p.state)) + 1u;
+  if (blockIdx.x == 0 && tid < p.world)
+    st_release_sys(reinterpret_cast<uint32_t*>(p.buf[tid] + p.off_flags) + slot * 8 + p.rank, step);
+  if (tid < p.world) {
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.buf[p.rank] + p.off_flags) + slot * 8 + tid;
+    if (!wait_step(mine, step)) atomicMax(p.status, kDevWaitTimeout);
+  }
+  __syncthreads();
+  const int64_t n16 = nbytes >> 4;                       // 16-byte words per rank
+  const int64_t total = n16 * p.world;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + tid; i < total; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t j = i + u * stride;
+      if (j < total) {
+        const int r = static_cast<int>(j / n16);
+        v[u] = ld_sys_v4(p.buf[r] + off_src + ((j - r * n16) << 4));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t j = i + u * stride;
+      if (j < total) reinterpret_cast<uint4*>(dst)[j] = v[u];
+    }
+  }
+  __syncthreads();
+  if (tid == 0) s_last = (atomicAdd(p.state + 1, 1) == static_cast<int>(gridDim.x) - 1);
+  __syncthreads();
+  if (s_last && tid == 0) {
+    p.state[1] = 0;
+    p.state[0] = static_cast<int32_t>(step);
+  }
+}
+
 void set_last_error(const char* msg);
 
 }  // namespace b200dsa
@@ -263,6 +309,42 @@ extern "C" int b200dsa_peer_barrier(void* const* bufs, int32_t rank, int32_t wor
   p.status = status;
   cudaError_t e = launch_chained(peer_barrier_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), p,
                                  static_cast<int>(slot));
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  return B200DSA_OK;
+}
+
+extern "C" int b200dsa_peer_gather(void* const* bufs, int32_t rank, int32_t world, int64_t off_src, int64_t nbytes,
+                                   void* dst, int64_t off_flags, int32_t slot, int32_t* state, int32_t* status,
+                                   void* stream) {
+  if (!bufs || !dst || !state || !status || world < 1 || world > kPeerMaxRanks || rank < 0 || rank >= world ||
+      off_src < 0 || nbytes <= 0 || ((off_src | nbytes | off_flags) & 15) || off_flags < 0 ||
+      (reinterpret_cast<uintptr_t>(dst) & 15) || slot < 0 || slot > 7 || slot == 0 || slot == 2) {
+    set_last_error("b200dsa_peer_gather: bad argument (1 <= world <= 8, slot 1 or 3..7, 16-byte aligned sizes)");
+    return B200DSA_EINVAL;
+  }
+  PeerCombineParams p{};
+  for (int r = 0; r < world; ++r) {
+    if (!bufs[r] || (reinterpret_cast<uintptr_t>(bufs[r]) & 15)) {
+      set_last_error("b200dsa_peer_gather: every rank's buffer must be mapped and 16-byte aligned");
+      return B200DSA_EALIGN;
+    }
+    p.buf[r] = static_cast<unsigned char*>(bufs[r]);
+  }
+  p.rank = rank;
+  p.world = world;
+  p.off_flags = off_flags;
+  p.state = state;
+  p.status = status;
+  int64_t grid = (nbytes / 16 * world + 1023) / 1024;
+  if (grid < 1) grid = 1;
+  if (grid > 148) grid = 148;          // every block waits for the peers: all must be resident
+  cudaError_t e = launch_chained(peer_gather_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0,
+                                 static_cast<cudaStream_t>(stream), p, static_cast<int>(slot), off_src, nbytes,
+                                 static_cast<unsigned char*>(dst));
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));

@@ -112,7 +112,6 @@ class SparseDecodeStep:
             self.ctx = self.peer.ctx.view(batch, n_heads, 512)
             self.lse = self.peer.lse.view(batch, n_heads)
             self.cand = self.peer.extra_of(self.peer.rank).view(i32).view(batch, 2 * topk)
-            self.seg_offsets = self.peer.element_offsets(4)
         if n > 1:
             self.cand_all = torch.empty(n, batch, 2 * topk, dtype=i32, device=dev)
             self.merged = torch.empty(batch, topk, dtype=i32, device=dev)
@@ -172,14 +171,11 @@ class SparseDecodeStep:
         """All-gather the per-rank candidates and select the global top-k (identical on every rank)."""
         n, k = self.shard.world_size, self.topk
         if self.peer is not None:
-            # no gather: after a node-wide barrier the merge reads every rank's candidates where they lie
-            self.peer.barrier(slot=1)
-            flat = self.cand.view(-1)
-            self.K.topk_select(flat[k:].view(torch.float32).view(1, -1), k, sorted=self.sorted_topk,
-                               pos_map=flat.view(1, -1), out=self.merged, n_cols=n * k, row_stride=2 * k,
-                               seg_cols=k, seg_offsets=self.seg_offsets, n_rows=self.B, pos_map_stride=2 * k)
-            return self.merged
-        dist.all_gather_into_tensor(self.cand_all.view(-1), self.cand.view(-1), group=self.shard.group)
+            # one kernel: node-wide barrier, then coalesced 16-byte peer loads of every rank's candidates
+            # into the local receive buffer (same layout as the NCCL all-gather delivers)
+            self.peer.gather_extra(self.cand_all, slot=1)
+        else:
+            dist.all_gather_into_tensor(self.cand_all.view(-1), self.cand.view(-1), group=self.shard.group)
         flat = self.cand_all.view(-1)
         scores = flat[k:].view(torch.float32)        # segment r, row b starts at r*B*2k + b*2k + k
         pos = flat                                   # positions start at r*B*2k + b*2k

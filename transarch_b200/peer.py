@@ -128,7 +128,7 @@ class PeerLseCombine:
         self.off_extra = self.off_flags + 256
         self.extra_bytes = extra_bytes
         self.buffers = PeerBuffers(self.off_extra + extra_bytes, device, group, emulate_world)
-        self.barrier_state = torch.zeros(8, dtype=torch.int32, device=device)
+        self.barrier_state = torch.zeros(16, dtype=torch.int32, device=device)
         self.rank, self.world = self.buffers.rank, self.buffers.world
         self.state = [torch.zeros(2, dtype=torch.int32, device=device) for _ in range(emulate_world or 1)]
         v = self.views_of(self.rank)
@@ -156,8 +156,20 @@ class PeerLseCombine:
         their buffers before their call can be read from this rank afterwards."""
         rc = _lib.load().b200dsa_peer_barrier(
             self.buffers._addr_array, self.rank, self.world, self.off_flags, slot,
-            ptr(self.barrier_state[slot:slot + 1]), ptr(status_word(self.buffers.device)), stream_ptr())
+            ptr(self.barrier_state[2 * slot - 2:2 * slot - 1]), ptr(status_word(self.buffers.device)), stream_ptr())
         check(rc, "b200dsa_peer_barrier")
+
+    def gather_extra(self, dst: torch.Tensor, slot: int = 1) -> torch.Tensor:
+        """Barrier, then copy the extra area of every rank into dst (local, contiguous,
+        world * extra_bytes bytes, rank-major); see b200dsa_peer_gather."""
+        if not dst.is_contiguous() or dst.numel() * dst.element_size() != self.world * self.extra_bytes:
+            raise _lib.B200DSAError("dst must be contiguous with world * extra_bytes bytes")
+        rc = _lib.load().b200dsa_peer_gather(
+            self.buffers._addr_array, self.rank, self.world, self.off_extra, self.extra_bytes, ptr(dst),
+            self.off_flags, slot, ptr(self.barrier_state[2 * slot - 2:2 * slot]),
+            ptr(status_word(self.buffers.device)), stream_ptr())
+        check(rc, "b200dsa_peer_gather")
+        return dst
 
     def run(self, rank: Optional[int] = None, no_sync: bool = False):
         """Launch on the current stream.  `rank` / no_sync are for single-GPU emulation only: there the
