@@ -331,31 +331,56 @@ def main():
     # Selection alone (q quantisation + indexer + top-k), replayed from its own CUDA graph: the
     # "indexer + top-k per step" figure without the host's launch gaps of the eager stage split above.
     select_us = None
-    if graphed is not None:
-        sel_q, sel_w, _ = dev_q[0]
+    partial_us = {}
+
+    def graph_time(fn):
+        """us per replay of fn captured into its own CUDA graph (max over ranks)."""
         s_cap = torch.cuda.Stream(device=dev)
         s_cap.wait_stream(torch.cuda.current_stream())
-        sel_graph = torch.cuda.CUDAGraph()
+        gr = torch.cuda.CUDAGraph()
         with torch.cuda.stream(s_cap):
-            with torch.cuda.graph(sel_graph, stream=s_cap):
-                step.select(sel_q, sel_w, state.k_cache, state.context_lens_local, state.block_table)
+            with torch.cuda.graph(gr, stream=s_cap):
+                fn()
         torch.cuda.current_stream().wait_stream(s_cap)
         for _ in range(3):
-            sel_graph.replay()
+            gr.replay()
         sync_all()
         g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         g0.record()
         for _ in range(args.steps):
-            sel_graph.replay()
+            gr.replay()
         g1.record()
         torch.cuda.synchronize()
-        select_ms = g0.elapsed_time(g1) / args.steps
+        ms = g0.elapsed_time(g1) / args.steps
         if world > 1:
-            ts = torch.tensor([select_ms], device=dev)
+            ts = torch.tensor([ms], device=dev)
             dist.all_reduce(ts, op=dist.ReduceOp.MAX)
-            select_ms = float(ts.item())
-        select_us = 1e3 * select_ms
-        sel_graph.reset()
+            ms = float(ts.item())
+        gr.reset()
+        return 1e3 * ms
+
+    if graphed is not None:
+        sel_q, sel_w, sel_lat = dev_q[0]
+
+        def do_select():
+            return step.select(sel_q, sel_w, state.k_cache, state.context_lens_local, state.block_table)
+
+        select_us = graph_time(do_select)
+        if world > 1:
+            # prefixes of the sharded step, each from its own graph: the differences are the exchange stages
+            def upto_merge():
+                do_select()
+                return step.merge_candidates()
+
+            def upto_attend():
+                idx_ = upto_merge()
+                step.attend(sel_lat, state.kv, state.kv_row_base, idx_, state.context_lens, q_pos_bias=-1)
+
+            t_merge = graph_time(upto_merge)
+            t_att = graph_time(upto_attend)
+            partial_us = {"select": round(select_us, 2), "exchange+merge": round(t_merge - select_us, 2),
+                          "compact+attention": round(t_att - t_merge, 2),
+                          "combine": round(1e3 * ms_per_step - t_att, 2)}
 
     # The dominant kernel by itself: back-to-back launches on the current stream between two events
     # (the per-stage times above include the host-side gaps of eager launches; these do not).
@@ -423,6 +448,7 @@ def main():
             "indexer_topk_hbm_frac": (None if select_us is None else
                                       (B * shard_len * (132 + 8)) / (select_us * 1e-6) / 1e9 / peaks["hbm_gbs"]),
             "stage_us": {k_: round(1e3 * v, 2) for k_, v in stage_ms.items()},
+            "graph_stage_us": partial_us,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps, "h2d_copy_alone_ms": h2d_only_ms,
                     "h2d_copy_alone_gbs": h2d / (h2d_only_ms * 1e-3) / 1e9},

@@ -117,13 +117,15 @@ __device__ __forceinline__ void stream_row(const float* __restrict__ src, int be
   if (vec_ok) {
     const int a0 = begin & ~3;
     const int n4 = (begin + n - a0 + 3) >> 2;
-    const float4* src4 = reinterpret_cast<const float4*>(src + a0);
     for (int base = 0; base < n4; base += nthr * 4) {
       float4 v[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int i4 = base + u * nthr + tid;
-        v[u] = (i4 < n4) ? __ldg(src4 + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        // off() maps a column to its element offset (segmented rows: four aligned columns never
+        // straddle a segment, the caller checked that segment sizes and offsets are multiples of 4)
+        v[u] = (i4 < n4) ? __ldg(reinterpret_cast<const float4*>(src + off(a0 + 4 * i4)))
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -438,7 +440,11 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   end = min(end, p.n_cols);
   const int n = end - begin;
   const float* src = p.scores + row * p.row_stride;
-  const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.scores) & 15) == 0) && ((p.row_stride & 3) == 0) && p.seg_cols <= 0;
+  bool vec_ok = ((reinterpret_cast<uintptr_t>(p.scores) & 15) == 0) && ((p.row_stride & 3) == 0);
+  if (p.seg_cols > 0) {
+    vec_ok = vec_ok && ((p.seg_cols & 3) == 0) && ((p.seg_stride & 3) == 0);
+    for (int r = 0; r < p.seg_off_n; ++r) vec_ok = vec_ok && ((p.seg_off[r] & 3) == 0);
+  }
   auto coff = [&](int col) { return col_offset(p, col); };
   int32_t* out_idx = p.out_idx + row * p.out_stride;
   float* out_val = p.out_val ? p.out_val + row * p.out_stride : nullptr;
@@ -763,7 +769,7 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;
   }
-  const int threads = n_cols > 16384 ? 1024 : (n_cols > 2048 ? 512 : 256);
+  const int threads = n_cols > 8192 ? 1024 : (n_cols > 2048 ? 512 : 256);
   e = launch_chained(topk_select_kernel, dim3(n_rows), dim3(threads), smem, static_cast<cudaStream_t>(stream), p, k_pow2,
                      cand_cap);
   if (e == cudaSuccess) e = cudaGetLastError();
