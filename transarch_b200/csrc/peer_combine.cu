@@ -90,7 +90,7 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float* a) {
   return v;
 }
 
-__global__ void __launch_bounds__(256) peer_lse_combine_kernel(const PeerCombineParams p) {
+__global__ void __launch_bounds__(256, 2) peer_lse_combine_kernel(const PeerCombineParams p) {
   // nothing may be signalled to the peers before the kernels that produced this rank's partial are done
   pdl_launch_dependents();
   pdl_wait_prior();
@@ -114,15 +114,7 @@ __global__ void __launch_bounds__(256) peer_lse_combine_kernel(const PeerCombine
   const int64_t r_end = r_begin + per < p.n_rows ? r_begin + per : p.n_rows;
   const int64_t warps_total = static_cast<int64_t>(gridDim.x) * 8;
   for (int64_t row = r_begin + static_cast<int64_t>(blockIdx.x) * 8 + warp; row < r_end; row += warps_total) {
-    float l = -INFINITY;
-    if (lane < p.world) l = ld_sys_f32(reinterpret_cast<const float*>(p.buf[lane] + p.off_lse) + row);
-    float m = l;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    const float w = (l == -INFINITY) ? 0.f : expf(l - m);
-    float den = w;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+    // every load of the row is issued before the first use: one NVLink round trip per row, not two
     uint4 va[kPeerMaxRanks], vb[kPeerMaxRanks];
 #pragma unroll
     for (int r = 0; r < kPeerMaxRanks; ++r) {
@@ -132,6 +124,15 @@ __global__ void __launch_bounds__(256) peer_lse_combine_kernel(const PeerCombine
         vb[r] = ld_sys_v4(src + 512);
       }
     }
+    float l = -INFINITY;
+    if (lane < p.world) l = ld_sys_f32(reinterpret_cast<const float*>(p.buf[lane] + p.off_lse) + row);
+    float m = l;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float w = (l == -INFINITY) ? 0.f : expf(l - m);
+    float den = w;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
     float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     const float inv = den > 0.f ? 1.0f / den : 0.f;
 #pragma unroll
@@ -157,10 +158,14 @@ __global__ void __launch_bounds__(256) peer_lse_combine_kernel(const PeerCombine
     if (lane < p.world) reinterpret_cast<float*>(p.buf[lane] + p.off_lse_out)[row] = lse_out;
   }
 
-  // ---- 3. all slices written everywhere
-  __threadfence_system();
+  // ---- 3. all slices written everywhere.  One system-scope fence per block, after the block barrier
+  //         (the barrier orders the other threads' peer stores before it).  Draining the peer stores is
+  //         the longest phase of the kernel (about 19 of 43 us at two ranks, cycle counters).
   __syncthreads();
-  if (tid == 0) s_last = (atomicAdd(p.state + 1, 1) == static_cast<int>(gridDim.x) - 1);
+  if (tid == 0) {
+    __threadfence_system();
+    s_last = (atomicAdd(p.state + 1, 1) == static_cast<int>(gridDim.x) - 1);
+  }
   __syncthreads();
   if (s_last) {
     __threadfence();
@@ -276,7 +281,7 @@ extern "C" int b200dsa_peer_lse_combine(void* const* bufs, int32_t rank, int32_t
   const int64_t per = (n_rows + world - 1) / world;
   int64_t grid = (per + 7) / 8;
   if (grid < 1) grid = 1;
-  if (grid > 148) grid = 148;          // every block must be resident: the last one waits for peers
+  if (grid > 296) grid = 296;          // every block must be resident (2 per SM): all of them wait for peers
   cudaError_t e = launch_chained(peer_lse_combine_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0,
                                  static_cast<cudaStream_t>(stream), p);
   if (e == cudaSuccess) e = cudaGetLastError();
