@@ -198,10 +198,10 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerCombineParam
 }
 
 // Barrier + all-gather in one kernel: after the flag exchange every block copies its share of every
-// rank's `nbytes` at `off_src` into the local buffer dst[r * nbytes ...] with 16-byte loads, four in
+// rank's `nbytes` at `off_src` into the local buffer dst[r * nbytes ...] with 16-byte loads, eight in
 // flight per thread (element-wise peer loads of a consumer kernel would pay NVLink latency per element).
 // state: [0] launches completed, [1] blocks finished in this launch.
-__global__ void __launch_bounds__(256) peer_gather_kernel(const PeerCombineParams p, int slot, int64_t off_src,
+__global__ void __launch_bounds__(256, 2) peer_gather_kernel(const PeerCombineParams p, int slot, int64_t off_src,
                                                           int64_t nbytes, unsigned char* __restrict__ dst) {
   pdl_launch_dependents();
   pdl_wait_prior();
@@ -218,10 +218,10 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const PeerCombineParam
   const int64_t n16 = nbytes >> 4;                       // 16-byte words per rank
   const int64_t total = n16 * p.world;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + tid; i < total; i += 4 * stride) {
-    uint4 v[4];
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + tid; i < total; i += 8 * stride) {
+    uint4 v[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 8; ++u) {
       const int64_t j = i + u * stride;
       if (j < total) {
         const int r = static_cast<int>(j / n16);
@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const PeerCombineParam
       }
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 8; ++u) {
       const int64_t j = i + u * stride;
       if (j < total) reinterpret_cast<uint4*>(dst)[j] = v[u];
     }
@@ -344,9 +344,9 @@ extern "C" int b200dsa_peer_gather(void* const* bufs, int32_t rank, int32_t worl
   p.off_flags = off_flags;
   p.state = state;
   p.status = status;
-  int64_t grid = (nbytes / 16 * world + 1023) / 1024;
+  int64_t grid = (nbytes / 16 * world + 2047) / 2048;
   if (grid < 1) grid = 1;
-  if (grid > 148) grid = 148;          // every block waits for the peers: all must be resident
+  if (grid > 296) grid = 296;          // two blocks per SM: the whole 8-rank payload is in flight at once
   cudaError_t e = launch_chained(peer_gather_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0,
                                  static_cast<cudaStream_t>(stream), p, static_cast<int>(slot), off_src, nbytes,
                                  static_cast<unsigned char*>(dst));
