@@ -247,6 +247,14 @@ int b200dsa_peer_gather(void* const* bufs, int32_t rank, int32_t world, int64_t 
                         void* dst, int64_t off_flags, int32_t slot, int32_t* state, int32_t* status,
                         void* stream);
 
+/* All-gather by posted stores: nbytes at off_src of THIS rank's buffer are stored into slot `rank`
+ * (off_dst + rank * nbytes) of EVERY rank's buffer; the call's kernel ends when all peers' slots
+ * have landed in this rank's buffer.  One NVLink crossing per byte, no load round trip.  state: two
+ * int32 of local device memory, zero before the first call. */
+int b200dsa_peer_push(void* const* bufs, int32_t rank, int32_t world, int64_t off_src, int64_t nbytes,
+                      int64_t off_dst, int64_t off_flags, int32_t slot, int32_t* state, int32_t* status,
+                      void* stream);
+
 /* Exchange buffers.  peer_alloc: zeroed device allocation on the current device plus the 64-byte
  * CUDA IPC handle another process passes to peer_open (with ITS device current) to map it;
  * peer_close unmaps, peer_free releases the allocation in the owning process. */

@@ -37,6 +37,7 @@ SIGNATURES = {
     "b200dsa_peer_lse_combine": [_vp, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _i32, _vp, _vp],
     "b200dsa_peer_barrier": [_vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp],
     "b200dsa_peer_gather": [_vp, _i32, _i32, _i64, _i64, _vp, _i64, _i32, _vp, _vp, _vp],
+    "b200dsa_peer_push": [_vp, _i32, _i32, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _vp],
     "b200dsa_peer_alloc": [_i64, _vp, _vp],
     "b200dsa_peer_open": [_vp, _vp],
     "b200dsa_peer_close": [_vp],

@@ -243,6 +243,67 @@ __global__ void __launch_bounds__(256, 2) peer_gather_kernel(const PeerCombinePa
   }
 }
 
+__device__ __forceinline__ uint4 ld_plain_v4(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+
+// Block-wide "everything this grid stored so far is visible system-wide, and I am the last block":
+// one system fence per block after the block barrier (the barrier orders the other threads' stores
+// before it), then a ticket.  Returns true in every thread of the last block.
+__device__ __forceinline__ bool grid_ticket(int32_t* counter, int* s_last) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    *s_last = (atomicAdd(counter, 1) == static_cast<int>(gridDim.x) - 1);
+  }
+  __syncthreads();
+  const bool last = *s_last != 0;
+  if (last) {
+    if (threadIdx.x == 0) *counter = 0;
+    __threadfence();
+  }
+  return last;
+}
+
+// All-gather by posted stores: every rank copies `nbytes` at off_src of its own buffer into slot
+// `rank` of the area at off_dst of EVERY rank's buffer, fences, and tells the peers; the last block
+// leaves only when every peer's data has landed here, so the kernel after it reads local memory.
+// One NVLink crossing per byte and per flag, no round trip.  state: [0] launches completed, [1] ticket.
+__global__ void __launch_bounds__(256, 2) peer_push_kernel(const PeerCombineParams p, int slot, int64_t off_src,
+                                                           int64_t nbytes, int64_t off_dst) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
+  __shared__ int s_last;
+  const int tid = threadIdx.x;
+  const uint32_t step = static_cast<uint32_t>(*reinterpret_cast<volatile int32_t*>(p.state)) + 1u;
+  const int64_t n16 = nbytes >> 4;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
+  const unsigned char* src = p.buf[p.rank] + off_src;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + tid; i < n16; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (i + u * stride < n16) v[u] = ld_plain_v4(src + ((i + u * stride) << 4));
+#pragma unroll
+    for (int r = 0; r < kPeerMaxRanks; ++r) {
+      if (r < p.world) {
+        unsigned char* dst = p.buf[r] + off_dst + p.rank * nbytes;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (i + u * stride < n16) *reinterpret_cast<uint4*>(dst + ((i + u * stride) << 4)) = v[u];
+      }
+    }
+  }
+  const bool last = grid_ticket(p.state + 1, &s_last);
+  if (last) {
+    if (tid < p.world) {
+      st_release_sys(reinterpret_cast<uint32_t*>(p.buf[tid] + p.off_flags) + slot * 8 + p.rank, step);
+      const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.buf[p.rank] + p.off_flags) + slot * 8 + tid;
+      if (!wait_step(mine, step)) atomicMax(p.status, kDevWaitTimeout);
+    }
+    __syncthreads();
+    if (tid == 0) p.state[0] = static_cast<int32_t>(step);
+  }
+}
+
 void set_last_error(const char* msg);
 
 }  // namespace b200dsa
@@ -350,6 +411,41 @@ extern "C" int b200dsa_peer_gather(void* const* bufs, int32_t rank, int32_t worl
   cudaError_t e = launch_chained(peer_gather_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0,
                                  static_cast<cudaStream_t>(stream), p, static_cast<int>(slot), off_src, nbytes,
                                  static_cast<unsigned char*>(dst));
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  return B200DSA_OK;
+}
+
+extern "C" int b200dsa_peer_push(void* const* bufs, int32_t rank, int32_t world, int64_t off_src, int64_t nbytes,
+                                 int64_t off_dst, int64_t off_flags, int32_t slot, int32_t* state, int32_t* status,
+                                 void* stream) {
+  if (!bufs || !state || !status || world < 1 || world > kPeerMaxRanks || rank < 0 || rank >= world ||
+      off_src < 0 || off_dst < 0 || nbytes <= 0 || ((off_src | off_dst | nbytes | off_flags) & 15) || off_flags < 0 ||
+      slot < 0 || slot > 7 || slot == 0 || slot == 2) {
+    set_last_error("b200dsa_peer_push: bad argument (1 <= world <= 8, slot 1 or 3..7, 16-byte aligned sizes)");
+    return B200DSA_EINVAL;
+  }
+  PeerCombineParams p{};
+  for (int r = 0; r < world; ++r) {
+    if (!bufs[r] || (reinterpret_cast<uintptr_t>(bufs[r]) & 15)) {
+      set_last_error("b200dsa_peer_push: every rank's buffer must be mapped and 16-byte aligned");
+      return B200DSA_EALIGN;
+    }
+    p.buf[r] = static_cast<unsigned char*>(bufs[r]);
+  }
+  p.rank = rank;
+  p.world = world;
+  p.off_flags = off_flags;
+  p.state = state;
+  p.status = status;
+  int64_t grid = (nbytes / 16 + 1023) / 1024;
+  if (grid < 1) grid = 1;
+  if (grid > 296) grid = 296;
+  cudaError_t e = launch_chained(peer_push_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0,
+                                 static_cast<cudaStream_t>(stream), p, static_cast<int>(slot), off_src, nbytes, off_dst);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));

@@ -105,15 +105,20 @@ class SparseDecodeStep:
             raise ValueError("combine='peer' needs an initialised process group of more than one rank")
         if n > 1 and combine != "nccl" and dev.type == "cuda" and dist.is_initialized() and \
                 getattr(backend, "__name__", "").endswith(".kernels"):
-            self.peer = self._open_peer_combine(batch * n_heads, dev, combine == "peer", batch * 2 * topk * 4)
+            self.cand_bytes = batch * 2 * topk * 4
+            self.peer = self._open_peer_combine(batch * n_heads, dev, combine == "peer", self.cand_bytes * (1 + n))
         if self.peer is not None:
             # attention writes its normalised bf16 partial straight into the exchange buffer, the local
-            # top-k its (position, score) candidates: peers read both in place over NVLink
+            # top-k its (position, score) candidates; the exchange kernels push both to the peers
             self.ctx = self.peer.ctx.view(batch, n_heads, 512)
             self.lse = self.peer.lse.view(batch, n_heads)
-            self.cand = self.peer.extra_of(self.peer.rank).view(i32).view(batch, 2 * topk)
+            extra = self.peer.extra_of(self.peer.rank)
+            self.cand = extra[:self.cand_bytes].view(i32).view(batch, 2 * topk)
         if n > 1:
-            self.cand_all = torch.empty(n, batch, 2 * topk, dtype=i32, device=dev)
+            if self.peer is not None:     # receive area inside the exchange buffer: peers store into it
+                self.cand_all = self.peer.extra_of(self.peer.rank)[self.cand_bytes:].view(i32).view(n, batch, 2 * topk)
+            else:
+                self.cand_all = torch.empty(n, batch, 2 * topk, dtype=i32, device=dev)
             self.merged = torch.empty(batch, topk, dtype=i32, device=dev)
             self.owned = torch.empty(batch, topk, dtype=i32, device=dev)
             self.owned_count = torch.empty(batch, dtype=i32, device=dev)
@@ -171,9 +176,10 @@ class SparseDecodeStep:
         """All-gather the per-rank candidates and select the global top-k (identical on every rank)."""
         n, k = self.shard.world_size, self.topk
         if self.peer is not None:
-            # one kernel: node-wide barrier, then coalesced 16-byte peer loads of every rank's candidates
-            # into the local receive buffer (same layout as the NCCL all-gather delivers)
-            self.peer.gather_extra(self.cand_all, slot=1)
+            # one kernel: this rank's candidates are stored into its slot of every rank's receive area
+            # (posted NVLink stores, same layout as the NCCL all-gather delivers); it ends when all
+            # peers' slots have landed here
+            self.peer.push_extra(self.cand_bytes, slot=1)
         else:
             dist.all_gather_into_tensor(self.cand_all.view(-1), self.cand.view(-1), group=self.shard.group)
         flat = self.cand_all.view(-1)

@@ -159,13 +159,27 @@ class PeerLseCombine:
             ptr(self.barrier_state[2 * slot - 2:2 * slot - 1]), ptr(status_word(self.buffers.device)), stream_ptr())
         check(rc, "b200dsa_peer_barrier")
 
-    def gather_extra(self, dst: torch.Tensor, slot: int = 1) -> torch.Tensor:
-        """Barrier, then copy the extra area of every rank into dst (local, contiguous,
-        world * extra_bytes bytes, rank-major); see b200dsa_peer_gather."""
-        if not dst.is_contiguous() or dst.numel() * dst.element_size() != self.world * self.extra_bytes:
-            raise _lib.B200DSAError("dst must be contiguous with world * extra_bytes bytes")
+    def push_extra(self, nbytes: int, slot: int = 1) -> torch.Tensor:
+        """All-gather by posted stores (b200dsa_peer_push): the first nbytes of this rank's extra area
+        are stored into slot `rank` of the receive area that follows it in EVERY rank's extra area
+        (extra_bytes >= nbytes * (1 + world)).  Returns the local receive area, uint8 [world, nbytes]."""
+        if nbytes * (1 + self.world) > self.extra_bytes:
+            raise _lib.B200DSAError("extra area too small for nbytes * (1 + world)")
+        rc = _lib.load().b200dsa_peer_push(
+            self.buffers._addr_array, self.rank, self.world, self.off_extra, nbytes, self.off_extra + nbytes,
+            self.off_flags, slot, ptr(self.barrier_state[2 * slot - 2:2 * slot]),
+            ptr(status_word(self.buffers.device)), stream_ptr())
+        check(rc, "b200dsa_peer_push")
+        return self.extra_of(self.rank)[nbytes:nbytes * (1 + self.world)].view(self.world, nbytes)
+
+    def gather_extra(self, dst: torch.Tensor, slot: int = 1, nbytes: Optional[int] = None) -> torch.Tensor:
+        """Barrier, then copy the first nbytes (default: all) of the extra area of every rank into dst
+        (local, contiguous, world * nbytes bytes, rank-major) with peer loads; see b200dsa_peer_gather."""
+        nbytes = self.extra_bytes if nbytes is None else nbytes
+        if not dst.is_contiguous() or dst.numel() * dst.element_size() != self.world * nbytes:
+            raise _lib.B200DSAError("dst must be contiguous with world * nbytes bytes")
         rc = _lib.load().b200dsa_peer_gather(
-            self.buffers._addr_array, self.rank, self.world, self.off_extra, self.extra_bytes, ptr(dst),
+            self.buffers._addr_array, self.rank, self.world, self.off_extra, nbytes, ptr(dst),
             self.off_flags, slot, ptr(self.barrier_state[2 * slot - 2:2 * slot]),
             ptr(status_word(self.buffers.device)), stream_ptr())
         check(rc, "b200dsa_peer_gather")
