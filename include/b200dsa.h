@@ -255,6 +255,13 @@ int b200dsa_peer_push(void* const* bufs, int32_t rank, int32_t world, int64_t of
                       int64_t off_dst, int64_t off_flags, int32_t slot, int32_t* state, int32_t* status,
                       void* stream);
 
+/* Bound of every wait for a peer's flag in the four peer kernels above, in SM clock cycles (default
+ * 2^31, about a second; 0 restores the default).  Process-wide; takes effect for launches made after
+ * the call.  A serving loop that prefers a quick error over a second-long stall when a peer is gone
+ * lowers it; when a wait runs out the kernel sets *status to 1, still advances its step counter and
+ * ends, so the stream and the context stay usable and the host can decide what to do. */
+int b200dsa_peer_set_wait_limit(int64_t cycles);
+
 /* Exchange buffers.  peer_alloc: zeroed device allocation on the current device plus the 64-byte
  * CUDA IPC handle another process passes to peer_open (with ITS device current) to map it;
  * peer_close unmaps, peer_free releases the allocation in the owning process. */
@@ -289,7 +296,10 @@ int b200dsa_lse_prescale_norm(const float* ctx, const float* lse_all, int32_t n_
 
 /* ---------------------------------------------------------------------------------------
  * FP8 quantisation of the index queries with the scale folded into the head weights:
- *   scale = max(amax|q[t,h,:]|, 1e-4)/448, q_fp8 = e4m3(q/scale), weights = w * scale * fold.
+ *   scale = max(amax|q[t,h,:]|, 1e-10)/448, q_fp8 = e4m3(q/scale), weights = w * scale * fold.
+ * use_ue8m0 != 0 rounds the scale UP to a power of two first, scale = 2^ceil(log2(scale)): the
+ * "ue8m0" scale format the reference always asks for (scale_fmt is "ue8m0" at
+ * misa_deepseek_v2.py:177, passed as use_ue8m0=self.scale_fmt is not None at :280-285).
  * Replaces MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/misa_deepseek_v2.py:279-292
  * (per_token_group_quant_fp8 over the 128-wide head + weight folding; fold carries
  * softmax_scale * n_head**-0.5 there).
@@ -297,7 +307,7 @@ int b200dsa_lse_prescale_norm(const float* ctx, const float* lse_all, int32_t n_
  *   q_fp8 [n_rows, 128] e4m3 out, weights [n_rows] fp32 out.
  * ------------------------------------------------------------------------------------- */
 int b200dsa_quant_q_fold_weights(const void* q_bf16, const float* w, int64_t n_rows, float fold,
-                                 void* q_fp8, float* weights, void* stream);
+                                 int32_t use_ue8m0, void* q_fp8, float* weights, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Block mean pooling of index keys: pooled[j] = mean(keys[j*block : min((j+1)*block, n)]),
@@ -328,8 +338,9 @@ int b200dsa_paged_mean_pool_fp8(const void* cache, int32_t num_pages, int32_t pa
  *               misa_ops.py:694-705 and :380-388.  pooled_keys is fp32 [n_sets, pooled_set_stride/128, 128];
  *               pooled_set (optional) maps a token to its set (decode: the request).
  *  linear     : logits = x[t,:] @ W_r (bf16 inputs, fp32 accumulate), top-n heads, weights =
- *               softmax over the kept logits.  No counterpart in the reference (the router the
- *               benchmark configuration describes); logits_out optional.
+ *               softmax over the kept logits.  No counterpart in the reference: a learned
+ *               router reading the token's hidden state (hidden = 7168, n = 8 of 64 heads in the
+ *               DeepSeek-V3.2 shape) instead of the query norms; logits_out optional.
  * ------------------------------------------------------------------------------------- */
 int b200dsa_router_qnorm_topk(const void* q_bf16, const float* w, int32_t n_tokens, int32_t n_keep,
                               float* weights_out, int32_t* head_idx, void* stream);
@@ -344,15 +355,16 @@ int b200dsa_router_linear_topk_softmax(const void* x_bf16, const void* w_r_bf16,
 
 /* ---------------------------------------------------------------------------------------
  * Insert new index keys into the paged FP8 cache: per-token e4m3 quantisation
- * (scale = max(amax,1e-4)/448) written to slot_mapping[t] = page*page_size + offset
- * (negative = skip).  Stands in for the third-party vLLM op the reference calls at
+ * (scale = max(amax,1e-4)/448, rounded up to a power of two when use_ue8m0 != 0, which is what
+ * the reference's scale_fmt = "ue8m0" selects) written to slot_mapping[t] = page*page_size +
+ * offset (negative = skip).  Stands in for the third-party vLLM op the reference calls at
  * MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/indexers.py:454-460
  * (ops.indexer_k_quant_and_cache), producing the page layout read at misa_ops.py:360-372.
  *   k_bf16 [n_tokens, 128], slot_mapping int64 [n_tokens], cache [num_pages, page_size*132].
  * ------------------------------------------------------------------------------------- */
 int b200dsa_indexer_k_quant_and_cache(const void* k_bf16, const int64_t* slot_mapping, int64_t n_tokens,
-                                      void* cache, int64_t num_pages, int32_t page_size, int32_t* status,
-                                      void* stream);
+                                      void* cache, int64_t num_pages, int32_t page_size, int32_t use_ue8m0,
+                                      int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -158,13 +158,27 @@ def lse_combine(ctx_parts, lse_parts):
 FP8_MAX = 448.0
 
 
-def quant_fp8_rows(x: torch.Tensor):
-    """Per-row e4m3 quantisation, scale = amax/448 (fp32).  Values the reference receives
-    from vLLM's indexer_k_quant_and_cache (call site
-    MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/indexers.py:454-460)."""
+def pow2_round_up(x: torch.Tensor) -> torch.Tensor:
+    """Smallest power of two >= x for positive finite x: exp2(ceil(log2(x))), the "ue8m0" scale
+    format, evaluated exactly through frexp (x = m * 2**e with 0.5 <= m < 1)."""
+    m, e = torch.frexp(x.float())
+    return torch.ldexp(torch.ones_like(m), torch.where(m > 0.5, e, e - 1))
+
+
+def quant_fp8_rows(x: torch.Tensor, ue8m0: bool = False, eps: float = 1e-4):
+    """Per-row e4m3 quantisation, scale = max(amax, eps)/448 (fp32), rounded up to a power of two
+    when ue8m0.  Published behaviour of the two third-party vLLM (pinned 0.17.0) quantisers the
+    reference calls, neither of which is under the TransArch checkout:
+      * keys: ops.indexer_k_quant_and_cache(k, kv_cache, slot_mapping, quant_block_size, scale_fmt)
+        at MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/indexers.py:454-460, eps = 1e-4,
+        ue8m0 when scale_fmt == "ue8m0" (the reference sets it so, misa_deepseek_v2.py:177);
+      * queries: per_token_group_quant_fp8(q, 128, use_ue8m0=scale_fmt is not None) at
+        misa_deepseek_v2.py:280-285, eps = 1e-10."""
     xf = x.float()
-    amax = xf.abs().amax(dim=-1, keepdim=True).clamp_min(1e-4)
+    amax = xf.abs().amax(dim=-1, keepdim=True).clamp_min(eps)
     scale = amax / FP8_MAX
+    if ue8m0:
+        scale = pow2_round_up(scale)
     q = (xf / scale).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
     return q, scale.squeeze(-1).contiguous()
 
@@ -233,13 +247,15 @@ def paged_indexer_logits(q, cache, w, context_lens, block_table, page_size, max_
     return out
 
 
-def quant_q_fold_weights(q: torch.Tensor, w: torch.Tensor, sm_scale: float, head_scale: float = 1.0):
+def quant_q_fold_weights(q: torch.Tensor, w: torch.Tensor, sm_scale: float, head_scale: float = 1.0,
+                         ue8m0: bool = False):
     """q -> e4m3 per (token, head) with its scale folded into the head weight.
     MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/misa_deepseek_v2.py:279-292
     (weights = w * q_scale * softmax_scale * n_head**-0.5; there the n_head factor is
-    applied here, in OpenDSA it is already inside w, hence head_scale)."""
+    applied here, in OpenDSA it is already inside w, hence head_scale).  ue8m0 is the
+    use_ue8m0 flag of :280-285 (True in the reference, whose scale_fmt is never None)."""
     T_, H, D = q.shape
-    q_fp8, q_scale = quant_fp8_rows(q.reshape(T_ * H, D))
+    q_fp8, q_scale = quant_fp8_rows(q.reshape(T_ * H, D), ue8m0=ue8m0, eps=1e-10)
     weights = w.float() * q_scale.view(T_, H) * (sm_scale * head_scale)
     return q_fp8.view(T_, H, D), weights
 
@@ -284,9 +300,12 @@ def hisa_block_logits(q, k_blk, w, ks, ke, block, sm_scale=None,
 
 def hisa_select_topk(q, k, w, ks, ke, *, block=128, block_topk=64, topk=2048,
                      sm_scale=None, keep_first=False, keep_last=True, q_chunk=64,
-                     return_blocks=False):
+                     return_blocks=False, blocks=None, return_scores=False):
     """HISA: pool -> block top-m -> token scores inside the chosen blocks -> top-k.
-    Returns int32 [T, topk] absolute positions (-1 padded).  Parity unpinned."""
+    Returns int32 [T, topk] absolute positions (-1 padded).  Parity unpinned.
+    blocks (int32 [T, m], -1 padded): skip stage 1 and run stage 2 inside these blocks (to check
+    stage 2 by itself).  return_scores adds the stage-2 scores as a dense [T, S_padded] tensor
+    (-inf outside the chosen blocks) for near-tie audits."""
     T_ = q.shape[0]
     S = k.shape[0]
     k_blk = block_mean_pool(k, block)
@@ -297,11 +316,16 @@ def hisa_select_topk(q, k, w, ks, ke, *, block=128, block_topk=64, topk=2048,
     kf = k.float()
     if pad:
         kf = torch.cat([kf, torch.zeros(pad, k.shape[1])], 0)
+    given = blocks
+    dense = torch.full((T_, nb * block), NEG_INF) if return_scores else None
     for t0 in range(0, T_, q_chunk):
         t1 = min(t0 + q_chunk, T_)
-        bl = hisa_block_logits(q[t0:t1], k_blk, w[t0:t1], ks[t0:t1], ke[t0:t1], block,
-                               sm_scale, keep_first, keep_last)
-        blocks = topk_rows(bl, block_topk, keep_pos_inf=True)                       # [c,m] (-1 padded)
+        if given is None:
+            bl = hisa_block_logits(q[t0:t1], k_blk, w[t0:t1], ks[t0:t1], ke[t0:t1], block,
+                                   sm_scale, keep_first, keep_last)
+            blocks = topk_rows(bl, block_topk, keep_pos_inf=True)                   # [c,m] (-1 padded)
+        else:
+            blocks = given[t0:t1]
         blocks_out[t0:t1] = blocks
         for i in range(t1 - t0):
             t = t0 + i
@@ -312,14 +336,15 @@ def hisa_select_topk(q, k, w, ks, ke, *, block=128, block_topk=64, topk=2048,
             sc = indexer_scores(q[t:t + 1], kf[pos], w[t:t + 1], sm_scale)[0]
             ok = (pos >= ks[t]) & (pos < ke[t])
             sc = sc.masked_fill(~ok, NEG_INF)
+            if dense is not None:
+                dense[t, pos] = sc
             pick = topk_rows(sc.view(1, -1), topk)[0]
             good = pick >= 0
             res = torch.full((topk,), -1, dtype=torch.int32)
             res[good] = pos[pick[good].long()].to(torch.int32)
             out[t] = res
-    if return_blocks:
-        return out, blocks_out
-    return out
+    res = (out,) + ((blocks_out,) if return_blocks else ()) + ((dense,) if return_scores else ())
+    return res if len(res) > 1 else out
 
 
 # --------------------------------------------------------------------------- #
@@ -371,6 +396,46 @@ def misa_mqa_logits(q, k, w, head_idx, ks, ke, stage1_topk, sm_scale=1.0):
 
 
 # --------------------------------------------------------------------------- #
+# one request of the decode step, end to end
+# --------------------------------------------------------------------------- #
+def decode_request_reference(q_idx, w, q_lat, pages, kv, ctx_len: int, topk: int, index_scale: float,
+                             attn_scale: float, page_size: int = 64, ue8m0: bool = False):
+    """Reference result of one decode request, driven as the reference's ops are driven for decode:
+    q quantisation + weight folding (misa_deepseek_v2.py:279-292), dequantised paged keys
+    (misa_ops.py:360-378), indexer_select_topk with q_global_pos = ctx_len - 1
+    (OpenDSA/opendsa/ops/topk_select.py:30-72) and the latent attention of sparse_mla.py:39-43.
+      q_idx [1,64,128], w [1,64], q_lat [1,H,576]; pages uint8 [n_pages, page_size*132] = the request's
+      cache pages in position order; kv [>=ctx_len, 576].
+    Returns (scores fp32 [1,ctx_len], idx int32 [1,topk], ctx fp32 [1,H,512], lse fp32 [1,H])."""
+    q_fp8, wf = quant_q_fold_weights(q_idx.float(), w.float(), index_scale, ue8m0=ue8m0)
+    keys = unpack_paged_fp8_cache(pages, page_size).reshape(-1, 128)[:ctx_len]
+    scores = indexer_scores(q_fp8.float(), keys, wf, 1.0)
+    idx = topk_rows(scores, topk)
+    ctx, lse = sparse_attend_latent(q_lat, kv[:ctx_len], idx, d_c=512, sm_scale=attn_scale,
+                                    q_pos=torch.tensor([ctx_len - 1]))
+    return scores, idx, ctx, lse
+
+
+def check_decode_request(scores_ref, idx_ref, got_logits, got_idx, got_ctx, got_lse, q_lat, kv, ctx_len: int,
+                         attn_scale: float):
+    """Compare one request of a decode step with decode_request_reference's result.  Returns a dict of
+    measured errors; raises AssertionError when a stated tolerance is missed: FP8 scores 1e-2 relative,
+    index sets recall >= 0.999 with only near-tie disagreements, attention 2e-2 (checked on the
+    implementation's own picks, so that ties cannot leak into the attention comparison)."""
+    res = {}
+    if got_logits is not None:
+        res["score_rel_err"] = rel_err(got_logits.float().view(1, -1)[:, :ctx_len], scores_ref)
+        assert res["score_rel_err"] < 1e-2, res
+    res["recall"] = assert_selection_parity(got_idx.view(1, -1), idx_ref, scores_ref, 1e-3, what="decode request")
+    c, l = sparse_attend_latent(q_lat, kv[:ctx_len], got_idx.view(1, -1), d_c=512, sm_scale=attn_scale,
+                                q_pos=torch.tensor([ctx_len - 1]))
+    res["attn_rel_err"] = float((got_ctx.float().view_as(c) - c).abs().max() / c.abs().max().clamp_min(1e-9))
+    res["lse_abs_err"] = float((got_lse.float().view_as(l) - l).abs().max())
+    assert res["attn_rel_err"] < 2e-2 and res["lse_abs_err"] < 2e-2, res
+    return res
+
+
+# --------------------------------------------------------------------------- #
 # metrics
 # --------------------------------------------------------------------------- #
 def set_recall(pred: torch.Tensor, ref: torch.Tensor) -> float:
@@ -389,10 +454,14 @@ def set_recall(pred: torch.Tensor, ref: torch.Tensor) -> float:
 
 
 def near_tie_audit(pred: torch.Tensor, ref: torch.Tensor, scores: torch.Tensor,
-                   rtol: float) -> Tuple[int, int]:
+                   rtol: float, stage1_scores: Optional[torch.Tensor] = None,
+                   stage1_k: int = 0) -> Tuple[int, int]:
     """Count disagreements and how many of them are NOT near-ties at the k-th score.
     A disagreement (in pred xor ref) is a near-tie when
-    |s[i] - s_kth| <= rtol * max(|s_kth|, rms(s_valid))."""
+    |s[i] - s_kth| <= rtol * max(|s_kth|, rms(s_valid)).
+    Two-stage selections (a stage-1 shortlist of the stage1_k best stage1_scores, then the top-k of
+    `scores` inside it) also excuse a disagreement whose stage-1 score is a near-tie at the
+    stage1_k-th stage-1 score: whether it was shortlisted at all was decided by a tie."""
     bad = 0
     total = 0
     for t in range(pred.shape[0]):
@@ -407,10 +476,40 @@ def near_tie_audit(pred: torch.Tensor, ref: torch.Tensor, scores: torch.Tensor,
         kth = srow[ref_idx].min()
         fin = srow[torch.isfinite(srow)]
         tol = rtol * max(float(kth.abs()), float(fin.pow(2).mean().sqrt()))
+        kth1 = tol1 = None
+        if stage1_scores is not None:
+            s1 = stage1_scores[t]
+            fin1 = s1[torch.isfinite(s1)]
+            if fin1.numel() > stage1_k > 0:
+                kth1 = float(torch.topk(fin1, stage1_k).values[-1])
+                tol1 = rtol * max(abs(kth1), float(fin1.pow(2).mean().sqrt()))
         for i in diff:
-            if abs(float(srow[i]) - float(kth)) > tol:
-                bad += 1
+            if abs(float(srow[i]) - float(kth)) <= tol:
+                continue
+            if kth1 is not None and abs(float(stage1_scores[t][i]) - kth1) <= tol1:
+                continue
+            bad += 1
     return total, bad
+
+
+def assert_selection_parity(pred: torch.Tensor, ref: torch.Tensor, scores: torch.Tensor, rtol: float,
+                            stage1_scores: Optional[torch.Tensor] = None, stage1_k: int = 0,
+                            what: str = "selection") -> float:
+    """The acceptance rule for index sets: recall >= 0.999 and every disagreement a near-tie."""
+    rec = set_recall(pred, ref)
+    total, bad = near_tie_audit(pred, ref, scores, rtol, stage1_scores, stage1_k)
+    assert bad == 0, f"{what}: {bad} of {total} disagreements are not near-ties (recall {rec:.5f})"
+    assert rec >= 0.999, f"{what}: recall {rec:.5f} < 0.999 ({total} disagreements, all near-ties)"
+    return rec
+
+
+def finite_top(scores: torch.Tensor) -> torch.Tensor:
+    """Replace +inf entries (force-kept blocks) by a finite value just above the largest finite score,
+    so that a near-tie audit can compute magnitudes without the infinities changing the order."""
+    fin = torch.where(torch.isfinite(scores), scores, torch.full_like(scores, NEG_INF))
+    top = fin.max(dim=1, keepdim=True).values
+    top = torch.where(torch.isfinite(top), top, torch.zeros_like(top))
+    return torch.where(torch.isposinf(scores), (top + top.abs() + 1.0).expand_as(scores), scores)
 
 
 def rel_err(x: torch.Tensor, ref: torch.Tensor, eps: float = 1e-2) -> float:

@@ -90,11 +90,26 @@ def test_misa_mqa_logits_prefill(use_qnorm):
         hs = O.misa_block_head_scores(qf, pooled, wf, ks.long() // 128, (ke.long() + 127) // 128)
         hidx = torch.topk(hs, 8, dim=-1).indices
     ref_logits, ref_cand = O.misa_mqa_logits(qf, kb, wf, hidx, ks.long(), ke.long(), s1)
-    assert O.set_recall(cand.cpu(), ref_cand) >= 0.995
+    q8, w8 = O.gather_heads(qf, wf, hidx)
+    s1_scores = O.mask_interval(O.indexer_scores(q8, kb, w8, 1.0), ks.long(), ke.long())
+    O.assert_selection_parity(cand.cpu(), ref_cand, s1_scores, 2e-3, what="stage-1 candidates")
     full = O.mask_interval(O.indexer_scores(qf, kb, wf, 1.0), ks.long(), ke.long())
     got = torch.gather(full, 1, cand.cpu().clamp(min=0).long())
     ok = cand.cpu() >= 0
     assert O.rel_err(logits.cpu()[ok], got[ok]) < 2e-3
+
+
+def _two_stage_ref(q8f, wf, hidx, kd, s1, k):
+    """Oracle two-stage selection of one query row: (picks int32 [1,k] -1 padded, all-head scores
+    [1,n], routed stage-1 scores [1,n])."""
+    qh, wh = O.gather_heads(q8f, wf, hidx)
+    st1 = O.indexer_scores(qh, kd, wh, 1.0)
+    c1 = torch.topk(st1, min(s1, kd.shape[0]), dim=-1).indices[0]
+    full = O.indexer_scores(q8f, kd, wf, 1.0)
+    pick = c1[torch.topk(full[0][c1], min(k, c1.numel())).indices]
+    ref = torch.full((1, k), -1, dtype=torch.int32)
+    ref[0, :pick.numel()] = pick.to(torch.int32)
+    return ref, full, st1
 
 
 def test_misa_page_logits_and_hook_decode_prefill():
@@ -113,13 +128,9 @@ def test_misa_page_logits_and_hook_decode_prefill():
     final = M.misa_final_topk(logits, cand, 64).cpu()
     for b, c in enumerate(ctxs):
         kd = qs[b][0].float() * qs[b][1].unsqueeze(-1)
-        q8, w8 = O.gather_heads(q_fp8[b:b + 1].float(), wf[b:b + 1], hidx[b:b + 1])
-        s1 = O.indexer_scores(q8, kd, w8, 1.0)
-        c1 = torch.topk(s1, min(256, c), dim=-1).indices
-        full = O.indexer_scores(q_fp8[b:b + 1].float(), kd, wf[b:b + 1], 1.0)
-        ref = c1[0][torch.topk(full[0][c1[0]], min(64, c1.shape[1])).indices]
-        got = final[b][final[b] >= 0]
-        assert len(set(got.tolist()) & set(ref.tolist())) >= 0.98 * ref.numel()
+        ref, full, st1 = _two_stage_ref(q_fp8[b:b + 1].float(), wf[b:b + 1], hidx[b:b + 1], kd, 256, 64)
+        O.assert_selection_parity(final[b:b + 1], ref, full, 1e-3, stage1_scores=st1, stage1_k=256,
+                                  what=f"paged two-stage, request {b}")
 
     # ---- hook, decode step: new key appended, then selection over the cache
     P = 64
@@ -136,8 +147,8 @@ def test_misa_page_logits_and_hook_decode_prefill():
     nkq, nsc = O.quant_fp8_rows(new_k.float())
     for b, c in enumerate(ctxs):
         kd = torch.cat([qs[b][0].float() * qs[b][1].unsqueeze(-1), (nkq[b].float() * nsc[b]).view(1, -1)])
-        ref = O.topk_rows(O.indexer_scores(q_fp8[b:b + 1].float(), kd, wf[b:b + 1], 1.0), 64)
-        assert O.set_recall(buf[b:b + 1].cpu(), ref) >= 0.98
+        sc = O.indexer_scores(q_fp8[b:b + 1].float(), kd, wf[b:b + 1], 1.0)
+        O.assert_selection_parity(buf[b:b + 1].cpu(), O.topk_rows(sc, 64), sc, 1e-3, what=f"hook decode {b}")
     assert (buf[B:] == 7).all()                                # rows of other tokens untouched
 
     # ---- hook, prefill chunk with two requests (MISA, q-norm heads)
@@ -169,17 +180,14 @@ def test_misa_page_logits_and_hook_decode_prefill():
     kq_all, sc_all = O.quant_fp8_rows(kf.float())
     kd_all = kq_all.float() * sc_all.unsqueeze(-1)
     res = buf2.cpu()
-    for t in [0, 5, 150, 199, 200, 260, 532]:
+    for t in range(T):
         r = 0 if t < 200 else 1
         off = 0 if r == 0 else 200
         kd = kd_all[off: ke[t]]
-        qh, wh = O.gather_heads(q8[t:t + 1].float(), w8[t:t + 1], hq[t:t + 1])
-        c1 = torch.topk(O.indexer_scores(qh, kd, wh, 1.0), min(128, kd.shape[0]), dim=-1).indices[0]
-        full = O.indexer_scores(q8[t:t + 1].float(), kd, w8[t:t + 1], 1.0)[0]
-        ref = c1[torch.topk(full[c1], min(32, c1.numel())).indices]
-        got = res[t][res[t] >= 0]
-        assert got.numel() == ref.numel()
-        assert len(set(got.tolist()) & set(ref.tolist())) >= 0.95 * ref.numel(), t
+        ref, full, st1 = _two_stage_ref(q8[t:t + 1].float(), w8[t:t + 1], hq[t:t + 1], kd, 128, 32)
+        assert int((res[t] >= 0).sum()) == int((ref >= 0).sum())
+        O.assert_selection_parity(res[t:t + 1], ref, full, 1e-3, stage1_scores=st1, stage1_k=128,
+                                  what=f"hook prefill token {t}")
 
 
 def test_single_pass_gated_and_full_scores():

@@ -54,16 +54,21 @@ def test_select_config1_shape_scores_and_sets():
     cu = torch.tensor([0, T])
     idx = D.indexer_select_topk(q.cuda(), k.cuda(), w.cuda(), cu.cuda(), 2048).cpu()
     qb, kb = q.bfloat16().float(), k.bfloat16().float()
-    sub = torch.arange(0, T, 37)                       # every 37th query keeps the CPU side short
-    ks, ke = torch.zeros(sub.numel(), dtype=torch.int64), sub + 1
-    scores = O.mask_interval(O.indexer_scores(qb[sub], kb, w[sub]), ks, ke)
-    ref = O.topk_rows(scores, 2048)
-    rec, total, bad = _audit(idx[sub], ref, scores)
-    assert rec >= 0.999 and bad == 0, (rec, total, bad)
-    # scores themselves (bf16 tolerance)
+    # index sets: ALL 4096 queries against the oracle (chunks keep the fp32 score matrix small)
     ksd, ked = D.prepare_ks_ke(cu.cuda())
     logits, _, _ = D.indexer_logits_flat(q.cuda().bfloat16(), k.cuda().bfloat16(), w.cuda(), ksd, ked, 128 ** -0.5)
-    assert O.rel_err(logits.cpu()[sub][:, :T], scores) < BF16_RTOL
+    logits = logits.cpu()
+    worst = 0.0
+    for t0 in range(0, T, 512):
+        t1 = t0 + 512
+        ks, ke = torch.zeros(512, dtype=torch.int64), torch.arange(t0, t1) + 1
+        scores = O.mask_interval(O.indexer_scores(qb[t0:t1], kb, w[t0:t1]), ks, ke)
+        ref = O.topk_rows(scores, 2048)
+        O.assert_selection_parity(idx[t0:t1], ref, scores, BF16_RTOL, what=f"queries {t0}..{t1}")
+        assert torch.equal(idx[t0:t1] < 0, ref < 0)
+        # scores themselves (bf16 tolerance)
+        worst = max(worst, O.rel_err(logits[t0:t1, :T], scores))
+    assert worst < BF16_RTOL, worst
 
 
 def test_attend_golden_through_dropin():
@@ -92,15 +97,25 @@ def test_hisa_two_stage_vs_oracle():
     ks[:8] = 3000                                              # a later document start
     cfg = HisaConfig(hisa_block_topk=16, index_topk=512)
     idx, blocks = hisa_select_topk(q.cuda(), k.cuda(), w.cuda(), ks.cuda(), ke.cuda(), cfg, return_blocks=True)
+    idx, blocks = idx.cpu(), blocks.cpu()
     ref, ref_blocks = O.hisa_select_topk(q, k, w, ks, ke, block=128, block_topk=16, topk=512, return_blocks=True)
-    assert O.set_recall(blocks.cpu(), ref_blocks) >= 0.99
-    assert O.set_recall(idx.cpu(), ref) >= 0.99
+    # stage 1: the kept blocks, audited on the oracle's block scores (the forced block carries +inf)
+    blk_scores = O.hisa_block_logits(q, O.block_mean_pool(k, 128), w, ks, ke, 128)
+    blk_scores = O.finite_top(blk_scores)               # the forced block's +inf -> just above the row's best
+    O.assert_selection_parity(blocks, ref_blocks, blk_scores, BF16_RTOL, what="HISA blocks")
+    # stage 2: token picks inside the blocks the kernel itself kept
+    ref2, tok_scores = O.hisa_select_topk(q, k, w, ks, ke, block=128, block_topk=16, topk=512, blocks=blocks,
+                                          return_scores=True)
+    O.assert_selection_parity(idx, ref2, tok_scores, BF16_RTOL, what="HISA tokens")
+    # both stages end to end: a block-level near-tie moves up to 128 candidates at once
+    assert O.set_recall(idx, ref) >= 0.999 or not torch.equal(torch.sort(blocks, 1).values,
+                                                              torch.sort(ref_blocks, 1).values)
     last = ((ke + 127) // 128 - 1).to(torch.int32)
-    assert (blocks.cpu()[:, 0] == last).all()                   # the forced block sorts first (+inf)
+    assert (blocks[:, 0] == last).all()                   # the forced block sorts first (+inf)
     # quality: overlap with the dense selection (HISA's own claim is > 99 % IoU on real data;
     # on white-noise keys block means carry little signal, so only a sanity bound is asserted)
     dense = O.topk_rows(O.mask_interval(O.indexer_scores(q, k, w), ks, ke), 512)
-    assert O.set_recall(idx.cpu(), dense) > 0.1
+    assert O.set_recall(idx, dense) > 0.1
 
 
 def test_hisa_equals_dense_when_every_block_is_kept():

@@ -60,6 +60,48 @@ def test_emulated_ranks_one_after_another(world, n_rows):
         pc.close()
 
 
+def test_wait_for_absent_peer_runs_out_and_is_reported():
+    """A bounded device wait that really runs out, on one GPU and without any fault: a barrier for a
+    world of two over two local buffers where nobody ever plays rank 1.  With the limit lowered to
+    about a millisecond the kernel must come back, raise the status word to 1 and advance its step
+    counter; the stream stays usable and a following ordinary call gives correct results."""
+    import time
+    from transarch_b200 import _lib
+    from transarch_b200.peer import PeerLseCombine
+    lib = _lib.load()
+    dev = torch.device("cuda")
+    n_rows = 64
+    pc = PeerLseCombine(n_rows, dev, emulate_world=2, extra_bytes=3 * 1024)
+    assert _lib.read_status(dev) == 0
+    assert lib.b200dsa_peer_set_wait_limit(1 << 21) == 0          # ~1 ms at 2 GHz
+    try:
+        t0 = time.perf_counter()
+        pc.barrier(slot=1)                                        # rank 0 of 2; rank 1's flag never arrives
+        torch.cuda.synchronize()
+        assert time.perf_counter() - t0 < 5.0
+        assert _lib.read_status(dev) == 1                         # reported (and cleared by the read)
+        assert int(pc.barrier_state[0]) == 1                      # the step counter still advanced
+        pc.push_extra(1024, slot=3)                               # the all-gather kernel gives up the same way
+        torch.cuda.synchronize()
+        assert _lib.read_status(dev) == 1
+    finally:
+        assert lib.b200dsa_peer_set_wait_limit(0) == 0            # back to the default
+    # the context is intact: an ordinary (emulated, no waiting) merge on the same buffers is correct
+    ctx, lse = _partials(2, n_rows, 3)
+    for r in range(2):
+        c, l, o, lo = pc.views_of(r)
+        c.copy_(ctx[r]); l.copy_(lse[r])
+    for r in range(2):
+        pc.run(rank=r, no_sync=True)
+    torch.cuda.synchronize()
+    want, want_lse = _expected(ctx, lse)
+    assert torch.allclose(pc.views_of(0)[2].float().cpu(), want, rtol=1e-2, atol=1e-2)
+    assert torch.allclose(pc.views_of(1)[3].cpu(), want_lse, rtol=1e-5, atol=1e-5)
+    assert _lib.read_status(dev) == 0
+    assert lib.b200dsa_peer_set_wait_limit(-1) == -1              # rejected
+    pc.close()
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -100,3 +100,32 @@ def test_large_scores_trigger_rescale():
     ctx, lse = K.sparse_mla_decode(q.cuda(), kv.cuda(), idx.cuda(), scale)
     rc, rl = O.sparse_attend_latent(q, kv, idx, d_c=512, sm_scale=scale, q_pos=torch.tensor([n_idx]))
     _check(ctx.cpu(), lse.cpu(), rc, rl)
+
+
+def test_out_of_range_row_is_skipped_and_reported():
+    """An index that points past the latent cache is not read: the kernel drops that key, raises the
+    status word to 2 (a skipped index) and the result equals attention over the remaining keys."""
+    from transarch_b200 import _lib, kernels as K
+    g = torch.Generator().manual_seed(9)
+    n_items, H, n_idx, rows = 2, 128, 200, 1000
+    q = torch.randn(n_items, H, 576, generator=g).bfloat16()
+    kv = (0.5 * torch.randn(rows, 576, generator=g)).bfloat16()
+    idx = torch.stack([torch.randperm(rows, generator=g)[:n_idx] for _ in range(n_items)]).to(torch.int32)
+    bad = idx.clone()
+    bad[1, 17] = rows + 5                                        # one row beyond the cache
+    scale = 192 ** -0.5
+    dev = torch.device("cuda")
+    assert _lib.read_status(dev) == 0
+    ctx, lse = K.sparse_mla_decode(q.cuda(), kv.cuda(), bad.cuda(), scale)
+    torch.cuda.synchronize()
+    assert _lib.read_status(dev) == 2
+    good = idx.clone()
+    good[1, 17] = -1
+    for b in range(n_items):
+        rc, rl = O.sparse_attend_latent(q[b:b + 1], kv, good[b:b + 1], d_c=512, sm_scale=scale,
+                                        q_pos=torch.tensor([rows]))
+        _check(ctx[b:b + 1].cpu(), lse[b:b + 1].cpu(), rc, rl)
+    # the word was cleared by the read; a clean call leaves it at 0
+    K.sparse_mla_decode(q.cuda(), kv.cuda(), good.cuda(), scale)
+    torch.cuda.synchronize()
+    assert _lib.read_status(dev) == 0

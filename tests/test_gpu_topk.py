@@ -188,3 +188,26 @@ def test_segments_in_separate_buffers():
     for r in range(rows):
         order = sorted(range(n_seg * k), key=lambda c: (-float(all_sc[r, c]), int(all_pos[r, c])))[:k]
         assert out[r].cpu().tolist() == [int(all_pos[r, c]) for c in order]
+
+
+def test_topk_split_private_list_overflow_falls_back():
+    """One collecting thread meets far more candidates than its private list holds (the winners are
+    bunched in the columns a single thread of a single slice streams): the row's list is marked
+    unusable and the last kernel selects from the row itself.  The result is still exact."""
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(77)
+    n_rows, n_cols, k, splits = 4, 131072, 2048, 4
+    s = torch.randn(n_rows, n_cols, generator=g)
+    # a collecting thread reads 4 consecutive columns out of every 2048 (512 threads x 16-byte loads):
+    # 16 such groups inside the first slice of 32768 columns -> 64 winners for that one thread
+    cols = (torch.arange(16).view(-1, 1) * 2048 + torch.arange(4).view(1, -1)).reshape(-1)
+    s[1, cols] = 10.0 + torch.rand(64, generator=g)
+    s[3, cols + 32768 + 4 * 137] = 12.0 + torch.rand(64, generator=g)      # another slice, another thread
+    s = s.cuda()
+    scratch = K.topk_scratch(n_rows, s.device)
+    ref = K.topk_select(s, k)
+    for _ in range(3):
+        out = K.topk_select_split(s, k, scratch, splits=splits)
+        assert torch.equal(out, ref)
+        assert (scratch[1][:n_rows] == 0).all()
+    assert set(cols.tolist()) <= set(out[1].cpu().tolist())

@@ -54,22 +54,34 @@ def test_two_rank_sharded_step_matches_unsharded(wire):
 
 
 def _absent_worker(rank, world, port, ret):
-    """Rank 1 never joins the candidate exchange: rank 0 must get an error from the collective
-    (short process-group timeout), not hang."""
+    """Both ranks complete one sharded step; then rank 1 leaves between steps with nothing in flight.
+    Rank 0's next step must end with an error from its first exchange (short process-group
+    timeout) instead of hanging, and must not hand back a result."""
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     import datetime
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
     try:
+        from tests import cpu_backend
+        from transarch_b200.decode import ShardInfo, SparseDecodeStep
+        torch.set_num_threads(2)
+        prob = make_global_problem(52, CTXS, H=8)
+        st = shard_state(prob, rank, world, SHARD, "cpu")
+        shard = ShardInfo(rank=rank, world_size=world, shard_len=SHARD)
+        step = SparseDecodeStep(len(CTXS), SHARD, topk=TOPK, n_heads=8, device=torch.device("cpu"), shard=shard,
+                                backend=cpu_backend, sorted_topk=True, wire="fp32")
+        args = (prob["q_idx"], prob["w"], prob["q_lat"], st["cache"], st["lens"], st["table"], st["kv"], st["base"])
+        idx, _, _ = step.run(*args)
+        ref_idx, _, _, _ = oracle_decode(prob, TOPK, 128 ** -0.5, 192 ** -0.5)
+        first_ok = torch.equal(idx, ref_idx)
         if rank == 1:
-            ret[1] = "left"
-            return                      # leaves between steps, nothing in flight
-        t = torch.zeros(4)
+            ret[1] = "left" if first_ok else "wrong first step"
+            return                      # leaves between steps
         try:
-            dist.all_reduce(t)
+            step.run(*args)
             ret[0] = "no error"
-        except Exception as e:          # noqa: BLE001
-            ret[0] = "error"
+        except Exception:               # noqa: BLE001 - the collective's timeout / peer-closed error
+            ret[0] = "error" if first_ok else "wrong first step"
     finally:
         try:
             dist.destroy_process_group()
@@ -77,7 +89,7 @@ def _absent_worker(rank, world, port, ret):
             pass
 
 
-def test_missing_rank_is_reported_not_hung():
+def test_rank_leaving_between_steps_fails_the_next_step_not_hangs():
     port = _free_port()
     mgr = mp.Manager()
     ret = mgr.dict()

@@ -38,6 +38,7 @@ SIGNATURES = {
     "b200dsa_peer_barrier": [_vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp],
     "b200dsa_peer_gather": [_vp, _i32, _i32, _i64, _i64, _vp, _i64, _i32, _vp, _vp, _vp],
     "b200dsa_peer_push": [_vp, _i32, _i32, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _vp],
+    "b200dsa_peer_set_wait_limit": [_i64],
     "b200dsa_peer_alloc": [_i64, _vp, _vp],
     "b200dsa_peer_open": [_vp, _vp],
     "b200dsa_peer_close": [_vp],
@@ -45,13 +46,13 @@ SIGNATURES = {
     "b200dsa_lse_prescale": [_vp, _vp, _vp, _i64, _vp, _vp],
     "b200dsa_lse_finalize": [_vp, _vp, _i64, _vp, _vp, _vp],
     "b200dsa_lse_prescale_norm": [_vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp],
-    "b200dsa_quant_q_fold_weights": [_vp, _vp, _i64, _f32, _vp, _vp, _vp],
+    "b200dsa_quant_q_fold_weights": [_vp, _vp, _i64, _f32, _i32, _vp, _vp, _vp],
     "b200dsa_block_mean_pool_bf16": [_vp, _i32, _i32, _vp, _vp, _vp],
     "b200dsa_paged_mean_pool_fp8": [_vp, _i32, _i32, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp],
     "b200dsa_router_qnorm_topk": [_vp, _vp, _i32, _i32, _vp, _vp, _vp],
     "b200dsa_router_block_score_topk": [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp],
     "b200dsa_router_linear_topk_softmax": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp],
-    "b200dsa_indexer_k_quant_and_cache": [_vp, _vp, _i64, _vp, _i64, _i32, _vp, _vp],
+    "b200dsa_indexer_k_quant_and_cache": [_vp, _vp, _i64, _vp, _i64, _i32, _i32, _vp, _vp],
 }
 
 _lib: Optional[C.CDLL] = None

@@ -26,7 +26,10 @@ namespace b200dsa {
 
 constexpr int kPeerMaxRanks = 8;
 constexpr int kPeerDv = 512;
-constexpr long long kPeerWaitCycles = 1ll << 31;   // about a second
+constexpr long long kPeerWaitCyclesDefault = 1ll << 31;   // about a second
+// Limit of every wait for a peer, in SM clock cycles; process-wide, set by b200dsa_peer_set_wait_limit
+// and copied into the parameters of each launch.
+static long long g_peer_wait_cycles = kPeerWaitCyclesDefault;
 constexpr int kPeerDoneSlot = 16;                  // flags: ready[0..7], done[16..23] (uint32 words)
 
 struct PeerCombineParams {
@@ -37,6 +40,7 @@ struct PeerCombineParams {
   int32_t* state;                     // local: [0] launches completed, [1] blocks finished in this launch
   int32_t* status;
   int no_sync;                        // skip the flag exchange (sequential emulation of ranks on one GPU)
+  long long wait_cycles;              // bound of every wait for a peer's flag
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -62,10 +66,10 @@ __device__ __forceinline__ float ld_sys_f32(const float* p) {
 }
 
 // true once *flag has reached `step` (wrap-safe), false when the bound ran out
-__device__ __forceinline__ bool wait_step(const uint32_t* flag, uint32_t step) {
+__device__ __forceinline__ bool wait_step(const uint32_t* flag, uint32_t step, long long limit) {
   const long long t0 = clock64();
   while (static_cast<int32_t>(ld_acquire_sys(flag) - step) < 0) {
-    if (clock64() - t0 > kPeerWaitCycles) return false;
+    if (clock64() - t0 > limit) return false;
   }
   return true;
 }
@@ -103,7 +107,7 @@ __global__ void __launch_bounds__(256, 2) peer_lse_combine_kernel(const PeerComb
   if (!p.no_sync) {
     if (blockIdx.x == 0 && tid < p.world)
       st_release_sys(reinterpret_cast<uint32_t*>(p.buf[tid] + p.off_flags) + p.rank, step);
-    if (tid < p.world && !wait_step(my_flags + tid, step)) atomicMax(p.status, kDevWaitTimeout);
+    if (tid < p.world && !wait_step(my_flags + tid, step, p.wait_cycles)) atomicMax(p.status, kDevWaitTimeout);
     __syncthreads();
   }
 
@@ -171,7 +175,7 @@ __global__ void __launch_bounds__(256, 2) peer_lse_combine_kernel(const PeerComb
     __threadfence();
     if (!p.no_sync && tid < p.world) {
       st_release_sys(reinterpret_cast<uint32_t*>(p.buf[tid] + p.off_flags) + kPeerDoneSlot + p.rank, step);
-      if (!wait_step(my_flags + kPeerDoneSlot + tid, step)) atomicMax(p.status, kDevWaitTimeout);
+      if (!wait_step(my_flags + kPeerDoneSlot + tid, step, p.wait_cycles)) atomicMax(p.status, kDevWaitTimeout);
     }
     __syncthreads();
     if (tid == 0) {
@@ -191,7 +195,7 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerCombineParam
   if (tid < p.world) {
     st_release_sys(reinterpret_cast<uint32_t*>(p.buf[tid] + p.off_flags) + slot * 8 + p.rank, step);
     const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.buf[p.rank] + p.off_flags) + slot * 8 + tid;
-    if (!wait_step(mine, step)) atomicMax(p.status, kDevWaitTimeout);
+    if (!wait_step(mine, step, p.wait_cycles)) atomicMax(p.status, kDevWaitTimeout);
   }
   __syncwarp();
   if (tid == 0) p.state[0] = static_cast<int32_t>(step);
@@ -212,7 +216,7 @@ __global__ void __launch_bounds__(256, 2) peer_gather_kernel(const PeerCombinePa
     st_release_sys(reinterpret_cast<uint32_t*>(p.buf[tid] + p.off_flags) + slot * 8 + p.rank, step);
   if (tid < p.world) {
     const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.buf[p.rank] + p.off_flags) + slot * 8 + tid;
-    if (!wait_step(mine, step)) atomicMax(p.status, kDevWaitTimeout);
+    if (!wait_step(mine, step, p.wait_cycles)) atomicMax(p.status, kDevWaitTimeout);
   }
   __syncthreads();
   const int64_t n16 = nbytes >> 4;                       // 16-byte words per rank
@@ -297,7 +301,7 @@ __global__ void __launch_bounds__(256, 2) peer_push_kernel(const PeerCombinePara
     if (tid < p.world) {
       st_release_sys(reinterpret_cast<uint32_t*>(p.buf[tid] + p.off_flags) + slot * 8 + p.rank, step);
       const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.buf[p.rank] + p.off_flags) + slot * 8 + tid;
-      if (!wait_step(mine, step)) atomicMax(p.status, kDevWaitTimeout);
+      if (!wait_step(mine, step, p.wait_cycles)) atomicMax(p.status, kDevWaitTimeout);
     }
     __syncthreads();
     if (tid == 0) p.state[0] = static_cast<int32_t>(step);
@@ -338,6 +342,7 @@ extern "C" int b200dsa_peer_lse_combine(void* const* bufs, int32_t rank, int32_t
   p.off_flags = off_flags;
   p.state = state;
   p.status = status;
+  p.wait_cycles = g_peer_wait_cycles;
   p.no_sync = no_sync;
   const int64_t per = (n_rows + world - 1) / world;
   int64_t grid = (per + 7) / 8;
@@ -373,6 +378,7 @@ extern "C" int b200dsa_peer_barrier(void* const* bufs, int32_t rank, int32_t wor
   p.off_flags = off_flags;
   p.state = state;
   p.status = status;
+  p.wait_cycles = g_peer_wait_cycles;
   cudaError_t e = launch_chained(peer_barrier_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), p,
                                  static_cast<int>(slot));
   if (e == cudaSuccess) e = cudaGetLastError();
@@ -405,6 +411,7 @@ extern "C" int b200dsa_peer_gather(void* const* bufs, int32_t rank, int32_t worl
   p.off_flags = off_flags;
   p.state = state;
   p.status = status;
+  p.wait_cycles = g_peer_wait_cycles;
   int64_t grid = (nbytes / 16 * world + 2047) / 2048;
   if (grid < 1) grid = 1;
   if (grid > 296) grid = 296;          // two blocks per SM: the whole 8-rank payload is in flight at once
@@ -441,6 +448,7 @@ extern "C" int b200dsa_peer_push(void* const* bufs, int32_t rank, int32_t world,
   p.off_flags = off_flags;
   p.state = state;
   p.status = status;
+  p.wait_cycles = g_peer_wait_cycles;
   int64_t grid = (nbytes / 16 + 1023) / 1024;
   if (grid < 1) grid = 1;
   if (grid > 296) grid = 296;
@@ -451,6 +459,15 @@ extern "C" int b200dsa_peer_push(void* const* bufs, int32_t rank, int32_t world,
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;
   }
+  return B200DSA_OK;
+}
+
+extern "C" int b200dsa_peer_set_wait_limit(int64_t cycles) {
+  if (cycles < 0) {
+    set_last_error("b200dsa_peer_set_wait_limit: the limit must be positive, or 0 for the default");
+    return B200DSA_EINVAL;
+  }
+  g_peer_wait_cycles = cycles == 0 ? kPeerWaitCyclesDefault : static_cast<long long>(cycles);
   return B200DSA_OK;
 }
 

@@ -1,5 +1,6 @@
 // Index-query quantisation with the scale folded into the head weights:
-//   scale[t,h] = max(amax_d |q[t,h,d]|, 1e-4) / 448;  q_fp8 = e4m3(q / scale)  (round to nearest even)
+//   scale[t,h] = max(amax_d |q[t,h,d]|, 1e-10) / 448, rounded UP to a power of two when the
+//   "ue8m0" scale format is asked for;  q_fp8 = e4m3(q / scale)  (round to nearest even)
 //   weights[t,h] = w[t,h] * scale[t,h] * fold
 // so that  sum_h weights * relu(<q_fp8, k_fp8>) * k_scale  equals the unquantised score up to
 // FP8 rounding.  One warp per (t, h) row of 128 values, four per lane.
@@ -10,9 +11,20 @@
 
 namespace b200dsa {
 
+// Smallest power of two that is >= x (x positive and finite): the "ue8m0" scale format, i.e.
+// exp2(ceil(log2(x))) evaluated exactly on the bit pattern instead of through log2f / exp2f.
+__device__ __forceinline__ float pow2_round_up(float x) {
+  const uint32_t u = __float_as_uint(x);
+  uint32_t e = u >> 23;
+  if (e == 0) return 1.17549435e-38f;          // subnormal input: the smallest normal power of two
+  if (u & 0x7fffffu) ++e;
+  return __uint_as_float(e << 23);
+}
+
 __global__ void __launch_bounds__(256) quant_q_fold_kernel(const __nv_bfloat16* __restrict__ q,
                                                            const float* __restrict__ w, int64_t n_rows, float fold,
-                                                           uint8_t* __restrict__ q_fp8, float* __restrict__ weights) {
+                                                           int use_ue8m0, uint8_t* __restrict__ q_fp8,
+                                                           float* __restrict__ weights) {
   pdl_launch_dependents();
   pdl_wait_prior();
   const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
@@ -24,7 +36,8 @@ __global__ void __launch_bounds__(256) quant_q_fold_kernel(const __nv_bfloat16* 
   float x[4] = {__low2float(a), __high2float(a), __low2float(b), __high2float(b)};
   float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  const float scale = __fdiv_rn(fmaxf(amax, 1e-4f), 448.0f);
+  float scale = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
+  if (use_ue8m0) scale = pow2_round_up(scale);
   uint32_t packed = 0;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -42,7 +55,7 @@ void set_last_error(const char* msg);
 using namespace b200dsa;
 
 extern "C" int b200dsa_quant_q_fold_weights(const void* q_bf16, const float* w, int64_t n_rows, float fold,
-                                            void* q_fp8, float* weights, void* stream) {
+                                            int32_t use_ue8m0, void* q_fp8, float* weights, void* stream) {
   if (n_rows == 0) return B200DSA_OK;
   if (!q_bf16 || !w || !q_fp8 || !weights || n_rows < 0) {
     set_last_error("b200dsa_quant_q_fold_weights: bad argument");
@@ -54,7 +67,8 @@ extern "C" int b200dsa_quant_q_fold_weights(const void* q_bf16, const float* w, 
   }
   const unsigned grid = static_cast<unsigned>((n_rows + 7) / 8);
   cudaError_t e_launch = launch_chained(quant_q_fold_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
-      static_cast<const __nv_bfloat16*>(q_bf16), w, n_rows, fold, static_cast<uint8_t*>(q_fp8), weights);
+      static_cast<const __nv_bfloat16*>(q_bf16), w, n_rows, fold, static_cast<int>(use_ue8m0 != 0),
+      static_cast<uint8_t*>(q_fp8), weights);
   cudaError_t e = e_launch != cudaSuccess ? e_launch : cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
@@ -63,14 +77,15 @@ extern "C" int b200dsa_quant_q_fold_weights(const void* q_bf16, const float* w, 
   return B200DSA_OK;
 }
 
-// Index-key insert: quantise each new key row to e4m3 with a per-token scale and write it into
+// Index-key insert: quantise each new key row to e4m3 with a per-token scale (max(amax, 1e-4)/448,
+// rounded up to a power of two for the "ue8m0" scale format) and write it into
 // its slot of the paged cache (page = P*128 fp8 bytes then P fp32 scales).  One warp per token.
 namespace b200dsa {
 
 __global__ void __launch_bounds__(256) k_quant_and_cache_kernel(const __nv_bfloat16* __restrict__ k,
                                                                 const int64_t* __restrict__ slot_mapping,
                                                                 int64_t n_tokens, int page_size, int64_t num_pages,
-                                                                uint8_t* __restrict__ cache,
+                                                                int use_ue8m0, uint8_t* __restrict__ cache,
                                                                 int32_t* __restrict__ status) {
   const int64_t tok = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (tok >= n_tokens) return;
@@ -89,7 +104,8 @@ __global__ void __launch_bounds__(256) k_quant_and_cache_kernel(const __nv_bfloa
   float x[4] = {__low2float(a), __high2float(a), __low2float(b), __high2float(b)};
   float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  const float scale = __fdiv_rn(fmaxf(amax, 1e-4f), 448.0f);
+  float scale = __fdiv_rn(fmaxf(amax, 1e-4f), 448.0f);
+  if (use_ue8m0) scale = pow2_round_up(scale);
   uint32_t packed = 0;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -104,8 +120,8 @@ __global__ void __launch_bounds__(256) k_quant_and_cache_kernel(const __nv_bfloa
 }  // namespace b200dsa
 
 extern "C" int b200dsa_indexer_k_quant_and_cache(const void* k_bf16, const int64_t* slot_mapping, int64_t n_tokens,
-                                                 void* cache, int64_t num_pages, int32_t page_size, int32_t* status,
-                                                 void* stream) {
+                                                 void* cache, int64_t num_pages, int32_t page_size,
+                                                 int32_t use_ue8m0, int32_t* status, void* stream) {
   if (n_tokens == 0) return B200DSA_OK;
   if (!k_bf16 || !slot_mapping || !cache || !status || n_tokens < 0 || num_pages < 1 || page_size < 1 ||
       (page_size & 3)) {
@@ -115,7 +131,7 @@ extern "C" int b200dsa_indexer_k_quant_and_cache(const void* k_bf16, const int64
   const unsigned grid = static_cast<unsigned>((n_tokens + 7) / 8);
   b200dsa::k_quant_and_cache_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(k_bf16), slot_mapping, n_tokens, page_size, num_pages,
-      static_cast<uint8_t*>(cache), status);
+      static_cast<int>(use_ue8m0 != 0), static_cast<uint8_t*>(cache), status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     b200dsa::set_last_error(cudaGetErrorString(e));

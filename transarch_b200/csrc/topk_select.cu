@@ -682,6 +682,7 @@ topk_collect_kernel(const TopkParams p, int splits, const int32_t* __restrict__ 
   const float thr = fmaxf(ordered_to_float(static_cast<uint32_t>(fl) << 20), -3.402823466e38f);
   const float vmax = p.keep_pos_inf ? INFINITY : 3.402823466e38f;
   if (tid == 0) s_overflow = 0;
+  __syncthreads();  // the flag is raised by any thread below; every return above is taken by the whole block
   const int slice = (((n + splits - 1) / splits) + 3) & ~3;
   const int my_begin = begin + split * slice;
   const int my_n = min(slice, end - my_begin);

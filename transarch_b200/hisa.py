@@ -31,8 +31,8 @@ class HisaConfig:
     hisa_k_block_size: int = 128
     hisa_block_topk: int = 64
     index_topk: int = 2048
-    keep_first_block: bool = False   # block_ops.py:576-666 keeps first and last; the benchmark
-    keep_last_block: bool = True     # configuration keeps only the last
+    keep_first_block: bool = False   # block_ops.py:576-666 force-keeps the first and the last valid block;
+    keep_last_block: bool = True     # the default here keeps only the last (the query's own block)
 
 
 @torch.no_grad()

@@ -70,11 +70,35 @@ def topk_select(scores: torch.Tensor, k: int, *, col_begin: Optional[torch.Tenso
 CAND_CAP = 8192  # candidate list entries per row of the split top-k scratch
 
 
+def _check_topk_outputs(out: torch.Tensor, out_values: Optional[torch.Tensor], n_rows: int, k: int) -> None:
+    """The kernels write row r of both outputs at r * out.stride(0): shapes, dtypes and strides must agree."""
+    if out.dtype != torch.int32 or out.dim() != 2 or out.stride(1) != 1 or out.shape[0] < n_rows or out.shape[1] < k:
+        raise _lib.B200DSAError("out must be int32 [>=n_rows, >=k] with unit column stride")
+    if out_values is not None and (out_values.dtype != torch.float32 or out_values.dim() != 2 or
+                                   out_values.stride(1) != 1 or out_values.stride(0) != out.stride(0) or
+                                   out_values.shape[0] < n_rows or out_values.shape[1] < k):
+        raise _lib.B200DSAError("out_values must be fp32 [>=n_rows, >=k] with the row stride of out")
+
+
 def topk_scratch(n_rows: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
     """Scratch for topk_select_split: (candidates uint64-as-int64 [n_rows, 8192], zeroed int32 [2*n_rows]:
     per-row counters then per-row bin floors).  Only the counters have to start at zero."""
     return (torch.empty(n_rows, CAND_CAP, dtype=torch.int64, device=device),
             torch.zeros(2 * n_rows, dtype=torch.int32, device=device))
+
+
+_scratch_cache = {}
+
+
+def topk_scratch_cached(n_rows: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One scratch pair per (device, row count), allocated on first use and kept: callers that run
+    every step (routers, the serving hook) must not allocate and zero-fill per call.  Calls that
+    share it must not overlap on the GPU (same stream, or ordered by events)."""
+    dev = torch.device(device)
+    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device(), n_rows)
+    if key not in _scratch_cache:
+        _scratch_cache[key] = topk_scratch(n_rows, dev)
+    return _scratch_cache[key]
 
 
 def topk_select_split(scores: torch.Tensor, k: int, scratch: Tuple[torch.Tensor, torch.Tensor], *,
@@ -95,8 +119,7 @@ def topk_select_split(scores: torch.Tensor, k: int, scratch: Tuple[torch.Tensor,
         splits = max(1, min(16, (2 * 148) // max(1, n_rows)))
     if out is None:
         out = torch.empty(n_rows, k, dtype=torch.int32, device=scores.device)
-    if out_values is not None and (out_values.dtype != torch.float32 or out_values.stride(0) != out.stride(0)):
-        raise _lib.B200DSAError("out_values must be fp32 with the row stride of out")
+    _check_topk_outputs(out, out_values, n_rows, k)
     rc = _lib.load().b200dsa_topk_select_split(
         ptr(scores), scores.stride(0), n_rows, n_cols, ptr(_i32(col_begin, "col_begin")),
         ptr(_i32(col_end, "col_end")), k, int(keep_pos_inf), int(sorted), ptr(_i32(row_pos_offset, "row_pos_offset")),
@@ -120,9 +143,10 @@ def topk_select_split_static(scores: torch.Tensor, k: int, *, col_begin: Optiona
     require_cuda(scores, col_begin, col_end, row_pos_offset, out, out_values)
     if scores.dtype != torch.float32 or scores.dim() != 2 or scores.stride(1) != 1:
         raise _lib.B200DSAError("scores must be a 2-D fp32 tensor with unit column stride")
-    if out is None or out.dtype != torch.int32 or out.stride(1) != 1 or out.shape[1] < k:
+    if out is None:
         raise _lib.B200DSAError("out must be a preallocated int32 [n_rows, >=k] tensor")
     n_rows, n_cols = scores.shape
+    _check_topk_outputs(out, out_values, n_rows, k)
     if splits <= 0:
         splits = max(1, min(16, (2 * 148) // max(1, n_rows)))
     rc = _lib.load().b200dsa_topk_select_split_static(
@@ -130,6 +154,8 @@ def topk_select_split_static(scores: torch.Tensor, k: int, *, col_begin: Optiona
         ptr(_i32(col_end, "col_end")), k, int(keep_pos_inf), int(sorted), ptr(_i32(row_pos_offset, "row_pos_offset")),
         splits, ptr(out), ptr(out_values), out.stride(0), stream_ptr())
     check(rc, "b200dsa_topk_select_split_static")
+    if out_values is not None:
+        return out[:n_rows, :k], out_values[:n_rows, :k]
     return out[:n_rows, :k]
 
 
@@ -289,9 +315,11 @@ def lse_combine(ctx_parts: torch.Tensor, lse_parts: torch.Tensor, *, ctx_out: Op
 
 
 def quant_q_fold_weights(q: torch.Tensor, w: torch.Tensor, fold: float, *, q_fp8: Optional[torch.Tensor] = None,
-                         weights: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+                         weights: Optional[torch.Tensor] = None, ue8m0: bool = False
+                         ) -> Tuple[torch.Tensor, torch.Tensor]:
     """(q_fp8 [..., H, 128] e4m3, weights [..., H] fp32) with the per-(token, head) scale folded
-    into the weights; see b200dsa_quant_q_fold_weights."""
+    into the weights; see b200dsa_quant_q_fold_weights.  ue8m0=True rounds every scale up to a
+    power of two (the reference's use_ue8m0=True)."""
     require_cuda(q, w)
     if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.shape[-1] != 128:
         raise _lib.B200DSAError("q must be contiguous bf16 [..., 128]")
@@ -302,8 +330,8 @@ def quant_q_fold_weights(q: torch.Tensor, w: torch.Tensor, fold: float, *, q_fp8
         q_fp8 = torch.empty(q.shape, dtype=torch.float8_e4m3fn, device=q.device)
     if weights is None:
         weights = torch.empty(w.shape, dtype=torch.float32, device=q.device)
-    rc = _lib.load().b200dsa_quant_q_fold_weights(ptr(q), ptr(w), n_rows, fold, ptr(q_fp8), ptr(weights),
-                                                  stream_ptr())
+    rc = _lib.load().b200dsa_quant_q_fold_weights(ptr(q), ptr(w), n_rows, fold, int(bool(ue8m0)), ptr(q_fp8),
+                                                  ptr(weights), stream_ptr())
     check(rc, "b200dsa_quant_q_fold_weights")
     return q_fp8, weights
 
@@ -414,9 +442,12 @@ def router_linear_topk_softmax(x: torch.Tensor, w_r: torch.Tensor, n_keep: int, 
 
 
 def indexer_k_quant_and_cache(k: torch.Tensor, cache: torch.Tensor, slot_mapping: torch.Tensor,
-                              page_size: int) -> None:
+                              page_size: int, scale_fmt: Optional[str] = None) -> None:
     """Quantise new index keys and write them into their cache slots; see
-    b200dsa_indexer_k_quant_and_cache."""
+    b200dsa_indexer_k_quant_and_cache.  scale_fmt "ue8m0" stores power-of-two scales, None plain
+    amax/448 scales; any other string is rejected."""
+    if scale_fmt not in (None, "ue8m0"):
+        raise _lib.B200DSAError(f"unknown scale_fmt {scale_fmt!r} (None or 'ue8m0')")
     require_cuda(k, cache, slot_mapping)
     if k.dtype != torch.bfloat16 or not k.is_contiguous() or k.shape[-1] != 128:
         raise _lib.B200DSAError("k must be contiguous bf16 [n, 128]")
@@ -427,7 +458,8 @@ def indexer_k_quant_and_cache(k: torch.Tensor, cache: torch.Tensor, slot_mapping
     n = slot_mapping.numel()
     num_pages = cache.numel() // (page_size * 132)
     check(_lib.load().b200dsa_indexer_k_quant_and_cache(ptr(k), ptr(slot_mapping), n, ptr(cache), num_pages,
-                                                        page_size, ptr(status_word(k.device)), stream_ptr()),
+                                                        page_size, int(scale_fmt == "ue8m0"),
+                                                        ptr(status_word(k.device)), stream_ptr()),
           "b200dsa_indexer_k_quant_and_cache")
 
 

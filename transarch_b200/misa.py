@@ -163,7 +163,7 @@ def misa_linear_router_decode(x: torch.Tensor, w_r: torch.Tensor, q_fp8: torch.T
                                         max_cols=max_cols, fill=False)
     if logits.shape[0] <= 148 and logits.shape[1] >= 32768 and topk <= 4096:
         # few long rows: several CTAs per row
-        idx = K.topk_select_split(logits, topk, K.topk_scratch(logits.shape[0], logits.device),
+        idx = K.topk_select_split(logits, topk, K.topk_scratch_cached(logits.shape[0], logits.device),
                                   col_end=context_lens, sorted=True)
     else:
         idx = K.topk_select(logits, topk, col_end=context_lens, sorted=True)

@@ -1,6 +1,6 @@
 """Seeded synthetic state for the decode path, generated on the device.
 
-Shapes and value laws follow the benchmark configurations: index keys N(0,1) quantised to
+Shapes and value laws of a DeepSeek-V3.2-style decode batch: index keys N(0,1) quantised to
 e4m3 with a per-token scale and packed into pages of `page_size` tokens
 (page = page_size*128 fp8 bytes then page_size fp32 scales) behind a shuffled block table;
 latent KV 0.5*N(0,1) bf16 [*, 576]; index queries N(0,1) bf16; head weights N(0,1)/8;
