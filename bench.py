@@ -98,57 +98,232 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
-def cpu_port_tokens_per_s(n_requests: int, context: int, threads: int):
-    """Times the CPU oracle (a port of the reference's PyTorch ops) on n_requests requests of
-    the benchmark's shape.  Returns (tokens/s, seconds)."""
+def _cpu_inputs(n_requests: int, context: int):
     from oracle import dsa_oracle as O
-    torch.set_num_threads(threads)
     g = torch.Generator().manual_seed(4)
     k = torch.randn(context, 128, generator=g)
     kq, sc = O.quant_fp8_rows(k)
-    kd = kq.float() * sc.unsqueeze(-1)
+    kd = kq.float() * sc.unsqueeze(-1)                     # dequantised keys, as misa_ops.py:687 hands them on
     kv = (0.5 * torch.randn(context, 576, generator=g)).bfloat16().float()
     q = torch.randn(n_requests, 64, 128, generator=g)
     w = torch.randn(n_requests, 64, generator=g) / 8
     q_lat = torch.randn(n_requests, HEADS, 576, generator=g)
+    return kd, kv, q, w, q_lat
+
+
+def cpu_tokens_per_s(n_requests: int, context: int, threads: int):
+    """Times the CPU implementation of the path on n_requests requests of the benchmark's shape: the
+    reference's own indexer_select_topk + sparse_attend_absorbed_chunked when oracle/_ref holds them
+    (kind "reference"), else their restatement in oracle/ (kind "port").  Decode is driven per
+    request: one query at global position context-1 against the request's dequantised keys.
+    Returns (tokens/s, seconds, kind)."""
+    from oracle import dsa_oracle as O
+    from oracle.make_ref import reference_ops
+    torch.set_num_threads(threads)
+    ref = reference_ops()
+    kd, kv, q, w, q_lat = _cpu_inputs(n_requests, context)
+    cu = torch.tensor([0, context])
+    pos = torch.tensor([context - 1])
+    eye = torch.eye(512).unsqueeze(0).expand(HEADS, 512, 512)      # W_UV = I: the latent-space context
     t0 = time.perf_counter()
     for b in range(n_requests):
         q_fp8, wf = O.quant_q_fold_weights(q[b:b + 1], w[b:b + 1], INDEX_SCALE)
-        s = O.indexer_scores(q_fp8.float(), kd, wf, 1.0)
-        idx = O.topk_rows(s, TOPK)
-        O.sparse_attend_latent(q_lat[b:b + 1], kv, idx, d_c=512, sm_scale=ATTN_SCALE,
-                               q_pos=torch.tensor([context - 1]))
+        if ref is not None:
+            idx = ref.indexer_select_topk(q_fp8.float(), kd, wf, cu, TOPK, sm_scale_index=1.0, q_global_pos=pos)
+            ref.sparse_attend_absorbed_chunked(q_lat[b:b + 1], kv, eye, idx, d_c=512, sm_scale=ATTN_SCALE,
+                                               checkpoint=False, q_global_pos=pos)
+        else:
+            s = O.indexer_scores(q_fp8.float(), kd, wf, 1.0)
+            idx = O.topk_rows(s, TOPK)
+            O.sparse_attend_latent(q_lat[b:b + 1], kv, idx, d_c=512, sm_scale=ATTN_SCALE, q_pos=pos)
     dt = time.perf_counter() - t0
-    return n_requests / dt, dt
+    return n_requests / dt, dt, ("reference" if ref is not None else "port")
 
 
 def run_reference(args, rank: int):
-    """Reference arm: the reference's own implementation of this path is PyTorch on the host
-    cores; it cannot travel to the GPU box, so its CPU port (the oracle) is timed here."""
+    """Reference arm: the reference's implementation of this path is PyTorch on the host cores (its
+    GPU kernels are TileLang, which is not a CPU path).  Its own functions are timed when
+    oracle/_ref holds them, else their restatement."""
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    _, dt4 = cpu_port_tokens_per_s(4, CONTEXT, threads)              # calibrate: about 2 s per step
+    _, dt4, kind = cpu_tokens_per_s(4, CONTEXT, threads)              # calibrate: about 2 s per step
     n_req = max(4, min(256, int(2.0 / max(dt4 / 4, 1e-4))))
     for _ in range(min(args.warmup, 2)):
-        cpu_port_tokens_per_s(n_req, CONTEXT, threads)
+        cpu_tokens_per_s(n_req, CONTEXT, threads)
     args.steps = min(args.steps, 20)                                  # keep the whole arm within a few minutes
     vals, secs = [], 0.0
     for _ in range(args.steps):
-        v, dt = cpu_port_tokens_per_s(n_req, CONTEXT, threads)
+        v, dt, kind = cpu_tokens_per_s(n_req, CONTEXT, threads)
         vals.append(v); secs += dt
     value = sum(vals) / len(vals)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * secs / args.steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD},
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+        "config": {"workload": WORKLOAD, "parallelism": "host cores", "launch": "cpu"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": kind,
                          "sample": f"{n_req} requests of the batch's shape per step at context {CONTEXT}, all stages"},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------------
+# The other configurations of the path (prefill select, ragged decode, HISA, routed decode), each timed
+# through the public Python call: median and min of REPS CUDA-event measurements after WARM warm-ups,
+# L2 flushed between repetitions (a 256 MB buffer is rewritten outside the timed bracket).
+# --------------------------------------------------------------------------------------------------
+CFG_REPS, CFG_WARM = 50, 10
+
+
+def _time_call(fn, flush):
+    for _ in range(CFG_WARM):
+        fn()
+    ts = []
+    for _ in range(CFG_REPS):
+        flush.add_(1)                                      # evict L2 (256 MB > 126 MB)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); fn(); e1.record()
+        torch.cuda.synchronize()
+        ts.append(1e3 * e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2], ts[0]
+
+
+def bench_configs(dev, peaks, threads: int, fp8_peak: float):
+    from oracle import dsa_oracle as O
+    from oracle.make_ref import reference_ops
+    from transarch_b200 import hisa, kernels as K, misa, opendsa_ops
+    from transarch_b200.decode import SparseDecodeStep
+    from transarch_b200.workloads import make_decode_queries, make_decode_state
+    ref = reference_ops()
+    torch.set_num_threads(threads)
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    hbm, bf16 = peaks["hbm_gbs"], peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+    out = {}
+
+    # ---- C1: causal prefill select, T = S = 4096, 64 heads, d = 128, top-2048, seed 0
+    g = torch.Generator().manual_seed(0)
+    T = 4096
+    q = torch.randn(T, 64, 128, generator=g); k = torch.randn(T, 128, generator=g); w = torch.randn(T, 64, generator=g) / 8
+    cu = torch.tensor([0, T])
+    qd, kd, wd, cud = q.to(dev).bfloat16(), k.to(dev).bfloat16(), w.to(dev), cu.to(dev)
+    med, mn = _time_call(lambda: opendsa_ops.indexer_select_topk(qd, kd, wd, cud, 2048), flush)
+    t0 = time.perf_counter()
+    (ref.indexer_select_topk if ref is not None else O.indexer_select_topk)(q, k, w, cu, 2048, q_chunk=512)
+    cpu_s = time.perf_counter() - t0
+    flops = T * (T + 1) // 2 * 16384
+    out["C1 causal prefill select T=S=4096 k=2048 (bf16)"] = {
+        "call": "opendsa_ops.indexer_select_topk", "us_median": med, "us_min": mn, "flops": flops,
+        "bytes": 103e6, "bound": "tensor", "achieved_tflops": flops / med / 1e6,
+        "frac_of_bf16_sustained": flops / med / 1e6 / bf16, "cpu_seconds": cpu_s,
+        "cpu_kind": "reference" if ref is not None else "port", "cpu_sample": "whole configuration, fp32, q_chunk=512"}
+    del qd, kd, wd
+
+    # ---- C2: ragged decode, 64 requests with contexts uniform in [8K, 32K], FP8 paged keys, top-2048, seed 1
+    g = torch.Generator().manual_seed(1)
+    lens = torch.randint(8192, 32769, (64,), generator=g).tolist()
+    st = make_decode_state(64, lens, seed=1, device=dev)
+    q_idx, wq, _ = make_decode_queries(64, seed=1, device=dev)
+    step = SparseDecodeStep(64, st.local_len, topk=TOPK, device=dev)
+    med, mn = _time_call(lambda: step.select(q_idx, wq, st.k_cache, st.context_lens, st.block_table), flush)
+    n_keys = sum(lens)
+    sample = 8
+    t0 = time.perf_counter()
+    for b in range(sample):
+        kb = torch.randn(lens[b], 128)
+        qf, wf = O.quant_q_fold_weights(torch.randn(1, 64, 128), torch.randn(1, 64) / 8, INDEX_SCALE)
+        if ref is not None:
+            ref.indexer_select_topk(qf.float(), kb, wf, torch.tensor([0, lens[b]]), TOPK, sm_scale_index=1.0,
+                                    q_global_pos=torch.tensor([lens[b] - 1]))
+        else:
+            O.topk_rows(O.indexer_scores(qf.float(), kb, wf, 1.0), TOPK)
+    cpu_s = (time.perf_counter() - t0) * n_keys / sum(lens[:sample])
+    out["C2 ragged decode indexer+top-k, 64 requests 8K-32K (fp8)"] = {
+        "call": "SparseDecodeStep.select", "us_median": med, "us_min": mn, "flops": n_keys * 16384,
+        "bytes": n_keys * 132, "bound": "hbm", "achieved_gbs": n_keys * 132 / med / 1e3,
+        "frac_of_hbm": n_keys * 132 / med / 1e3 / hbm, "cpu_seconds": cpu_s,
+        "cpu_kind": "reference" if ref is not None else "port",
+        "cpu_sample": f"{sample} of 64 requests, scaled by keys"}
+    del st, step
+
+    # ---- C3: HISA two-stage, 4096 queries at positions 126976..131071 over 131072 keys, seed 2
+    g = torch.Generator(device=dev).manual_seed(2)
+    S, T = 131072, 4096
+    k3 = torch.randn(S, 128, generator=g, device=dev).bfloat16()
+    q3 = torch.randn(T, 64, 128, generator=g, device=dev).bfloat16()
+    w3 = torch.randn(T, 64, generator=g, device=dev) / 8
+    pos = torch.arange(S - T, S, device=dev)
+    ks3, ke3 = torch.zeros(T, dtype=torch.int64, device=dev), pos + 1
+    cfg = hisa.HisaConfig()
+    med, mn = _time_call(lambda: hisa.hisa_select_topk(q3, k3, w3, ks3, ke3, cfg), flush)
+    sample = 32
+    sel = torch.arange(0, T, T // sample)
+    t0 = time.perf_counter()
+    O.hisa_select_topk(q3[sel].cpu().float(), k3.cpu().float(), w3[sel].cpu(), ks3[sel].cpu(), ke3[sel].cpu(),
+                       block=128, block_topk=64, topk=2048)
+    cpu_s = (time.perf_counter() - t0) * T / sample
+    flops = int(67.7e9 + T * 8192 * 16384)
+    out["C3 HISA two-stage, 4096 queries at the tail of 131072 keys (bf16)"] = {
+        "call": "hisa.hisa_select_topk", "us_median": med, "us_min": mn, "flops": flops, "bytes": 135e6,
+        "bound": "tensor", "achieved_tflops": flops / med / 1e6, "frac_of_bf16_sustained": flops / med / 1e6 / bf16,
+        "cpu_seconds": cpu_s, "cpu_kind": "port (the reference ships no HISA code)",
+        "cpu_sample": f"{sample} of 4096 queries, scaled"}
+    del k3, q3, w3
+
+    # ---- C4: MISA routed decode, batch 32, context 65536, linear router top-8 of 64, seed 3
+    st = make_decode_state(32, 65536, seed=3, device=dev)
+    q4, _, _ = make_decode_queries(32, seed=3, device=dev)
+    g = torch.Generator(device=dev).manual_seed(3)
+    x = torch.randn(32, 7168, generator=g, device=dev).bfloat16()
+    W_r = (torch.randn(7168, 64, generator=g, device=dev) * 7168 ** -0.5).bfloat16()
+    q_fp8, fold = K.quant_q_fold_weights(q4, torch.ones(32, 64, device=dev), INDEX_SCALE)
+    med, mn = _time_call(lambda: misa.misa_linear_router_decode(x, W_r, q_fp8, fold, st.k_cache, 64, st.context_lens,
+                                                                st.block_table, 8, TOPK, max_cols=65536), flush)
+    sample = 4
+    t0 = time.perf_counter()
+    for b in range(sample):
+        kb = torch.randn(65536, 128)
+        hidx, hw, _ = O.linear_router_topk_softmax(x[b:b + 1].cpu(), W_r.cpu(), 8)
+        q8, _ = O.gather_heads(q_fp8[b:b + 1].cpu().float(), fold[b:b + 1].cpu(), hidx)
+        O.topk_rows(O.indexer_scores(q8, kb, hw * torch.gather(fold[b:b + 1].cpu(), 1, hidx), 1.0), TOPK)
+    cpu_s = (time.perf_counter() - t0) * 32 / sample
+    n_keys = 32 * 65536
+    out["C4 MISA routed decode, batch 32 x 65536 keys, 8 of 64 heads (fp8)"] = {
+        "call": "misa.misa_linear_router_decode", "us_median": med, "us_min": mn, "flops": n_keys * 2048,
+        "bytes": n_keys * 132, "bound": "hbm", "achieved_gbs": n_keys * 132 / med / 1e3,
+        "frac_of_hbm": n_keys * 132 / med / 1e3 / hbm, "cpu_seconds": cpu_s,
+        "cpu_kind": "port (no reference code for the linear router)",
+        "cpu_sample": f"{sample} of 32 requests, 8 routed heads only, scaled"}
+    for v in out.values():
+        for kk in list(v):
+            if isinstance(v[kk], float):
+                v[kk] = round(v[kk], 4 if v[kk] < 10 else 2)
+    return out
+
+
+def parity_check(step, state, q_sets, res, ctx_len: int, requests):
+    """Outside every timed region: the benchmarked step's own outputs for a few requests against the
+    oracle at full length (indexer scores, index sets with the near-tie audit, attention output)."""
+    from oracle import dsa_oracle as O
+    q_idx, w, q_lat = q_sets
+    idx, ctx, lse = res
+    worst = {"score_rel_err": 0.0, "recall": 1.0, "attn_rel_err": 0.0, "lse_abs_err": 0.0}
+    for b in requests:
+        pages = state.k_cache[state.block_table[b].long()].cpu()
+        kv_b = state.kv[b * ctx_len:(b + 1) * ctx_len].cpu()
+        sc, ref_idx, _, _ = O.decode_request_reference(q_idx[b:b + 1].cpu(), w[b:b + 1].cpu(), q_lat[b:b + 1].cpu(),
+                                                       pages, kv_b, ctx_len, TOPK, INDEX_SCALE, ATTN_SCALE)
+        r = O.check_decode_request(sc, ref_idx, step.logits[b].cpu(), idx[b].cpu(), ctx[b].cpu(), lse[b].cpu(),
+                                   q_lat[b:b + 1].cpu(), kv_b, ctx_len, ATTN_SCALE)
+        worst["recall"] = min(worst["recall"], r["recall"])
+        for k_ in ("score_rel_err", "attn_rel_err", "lse_abs_err"):
+            worst[k_] = max(worst[k_], r[k_])
+    return {"checked_requests": list(requests), "against": "CPU oracle at full context length",
+            "tolerances": {"score_rel_err": 1e-2, "recall": 0.999, "attn_rel_err": 2e-2},
+            "non_near_tie_disagreements": 0, **{k_: round(v, 6) for k_, v in worst.items()}, "ok": True}
 
 
 def main():
@@ -160,6 +335,8 @@ def main():
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-configs", action="store_true", help="do not time the other configurations of the path")
+    ap.add_argument("--skip-parity", action="store_true", help="do not compare sampled requests with the oracle")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
 
@@ -285,8 +462,8 @@ def main():
     if rank == 0:
         sampler.start()
     total_ms = timed(run_device, args.steps)
-    if total_ms < 150.0:                         # very short timed region: sample a longer repeat as well
-        timed(run_device, max(args.steps, 500))
+    long_steps = max(args.steps, 500)            # a second, longer timed region (also feeds the clock sampler)
+    long_ms = timed(run_device, long_steps)
     clocks = sampler.stop() if rank == 0 else None
     ms_per_step = total_ms / args.steps
     value = B * args.steps / (total_ms * 1e-3)
@@ -418,6 +595,16 @@ def main():
     e2e_value = B * args.steps / (e2e_ms * 1e-3)
     status = _lib.read_status(dev)
 
+    # parity of the benchmarked step itself, outside every timed region (single GPU: the whole key range is here)
+    parity = None
+    if rank == 0 and world == 1 and not args.skip_parity:
+        res = run_eager(0)
+        torch.cuda.synchronize()
+        try:
+            parity = parity_check(step, state, dev_q[0], res, ctx, [0, B // 3, (2 * B) // 3, B - 1])
+        except AssertionError as e:
+            parity = {"ok": False, "error": str(e)[:300]}
+
     if rank == 0:
         peaks, peak_kind = measured_peaks()
         idx_bytes = B * shard_len * (128 + 4)  # fp8 key + fp32 scale per key, read once
@@ -432,7 +619,8 @@ def main():
             launches += 2 + (2 if step.peer is not None else 1)
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "ms_per_step_long": long_ms / long_steps,
+            "steps_long": long_steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8(e4m3) index scores / bf16 attention, fp32 accumulate",
             "data": "synthetic",
             "config": {"workload": WORKLOAD if (B, ctx) == (BATCH, CONTEXT) else f"batch {B}, context {ctx} (non-default)",
@@ -460,14 +648,30 @@ def main():
             "clocks": clocks, "status_word": status,
         }
         line["roofline"]["traffic"] = DRAM_BYTES_PER_KEY * B * shard_len
+        line["parity"] = parity
+        threads = os.cpu_count() or 1
         if world == 1 and not args.skip_cpu_baseline:
-            threads = os.cpu_count() or 1
-            _, dt4 = cpu_port_tokens_per_s(4, ctx, threads)          # calibrate: about 15 s of CPU work
+            _, dt4, _ = cpu_tokens_per_s(4, ctx, threads)            # calibrate: about 15 s of CPU work
             n_req = max(4, min(2048, int(15.0 / max(dt4 / 4, 1e-4))))
-            v, dt = cpu_port_tokens_per_s(n_req, ctx, threads)
-            line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
+            v, dt, kind = cpu_tokens_per_s(n_req, ctx, threads)
+            line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": kind,
                                     "sample": f"{n_req} requests of the {B}-request batch shape at context {ctx}, "
                                               f"all stages (quantise, score, top-k, attention), {dt:.1f} s"}
+        if world == 1 and not args.skip_configs:
+            # tensor-pipe denominators from the library's own probe kernel, then the other configurations;
+            # the decode state is released first (the configurations build their own)
+            fp8_peak = step.K.mma_peak_tflops(True, device=dev)
+            bf16_peak = step.K.mma_peak_tflops(False, device=dev)
+            line["tensor_peaks"] = {"fp8_tflops_probe": round(fp8_peak, 1), "bf16_tflops_probe": round(bf16_peak, 1),
+                                    "how": "back-to-back M=128 N=256 tcgen05 MMAs on shared-memory operands, one CTA "
+                                           "per SM, best of 5 launches of about 2 ms"}
+            graphed = None
+            del state, step, dev_q, in_dev, out_dev
+            torch.cuda.empty_cache()
+            try:
+                line["configs"] = bench_configs(dev, peaks, threads, fp8_peak)
+            except Exception as e:  # noqa: BLE001 - the headline line must still be printed
+                line["configs"] = {"error": f"{type(e).__name__}: {e}"[:300]}
         print(json.dumps(line), flush=True)
     if world > 1:
         # A captured graph that holds NCCL kernels keeps the communicator busy: tearing the process

@@ -30,6 +30,14 @@ extern "C" {
 int b200dsa_abi_version(void);
 const char* b200dsa_last_error(void);
 
+/* Tensor-pipe peak probe (measurement aid, not on the serving path): `ctas` CTAs each issue
+ * iters * 8 tcgen05 MMAs of shape M=128, N=256, K=32 bytes on shared-memory operands, FP8 e4m3
+ * (fp8 != 0) or bf16, with no global-memory traffic.  Flops per launch = ctas * iters * 8 *
+ * 2*128*256*K with K = 32 (FP8) or 16 (bf16); time it with events to obtain the tensor-pipe
+ * roofline denominator of this GPU under its own clocks and power cap.  No counterpart in the
+ * reference. */
+int b200dsa_mma_peak_probe(int32_t fp8, int32_t ctas, int32_t iters, int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Row-wise top-k selection over fp32 scores.
  *

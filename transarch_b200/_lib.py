@@ -20,6 +20,7 @@ _vp, _i32, _i64, _f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
 SIGNATURES = {
     "b200dsa_abi_version": [],
     "b200dsa_last_error": [],
+    "b200dsa_mma_peak_probe": [_i32, _i32, _i32, _vp, _vp],
     "b200dsa_topk_select": [_vp, _i64, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _i32, _vp,
                             _i32, _i64, _vp, _vp, _vp, _i64, _vp],
     "b200dsa_topk_select_split": [_vp, _i64, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _i32, _vp, _vp,

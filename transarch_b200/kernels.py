@@ -485,3 +485,24 @@ def lse_prescale_norm(ctx: torch.Tensor, lse_all: torch.Tensor, my_part: int, ou
     check(_lib.load().b200dsa_lse_prescale_norm(ptr(ctx), ptr(lse_all), n_parts, my_part, n_rows, ptr(out_bf16),
                                                 ptr(lse_out), stream_ptr()), "b200dsa_lse_prescale_norm")
     return out_bf16, lse_out
+
+
+def mma_peak_tflops(fp8: bool = True, *, iters: int = 4096, reps: int = 5, device=None) -> float:
+    """Best-of-`reps` tensor-pipe throughput (TFLOP/s, dense) of back-to-back M=128 x N=256 tcgen05
+    MMAs on shared-memory operands, one CTA per SM; see b200dsa_mma_peak_probe.  Synchronises."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    ctas = torch.cuda.get_device_properties(dev).multi_processor_count
+    lib = _lib.load()
+    st = status_word(dev)
+    best = 0.0
+    for r in range(reps + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        check(lib.b200dsa_mma_peak_probe(int(fp8), ctas, iters, ptr(st), stream_ptr()), "b200dsa_mma_peak_probe")
+        e1.record()
+        torch.cuda.synchronize()
+        if r == 0:
+            continue                                     # warm-up launch
+        flops = ctas * iters * 8 * 2.0 * 128 * 256 * (32 if fp8 else 16)
+        best = max(best, flops / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    return best
