@@ -36,9 +36,12 @@ class HisaConfig:
 
 
 @torch.no_grad()
-def hisa_block_topk(q: torch.Tensor, k_pooled: torch.Tensor, w: torch.Tensor, ks: torch.Tensor, ke: torch.Tensor,
-                    cfg: HisaConfig, sm_scale: float) -> torch.Tensor:
-    """Stage 1: int32 [T, m] ids of the kept key blocks, best first, -1 padded."""
+def hisa_block_logits(q: torch.Tensor, k_pooled: torch.Tensor, w: torch.Tensor, ks: torch.Tensor, ke: torch.Tensor,
+                      cfg: HisaConfig, sm_scale: float) -> torch.Tensor:
+    """Stage-1 block scores fp32 [T, 128*ceil(n_blocks/128)]: the indexer formula on the pooled keys,
+    -inf outside the query's block range [ks // P, ceil(ke / P)), +inf on the force-kept blocks (what
+    the reference's clean_and_maintain_logits_ fragment does to a block-score matrix,
+    block_ops.py:636-666)."""
     P = cfg.hisa_k_block_size
     T = q.shape[0]
     nb = k_pooled.shape[0]
@@ -60,6 +63,14 @@ def hisa_block_topk(q: torch.Tensor, k_pooled: torch.Tensor, w: torch.Tensor, ks
     if cfg.keep_first_block:
         col = bks.clamp(max=logits.shape[1] - 1).long().view(-1, 1)
         logits.scatter_(1, col, torch.where(has, inf, logits.gather(1, col)))
+    return logits
+
+
+@torch.no_grad()
+def hisa_block_topk(q: torch.Tensor, k_pooled: torch.Tensor, w: torch.Tensor, ks: torch.Tensor, ke: torch.Tensor,
+                    cfg: HisaConfig, sm_scale: float) -> torch.Tensor:
+    """Stage 1: int32 [T, m] ids of the kept key blocks, best first, -1 padded."""
+    logits = hisa_block_logits(q, k_pooled, w, ks, ke, cfg, sm_scale)
     return K.topk_select(logits, cfg.hisa_block_topk, keep_pos_inf=True, sorted=True)
 
 
