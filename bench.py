@@ -611,10 +611,11 @@ def main():
         achieved = idx_bytes / (indexer_ms * 1e-3) / 1e9
         h2d = sum(t.numel() * t.element_size() for t in host_q[0])
         d2h = sum(t.numel() * t.element_size() for t in out_host[0])
-        # our kernels per step: q quantisation, indexer, top-k (3 in the split form), attention; sharded:
+        # our kernels per step: q quantisation, indexer + select (fused: 2 launches; else indexer and a top-k of
+        # 3 kernels in the split form), attention; sharded:
         # + merge top-k, compaction and either barrier + peer combine or the bf16 share kernel (NCCL's
         # own kernels are not counted)
-        launches = 2 + (3 if step.topk_scratch is not None else 1) + 1
+        launches = 1 + (2 if step.fused_scratch is not None else 1 + (3 if step.topk_scratch is not None else 1)) + 1
         if world > 1:
             launches += 2 + (2 if step.peer is not None else 1)
         line = {

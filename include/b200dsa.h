@@ -5,7 +5,8 @@
  * Return value: 0 on success, a negative B200DSA_E* code when the arguments are rejected
  * (nothing is launched in that case).  Kernels that contain bounded waits or index checks
  * report through a caller-owned int32 `status` word in device memory (0 = ok,
- * 1 = a wait gave up, 2 = an out-of-range index was skipped); the caller zeroes it once
+ * 1 = a wait gave up, 2 = an out-of-range index was skipped, 3 = a fused selection without logits
+ * could not prove a candidate list complete); the caller zeroes it once
  * and may read it whenever convenient.
  *
  * "Reference" citations name files of the TransArch repository whose behaviour the entry
@@ -150,6 +151,36 @@ int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* weights, co
                                      int32_t max_cols, float out_scale,
                                      float* logits, int64_t logits_stride, const uint64_t* head_mask,
                                      float* logits_gated, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Fused decode selection: the same scores as b200dsa_indexer_paged_fp8_logits and, from them, the
+ * top-k key positions of every row, in two launches and without a pass over the logits.  The
+ * indexer's epilogue appends every score at or above a floor (taken from the first tiles each CTA
+ * scores of a row) to the row's candidate list; the second kernel selects exactly from the list.
+ * A list that cannot be proven complete (fewer than k entries at or above the largest floor used
+ * for the row, or more than 8192 entries) is not trusted: the row is then selected from `logits`.
+ * Replaces, in one call, MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/misa_ops.py:182
+ * (+ :393-401, the logits matrix) and the torch.topk at indexers.py:566-568.
+ *
+ *   arguments up to out_scale: as b200dsa_indexer_paged_fp8_logits (no head mask)
+ *   logits / logits_stride    [n_rows, >= max_cols] fp32, written as a by-product and read only by the
+ *                             fallback.  May be NULL: nothing but the candidate lists is then written,
+ *                             and a row whose list is not provably complete (probability below 1e-6
+ *                             per row) is selected from the list anyway with *status raised to 3.
+ *   k <= 2048, sorted, row_pos_offset, out_idx / out_val / out_stride: as b200dsa_topk_select_split;
+ *                             results equal b200dsa_topk_select's on the same logits
+ *   scratch_cand              n_rows * 8192 uint64 (8-byte aligned)
+ *   scratch_count             2 * n_rows int32, ZERO before the first call; left zero by every call
+ * Calls that share scratch must not overlap on the GPU.
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_indexer_paged_fp8_topk(const void* q_fp8, const float* weights, const void* cache,
+                                   int32_t num_pages, int32_t page_size, const int32_t* context_lens,
+                                   const int32_t* block_table, int64_t block_table_stride,
+                                   const int32_t* row_table, int32_t n_rows, int32_t next_n,
+                                   int32_t max_cols, float out_scale, float* logits, int64_t logits_stride,
+                                   int32_t k, int32_t sorted, const int32_t* row_pos_offset,
+                                   void* scratch_cand, int32_t* scratch_count, int32_t* out_idx,
+                                   float* out_val, int64_t out_stride, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Token logits inside per-row lists of 128-key blocks, bf16 keys (tcgen05 bf16 contraction).

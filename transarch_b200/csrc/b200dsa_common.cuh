@@ -16,6 +16,7 @@ namespace b200dsa {
 constexpr int kDevOk = 0;
 constexpr int kDevWaitTimeout = 1;   // a bounded wait gave up
 constexpr int kDevBadIndex = 2;      // an index / page id outside the stated range was skipped
+constexpr int kDevSelectIncomplete = 3;  // fused selection without logits: a candidate list could not be proven complete
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

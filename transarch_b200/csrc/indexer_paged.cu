@@ -17,6 +17,8 @@
 // grid is persistent: the list of all (row, tile) pairs is split evenly over the CTAs, so
 // ragged context lengths stay balanced.  Every wait is bounded; on a timeout the CTA raises
 // the status word, drains its loads, frees TMEM and returns.
+#include <stdio.h>
+
 #include "b200dsa_common.cuh"
 
 namespace b200dsa {
@@ -27,12 +29,26 @@ constexpr int kDim = 128;
 constexpr int kMaxRows = 1024;  // rows per launch (host loops beyond that)
 constexpr int kThreads = 192;
 
-template <bool kFp8>
+// Fused selection (kEmit): the epilogue also appends every score at or above a per-segment floor to
+// the row's candidate list in global memory, so that the top-k kernel never reads the logits.
+//   segment  = the run of consecutive tiles of one row inside a CTA's share of the tile list
+//   floor    = taken from the scores of the segment's first kSampleTiles tiles (buffered in shared
+//              memory, histogrammed over the top 12 key bits): the lower edge of the bin at which the
+//              sample holds j' = j0 + 4 sqrt(j0) + 2 scores, j0 = sample share of cand_target
+//   row_floor[row] = max of the floors of the row's segments: the list is complete above it
+constexpr int kSampleTiles = 16;
+constexpr int kSampleMax = kSampleTiles * kTileKeys;   // 2048 buffered scores
+constexpr int kEmitHistWords = 2048;                   // 4096 bins, two 16-bit counters per word
+constexpr int kWarpBuf = 128;                          // private candidate buffer of an epilogue warp
+constexpr int kEmitCap = 8192;                         // entries per row of the global candidate lists
+
+template <bool kFp8, bool kEmit = false>
 struct PagedCfg {
   static constexpr int kElem = kFp8 ? 1 : 2;
   static constexpr int kStageBytes = kTileKeys * kDim * kElem;  // 16 KB / 32 KB
   static constexpr int kQBytes = kHeads * kDim * kElem;         // 8 KB / 16 KB
-  static constexpr int kStages = kFp8 ? 5 : 5;
+  static constexpr int kStages = kEmit ? 4 : 5;
+  static constexpr int kEmitBytes = kEmit ? (kSampleMax * 4 + kEmitHistWords * 4 + 4 * kWarpBuf * 8 + 64) : 0;
   static constexpr int kCtasPerSm = kFp8 ? 2 : 1;
   static constexpr int kKSteps = kFp8 ? 4 : 8;                  // MMAs per tile (32 B of K each)
   // Per-tile key scales travel through their own ring.  A slot is reused kScaleSlots tiles
@@ -41,7 +57,7 @@ struct PagedCfg {
   static constexpr int kScaleSlots = kStages + 2;
   static constexpr int kScaleBytes = kFp8 ? kScaleSlots * kTileKeys * 4 : 0;
   static constexpr int kSmemBytes =
-      kStages * kStageBytes + 2 * kQBytes + kScaleBytes + 1024 /*align*/ + 512 /*barriers*/;
+      kStages * kStageBytes + 2 * kQBytes + kScaleBytes + 1024 /*align*/ + 512 /*barriers*/ + kEmitBytes;
 };
 
 struct PagedIndexerParams {
@@ -66,13 +82,19 @@ struct PagedIndexerParams {
   const uint64_t* head_mask;    // nullable [n_rows]: bit h set = head h counts towards logits_gated
   float* logits_gated;          // nullable [n_rows, logits_stride]: the same sum over the masked heads only
   int32_t* status;
+  // fused selection (kEmit kernels only)
+  uint64_t* cand;               // [n_rows, kEmitCap] composites (ordered score << 32 | ~position)
+  int32_t* cand_count;          // [n_rows] entries appended (may exceed kEmitCap: list unusable)
+  uint32_t* row_floor;          // [n_rows] largest floor any segment of the row used (ordered-float bits; 0 = none)
+  const int32_t* row_pos_offset;  // nullable [n_rows]: added to the column to give the output position
+  int32_t cand_target;          // candidates per row the floors aim at before the safety margin
 };
 
-template <bool kFp8>
-__global__ void __launch_bounds__(kThreads, PagedCfg<kFp8>::kCtasPerSm)
+template <bool kFp8, bool kEmit = false>
+__global__ void __launch_bounds__(kThreads, PagedCfg<kFp8, kEmit>::kCtasPerSm)
 indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
                      const PagedIndexerParams p) {
-  using Cfg = PagedCfg<kFp8>;
+  using Cfg = PagedCfg<kFp8, kEmit>;
   pdl_launch_dependents();
   pdl_wait_prior();
   extern __shared__ uint8_t smem_dyn[];
@@ -93,6 +115,13 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
   uint64_t* acc_full = q_empty + 2;            // [2]
   uint64_t* acc_empty = acc_full + 2;          // [2]
   uint64_t* sc_full = acc_empty + 2;           // [kScaleSlots]
+  uint64_t* rv_bar = sc_full + Cfg::kScaleSlots;  // [1] rendezvous of the 128 epilogue threads (kEmit)
+  uint8_t* emit_mem = reinterpret_cast<uint8_t*>(bars) + 512;
+  float* s_samp = reinterpret_cast<float*>(emit_mem);                                  // [kSampleMax]
+  uint32_t* s_hist = reinterpret_cast<uint32_t*>(emit_mem + kSampleMax * 4);           // [kEmitHistWords]
+  uint64_t* s_wbuf = reinterpret_cast<uint64_t*>(emit_mem + kSampleMax * 4 + kEmitHistWords * 4);  // [4][kWarpBuf]
+  float* s_floor = reinterpret_cast<float*>(emit_mem + kSampleMax * 4 + kEmitHistWords * 4 + 4 * kWarpBuf * 8);
+  int* s_wtot = reinterpret_cast<int*>(s_floor + 1);                                   // [4] + [1] total
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -124,6 +153,7 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       mbar_init(&acc_empty[s], 128);
     }
     for (int s = 0; s < Cfg::kScaleSlots; ++s) mbar_init(&sc_full[s], 1);
+    mbar_init(rv_bar, 128);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -311,6 +341,44 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
     uint32_t hm0 = 0, hm1 = 0;
     const bool dual = p.logits_gated != nullptr;
     const int32_t* trow = p.table;
+    // fused selection state (identical in all 128 epilogue threads except wcnt, which is per warp)
+    const int tix = lane_base + lane;                 // this thread's key inside a tile
+    const bool emit = kEmit && p.cand != nullptr;
+    uint64_t* wbuf = s_wbuf + (warp & 3) * kWarpBuf;
+    int seg_g0 = 0, samp_tiles = 0, wcnt = 0, rv_phase = 0, posoff = 0;
+    float floor_v = -3.402823466e38f;
+    bool floor_ready = false, emit_abort = false;
+    // append the warp's buffered candidates to the row's global list (one atomic per flush)
+    auto flush_warp = [&](int r) {
+      __syncwarp();
+      if (wcnt > 0) {
+        int base = 0;
+        if (lane == 0) base = atomicAdd(p.cand_count + r, wcnt);
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (base + wcnt <= kEmitCap) {
+          uint64_t* dst = p.cand + static_cast<int64_t>(r) * kEmitCap + base;
+          for (int i = lane; i < wcnt; i += 32) dst[i] = wbuf[i];
+        }
+        wcnt = 0;
+      }
+      __syncwarp();
+    };
+    auto emit_one = [&](float v, int32_t pos, int r) {
+      const bool take = v >= floor_v && v <= 3.402823466e38f;   // NaN, -inf and +inf never qualify
+      const unsigned act = __ballot_sync(0xffffffffu, take);
+      if (take)
+        wbuf[wcnt + __popc(act & ((1u << lane) - 1))] =
+            (static_cast<uint64_t>(float_to_ordered(v)) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(pos));
+      wcnt += __popc(act);
+      if (wcnt > kWarpBuf - 32) flush_warp(r);
+    };
+    // bounded rendezvous of the 128 epilogue threads (shared-memory writes before it are visible after it)
+    auto rendezvous = [&]() {
+      mbar_arrive(rv_bar);
+      const bool ok = mbar_wait(rv_bar, rv_phase & 1, abort_flag);
+      ++rv_phase;
+      return __all_sync(0xffffffffu, ok);
+    };
     for (int g = g0; g < g1; ++g) {
       while (g >= s_prefix[row + 1]) ++row;
       const int t = g - s_prefix[row];
@@ -331,6 +399,12 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
           hm1 = static_cast<uint32_t>(hm >> 32);
         }
         prev_row = row;
+        if (emit) {   // a new segment: sample its first tiles before anything is appended
+          seg_g0 = g;
+          samp_tiles = min(kSampleTiles, min(g1, s_prefix[row + 1]) - g);
+          floor_ready = false;
+          posoff = p.row_pos_offset ? p.row_pos_offset[row] : 0;
+        }
       }
       const int key = t * kTileKeys + lane_base + lane;  // column of this thread
       float kscale = 1.0f;
@@ -382,12 +456,82 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
           acc1 = fmaf(fmaxf(__uint_as_float(v1[j]), 0.f), w[32 + j], acc1);
         }
       }
-      if (key < tile_cols) {
-        const float out = keep ? (acc0 + acc1) * kscale * p.out_scale : -INFINITY;
-        p.logits[static_cast<int64_t>(row) * p.logits_stride + key] = out;
+      const float out = keep ? (acc0 + acc1) * kscale * p.out_scale : -INFINITY;
+      if (key < tile_cols && p.logits) p.logits[static_cast<int64_t>(row) * p.logits_stride + key] = out;
+      if constexpr (kEmit) {
+        if (emit) {
+          const int seg_tile = g - seg_g0;
+          if (!floor_ready) {
+            s_samp[seg_tile * kTileKeys + tix] = out;
+            if (seg_tile == samp_tiles - 1) {
+              // ---- floor of this segment from its buffered head
+              const int n_samp = samp_tiles * kTileKeys;
+              const int key0 = (t - seg_tile) * kTileKeys;                      // first key of the segment
+              const int m_valid = max(0, min(n_samp, cols - key0));
+              const float j0 = static_cast<float>(p.cand_target) * static_cast<float>(m_valid) /
+                               static_cast<float>(max(cols, 1));
+              const int want = static_cast<int>(ceilf(j0 + 4.0f * sqrtf(j0) + 2.0f));
+              floor_v = -3.402823466e38f;
+              if (want < (m_valid * 9) / 10) {                                  // uniform over the 128 threads
+                for (int i = tix; i < kEmitHistWords; i += 128) s_hist[i] = 0;
+                if (!rendezvous()) { emit_abort = true; break; }              // samples written, histogram clear
+                for (int i = 0; i < samp_tiles; ++i) {
+                  const float v = s_samp[i * kTileKeys + tix];
+                  if (v >= -3.402823466e38f && v <= 3.402823466e38f) {
+                    const uint32_t bin = float_to_ordered(v) >> 20;
+                    atomicAdd(&s_hist[bin >> 1], 1u << (16 * (bin & 1)));
+                  }
+                }
+                if (!rendezvous()) { emit_abort = true; break; }
+                // thread tix owns bins [32 tix, 32 tix + 32); higher threads hold higher bins
+                int chunk = 0;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  const uint32_t wv = s_hist[16 * tix + i];
+                  chunk += static_cast<int>(wv & 0xffffu) + static_cast<int>(wv >> 16);
+                }
+                int suf = chunk;                       // inclusive suffix over the lanes of this warp
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                  const int u = __shfl_down_sync(0xffffffffu, suf, o);
+                  if (lane + o < 32) suf += u;
+                }
+                if (lane == 0) s_wtot[warp & 3] = suf;
+                if (tix == 0) *s_floor = -3.402823466e38f;                      // fewer valid samples than wanted
+                if (!rendezvous()) { emit_abort = true; break; }
+                int above = suf - chunk;               // samples in the bins above this thread's
+                for (int wq = (warp & 3) + 1; wq < 4; ++wq) above += s_wtot[wq];
+                if (above < want && above + chunk >= want) {
+                  for (int b = 31; b >= 0; --b) {
+                    const uint32_t wv = s_hist[16 * tix + (b >> 1)];
+                    const int c = static_cast<int>((b & 1) ? (wv >> 16) : (wv & 0xffffu));
+                    if (above + c >= want) {
+                      *s_floor = fmaxf(ordered_to_float(static_cast<uint32_t>(32 * tix + b) << 20), -3.402823466e38f);
+                      break;
+                    }
+                    above += c;
+                  }
+                }
+                if (!rendezvous()) { emit_abort = true; break; }
+                floor_v = *s_floor;
+              }
+              floor_ready = true;
+              for (int i = 0; i < samp_tiles; ++i)                              // replay the buffered head
+                emit_one(s_samp[i * kTileKeys + tix], (t - seg_tile + i) * kTileKeys + tix + posoff, row);
+              if (!rendezvous()) { emit_abort = true; break; }                // buffer free for the next segment
+            }
+          } else {
+            emit_one(out, key + posoff, row);
+          }
+          if ((g + 1 == g1) || (g + 1 >= s_prefix[row + 1])) {                 // end of the segment
+            flush_warp(row);
+            if (tix == 0) atomicMax(p.row_floor + row, float_to_ordered(floor_v));
+          }
+        }
       }
       ++ait;
     }
+    if (emit_abort) *abort_flag = 1;
   }
 
   // ---------------------------------------------------------------------- common tail
@@ -436,11 +580,11 @@ static int sm_count() {
   return n;
 }
 
-template <bool kFp8>
+template <bool kFp8, bool kEmit = false>
 static int launch_paged(const CUtensorMap& mk, const CUtensorMap& mq, PagedIndexerParams p, int64_t est_tiles,
                         cudaStream_t stream) {
-  using Cfg = PagedCfg<kFp8>;
-  cudaError_t e = cudaFuncSetAttribute(indexer_paged_kernel<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  using Cfg = PagedCfg<kFp8, kEmit>;
+  cudaError_t e = cudaFuncSetAttribute(indexer_paged_kernel<kFp8, kEmit>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg::kSmemBytes);
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
@@ -448,7 +592,7 @@ static int launch_paged(const CUtensorMap& mk, const CUtensorMap& mq, PagedIndex
   }
   int grid = sm_count() * Cfg::kCtasPerSm;
   if (est_tiles > 0 && est_tiles < grid) grid = static_cast<int>(est_tiles);
-  e = launch_chained(indexer_paged_kernel<kFp8>, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, mk, mq, p);
+  e = launch_chained(indexer_paged_kernel<kFp8, kEmit>, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, mk, mq, p);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
@@ -461,27 +605,40 @@ static int launch_paged(const CUtensorMap& mk, const CUtensorMap& mq, PagedIndex
 
 using namespace b200dsa;
 
-extern "C" int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* weights, const void* cache,
-                                                int32_t num_pages, int32_t page_size, const int32_t* context_lens,
-                                                const int32_t* block_table, int64_t block_table_stride,
-                                                const int32_t* row_table, int32_t n_rows, int32_t next_n,
-                                                int32_t max_cols, float out_scale,
-                                                float* logits, int64_t logits_stride, const uint64_t* head_mask,
-                                                float* logits_gated, int32_t* status, void* stream) {
-  if (n_rows == 0) return B200DSA_OK;
-  if (!q_fp8 || !weights || !cache || !context_lens || !block_table || !logits || !status || n_rows < 0 ||
-      next_n < 1 || num_pages < 1 || max_cols < 0 || logits_stride < max_cols ||
-      ((head_mask == nullptr) != (logits_gated == nullptr))) {
-    set_last_error("b200dsa_indexer_paged_fp8_logits: bad argument");
+namespace b200dsa {
+
+struct EmitArgs {
+  uint64_t* cand = nullptr;
+  int32_t* cand_count = nullptr;
+  uint32_t* row_floor = nullptr;
+  const int32_t* row_pos_offset = nullptr;
+  int32_t cand_target = 0;
+};
+
+// Validation, tensor maps and launches shared by the logits entry point and the fused selection.
+int paged_fp8_launch(const char* who, const void* q_fp8, const float* weights, const void* cache, int32_t num_pages,
+                     int32_t page_size, const int32_t* context_lens, const int32_t* block_table,
+                     int64_t block_table_stride, const int32_t* row_table, int32_t n_rows, int32_t next_n,
+                     int32_t max_cols, float out_scale, float* logits, int64_t logits_stride,
+                     const uint64_t* head_mask, float* logits_gated, int32_t* status, const EmitArgs& em,
+                     cudaStream_t stream) {
+  char msg[160];
+  if (!q_fp8 || !weights || !cache || !context_lens || !block_table || !status || n_rows < 0 || next_n < 1 ||
+      num_pages < 1 || max_cols < 0 || (logits && logits_stride < max_cols) || (!logits && !em.cand) ||
+      ((head_mask == nullptr) != (logits_gated == nullptr)) || (logits_gated && !logits)) {
+    snprintf(msg, sizeof(msg), "%s: bad argument", who);
+    set_last_error(msg);
     return B200DSA_EINVAL;
   }
   if (page_size != 32 && page_size != 64 && page_size != 128) {
-    set_last_error("b200dsa_indexer_paged_fp8_logits: page_size must be 32, 64 or 128");
+    snprintf(msg, sizeof(msg), "%s: page_size must be 32, 64 or 128", who);
+    set_last_error(msg);
     return B200DSA_EUNSUPPORTED;
   }
   if ((reinterpret_cast<uintptr_t>(q_fp8) & 15) || (reinterpret_cast<uintptr_t>(cache) & 15) ||
       (reinterpret_cast<uintptr_t>(weights) & 15)) {
-    set_last_error("b200dsa_indexer_paged_fp8_logits: q, weights and cache must be 16-byte aligned");
+    snprintf(msg, sizeof(msg), "%s: q, weights and cache must be 16-byte aligned", who);
+    set_last_error(msg);
     return B200DSA_EALIGN;
   }
   const int64_t page_bytes = static_cast<int64_t>(page_size) * (kDim + 4);
@@ -497,7 +654,8 @@ extern "C" int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* 
     const int nr = n_rows - r0 < kMaxRows ? n_rows - r0 : kMaxRows;
     // chunk boundaries must not split the next_n rows of one request
     if (!row_table && r0 % next_n != 0) {
-      set_last_error("b200dsa_indexer_paged_fp8_logits: next_n must divide 1024 when n_rows > 1024");
+      snprintf(msg, sizeof(msg), "%s: next_n must divide 1024 when n_rows > 1024", who);
+      set_last_error(msg);
       return B200DSA_EUNSUPPORTED;
     }
     const uint8_t* qbase = static_cast<const uint8_t*>(q_fp8) + static_cast<int64_t>(r0) * kHeads * kDim;
@@ -522,16 +680,80 @@ extern "C" int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* 
     p.pos_hi = nullptr;
     p.n_rows = nr;
     p.out_scale = out_scale;
-    p.logits = logits + static_cast<int64_t>(r0) * logits_stride;
+    p.logits = logits ? logits + static_cast<int64_t>(r0) * logits_stride : nullptr;
     p.logits_stride = logits_stride;
     p.logits_cols = max_cols;
     p.head_mask = head_mask ? head_mask + r0 : nullptr;
     p.logits_gated = logits_gated ? logits_gated + static_cast<int64_t>(r0) * logits_stride : nullptr;
     p.status = status;
-    rc = launch_paged<true>(mk, mq, p, 0, static_cast<cudaStream_t>(stream));
+    if (em.cand) {
+      p.cand = em.cand + static_cast<int64_t>(r0) * kEmitCap;
+      p.cand_count = em.cand_count + r0;
+      p.row_floor = em.row_floor + r0;
+      p.row_pos_offset = em.row_pos_offset ? em.row_pos_offset + r0 : nullptr;
+      p.cand_target = em.cand_target;
+      rc = launch_paged<true, true>(mk, mq, p, 0, stream);
+    } else {
+      rc = launch_paged<true, false>(mk, mq, p, 0, stream);
+    }
     if (rc) return rc;
   }
   return B200DSA_OK;
+}
+
+}  // namespace b200dsa
+
+extern "C" int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* weights, const void* cache,
+                                                int32_t num_pages, int32_t page_size, const int32_t* context_lens,
+                                                const int32_t* block_table, int64_t block_table_stride,
+                                                const int32_t* row_table, int32_t n_rows, int32_t next_n,
+                                                int32_t max_cols, float out_scale,
+                                                float* logits, int64_t logits_stride, const uint64_t* head_mask,
+                                                float* logits_gated, int32_t* status, void* stream) {
+  if (n_rows == 0) return B200DSA_OK;
+  if (!logits) {
+    set_last_error("b200dsa_indexer_paged_fp8_logits: bad argument");
+    return B200DSA_EINVAL;
+  }
+  return paged_fp8_launch("b200dsa_indexer_paged_fp8_logits", q_fp8, weights, cache, num_pages, page_size, context_lens,
+                          block_table, block_table_stride, row_table, n_rows, next_n, max_cols, out_scale, logits,
+                          logits_stride, head_mask, logits_gated, status, EmitArgs{}, static_cast<cudaStream_t>(stream));
+}
+
+namespace b200dsa {
+int topk_select_from_lists(const float* scores, int64_t row_stride, int32_t n_rows, int32_t n_cols,
+                           const int32_t* col_end, int32_t k, int32_t sorted, const int32_t* row_pos_offset,
+                           uint64_t* cand, int32_t* count, uint32_t* floor_bits, int32_t* out_idx, float* out_val,
+                           int64_t out_stride, int32_t* status, cudaStream_t stream);
+}
+
+extern "C" int b200dsa_indexer_paged_fp8_topk(const void* q_fp8, const float* weights, const void* cache,
+                                              int32_t num_pages, int32_t page_size, const int32_t* context_lens,
+                                              const int32_t* block_table, int64_t block_table_stride,
+                                              const int32_t* row_table, int32_t n_rows, int32_t next_n,
+                                              int32_t max_cols, float out_scale, float* logits, int64_t logits_stride,
+                                              int32_t k, int32_t sorted, const int32_t* row_pos_offset,
+                                              void* scratch_cand, int32_t* scratch_count, int32_t* out_idx,
+                                              float* out_val, int64_t out_stride, int32_t* status, void* stream) {
+  if (n_rows == 0) return B200DSA_OK;
+  if (!scratch_cand || !scratch_count || !out_idx || k < 1 || k > 2048 || out_stride < k ||
+      (reinterpret_cast<uintptr_t>(scratch_cand) & 7)) {
+    set_last_error("b200dsa_indexer_paged_fp8_topk: bad argument (1 <= k <= 2048, out_stride >= k, 8-byte aligned scratch)");
+    return B200DSA_EINVAL;
+  }
+  EmitArgs em;
+  em.cand = static_cast<uint64_t*>(scratch_cand);
+  em.cand_count = scratch_count;
+  em.row_floor = reinterpret_cast<uint32_t*>(scratch_count + n_rows);
+  em.row_pos_offset = row_pos_offset;
+  em.cand_target = k + k / 2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = paged_fp8_launch("b200dsa_indexer_paged_fp8_topk", q_fp8, weights, cache, num_pages, page_size, context_lens,
+                            block_table, block_table_stride, row_table, n_rows, next_n, max_cols, out_scale, logits,
+                            logits_stride, nullptr, nullptr, status, em, st);
+  if (rc) return rc;
+  return topk_select_from_lists(logits, logits_stride, n_rows, max_cols, context_lens, k, sorted, row_pos_offset,
+                                em.cand, em.cand_count, em.row_floor, out_idx, out_val, out_stride, status, st);
 }
 
 extern "C" int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const float* weights, const void* keys_bf16,
@@ -591,7 +813,7 @@ extern "C" int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const f
     p.head_mask = head_mask ? head_mask + r0 : nullptr;
     p.logits_gated = logits_gated ? logits_gated + static_cast<int64_t>(r0) * logits_stride : nullptr;
     p.status = status;
-    rc = launch_paged<false>(mk, mq, p, 0, static_cast<cudaStream_t>(stream));
+    rc = launch_paged<false, false>(mk, mq, p, 0, static_cast<cudaStream_t>(stream));
     if (rc) return rc;
   }
   return B200DSA_OK;

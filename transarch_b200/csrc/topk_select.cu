@@ -54,6 +54,12 @@ struct TopkParams {
   // from `scores` / `pos_map` instead of r * seg_stride
   int32_t seg_off_n;
   int64_t seg_off[8];
+  // lists collected by the indexer's own epilogue (fused selection): pre_floor[row] is the largest
+  // score floor any part of the row was collected with (ordered-float bits), so the list holds EVERY
+  // score of the row at or above it; the selection from the list is exact iff at least k entries
+  // reach that floor.  `scores` may then be NULL (no fallback: *status gets kDevSelectIncomplete).
+  uint32_t* pre_floor;
+  int32_t* status;
 };
 
 __device__ __forceinline__ bool score_valid(float v, int keep_pos_inf) {
@@ -473,13 +479,46 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   int cnt = 0;  // total candidates
   bool have_pre = false;
   if (p.pre_cand) {
-    // split mode: the candidates of this row were collected by topk_collect_kernel
+    // split / fused mode: the candidates of this row were collected by an earlier kernel
     const int c = p.pre_count[row];
+    const uint32_t fl = p.pre_floor ? p.pre_floor[row] : 0u;
     __syncthreads();
-    if (tid == 0) p.pre_count[row] = 0;  // re-arm the counter for the next call
-    if (c >= k && c <= kCandCap) {
+    if (tid == 0) {          // re-arm for the next call
+      p.pre_count[row] = 0;
+      if (p.pre_floor) p.pre_floor[row] = 0u;
+    }
+    bool usable = c <= kCandCap && (p.pre_floor || c >= k);
+    if (usable) {
       const uint64_t* g = p.pre_cand + static_cast<int64_t>(row) * kCandCap;
-      for (int i = tid; i < c; i += nthr) cand[i] = g[i];
+      int n_ge = 0;
+      for (int i = tid; i < c; i += nthr) {
+        const uint64_t e = g[i];
+        cand[i] = e;
+        n_ge += static_cast<uint32_t>(e >> 32) >= fl;
+      }
+      if (p.pre_floor) {
+        // the list is complete at and above the floor; a floor of -FLT_MAX means the whole row is in it
+        if (tid == 0) s_res[0] = 0;
+        __syncthreads();
+        if (n_ge) atomicAdd(&s_res[0], n_ge);
+        __syncthreads();
+        usable = (s_res[0] >= k) || (fl == 0x00800000u);
+        __syncthreads();
+      }
+    }
+    if (!usable && p.pre_floor && p.scores == nullptr) {
+      // no logits to fall back to: report, and return the best of what the list holds
+      if (tid == 0 && p.status) atomicMax(p.status, kDevSelectIncomplete);
+      usable = c <= kCandCap;
+      if (!usable) {
+        for (int j = tid; j < k; j += nthr) {
+          out_idx[j] = -1;
+          if (out_val) out_val[j] = -INFINITY;
+        }
+        return;
+      }
+    }
+    if (usable) {
       if (tid < n_warps) s_warp_cnt[tid] = max(0, min(seg_cap, c - tid * seg_cap));
       __syncthreads();
       have_pre = true;
@@ -828,6 +867,34 @@ extern "C" int b200dsa_topk_select_split(const float* scores, int64_t row_stride
   }
   return B200DSA_OK;
 }
+
+// Last kernel of the fused selection: exact top-k of every row from the candidate list the indexer's
+// epilogue collected (see indexer_paged.cu), falling back to the row's logits when a list cannot be
+// proven complete (scores may be NULL: then *status reports it).
+namespace b200dsa {
+int topk_select_from_lists(const float* scores, int64_t row_stride, int32_t n_rows, int32_t n_cols,
+                           const int32_t* col_end, int32_t k, int32_t sorted, const int32_t* row_pos_offset,
+                           uint64_t* cand, int32_t* count, uint32_t* floor_bits, int32_t* out_idx, float* out_val,
+                           int64_t out_stride, int32_t* status, cudaStream_t stream) {
+  TopkParams p{scores, row_stride, n_rows, n_cols, nullptr, col_end, k, 0, nullptr, 0, nullptr, 0, 0,
+               row_pos_offset, out_idx, out_val, out_stride, sorted, 0, 0, cand, count};
+  p.pre_floor = floor_bits;
+  p.status = status;
+  int k_pow2 = 32;
+  while (k_pow2 < k) k_pow2 <<= 1;
+  const size_t smem = kHistBins * sizeof(uint32_t) + (kCandCap + kEqCap + k_pow2) * sizeof(uint64_t);
+  cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kHistBins * sizeof(uint32_t) + (2 * kCandCap + kEqCap) * sizeof(uint64_t)));
+  if (e == cudaSuccess)
+    e = launch_chained(topk_select_kernel, dim3(n_rows), dim3(1024), smem, stream, p, k_pow2, static_cast<int>(kCandCap));
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  return B200DSA_OK;
+}
+}  // namespace b200dsa
 
 // ---------------------------------------------------------------------------------------------
 // Split top-k without caller-provided scratch.

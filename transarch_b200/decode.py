@@ -67,7 +67,7 @@ class SparseDecodeStep:
                  n_heads: int = 128, index_scale: float = 128 ** -0.5, attn_scale: float = 192 ** -0.5,
                  device: Optional[torch.device] = None, shard: Optional[ShardInfo] = None, backend=None,
                  sorted_topk: bool = False, wire: str = "bf16", ctx_dtype: torch.dtype = torch.float32,
-                 combine: str = "auto"):
+                 combine: str = "auto", fused_select: bool = True, keep_logits: bool = True):
         if backend is None:
             from . import kernels as backend  # the CUDA kernels; fails loudly without the library
         self.K = backend
@@ -100,6 +100,12 @@ class SparseDecodeStep:
         self.topk_scratch = None
         if hasattr(backend, "topk_scratch") and batch <= 148 and max_local_ctx >= 16384:
             self.topk_scratch = backend.topk_scratch(batch, dev)
+        # fused selection: the indexer's epilogue collects the top-k candidates itself (two launches, no
+        # pass over the logits; they are still written, unless keep_logits=False, as the exact fallback)
+        self.fused_scratch = None
+        self.keep_logits = keep_logits
+        if fused_select and hasattr(backend, "indexer_paged_fp8_topk") and topk <= 2048:
+            self.fused_scratch = backend.topk_scratch(batch, dev)
         self.peer = None
         if combine == "peer" and not (n > 1 and dist.is_initialized()):
             raise ValueError("combine='peer' needs an initialised process group of more than one rank")
@@ -159,11 +165,17 @@ class SparseDecodeStep:
         """Indexer + top-k on this rank's keys; returns int32 [B, k] global positions."""
         K = self.K
         K.quant_q_fold_weights(q_idx, w, self.index_scale, q_fp8=self.q_fp8, weights=self.weights)
-        K.indexer_paged_fp8_logits(self.q_fp8, self.weights, k_cache, self.P, context_lens_local, block_table,
-                                   max_cols=self.max_cols, out=self.logits)
         idx = self.cand[:, : self.topk]
         val = self.cand[:, self.topk:].view(torch.float32)
         offset = self.pos_offset if self.shard.world_size > 1 else None
+        if self.fused_scratch is not None:
+            K.indexer_paged_fp8_topk(self.q_fp8, self.weights, k_cache, self.P, context_lens_local, block_table,
+                                     self.topk, self.fused_scratch, max_cols=self.max_cols, logits=self.logits,
+                                     keep_logits=self.keep_logits, row_pos_offset=offset, sorted=self.sorted_topk,
+                                     out=idx, out_values=val)
+            return idx
+        K.indexer_paged_fp8_logits(self.q_fp8, self.weights, k_cache, self.P, context_lens_local, block_table,
+                                   max_cols=self.max_cols, out=self.logits)
         if self.topk_scratch is not None:
             K.topk_select_split(self.logits, self.topk, self.topk_scratch, col_end=context_lens_local,
                                 sorted=self.sorted_topk, row_pos_offset=offset, out=idx, out_values=val)

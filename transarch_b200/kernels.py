@@ -201,6 +201,59 @@ def indexer_paged_fp8_logits(q_fp8: torch.Tensor, weights: torch.Tensor, cache: 
     return out if head_mask is None else (out, out_gated)
 
 
+def indexer_paged_fp8_topk(q_fp8: torch.Tensor, weights: torch.Tensor, cache: torch.Tensor, page_size: int,
+                           context_lens: torch.Tensor, block_table: torch.Tensor, k: int,
+                           scratch: Tuple[torch.Tensor, torch.Tensor], *, next_n: int = 1,
+                           max_cols: Optional[int] = None, out_scale: float = 1.0,
+                           logits: Optional[torch.Tensor] = None, keep_logits: bool = True,
+                           row_table: Optional[torch.Tensor] = None, row_pos_offset: Optional[torch.Tensor] = None,
+                           sorted: bool = False, out: Optional[torch.Tensor] = None,
+                           out_values: Optional[torch.Tensor] = None):
+    """Indexer scores and their top-k positions in two launches, the candidates collected by the
+    indexer's own epilogue; see b200dsa_indexer_paged_fp8_topk.  `scratch` comes from topk_scratch().
+    keep_logits=True (default) also writes the logits (into `logits`, allocated when not given) so
+    that a row whose candidate list is not provably complete is selected exactly from them;
+    keep_logits=False writes no logits at all (status word 3 on such a row)."""
+    require_cuda(q_fp8, weights, cache, context_lens, block_table, row_table, row_pos_offset, logits, out, out_values)
+    if q_fp8.dtype != torch.float8_e4m3fn or not q_fp8.is_contiguous() or q_fp8.shape[-2:] != (64, 128):
+        raise _lib.B200DSAError("q_fp8 must be contiguous float8_e4m3fn [..., 64, 128]")
+    n_rows = q_fp8.numel() // (64 * 128)
+    if weights.dtype != torch.float32 or not weights.is_contiguous() or weights.numel() != n_rows * 64:
+        raise _lib.B200DSAError("weights must be contiguous fp32 [n_rows, 64]")
+    if cache.dtype != torch.uint8 or not cache.is_contiguous() or cache.numel() % (page_size * 132):
+        raise _lib.B200DSAError("cache must be contiguous uint8 with page_size*(128+4) bytes per page")
+    num_pages = cache.numel() // (page_size * 132)
+    _i32(context_lens, "context_lens"); _i32(block_table, "block_table")
+    if context_lens.numel() != n_rows:
+        raise _lib.B200DSAError("context_lens must have one entry per row")
+    if not 1 <= k <= 2048:
+        raise _lib.B200DSAError("the fused selection supports 1 <= k <= 2048")
+    if max_cols is None:
+        max_cols = block_table.shape[-1] * page_size
+    cand, count = scratch
+    if cand.numel() < n_rows * CAND_CAP or count.numel() < 2 * n_rows:
+        raise _lib.B200DSAError("scratch is too small for this many rows")
+    if keep_logits and logits is None:
+        logits = torch.empty(n_rows, max_cols, dtype=torch.float32, device=q_fp8.device)
+    if not keep_logits:
+        logits = None
+    if logits is not None and (logits.dtype != torch.float32 or logits.stride(1) != 1 or logits.shape[0] < n_rows or
+                               logits.shape[1] < max_cols):
+        raise _lib.B200DSAError("logits must be fp32 [>=n_rows, >=max_cols] with unit column stride")
+    if out is None:
+        out = torch.empty(n_rows, k, dtype=torch.int32, device=q_fp8.device)
+    _check_topk_outputs(out, out_values, n_rows, k)
+    rc = _lib.load().b200dsa_indexer_paged_fp8_topk(
+        ptr(q_fp8), ptr(weights), ptr(cache), num_pages, page_size, ptr(context_lens), ptr(block_table),
+        block_table.stride(0), ptr(_i32(row_table, "row_table")), n_rows, next_n, max_cols, out_scale, ptr(logits),
+        logits.stride(0) if logits is not None else 0, k, int(sorted), ptr(_i32(row_pos_offset, "row_pos_offset")),
+        ptr(cand), ptr(count), ptr(out), ptr(out_values), out.stride(0), ptr(status_word(q_fp8.device)), stream_ptr())
+    check(rc, "b200dsa_indexer_paged_fp8_topk")
+    if out_values is not None:
+        return out[:n_rows, :k], out_values[:n_rows, :k]
+    return out[:n_rows, :k]
+
+
 def _gated_output(head_mask, out_gated, out, n_rows, fill=True):
     if head_mask is None:
         if out_gated is not None:
