@@ -409,6 +409,25 @@ def main():
     ev_in_free = [torch.cuda.Event() for _ in range(slots)]
     e2e_started = [False] * slots
 
+    # Sharded: the queries are replicated, but only 1/world of their bytes crosses each rank's host link;
+    # an NVLink all-gather (posted peer stores, one kernel) replicates them inside the node.  Each rank
+    # returns its 1/world of the result rows to its host.
+    ag = None
+    if world > 1 and step.peer is not None:
+        from transarch_b200.peer import PeerAllGather
+        sizes = [t.numel() * t.element_size() for t in host_q[0]]
+        offs = [sum(sizes[:j]) for j in range(len(sizes))]
+        total_in = sum(sizes)
+        ag = PeerAllGather(total_in, dev, n_send=slots)
+        host_cat = []
+        for hq in host_q:                                           # one pinned byte buffer per query set
+            cat = torch.empty(ag.chunk * world, dtype=torch.uint8).pin_memory()
+            for t, o in zip(hq, offs):
+                cat[o:o + t.numel() * t.element_size()] = t.contiguous().view(torch.uint8).reshape(-1)
+            host_cat.append(cat)
+        recv_views = [ag.recv[o:o + n].view(t.dtype).view(t.shape) for t, o, n in zip(host_q[0], offs, sizes)]
+        rows_lo, rows_hi = rank * B // world, (rank + 1) * B // world
+
     def run_e2e(i):
         sl = i % slots
         main = torch.cuda.current_stream()
@@ -416,23 +435,39 @@ def main():
             ev_out[sl].synchronize()                     # result of step i-2 is on the host
             s_in.wait_event(ev_in_free[sl])
         with torch.cuda.stream(s_in):
-            for dst, src in zip(in_dev[sl], host_q[i % n_sets]):
-                dst.copy_(src, non_blocking=True)
+            if ag is not None:
+                ag.send[sl].copy_(host_cat[i % n_sets][rank * ag.chunk:(rank + 1) * ag.chunk], non_blocking=True)
+            else:
+                for dst, src in zip(in_dev[sl], host_q[i % n_sets]):
+                    dst.copy_(src, non_blocking=True)
             ev_in[sl].record(s_in)
         main.wait_event(ev_in[sl])
+        if ag is not None:
+            ag.run(sl)
+            ins = recv_views
+        else:
+            ins = in_dev[sl]
         if graphed is None:
-            idx, c, _ = step.run(in_dev[sl][0], in_dev[sl][1], in_dev[sl][2], state.k_cache, state.context_lens,
+            idx, c, _ = step.run(ins[0], ins[1], ins[2], state.k_cache, state.context_lens,
                                  state.block_table, state.kv, state.kv_row_base, state.context_lens_local)
         else:
-            idx, c, _ = graphed.replay(*in_dev[sl])
+            idx, c, _ = graphed.replay(*ins)
         ev_in_free[sl].record(main)
-        out_dev[sl][0].copy_(idx, non_blocking=True)
-        out_dev[sl][1].copy_(c, non_blocking=True)
+        if ag is not None:
+            out_dev[sl][0][rows_lo:rows_hi].copy_(idx[rows_lo:rows_hi], non_blocking=True)
+            out_dev[sl][1][rows_lo:rows_hi].copy_(c[rows_lo:rows_hi], non_blocking=True)
+        else:
+            out_dev[sl][0].copy_(idx, non_blocking=True)
+            out_dev[sl][1].copy_(c, non_blocking=True)
         ev_done[sl].record(main)
         s_out.wait_event(ev_done[sl])
         with torch.cuda.stream(s_out):
-            out_host[sl][0].copy_(out_dev[sl][0], non_blocking=True)
-            out_host[sl][1].copy_(out_dev[sl][1], non_blocking=True)
+            if ag is not None:
+                out_host[sl][0][rows_lo:rows_hi].copy_(out_dev[sl][0][rows_lo:rows_hi], non_blocking=True)
+                out_host[sl][1][rows_lo:rows_hi].copy_(out_dev[sl][1][rows_lo:rows_hi], non_blocking=True)
+            else:
+                out_host[sl][0].copy_(out_dev[sl][0], non_blocking=True)
+                out_host[sl][1].copy_(out_dev[sl][1], non_blocking=True)
             ev_out[sl].record(s_out)
         e2e_started[sl] = True
 
@@ -468,40 +503,47 @@ def main():
     ms_per_step = total_ms / args.steps
     value = B * args.steps / (total_ms * 1e-3)
 
-    # per-stage device times inside a second timed region (events around each launch)
-    stage_ms = {"quant+indexer": 0.0, "topk": 0.0, "attention+merge": 0.0}
+    # per-stage device times inside a second timed region (events around each stage of the step, eager
+    # launches: these include the host's launch gaps; the graph-replayed figures follow)
+    stage_ms = {}
+
+    def add(name, a, b_):
+        stage_ms[name] = stage_ms.get(name, 0.0) + a.elapsed_time(b_)
+
     sync_all()
     for i in range(args.steps):
         q_idx, w, q_lat = dev_q[i % n_sets]
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
         ev[0].record()
-        K = step.K
-        K.quant_q_fold_weights(q_idx, w, step.index_scale, q_fp8=step.q_fp8, weights=step.weights)
-        ev_i0 = torch.cuda.Event(enable_timing=True); ev_i0.record()
-        K.indexer_paged_fp8_logits(step.q_fp8, step.weights, state.k_cache, PAGE, state.context_lens_local,
-                                   state.block_table, max_cols=step.max_cols, out=step.logits)
+        idx = step.select(q_idx, w, state.k_cache, state.context_lens_local, state.block_table)
         ev[1].record()
-        K.topk_select_split(step.logits, TOPK, step.topk_scratch, col_end=state.context_lens_local, sorted=False,
-                            out=step.cand[:, :TOPK], out_values=step.cand[:, TOPK:].view(torch.float32),
-                            row_pos_offset=step.pos_offset if world > 1 else None)
+        if world > 1:
+            idx = step.merge_candidates()
         ev[2].record()
-        sub = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        idx = step.merge_candidates() if world > 1 else step.cand[:, :TOPK]
-        sub[0].record()
         step.attend(q_lat, state.kv, state.kv_row_base, idx, state.context_lens, q_pos_bias=-1)
-        sub[1].record()
+        ev[3].record()
         if world > 1:
             step.combine()
-        sub[2].record()
-        ev[3].record()
+        ev[4].record()
         torch.cuda.synchronize()
-        stage_ms["quant+indexer"] += ev[0].elapsed_time(ev[1])
-        stage_ms["topk"] += ev[1].elapsed_time(ev[2])
-        stage_ms["attention+merge"] += ev[2].elapsed_time(ev[3])
-        for nm, a, b_ in (("gather+merge", ev[2], sub[0]), ("attention", sub[0], sub[1]), ("combine", sub[1], sub[2])):
-            stage_ms[nm] = stage_ms.get(nm, 0.0) + a.elapsed_time(b_)
-        stage_ms.setdefault("indexer", 0.0)
-        stage_ms["indexer"] += ev_i0.elapsed_time(ev[1])
+        for nm, a, b_ in (("select", ev[0], ev[1]), ("exchange+merge", ev[1], ev[2]), ("attention", ev[2], ev[3]),
+                          ("combine", ev[3], ev[4])):
+            add(nm, a, b_)
+    if world == 1:
+        # the unfused pair, for comparison: indexer writing logits, then the split top-k reading them
+        K = step.K
+        scratch = step.topk_scratch if step.topk_scratch is not None else K.topk_scratch(B, dev)
+        for i in range(args.steps):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            ev[0].record()
+            K.indexer_paged_fp8_logits(step.q_fp8, step.weights, state.k_cache, PAGE, state.context_lens_local,
+                                       state.block_table, max_cols=step.max_cols, out=step.logits)
+            ev[1].record()
+            K.topk_select_split(step.logits, TOPK, scratch, col_end=state.context_lens_local, sorted=False,
+                                out=step.cand[:, :TOPK], out_values=step.cand[:, TOPK:].view(torch.float32))
+            ev[2].record()
+            torch.cuda.synchronize()
+            add("unfused_indexer", ev[0], ev[1]); add("unfused_topk_split", ev[1], ev[2])
     for k_ in stage_ms:
         stage_ms[k_] /= args.steps
 
@@ -545,19 +587,38 @@ def main():
         select_us = graph_time(do_select)
         if world > 1:
             # prefixes of the sharded step, each from its own graph: the differences are the exchange stages
+            # Every prefix ends with a node barrier (its own kernel) so that no rank starts the next replay
+            # while a peer still reads what the replay overwrites; the barrier alone is timed and subtracted.
+            def fence():
+                if step.peer is not None:
+                    step.peer.barrier(slot=3)
+
+            def only_fence():
+                fence()
+
+            def select_fenced():
+                do_select()
+                fence()
+
             def upto_merge():
                 do_select()
-                return step.merge_candidates()
+                step.merge_candidates()
+                fence()
 
             def upto_attend():
-                idx_ = upto_merge()
-                step.attend(sel_lat, state.kv, state.kv_row_base, idx_, state.context_lens, q_pos_bias=-1)
+                do_select()
+                idx_ = step.merge_candidates()
+                step.attend(sel_lat, state.kv, state.kv_row_base, idx_, state.context_lens, q_pos_bias=-1,
+                            signal=False)
+                fence()
 
-            t_merge = graph_time(upto_merge)
-            t_att = graph_time(upto_attend)
-            partial_us = {"select": round(select_us, 2), "exchange+merge": round(t_merge - select_us, 2),
-                          "compact+attention": round(t_att - t_merge, 2),
-                          "combine": round(1e3 * ms_per_step - t_att, 2)}
+            t_fence = graph_time(only_fence) if step.peer is not None else 0.0
+            t_sel = graph_time(select_fenced) - t_fence
+            t_merge = graph_time(upto_merge) - t_fence
+            t_att = graph_time(upto_attend) - t_fence
+            partial_us = {"select": round(t_sel, 2), "exchange+merge": round(t_merge - t_sel, 2),
+                          "attention": round(t_att - t_merge, 2),
+                          "combine": round(1e3 * ms_per_step - t_att, 2), "node_barrier_alone": round(t_fence, 2)}
 
     # The dominant kernel by itself: back-to-back launches on the current stream between two events
     # (the per-stage times above include the host-side gaps of eager launches; these do not).
@@ -611,6 +672,11 @@ def main():
         achieved = idx_bytes / (indexer_ms * 1e-3) / 1e9
         h2d = sum(t.numel() * t.element_size() for t in host_q[0])
         d2h = sum(t.numel() * t.element_size() for t in out_host[0])
+        e2e_note = "every step: inputs from pinned host memory, indices and bf16 context back to the host"
+        if ag is not None:
+            e2e_note = (f"per rank and step: {ag.chunk} input bytes over the host link (1/{world} of the replicated "
+                        f"queries, replicated inside the node by an NVLink all-gather kernel) and 1/{world} of the "
+                        "result rows back; the byte counts below are the node totals")
         # our kernels per step: q quantisation, indexer + select (fused: 2 launches; else indexer and a top-k of
         # 3 kernels in the split form), attention; sharded:
         # + merge top-k, compaction and either barrier + peer combine or the bf16 share kernel (NCCL's
@@ -631,15 +697,14 @@ def main():
                        "launch": "eager" if graphed is None else "cuda-graph replay",
                        "l2": "inputs larger than L2 (index-key cache %.2f GB per GPU, 4 rotating query sets)"
                              % (idx_bytes / 1e9)},
-            "indexer_topk_us_per_step": select_us if select_us is not None
-            else 1e3 * (stage_ms["quant+indexer"] + stage_ms["topk"]),
+            "indexer_topk_us_per_step": select_us if select_us is not None else 1e3 * stage_ms["select"],
             # bytes the selection must move: keys + scales read, logits written once and read once
             "indexer_topk_hbm_frac": (None if select_us is None else
                                       (B * shard_len * (132 + 8)) / (select_us * 1e-6) / 1e9 / peaks["hbm_gbs"]),
             "stage_us": {k_: round(1e3 * v, 2) for k_, v in stage_ms.items()},
             "graph_stage_us": partial_us,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / args.steps, "h2d_copy_alone_ms": h2d_only_ms,
+                    "ms_per_step": e2e_ms / args.steps, "note": e2e_note, "h2d_copy_alone_ms": h2d_only_ms,
                     "h2d_copy_alone_gbs": h2d / (h2d_only_ms * 1e-3) / 1e9},
             "gpu_launches": launches * args.steps,
             "roofline": {"kernel": "indexer_paged_kernel<fp8>", "bound": "hbm", "achieved": achieved,

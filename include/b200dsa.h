@@ -31,6 +31,22 @@ extern "C" {
 int b200dsa_abi_version(void);
 const char* b200dsa_last_error(void);
 
+/* The GPUs of one node as the kernels of the key-sharded step see them: the exchange buffer of every
+ * rank (b200dsa_peer_alloc / b200dsa_peer_open), a flag slot inside it, and this rank's step counter.
+ *   bufs      HOST array of `world` device pointers as seen from the calling process
+ *   off_flags byte offset of the 256 bytes of flags in every buffer (zero before the first call)
+ *   slot      1 or 3..7 (0 and 2 belong to b200dsa_peer_lse_combine); one slot per kind of exchange
+ *   state     two int32 of LOCAL device memory, zero before the first call: the step counter of this
+ *             slot's user (kernels advance it themselves, so captured launches can be replayed)
+ * Flags are step numbers that only grow; every wait is bounded (b200dsa_peer_set_wait_limit). */
+typedef struct b200dsa_peer_link {
+  void* const* bufs;
+  int32_t rank, world;
+  int64_t off_flags;
+  int32_t slot;
+  int32_t* state;
+} b200dsa_peer_link;
+
 /* Tensor-pipe peak probe (measurement aid, not on the serving path): `ctas` CTAs each issue
  * iters * 8 tcgen05 MMAs of shape M=128, N=256, K=32 bytes on shared-memory operands, FP8 e4m3
  * (fp8 != 0) or bf16, with no global-memory traffic.  Flops per launch = ctas * iters * 8 *
@@ -182,6 +198,34 @@ int b200dsa_indexer_paged_fp8_topk(const void* q_fp8, const float* weights, cons
                                    void* scratch_cand, int32_t* scratch_count, int32_t* out_idx,
                                    float* out_val, int64_t out_stride, int32_t* status, void* stream);
 
+/* b200dsa_indexer_paged_fp8_topk whose selection kernel also delivers the result to the peers (first
+ * exchange of the key-sharded step, no kernel of its own): row r's k positions and k score bit patterns
+ * are stored, as [2k] int32, at off_recv + (link->rank * n_rows + r) * 8k bytes of EVERY rank's buffer
+ * (posted NVLink stores from the selection's write loop); the last CTA fences and raises this rank's
+ * flag word (link->slot) on every rank and advances link->state[0].  It does not wait:
+ * b200dsa_topk_merge_owned does.  No counterpart in the reference (single GPU). */
+int b200dsa_indexer_paged_fp8_topk_push(const void* q_fp8, const float* weights, const void* cache,
+                                        int32_t num_pages, int32_t page_size, const int32_t* context_lens,
+                                        const int32_t* block_table, int64_t block_table_stride,
+                                        const int32_t* row_table, int32_t n_rows, int32_t next_n,
+                                        int32_t max_cols, float out_scale, float* logits, int64_t logits_stride,
+                                        int32_t k, int32_t sorted, const int32_t* row_pos_offset,
+                                        void* scratch_cand, int32_t* scratch_count, int32_t* out_idx,
+                                        float* out_val, int64_t out_stride, const b200dsa_peer_link* link,
+                                        int64_t off_recv, int32_t* status, void* stream);
+
+/* Merge of the pushed per-rank selections: waits (bounded) until every rank's flag of link->slot reached
+ * link->state[0] (the step this rank's own push recorded), then selects the global top-k of every row from
+ * the world * k candidates in the LOCAL receive area recv = [world, n_rows, 2k] int32 (positions then
+ * score bit patterns), exactly as b200dsa_topk_select would on the concatenated lists (ties to the lowest
+ * position, so every rank gets the same result), and also writes the winners inside [own_lo, own_hi),
+ * compacted and -1 padded, to owned [n_rows, owned_stride] with their number in owned_count[n_rows]:
+ * the keys this rank attends.  Replaces all-gather + top-k + ownership compaction. */
+int b200dsa_topk_merge_owned(const int32_t* recv, int32_t world, int32_t n_rows, int32_t k, int32_t sorted,
+                             int32_t own_lo, int32_t own_hi, int32_t* out_idx, int64_t out_stride,
+                             int32_t* owned, int64_t owned_stride, int32_t* owned_count,
+                             const b200dsa_peer_link* link, int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Token logits inside per-row lists of 128-key blocks, bf16 keys (tcgen05 bf16 contraction).
  * HISA stage 2 / block-sparse re-scoring.
@@ -233,6 +277,18 @@ int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16, int64_t k
                               int32_t n_items, int32_t n_heads, float sm_scale, void* ctx, int32_t ctx_bf16,
                               float* lse, int32_t* status, void* stream);
 
+/* b200dsa_sparse_mla_decode for a rank of the key-sharded step: after the last CTA has written (and
+ * fenced) its part of ctx / lse, which the caller placed in this rank's exchange buffer, the kernel raises
+ * this rank's "partial ready" flag on every rank, so that b200dsa_peer_lse_combine(pre_signalled = 1)
+ * starts with the wait alone.  link: the combine's buffers and ITS state word (slot 0; read, not advanced);
+ * ticket: one int32 of local device memory, zero before the first call. */
+int b200dsa_sparse_mla_decode_signal(const void* q_bf16, const void* kv_bf16, int64_t kv_rows,
+                                     const int64_t* kv_row_base, const int32_t* indices, int64_t idx_stride,
+                                     int32_t n_idx, const int32_t* n_idx_item, const int32_t* q_pos,
+                                     int32_t q_pos_bias, int32_t pos_lo, int32_t pos_hi, int32_t n_items,
+                                     int32_t n_heads, float sm_scale, void* ctx, int32_t ctx_bf16, float* lse,
+                                     const b200dsa_peer_link* link, int32_t* ticket, int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Merge attention partials computed over disjoint key sets (key shards of several GPUs, or
  * splits on one GPU):  out = sum_r exp(lse_r - m) ctx_r / sum_r exp(lse_r - m),
@@ -263,12 +319,14 @@ int b200dsa_lse_combine(const float* ctx_parts, const float* lse_parts, int32_t 
  * Waits for peers are bounded (about a second): on expiry *status gets 1 and the call
  * completes with an unusable result instead of hanging.  no_sync != 0 skips the flag exchange:
  * ranks emulated one after another on a single GPU (tests); ranks that wait for each other
- * must run on different GPUs.  1 <= world <= 8.
+ * must run on different GPUs.  pre_signalled != 0: the kernel that wrote the partial
+ * (b200dsa_sparse_mla_decode_signal) has already raised this rank's "ready" flags, so the call
+ * only waits for the peers'.  1 <= world <= 8.
  * ------------------------------------------------------------------------------------- */
 int b200dsa_peer_lse_combine(void* const* bufs, int32_t rank, int32_t world, int64_t n_rows,
                              int64_t off_ctx, int64_t off_lse, int64_t off_out, int64_t off_lse_out,
-                             int64_t off_flags, int32_t* state, int32_t no_sync, int32_t* status,
-                             void* stream);
+                             int64_t off_flags, int32_t* state, int32_t no_sync, int32_t pre_signalled,
+                             int32_t* status, void* stream);
 
 /* Node-wide barrier on the stream: one small kernel writes this rank's step number into every
  * peer's flag word `slot*8 + rank` (uint32 words at off_flags; slots 0 and 2 belong to

@@ -190,3 +190,81 @@ def test_two_gpus_exchange_over_peer_memory():
         p.kill()
     assert not stuck, "a rank did not finish"
     assert ret.get(0) is True and ret.get(1) is True
+
+
+def test_folded_exchanges_on_one_gpu():
+    """The three kernels that carry the exchanges of the key-sharded step, checked on one GPU with the
+    two ranks' buffers as two local allocations (nothing waits): the selection's push lands in every
+    buffer's receive slot and raises the flag; the merge of pushed lists equals top-k + compaction; the
+    attention kernel raises the merge kernel's "ready" flag without changing its results."""
+    from transarch_b200 import _lib, kernels as K
+    from transarch_b200.peer import PeerLseCombine
+    from transarch_b200.workloads import make_decode_state
+    dev = torch.device("cuda")
+    B, k, H, world = 5, 256, 128, 2
+    ctxs = [3000, 9000, 700, 100, 0]
+    st = make_decode_state(B, ctxs, page_size=64, seed=11)
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(B, 64, 128, generator=g).bfloat16().cuda()
+    w = (torch.randn(B, 64, generator=g) / 8).cuda()
+    q_fp8, wf = K.quant_q_fold_weights(q, w, 128 ** -0.5)
+    cand_bytes = B * 2 * k * 4
+    pc = PeerLseCombine(B * H, dev, emulate_world=world, extra_bytes=cand_bytes * (1 + world))
+    try:
+        scratch = K.topk_scratch(B, dev)
+        off = torch.full((B,), 1000, dtype=torch.int32, device=dev)
+        ref_idx, ref_val = K.indexer_paged_fp8_topk(q_fp8, wf, st.k_cache, 64, st.context_lens, st.block_table, k,
+                                                    scratch, max_cols=st.local_len, row_pos_offset=off, sorted=True,
+                                                    out_values=torch.empty(B, k, device=dev))
+        link = pc.link(1)                                               # rank 0 of 2
+        for rep in range(2):
+            idx, val = K.indexer_paged_fp8_topk(q_fp8, wf, st.k_cache, 64, st.context_lens, st.block_table, k, scratch,
+                                                max_cols=st.local_len, row_pos_offset=off, sorted=True,
+                                                out_values=torch.empty(B, k, device=dev),
+                                                push=(link, pc.off_extra + cand_bytes))
+            torch.cuda.synchronize()
+            assert torch.equal(idx, ref_idx) and torch.equal(val, ref_val)
+            for r in range(world):                                      # slot 0 (this rank) of both receive areas
+                recv = pc.extra_of(r)[cand_bytes:].view(torch.int32).view(world, B, 2 * k)
+                assert torch.equal(recv[0, :, :k], ref_idx)
+                assert torch.equal(recv[0, :, k:].view(torch.float32), ref_val)
+                flags = pc.buffers.views[r][pc.off_flags:pc.off_flags + 256].view(torch.int32)
+                assert int(flags[1 * 8 + 0]) == rep + 1                 # flag word slot 1, written by rank 0
+            assert int(pc.barrier_state[0]) == rep + 1 and int(pc.barrier_state[1]) == 0
+        # ---- merge of pushed lists (no link: nothing to wait for) against select + compaction
+        recv = torch.empty(world, B, 2 * k, dtype=torch.int32, device=dev)
+        for r in range(world):
+            pos = torch.stack([torch.randperm(5000, generator=g)[:k] + 5000 * r for _ in range(B)]).to(torch.int32)
+            sc = torch.randn(B, k, generator=g)
+            sc[0, :7] = float("-inf"); pos[0, :7] = -1
+            recv[r, :, :k] = pos.cuda(); recv[r, :, k:] = sc.view(torch.int32).cuda()
+        merged = torch.empty(B, k, dtype=torch.int32, device=dev)
+        owned = torch.empty(B, k, dtype=torch.int32, device=dev)
+        cnt = torch.empty(B, dtype=torch.int32, device=dev)
+        K.topk_merge_owned(recv, k, 5000, 10000, out=merged, owned=owned, owned_count=cnt, sorted=True)
+        flat = recv.view(-1)
+        want = K.topk_select(flat[k:].view(torch.float32).view(1, -1), k, sorted=True, pos_map=flat.view(1, -1),
+                             n_cols=world * k, row_stride=2 * k, seg_cols=k, seg_stride=B * 2 * k, n_rows=B,
+                             pos_map_stride=2 * k)
+        assert torch.equal(merged, want)
+        for b in range(B):
+            own = want[b][(want[b] >= 5000) & (want[b] < 10000)]
+            assert int(cnt[b]) == own.numel()
+            assert torch.equal(torch.sort(owned[b, :own.numel()]).values, torch.sort(own).values)
+            assert (owned[b, own.numel():] == -1).all()
+        # ---- attention raising the merge kernel's "ready" flag
+        kv = (0.5 * torch.randn(2000, 576, generator=g)).bfloat16().cuda()
+        q_lat = torch.randn(B, H, 576, generator=g).bfloat16().cuda()
+        sel = torch.stack([torch.randperm(2000, generator=g)[:k] for _ in range(B)]).to(torch.int32).cuda()
+        c0, l0 = K.sparse_mla_decode(q_lat, kv, sel, 192 ** -0.5)
+        c0, l0 = c0.clone(), l0.clone()
+        c1, l1 = K.sparse_mla_decode(q_lat, kv, sel, 192 ** -0.5, signal=(pc.link(0), pc.ticket))
+        torch.cuda.synchronize()
+        assert torch.equal(c0, c1) and torch.equal(l0, l1)
+        for r in range(world):
+            flags = pc.buffers.views[r][pc.off_flags:pc.off_flags + 256].view(torch.int32)
+            assert int(flags[0]) == int(pc.state[0][0]) + 1             # "ready" word of rank 0, next step
+        assert int(pc.ticket) == 0
+        assert _lib.read_status(dev) == 0
+    finally:
+        pc.close()

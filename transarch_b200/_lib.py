@@ -37,7 +37,12 @@ SIGNATURES = {
     "b200dsa_sparse_mla_decode": [_vp, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32,
                                   _vp, _i32, _vp, _vp, _vp],
     "b200dsa_lse_combine": [_vp, _vp, _i32, _i64, _vp, _vp, _vp],
-    "b200dsa_peer_lse_combine": [_vp, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _i32, _vp, _vp],
+    "b200dsa_peer_lse_combine": [_vp, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _i32, _i32, _vp, _vp],
+    "b200dsa_indexer_paged_fp8_topk_push": [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _f32,
+                                            _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp],
+    "b200dsa_topk_merge_owned": [_vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp],
+    "b200dsa_sparse_mla_decode_signal": [_vp, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32,
+                                         _f32, _vp, _i32, _vp, _vp, _vp, _vp, _vp],
     "b200dsa_peer_barrier": [_vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp],
     "b200dsa_peer_gather": [_vp, _i32, _i32, _i64, _i64, _vp, _i64, _i32, _vp, _vp, _vp],
     "b200dsa_peer_push": [_vp, _i32, _i32, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _vp],
@@ -57,6 +62,14 @@ SIGNATURES = {
     "b200dsa_router_linear_topk_softmax": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp],
     "b200dsa_indexer_k_quant_and_cache": [_vp, _vp, _i64, _vp, _i64, _i32, _i32, _vp, _vp],
 }
+
+
+
+class PeerLink(C.Structure):
+    """b200dsa_peer_link of include/b200dsa.h."""
+    _fields_ = [("bufs", C.c_void_p), ("rank", C.c_int32), ("world", C.c_int32), ("off_flags", C.c_int64),
+                ("slot", C.c_int32), ("state", C.c_void_p)]
+
 
 _lib: Optional[C.CDLL] = None
 

@@ -253,6 +253,58 @@ __device__ __forceinline__ float ordered_to_float(uint32_t k) {
   return __uint_as_float(u);
 }
 
+// ---------------------------------------------------------------------------------------
+// System-scope flag words and loads used between the GPUs of a node (plain NVLink peer memory)
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_sys_f32(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// true once *flag has reached `step` (wrap-safe), false when the bound ran out
+__device__ __forceinline__ bool wait_step(const uint32_t* flag, uint32_t step, long long limit) {
+  const long long t0 = clock64();
+  while (static_cast<int32_t>(ld_acquire_sys(flag) - step) < 0) {
+    if (clock64() - t0 > limit) return false;
+  }
+  return true;
+}
+
+
+// A link to the peers of a node, as kernels receive it: the exchange buffer of every rank, where the
+// flag words live in it, and this rank's step counter.
+constexpr int kLinkMaxRanks = 8;
+struct PeerLinkDev {
+  unsigned char* buf[kLinkMaxRanks];
+  int rank, world;
+  int64_t off_flags;
+  int slot;                 // flag word of rank r in a buffer: off_flags + 4 * (slot * 8 + r)
+  int32_t* state;           // local device memory: [0] steps completed, [1] ticket of the running launch
+  long long wait_cycles;
+};
+__device__ __forceinline__ uint32_t* link_flag(const PeerLinkDev& l, int in_rank, int of_rank) {
+  return reinterpret_cast<uint32_t*>(l.buf[in_rank] + l.off_flags) + l.slot * 8 + of_rank;
+}
+
+bool make_link(const b200dsa_peer_link* in, PeerLinkDev* out, const char* who);   // runtime.cu
+
 // Host: build tensor maps through the driver entry point (no link-time libcuda dependency).
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

@@ -724,7 +724,38 @@ namespace b200dsa {
 int topk_select_from_lists(const float* scores, int64_t row_stride, int32_t n_rows, int32_t n_cols,
                            const int32_t* col_end, int32_t k, int32_t sorted, const int32_t* row_pos_offset,
                            uint64_t* cand, int32_t* count, uint32_t* floor_bits, int32_t* out_idx, float* out_val,
-                           int64_t out_stride, int32_t* status, cudaStream_t stream);
+                           int64_t out_stride, int32_t* status, const PeerLinkDev* push, int64_t push_off,
+                           cudaStream_t stream);
+}
+
+static int fused_topk(const char* who, const void* q_fp8, const float* weights, const void* cache, int32_t num_pages,
+                      int32_t page_size, const int32_t* context_lens, const int32_t* block_table,
+                      int64_t block_table_stride, const int32_t* row_table, int32_t n_rows, int32_t next_n,
+                      int32_t max_cols, float out_scale, float* logits, int64_t logits_stride, int32_t k,
+                      int32_t sorted, const int32_t* row_pos_offset, void* scratch_cand, int32_t* scratch_count,
+                      int32_t* out_idx, float* out_val, int64_t out_stride, const PeerLinkDev* push, int64_t push_off,
+                      int32_t* status, void* stream) {
+  if (!scratch_cand || !scratch_count || !out_idx || k < 1 || k > 2048 || out_stride < k ||
+      (reinterpret_cast<uintptr_t>(scratch_cand) & 7)) {
+    char msg[200];
+    snprintf(msg, sizeof(msg), "%s: bad argument (1 <= k <= 2048, out_stride >= k, 8-byte aligned scratch)", who);
+    set_last_error(msg);
+    return B200DSA_EINVAL;
+  }
+  EmitArgs em;
+  em.cand = static_cast<uint64_t*>(scratch_cand);
+  em.cand_count = scratch_count;
+  em.row_floor = reinterpret_cast<uint32_t*>(scratch_count + n_rows);
+  em.row_pos_offset = row_pos_offset;
+  em.cand_target = k + k / 2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = paged_fp8_launch(who, q_fp8, weights, cache, num_pages, page_size, context_lens, block_table,
+                            block_table_stride, row_table, n_rows, next_n, max_cols, out_scale, logits, logits_stride,
+                            nullptr, nullptr, status, em, st);
+  if (rc) return rc;
+  return topk_select_from_lists(logits, logits_stride, n_rows, max_cols, context_lens, k, sorted, row_pos_offset,
+                                em.cand, em.cand_count, em.row_floor, out_idx, out_val, out_stride, status, push,
+                                push_off, st);
 }
 
 extern "C" int b200dsa_indexer_paged_fp8_topk(const void* q_fp8, const float* weights, const void* cache,
@@ -736,24 +767,32 @@ extern "C" int b200dsa_indexer_paged_fp8_topk(const void* q_fp8, const float* we
                                               void* scratch_cand, int32_t* scratch_count, int32_t* out_idx,
                                               float* out_val, int64_t out_stride, int32_t* status, void* stream) {
   if (n_rows == 0) return B200DSA_OK;
-  if (!scratch_cand || !scratch_count || !out_idx || k < 1 || k > 2048 || out_stride < k ||
-      (reinterpret_cast<uintptr_t>(scratch_cand) & 7)) {
-    set_last_error("b200dsa_indexer_paged_fp8_topk: bad argument (1 <= k <= 2048, out_stride >= k, 8-byte aligned scratch)");
+  return fused_topk("b200dsa_indexer_paged_fp8_topk", q_fp8, weights, cache, num_pages, page_size, context_lens,
+                    block_table, block_table_stride, row_table, n_rows, next_n, max_cols, out_scale, logits,
+                    logits_stride, k, sorted, row_pos_offset, scratch_cand, scratch_count, out_idx, out_val,
+                    out_stride, nullptr, 0, status, stream);
+}
+
+extern "C" int b200dsa_indexer_paged_fp8_topk_push(const void* q_fp8, const float* weights, const void* cache,
+                                                   int32_t num_pages, int32_t page_size, const int32_t* context_lens,
+                                                   const int32_t* block_table, int64_t block_table_stride,
+                                                   const int32_t* row_table, int32_t n_rows, int32_t next_n,
+                                                   int32_t max_cols, float out_scale, float* logits,
+                                                   int64_t logits_stride, int32_t k, int32_t sorted,
+                                                   const int32_t* row_pos_offset, void* scratch_cand,
+                                                   int32_t* scratch_count, int32_t* out_idx, float* out_val,
+                                                   int64_t out_stride, const b200dsa_peer_link* link, int64_t off_recv,
+                                                   int32_t* status, void* stream) {
+  PeerLinkDev dev_link;
+  if (!make_link(link, &dev_link, "b200dsa_indexer_paged_fp8_topk_push")) return B200DSA_EINVAL;
+  if (off_recv < 0 || (off_recv & 15) || n_rows < 1) {
+    set_last_error("b200dsa_indexer_paged_fp8_topk_push: off_recv must be 16-byte aligned and n_rows >= 1");
     return B200DSA_EINVAL;
   }
-  EmitArgs em;
-  em.cand = static_cast<uint64_t*>(scratch_cand);
-  em.cand_count = scratch_count;
-  em.row_floor = reinterpret_cast<uint32_t*>(scratch_count + n_rows);
-  em.row_pos_offset = row_pos_offset;
-  em.cand_target = k + k / 2;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc = paged_fp8_launch("b200dsa_indexer_paged_fp8_topk", q_fp8, weights, cache, num_pages, page_size, context_lens,
-                            block_table, block_table_stride, row_table, n_rows, next_n, max_cols, out_scale, logits,
-                            logits_stride, nullptr, nullptr, status, em, st);
-  if (rc) return rc;
-  return topk_select_from_lists(logits, logits_stride, n_rows, max_cols, context_lens, k, sorted, row_pos_offset,
-                                em.cand, em.cand_count, em.row_floor, out_idx, out_val, out_stride, status, st);
+  return fused_topk("b200dsa_indexer_paged_fp8_topk_push", q_fp8, weights, cache, num_pages, page_size, context_lens,
+                    block_table, block_table_stride, row_table, n_rows, next_n, max_cols, out_scale, logits,
+                    logits_stride, k, sorted, row_pos_offset, scratch_cand, scratch_count, out_idx, out_val,
+                    out_stride, &dev_link, off_recv, status, stream);
 }
 
 extern "C" int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const float* weights, const void* keys_bf16,

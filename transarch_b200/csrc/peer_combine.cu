@@ -30,6 +30,7 @@ constexpr long long kPeerWaitCyclesDefault = 1ll << 31;   // about a second
 // Limit of every wait for a peer, in SM clock cycles; process-wide, set by b200dsa_peer_set_wait_limit
 // and copied into the parameters of each launch.
 static long long g_peer_wait_cycles = kPeerWaitCyclesDefault;
+long long peer_wait_cycles() { return g_peer_wait_cycles; }
 constexpr int kPeerDoneSlot = 16;                  // flags: ready[0..7], done[16..23] (uint32 words)
 
 struct PeerCombineParams {
@@ -40,39 +41,9 @@ struct PeerCombineParams {
   int32_t* state;                     // local: [0] launches completed, [1] blocks finished in this launch
   int32_t* status;
   int no_sync;                        // skip the flag exchange (sequential emulation of ranks on one GPU)
+  int pre_signalled;                  // the "partial ready" flags were raised by the kernel that wrote the partial
   long long wait_cycles;              // bound of every wait for a peer's flag
 };
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_sys_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ float ld_sys_f32(const float* p) {
-  float v;
-  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// true once *flag has reached `step` (wrap-safe), false when the bound ran out
-__device__ __forceinline__ bool wait_step(const uint32_t* flag, uint32_t step, long long limit) {
-  const long long t0 = clock64();
-  while (static_cast<int32_t>(ld_acquire_sys(flag) - step) < 0) {
-    if (clock64() - t0 > limit) return false;
-  }
-  return true;
-}
 
 __device__ __forceinline__ void fma_bf16x8(float* acc, const uint4& v, float w) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -105,7 +76,7 @@ __global__ void __launch_bounds__(256, 2) peer_lse_combine_kernel(const PeerComb
 
   // ---- 1. partials of this step are ready everywhere
   if (!p.no_sync) {
-    if (blockIdx.x == 0 && tid < p.world)
+    if (blockIdx.x == 0 && tid < p.world && !p.pre_signalled)
       st_release_sys(reinterpret_cast<uint32_t*>(p.buf[tid] + p.off_flags) + p.rank, step);
     if (tid < p.world && !wait_step(my_flags + tid, step, p.wait_cycles)) atomicMax(p.status, kDevWaitTimeout);
     __syncthreads();
@@ -316,8 +287,8 @@ using namespace b200dsa;
 
 extern "C" int b200dsa_peer_lse_combine(void* const* bufs, int32_t rank, int32_t world, int64_t n_rows,
                                         int64_t off_ctx, int64_t off_lse, int64_t off_out, int64_t off_lse_out,
-                                        int64_t off_flags, int32_t* state, int32_t no_sync, int32_t* status,
-                                        void* stream) {
+                                        int64_t off_flags, int32_t* state, int32_t no_sync, int32_t pre_signalled,
+                                        int32_t* status, void* stream) {
   if (!bufs || !state || !status || world < 1 || world > kPeerMaxRanks || rank < 0 || rank >= world || n_rows < 0 ||
       ((off_ctx | off_lse | off_out | off_lse_out | off_flags) & 15) || off_ctx < 0 || off_lse < 0 || off_out < 0 ||
       off_lse_out < 0 || off_flags < 0) {
@@ -344,6 +315,7 @@ extern "C" int b200dsa_peer_lse_combine(void* const* bufs, int32_t rank, int32_t
   p.status = status;
   p.wait_cycles = g_peer_wait_cycles;
   p.no_sync = no_sync;
+  p.pre_signalled = pre_signalled;
   const int64_t per = (n_rows + world - 1) / world;
   int64_t grid = (per + 7) / 8;
   if (grid < 1) grid = 1;

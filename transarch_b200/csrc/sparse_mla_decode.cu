@@ -70,6 +70,13 @@ struct MlaParams {
   int ctx_bf16;
   float* lse;                  // [n_items, n_heads] fp32 (natural log)
   int32_t* status;
+  // key-sharded decode: when every CTA has written (and fenced) its part of ctx / lse, the last one
+  // raises this rank's flag word on every rank: "my partial of step state[0] + 1 is ready".  The
+  // kernel that merges the partials (b200dsa_peer_lse_combine with pre_signalled) owns and advances
+  // the step counter; this kernel only reads it.
+  int signal_on;
+  PeerLinkDev link;
+  int32_t* ticket;             // local int32, zero between launches
 };
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
@@ -145,7 +152,27 @@ sparse_mla_decode_kernel(const MlaParams p) {
 
   const int item = blockIdx.x >> 1;
   const int hh = blockIdx.x & 1;
-  if (hh * kMlaHeadsTile >= p.n_heads) return;  // nothing to do for this head half (whole CTA)
+  // after its last store every CTA takes a ticket; the last one tells the peers (see MlaParams)
+  auto signal_peers = [&]() {
+    if (!p.signal_on) return;
+    __shared__ int s_last_cta;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      s_last_cta = (atomicAdd(p.ticket, 1) == static_cast<int>(gridDim.x) - 1);
+    }
+    __syncthreads();
+    if (s_last_cta) {
+      __threadfence();
+      const uint32_t step = static_cast<uint32_t>(*reinterpret_cast<volatile int32_t*>(p.link.state)) + 1u;
+      if (threadIdx.x < p.link.world) st_release_sys(link_flag(p.link, threadIdx.x, p.link.rank), step);
+      if (threadIdx.x == 0) *p.ticket = 0;
+    }
+  };
+  if (hh * kMlaHeadsTile >= p.n_heads) {  // nothing to do for this head half (whole CTA)
+    signal_peers();
+    return;
+  }
 
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_dyn + (smem_base - smem_u32(smem_dyn));
@@ -494,6 +521,7 @@ sparse_mla_decode_kernel(const MlaParams p) {
   tc_fence_after();
   if (warp == 8) tmem_dealloc(tmem_base, kMlaTmemCols);
   if (tid == 0 && s_abort) atomicMax(p.status, kDevWaitTimeout);
+  signal_peers();
 }
 
 void set_last_error(const char* msg);
@@ -502,12 +530,55 @@ void set_last_error(const char* msg);
 
 using namespace b200dsa;
 
+static int mla_decode_launch(const void* q_bf16, const void* kv_bf16, int64_t kv_rows, const int64_t* kv_row_base,
+                             const int32_t* indices, int64_t idx_stride, int32_t n_idx, const int32_t* n_idx_item,
+                             const int32_t* q_pos, int32_t q_pos_bias, int32_t pos_lo, int32_t pos_hi, int32_t n_items,
+                             int32_t n_heads, float sm_scale, void* ctx, int32_t ctx_bf16, float* lse, int32_t* status,
+                             const PeerLinkDev* link, int32_t* ticket, void* stream);
+
 extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16, int64_t kv_rows,
                                          const int64_t* kv_row_base, const int32_t* indices, int64_t idx_stride,
                                          int32_t n_idx, const int32_t* n_idx_item, const int32_t* q_pos,
                                          int32_t q_pos_bias, int32_t pos_lo, int32_t pos_hi,
                                          int32_t n_items, int32_t n_heads, float sm_scale, void* ctx, int32_t ctx_bf16,
                                          float* lse, int32_t* status, void* stream) {
+  return mla_decode_launch(q_bf16, kv_bf16, kv_rows, kv_row_base, indices, idx_stride, n_idx, n_idx_item, q_pos,
+                           q_pos_bias, pos_lo, pos_hi, n_items, n_heads, sm_scale, ctx, ctx_bf16, lse, status, nullptr,
+                           nullptr, stream);
+}
+
+extern "C" int b200dsa_sparse_mla_decode_signal(const void* q_bf16, const void* kv_bf16, int64_t kv_rows,
+                                                const int64_t* kv_row_base, const int32_t* indices,
+                                                int64_t idx_stride, int32_t n_idx, const int32_t* n_idx_item,
+                                                const int32_t* q_pos, int32_t q_pos_bias, int32_t pos_lo,
+                                                int32_t pos_hi, int32_t n_items, int32_t n_heads, float sm_scale,
+                                                void* ctx, int32_t ctx_bf16, float* lse,
+                                                const b200dsa_peer_link* link, int32_t* ticket, int32_t* status,
+                                                void* stream) {
+  PeerLinkDev dev_link;
+  if (!ticket || n_items < 1) {
+    set_last_error("b200dsa_sparse_mla_decode_signal: ticket is required and n_items >= 1");
+    return B200DSA_EINVAL;
+  }
+  // the flag words of the combine kernel itself are used: slot 0
+  b200dsa_peer_link l = *link;
+  if (l.slot != 0) {
+    set_last_error("b200dsa_sparse_mla_decode_signal: the link must name slot 0, the combine kernel's 'ready' flags");
+    return B200DSA_EINVAL;
+  }
+  l.slot = 1;   // validated as an ordinary slot, then set back
+  if (!make_link(&l, &dev_link, "b200dsa_sparse_mla_decode_signal")) return B200DSA_EINVAL;
+  dev_link.slot = 0;
+  return mla_decode_launch(q_bf16, kv_bf16, kv_rows, kv_row_base, indices, idx_stride, n_idx, n_idx_item, q_pos,
+                           q_pos_bias, pos_lo, pos_hi, n_items, n_heads, sm_scale, ctx, ctx_bf16, lse, status, &dev_link,
+                           ticket, stream);
+}
+
+static int mla_decode_launch(const void* q_bf16, const void* kv_bf16, int64_t kv_rows, const int64_t* kv_row_base,
+                             const int32_t* indices, int64_t idx_stride, int32_t n_idx, const int32_t* n_idx_item,
+                             const int32_t* q_pos, int32_t q_pos_bias, int32_t pos_lo, int32_t pos_hi, int32_t n_items,
+                             int32_t n_heads, float sm_scale, void* ctx, int32_t ctx_bf16, float* lse, int32_t* status,
+                             const PeerLinkDev* link, int32_t* ticket, void* stream) {
   if (n_items == 0) return B200DSA_OK;
   if (!q_bf16 || !kv_bf16 || !indices || !ctx || !lse || !status || n_items < 0 || n_heads < 1 ||
       n_heads > kMlaMaxHeads || n_idx < 0 || idx_stride < n_idx || kv_rows < 1 || pos_hi < pos_lo) {
@@ -545,6 +616,11 @@ extern "C" int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16
   p.ctx_bf16 = ctx_bf16;
   p.lse = lse;
   p.status = status;
+  if (link) {
+    p.signal_on = 1;
+    p.link = *link;
+    p.ticket = ticket;
+  }
   e = launch_chained(sparse_mla_decode_kernel, dim3(n_items * 2), dim3(kMlaThreads), kMlaSmemBytes,
                      static_cast<cudaStream_t>(stream), p);
   if (e == cudaSuccess) e = cudaGetLastError();

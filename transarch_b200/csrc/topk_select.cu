@@ -60,6 +60,20 @@ struct TopkParams {
   // reach that floor.  `scores` may then be NULL (no fallback: *status gets kDevSelectIncomplete).
   uint32_t* pre_floor;
   int32_t* status;
+  // key-sharded decode, first exchange folded into the two selections:
+  //  push (local selection): row r's k positions and k score bit patterns are also stored as
+  //    [2k] int32 at push_off + (push.rank * n_rows + r) * 2k * 4 of EVERY rank's exchange buffer;
+  //    when the last CTA has fenced its stores it raises this rank's flag word on every rank
+  //  wait (merge of the pushed lists): the kernel starts by waiting, bounded, until every rank's flag
+  //    reached the step this rank's own push recorded in wait.state[0]
+  //  owned: the winners inside [own_lo, own_hi) are also written, compacted and -1 padded, to `owned`
+  int32_t push_on, wait_on;
+  PeerLinkDev link;
+  int64_t push_off;
+  int32_t own_lo, own_hi;
+  int32_t* owned;
+  int64_t owned_stride;
+  int32_t* owned_count;
 };
 
 __device__ __forceinline__ bool score_valid(float v, int keep_pos_inf) {
@@ -434,7 +448,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + kHistBins * sizeof(uint32_t));
   uint64_t* eq = cand + cand_cap;   // cand_cap <= kCandCap: rows that fit entirely get a smaller list
   uint64_t* sel = eq + kEqCap;  // k_pow2 entries
-  __shared__ int s_eq_cnt, s_sel_cnt, s_res[3], s_warp_cnt[32], s_overflow;
+  __shared__ int s_eq_cnt, s_sel_cnt, s_res[3], s_warp_cnt[32], s_overflow, s_own_cnt, s_last;
   __shared__ uint32_t s_seg[32];
 
   const int row = blockIdx.x;
@@ -456,20 +470,74 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   float* out_val = p.out_val ? p.out_val + row * p.out_stride : nullptr;
   const int k = p.k;
 
-  if (n <= 0) {
-    for (int j = tid; j < k; j += nthr) {
-      out_idx[j] = -1;
-      if (out_val) out_val[j] = -INFINITY;
-    }
-    return;
-  }
-
   if (tid == 0) {
     s_overflow = 0;
     s_eq_cnt = 0;
     s_sel_cnt = 0;
+    s_own_cnt = 0;
+  }
+  if (p.wait_on) {
+    // the rows of this launch were pushed by the peers' selections: wait for every rank's flag
+    const uint32_t step = static_cast<uint32_t>(*reinterpret_cast<volatile int32_t*>(p.link.state));
+    if (tid < p.link.world && !wait_step(link_flag(p.link, p.link.rank, tid), step, p.link.wait_cycles))
+      atomicMax(p.status, kDevWaitTimeout);
   }
   __syncthreads();
+
+  // Writes the first n_out composites of `src_keys` (or nothing) as the row's result, -1 / -inf padded:
+  // locally, into every peer's receive slot when pushing, and compacted into the owned list.
+  auto write_row = [&](const uint64_t* src_keys, int n_out) {
+    int32_t* own_row = p.owned ? p.owned + row * p.owned_stride : nullptr;
+    const int64_t push_row = (static_cast<int64_t>(p.link.rank) * p.n_rows + row) * 2 * k;
+    for (int j = tid; j < k; j += nthr) {
+      int32_t pos = -1;
+      float val = -INFINITY;
+      if (j < n_out) {
+        const uint64_t key = src_keys[j];
+        pos = static_cast<int32_t>(~static_cast<uint32_t>(key & 0xffffffffu));
+        val = ordered_to_float(static_cast<uint32_t>(key >> 32));
+      }
+      out_idx[j] = pos;
+      if (out_val) out_val[j] = val;
+      if (p.push_on) {
+        for (int r = 0; r < p.link.world; ++r) {
+          int32_t* dst = reinterpret_cast<int32_t*>(p.link.buf[r] + p.push_off) + push_row;
+          dst[j] = pos;
+          dst[k + j] = __float_as_int(val);
+        }
+      }
+      if (own_row && pos >= p.own_lo && pos < p.own_hi) own_row[atomicAdd(&s_own_cnt, 1)] = pos;
+    }
+    if (own_row) {
+      __syncthreads();
+      const int n_own = s_own_cnt;
+      for (int j = n_own + tid; j < k; j += nthr) own_row[j] = -1;
+      if (tid == 0) p.owned_count[row] = n_own;
+    }
+    if (p.push_on) {
+      // every CTA of the grid takes a ticket after fencing its peer stores; the last one raises the flags
+      __syncthreads();
+      if (tid == 0) {
+        __threadfence_system();
+        s_last = (atomicAdd(p.link.state + 1, 1) == static_cast<int>(gridDim.x) - 1);
+      }
+      __syncthreads();
+      if (s_last) {
+        __threadfence();
+        const uint32_t step = static_cast<uint32_t>(*reinterpret_cast<volatile int32_t*>(p.link.state)) + 1u;
+        if (tid < p.link.world) st_release_sys(link_flag(p.link, tid, p.link.rank), step);
+        if (tid == 0) {
+          p.link.state[1] = 0;
+          p.link.state[0] = static_cast<int32_t>(step);
+        }
+      }
+    }
+  };
+
+  if (n <= 0) {
+    write_row(nullptr, 0);
+    return;
+  }
 
   // ------------------------------------------------------------------ candidate collection
   const int warp_id = tid >> 5, lane_id = tid & 31, n_warps = nthr >> 5;
@@ -511,10 +579,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
       if (tid == 0 && p.status) atomicMax(p.status, kDevSelectIncomplete);
       usable = c <= kCandCap;
       if (!usable) {
-        for (int j = tid; j < k; j += nthr) {
-          out_idx[j] = -1;
-          if (out_val) out_val[j] = -INFINITY;
-        }
+        write_row(nullptr, 0);
         return;
       }
     }
@@ -649,17 +714,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     for (int i = n_sel + tid; i < n_pow2; i += nthr) sel[i] = 0;
     sort_desc(sel, n_pow2);
   }
-  const int n_out = min(n_sel, k);
-  for (int j = tid; j < k; j += nthr) {
-    if (j < n_out) {
-      const uint64_t key = sel[j];
-      out_idx[j] = static_cast<int32_t>(~static_cast<uint32_t>(key & 0xffffffffu));
-      if (out_val) out_val[j] = ordered_to_float(static_cast<uint32_t>(key >> 32));
-    } else {
-      out_idx[j] = -1;
-      if (out_val) out_val[j] = -INFINITY;
-    }
-  }
+  write_row(sel, min(n_sel, k));
 }
 
 
@@ -875,11 +930,17 @@ namespace b200dsa {
 int topk_select_from_lists(const float* scores, int64_t row_stride, int32_t n_rows, int32_t n_cols,
                            const int32_t* col_end, int32_t k, int32_t sorted, const int32_t* row_pos_offset,
                            uint64_t* cand, int32_t* count, uint32_t* floor_bits, int32_t* out_idx, float* out_val,
-                           int64_t out_stride, int32_t* status, cudaStream_t stream) {
+                           int64_t out_stride, int32_t* status, const PeerLinkDev* push, int64_t push_off,
+                           cudaStream_t stream) {
   TopkParams p{scores, row_stride, n_rows, n_cols, nullptr, col_end, k, 0, nullptr, 0, nullptr, 0, 0,
                row_pos_offset, out_idx, out_val, out_stride, sorted, 0, 0, cand, count};
   p.pre_floor = floor_bits;
   p.status = status;
+  if (push) {
+    p.push_on = 1;
+    p.link = *push;
+    p.push_off = push_off;
+  }
   int k_pow2 = 32;
   while (k_pow2 < k) k_pow2 <<= 1;
   const size_t smem = kHistBins * sizeof(uint32_t) + (kCandCap + kEqCap + k_pow2) * sizeof(uint64_t);
@@ -895,6 +956,54 @@ int topk_select_from_lists(const float* scores, int64_t row_stride, int32_t n_ro
   return B200DSA_OK;
 }
 }  // namespace b200dsa
+
+extern "C" int b200dsa_topk_merge_owned(const int32_t* recv, int32_t world, int32_t n_rows, int32_t k, int32_t sorted,
+                                        int32_t own_lo, int32_t own_hi, int32_t* out_idx, int64_t out_stride,
+                                        int32_t* owned, int64_t owned_stride, int32_t* owned_count,
+                                        const b200dsa_peer_link* link, int32_t* status, void* stream) {
+  if (n_rows == 0) return B200DSA_OK;
+  if (!recv || !out_idx || !owned || !owned_count || !status || world < 1 || world > 8 || n_rows < 0 || k < 1 ||
+      k > kCandCap || out_stride < k || owned_stride < k || (reinterpret_cast<uintptr_t>(recv) & 15) || (k & 3)) {
+    set_last_error("b200dsa_topk_merge_owned: bad argument (1 <= world <= 8, k a multiple of 4, strides >= k)");
+    return B200DSA_EINVAL;
+  }
+  // column c of row r = candidate c % k of rank c / k: scores at recv + rank*n_rows*2k + r*2k + k + c%k,
+  // positions k ints before them
+  const float* scores = reinterpret_cast<const float*>(recv) + k;
+  TopkParams p{scores, 2 * static_cast<int64_t>(k), n_rows, world * k, nullptr, nullptr, k, 0, recv,
+               2 * static_cast<int64_t>(k), nullptr, 0, 0, nullptr, out_idx, nullptr, out_stride, sorted, k,
+               static_cast<int64_t>(n_rows) * 2 * k};
+  p.status = status;
+  p.own_lo = own_lo;
+  p.own_hi = own_hi;
+  p.owned = owned;
+  p.owned_stride = owned_stride;
+  p.owned_count = owned_count;
+  if (link) {
+    if (!make_link(link, &p.link, "b200dsa_topk_merge_owned")) return B200DSA_EINVAL;
+    p.wait_on = 1;
+  }
+  int k_pow2 = 32;
+  while (k_pow2 < k) k_pow2 <<= 1;
+  int cand_cap = kCandCap;
+  if (world * k <= kCandCap) {
+    cand_cap = 1024;
+    while (cand_cap < world * k) cand_cap <<= 1;
+  }
+  const size_t smem = kHistBins * sizeof(uint32_t) + (static_cast<size_t>(cand_cap) + kEqCap + k_pow2) * sizeof(uint64_t);
+  cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kHistBins * sizeof(uint32_t) + (2 * kCandCap + kEqCap) * sizeof(uint64_t)));
+  const int threads = world * k > 8192 ? 1024 : (world * k > 2048 ? 512 : 256);
+  if (e == cudaSuccess)
+    e = launch_chained(topk_select_kernel, dim3(n_rows), dim3(threads), smem, static_cast<cudaStream_t>(stream), p,
+                       k_pow2, cand_cap);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  return B200DSA_OK;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Split top-k without caller-provided scratch.

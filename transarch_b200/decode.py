@@ -120,6 +120,9 @@ class SparseDecodeStep:
             self.lse = self.peer.lse.view(batch, n_heads)
             extra = self.peer.extra_of(self.peer.rank)
             self.cand = extra[:self.cand_bytes].view(i32).view(batch, 2 * topk)
+        # both exchanges folded into the compute kernels: the selection pushes its rows to the peers, the merge
+        # waits for them and emits the owned keys, the attention kernel raises the "partial ready" flags
+        self.peer_fused = self.peer is not None and self.fused_scratch is not None
         if n > 1:
             if self.peer is not None:     # receive area inside the exchange buffer: peers store into it
                 self.cand_all = self.peer.extra_of(self.peer.rank)[self.cand_bytes:].view(i32).view(n, batch, 2 * topk)
@@ -169,10 +172,13 @@ class SparseDecodeStep:
         val = self.cand[:, self.topk:].view(torch.float32)
         offset = self.pos_offset if self.shard.world_size > 1 else None
         if self.fused_scratch is not None:
+            push = None
+            if self.peer_fused:           # receive area: right after this rank's own candidates in the extra area
+                push = (self.peer.link(1), self.peer.off_extra + self.cand_bytes)
             K.indexer_paged_fp8_topk(self.q_fp8, self.weights, k_cache, self.P, context_lens_local, block_table,
                                      self.topk, self.fused_scratch, max_cols=self.max_cols, logits=self.logits,
                                      keep_logits=self.keep_logits, row_pos_offset=offset, sorted=self.sorted_topk,
-                                     out=idx, out_values=val)
+                                     out=idx, out_values=val, push=push)
             return idx
         K.indexer_paged_fp8_logits(self.q_fp8, self.weights, k_cache, self.P, context_lens_local, block_table,
                                    max_cols=self.max_cols, out=self.logits)
@@ -187,6 +193,13 @@ class SparseDecodeStep:
     def merge_candidates(self) -> torch.Tensor:
         """All-gather the per-rank candidates and select the global top-k (identical on every rank)."""
         n, k = self.shard.world_size, self.topk
+        if self.peer_fused:
+            # the selections pushed their rows already: wait for the peers' flags inside the merge kernel,
+            # which also compacts the winners this rank owns
+            self.K.topk_merge_owned(self.cand_all, k, self.shard.pos_lo, self.shard.pos_hi, out=self.merged,
+                                    owned=self.owned, owned_count=self.owned_count, sorted=self.sorted_topk,
+                                    link=self.peer.link(1))
+            return self.merged
         if self.peer is not None:
             # one kernel: this rank's candidates are stored into its slot of every rank's receive area
             # (posted NVLink stores, same layout as the NCCL all-gather delivers); it ends when all
@@ -202,10 +215,21 @@ class SparseDecodeStep:
                            seg_stride=self.B * 2 * k, n_rows=self.B, pos_map_stride=2 * k)
         return self.merged
 
-    def attend(self, q_lat, kv, kv_row_base, indices, q_pos, q_pos_bias: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+    def attend(self, q_lat, kv, kv_row_base, indices, q_pos, q_pos_bias: int = 0,
+               signal: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
         """Attention over the selected keys this rank owns (all of them when unsharded).  Keys beyond
-        q_pos + q_pos_bias are masked (context lengths with a bias of -1 save a subtraction kernel)."""
+        q_pos + q_pos_bias are masked (context lengths with a bias of -1 save a subtraction kernel).
+        signal=False: do not tell the peers that the partial is ready (combine() then does, as when the
+        exchanges are separate kernels)."""
         count = None
+        self._signalled = False
+        if self.peer_fused and indices is self.merged:
+            self._signalled = signal
+            return self.K.sparse_mla_decode(q_lat, kv, self.owned, self.attn_scale, kv_row_base=kv_row_base, q_pos=q_pos,
+                                            pos_lo=self.shard.pos_lo, pos_hi=self.shard.pos_hi,
+                                            n_idx_item=self.owned_count, ctx=self.ctx, lse=self.lse,
+                                            q_pos_bias=q_pos_bias,
+                                            signal=(self.peer.link(0), self.peer.ticket) if signal else None)
         if self.shard.world_size > 1 and hasattr(self.K, "compact_owned"):
             # only about 1/N of the selection lives here: compact it so the kernel walks just those
             indices, count = self.K.compact_owned(indices, self.shard.pos_lo, self.shard.pos_hi, self.owned,
@@ -220,7 +244,7 @@ class SparseDecodeStep:
         if self.peer is not None:
             # one kernel: flags, peer loads of all partials of the rows this rank owns, merged rows
             # stored to every rank
-            out, lse_out = self.peer.run()
+            out, lse_out = self.peer.run(pre_signalled=getattr(self, "_signalled", False))
             return out.view(self.B, self.H, 512), lse_out.view(self.B, self.H)
         if self.wire_mode == "bf16":
             # gather the lse of every rank (4 B per row and rank): each rank then knows the common

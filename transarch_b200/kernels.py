@@ -208,12 +208,14 @@ def indexer_paged_fp8_topk(q_fp8: torch.Tensor, weights: torch.Tensor, cache: to
                            logits: Optional[torch.Tensor] = None, keep_logits: bool = True,
                            row_table: Optional[torch.Tensor] = None, row_pos_offset: Optional[torch.Tensor] = None,
                            sorted: bool = False, out: Optional[torch.Tensor] = None,
-                           out_values: Optional[torch.Tensor] = None):
+                           out_values: Optional[torch.Tensor] = None, push=None):
     """Indexer scores and their top-k positions in two launches, the candidates collected by the
     indexer's own epilogue; see b200dsa_indexer_paged_fp8_topk.  `scratch` comes from topk_scratch().
     keep_logits=True (default) also writes the logits (into `logits`, allocated when not given) so
     that a row whose candidate list is not provably complete is selected exactly from them;
-    keep_logits=False writes no logits at all (status word 3 on such a row)."""
+    keep_logits=False writes no logits at all (status word 3 on such a row).
+    push=(link, off_recv): the selection also stores its rows into every peer's receive area and
+    raises this rank's flag (b200dsa_indexer_paged_fp8_topk_push; link from PeerLseCombine.link())."""
     require_cuda(q_fp8, weights, cache, context_lens, block_table, row_table, row_pos_offset, logits, out, out_values)
     if q_fp8.dtype != torch.float8_e4m3fn or not q_fp8.is_contiguous() or q_fp8.shape[-2:] != (64, 128):
         raise _lib.B200DSAError("q_fp8 must be contiguous float8_e4m3fn [..., 64, 128]")
@@ -243,11 +245,16 @@ def indexer_paged_fp8_topk(q_fp8: torch.Tensor, weights: torch.Tensor, cache: to
     if out is None:
         out = torch.empty(n_rows, k, dtype=torch.int32, device=q_fp8.device)
     _check_topk_outputs(out, out_values, n_rows, k)
-    rc = _lib.load().b200dsa_indexer_paged_fp8_topk(
-        ptr(q_fp8), ptr(weights), ptr(cache), num_pages, page_size, ptr(context_lens), ptr(block_table),
-        block_table.stride(0), ptr(_i32(row_table, "row_table")), n_rows, next_n, max_cols, out_scale, ptr(logits),
-        logits.stride(0) if logits is not None else 0, k, int(sorted), ptr(_i32(row_pos_offset, "row_pos_offset")),
-        ptr(cand), ptr(count), ptr(out), ptr(out_values), out.stride(0), ptr(status_word(q_fp8.device)), stream_ptr())
+    args = (ptr(q_fp8), ptr(weights), ptr(cache), num_pages, page_size, ptr(context_lens), ptr(block_table),
+            block_table.stride(0), ptr(_i32(row_table, "row_table")), n_rows, next_n, max_cols, out_scale, ptr(logits),
+            logits.stride(0) if logits is not None else 0, k, int(sorted), ptr(_i32(row_pos_offset, "row_pos_offset")),
+            ptr(cand), ptr(count), ptr(out), ptr(out_values), out.stride(0))
+    if push is None:
+        rc = _lib.load().b200dsa_indexer_paged_fp8_topk(*args, ptr(status_word(q_fp8.device)), stream_ptr())
+    else:
+        link, off_recv = push
+        rc = _lib.load().b200dsa_indexer_paged_fp8_topk_push(*args, ctypes.byref(link), off_recv,
+                                                             ptr(status_word(q_fp8.device)), stream_ptr())
     check(rc, "b200dsa_indexer_paged_fp8_topk")
     if out_values is not None:
         return out[:n_rows, :k], out_values[:n_rows, :k]
@@ -318,10 +325,11 @@ def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, 
                       kv_row_base: Optional[torch.Tensor] = None, q_pos: Optional[torch.Tensor] = None,
                       pos_lo: int = 0, pos_hi: int = 2 ** 31 - 1, n_idx_item: Optional[torch.Tensor] = None,
                       ctx: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
-                      q_pos_bias: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+                      q_pos_bias: int = 0, signal=None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Latent-space sparse attention: (ctx [n, H, 512], lse [n, H] fp32); see
     b200dsa_sparse_mla_decode.  ctx is fp32 unless a bf16 buffer is passed in; q_pos_bias is added to
-    q_pos (-1: q_pos holds context lengths)."""
+    q_pos (-1: q_pos holds context lengths).  signal=(link, ticket): the kernel's last CTA raises this
+    rank's "partial ready" flag on every rank (b200dsa_sparse_mla_decode_signal)."""
     require_cuda(q, kv, indices, kv_row_base, q_pos)
     if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.dim() != 3 or q.shape[2] != 576:
         raise _lib.B200DSAError("q must be contiguous bf16 [n_items, n_heads, 576]")
@@ -340,12 +348,38 @@ def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, 
     if ctx.dtype not in (torch.float32, torch.bfloat16) or not ctx.is_contiguous() or ctx.shape != (n, H, 512):
         raise _lib.B200DSAError("ctx must be contiguous fp32 or bf16 [n_items, n_heads, 512]")
     lib = _lib.load()
-    rc = lib.b200dsa_sparse_mla_decode(
-        ptr(q), ptr(kv), kv.shape[0], ptr(kv_row_base), ptr(indices), indices.stride(0), indices.shape[1],
-        ptr(_i32(n_idx_item, "n_idx_item")), ptr(q_pos), q_pos_bias, pos_lo, pos_hi, n, H, sm_scale, ptr(ctx),
-        int(ctx.dtype == torch.bfloat16), ptr(lse), ptr(status_word(q.device)), stream_ptr())
+    args = (ptr(q), ptr(kv), kv.shape[0], ptr(kv_row_base), ptr(indices), indices.stride(0), indices.shape[1],
+            ptr(_i32(n_idx_item, "n_idx_item")), ptr(q_pos), q_pos_bias, pos_lo, pos_hi, n, H, sm_scale, ptr(ctx),
+            int(ctx.dtype == torch.bfloat16), ptr(lse))
+    if signal is None:
+        rc = lib.b200dsa_sparse_mla_decode(*args, ptr(status_word(q.device)), stream_ptr())
+    else:
+        link, ticket = signal
+        rc = lib.b200dsa_sparse_mla_decode_signal(*args, ctypes.byref(link), ptr(ticket), ptr(status_word(q.device)),
+                                                  stream_ptr())
     check(rc, "b200dsa_sparse_mla_decode")
     return ctx, lse
+
+
+def topk_merge_owned(recv: torch.Tensor, k: int, own_lo: int, own_hi: int, *, out: torch.Tensor,
+                     owned: torch.Tensor, owned_count: torch.Tensor, sorted: bool = False, link=None):
+    """Global top-k of every row from the per-rank selections in recv int32 [world, n_rows, 2k]
+    (positions, then score bit patterns), plus the winners inside [own_lo, own_hi) compacted into
+    `owned`; see b200dsa_topk_merge_owned.  link: wait for the peers' pushes first."""
+    require_cuda(recv, out, owned, owned_count)
+    if recv.dtype != torch.int32 or not recv.is_contiguous() or recv.dim() != 3 or recv.shape[2] != 2 * k:
+        raise _lib.B200DSAError("recv must be contiguous int32 [world, n_rows, 2k]")
+    world, n_rows, _ = recv.shape
+    _check_topk_outputs(out, None, n_rows, k)
+    _check_topk_outputs(owned, None, n_rows, k)
+    if _i32(owned_count, "owned_count").numel() < n_rows:
+        raise _lib.B200DSAError("owned_count needs one entry per row")
+    rc = _lib.load().b200dsa_topk_merge_owned(
+        ptr(recv), world, n_rows, k, int(sorted), own_lo, own_hi, ptr(out), out.stride(0), ptr(owned),
+        owned.stride(0), ptr(owned_count), ctypes.byref(link) if link is not None else None,
+        ptr(status_word(recv.device)), stream_ptr())
+    check(rc, "b200dsa_topk_merge_owned")
+    return out[:n_rows, :k], owned, owned_count
 
 
 def lse_combine(ctx_parts: torch.Tensor, lse_parts: torch.Tensor, *, ctx_out: Optional[torch.Tensor] = None,

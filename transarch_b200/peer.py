@@ -129,6 +129,8 @@ class PeerLseCombine:
         self.extra_bytes = extra_bytes
         self.buffers = PeerBuffers(self.off_extra + extra_bytes, device, group, emulate_world)
         self.barrier_state = torch.zeros(16, dtype=torch.int32, device=device)
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=device)
+        self._links = {}
         self.rank, self.world = self.buffers.rank, self.buffers.world
         self.state = [torch.zeros(2, dtype=torch.int32, device=device) for _ in range(emulate_world or 1)]
         v = self.views_of(self.rank)
@@ -150,6 +152,16 @@ class PeerLseCombine:
         """Offset of every rank's buffer from this rank's, in elements of `itemsize` bytes."""
         base = self.buffers.addresses[self.rank]
         return [(a - base) // itemsize for a in self.buffers.addresses]
+
+    def link(self, slot: int):
+        """b200dsa_peer_link for kernels that exchange through these buffers.  Slot 0 names the merge
+        kernel's own "partial ready" flags and step counter (for the attention kernel that raises them);
+        slots 1, 3..7 carry their own step counters."""
+        if slot not in self._links:
+            state = self.state[0] if slot == 0 else self.barrier_state[2 * slot - 2:2 * slot]
+            self._links[slot] = _lib.PeerLink(ctypes.cast(self.buffers._addr_array, ctypes.c_void_p).value, self.rank,
+                                              self.world, self.off_flags, slot, state.data_ptr())
+        return self._links[slot]
 
     def barrier(self, slot: int = 1) -> None:
         """Node-wide barrier on the current stream (b200dsa_peer_barrier): what the peers wrote into
@@ -185,20 +197,55 @@ class PeerLseCombine:
         check(rc, "b200dsa_peer_gather")
         return dst
 
-    def run(self, rank: Optional[int] = None, no_sync: bool = False):
+    def run(self, rank: Optional[int] = None, no_sync: bool = False, pre_signalled: bool = False):
         """Launch on the current stream.  `rank` / no_sync are for single-GPU emulation only: there the
-        ranks run one after another and must not wait for each other."""
+        ranks run one after another and must not wait for each other.  pre_signalled: the attention
+        kernel already raised this rank's "partial ready" flags (sparse_mla_decode(signal=...))."""
         r = self.rank if rank is None else rank
         if self.buffers.world > 1 and rank is not None and not no_sync:
             raise _lib.B200DSAError("emulated ranks on one GPU must run with no_sync")
         state = self.state[r if len(self.state) > 1 else 0]
         rc = _lib.load().b200dsa_peer_lse_combine(
             self.buffers._addr_array, r, self.world, self.n_rows, self.off_ctx, self.off_lse, self.off_out,
-            self.off_lse_out, self.off_flags, ptr(state), int(no_sync), ptr(status_word(self.buffers.device)),
-            stream_ptr())
+            self.off_lse_out, self.off_flags, ptr(state), int(no_sync), int(pre_signalled),
+            ptr(status_word(self.buffers.device)), stream_ptr())
         check(rc, "b200dsa_peer_lse_combine")
         return self.out, self.lse_out
 
     def close(self) -> None:
         self.ctx = self.lse = self.out = self.lse_out = None
+        self.buffers.close()
+
+
+class PeerAllGather:
+    """All-gather of one byte range over NVLink by posted stores (b200dsa_peer_push): every rank
+    contributes `chunk` bytes and ends with all `world * chunk` bytes in local memory.  Used to replicate
+    a step's inputs inside the node when only 1/world of them crossed each rank's host link.
+
+    Buffer of a rank: `n_send` send areas of `chunk` bytes (one per in-flight step), then the receive
+    area [world, chunk], then 256 bytes of flags.  The constructor is collective."""
+
+    def __init__(self, total_bytes: int, device: torch.device, group=None, n_send: int = 1,
+                 emulate_world: Optional[int] = None):
+        world = emulate_world if emulate_world is not None else dist.get_world_size(group)
+        self.chunk = _align((total_bytes + world - 1) // world, 256)
+        self.n_send = n_send
+        self.off_recv = n_send * self.chunk
+        self.off_flags = self.off_recv + world * self.chunk
+        self.buffers = PeerBuffers(self.off_flags + 256, device, group, emulate_world)
+        self.rank, self.world = self.buffers.rank, self.buffers.world
+        self.state = torch.zeros(2, dtype=torch.int32, device=device)
+        self.send = [self.buffers.local[i * self.chunk:(i + 1) * self.chunk] for i in range(n_send)]
+        self.recv = self.buffers.local[self.off_recv:self.off_recv + world * self.chunk]
+
+    def run(self, send_slot: int = 0) -> torch.Tensor:
+        """Launch on the current stream; when the kernel ends every rank's chunk is in `recv`."""
+        rc = _lib.load().b200dsa_peer_push(
+            self.buffers._addr_array, self.rank, self.world, send_slot * self.chunk, self.chunk, self.off_recv,
+            self.off_flags, 1, ptr(self.state), ptr(status_word(self.buffers.device)), stream_ptr())
+        check(rc, "b200dsa_peer_push")
+        return self.recv
+
+    def close(self) -> None:
+        self.send, self.recv = [], None
         self.buffers.close()
