@@ -338,6 +338,8 @@ def main():
     ap.add_argument("--skip-configs", action="store_true", help="do not time the other configurations of the path")
     ap.add_argument("--skip-parity", action="store_true", help="do not compare sampled requests with the oracle")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--result", default="replicated", choices=["replicated", "sharded"],
+                    help="sharded run: every rank ends with all result rows, or only with its slice of them")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -365,7 +367,8 @@ def main():
     state = make_decode_state(B, ctx, page_size=PAGE, seed=4, rank=rank, world_size=world, shard_len=shard_len,
                               device=dev)
     step = SparseDecodeStep(B, shard_len, page_size=PAGE, topk=TOPK, n_heads=HEADS, index_scale=INDEX_SCALE,
-                            attn_scale=ATTN_SCALE, device=dev, shard=shard, ctx_dtype=torch.bfloat16)
+                            attn_scale=ATTN_SCALE, device=dev, shard=shard, ctx_dtype=torch.bfloat16,
+                            result=args.result)
     n_sets = 4  # rotating query sets so consecutive steps differ
     dev_q = [make_decode_queries(B, HEADS, seed=100 + i, device=dev) for i in range(n_sets)]
     host_q = [make_decode_queries(B, HEADS, seed=100 + i, pinned=True) for i in range(n_sets)]
@@ -692,6 +695,7 @@ def main():
             "data": "synthetic",
             "config": {"workload": WORKLOAD if (B, ctx) == (BATCH, CONTEXT) else f"batch {B}, context {ctx} (non-default)",
                        "parallelism": f"key-sharded x{world}",
+                       "result": "n/a" if world == 1 else args.result,
                        "exchange": "none" if world == 1 else ("peer memory (NVLink loads/stores in our kernels)"
                                                               if step.peer is not None else "NCCL"),
                        "launch": "eager" if graphed is None else "cuda-graph replay",

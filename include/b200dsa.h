@@ -321,12 +321,15 @@ int b200dsa_lse_combine(const float* ctx_parts, const float* lse_parts, int32_t 
  * ranks emulated one after another on a single GPU (tests); ranks that wait for each other
  * must run on different GPUs.  pre_signalled != 0: the kernel that wrote the partial
  * (b200dsa_sparse_mla_decode_signal) has already raised this rank's "ready" flags, so the call
- * only waits for the peers'.  1 <= world <= 8.
+ * only waits for the peers'.  local_only != 0 is the reduce-scatter form: the rank merges its
+ * slice of the rows (rows [rank*ceil(n_rows/world), ...)) into its OWN result area and neither stores
+ * to the peers nor waits for them a second time; the other rows of its result area are not written
+ * (a tensor-parallel output projection consumes exactly such a slice).  1 <= world <= 8.
  * ------------------------------------------------------------------------------------- */
 int b200dsa_peer_lse_combine(void* const* bufs, int32_t rank, int32_t world, int64_t n_rows,
                              int64_t off_ctx, int64_t off_lse, int64_t off_out, int64_t off_lse_out,
                              int64_t off_flags, int32_t* state, int32_t no_sync, int32_t pre_signalled,
-                             int32_t* status, void* stream);
+                             int32_t local_only, int32_t* status, void* stream);
 
 /* Node-wide barrier on the stream: one small kernel writes this rank's step number into every
  * peer's flag word `slot*8 + rank` (uint32 words at off_flags; slots 0 and 2 belong to

@@ -55,6 +55,19 @@ def test_emulated_ranks_one_after_another(world, n_rows):
                 assert torch.allclose(lo.cpu(), want_lse, rtol=1e-5, atol=1e-5)
                 assert (o[2] == 0).all()
             assert [int(s[0]) for s in pc.state] == [step + 1] * world
+        # reduce-scatter form: each rank keeps only its own slice of the rows, in its own buffer
+        for r in range(world):
+            _, _, o, lo = pc.views_of(r)
+            o.fill_(7.0); lo.fill_(7.0)
+        for r in range(world):
+            pc.run(rank=r, no_sync=True, local_only=True)
+        torch.cuda.synchronize()
+        for r in range(world):
+            a, b = pc.row_slice(r)
+            _, _, o, lo = pc.views_of(r)
+            assert torch.allclose(o[a:b].float().cpu(), want[a:b], rtol=1e-2, atol=1e-2)
+            assert torch.allclose(lo[a:b].cpu(), want_lse[a:b], rtol=1e-5, atol=1e-5)
+            assert (o[:a] == 7).all() and (o[b:] == 7).all()
         assert _lib.read_status(dev) == 0
     finally:
         pc.close()

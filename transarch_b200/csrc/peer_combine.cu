@@ -42,6 +42,7 @@ struct PeerCombineParams {
   int32_t* status;
   int no_sync;                        // skip the flag exchange (sequential emulation of ranks on one GPU)
   int pre_signalled;                  // the "partial ready" flags were raised by the kernel that wrote the partial
+  int local_only;                     // reduce-scatter form: keep the merged rows of this rank's slice, tell nobody
   long long wait_cycles;              // bound of every wait for a peer's flag
 };
 
@@ -122,6 +123,13 @@ __global__ void __launch_bounds__(256, 2) peer_lse_combine_kernel(const PeerComb
     }
     const uint4 oa = pack_bf16x8(a), ob = pack_bf16x8(b);
     const float lse_out = den > 0.f ? m + logf(den) : -INFINITY;
+    if (p.local_only) {
+      unsigned char* dst = p.buf[p.rank] + p.off_out + row * (kPeerDv * 2) + lane * 16;
+      *reinterpret_cast<uint4*>(dst) = oa;
+      *reinterpret_cast<uint4*>(dst + 512) = ob;
+      if (lane == 0) reinterpret_cast<float*>(p.buf[p.rank] + p.off_lse_out)[row] = lse_out;
+      continue;
+    }
 #pragma unroll
     for (int r = 0; r < kPeerMaxRanks; ++r) {
       if (r < p.world) {
@@ -144,7 +152,7 @@ __global__ void __launch_bounds__(256, 2) peer_lse_combine_kernel(const PeerComb
   __syncthreads();
   if (s_last) {
     __threadfence();
-    if (!p.no_sync && tid < p.world) {
+    if (!p.no_sync && !p.local_only && tid < p.world) {
       st_release_sys(reinterpret_cast<uint32_t*>(p.buf[tid] + p.off_flags) + kPeerDoneSlot + p.rank, step);
       if (!wait_step(my_flags + kPeerDoneSlot + tid, step, p.wait_cycles)) atomicMax(p.status, kDevWaitTimeout);
     }
@@ -288,7 +296,7 @@ using namespace b200dsa;
 extern "C" int b200dsa_peer_lse_combine(void* const* bufs, int32_t rank, int32_t world, int64_t n_rows,
                                         int64_t off_ctx, int64_t off_lse, int64_t off_out, int64_t off_lse_out,
                                         int64_t off_flags, int32_t* state, int32_t no_sync, int32_t pre_signalled,
-                                        int32_t* status, void* stream) {
+                                        int32_t local_only, int32_t* status, void* stream) {
   if (!bufs || !state || !status || world < 1 || world > kPeerMaxRanks || rank < 0 || rank >= world || n_rows < 0 ||
       ((off_ctx | off_lse | off_out | off_lse_out | off_flags) & 15) || off_ctx < 0 || off_lse < 0 || off_out < 0 ||
       off_lse_out < 0 || off_flags < 0) {
@@ -316,6 +324,7 @@ extern "C" int b200dsa_peer_lse_combine(void* const* bufs, int32_t rank, int32_t
   p.wait_cycles = g_peer_wait_cycles;
   p.no_sync = no_sync;
   p.pre_signalled = pre_signalled;
+  p.local_only = local_only;
   const int64_t per = (n_rows + world - 1) / world;
   int64_t grid = (per + 7) / 8;
   if (grid < 1) grid = 1;

@@ -67,7 +67,8 @@ class SparseDecodeStep:
                  n_heads: int = 128, index_scale: float = 128 ** -0.5, attn_scale: float = 192 ** -0.5,
                  device: Optional[torch.device] = None, shard: Optional[ShardInfo] = None, backend=None,
                  sorted_topk: bool = False, wire: str = "bf16", ctx_dtype: torch.dtype = torch.float32,
-                 combine: str = "auto", fused_select: bool = True, keep_logits: bool = True):
+                 combine: str = "auto", fused_select: bool = True, keep_logits: bool = True,
+                 result: str = "replicated"):
         if backend is None:
             from . import kernels as backend  # the CUDA kernels; fails loudly without the library
         self.K = backend
@@ -80,6 +81,10 @@ class SparseDecodeStep:
         self.wire_mode = wire if hasattr(backend, "lse_prescale_norm") else "fp32"
         if combine not in ("auto", "peer", "nccl"):
             raise ValueError("combine must be 'auto', 'peer' or 'nccl'")
+        if result not in ("replicated", "sharded"):
+            raise ValueError("result must be 'replicated' (every rank ends with all rows) or 'sharded' (each rank "
+                             "keeps the (item, head) rows of its slice: what a tensor-parallel output projection reads)")
+        self.result = result
         dev = device if device is not None else torch.device("cuda")
         self.dev = dev
         f32, i32 = torch.float32, torch.int32
@@ -244,7 +249,8 @@ class SparseDecodeStep:
         if self.peer is not None:
             # one kernel: flags, peer loads of all partials of the rows this rank owns, merged rows
             # stored to every rank
-            out, lse_out = self.peer.run(pre_signalled=getattr(self, "_signalled", False))
+            out, lse_out = self.peer.run(pre_signalled=getattr(self, "_signalled", False),
+                                         local_only=self.result == "sharded")
             return out.view(self.B, self.H, 512), lse_out.view(self.B, self.H)
         if self.wire_mode == "bf16":
             # gather the lse of every rank (4 B per row and rank): each rank then knows the common

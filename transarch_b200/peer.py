@@ -197,17 +197,25 @@ class PeerLseCombine:
         check(rc, "b200dsa_peer_gather")
         return dst
 
-    def run(self, rank: Optional[int] = None, no_sync: bool = False, pre_signalled: bool = False):
+    def row_slice(self, r: Optional[int] = None):
+        """(first, last+1) rows of the merged result that rank r computes (and, with local_only, keeps)."""
+        r = self.rank if r is None else r
+        per = (self.n_rows + self.world - 1) // self.world
+        return min(r * per, self.n_rows), min((r + 1) * per, self.n_rows)
+
+    def run(self, rank: Optional[int] = None, no_sync: bool = False, pre_signalled: bool = False,
+            local_only: bool = False):
         """Launch on the current stream.  `rank` / no_sync are for single-GPU emulation only: there the
         ranks run one after another and must not wait for each other.  pre_signalled: the attention
-        kernel already raised this rank's "partial ready" flags (sparse_mla_decode(signal=...))."""
+        kernel already raised this rank's "partial ready" flags (sparse_mla_decode(signal=...)).
+        local_only: reduce-scatter form, only rows row_slice() of `out` / `lse_out` are produced."""
         r = self.rank if rank is None else rank
         if self.buffers.world > 1 and rank is not None and not no_sync:
             raise _lib.B200DSAError("emulated ranks on one GPU must run with no_sync")
         state = self.state[r if len(self.state) > 1 else 0]
         rc = _lib.load().b200dsa_peer_lse_combine(
             self.buffers._addr_array, r, self.world, self.n_rows, self.off_ctx, self.off_lse, self.off_out,
-            self.off_lse_out, self.off_flags, ptr(state), int(no_sync), int(pre_signalled),
+            self.off_lse_out, self.off_flags, ptr(state), int(no_sync), int(pre_signalled), int(local_only),
             ptr(status_word(self.buffers.device)), stream_ptr())
         check(rc, "b200dsa_peer_lse_combine")
         return self.out, self.lse_out
