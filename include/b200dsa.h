@@ -169,6 +169,26 @@ int b200dsa_indexer_paged_fp8_logits(const void* q_fp8, const float* weights, co
                                      float* logits_gated, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Token logits inside per-row lists of 128-key blocks of the PAGED FP8 cache (HISA stage 2 / block-sparse
+ * re-scoring while serving): column c of row r is key position block_list[r, c/128]*128 + c%128 of the row's
+ * request, found through the block table;
+ *   logits[r, c] = out_scale * k_scale * sum_h weights[r,h]*relu(<q[r,h,:], k_fp8[pos,:]>)
+ * when c < row_cols[r], block id >= 0 and pos < context_lens[r]; -inf otherwise (for c < row_cols[r] rounded
+ * up to 128; columns beyond are left untouched).
+ * Replaces MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/block_ops.py:151-379
+ * (paged_block_sparse_mqa_attn_return_logits + interface), reading the FP8 pages in place instead of a
+ * bf16 copy of the cache.  q / weights / cache / context_lens / block_table / row_table / next_n as for
+ * b200dsa_indexer_paged_fp8_logits; row_cols [n_rows] = 128 * (listed blocks of the row).
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_indexer_paged_blocklist_fp8_logits(const void* q_fp8, const float* weights, const void* cache,
+                                               int32_t num_pages, int32_t page_size, const int32_t* context_lens,
+                                               const int32_t* block_table, int64_t block_table_stride,
+                                               const int32_t* row_table, int32_t n_rows, int32_t next_n,
+                                               const int32_t* block_list, int64_t block_list_stride,
+                                               const int32_t* row_cols, int32_t max_cols, float out_scale,
+                                               float* logits, int64_t logits_stride, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Fused decode selection: the same scores as b200dsa_indexer_paged_fp8_logits and, from them, the
  * top-k key positions of every row, in two launches and without a pass over the logits.  The
  * indexer's epilogue appends every score at or above a floor (taken from the first tiles each CTA

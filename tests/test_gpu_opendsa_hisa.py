@@ -132,3 +132,41 @@ def test_hisa_equals_dense_when_every_block_is_kept():
     dense = D.indexer_select_topk(q.cuda(), k.cuda(), w.cuda(), torch.tensor([0, S]).cuda(), 256,
                                   q_global_pos=(ke - 1))
     assert torch.equal(torch.sort(idx, 1).values, torch.sort(dense, 1).values)
+
+
+def test_hisa_paged_fp8_two_stage_vs_oracle():
+    """HISA over the paged FP8 cache (decode rows, two rows per request): block selection and token
+    selection against the oracle's two-stage restatement on the dequantised keys.  Power-of-two key scales
+    make the dequantised keys exact in bf16, so both sides pool and score identical numbers."""
+    from transarch_b200 import _lib, kernels as K
+    from transarch_b200.hisa import HisaConfig, hisa_select_topk_paged
+    P, ctxs, next_n = 64, [9000, 2500, 16384, 130], 2
+    g = torch.Generator().manual_seed(21)
+    qs = [O.quant_fp8_rows(torch.randn(c, 128, generator=g), ue8m0=True) for c in ctxs]
+    n_pages = sum((c + P - 1) // P for c in ctxs) + 4
+    cache, table = O.pack_paged_fp8_cache([a for a, _ in qs], [b for _, b in qs], P, n_pages, g)
+    table = table.clamp(min=0)
+    rows = len(ctxs) * next_n
+    q = torch.randn(rows, 64, 128, generator=g)
+    w = torch.randn(rows, 64, generator=g) / 8
+    q_fp8, wf = O.quant_q_fold_weights(q, w, 128 ** -0.5, ue8m0=True)
+    lens = torch.tensor(ctxs, dtype=torch.int32)
+    row_ctx = (lens.view(-1, 1) - next_n + torch.arange(next_n, dtype=torch.int32).view(1, -1) + 1).reshape(-1)
+    cfg = HisaConfig(hisa_block_topk=8, index_topk=256)
+    idx, blocks = hisa_select_topk_paged(q_fp8.cuda(), wf.cuda(), cache.cuda(), P, row_ctx.cuda(), table.cuda(), cfg,
+                                         next_n=next_n, return_blocks=True)
+    assert _lib.read_status(idx.device) == 0
+    idx, blocks = idx.cpu(), blocks.cpu()
+    for r in range(rows):
+        b, n = r // next_n, int(row_ctx[r])
+        kd = (qs[b][0].float() * qs[b][1].unsqueeze(-1))[:n].bfloat16()
+        ks, ke = torch.zeros(1, dtype=torch.int64), torch.tensor([n])
+        qf, wr = q_fp8[r:r + 1].float(), wf[r:r + 1]
+        blk_scores = O.finite_top(O.hisa_block_logits(qf, O.block_mean_pool(kd, 128), wr, ks, ke, 128, 1.0))
+        ref_blocks = O.topk_rows(O.hisa_block_logits(qf, O.block_mean_pool(kd, 128), wr, ks, ke, 128, 1.0), 8,
+                                 keep_pos_inf=True)
+        O.assert_selection_parity(blocks[r:r + 1], ref_blocks, blk_scores, BF16_RTOL, what=f"row {r} blocks")
+        ref2, tok_scores = O.hisa_select_topk(qf, kd, wr, ks, ke, block=128, block_topk=8, topk=256, sm_scale=1.0,
+                                              blocks=blocks[r:r + 1], return_scores=True)
+        O.assert_selection_parity(idx[r:r + 1], ref2, tok_scores, 1e-3, what=f"row {r} tokens")
+        assert int(blocks[r, 0]) == (n + 127) // 128 - 1          # the row's last block is always kept

@@ -159,3 +159,36 @@ def test_clean_and_force_keep_masks_against_tilelang():
     _run_ref(kern, ref, bks, bke)
     assert mine.shape[1] == 4096 and pooled.shape[0] == 4096
     assert torch.equal(mine, ref)
+
+
+def test_paged_block_sparse_logits_against_tilelang():
+    """paged_block_sparse_mqa_attn_return_logits (block_ops.py:151-379): token logits inside listed
+    128-key blocks of the paged cache."""
+    _, RB = _ref_modules()
+    from transarch_b200 import kernels as K
+    P, ctxs, m = 64, [3000, 700, 4096], 8
+    g = torch.Generator().manual_seed(46)
+    qs = [O.quant_fp8_rows(torch.randn(c, 128, generator=g), ue8m0=True) for c in ctxs]
+    n_pages = sum((c + P - 1) // P for c in ctxs) + 5
+    cache, table = O.pack_paged_fp8_cache([a for a, _ in qs], [b for _, b in qs], P, n_pages, g)
+    table = table.clamp(min=0)
+    B = len(ctxs)
+    q = torch.randn(B, 64, 128, generator=g)
+    w = torch.randn(B, 64, generator=g) / 8
+    q_fp8, wf = O.quant_q_fold_weights(q, w, 128 ** -0.5, 64 ** -0.5, ue8m0=True)
+    wf = wf.bfloat16().float()
+    lens = torch.tensor(ctxs, dtype=torch.int32)
+    blocks = torch.stack([torch.randperm((c + 127) // 128, generator=g)[:m] if (c + 127) // 128 >= m else
+                          torch.cat([torch.randperm((c + 127) // 128, generator=g),
+                                     torch.full((m - (c + 127) // 128,), 0, dtype=torch.long)]) for c in ctxs]).to(torch.int32)
+    keys_bf16 = O.unpack_paged_fp8_cache(cache, P).bfloat16().view(n_pages, P, 1, 128).cuda()
+    ref = _run_ref(RB.paged_block_sparse_mqa_attn_return_logits_interface, q_fp8.bfloat16().view(B, 1, 64, 128).cuda(),
+                   keys_bf16, blocks.view(B, 1, m).cuda(), 128, wf.bfloat16().cuda(), lens.cuda(), table.cuda())
+    row_cols = torch.full((B,), m * 128, dtype=torch.int32)
+    mine = K.indexer_paged_blocklist_fp8_logits(q_fp8.cuda(), wf.cuda(), cache.cuda(), P, lens.cuda(), table.cuda(),
+                                                blocks.cuda(), row_cols.cuda())
+    ref = ref.float().view(B, m * 128).cpu()
+    mine = mine.cpu()
+    assert torch.equal(torch.isinf(ref), torch.isinf(mine))
+    fin = torch.isfinite(ref)
+    assert float((ref[fin] - mine[fin]).abs().max() / mine[fin].pow(2).mean().sqrt()) < BF16_RTOL

@@ -29,6 +29,8 @@ SIGNATURES = {
                                          _vp, _vp, _i64, _vp],
     "b200dsa_indexer_paged_fp8_logits": [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _f32,
                                          _vp, _i64, _vp, _vp, _vp, _vp],
+    "b200dsa_indexer_paged_blocklist_fp8_logits": [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _vp, _i32, _i32, _vp, _i64,
+                                                   _vp, _i32, _f32, _vp, _i64, _vp, _vp],
     "b200dsa_indexer_paged_fp8_topk": [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _f32,
                                        _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp],
     "b200dsa_indexer_blocklist_bf16_logits": [_vp, _vp, _vp, _i32, _vp, _i64, _vp, _vp, _vp, _i32, _i32, _f32,

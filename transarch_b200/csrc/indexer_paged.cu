@@ -82,6 +82,11 @@ struct PagedIndexerParams {
   const uint64_t* head_mask;    // nullable [n_rows]: bit h set = head h counts towards logits_gated
   float* logits_gated;          // nullable [n_rows, logits_stride]: the same sum over the masked heads only
   int32_t* status;
+  // fp8 mode over per-row lists of 128-key logical blocks (HISA stage 2 on the paged cache): tile t of
+  // row r scores keys [128 b, 128 b + 128) of the row's request, b = klist[r * klist_stride + t], found
+  // through the block table; keys at or beyond pos_hi[r] (the context length) are masked
+  const int32_t* klist;
+  int64_t klist_stride;
   // fused selection (kEmit kernels only)
   uint64_t* cand;               // [n_rows, kEmitCap] composites (ordered score << 32 | ~position)
   int32_t* cand_count;          // [n_rows] entries appended (may exceed kEmitCap: list unusable)
@@ -226,10 +231,22 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       if (!__all_sync(0xffffffffu, oke)) break;
       uint8_t* dst = stage_mem + s * Cfg::kStageBytes;
       const int key0 = t * kTileKeys;
-      const int nkeys = min(kTileKeys, cols - key0);
-      const int first = key0 >> p_shift;
+      int nkeys = min(kTileKeys, cols - key0);
+      int first = key0 >> p_shift;
+      bool listed = false;
+      if constexpr (kFp8) listed = p.klist != nullptr;
+      if (listed) {
+        // the tile is logical block b of the request: its pages, as far as the context reaches
+        const int b = p.klist[static_cast<int64_t>(row) * p.klist_stride + t];
+        const int hi = p.pos_hi[row];
+        nkeys = (b < 0) ? 0 : max(0, min(kTileKeys, hi - b * kTileKeys));
+        first = (b < 0 ? 0 : b) * (kTileKeys >> p_shift);
+        tbl_base = first;
+        const int e = first + lane;
+        tbl_entry = (lane < 4 && e < p.table_cols) ? trow[e] : -1;
+      }
       const int npages = (nkeys + P - 1) >> p_shift;
-      if (tbl_base < 0 || first < tbl_base || first + npages > tbl_base + 32) {
+      if (!listed && (tbl_base < 0 || first < tbl_base || first + npages > tbl_base + 32)) {
         tbl_base = first;
         const int e = tbl_base + lane;
         tbl_entry = (e < tbl_len) ? (p.table ? trow[e] : ident0 + e) : -1;
@@ -392,7 +409,8 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
         cols = max(0, min(p.row_cols[row], p.logits_cols));
         if (p.table)
           trow = p.table + static_cast<int64_t>(p.row_table ? p.row_table[row] : row / p.table_row_div) * p.table_stride;
-        if (p.pos_lo) { lo = p.pos_lo[row]; hi = p.pos_hi[row]; }
+        if (p.pos_lo) lo = p.pos_lo[row];
+        if (p.pos_hi) hi = p.pos_hi[row];
         if (dual) {
           const uint64_t hm = p.head_mask[row];
           hm0 = static_cast<uint32_t>(hm);
@@ -415,6 +433,11 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
         if (!__all_sync(0xffffffffu, sc_ready)) break;
         kscale = sc_mem[slot * kTileKeys + lane_base + lane];
         keep = keep && (kscale >= 0.0f);
+        if (p.klist) {
+          const int b = p.klist[static_cast<int64_t>(row) * p.klist_stride + t];
+          const int pos = b * kTileKeys + lane_base + lane;
+          keep = keep && b >= 0 && pos >= lo && pos < hi;
+        }
       } else {
         if (keep) {
           const int blk = p.table ? trow[t] : (lo >> 7) + t;
@@ -607,6 +630,12 @@ using namespace b200dsa;
 
 namespace b200dsa {
 
+struct ListArgs {            // per-row lists of 128-key logical blocks (fp8 paged mode)
+  const int32_t* klist = nullptr;
+  int64_t klist_stride = 0;
+  const int32_t* list_cols = nullptr;   // [n_rows] 128 * (number of listed blocks)
+};
+
 struct EmitArgs {
   uint64_t* cand = nullptr;
   int32_t* cand_count = nullptr;
@@ -621,7 +650,7 @@ int paged_fp8_launch(const char* who, const void* q_fp8, const float* weights, c
                      int64_t block_table_stride, const int32_t* row_table, int32_t n_rows, int32_t next_n,
                      int32_t max_cols, float out_scale, float* logits, int64_t logits_stride,
                      const uint64_t* head_mask, float* logits_gated, int32_t* status, const EmitArgs& em,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, const ListArgs& ls = ListArgs{}) {
   char msg[160];
   if (!q_fp8 || !weights || !cache || !context_lens || !block_table || !status || n_rows < 0 || next_n < 1 ||
       num_pages < 1 || max_cols < 0 || (logits && logits_stride < max_cols) || (!logits && !em.cand) ||
@@ -671,13 +700,18 @@ int paged_fp8_launch(const char* who, const void* q_fp8, const float* weights, c
     p.num_pages = num_pages;
     p.weights = weights + static_cast<int64_t>(r0) * kHeads;
     p.row_cols = context_lens + r0;
+    if (ls.klist) {
+      p.row_cols = ls.list_cols + r0;
+      p.klist = ls.klist + static_cast<int64_t>(r0) * ls.klist_stride;
+      p.klist_stride = ls.klist_stride;
+    }
     p.table = row_table ? block_table : block_table + static_cast<int64_t>(r0 / next_n) * block_table_stride;
     p.row_table = row_table ? row_table + r0 : nullptr;
     p.table_stride = block_table_stride;
     p.table_cols = static_cast<int32_t>(block_table_stride);
     p.table_row_div = next_n;
     p.pos_lo = nullptr;
-    p.pos_hi = nullptr;
+    p.pos_hi = ls.klist ? context_lens + r0 : nullptr;
     p.n_rows = nr;
     p.out_scale = out_scale;
     p.logits = logits ? logits + static_cast<int64_t>(r0) * logits_stride : nullptr;
@@ -726,6 +760,31 @@ int topk_select_from_lists(const float* scores, int64_t row_stride, int32_t n_ro
                            uint64_t* cand, int32_t* count, uint32_t* floor_bits, int32_t* out_idx, float* out_val,
                            int64_t out_stride, int32_t* status, const PeerLinkDev* push, int64_t push_off,
                            cudaStream_t stream);
+}
+
+extern "C" int b200dsa_indexer_paged_blocklist_fp8_logits(const void* q_fp8, const float* weights, const void* cache,
+                                                          int32_t num_pages, int32_t page_size,
+                                                          const int32_t* context_lens, const int32_t* block_table,
+                                                          int64_t block_table_stride, const int32_t* row_table,
+                                                          int32_t n_rows, int32_t next_n, const int32_t* block_list,
+                                                          int64_t block_list_stride, const int32_t* row_cols,
+                                                          int32_t max_cols, float out_scale, float* logits,
+                                                          int64_t logits_stride, int32_t* status, void* stream) {
+  if (n_rows == 0) return B200DSA_OK;
+  if (!logits || !block_list || !row_cols || block_list_stride < 0 || (max_cols & 127) ||
+      block_list_stride * 128 < max_cols) {
+    set_last_error("b200dsa_indexer_paged_blocklist_fp8_logits: bad argument (max_cols a multiple of 128, at most "
+                   "128 * block_list_stride)");
+    return B200DSA_EINVAL;
+  }
+  ListArgs ls;
+  ls.klist = block_list;
+  ls.klist_stride = block_list_stride;
+  ls.list_cols = row_cols;
+  return paged_fp8_launch("b200dsa_indexer_paged_blocklist_fp8_logits", q_fp8, weights, cache, num_pages, page_size,
+                          context_lens, block_table, block_table_stride, row_table, n_rows, next_n, max_cols, out_scale,
+                          logits, logits_stride, nullptr, nullptr, status, EmitArgs{}, static_cast<cudaStream_t>(stream),
+                          ls);
 }
 
 static int fused_topk(const char* who, const void* q_fp8, const float* weights, const void* cache, int32_t num_pages,

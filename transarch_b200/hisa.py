@@ -97,3 +97,59 @@ def hisa_select_topk(index_q, index_k, index_w, ks, ke, cfg: Optional[HisaConfig
                                              pos_hi=ke.to(torch.int32).contiguous(), out_scale=sf)
     idx = K.topk_select(logits, cfg.index_topk, col_end=row_cols, page_table=blocks, page_size=128, sorted=True)
     return (idx, blocks) if return_blocks else idx
+
+
+@torch.no_grad()
+def hisa_select_topk_paged(q_fp8: torch.Tensor, weights: torch.Tensor, cache: torch.Tensor, page_size: int,
+                           context_lens: torch.Tensor, block_table: torch.Tensor, cfg: Optional[HisaConfig] = None,
+                           *, next_n: int = 1, max_model_len: Optional[int] = None, return_blocks: bool = False):
+    """The two-stage HISA selection over the paged FP8 index-key cache (the serving layout): decode rows
+    score the block means of their request, keep the top-m 128-key blocks (the last one always), then score
+    tokens only inside those blocks, reading the FP8 pages in place.
+
+      q_fp8 [rows, 64, 128] e4m3 and weights [rows, 64] fp32 (query scale folded in), rows = requests * next_n
+      cache uint8 [num_pages, page_size*132], context_lens int32 [rows] (keys visible to each row),
+      block_table int32 [requests, max_pages]
+    Returns int32 [rows, index_topk] key positions inside the request (descending score, -1 padded).
+    Stage 2 follows the reference's paged block-sparse fragment (block_ops.py:151-379); pooling is its
+    paged_mean_pooling (:381-486)."""
+    cfg = cfg or HisaConfig()
+    if cfg.hisa_k_block_size != 128:
+        raise B200DSAError("hisa_k_block_size must be 128 (one block per tensor-core key tile)")
+    rows = q_fp8.shape[0]
+    n_req = rows // next_n
+    ctx = context_lens.to(torch.int32).contiguous()
+    dev = q_fp8.device
+    if max_model_len is None:
+        max_model_len = block_table.shape[1] * page_size
+    max_pool = ((max_model_len + 127) // 128 + 127) // 128 * 128         # pooled blocks per request, whole tiles
+    req_ctx = ctx.view(n_req, next_n).max(dim=1).values.contiguous()
+    pooled = K.paged_mean_pool_fp8(cache, page_size, req_ctx, block_table, 128, max_pool)
+    k_pooled = pooled.view(n_req * max_pool, 128).to(torch.bfloat16)
+    w = weights.to(torch.float32).contiguous()
+    qb = q_fp8.to(torch.bfloat16).contiguous()
+    # stage 1: row r reads the pooled set of its request (tiles req*max_pool/128 ...), block range [0, ceil(ctx/128))
+    req = torch.arange(rows, device=dev, dtype=torch.int32) // next_n
+    tiles = max_pool // 128
+    lists = (req.view(-1, 1) * tiles + torch.arange(tiles, device=dev, dtype=torch.int32).view(1, -1)).contiguous()
+    row_cols = torch.full((rows,), max_pool, dtype=torch.int32, device=dev)
+    base = req * max_pool
+    n_blk_ctx = (ctx + 127) // 128
+    logits = K.indexer_blocklist_bf16_logits(qb, w, k_pooled, lists, row_cols, pos_lo=base.contiguous(),
+                                             pos_hi=(base + n_blk_ctx).contiguous())
+    has = (n_blk_ctx > 0).view(-1, 1)
+    inf = torch.full((rows, 1), float("inf"), device=dev)
+    if cfg.keep_last_block:
+        col = (n_blk_ctx - 1).clamp(min=0).long().view(-1, 1)
+        logits.scatter_(1, col, torch.where(has, inf, logits.gather(1, col)))
+    if cfg.keep_first_block:
+        col = torch.zeros(rows, 1, dtype=torch.long, device=dev)
+        logits.scatter_(1, col, torch.where(has, inf, logits.gather(1, col)))
+    blocks = K.topk_select(logits, cfg.hisa_block_topk, keep_pos_inf=True, sorted=True)
+    # stage 2: tokens inside the kept blocks, straight from the FP8 pages
+    n_blk = (blocks >= 0).sum(dim=1).to(torch.int32)
+    tok_cols = (n_blk * 128).contiguous()
+    tok = K.indexer_paged_blocklist_fp8_logits(q_fp8, w, cache, page_size, ctx, block_table, blocks, tok_cols,
+                                               next_n=next_n)
+    idx = K.topk_select(tok, cfg.index_topk, col_end=tok_cols, page_table=blocks, page_size=128, sorted=True)
+    return (idx, blocks) if return_blocks else idx

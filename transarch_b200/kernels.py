@@ -201,6 +201,42 @@ def indexer_paged_fp8_logits(q_fp8: torch.Tensor, weights: torch.Tensor, cache: 
     return out if head_mask is None else (out, out_gated)
 
 
+def indexer_paged_blocklist_fp8_logits(q_fp8: torch.Tensor, weights: torch.Tensor, cache: torch.Tensor, page_size: int,
+                                       context_lens: torch.Tensor, block_table: torch.Tensor,
+                                       block_list: torch.Tensor, row_cols: torch.Tensor, *, next_n: int = 1,
+                                       out_scale: float = 1.0, row_table: Optional[torch.Tensor] = None,
+                                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Token logits [n_rows, 128*list_len] inside per-row lists of 128-key blocks of the paged FP8 cache
+    (-inf for unlisted / masked columns); see b200dsa_indexer_paged_blocklist_fp8_logits."""
+    require_cuda(q_fp8, weights, cache, context_lens, block_table, block_list, row_cols, row_table, out)
+    if q_fp8.dtype != torch.float8_e4m3fn or not q_fp8.is_contiguous() or q_fp8.shape[-2:] != (64, 128):
+        raise _lib.B200DSAError("q_fp8 must be contiguous float8_e4m3fn [..., 64, 128]")
+    n_rows = q_fp8.numel() // (64 * 128)
+    if weights.dtype != torch.float32 or not weights.is_contiguous() or weights.numel() != n_rows * 64:
+        raise _lib.B200DSAError("weights must be contiguous fp32 [n_rows, 64]")
+    if cache.dtype != torch.uint8 or not cache.is_contiguous() or cache.numel() % (page_size * 132):
+        raise _lib.B200DSAError("cache must be contiguous uint8 with page_size*(128+4) bytes per page")
+    num_pages = cache.numel() // (page_size * 132)
+    for t_, nm in ((context_lens, "context_lens"), (block_table, "block_table"), (block_list, "block_list"),
+                   (row_cols, "row_cols")):
+        _i32(t_, nm)
+    if block_list.dim() != 2 or block_list.shape[0] != n_rows or context_lens.numel() != n_rows or \
+            row_cols.numel() != n_rows:
+        raise _lib.B200DSAError("block_list must be [n_rows, list_len]; context_lens and row_cols one entry per row")
+    max_cols = block_list.shape[1] * 128
+    if out is None:
+        out = torch.full((n_rows, max_cols), NEG_INF, dtype=torch.float32, device=q_fp8.device)
+    elif out.dtype != torch.float32 or out.stride(1) != 1 or out.shape[0] < n_rows or out.shape[1] < max_cols:
+        raise _lib.B200DSAError("out must be fp32 [>=n_rows, >=128*list_len] with unit column stride")
+    rc = _lib.load().b200dsa_indexer_paged_blocklist_fp8_logits(
+        ptr(q_fp8), ptr(weights), ptr(cache), num_pages, page_size, ptr(context_lens), ptr(block_table),
+        block_table.stride(0), ptr(_i32(row_table, "row_table")), n_rows, next_n, ptr(block_list),
+        block_list.stride(0), ptr(row_cols), max_cols, out_scale, ptr(out), out.stride(0),
+        ptr(status_word(q_fp8.device)), stream_ptr())
+    check(rc, "b200dsa_indexer_paged_blocklist_fp8_logits")
+    return out
+
+
 def indexer_paged_fp8_topk(q_fp8: torch.Tensor, weights: torch.Tensor, cache: torch.Tensor, page_size: int,
                            context_lens: torch.Tensor, block_table: torch.Tensor, k: int,
                            scratch: Tuple[torch.Tensor, torch.Tensor], *, next_n: int = 1,
