@@ -430,6 +430,33 @@ int b200dsa_quant_q_fold_weights(const void* q_bf16, const float* w, int64_t n_r
                                  int32_t use_ue8m0, void* q_fp8, float* weights, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Elementwise tails of the indexer's projections, fused (the three dense projections themselves are
+ * plain GEMMs and stay with the BLAS library):
+ *
+ * keys:    k = RoPE(LayerNorm(wk(h))): LayerNorm over the 128 dims (weight, bias, eps), rotate-half
+ *          RoPE on 64 rope dims with per-token cos / sin [n_tokens, 64] fp32.  rope_first = 0: the rope
+ *          dims are the last 64 (OpenDSA/opendsa/modeling/indexer.py:70-79); 1: the first 64
+ *          (MISA_preprint/.../misa_deepseek_v2.py:232-250).  k_out (optional) receives the rows in the
+ *          input's dtype; with a cache the rows are also quantised (as b200dsa_indexer_k_quant_and_cache
+ *          would quantise their bf16 rounding) and stored at slot_mapping[t]: the cache insert fused with
+ *          norm + RoPE, no bf16 row round trip (the step before the selection path,
+ *          indexers.py:454-460).  ln_w / cos may be NULL to skip that stage.
+ * queries: RoPE on every (token, head) row of wq(q_in) [n_tokens, n_heads, 128]; q_out (optional) receives
+ *          the rows; with q_fp8 the rows are also quantised per (token, head) and weights[t,h] =
+ *          w[t,h] * scale * fold (misa_deepseek_v2.py:279-292 fused with the RoPE before it).
+ * in_f32: inputs (and row outputs) are fp32 instead of bf16.
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_indexer_k_norm_rope(const void* k_proj, int32_t in_f32, int64_t n_tokens, const float* ln_w,
+                                const float* ln_b, float ln_eps, const float* cos, const float* sin,
+                                int32_t rope_first, void* k_out, const int64_t* slot_mapping, void* cache,
+                                int64_t num_pages, int32_t page_size, int32_t use_ue8m0, int32_t* status,
+                                void* stream);
+int b200dsa_indexer_q_rope(const void* q_proj, int32_t in_f32, int64_t n_tokens, int32_t n_heads,
+                           const float* cos, const float* sin, int32_t rope_first, void* q_out,
+                           const float* w, float fold, int32_t use_ue8m0, void* q_fp8, float* weights,
+                           void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Block mean pooling of index keys: pooled[j] = mean(keys[j*block : min((j+1)*block, n)]),
  * fp32 accumulation, the tail block divided by its true length.
  * Replaces MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/block_ops.py:685-754

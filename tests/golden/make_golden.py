@@ -32,6 +32,32 @@ ATTEND_CASES = [
 ]
 
 
+# (name, seed, B, L, hidden, n_heads)
+INDEXER_CASES = [
+    ("lightning_indexer_fp32", 30, 2, 16, 32, 8),
+]
+
+
+def golden_inputs_indexer(seed, B, L, hidden, n_heads):
+    """Inputs and parameters of the indexer module, all from the seed (fp32): hidden states, rotary
+    cos / sin of real positions (rotate-half convention: both halves carry the same angles), and a state
+    dict with the reference's parameter names."""
+    g = torch.Generator().manual_seed(seed)
+    h = torch.randn(B, L, hidden, generator=g)
+    pos = torch.arange(L, dtype=torch.float32).view(1, L, 1) + torch.tensor([0.0, 100.0]).view(B, 1, 1)
+    inv = 10000.0 ** (-torch.arange(0, 32, dtype=torch.float32) / 32.0)
+    ang = torch.cat([pos * inv, pos * inv], dim=-1)
+    cos, sin = ang.cos(), ang.sin()
+    state = {
+        "wq.weight": torch.randn(n_heads * 128, hidden, generator=g) / hidden ** 0.5,
+        "wk.weight": torch.randn(128, hidden, generator=g) / hidden ** 0.5,
+        "k_norm.weight": 1.0 + 0.1 * torch.randn(128, generator=g),
+        "k_norm.bias": 0.1 * torch.randn(128, generator=g),
+        "w_proj.weight": torch.randn(n_heads, hidden, generator=g) / hidden ** 0.5,
+    }
+    return h, cos, sin, state
+
+
 def golden_inputs_select(seed, Lq, Lk, H, d, docs, mode):
     g = torch.Generator().manual_seed(seed)
     q = torch.randn(Lq, H, d, generator=g)
@@ -90,5 +116,22 @@ def main(ref_root: str):
         print(name, tuple(out.shape))
 
 
+def main_indexer(ref_root: str):
+    sys.path.insert(0, os.path.join(ref_root, "OpenDSA"))
+    from opendsa.modeling.indexer import LightningIndexer
+    for name, seed, B, L, hidden, n_heads in INDEXER_CASES:
+        h, cos, sin, state = golden_inputs_indexer(seed, B, L, hidden, n_heads)
+        mod = LightningIndexer(hidden, n_heads=n_heads, head_dim=128, rope_dim=64, dtype=torch.float32)
+        mod.load_state_dict(state)
+        with torch.no_grad():
+            q, k, w = mod(h, h, cos, sin)
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), q=q.numpy(), k=k.numpy(), w=w.numpy())
+        print(name, tuple(q.shape), tuple(k.shape), tuple(w.shape))
+
+
 if __name__ == "__main__":
+    if len(sys.argv) > 2 and sys.argv[2] == "indexer":
+        main_indexer(sys.argv[1])
+        sys.exit(0)
     main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TRANSARCH_ROOT", "."))
+    main_indexer(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TRANSARCH_ROOT", "."))

@@ -629,3 +629,70 @@ def mma_peak_tflops(fp8: bool = True, *, iters: int = 4096, reps: int = 5, devic
         flops = ctas * iters * 8 * 2.0 * 128 * 256 * (32 if fp8 else 16)
         best = max(best, flops / (e0.elapsed_time(e1) * 1e-3) / 1e12)
     return best
+
+
+def _f32c(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    return None if t is None else t.to(torch.float32).contiguous()
+
+
+def indexer_k_norm_rope(k_proj: torch.Tensor, ln_weight: Optional[torch.Tensor], ln_bias: Optional[torch.Tensor],
+                        eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], *,
+                        rope_first: bool = False, want_rows: bool = True, cache: Optional[torch.Tensor] = None,
+                        slot_mapping: Optional[torch.Tensor] = None, page_size: int = 64,
+                        scale_fmt: Optional[str] = None) -> Optional[torch.Tensor]:
+    """k = RoPE(LayerNorm(k_proj)) for rows [n_tokens, 128] (bf16 or fp32); see b200dsa_indexer_k_norm_rope.
+    Returns the rows (input dtype) unless want_rows=False; with `cache` + `slot_mapping` the rows are also
+    quantised and written into their cache slots in the same kernel."""
+    require_cuda(k_proj, ln_weight, ln_bias, cos, sin, cache, slot_mapping)
+    if k_proj.dtype not in (torch.bfloat16, torch.float32) or not k_proj.is_contiguous() or k_proj.shape[-1] != 128:
+        raise _lib.B200DSAError("k_proj must be contiguous bf16 or fp32 [..., 128]")
+    if scale_fmt not in (None, "ue8m0"):
+        raise _lib.B200DSAError(f"unknown scale_fmt {scale_fmt!r} (None or 'ue8m0')")
+    n = k_proj.numel() // 128
+    lw, lb, c, s_ = _f32c(ln_weight), _f32c(ln_bias), _f32c(cos), _f32c(sin)
+    if c is not None and (c.numel() != n * 64 or s_.numel() != n * 64):
+        raise _lib.B200DSAError("cos / sin must hold 64 values per token")
+    out = torch.empty_like(k_proj) if want_rows else None
+    num_pages = 0
+    if cache is not None:
+        if cache.dtype != torch.uint8 or not cache.is_contiguous() or slot_mapping is None or \
+                slot_mapping.dtype != torch.int64 or slot_mapping.numel() != n:
+            raise _lib.B200DSAError("cache must be contiguous uint8 and slot_mapping int64 with one entry per token")
+        num_pages = cache.numel() // (page_size * 132)
+    rc = _lib.load().b200dsa_indexer_k_norm_rope(
+        ptr(k_proj), int(k_proj.dtype == torch.float32), n, ptr(lw), ptr(lb), eps, ptr(c), ptr(s_), int(rope_first),
+        ptr(out), ptr(slot_mapping), ptr(cache), num_pages, page_size, int(scale_fmt == "ue8m0"),
+        ptr(status_word(k_proj.device)), stream_ptr())
+    check(rc, "b200dsa_indexer_k_norm_rope")
+    return out
+
+
+def indexer_q_rope(q_proj: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], *,
+                   rope_first: bool = False, want_rows: bool = True, w: Optional[torch.Tensor] = None,
+                   fold: float = 1.0, ue8m0: bool = False):
+    """RoPE on the rows of q_proj [n_tokens, n_heads, 128] (bf16 or fp32); see b200dsa_indexer_q_rope.
+    Returns the rows, or with `w` [n_tokens, n_heads] (rows, q_fp8, weights) / (q_fp8, weights): the FP8
+    quantisation with the scale folded into the head weights, from the same kernel."""
+    require_cuda(q_proj, cos, sin, w)
+    if q_proj.dtype not in (torch.bfloat16, torch.float32) or not q_proj.is_contiguous() or q_proj.dim() != 3 or \
+            q_proj.shape[-1] != 128:
+        raise _lib.B200DSAError("q_proj must be contiguous bf16 or fp32 [n_tokens, n_heads, 128]")
+    T, H, _ = q_proj.shape
+    c, s_ = _f32c(cos), _f32c(sin)
+    if c is not None and (c.numel() != T * 64 or s_.numel() != T * 64):
+        raise _lib.B200DSAError("cos / sin must hold 64 values per token")
+    out = torch.empty_like(q_proj) if want_rows else None
+    q_fp8 = weights = wc = None
+    if w is not None:
+        wc = w.to(torch.float32).contiguous()
+        if wc.numel() != T * H:
+            raise _lib.B200DSAError("w must hold one weight per (token, head)")
+        q_fp8 = torch.empty(T, H, 128, dtype=torch.float8_e4m3fn, device=q_proj.device)
+        weights = torch.empty(T, H, dtype=torch.float32, device=q_proj.device)
+    rc = _lib.load().b200dsa_indexer_q_rope(
+        ptr(q_proj), int(q_proj.dtype == torch.float32), T, H, ptr(c), ptr(s_), int(rope_first), ptr(out), ptr(wc),
+        fold, int(bool(ue8m0)), ptr(q_fp8), ptr(weights), stream_ptr())
+    check(rc, "b200dsa_indexer_q_rope")
+    if w is None:
+        return out
+    return (out, q_fp8, weights) if want_rows else (q_fp8, weights)
