@@ -310,6 +310,16 @@ int b200dsa_sparse_mla_decode_signal(const void* q_bf16, const void* kv_bf16, in
                                      const b200dsa_peer_link* link, int32_t* ticket, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Value up-projection of the latent-space context, the step right after the attention kernel:
+ *   out[t, h, v] = sum_l ctx[t, h, l] * W_UV[h, v, l]        (a tcgen05 GEMM per head, K = 512)
+ * Replaces the einsum at OpenDSA/opendsa/ops/sparse_mla.py:44 ("thl,hvl->thv").
+ *   ctx_bf16 [n_tokens, n_heads, 512] bf16 (what b200dsa_sparse_mla_decode writes with ctx_bf16 = 1),
+ *   w_uv_bf16 [n_heads, dv, 512] bf16, 1 <= dv <= 256, out [n_tokens, n_heads, dv] bf16 or fp32.
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_wuv_up_project(const void* ctx_bf16, const void* w_uv_bf16, int32_t n_tokens, int32_t n_heads,
+                           int32_t dv, void* out, int32_t out_f32, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Merge attention partials computed over disjoint key sets (key shards of several GPUs, or
  * splits on one GPU):  out = sum_r exp(lse_r - m) ctx_r / sum_r exp(lse_r - m),
  * lse_out = m + log(sum_r exp(lse_r - m)),  m = max_r lse_r.  No counterpart call in the

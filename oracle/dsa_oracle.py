@@ -49,6 +49,33 @@ def prepare_ks_ke_cp(cu_full: torch.Tensor, q_global_pos: torch.Tensor):
 
 
 # --------------------------------------------------------------------------- #
+# the indexer's producer: projections, key LayerNorm, RoPE
+# --------------------------------------------------------------------------- #
+def rope_rotate_half(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x * cos + rotate_half(x) * sin on the last dim (64 rope dims).
+    OpenDSA/opendsa/modeling/indexer.py:27-37."""
+    half = x.shape[-1] // 2
+    rot = torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+    return x * cos + rot * sin
+
+
+def lightning_indexer_forward(h, q_in, cos, sin, state, n_heads: int, head_dim: int = 128, rope_dim: int = 64,
+                              ln_eps: float = 1e-5):
+    """q = wq(q_in) [B,L,H,d]; k = LayerNorm(wk(h)) [B,L,d]; RoPE on the LAST rope_dim dims of both;
+    w = w_proj(h) * H^-0.5.  OpenDSA/opendsa/modeling/indexer.py:64-83.  `state` holds the module's
+    parameters under its own names."""
+    B, L, _ = h.shape
+    q = (q_in.float() @ state["wq.weight"].float().T).view(B, L, n_heads, head_dim)
+    k = torch.nn.functional.layer_norm(h.float() @ state["wk.weight"].float().T, (head_dim,),
+                                       state["k_norm.weight"].float(), state["k_norm.bias"].float(), ln_eps)
+    d0 = head_dim - rope_dim
+    q = torch.cat([q[..., :d0], rope_rotate_half(q[..., d0:], cos.unsqueeze(2), sin.unsqueeze(2))], dim=-1)
+    k = torch.cat([k[..., :d0], rope_rotate_half(k[..., d0:], cos, sin)], dim=-1)
+    w = (h.float() @ state["w_proj.weight"].float().T) * n_heads ** -0.5
+    return q, k, w
+
+
+# --------------------------------------------------------------------------- #
 # lightning-indexer score and top-k
 # --------------------------------------------------------------------------- #
 def indexer_scores(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor,

@@ -129,3 +129,18 @@ def test_out_of_range_row_is_skipped_and_reported():
     K.sparse_mla_decode(q.cuda(), kv.cuda(), good.cuda(), scale)
     torch.cuda.synchronize()
     assert _lib.read_status(dev) == 0
+
+
+@pytest.mark.parametrize("T,H,dv", [(64, 128, 128), (200, 16, 96), (5, 8, 8), (129, 3, 256)])
+def test_wuv_up_projection_matches_einsum(T, H, dv):
+    """out[t,h,:] = ctx[t,h,:] @ W_UV[h]^T (OpenDSA/opendsa/ops/sparse_mla.py:44) on tensor cores."""
+    from transarch_b200 import _lib, kernels as K
+    g = torch.Generator().manual_seed(T + dv)
+    ctx = torch.randn(T, H, 512, generator=g).bfloat16()
+    w = (torch.randn(H, dv, 512, generator=g) / 512 ** 0.5).bfloat16()
+    ref = torch.einsum("thl,hvl->thv", ctx.float(), w.float())
+    out32 = K.wuv_up_project(ctx.cuda(), w.cuda(), out_dtype=torch.float32)
+    out16 = K.wuv_up_project(ctx.cuda(), w.cuda())
+    assert _lib.read_status(out32.device) == 0
+    assert (out32.cpu() - ref).abs().max() < 1e-4 * ref.abs().max()        # bf16 products are exact in fp32
+    assert (out16.float().cpu() - ref).abs().max() < 1e-2 * ref.abs().max()

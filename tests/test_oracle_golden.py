@@ -94,3 +94,16 @@ def test_block_mean_pool_tail():
     k = torch.arange(10, dtype=torch.float32).view(10, 1).repeat(1, 4)
     p = O.block_mean_pool(k, 4)
     assert torch.allclose(p[:, 0], torch.tensor([1.5, 5.5, 8.5]))
+
+
+def test_indexer_producer_matches_reference_module():
+    """The oracle's restatement of LightningIndexer.forward against the stored outputs of the
+    reference module (tests/golden/make_golden.py, fp32)."""
+    from tests.golden.make_golden import INDEXER_CASES, golden_inputs_indexer
+    name, seed, B, L, hidden, H = INDEXER_CASES[0]
+    h, cos, sin, state = golden_inputs_indexer(seed, B, L, hidden, H)
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", name + ".npz"))
+    q, k, w = O.lightning_indexer_forward(h, h, cos, sin, state, H)
+    for got, key in ((q, "q"), (k, "k"), (w, "w")):
+        want = torch.from_numpy(g[key])
+        assert got.shape == want.shape and (got - want).abs().max() < 1e-5 * want.abs().max().clamp_min(1.0)

@@ -696,3 +696,25 @@ def indexer_q_rope(q_proj: torch.Tensor, cos: Optional[torch.Tensor], sin: Optio
     if w is None:
         return out
     return (out, q_fp8, weights) if want_rows else (q_fp8, weights)
+
+
+def wuv_up_project(ctx: torch.Tensor, w_uv: torch.Tensor, *, out_dtype: torch.dtype = torch.bfloat16,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t,h,:] = ctx[t,h,:] @ W_UV[h]^T: ctx bf16 [T, H, 512], W_UV bf16 [H, Dv, 512] -> [T, H, Dv];
+    see b200dsa_wuv_up_project."""
+    require_cuda(ctx, w_uv, out)
+    if ctx.dtype != torch.bfloat16 or not ctx.is_contiguous() or ctx.dim() != 3 or ctx.shape[2] != 512:
+        raise _lib.B200DSAError("ctx must be contiguous bf16 [n_tokens, n_heads, 512]")
+    T, H, _ = ctx.shape
+    if w_uv.dtype != torch.bfloat16 or not w_uv.is_contiguous() or w_uv.dim() != 3 or w_uv.shape[0] != H or \
+            w_uv.shape[2] != 512 or not 1 <= w_uv.shape[1] <= 256:
+        raise _lib.B200DSAError("W_UV must be contiguous bf16 [n_heads, dv <= 256, 512]")
+    dv = w_uv.shape[1]
+    if out is None:
+        out = torch.empty(T, H, dv, dtype=out_dtype, device=ctx.device)
+    if out.dtype not in (torch.bfloat16, torch.float32) or not out.is_contiguous() or out.shape != (T, H, dv):
+        raise _lib.B200DSAError("out must be contiguous bf16 or fp32 [n_tokens, n_heads, dv]")
+    rc = _lib.load().b200dsa_wuv_up_project(ptr(ctx), ptr(w_uv), T, H, dv, ptr(out), int(out.dtype == torch.float32),
+                                            ptr(status_word(ctx.device)), stream_ptr())
+    check(rc, "b200dsa_wuv_up_project")
+    return out

@@ -123,13 +123,17 @@ def indexer_select_topk(index_q, index_k, index_w, cu_seqlens, topk, *, sm_scale
 
 
 @torch.no_grad()
-def sparse_attend_latent(q_lat, latent, indices, *, sm_scale: float, q_pos: Optional[torch.Tensor] = None):
-    """Latent-space context and log-sum-exp: (ctx fp32 [L,H,512], lse fp32 [L,H])."""
+def sparse_attend_latent(q_lat, latent, indices, *, sm_scale: float, q_pos: Optional[torch.Tensor] = None,
+                         ctx_dtype: torch.dtype = torch.float32):
+    """Latent-space context and log-sum-exp: (ctx [L,H,512] fp32 or bf16, lse fp32 [L,H])."""
     if q_lat.shape[-1] != 576 or latent.shape[-1] != 576:
         raise B200DSAError("latent width must be 576 (512 value dims + 64 rope dims)")
+    ctx = None
+    if ctx_dtype == torch.bfloat16:
+        ctx = torch.empty(q_lat.shape[0], q_lat.shape[1], 512, dtype=torch.bfloat16, device=q_lat.device)
     return K.sparse_mla_decode(q_lat.to(torch.bfloat16).contiguous(), latent.to(torch.bfloat16).contiguous(),
                                indices.to(torch.int32).contiguous(), sm_scale,
-                               q_pos=None if q_pos is None else q_pos.to(torch.int32).contiguous())
+                               q_pos=None if q_pos is None else q_pos.to(torch.int32).contiguous(), ctx=ctx)
 
 
 def sparse_attend_absorbed_chunked(q_lat, latent, W_UV, indices, *, d_c: int, sm_scale: float, cu_seqlens=None,
@@ -148,8 +152,13 @@ def sparse_attend_absorbed_chunked(q_lat, latent, W_UV, indices, *, d_c: int, sm
         q_pos = prepare_ks_ke(cu_seqlens)[1] - 1
     else:
         q_pos = torch.arange(L, device=q_lat.device)
-    ctx, _ = sparse_attend_latent(q_lat, latent, indices, sm_scale=sm_scale, q_pos=q_pos)
-    return torch.einsum("thl,hvl->thv", ctx.to(W_UV.dtype), W_UV)
+    # bf16 context straight from the attention kernel, then the per-head up-projection on tensor cores
+    ctx, _ = sparse_attend_latent(q_lat, latent, indices, sm_scale=sm_scale, q_pos=q_pos, ctx_dtype=torch.bfloat16)
+    if W_UV.shape[1] > 256:
+        return torch.einsum("thl,hvl->thv", ctx.to(W_UV.dtype), W_UV)
+    out_dtype = W_UV.dtype if W_UV.dtype in (torch.bfloat16, torch.float32) else torch.float32
+    out = K.wuv_up_project(ctx, W_UV.to(torch.bfloat16).contiguous(), out_dtype=out_dtype)
+    return out.to(W_UV.dtype)
 
 
 def patch_opendsa() -> None:
