@@ -211,6 +211,9 @@ def bench_configs(dev, peaks, threads: int, fp8_peak: float):
     cu = torch.tensor([0, T])
     qd, kd, wd, cud = q.to(dev).bfloat16(), k.to(dev).bfloat16(), w.to(dev), cu.to(dev)
     med, mn = _time_call(lambda: opendsa_ops.indexer_select_topk(qd, kd, wd, cud, 2048), flush)
+    med_u, _ = _time_call(lambda: opendsa_ops.indexer_select_topk(qd, kd, wd, cud, 2048, sorted=False), flush)
+    ksd, ked = opendsa_ops.prepare_ks_ke(cud, total=T)
+    med_l, _ = _time_call(lambda: opendsa_ops.indexer_logits_flat(qd, kd, wd, ksd, ked, 128 ** -0.5), flush)
     t0 = time.perf_counter()
     (ref.indexer_select_topk if ref is not None else O.indexer_select_topk)(q, k, w, cu, 2048, q_chunk=512)
     cpu_s = time.perf_counter() - t0
@@ -218,7 +221,9 @@ def bench_configs(dev, peaks, threads: int, fp8_peak: float):
     out["C1 causal prefill select T=S=4096 k=2048 (bf16)"] = {
         "call": "opendsa_ops.indexer_select_topk", "us_median": med, "us_min": mn, "flops": flops,
         "bytes": 103e6, "bound": "tensor", "achieved_tflops": flops / med / 1e6,
-        "frac_of_bf16_sustained": flops / med / 1e6 / bf16, "cpu_seconds": cpu_s,
+        "frac_of_bf16_sustained": flops / med / 1e6 / bf16, "us_median_unsorted_output": med_u,
+        "us_median_logits_only": med_l, "logits_only_frac_of_bf16_sustained": flops / med_l / 1e6 / bf16,
+        "cpu_seconds": cpu_s,
         "cpu_kind": "reference" if ref is not None else "port", "cpu_sample": "whole configuration, fp32, q_chunk=512"}
     del qd, kd, wd
 

@@ -271,6 +271,24 @@ int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const float* weigh
                                           float* logits_gated, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Prefill token logits over flat bf16 keys with per-query intervals (tcgen05, four queries per key tile):
+ *   column c of row r is key position col0[r] + c, col0[r] = 128 * (pos_lo[r] / 128);
+ *   logits[r, c] = out_scale * sum_h weights[r,h]*relu(<q[r,h,:], keys[pos,:]>) for pos_lo[r] <= pos <
+ *   pos_hi[r], -inf for the other columns c < row_cols[r]; columns beyond row_cols[r] are left untouched.
+ * Replaces the score + mask steps of OpenDSA/opendsa/ops/topk_select.py:57-65 and
+ * MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/misa_ops.py:415-515 (T1) without the fp32
+ * [chunk, 64, Lk] intermediate.  Consecutive queries share each key tile (N = 256 per MMA), so keys are
+ * fetched once per four queries.
+ *   q_bf16 [n_rows, 64, 128], keys_bf16 [n_keys, 128] (16-byte aligned), weights [n_rows, 64] fp32,
+ *   row_cols [n_rows] = 128 * ceil(pos_hi/128) - col0 (a multiple of 128).
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_indexer_flat_bf16_logits(const void* q_bf16, const float* weights, const void* keys_bf16,
+                                     int32_t n_keys, const int32_t* pos_lo, const int32_t* pos_hi,
+                                     const int32_t* row_cols, int32_t n_rows, int32_t max_cols,
+                                     float out_scale, float* logits, int64_t logits_stride,
+                                     int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Sparse MLA attention over selected keys in the absorbed latent space (tcgen05), one query
  * token per item; emits the latent-space context and the log-sum-exp so that partial results
  * over disjoint key sets can be merged.

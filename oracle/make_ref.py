@@ -11,6 +11,9 @@ package imports it.
 Installed:
   oracle/_ref/opendsa/ops/{topk_select,sparse_mla,flashkl_warmup}.py   <- OpenDSA/opendsa/ops/
       indexer_select_topk, sparse_attend_absorbed_chunked, prepare_ks_ke[_cp]: what the CPU baseline times
+  oracle/_ref/opendsa/{modeling,dist}/*.py                             <- OpenDSA/opendsa/{modeling,dist}/
+      the attention module that binds the two ops by name (the target of patch_opendsa()) and the
+      LightningIndexer module (torch only)
   oracle/_ref/misa_vllm_patch/{misa_ops,block_ops}.py                  <- MISA_preprint/misa_vllm_patch_2stage/
       the TileLang kernels (torch + tilelang only), for a GPU-side comparator where TileLang can run them
 """
@@ -29,6 +32,14 @@ FILES = [
     ("OpenDSA/opendsa/ops/flashkl_warmup.py", "opendsa/ops/flashkl_warmup.py"),
     ("OpenDSA/opendsa/ops/__init__.py", "opendsa/ops/__init__.py"),
     ("OpenDSA/opendsa/__init__.py", "opendsa/__init__.py"),
+    # the modules that bind the two ops by name at import (what patch_opendsa() rebinds) and the indexer module
+    ("OpenDSA/opendsa/modeling/__init__.py", "opendsa/modeling/__init__.py"),
+    ("OpenDSA/opendsa/modeling/dsa_attention.py", "opendsa/modeling/dsa_attention.py"),
+    ("OpenDSA/opendsa/modeling/indexer.py", "opendsa/modeling/indexer.py"),
+    ("OpenDSA/opendsa/modeling/patch_deepseek.py", "opendsa/modeling/patch_deepseek.py"),
+    ("OpenDSA/opendsa/modeling/ep_moe.py", "opendsa/modeling/ep_moe.py"),
+    ("OpenDSA/opendsa/dist/__init__.py", "opendsa/dist/__init__.py"),
+    ("OpenDSA/opendsa/dist/pg.py", "opendsa/dist/pg.py"),
     ("MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/misa_ops.py", "misa_vllm_patch/misa_ops.py"),
     ("MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/block_ops.py", "misa_vllm_patch/block_ops.py"),
 ]

@@ -88,3 +88,35 @@ def test_blocklist_bf16_logits():
             ref[t, j * 128:(j + 1) * 128][ok] = full[t, pos[ok]]
     assert torch.equal(torch.isfinite(out), torch.isfinite(ref))
     assert O.rel_err(out, ref) < BF16_RTOL
+
+
+def test_flat_prefill_groups_of_four_queries_match_the_per_query_kernel():
+    """The prefill kernel (four queries per key tile) against the per-query block-list kernel on packed
+    documents with ragged intervals, a row count that is not a multiple of four, empty rows and key counts
+    that are not a multiple of 128: identical -inf pattern, scores equal up to fp32 summation order."""
+    from transarch_b200 import _lib, kernels as K
+    g = torch.Generator().manual_seed(91)
+    T, S = 203, 5000 + 37
+    q = torch.randn(T, 64, 128, generator=g).bfloat16().cuda()
+    k = torch.randn(S, 128, generator=g).bfloat16().cuda()
+    w = (torch.randn(T, 64, generator=g) / 8).cuda()
+    lo = torch.randint(0, 3000, (T,), generator=g, dtype=torch.int32)
+    hi = (lo + torch.randint(1, 2000, (T,), generator=g, dtype=torch.int32)).clamp(max=S)
+    hi[5] = lo[5]                                             # an empty interval
+    lo[6], hi[6] = 0, S                                       # the whole key range
+    lo, hi = lo.cuda(), hi.cuda()
+    col0 = (lo >> 7) << 7
+    row_cols = ((((hi + 127) >> 7) << 7) - col0).clamp(min=0).contiguous()
+    cols = (S + 127) // 128 * 128
+    ref = K.indexer_blocklist_bf16_logits(q, w, k, None, row_cols, pos_lo=lo, pos_hi=hi, out_scale=0.5, max_cols=cols)
+    got = K.indexer_flat_bf16_logits(q, w, k, lo, hi, row_cols, cols, out_scale=0.5)
+    assert _lib.read_status(q.device) == 0
+    assert torch.equal(torch.isinf(got), torch.isinf(ref))
+    fin = torch.isfinite(ref)
+    assert (got[fin] - ref[fin]).abs().max() < 1e-5 * ref[fin].abs().max()
+    # and against the oracle on a few rows
+    for r in (0, 6, 100, 202):
+        sc = O.indexer_scores(q[r:r + 1].cpu().float(), k.cpu().float(), w[r:r + 1].cpu(), 0.5)[0]
+        a, b = int(lo[r]), int(hi[r])
+        c0 = int(col0[r])
+        assert O.rel_err(got[r, a - c0:b - c0].cpu().view(1, -1), sc[a:b].view(1, -1)) < 2e-3

@@ -170,3 +170,50 @@ def test_hisa_paged_fp8_two_stage_vs_oracle():
                                               blocks=blocks[r:r + 1], return_scores=True)
         O.assert_selection_parity(idx[r:r + 1], ref2, tok_scores, 1e-3, what=f"row {r} tokens")
         assert int(blocks[r, 0]) == (n + 127) // 128 - 1          # the row's last block is always kept
+
+
+def test_patch_opendsa_rebinds_the_reference_names():
+    """patch_opendsa() against the reference package itself (installed by oracle/make_ref.py): the names the
+    reference's attention module bound at import now run this library, and its indexer module's state dict
+    loads into ours unchanged."""
+    import sys
+    ref_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref")
+    if not os.path.exists(os.path.join(ref_dir, "opendsa", "modeling", "dsa_attention.py")):
+        pytest.skip("oracle/_ref is not installed (python -m oracle.make_ref needs the TransArch checkout)")
+    if ref_dir not in sys.path:
+        sys.path.insert(0, ref_dir)
+    import opendsa.modeling.dsa_attention as att
+    import opendsa.ops as ops
+    from opendsa.modeling.indexer import LightningIndexer as RefIndexer
+    from transarch_b200 import opendsa_ops as D
+    from transarch_b200.indexer_module import LightningIndexer
+    ref_select, ref_attend = ops.indexer_select_topk, ops.sparse_attend_absorbed_chunked
+    assert att.indexer_select_topk is ref_select
+    try:
+        D.patch_opendsa()
+        assert att.indexer_select_topk is D.indexer_select_topk and ops.indexer_select_topk is D.indexer_select_topk
+        assert att.sparse_attend_absorbed_chunked is D.sparse_attend_absorbed_chunked
+        # through the patched module, on a golden case: the reference's own stored output
+        name, seed, Lq, Lk, H, d, topk, docs, mode = [c for c in SELECT_CASES if c[0] == "select_packed_docs"][0]
+        q, k, w, cu, gpos = golden_inputs_select(seed, Lq, Lk, H, d, docs, mode)
+        g = np.load(os.path.join(GOLD, name + ".npz"))
+        idx = att.indexer_select_topk(q.cuda(), k.cuda(), w.cuda(), cu.cuda(), topk).cpu()
+        assert torch.equal(idx < 0, torch.from_numpy(g["idx"]) < 0)
+        assert O.set_recall(idx, torch.from_numpy(g["idx"])) >= 0.97      # bf16 operands vs the fp32 reference run
+    finally:
+        for mod in (att, ops):
+            mod.indexer_select_topk, mod.sparse_attend_absorbed_chunked = ref_select, ref_attend
+    # the indexer module: same parameter names and shapes, and the same outputs on the reference's CPU run
+    ref_mod = RefIndexer(48, n_heads=8, dtype=torch.float32)
+    mine = LightningIndexer(48, n_heads=8, dtype=torch.float32)
+    mine.load_state_dict(ref_mod.state_dict(), strict=True)
+    g2 = torch.Generator().manual_seed(5)
+    h = torch.randn(1, 9, 48, generator=g2)
+    ang = torch.rand(1, 9, 32, generator=g2) * 6.28
+    cos, sin = torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)
+    with torch.no_grad():
+        rq, rk, rw = ref_mod(h, h, cos, sin)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    mq, mk, mw = mine.cuda()(h.cuda(), h.cuda(), cos.cuda(), sin.cuda())
+    for a, b in ((mq, rq), (mk, rk), (mw, rw)):
+        assert (a.cpu() - b).abs().max() < 2e-4 * b.abs().max()

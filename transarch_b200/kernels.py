@@ -357,6 +357,33 @@ def indexer_blocklist_bf16_logits(q: torch.Tensor, weights: torch.Tensor, keys: 
     return out if head_mask is None else (out, out_gated)
 
 
+def indexer_flat_bf16_logits(q: torch.Tensor, weights: torch.Tensor, keys: torch.Tensor, pos_lo: torch.Tensor,
+                             pos_hi: torch.Tensor, row_cols: torch.Tensor, max_cols: int, *, out_scale: float = 1.0,
+                             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Prefill token logits [n_rows, max_cols] over flat bf16 keys, four queries per key tile; see
+    b200dsa_indexer_flat_bf16_logits (column c of row r = position 128*(pos_lo[r]//128) + c)."""
+    require_cuda(q, weights, keys, pos_lo, pos_hi, row_cols, out)
+    if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.shape[-2:] != (64, 128):
+        raise _lib.B200DSAError("q must be contiguous bf16 [n_rows, 64, 128]")
+    if keys.dtype != torch.bfloat16 or not keys.is_contiguous() or keys.shape[-1] != 128:
+        raise _lib.B200DSAError("keys must be contiguous bf16 [n_keys, 128]")
+    n_rows = q.shape[0]
+    if weights.dtype != torch.float32 or not weights.is_contiguous() or weights.numel() != n_rows * 64:
+        raise _lib.B200DSAError("weights must be contiguous fp32 [n_rows, 64]")
+    for t_, nm in ((pos_lo, "pos_lo"), (pos_hi, "pos_hi"), (row_cols, "row_cols")):
+        if _i32(t_, nm).numel() != n_rows:
+            raise _lib.B200DSAError(f"{nm} must have one entry per row")
+    if out is None:
+        out = torch.full((n_rows, max_cols), NEG_INF, dtype=torch.float32, device=q.device)
+    elif out.dtype != torch.float32 or out.stride(1) != 1 or out.shape[0] < n_rows or out.shape[1] < max_cols:
+        raise _lib.B200DSAError("out must be fp32 [>=n_rows, >=max_cols] with unit column stride")
+    rc = _lib.load().b200dsa_indexer_flat_bf16_logits(
+        ptr(q), ptr(weights), ptr(keys), keys.shape[0], ptr(pos_lo), ptr(pos_hi), ptr(row_cols), n_rows, max_cols,
+        out_scale, ptr(out), out.stride(0), ptr(status_word(q.device)), stream_ptr())
+    check(rc, "b200dsa_indexer_flat_bf16_logits")
+    return out
+
+
 def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: float, *,
                       kv_row_base: Optional[torch.Tensor] = None, q_pos: Optional[torch.Tensor] = None,
                       pos_lo: int = 0, pos_hi: int = 2 ** 31 - 1, n_idx_item: Optional[torch.Tensor] = None,

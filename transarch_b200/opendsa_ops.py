@@ -76,24 +76,27 @@ def indexer_logits_flat(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, ks: t
                         sm_scale: float):
     """Token logits of every row over the 128-key blocks covering its interval [ks, ke):
     (logits fp32 [T, cols] with -inf outside the interval, col0 int32 [T] = position of column 0 of
-    each row, row_cols int32 [T]).  No block list is built: the kernel walks consecutive blocks."""
+    each row, row_cols int32 [T]).  No block list is built: the kernel walks consecutive blocks, and four
+    consecutive queries share every key tile."""
     lo = ks.to(torch.int32).contiguous()
     hi = ke.to(torch.int32).contiguous()
     col0 = (lo >> 7) << 7
     row_cols = (((hi + (_BLOCK - 1)) >> 7) << 7) - col0
     row_cols.clamp_(min=0)
     cols = ((k.shape[0] + _BLOCK - 1) // _BLOCK) * _BLOCK
-    logits = K.indexer_blocklist_bf16_logits(q, w, k, None, row_cols, pos_lo=lo, pos_hi=hi, out_scale=sm_scale,
-                                             max_cols=cols)
+    logits = K.indexer_flat_bf16_logits(q, w, k, lo, hi, row_cols.contiguous(), cols, out_scale=sm_scale)
     return logits, col0, row_cols
 
 
 @torch.no_grad()
 def indexer_select_topk(index_q, index_k, index_w, cu_seqlens, topk, *, sm_scale_index: Optional[float] = None,
-                        q_chunk: int = 4096, q_global_pos=None) -> torch.Tensor:
+                        q_chunk: int = 4096, q_global_pos=None, sorted: bool = True) -> torch.Tensor:
     """Per-query top-k causal key positions by the lightning-indexer score
     I[t,j] = sm_scale * sum_h w[t,h] * relu(<q[t,h], k[j]>); int32 [Lq, topk], absolute
-    positions in descending score order, -1 where fewer than topk keys are visible."""
+    positions in descending score order, -1 where fewer than topk keys are visible.
+    sorted=False (not a reference argument) returns the same set of positions in no particular order:
+    the attention that consumes them is order-invariant (OpenDSA/opendsa/ops/sparse_mla.py:39-43), and
+    ordering 2048 winners per query costs more than scoring them."""
     if not index_q.is_cuda:
         raise B200DSAError("indexer_select_topk needs CUDA tensors (no CPU path)")
     Lq, H, d = index_q.shape
@@ -118,7 +121,7 @@ def indexer_select_topk(index_q, index_k, index_w, cu_seqlens, topk, *, sm_scale
     for t0 in range(0, Lq, rows_per):
         t1 = min(t0 + rows_per, Lq)
         logits, col0, row_cols = indexer_logits_flat(q[t0:t1], k, w[t0:t1], ks[t0:t1], ke[t0:t1], sf)
-        K.topk_select(logits, k_eff, col_end=row_cols, row_pos_offset=col0, sorted=True, out=out[t0:t1])
+        K.topk_select(logits, k_eff, col_end=row_cols, row_pos_offset=col0, sorted=sorted, out=out[t0:t1])
     return out
 
 
