@@ -11,11 +11,14 @@
 // key tile from L2 for each query).  A group's tiles run from the lowest block any of its rows starts in
 // to the highest block any of them ends in; rows mask their own interval in the epilogue.
 //
-// Roles (192 threads): warp 0 issues TMA loads (keys into a 4-stage ring, the group's 64 KB of queries
+// Roles (320 threads): warp 0 issues TMA loads (keys into a 4-stage ring, the group's 64 KB of queries
 // into a single buffer that is refilled when the previous group's MMAs have retired), warp 1 issues the
-// MMAs into two 256-column TMEM accumulators, warps 2-5 read them (thread = key), reduce the heads of
-// each of the four queries with its weights and store four logits.  Persistent grid over the list of
-// (group, tile) pairs; bounded waits throughout.
+// MMAs into two 256-column TMEM accumulators, warps 2-9 read them: two warps per 32-lane TMEM quadrant
+// (thread = key), one taking queries 0-1 of the group and the other queries 2-3, so that every scheduler
+// has two epilogue warps to switch between.  A warp keeps the 128 head weights of its two queries in its
+// own slice of shared memory (reloaded when the group changes), loads the second query's accumulator
+// columns while it reduces the first, and sums the heads in four independent chains.  Persistent grid over
+// the list of (group, tile) pairs; bounded waits throughout.
 #include <stdio.h>
 
 #include "b200dsa_common.cuh"
@@ -25,12 +28,13 @@ namespace b200dsa {
 constexpr int kFlatTile = 128;
 constexpr int kFlatGroup = 4;                     // queries per MMA
 constexpr int kFlatHeads = 64;
-constexpr int kFlatThreads = 192;
+constexpr int kFlatThreads = 320;
 constexpr int kFlatStages = 4;
 constexpr int kFlatStageBytes = kFlatTile * 128 * 2;          // 32 KB
 constexpr int kFlatQBytes = kFlatGroup * kFlatHeads * 128 * 2;  // 64 KB
 constexpr int kFlatMaxGroups = 1024;              // groups per launch (4096 rows)
-constexpr int kFlatSmem = kFlatStages * kFlatStageBytes + kFlatQBytes + 1024 + 256;
+constexpr int kFlatWBytes = 8 * 128 * 4;                      // per epilogue warp: the weights of its two queries
+constexpr int kFlatSmem = kFlatStages * kFlatStageBytes + kFlatQBytes + 1024 + 256 + kFlatWBytes;
 
 struct FlatParams {
   const float* weights;      // [n_rows, 64]
@@ -65,6 +69,7 @@ indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   uint64_t* q_empty = q_full + 1;               // [1]
   uint64_t* acc_full = q_empty + 1;             // [2]
   uint64_t* acc_empty = acc_full + 2;           // [2]
+  float* w_mem = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);   // [8 warps][2 queries][64]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_groups = (p.n_rows + kFlatGroup - 1) / kFlatGroup;
 
@@ -99,7 +104,7 @@ indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     mbar_init(q_empty, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&acc_full[s], 1);
-      mbar_init(&acc_empty[s], 128);
+      mbar_init(&acc_empty[s], 256);
     }
     mbar_fence_init();
   }
@@ -195,16 +200,19 @@ indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       ++it;
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int lane_base = (warp & 3) * 32;
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    const int lane_base = (warp & 3) * 32;          // TMEM lanes this warp may read
+    const int qh = (warp >= 6) ? 2 : 0;             // first of the two queries of the group this warp reduces
+    float* wq = w_mem + (warp - 2) * 128;
     int grp = grp0, prev = -1, it = 0;
-    int lo[kFlatGroup], hi[kFlatGroup], col0[kFlatGroup], ncol[kFlatGroup];
+    int lo[2], hi[2], col0[2], ncol[2];
     for (int g = g0; g < g1; ++g) {
       while (g >= s_prefix[grp + 1]) ++grp;
       if (grp != prev) {
+        __syncwarp();
 #pragma unroll
-        for (int j = 0; j < kFlatGroup; ++j) {
-          const int r = grp * kFlatGroup + j;
+        for (int j = 0; j < 2; ++j) {
+          const int r = grp * kFlatGroup + qh + j;
           lo[j] = hi[j] = col0[j] = ncol[j] = 0;
           if (r < p.n_rows) {
             lo[j] = p.pos_lo[r];
@@ -213,6 +221,13 @@ indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             ncol[j] = max(0, min(p.row_cols[r], p.logits_cols));
           }
         }
+        // 128 weights = 32 lanes x float4: rows r0, r0+1 are contiguous in the weight matrix
+        const int r0 = grp * kFlatGroup + qh;
+        float4 wv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r0 + (lane >> 4) < p.n_rows)
+          wv = __ldg(reinterpret_cast<const float4*>(p.weights + static_cast<int64_t>(r0) * kFlatHeads) + lane);
+        reinterpret_cast<float4*>(wq)[lane] = wv;
+        __syncwarp();
         prev = grp;
       }
       const int blk = s_b0[grp] + (g - s_prefix[grp]);
@@ -221,36 +236,41 @@ indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       const bool ready = mbar_wait(&acc_full[as], (it >> 1) & 1, abort_flag);
       if (!__all_sync(0xffffffffu, ready)) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + as * 256;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + as * 256 + qh * 64;
+      uint32_t va[64], vb[64];
+      tmem_ld_32x32(taddr, *reinterpret_cast<uint32_t(*)[32]>(va));
+      tmem_ld_32x32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(va + 32));
+      tc_wait_ld();
+      tmem_ld_32x32(taddr + 64, *reinterpret_cast<uint32_t(*)[32]>(vb));       // lands while query 0 is reduced
+      tmem_ld_32x32(taddr + 96, *reinterpret_cast<uint32_t(*)[32]>(vb + 32));
+      float res[2];
 #pragma unroll
-      for (int j = 0; j < kFlatGroup; ++j) {
-        uint32_t v0[32], v1[32];
-        tmem_ld_32x32(taddr + j * 64, v0);
-        tmem_ld_32x32(taddr + j * 64 + 32, v1);
-        tc_wait_ld();
-        const int r = grp * kFlatGroup + j;
-        const int c = pos - col0[j];
-        if (r < p.n_rows && c >= 0 && c < ncol[j]) {          // inside the row's column range
-          const float4* wr = reinterpret_cast<const float4*>(p.weights + static_cast<int64_t>(r) * kFlatHeads);
-          float acc0 = 0.f, acc1 = 0.f;
+      for (int j = 0; j < 2; ++j) {
+        if (j == 1) tc_wait_ld();
+        const uint32_t* v = j ? vb : va;
+        const float4* w4 = reinterpret_cast<const float4*>(wq + j * 64);
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4) {
-            const float4 wa = __ldg(wr + q4), wb = __ldg(wr + 8 + q4);
-            acc0 = fmaf(fmaxf(__uint_as_float(v0[4 * q4 + 0]), 0.f), wa.x, acc0);
-            acc0 = fmaf(fmaxf(__uint_as_float(v0[4 * q4 + 1]), 0.f), wa.y, acc0);
-            acc0 = fmaf(fmaxf(__uint_as_float(v0[4 * q4 + 2]), 0.f), wa.z, acc0);
-            acc0 = fmaf(fmaxf(__uint_as_float(v0[4 * q4 + 3]), 0.f), wa.w, acc0);
-            acc1 = fmaf(fmaxf(__uint_as_float(v1[4 * q4 + 0]), 0.f), wb.x, acc1);
-            acc1 = fmaf(fmaxf(__uint_as_float(v1[4 * q4 + 1]), 0.f), wb.y, acc1);
-            acc1 = fmaf(fmaxf(__uint_as_float(v1[4 * q4 + 2]), 0.f), wb.z, acc1);
-            acc1 = fmaf(fmaxf(__uint_as_float(v1[4 * q4 + 3]), 0.f), wb.w, acc1);
-          }
-          const bool keep = pos >= lo[j] && pos < hi[j];
-          p.logits[static_cast<int64_t>(r) * p.logits_stride + c] = keep ? (acc0 + acc1) * p.out_scale : -INFINITY;
+        for (int q4 = 0; q4 < 16; ++q4) {
+          const float4 ww = w4[q4];                                               // same address in every lane
+          a0 = fmaf(fmaxf(__uint_as_float(v[4 * q4 + 0]), 0.f), ww.x, a0);
+          a1 = fmaf(fmaxf(__uint_as_float(v[4 * q4 + 1]), 0.f), ww.y, a1);
+          a2 = fmaf(fmaxf(__uint_as_float(v[4 * q4 + 2]), 0.f), ww.z, a2);
+          a3 = fmaf(fmaxf(__uint_as_float(v[4 * q4 + 3]), 0.f), ww.w, a3);
         }
+        res[j] = (a0 + a1) + (a2 + a3);
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[as]);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int r = grp * kFlatGroup + qh + j;
+        const int c = pos - col0[j];
+        if (r < p.n_rows && c >= 0 && c < ncol[j]) {          // inside the row's column range
+          const bool keep = pos >= lo[j] && pos < hi[j];
+          p.logits[static_cast<int64_t>(r) * p.logits_stride + c] = keep ? res[j] * p.out_scale : -INFINITY;
+        }
+      }
       ++it;
     }
   }

@@ -47,9 +47,11 @@ struct PagedCfg {
   static constexpr int kElem = kFp8 ? 1 : 2;
   static constexpr int kStageBytes = kTileKeys * kDim * kElem;  // 16 KB / 32 KB
   static constexpr int kQBytes = kHeads * kDim * kElem;         // 8 KB / 16 KB
-  static constexpr int kStages = kEmit ? 4 : 5;
+  // bf16 keys (HISA stages, routed prefill) come out of L2 and the kernel is bound by its epilogue: two
+  // stages leave room for a second CTA per SM, which doubles the epilogue warps per scheduler
+  static constexpr int kStages = kFp8 ? (kEmit ? 4 : 5) : 2;
   static constexpr int kEmitBytes = kEmit ? (kSampleMax * 4 + kEmitHistWords * 4 + 4 * kWarpBuf * 8 + 64) : 0;
-  static constexpr int kCtasPerSm = kFp8 ? 2 : 1;
+  static constexpr int kCtasPerSm = 2;
   static constexpr int kKSteps = kFp8 ? 4 : 8;                  // MMAs per tile (32 B of K each)
   // Per-tile key scales travel through their own ring.  A slot is reused kScaleSlots tiles
   // later; by then the MMA of tile (it + 2) has retired, which needed the epilogue of tile
@@ -459,25 +461,40 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       float acc0 = 0.f, acc1 = 0.f;
       const int tile_cols = min(p.logits_cols, (t + 1) * kTileKeys);
       if (dual) {
-        // one pass, two sums: all heads, and the routed heads only (a zero weight elsewhere)
-        float gat0 = 0.f, gat1 = 0.f;
+        // one pass, two sums: all heads, and the routed heads only (a zero weight elsewhere); the same four
+        // chains as the single-sum path, so that either sum equals a separate pass bit for bit
+        float gat0 = 0.f, gat1 = 0.f, acc2 = 0.f, acc3 = 0.f, gat2 = 0.f, gat3 = 0.f;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < 32; j += 2) {
           const float r0 = fmaxf(__uint_as_float(v0[j]), 0.f), r1 = fmaxf(__uint_as_float(v1[j]), 0.f);
+          const float r2 = fmaxf(__uint_as_float(v0[j + 1]), 0.f), r3 = fmaxf(__uint_as_float(v1[j + 1]), 0.f);
           acc0 = fmaf(r0, w[j], acc0);
+          acc2 = fmaf(r2, w[j + 1], acc2);
           acc1 = fmaf(r1, w[32 + j], acc1);
+          acc3 = fmaf(r3, w[33 + j], acc3);
           gat0 = fmaf(r0, ((hm0 >> j) & 1u) ? w[j] : 0.f, gat0);
+          gat2 = fmaf(r2, ((hm0 >> (j + 1)) & 1u) ? w[j + 1] : 0.f, gat2);
           gat1 = fmaf(r1, ((hm1 >> j) & 1u) ? w[32 + j] : 0.f, gat1);
+          gat3 = fmaf(r3, ((hm1 >> (j + 1)) & 1u) ? w[33 + j] : 0.f, gat3);
         }
+        acc0 += acc2;
+        acc1 += acc3;
+        gat0 += gat2;
+        gat1 += gat3;
         if (key < tile_cols)
           p.logits_gated[static_cast<int64_t>(row) * p.logits_stride + key] =
               keep ? (gat0 + gat1) * kscale * p.out_scale : -INFINITY;
       } else {
+        float acc2 = 0.f, acc3 = 0.f;   // four independent chains of 16
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < 32; j += 2) {
           acc0 = fmaf(fmaxf(__uint_as_float(v0[j]), 0.f), w[j], acc0);
+          acc2 = fmaf(fmaxf(__uint_as_float(v0[j + 1]), 0.f), w[j + 1], acc2);
           acc1 = fmaf(fmaxf(__uint_as_float(v1[j]), 0.f), w[32 + j], acc1);
+          acc3 = fmaf(fmaxf(__uint_as_float(v1[j + 1]), 0.f), w[33 + j], acc3);
         }
+        acc0 += acc2;
+        acc1 += acc3;
       }
       const float out = keep ? (acc0 + acc1) * kscale * p.out_scale : -INFINITY;
       if (key < tile_cols && p.logits) p.logits[static_cast<int64_t>(row) * p.logits_stride + key] = out;
