@@ -192,116 +192,134 @@ def _time_call(fn, flush):
     return ts[len(ts) // 2], ts[0]
 
 
-def bench_configs(dev, peaks, threads: int, fp8_peak: float):
+def bench_configs(dev, peaks, threads: int, fp8_peak: float, only=None, with_cpu: bool = True):
     from oracle import dsa_oracle as O
     from oracle.make_ref import reference_ops
     from transarch_b200 import hisa, kernels as K, misa, opendsa_ops
     from transarch_b200.decode import SparseDecodeStep
     from transarch_b200.workloads import make_decode_queries, make_decode_state
-    ref = reference_ops()
+    ref = reference_ops() if with_cpu else None
     torch.set_num_threads(threads)
     flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
     hbm, bf16 = peaks["hbm_gbs"], peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
     out = {}
 
-    # ---- C1: causal prefill select, T = S = 4096, 64 heads, d = 128, top-2048, seed 0
-    g = torch.Generator().manual_seed(0)
-    T = 4096
-    q = torch.randn(T, 64, 128, generator=g); k = torch.randn(T, 128, generator=g); w = torch.randn(T, 64, generator=g) / 8
-    cu = torch.tensor([0, T])
-    qd, kd, wd, cud = q.to(dev).bfloat16(), k.to(dev).bfloat16(), w.to(dev), cu.to(dev)
-    med, mn = _time_call(lambda: opendsa_ops.indexer_select_topk(qd, kd, wd, cud, 2048), flush)
-    med_u, _ = _time_call(lambda: opendsa_ops.indexer_select_topk(qd, kd, wd, cud, 2048, sorted=False), flush)
-    ksd, ked = opendsa_ops.prepare_ks_ke(cud, total=T)
-    med_l, _ = _time_call(lambda: opendsa_ops.indexer_logits_flat(qd, kd, wd, ksd, ked, 128 ** -0.5), flush)
-    t0 = time.perf_counter()
-    (ref.indexer_select_topk if ref is not None else O.indexer_select_topk)(q, k, w, cu, 2048, q_chunk=512)
-    cpu_s = time.perf_counter() - t0
-    flops = T * (T + 1) // 2 * 16384
-    out["C1 causal prefill select T=S=4096 k=2048 (bf16)"] = {
-        "call": "opendsa_ops.indexer_select_topk", "us_median": med, "us_min": mn, "flops": flops,
-        "bytes": 103e6, "bound": "tensor", "achieved_tflops": flops / med / 1e6,
-        "frac_of_bf16_sustained": flops / med / 1e6 / bf16, "us_median_unsorted_output": med_u,
-        "us_median_logits_only": med_l, "logits_only_frac_of_bf16_sustained": flops / med_l / 1e6 / bf16,
-        "cpu_seconds": cpu_s,
-        "cpu_kind": "reference" if ref is not None else "port", "cpu_sample": "whole configuration, fp32, q_chunk=512"}
-    del qd, kd, wd
+    def want(tag):
+        return only is None or tag in only
 
-    # ---- C2: ragged decode, 64 requests with contexts uniform in [8K, 32K], FP8 paged keys, top-2048, seed 1
-    g = torch.Generator().manual_seed(1)
-    lens = torch.randint(8192, 32769, (64,), generator=g).tolist()
-    st = make_decode_state(64, lens, seed=1, device=dev)
-    q_idx, wq, _ = make_decode_queries(64, seed=1, device=dev)
-    step = SparseDecodeStep(64, st.local_len, topk=TOPK, device=dev)
-    med, mn = _time_call(lambda: step.select(q_idx, wq, st.k_cache, st.context_lens, st.block_table), flush)
-    n_keys = sum(lens)
-    sample = 8
-    t0 = time.perf_counter()
-    for b in range(sample):
-        kb = torch.randn(lens[b], 128)
-        qf, wf = O.quant_q_fold_weights(torch.randn(1, 64, 128), torch.randn(1, 64) / 8, INDEX_SCALE)
-        if ref is not None:
-            ref.indexer_select_topk(qf.float(), kb, wf, torch.tensor([0, lens[b]]), TOPK, sm_scale_index=1.0,
-                                    q_global_pos=torch.tensor([lens[b] - 1]))
-        else:
-            O.topk_rows(O.indexer_scores(qf.float(), kb, wf, 1.0), TOPK)
-    cpu_s = (time.perf_counter() - t0) * n_keys / sum(lens[:sample])
-    out["C2 ragged decode indexer+top-k, 64 requests 8K-32K (fp8)"] = {
-        "call": "SparseDecodeStep.select", "us_median": med, "us_min": mn, "flops": n_keys * 16384,
-        "bytes": n_keys * 132, "bound": "hbm", "achieved_gbs": n_keys * 132 / med / 1e3,
-        "frac_of_hbm": n_keys * 132 / med / 1e3 / hbm, "cpu_seconds": cpu_s,
-        "cpu_kind": "reference" if ref is not None else "port",
-        "cpu_sample": f"{sample} of 64 requests, scaled by keys"}
-    del st, step
+    def cpu_time(fn):
+        if not with_cpu:
+            return None
+        t0 = time.perf_counter()
+        fn()
+        return time.perf_counter() - t0
 
-    # ---- C3: HISA two-stage, 4096 queries at positions 126976..131071 over 131072 keys, seed 2
-    g = torch.Generator(device=dev).manual_seed(2)
-    S, T = 131072, 4096
-    k3 = torch.randn(S, 128, generator=g, device=dev).bfloat16()
-    q3 = torch.randn(T, 64, 128, generator=g, device=dev).bfloat16()
-    w3 = torch.randn(T, 64, generator=g, device=dev) / 8
-    pos = torch.arange(S - T, S, device=dev)
-    ks3, ke3 = torch.zeros(T, dtype=torch.int64, device=dev), pos + 1
-    cfg = hisa.HisaConfig()
-    med, mn = _time_call(lambda: hisa.hisa_select_topk(q3, k3, w3, ks3, ke3, cfg), flush)
-    sample = 32
-    sel = torch.arange(0, T, T // sample)
-    t0 = time.perf_counter()
-    O.hisa_select_topk(q3[sel].cpu().float(), k3.cpu().float(), w3[sel].cpu(), ks3[sel].cpu(), ke3[sel].cpu(),
-                       block=128, block_topk=64, topk=2048)
-    cpu_s = (time.perf_counter() - t0) * T / sample
-    flops = int(67.7e9 + T * 8192 * 16384)
-    out["C3 HISA two-stage, 4096 queries at the tail of 131072 keys (bf16)"] = {
-        "call": "hisa.hisa_select_topk", "us_median": med, "us_min": mn, "flops": flops, "bytes": 135e6,
-        "bound": "tensor", "achieved_tflops": flops / med / 1e6, "frac_of_bf16_sustained": flops / med / 1e6 / bf16,
-        "cpu_seconds": cpu_s, "cpu_kind": "port (the reference ships no HISA code)",
-        "cpu_sample": f"{sample} of 4096 queries, scaled"}
-    del k3, q3, w3
+    def c1():
+        """causal prefill select, T = S = 4096, 64 heads, d = 128, top-2048, seed 0"""
+        g = torch.Generator().manual_seed(0)
+        T = 4096
+        q = torch.randn(T, 64, 128, generator=g); k = torch.randn(T, 128, generator=g)
+        w = torch.randn(T, 64, generator=g) / 8
+        cu = torch.tensor([0, T])
+        qd, kd, wd, cud = q.to(dev).bfloat16(), k.to(dev).bfloat16(), w.to(dev), cu.to(dev)
+        med, mn = _time_call(lambda: opendsa_ops.indexer_select_topk(qd, kd, wd, cud, 2048), flush)
+        med_u, _ = _time_call(lambda: opendsa_ops.indexer_select_topk(qd, kd, wd, cud, 2048, sorted=False), flush)
+        ksd, ked = opendsa_ops.prepare_ks_ke(cud, total=T)
+        med_l, _ = _time_call(lambda: opendsa_ops.indexer_logits_flat(qd, kd, wd, ksd, ked, 128 ** -0.5), flush)
+        cpu_s = cpu_time(lambda: (ref.indexer_select_topk if ref is not None else O.indexer_select_topk)(
+            q, k, w, cu, 2048, q_chunk=512))
+        flops = T * (T + 1) // 2 * 16384
+        out["C1 causal prefill select T=S=4096 k=2048 (bf16)"] = {
+            "call": "opendsa_ops.indexer_select_topk", "us_median": med, "us_min": mn, "flops": flops,
+            "bytes": 103e6, "bound": "tensor", "achieved_tflops": flops / med / 1e6,
+            "frac_of_bf16_sustained": flops / med / 1e6 / bf16, "us_median_unsorted_output": med_u,
+            "us_median_logits_only": med_l, "logits_only_frac_of_bf16_sustained": flops / med_l / 1e6 / bf16,
+            "cpu_seconds": cpu_s, "cpu_kind": "reference" if ref is not None else "port",
+            "cpu_sample": "whole configuration, fp32, q_chunk=512"}
 
-    # ---- C4: MISA routed decode, batch 32, context 65536, linear router top-8 of 64, seed 3
-    st = make_decode_state(32, 65536, seed=3, device=dev)
-    q4, _, _ = make_decode_queries(32, seed=3, device=dev)
-    g = torch.Generator(device=dev).manual_seed(3)
-    x = torch.randn(32, 7168, generator=g, device=dev).bfloat16()
-    W_r = (torch.randn(7168, 64, generator=g, device=dev) * 7168 ** -0.5).bfloat16()
-    q_fp8, fold = K.quant_q_fold_weights(q4, torch.ones(32, 64, device=dev), INDEX_SCALE)
-    med, mn = _time_call(lambda: misa.misa_linear_router_decode(x, W_r, q_fp8, fold, st.k_cache, 64, st.context_lens,
-                                                                st.block_table, 8, TOPK, max_cols=65536), flush)
-    sample = 4
-    t0 = time.perf_counter()
-    for b in range(sample):
-        kb = torch.randn(65536, 128)
-        hidx, hw, _ = O.linear_router_topk_softmax(x[b:b + 1].cpu(), W_r.cpu(), 8)
-        q8, _ = O.gather_heads(q_fp8[b:b + 1].cpu().float(), fold[b:b + 1].cpu(), hidx)
-        O.topk_rows(O.indexer_scores(q8, kb, hw * torch.gather(fold[b:b + 1].cpu(), 1, hidx), 1.0), TOPK)
-    cpu_s = (time.perf_counter() - t0) * 32 / sample
-    n_keys = 32 * 65536
-    out["C4 MISA routed decode, batch 32 x 65536 keys, 8 of 64 heads (fp8)"] = {
-        "call": "misa.misa_linear_router_decode", "us_median": med, "us_min": mn, "flops": n_keys * 2048,
-        "bytes": n_keys * 132, "bound": "hbm", "achieved_gbs": n_keys * 132 / med / 1e3,
-        "frac_of_hbm": n_keys * 132 / med / 1e3 / hbm, "cpu_seconds": cpu_s,
-        "cpu_kind": "port (no reference code for the linear router)",
-        "cpu_sample": f"{sample} of 32 requests, 8 routed heads only, scaled"}
+    def c2():
+        """ragged decode, 64 requests with contexts uniform in [8K, 32K], FP8 paged keys, top-2048, seed 1"""
+        g = torch.Generator().manual_seed(1)
+        lens = torch.randint(8192, 32769, (64,), generator=g).tolist()
+        st = make_decode_state(64, lens, seed=1, device=dev)
+        q_idx, wq, _ = make_decode_queries(64, seed=1, device=dev)
+        step = SparseDecodeStep(64, st.local_len, topk=TOPK, device=dev)
+        med, mn = _time_call(lambda: step.select(q_idx, wq, st.k_cache, st.context_lens, st.block_table), flush)
+        n_keys = sum(lens)
+        sample = 8
+
+        def cpu():
+            for b in range(sample):
+                kb = torch.randn(lens[b], 128)
+                qf, wf = O.quant_q_fold_weights(torch.randn(1, 64, 128), torch.randn(1, 64) / 8, INDEX_SCALE)
+                if ref is not None:
+                    ref.indexer_select_topk(qf.float(), kb, wf, torch.tensor([0, lens[b]]), TOPK, sm_scale_index=1.0,
+                                            q_global_pos=torch.tensor([lens[b] - 1]))
+                else:
+                    O.topk_rows(O.indexer_scores(qf.float(), kb, wf, 1.0), TOPK)
+        cpu_s = cpu_time(cpu)
+        out["C2 ragged decode indexer+top-k, 64 requests 8K-32K (fp8)"] = {
+            "call": "SparseDecodeStep.select", "us_median": med, "us_min": mn, "flops": n_keys * 16384,
+            "bytes": n_keys * 132, "bound": "hbm", "achieved_gbs": n_keys * 132 / med / 1e3,
+            "frac_of_hbm": n_keys * 132 / med / 1e3 / hbm,
+            "cpu_seconds": None if cpu_s is None else cpu_s * n_keys / sum(lens[:sample]),
+            "cpu_kind": "reference" if ref is not None else "port", "cpu_sample": f"{sample} of 64 requests, scaled by keys"}
+
+    def c3():
+        """HISA two-stage, 4096 queries at positions 126976..131071 over 131072 keys, seed 2"""
+        g = torch.Generator(device=dev).manual_seed(2)
+        S, T = 131072, 4096
+        k3 = torch.randn(S, 128, generator=g, device=dev).bfloat16()
+        q3 = torch.randn(T, 64, 128, generator=g, device=dev).bfloat16()
+        w3 = torch.randn(T, 64, generator=g, device=dev) / 8
+        pos = torch.arange(S - T, S, device=dev)
+        ks3, ke3 = torch.zeros(T, dtype=torch.int64, device=dev), pos + 1
+        cfg = hisa.HisaConfig()
+        med, mn = _time_call(lambda: hisa.hisa_select_topk(q3, k3, w3, ks3, ke3, cfg), flush)
+        sample = 32
+        sel = torch.arange(0, T, T // sample)
+        cpu_s = cpu_time(lambda: O.hisa_select_topk(q3[sel].cpu().float(), k3.cpu().float(), w3[sel].cpu(), ks3[sel].cpu(),
+                                                    ke3[sel].cpu(), block=128, block_topk=64, topk=2048))
+        flops = int(67.7e9 + T * 8192 * 16384)
+        out["C3 HISA two-stage, 4096 queries at the tail of 131072 keys (bf16)"] = {
+            "call": "hisa.hisa_select_topk", "us_median": med, "us_min": mn, "flops": flops, "bytes": 135e6,
+            "bound": "tensor", "achieved_tflops": flops / med / 1e6, "frac_of_bf16_sustained": flops / med / 1e6 / bf16,
+            "cpu_seconds": None if cpu_s is None else cpu_s * T / sample,
+            "cpu_kind": "port (the reference ships no HISA code)", "cpu_sample": f"{sample} of 4096 queries, scaled"}
+
+    def c4():
+        """MISA routed decode, batch 32, context 65536, linear router top-8 of 64, seed 3"""
+        st = make_decode_state(32, 65536, seed=3, device=dev)
+        q4, _, _ = make_decode_queries(32, seed=3, device=dev)
+        g = torch.Generator(device=dev).manual_seed(3)
+        x = torch.randn(32, 7168, generator=g, device=dev).bfloat16()
+        W_r = (torch.randn(7168, 64, generator=g, device=dev) * 7168 ** -0.5).bfloat16()
+        q_fp8, fold = K.quant_q_fold_weights(q4, torch.ones(32, 64, device=dev), INDEX_SCALE)
+        med, mn = _time_call(lambda: misa.misa_linear_router_decode(x, W_r, q_fp8, fold, st.k_cache, 64,
+                                                                    st.context_lens, st.block_table, 8, TOPK,
+                                                                    max_cols=65536), flush)
+        sample = 4
+
+        def cpu():
+            for b in range(sample):
+                kb = torch.randn(65536, 128)
+                hidx, hw, _ = O.linear_router_topk_softmax(x[b:b + 1].cpu(), W_r.cpu(), 8)
+                q8, _ = O.gather_heads(q_fp8[b:b + 1].cpu().float(), fold[b:b + 1].cpu(), hidx)
+                O.topk_rows(O.indexer_scores(q8, kb, hw * torch.gather(fold[b:b + 1].cpu(), 1, hidx), 1.0), TOPK)
+        cpu_s = cpu_time(cpu)
+        n_keys = 32 * 65536
+        out["C4 MISA routed decode, batch 32 x 65536 keys, 8 of 64 heads (fp8)"] = {
+            "call": "misa.misa_linear_router_decode", "us_median": med, "us_min": mn, "flops": n_keys * 2048,
+            "bytes": n_keys * 132, "bound": "hbm", "achieved_gbs": n_keys * 132 / med / 1e3,
+            "frac_of_hbm": n_keys * 132 / med / 1e3 / hbm,
+            "cpu_seconds": None if cpu_s is None else cpu_s * 32 / sample,
+            "cpu_kind": "port (no reference code for the linear router)",
+            "cpu_sample": f"{sample} of 32 requests, 8 routed heads only, scaled"}
+
+    for tag, fn in (("C1", c1), ("C2", c2), ("C3", c3), ("C4", c4)):
+        if want(tag):
+            fn()
+            torch.cuda.empty_cache()
     for v in out.values():
         for kk in list(v):
             if isinstance(v[kk], float):
@@ -342,6 +360,9 @@ def main():
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-configs", action="store_true", help="do not time the other configurations of the path")
     ap.add_argument("--skip-parity", action="store_true", help="do not compare sampled requests with the oracle")
+    ap.add_argument("--configs-only", default="", help="comma-separated subset of C1,C2,C3,C4: time only these "
+                    "configurations (no decode step) and print them; for profiling single kernels")
+    ap.add_argument("--config-reps", type=int, default=0, help="timed repetitions per configuration (default 50)")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--result", default="replicated", choices=["replicated", "sharded"],
                     help="sharded run: every rank ends with all result rows, or only with its slice of them")
@@ -352,6 +373,16 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.configs_only:
+        global CFG_REPS, CFG_WARM
+        if args.config_reps > 0:
+            CFG_REPS, CFG_WARM = args.config_reps, min(CFG_WARM, args.config_reps)
+        torch.cuda.set_device(local_rank)
+        peaks, _ = measured_peaks()
+        out = bench_configs(torch.device("cuda", local_rank), peaks, os.cpu_count() or 1, 0.0,
+                            only=set(args.configs_only.split(",")), with_cpu=False)
+        print(json.dumps({"configs": out}), flush=True)
         return
 
     import torch.distributed as dist

@@ -97,7 +97,10 @@ struct PagedIndexerParams {
   int32_t cand_target;          // candidates per row the floors aim at before the safety margin
 };
 
-template <bool kFp8, bool kEmit = false>
+// kList (fp8 only): rows address the cache through per-row lists of logical 128-key blocks.  A template
+// parameter, not a run-time test: the plain decode kernel is bound by HBM closely enough that two extra
+// branches per tile in its producer and epilogue cost 4 % of its time.
+template <bool kFp8, bool kEmit = false, bool kList = false>
 __global__ void __launch_bounds__(kThreads, PagedCfg<kFp8, kEmit>::kCtasPerSm)
 indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
                      const PagedIndexerParams p) {
@@ -235,9 +238,8 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       const int key0 = t * kTileKeys;
       int nkeys = min(kTileKeys, cols - key0);
       int first = key0 >> p_shift;
-      bool listed = false;
-      if constexpr (kFp8) listed = p.klist != nullptr;
-      if (listed) {
+      constexpr bool listed = kFp8 && kList;
+      if constexpr (listed) {
         // the tile is logical block b of the request: its pages, as far as the context reaches
         const int b = p.klist[static_cast<int64_t>(row) * p.klist_stride + t];
         const int hi = p.pos_hi[row];
@@ -435,7 +437,7 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
         if (!__all_sync(0xffffffffu, sc_ready)) break;
         kscale = sc_mem[slot * kTileKeys + lane_base + lane];
         keep = keep && (kscale >= 0.0f);
-        if (p.klist) {
+        if constexpr (kList) {
           const int b = p.klist[static_cast<int64_t>(row) * p.klist_stride + t];
           const int pos = b * kTileKeys + lane_base + lane;
           keep = keep && b >= 0 && pos >= lo && pos < hi;
@@ -464,6 +466,16 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
         // one pass, two sums: all heads, and the routed heads only (a zero weight elsewhere); the same four
         // chains as the single-sum path, so that either sum equals a separate pass bit for bit
         float gat0 = 0.f, gat1 = 0.f, acc2 = 0.f, acc3 = 0.f, gat2 = 0.f, gat3 = 0.f;
+        if constexpr (kFp8) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float r0 = fmaxf(__uint_as_float(v0[j]), 0.f), r1 = fmaxf(__uint_as_float(v1[j]), 0.f);
+            acc0 = fmaf(r0, w[j], acc0);
+            acc1 = fmaf(r1, w[32 + j], acc1);
+            gat0 = fmaf(r0, ((hm0 >> j) & 1u) ? w[j] : 0.f, gat0);
+            gat1 = fmaf(r1, ((hm1 >> j) & 1u) ? w[32 + j] : 0.f, gat1);
+          }
+        } else {
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
           const float r0 = fmaxf(__uint_as_float(v0[j]), 0.f), r1 = fmaxf(__uint_as_float(v1[j]), 0.f);
@@ -477,6 +489,7 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
           gat1 = fmaf(r1, ((hm1 >> j) & 1u) ? w[32 + j] : 0.f, gat1);
           gat3 = fmaf(r3, ((hm1 >> (j + 1)) & 1u) ? w[33 + j] : 0.f, gat3);
         }
+        }
         acc0 += acc2;
         acc1 += acc3;
         gat0 += gat2;
@@ -484,8 +497,15 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
         if (key < tile_cols)
           p.logits_gated[static_cast<int64_t>(row) * p.logits_stride + key] =
               keep ? (gat0 + gat1) * kscale * p.out_scale : -INFINITY;
+      } else if constexpr (kFp8) {
+        // two chains of 32: the decode kernel is bound by HBM, and the shorter instruction stream is faster there
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          acc0 = fmaf(fmaxf(__uint_as_float(v0[j]), 0.f), w[j], acc0);
+          acc1 = fmaf(fmaxf(__uint_as_float(v1[j]), 0.f), w[32 + j], acc1);
+        }
       } else {
-        float acc2 = 0.f, acc3 = 0.f;   // four independent chains of 16
+        float acc2 = 0.f, acc3 = 0.f;   // four independent chains of 16: the bf16 modes are bound by this loop
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
           acc0 = fmaf(fmaxf(__uint_as_float(v0[j]), 0.f), w[j], acc0);
@@ -620,19 +640,20 @@ static int sm_count() {
   return n;
 }
 
-template <bool kFp8, bool kEmit = false>
+template <bool kFp8, bool kEmit = false, bool kList = false>
 static int launch_paged(const CUtensorMap& mk, const CUtensorMap& mq, PagedIndexerParams p, int64_t est_tiles,
                         cudaStream_t stream) {
   using Cfg = PagedCfg<kFp8, kEmit>;
-  cudaError_t e = cudaFuncSetAttribute(indexer_paged_kernel<kFp8, kEmit>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       Cfg::kSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(indexer_paged_kernel<kFp8, kEmit, kList>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;
   }
   int grid = sm_count() * Cfg::kCtasPerSm;
   if (est_tiles > 0 && est_tiles < grid) grid = static_cast<int>(est_tiles);
-  e = launch_chained(indexer_paged_kernel<kFp8, kEmit>, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, mk, mq, p);
+  e = launch_chained(indexer_paged_kernel<kFp8, kEmit, kList>, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, mk,
+                     mq, p);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
@@ -744,8 +765,10 @@ int paged_fp8_launch(const char* who, const void* q_fp8, const float* weights, c
       p.row_pos_offset = em.row_pos_offset ? em.row_pos_offset + r0 : nullptr;
       p.cand_target = em.cand_target;
       rc = launch_paged<true, true>(mk, mq, p, 0, stream);
+    } else if (ls.klist) {
+      rc = launch_paged<true, false, true>(mk, mq, p, 0, stream);
     } else {
-      rc = launch_paged<true, false>(mk, mq, p, 0, stream);
+      rc = launch_paged<true, false, false>(mk, mq, p, 0, stream);
     }
     if (rc) return rc;
   }
