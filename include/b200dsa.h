@@ -194,18 +194,19 @@ int b200dsa_indexer_paged_blocklist_fp8_logits(const void* q_fp8, const float* w
  * indexer's epilogue appends every score at or above a floor (taken from the first tiles each CTA
  * scores of a row) to the row's candidate list; the second kernel selects exactly from the list.
  * A list that cannot be proven complete (fewer than k entries at or above the largest floor used
- * for the row, or more than 8192 entries) is not trusted: the row is then selected from `logits`.
+ * for the row, or more than 16384 entries) is not trusted: the row is then selected from `logits`.
  * Replaces, in one call, MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/misa_ops.py:182
  * (+ :393-401, the logits matrix) and the torch.topk at indexers.py:566-568.
  *
  *   arguments up to out_scale: as b200dsa_indexer_paged_fp8_logits (no head mask)
  *   logits / logits_stride    [n_rows, >= max_cols] fp32, written as a by-product and read only by the
  *                             fallback.  May be NULL: nothing but the candidate lists is then written,
- *                             and a row whose list is not provably complete (probability below 1e-6
- *                             per row) is selected from the list anyway with *status raised to 3.
+ *                             and a row whose list is not provably complete (about 1e-7 per row for
+ *                             scores without long runs of ties) is selected from the list anyway with
+ *                             *status raised to 3.
  *   k <= 2048, sorted, row_pos_offset, out_idx / out_val / out_stride: as b200dsa_topk_select_split;
  *                             results equal b200dsa_topk_select's on the same logits
- *   scratch_cand              n_rows * 8192 uint64 (8-byte aligned)
+ *   scratch_cand              n_rows * 16384 uint64 (8-byte aligned)
  *   scratch_count             2 * n_rows int32, ZERO before the first call; left zero by every call
  * Calls that share scratch must not overlap on the GPU.
  * ------------------------------------------------------------------------------------- */

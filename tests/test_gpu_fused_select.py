@@ -37,7 +37,7 @@ def test_fused_equals_unfused(ctxs, k):
     st, q, w = _state(len(ctxs) + k, ctxs)
     q_fp8, wf = K.quant_q_fold_weights(q, w, 128 ** -0.5)
     ref_logits, ref_idx, ref_val = _unfused(K, q_fp8, wf, st, st.context_lens, k)
-    scratch = K.topk_scratch(len(ctxs), q.device)
+    scratch = K.fused_scratch(len(ctxs), q.device)
     logits = torch.full_like(ref_logits, float("nan"))
     for rep in range(3):                                        # the scratch is re-armed by every call
         idx, val = K.indexer_paged_fp8_topk(q_fp8, wf, st.k_cache, P, st.context_lens, st.block_table, k, scratch,
@@ -67,7 +67,7 @@ def test_fused_against_oracle_with_offsets_and_two_rows_per_request():
     row_ctx = (st.context_lens.view(-1, 1) - next_n + torch.arange(next_n, device="cuda", dtype=torch.int32).view(1, -1) + 1)
     row_ctx = row_ctx.reshape(-1).contiguous()
     off = (torch.arange(len(ctxs) * next_n, dtype=torch.int32, device="cuda") * 100000).contiguous()
-    scratch = K.topk_scratch(row_ctx.numel(), q.device)
+    scratch = K.fused_scratch(row_ctx.numel(), q.device)
     idx = K.indexer_paged_fp8_topk(q_fp8, wf, st.k_cache, P, row_ctx, st.block_table, k, scratch, next_n=next_n,
                                    max_cols=st.local_len, row_pos_offset=off, sorted=True).cpu()
     assert _lib.read_status(q.device) == 0
@@ -89,7 +89,7 @@ def test_fused_ties_fall_back_to_the_logits():
     ctxs, k = [30000, 9000], 2048
     st, q, w = _state(6, ctxs)
     q_fp8, wf = K.quant_q_fold_weights(torch.zeros_like(q), w, 128 ** -0.5)
-    scratch = K.topk_scratch(2, q.device)
+    scratch = K.fused_scratch(2, q.device)
     idx = K.indexer_paged_fp8_topk(q_fp8, wf, st.k_cache, P, st.context_lens, st.block_table, k, scratch,
                                    max_cols=st.local_len, sorted=True)
     assert _lib.read_status(q.device) == 0
@@ -118,7 +118,7 @@ def test_fused_skewed_scores_still_exact():
         cache[pages, P * 128:] = sc.contiguous().view(torch.uint8)
     q_fp8, wf = K.quant_q_fold_weights(q, w.abs(), 128 ** -0.5)
     ref_logits, ref_idx, _ = _unfused(K, q_fp8, wf, st, st.context_lens, k)
-    scratch = K.topk_scratch(len(ctxs), q.device)
+    scratch = K.fused_scratch(len(ctxs), q.device)
     idx = K.indexer_paged_fp8_topk(q_fp8, wf, st.k_cache, P, st.context_lens, st.block_table, k, scratch,
                                    max_cols=st.local_len)
     assert torch.equal(torch.sort(idx, 1).values, torch.sort(ref_idx, 1).values)

@@ -224,7 +224,7 @@ def test_folded_exchanges_on_one_gpu():
     cand_bytes = B * 2 * k * 4
     pc = PeerLseCombine(B * H, dev, emulate_world=world, extra_bytes=cand_bytes * (1 + world))
     try:
-        scratch = K.topk_scratch(B, dev)
+        scratch = K.fused_scratch(B, dev)
         off = torch.full((B,), 1000, dtype=torch.int32, device=dev)
         ref_idx, ref_val = K.indexer_paged_fp8_topk(q_fp8, wf, st.k_cache, 64, st.context_lens, st.block_table, k,
                                                     scratch, max_cols=st.local_len, row_pos_offset=off, sorted=True,

@@ -33,14 +33,19 @@ constexpr int kThreads = 192;
 // the row's candidate list in global memory, so that the top-k kernel never reads the logits.
 //   segment  = the run of consecutive tiles of one row inside a CTA's share of the tile list
 //   floor    = taken from the scores of the segment's first kSampleTiles tiles (buffered in shared
-//              memory, histogrammed over the top 12 key bits): the lower edge of the bin at which the
-//              sample holds j' = j0 + 4 sqrt(j0) + 2 scores, j0 = sample share of cand_target
+//              memory): the want-th largest sampled score, found with a 4096-bin histogram of the top 12
+//              key bits and an exact rank inside the bin that holds it.  With m sampled keys of a row of n,
+//              jk = k m / n of them are expected among the row's top k; want = jk + z sqrt(want), z = 5.5,
+//              so that fewer than k of the row's scores reach the floor with probability about 1e-8 per
+//              segment, while the list is expected to hold n want / m entries (5 200 of 8 388 608... per
+//              row at n = 131072, 11 500 at n = 524288, under the 16384-entry capacity)
 //   row_floor[row] = max of the floors of the row's segments: the list is complete above it
 constexpr int kSampleTiles = 16;
 constexpr int kSampleMax = kSampleTiles * kTileKeys;   // 2048 buffered scores
 constexpr int kEmitHistWords = 2048;                   // 4096 bins, two 16-bit counters per word
 constexpr int kWarpBuf = 128;                          // private candidate buffer of an epilogue warp
-constexpr int kEmitCap = 8192;                         // entries per row of the global candidate lists
+constexpr int kEmitCap = 16384;                        // entries per row of the global candidate lists
+constexpr int kEmitEqMax = 256;                        // samples ranked exactly inside the threshold bin
 
 template <bool kFp8, bool kEmit = false>
 struct PagedCfg {
@@ -94,7 +99,7 @@ struct PagedIndexerParams {
   int32_t* cand_count;          // [n_rows] entries appended (may exceed kEmitCap: list unusable)
   uint32_t* row_floor;          // [n_rows] largest floor any segment of the row used (ordered-float bits; 0 = none)
   const int32_t* row_pos_offset;  // nullable [n_rows]: added to the column to give the output position
-  int32_t cand_target;          // candidates per row the floors aim at before the safety margin
+  int32_t cand_target;          // k: how many of a row's scores the selection after this kernel wants
 };
 
 // kList (fp8 only): rows address the cache through per-row lists of logical 128-key blocks.  A template
@@ -131,7 +136,9 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(emit_mem + kSampleMax * 4);           // [kEmitHistWords]
   uint64_t* s_wbuf = reinterpret_cast<uint64_t*>(emit_mem + kSampleMax * 4 + kEmitHistWords * 4);  // [4][kWarpBuf]
   float* s_floor = reinterpret_cast<float*>(emit_mem + kSampleMax * 4 + kEmitHistWords * 4 + 4 * kWarpBuf * 8);
-  int* s_wtot = reinterpret_cast<int*>(s_floor + 1);                                   // [4] + [1] total
+  int* s_wtot = reinterpret_cast<int*>(s_floor + 1);                                   // [4] warp totals
+  int* s_eqn = s_wtot + 4;                                                             // [3] entries, bin, rank wanted
+  float* s_eq = reinterpret_cast<float*>(s_hist);                                      // reuses the histogram
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -528,13 +535,14 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
               const int n_samp = samp_tiles * kTileKeys;
               const int key0 = (t - seg_tile) * kTileKeys;                      // first key of the segment
               const int m_valid = max(0, min(n_samp, cols - key0));
-              const float j0 = static_cast<float>(p.cand_target) * static_cast<float>(m_valid) /
+              // samples expected among the row's top k, and the sample rank that leaves a 5.5-sigma margin
+              const float jk = static_cast<float>(p.cand_target) * static_cast<float>(m_valid) /
                                static_cast<float>(max(cols, 1));
-              const int want = static_cast<int>(ceilf(j0 + 4.0f * sqrtf(j0) + 2.0f));
+              const int want = static_cast<int>(ceilf(jk + 15.125f + 5.5f * sqrtf(jk + 7.5625f)));
               floor_v = -3.402823466e38f;
               if (want < (m_valid * 9) / 10) {                                  // uniform over the 128 threads
                 for (int i = tix; i < kEmitHistWords; i += 128) s_hist[i] = 0;
-                if (!rendezvous()) { emit_abort = true; break; }              // samples written, histogram clear
+                if (!rendezvous()) { emit_abort = true; break; }              // histogram clear
                 for (int i = 0; i < samp_tiles; ++i) {
                   const float v = s_samp[i * kTileKeys + tix];
                   if (v >= -3.402823466e38f && v <= 3.402823466e38f) {
@@ -557,7 +565,11 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
                   if (lane + o < 32) suf += u;
                 }
                 if (lane == 0) s_wtot[warp & 3] = suf;
-                if (tix == 0) *s_floor = -3.402823466e38f;                      // fewer valid samples than wanted
+                if (tix == 0) {
+                  *s_floor = -3.402823466e38f;         // fewer valid samples than wanted: everything is taken
+                  s_eqn[0] = 0;
+                  s_eqn[1] = -1;
+                }
                 if (!rendezvous()) { emit_abort = true; break; }
                 int above = suf - chunk;               // samples in the bins above this thread's
                 for (int wq = (warp & 3) + 1; wq < 4; ++wq) above += s_wtot[wq];
@@ -567,9 +579,37 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
                     const int c = static_cast<int>((b & 1) ? (wv >> 16) : (wv & 0xffffu));
                     if (above + c >= want) {
                       *s_floor = fmaxf(ordered_to_float(static_cast<uint32_t>(32 * tix + b) << 20), -3.402823466e38f);
+                      s_eqn[1] = 32 * tix + b;         // the bin that holds the want-th largest sample ...
+                      s_eqn[2] = want - above;         // ... which is the s_eqn[2]-th largest inside it
                       break;
                     }
                     above += c;
+                  }
+                }
+                if (!rendezvous()) { emit_abort = true; break; }              // histogram no longer read
+                const int tbin = s_eqn[1];
+                if (tbin >= 0) {
+                  for (int i = 0; i < samp_tiles; ++i) {
+                    const float v = s_samp[i * kTileKeys + tix];
+                    if (v >= -3.402823466e38f && v <= 3.402823466e38f &&
+                        static_cast<int>(float_to_ordered(v) >> 20) == tbin) {
+                      const int slot = atomicAdd(&s_eqn[0], 1);
+                      if (slot < kEmitEqMax) s_eq[slot] = v;
+                    }
+                  }
+                }
+                if (!rendezvous()) { emit_abort = true; break; }
+                const int n_eq = s_eqn[0];
+                if (tbin >= 0 && n_eq <= kEmitEqMax) {
+                  // exact rank inside the bin (a crowded bin keeps its lower edge as the floor)
+                  for (int i = tix; i < n_eq; i += 128) {
+                    const float v = s_eq[i];
+                    int rank = 0;
+                    for (int j = 0; j < n_eq; ++j) {
+                      const float u = s_eq[j];
+                      rank += (u > v) || (u == v && j < i);
+                    }
+                    if (rank == s_eqn[2] - 1) *s_floor = v;
                   }
                 }
                 if (!rendezvous()) { emit_abort = true; break; }
@@ -846,7 +886,7 @@ static int fused_topk(const char* who, const void* q_fp8, const float* weights, 
   em.cand_count = scratch_count;
   em.row_floor = reinterpret_cast<uint32_t*>(scratch_count + n_rows);
   em.row_pos_offset = row_pos_offset;
-  em.cand_target = k + k / 2;
+  em.cand_target = k;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc = paged_fp8_launch(who, q_fp8, weights, cache, num_pages, page_size, context_lens, block_table,
                             block_table_stride, row_table, n_rows, next_n, max_cols, out_scale, logits, logits_stride,

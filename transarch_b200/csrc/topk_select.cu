@@ -23,6 +23,8 @@ namespace b200dsa {
 
 constexpr int kHistBins = 4096;
 constexpr int kCandCap = 8192;   // candidate list entries (64 KB)
+constexpr int kListCap = 16384;  // entries per row of the lists the indexer's epilogue collects (128 KB)
+constexpr int kMaxSelectSmem = kHistBins * 4 + (kListCap + kEqCap + kCandCap) * 8;   // largest configuration
 constexpr int kEqCap = 1024;     // undecided-bin list (8 KB)
 constexpr int kSampleChunk = 128;
 constexpr int kSampleMax = 8192;
@@ -555,9 +557,10 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
       p.pre_count[row] = 0;
       if (p.pre_floor) p.pre_floor[row] = 0u;
     }
-    bool usable = c <= kCandCap && (p.pre_floor || c >= k);
+    // lists are cand_cap entries apart (8192 in the split form, 16384 when the indexer collected them)
+    bool usable = c <= cand_cap && (p.pre_floor || c >= k);
     if (usable) {
-      const uint64_t* g = p.pre_cand + static_cast<int64_t>(row) * kCandCap;
+      const uint64_t* g = p.pre_cand + static_cast<int64_t>(row) * cand_cap;
       int n_ge = 0;
       for (int i = tid; i < c; i += nthr) {
         const uint64_t e = g[i];
@@ -577,7 +580,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     if (!usable && p.pre_floor && p.scores == nullptr) {
       // no logits to fall back to: report, and return the best of what the list holds
       if (tid == 0 && p.status) atomicMax(p.status, kDevSelectIncomplete);
-      usable = c <= kCandCap;
+      usable = c <= cand_cap;
       if (!usable) {
         write_row(nullptr, 0);
         return;
@@ -858,8 +861,7 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
   }
   const size_t smem = kHistBins * sizeof(uint32_t) + (static_cast<size_t>(cand_cap) + kEqCap + k_pow2) * sizeof(uint64_t);
   cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(kHistBins * sizeof(uint32_t) +
-                                                        (2 * kCandCap + kEqCap) * sizeof(uint64_t)));
+                                       kMaxSelectSmem);
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;
@@ -902,7 +904,7 @@ extern "C" int b200dsa_topk_select_split(const float* scores, int64_t row_stride
                                        static_cast<int>(smem_a));
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(kHistBins * sizeof(uint32_t) + (2 * kCandCap + kEqCap) * sizeof(uint64_t)));
+                             kMaxSelectSmem);
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;
@@ -943,11 +945,10 @@ int topk_select_from_lists(const float* scores, int64_t row_stride, int32_t n_ro
   }
   int k_pow2 = 32;
   while (k_pow2 < k) k_pow2 <<= 1;
-  const size_t smem = kHistBins * sizeof(uint32_t) + (kCandCap + kEqCap + k_pow2) * sizeof(uint64_t);
-  cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(kHistBins * sizeof(uint32_t) + (2 * kCandCap + kEqCap) * sizeof(uint64_t)));
+  const size_t smem = kHistBins * sizeof(uint32_t) + (kListCap + kEqCap + k_pow2) * sizeof(uint64_t);
+  cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSelectSmem);
   if (e == cudaSuccess)
-    e = launch_chained(topk_select_kernel, dim3(n_rows), dim3(1024), smem, stream, p, k_pow2, static_cast<int>(kCandCap));
+    e = launch_chained(topk_select_kernel, dim3(n_rows), dim3(1024), smem, stream, p, k_pow2, static_cast<int>(kListCap));
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
@@ -992,7 +993,7 @@ extern "C" int b200dsa_topk_merge_owned(const int32_t* recv, int32_t world, int3
   }
   const size_t smem = kHistBins * sizeof(uint32_t) + (static_cast<size_t>(cand_cap) + kEqCap + k_pow2) * sizeof(uint64_t);
   cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(kHistBins * sizeof(uint32_t) + (2 * kCandCap + kEqCap) * sizeof(uint64_t)));
+                                       kMaxSelectSmem);
   const int threads = world * k > 8192 ? 1024 : (world * k > 2048 ? 512 : 256);
   if (e == cudaSuccess)
     e = launch_chained(topk_select_kernel, dim3(n_rows), dim3(threads), smem, static_cast<cudaStream_t>(stream), p,

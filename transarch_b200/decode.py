@@ -110,7 +110,7 @@ class SparseDecodeStep:
         self.fused_scratch = None
         self.keep_logits = keep_logits
         if fused_select and hasattr(backend, "indexer_paged_fp8_topk") and topk <= 2048:
-            self.fused_scratch = backend.topk_scratch(batch, dev)
+            self.fused_scratch = backend.fused_scratch(batch, dev)
         self.peer = None
         if combine == "peer" and not (n > 1 and dist.is_initialized()):
             raise ValueError("combine='peer' needs an initialised process group of more than one rank")

@@ -87,6 +87,17 @@ def topk_scratch(n_rows: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
             torch.zeros(2 * n_rows, dtype=torch.int32, device=device))
 
 
+FUSED_CAND_CAP = 16384  # candidate list entries per row that the indexer's epilogue may collect
+
+
+def fused_scratch(n_rows: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Scratch for indexer_paged_fp8_topk: (candidates uint64-as-int64 [n_rows, 16384], zeroed int32
+    [2*n_rows]: per-row counters then per-row floors).  Both halves of the int32 part must be zero before
+    the first call; every call leaves them zero.  Not interchangeable with topk_scratch()."""
+    return (torch.empty(n_rows, FUSED_CAND_CAP, dtype=torch.int64, device=device),
+            torch.zeros(2 * n_rows, dtype=torch.int32, device=device))
+
+
 _scratch_cache = {}
 
 
@@ -246,7 +257,7 @@ def indexer_paged_fp8_topk(q_fp8: torch.Tensor, weights: torch.Tensor, cache: to
                            sorted: bool = False, out: Optional[torch.Tensor] = None,
                            out_values: Optional[torch.Tensor] = None, push=None):
     """Indexer scores and their top-k positions in two launches, the candidates collected by the
-    indexer's own epilogue; see b200dsa_indexer_paged_fp8_topk.  `scratch` comes from topk_scratch().
+    indexer's own epilogue; see b200dsa_indexer_paged_fp8_topk.  `scratch` comes from fused_scratch().
     keep_logits=True (default) also writes the logits (into `logits`, allocated when not given) so
     that a row whose candidate list is not provably complete is selected exactly from them;
     keep_logits=False writes no logits at all (status word 3 on such a row).
@@ -269,8 +280,8 @@ def indexer_paged_fp8_topk(q_fp8: torch.Tensor, weights: torch.Tensor, cache: to
     if max_cols is None:
         max_cols = block_table.shape[-1] * page_size
     cand, count = scratch
-    if cand.numel() < n_rows * CAND_CAP or count.numel() < 2 * n_rows:
-        raise _lib.B200DSAError("scratch is too small for this many rows")
+    if cand.numel() < n_rows * FUSED_CAND_CAP or count.numel() < 2 * n_rows:
+        raise _lib.B200DSAError("scratch is too small for this many rows (use fused_scratch())")
     if keep_logits and logits is None:
         logits = torch.empty(n_rows, max_cols, dtype=torch.float32, device=q_fp8.device)
     if not keep_logits:
