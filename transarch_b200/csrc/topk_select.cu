@@ -23,9 +23,9 @@ namespace b200dsa {
 
 constexpr int kHistBins = 4096;
 constexpr int kCandCap = 8192;   // candidate list entries (64 KB)
+constexpr int kEqCap = 1024;     // undecided-bin list (8 KB)
 constexpr int kListCap = 16384;  // entries per row of the lists the indexer's epilogue collects (128 KB)
 constexpr int kMaxSelectSmem = kHistBins * 4 + (kListCap + kEqCap + kCandCap) * 8;   // largest configuration
-constexpr int kEqCap = 1024;     // undecided-bin list (8 KB)
 constexpr int kSampleChunk = 128;
 constexpr int kSampleMax = 8192;
 
