@@ -18,8 +18,8 @@
 // lane 16+i of warp 4+w owns head row 16w+i (row max / sum are thread-local); lane i of the
 // same warp owns that row of O.
 //
-// Roles (320 threads): warps 0-3 gather (warp w owns 16 rows of every tile, one row per three
-// instructions), warps 4-7 softmax, warp 8 issues the score MMAs, warp 9 the value MMAs.
+// Roles (288 threads): warps 0-3 gather (warp w owns 16 rows of every tile, one row per three
+// instructions), warps 4-7 softmax, warp 8 issues the score and the value MMAs.
 // All waits are bounded.
 #include <cuda_bf16.h>
 
@@ -32,7 +32,7 @@ constexpr int kMlaMaxHeads = 128;
 constexpr int kMlaD = 576;          // latent width (512 value dims + 64 rope dims)
 constexpr int kMlaDv = 512;
 constexpr int kMlaChunks = 9;       // 576 / 64 elements (128-byte chunks)
-constexpr int kMlaThreads = 320;
+constexpr int kMlaThreads = 288;
 // keys per tile and gather pipeline depth: smaller tiles allow more row gathers in flight
 constexpr int kMlaTile = 64;
 constexpr int kMlaStages = 3;
@@ -41,6 +41,11 @@ constexpr int kMlaChunkBytesK = kMlaTile * 128;
 constexpr int kMlaPBytes = kMlaHeadsTile * kMlaTile * 2;
 constexpr int kMlaSmemBytes = kMlaStages * kMlaStageBytes + kMlaPBytes + 1024 + 256;
 static_assert(kMlaTile == 32 || kMlaTile == 64, "tile must be 32 or 64 keys");
+// Q staging: the last 72 KB of the key ring, rows padded to 1168 bytes (the tail reaches into the P tile)
+constexpr int kMlaQRowBytes = kMlaD * 2 + 16;
+constexpr int kMlaQStageOff = kMlaStages * kMlaStageBytes - kMlaHeadsTile * kMlaD * 2;
+static_assert(kMlaQStageOff >= 0 && kMlaQStageOff % 16 == 0, "Q staging must lie inside the ring");
+static_assert(kMlaQStageOff + kMlaHeadsTile * kMlaQRowBytes <= kMlaStages * kMlaStageBytes + kMlaPBytes, "Q staging overruns the P tile");
 constexpr uint32_t kMlaTmemCols = 512;
 constexpr uint32_t kMlaTmemO = 0;                 // lanes 0-15 of every sub-partition, columns 0..511
 constexpr uint32_t kMlaTmemS = (16u << 16);       // lanes 16-31 of every sub-partition, columns 0..127
@@ -186,6 +191,7 @@ sparse_mla_decode_kernel(const MlaParams p) {
   uint64_t* pv_done = bars + 6;                  // [1] value MMA retired (P buffer free, O stable)
   uint64_t* kv_full = bars + 7;                  // [stages] 128 gather threads (arrivals of their copies)
   uint64_t* kv_empty = bars + 7 + kMlaStages;    // [stages] value MMA retired
+  uint64_t* q_land = bars + 7 + 2 * kMlaStages;  // [1] bytes of the Q rows
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -207,6 +213,7 @@ sparse_mla_decode_kernel(const MlaParams p) {
     }
     mbar_init(p_full, 128);
     mbar_init(pv_done, 1);
+    mbar_init(q_land, 1);
     mbar_fence_init();
   }
   if (warp == 8) {
@@ -244,7 +251,9 @@ sparse_mla_decode_kernel(const MlaParams p) {
         valid = false;
         atomicMax(p.status, kDevBadIndex);
       }
-      const bool ok = mbar_wait(&kv_empty[s], ((t / kMlaStages) & 1) ^ 1, abort_flag);
+      bool ok = mbar_wait(&kv_empty[s], ((t / kMlaStages) & 1) ^ 1, abort_flag);
+      // the tail of the ring holds the Q rows until the softmax threads have moved them to TMEM
+      if (t < kMlaStages && (t + 1) * kMlaStageBytes > kMlaQStageOff) ok = ok && mbar_wait(q_full, 0, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) break;
       const unsigned vmask = __ballot_sync(0xffffffffu, valid) & ((1u << kRowsPerWarp) - 1u);
       const uint32_t stage_addr = kv_addr + s * kMlaStageBytes;
@@ -284,20 +293,37 @@ sparse_mla_decode_kernel(const MlaParams p) {
     float m_ref = -INFINITY, l = 0.f;
     bool aborted = false;
     {
-      // Q -> TMEM once: lane 16+i of this warp stores head row 16*wq+i into the upper half-lanes
-      // (two bf16 per 32-bit cell, 288 cells per row).  The lower half-lanes of these columns
-      // belong to O, which nothing has written yet.
+      // Q -> TMEM once.  The 64 rows of this CTA (72 KB) are fetched by one bulk copy per row into the
+      // tail of the key ring, which the gather does not touch before q_full (rows padded by 16 bytes so
+      // that one row per lane reads without bank conflicts; the last row spills into the P tile, unused
+      // so far): one memory round trip instead of nine dependent ones.  Then lane 16+i of this warp
+      // stores head row 16*wq+i into the upper half-lanes (two bf16 per 32-bit cell, 288 cells per row).
+      // The lower half-lanes of these columns belong to O, which nothing has written yet.
       const int qhead = hh * kMlaHeadsTile + row;
       const bool have = is_s && qhead < p.n_heads;
-      const uint4* qrow = reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(item) * p.n_heads + (have ? qhead : 0)) * kMlaD);
+      const int rows_have = min(kMlaHeadsTile, p.n_heads - hh * kMlaHeadsTile);
+      if (warp == 4) {
+        if (lane == 0) mbar_arrive_expect_tx(q_land, static_cast<uint32_t>(rows_have) * (kMlaD * 2));
+        __syncwarp();
+        const __nv_bfloat16* q0 = p.q + (static_cast<int64_t>(item) * p.n_heads + hh * kMlaHeadsTile) * kMlaD;
+        for (int r = lane; r < rows_have; r += 32)
+          bulk_load_1d(smem_al + kMlaQStageOff + r * kMlaQRowBytes, q0 + static_cast<int64_t>(r) * kMlaD, kMlaD * 2, q_land);
+      }
+      const bool okq = mbar_wait(q_land, 0, abort_flag);
+      aborted = !__all_sync(0xffffffffu, okq);
+      const uint32_t qrow = smem_base + kMlaQStageOff + row * kMlaQRowBytes;
 #pragma unroll 1
-      for (int c = 0; c < kMlaD / 64; ++c) {
+      for (int c = 0; c < kMlaD / 64 && !aborted; ++c) {
         uint32_t qv[32];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          uint4 x = make_uint4(0u, 0u, 0u, 0u);
-          if (have) x = __ldg(qrow + c * 8 + j);
-          qv[4 * j] = x.x; qv[4 * j + 1] = x.y; qv[4 * j + 2] = x.z; qv[4 * j + 3] = x.w;
+          if (have) {
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(qv[4 * j]), "=r"(qv[4 * j + 1]), "=r"(qv[4 * j + 2]), "=r"(qv[4 * j + 3])
+                         : "r"(qrow + c * 128 + j * 16));
+          } else {
+            qv[4 * j] = qv[4 * j + 1] = qv[4 * j + 2] = qv[4 * j + 3] = 0u;
+          }
         }
         tmem_st_32x32(tmem_base + lane_addr + 128 + c * 32, qv);
       }
@@ -305,7 +331,7 @@ sparse_mla_decode_kernel(const MlaParams p) {
       tc_fence_before();
       mbar_arrive(q_full);
     }
-    for (int t = 0; t < n_tiles; ++t) {
+    for (int t = 0; t < n_tiles && !aborted; ++t) {
       const int sb = t & 1;
       bool ok = mbar_wait(&s_full[sb], (t >> 1) & 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) { aborted = true; break; }
@@ -457,18 +483,20 @@ sparse_mla_decode_kernel(const MlaParams p) {
               (l_o > 0.f) ? (m_o + log2f(l_o)) * 0.6931471805599453f : -INFINITY;
       }
     }
-  } else if (warp == 8) {
-    // ------------------------------------------------------------------ score MMA issuer (warp 8)
-    // Scores and values are issued by different warps so that neither waits for the other's
-    // barriers: the tensor pipe sees S(t+1), S(t+2) ... interleaved with PV(t) as they become ready.
+  } else {
+    // ------------------------------------------------------------------ MMA issuer (warp 8)
+    // One warp issues everything, in the order S(0), S(1), PV(0), S(2), PV(1), ...: the tensor pipe runs
+    // its instructions in issue order, so S(t+1) keeps it busy while the softmax of tile t runs, and the
+    // ring stage that PV(t-1) frees is not needed before S(t+2), a whole tile of tensor work later, which
+    // is the time the gather of tile t+2 has to land.  (Issuing the scores as early as their buffers allow
+    // puts S(t+2) directly behind PV(t-1) and exposes the whole gather latency on every tile.)
     constexpr uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, kMlaHeadsTile, kMlaTile);
-    bool ok = mbar_wait(q_full, 0, abort_flag);
-    ok = __all_sync(0xffffffffu, ok);
-    for (int t = 0; ok && t < n_tiles; ++t) {
+    constexpr uint32_t idesc_pv = make_idesc(kFmtBF16, kFmtBF16, kMlaHeadsTile, 256, 0, 1);
+    auto issue_scores = [&](int t) -> bool {
       const int s = t % kMlaStages, sb = t & 1;
       const bool w = mbar_wait(&kv_full[s], (t / kMlaStages) & 1, abort_flag) &&
                      mbar_wait(&s_empty[sb], ((t >> 1) & 1) ^ 1, abort_flag);
-      if (!__all_sync(0xffffffffu, w)) break;
+      if (!__all_sync(0xffffffffu, w)) return false;
       fence_proxy_async();  // gathered rows were written through the generic proxy
       tc_fence_after();
       if (elect_one()) {
@@ -486,14 +514,15 @@ sparse_mla_decode_kernel(const MlaParams p) {
         tc_commit(&s_full[sb]);
       }
       __syncwarp();
-    }
-  } else {
-    // ------------------------------------------------------------------ value MMA issuer (warp 9)
-    constexpr uint32_t idesc_pv = make_idesc(kFmtBF16, kFmtBF16, kMlaHeadsTile, 256, 0, 1);
-    for (int t = 0; t < n_tiles; ++t) {
+      return true;
+    };
+    bool ok = mbar_wait(q_full, 0, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok && n_tiles > 0) ok = issue_scores(0);
+    for (int t = 0; ok && t < n_tiles; ++t) {
+      if (t + 1 < n_tiles && !issue_scores(t + 1)) break;
       const int s = t % kMlaStages;
-      const bool w = mbar_wait(p_full, t & 1, abort_flag) &&
-                     mbar_wait(&kv_full[s], (t / kMlaStages) & 1, abort_flag);  // long complete; orders the V reads
+      const bool w = mbar_wait(p_full, t & 1, abort_flag);
       if (!__all_sync(0xffffffffu, w)) break;
       fence_proxy_async();
       tc_fence_after();
