@@ -499,6 +499,20 @@ int b200dsa_paged_mean_pool_fp8(const void* cache, int32_t num_pages, int32_t pa
                                 const int32_t* context_lens, const int32_t* block_table,
                                 int64_t block_table_stride, int32_t n_requests, int32_t block,
                                 int32_t max_pool_blocks, float* out, int32_t* status, void* stream);
+/* Pooled-key maintenance for decode: the same means, kept up to date instead of pooled again every step
+ * (the reference pools the whole cache on every call, misa_ops.py:381).  sums and out are persistent
+ * fp32 [n_requests, max_pool_blocks, 128]; request b went from prev_lens[b] to context_lens[b] keys since
+ * the last call and only those keys are read.  prev_lens[b] = 0 rebuilds request b from the cache and
+ * clears the blocks beyond its context (a slot taken over by a new request).  The running sums add in
+ * position order, as the full kernel does: out is bit-identical to b200dsa_paged_mean_pool_fp8 on the
+ * same cache.  ctas_per_request CTAs share the blocks of one request (1-2 for decode steps, more when
+ * requests are rebuilt). */
+int b200dsa_paged_mean_pool_fp8_update(const void* cache, int32_t num_pages, int32_t page_size,
+                                       const int32_t* prev_lens, const int32_t* context_lens,
+                                       const int32_t* block_table, int64_t block_table_stride,
+                                       int32_t n_requests, int32_t block, int32_t max_pool_blocks,
+                                       int32_t ctas_per_request, float* sums, float* out, int32_t* status,
+                                       void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * MISA head routers.  Each writes head_idx [n_tokens, n_keep] int32 (descending router score,

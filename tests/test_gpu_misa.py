@@ -67,6 +67,43 @@ def test_pooling_matches_oracle():
         assert (pooled[b, ref.shape[0]:] == 0).all()
 
 
+def test_pooled_key_cache_follows_the_cache_bit_exactly():
+    """Incremental pooled-key maintenance: after every growth step (one token, a few tokens, across a
+    block boundary, a slot taken over by a shorter request) the kept means equal pooling the whole
+    cache again, bit for bit, and feed misa_page_mqa_logits to the same result."""
+    from transarch_b200 import kernels as K, misa as M
+    ctx_final = [700, 64, 1000]
+    g, qs, cache, table = _paged(36, ctx_final)
+    cache, table = cache.cuda(), table.cuda()
+    state = K.PooledKeyCache(3, 8, 128, "cuda")
+    steps = [[300, 10, 500], [301, 11, 501], [304, 12, 640], [513, 64, 641], [513, 64, 1000]]
+    for lens in steps:
+        lens_t = torch.tensor(lens, dtype=torch.int32, device="cuda")
+        got = state.update(cache, 64, lens_t, table)
+        ref = K.paged_mean_pool_fp8(cache, 64, lens_t, table, 128, 8)
+        assert torch.equal(got, ref), lens
+    # slot 0 is taken over by a new, shorter request (same pages here, other length): rebuilt and cleared
+    state.reset(torch.tensor([0], device="cuda"))
+    lens_t = torch.tensor([130, 64, 1000], dtype=torch.int32, device="cuda")
+    got = state.update(cache, 64, lens_t, table)
+    assert torch.equal(got, K.paged_mean_pool_fp8(cache, 64, lens_t, table, 128, 8))
+    assert (got[0, 2:] == 0).all()
+    from transarch_b200 import _lib
+    assert _lib.read_status(torch.device("cuda")) == 0
+    # the routed decode logits are the same with the kept means
+    q = torch.randn(3, 1, 64, 128, generator=g)
+    q_fp8 = q.cuda().to(torch.float8_e4m3fn)
+    w = (torch.randn(3, 64, generator=g) / 8).cuda()
+    a = M.misa_page_mqa_logits(q_fp8, cache.view(-1, 64, 1, 132), w, None, lens_t, table, 1024, 8, False, 256, 128)
+    b = M.misa_page_mqa_logits(q_fp8, cache.view(-1, 64, 1, 132), w, None, lens_t, table, 1024, 8, False, 256, 128,
+                               pooled=got)
+    # the stage-1 candidates come out in no particular order: compare them as sorted (position, logit) pairs
+    for x, y in ((a, b),):
+        ox, oy = torch.sort(x[1], dim=1).indices, torch.sort(y[1], dim=1).indices
+        assert torch.equal(torch.gather(x[1], 1, ox), torch.gather(y[1], 1, oy))
+        assert torch.equal(torch.gather(x[0], 1, ox), torch.gather(y[0], 1, oy))
+
+
 @pytest.mark.parametrize("use_qnorm", [True, False])
 def test_misa_mqa_logits_prefill(use_qnorm):
     from transarch_b200 import misa as M

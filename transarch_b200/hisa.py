@@ -102,7 +102,8 @@ def hisa_select_topk(index_q, index_k, index_w, ks, ke, cfg: Optional[HisaConfig
 @torch.no_grad()
 def hisa_select_topk_paged(q_fp8: torch.Tensor, weights: torch.Tensor, cache: torch.Tensor, page_size: int,
                            context_lens: torch.Tensor, block_table: torch.Tensor, cfg: Optional[HisaConfig] = None,
-                           *, next_n: int = 1, max_model_len: Optional[int] = None, return_blocks: bool = False):
+                           *, next_n: int = 1, max_model_len: Optional[int] = None, return_blocks: bool = False,
+                           pooled: Optional[torch.Tensor] = None):
     """The two-stage HISA selection over the paged FP8 index-key cache (the serving layout): decode rows
     score the block means of their request, keep the top-m 128-key blocks (the last one always), then score
     tokens only inside those blocks, reading the FP8 pages in place.
@@ -112,7 +113,9 @@ def hisa_select_topk_paged(q_fp8: torch.Tensor, weights: torch.Tensor, cache: to
       block_table int32 [requests, max_pages]
     Returns int32 [rows, index_topk] key positions inside the request (descending score, -1 padded).
     Stage 2 follows the reference's paged block-sparse fragment (block_ops.py:151-379); pooling is its
-    paged_mean_pooling (:381-486)."""
+    paged_mean_pooling (:381-486).  pooled: the block means fp32 [requests, max_pool, 128] (max_pool =
+    ceil(max_model_len / 128) rounded up to 128) from a kernels.PooledKeyCache that follows the cache,
+    instead of pooling the whole cache in this call."""
     cfg = cfg or HisaConfig()
     if cfg.hisa_k_block_size != 128:
         raise B200DSAError("hisa_k_block_size must be 128 (one block per tensor-core key tile)")
@@ -124,7 +127,10 @@ def hisa_select_topk_paged(q_fp8: torch.Tensor, weights: torch.Tensor, cache: to
         max_model_len = block_table.shape[1] * page_size
     max_pool = ((max_model_len + 127) // 128 + 127) // 128 * 128         # pooled blocks per request, whole tiles
     req_ctx = ctx.view(n_req, next_n).max(dim=1).values.contiguous()
-    pooled = K.paged_mean_pool_fp8(cache, page_size, req_ctx, block_table, 128, max_pool)
+    if pooled is None:
+        pooled = K.paged_mean_pool_fp8(cache, page_size, req_ctx, block_table, 128, max_pool)
+    elif pooled.shape != (n_req, max_pool, 128) or pooled.dtype != torch.float32 or not pooled.is_contiguous():
+        raise B200DSAError("pooled must be contiguous fp32 [requests, max_pool, 128]")
     k_pooled = pooled.view(n_req * max_pool, 128).to(torch.bfloat16)
     w = weights.to(torch.float32).contiguous()
     qb = q_fp8.to(torch.bfloat16).contiguous()

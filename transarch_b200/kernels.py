@@ -112,6 +112,15 @@ def topk_scratch_cached(n_rows: int, device) -> Tuple[torch.Tensor, torch.Tensor
     return _scratch_cache[key]
 
 
+def fused_scratch_cached(n_rows: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """fused_scratch() kept per (device, row count); the same sharing rule as topk_scratch_cached."""
+    dev = torch.device(device)
+    key = ("fused", dev.type, dev.index if dev.index is not None else torch.cuda.current_device(), n_rows)
+    if key not in _scratch_cache:
+        _scratch_cache[key] = fused_scratch(n_rows, dev)
+    return _scratch_cache[key]
+
+
 def topk_select_split(scores: torch.Tensor, k: int, scratch: Tuple[torch.Tensor, torch.Tensor], *,
                       col_begin: Optional[torch.Tensor] = None, col_end: Optional[torch.Tensor] = None,
                       keep_pos_inf: bool = False, row_pos_offset: Optional[torch.Tensor] = None,
@@ -550,6 +559,45 @@ def paged_mean_pool_fp8(cache: torch.Tensor, page_size: int, context_lens: torch
                                                  ptr(out), ptr(status_word(cache.device)), stream_ptr()),
           "b200dsa_paged_mean_pool_fp8")
     return out
+
+
+class PooledKeyCache:
+    """Block means of the paged FP8 index-key cache kept up to date across decode steps
+    (b200dsa_paged_mean_pool_fp8_update): every update() reads only the keys a request gained since
+    the previous one.  One slot per request row; reset(rows) marks slots whose request changed so
+    that the next update rebuilds them from the cache.  means is fp32 [n_slots, max_pool_blocks, 128],
+    bit-identical to paged_mean_pool_fp8 on the same cache, lengths and tables."""
+
+    def __init__(self, n_slots: int, max_pool_blocks: int, block: int, device):
+        self.block, self.max_pool_blocks = block, max_pool_blocks
+        self.sums = torch.zeros(n_slots, max_pool_blocks, 128, dtype=torch.float32, device=device)
+        self.means = torch.zeros_like(self.sums)
+        self.lens = torch.zeros(n_slots, dtype=torch.int32, device=device)
+        self._fresh = True
+
+    def reset(self, rows: Optional[torch.Tensor] = None) -> None:
+        if rows is None:
+            self.lens.zero_()
+        else:
+            self.lens[rows.long()] = 0
+        self._fresh = True
+
+    def update(self, cache: torch.Tensor, page_size: int, context_lens: torch.Tensor,
+               block_table: torch.Tensor) -> torch.Tensor:
+        require_cuda(cache, context_lens, block_table)
+        _i32(context_lens, "context_lens"); _i32(block_table, "block_table")
+        B = context_lens.numel()
+        if B != self.lens.numel():
+            raise _lib.B200DSAError("one context length per slot")
+        num_pages = cache.numel() // (page_size * 132)
+        ctas = min(self.max_pool_blocks, 256) if self._fresh else 2
+        check(_lib.load().b200dsa_paged_mean_pool_fp8_update(
+            ptr(cache), num_pages, page_size, ptr(self.lens), ptr(context_lens), ptr(block_table),
+            block_table.stride(0), B, self.block, self.max_pool_blocks, ctas, ptr(self.sums), ptr(self.means),
+            ptr(status_word(cache.device)), stream_ptr()), "b200dsa_paged_mean_pool_fp8_update")
+        self.lens.copy_(context_lens)
+        self._fresh = False
+        return self.means
 
 
 def _router_out(n_tokens: int, n_keep: int, device):

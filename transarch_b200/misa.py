@@ -99,10 +99,13 @@ def misa_mqa_logits(q: torch.Tensor, kv: Tuple[torch.Tensor, torch.Tensor], weig
 def misa_page_mqa_logits(q_fp8: torch.Tensor, kv_cache_fp8: torch.Tensor, weights: torch.Tensor,
                          q_head_topk_indices: Optional[torch.Tensor], context_lens: torch.Tensor,
                          block_tables: torch.Tensor, max_model_len: int, decode_topk_heads: int, use_qnorm: bool,
-                         stage1_topk: int, k_block_size: Optional[int] = None):
+                         stage1_topk: int, k_block_size: Optional[int] = None, *,
+                         pooled: Optional[torch.Tensor] = None):
     """Routed decode logits over the paged FP8 cache.  q_fp8 [B, next_n, 64, 128] e4m3,
     kv_cache_fp8 uint8 [num_blocks, block_size, 1, 132] (or any view of those bytes), weights
-    fp32 [B*next_n, 64].  Returns (logits [B*next_n, s1], sparse_topk_indices int32 [B*next_n, s1])."""
+    fp32 [B*next_n, 64].  Returns (logits [B*next_n, s1], sparse_topk_indices int32 [B*next_n, s1]).
+    pooled (not in the reference's signature): block means fp32 [B, ceil(max_model_len / k_block_size), 128]
+    kept up to date by kernels.PooledKeyCache, instead of pooling the whole cache again on every call."""
     B, next_n = q_fp8.shape[0], q_fp8.shape[1]
     page_size = kv_cache_fp8.shape[1]
     cache = kv_cache_fp8.reshape(kv_cache_fp8.shape[0], -1)
@@ -124,7 +127,10 @@ def misa_page_mqa_logits(q_fp8: torch.Tensor, kv_cache_fp8: torch.Tensor, weight
         if k_block_size is None:
             raise B200DSAError("k_block_size must be provided for the block-score router")
         max_pool = (max_model_len + k_block_size - 1) // k_block_size
-        pooled = K.paged_mean_pool_fp8(cache, page_size, ctx, tables, k_block_size, max_pool)
+        if pooled is None:
+            pooled = K.paged_mean_pool_fp8(cache, page_size, ctx, tables, k_block_size, max_pool)
+        elif pooled.shape != (B, max_pool, 128) or pooled.dtype != torch.float32 or not pooled.is_contiguous():
+            raise B200DSAError("pooled must be contiguous fp32 [B, ceil(max_model_len / k_block_size), 128]")
         n_pool = ((row_ctx + k_block_size - 1) // k_block_size).to(torch.int32).contiguous()
         req = torch.arange(rows, device=ctx.device, dtype=torch.int32) // next_n
         qb = q_fp8.to(torch.bfloat16).reshape(rows, 64, 128).contiguous()
@@ -159,6 +165,13 @@ def misa_linear_router_decode(x: torch.Tensor, w_r: torch.Tensor, q_fp8: torch.T
     of the quantised queries), then indexer + top-k.  Returns (indices int32 [B, topk], head_idx)."""
     gate, head_idx = K.router_linear_topk_softmax(x.contiguous(), w_r.contiguous(), n_keep)
     weights = (gate * q_scale_fold).contiguous()
+    n_rows = q_fp8.numel() // (64 * 128)
+    if topk <= 2048:
+        # candidates collected by the indexer's own epilogue, one selection launch, logits kept only as the
+        # exact fallback of a row whose list cannot be proven complete
+        idx = K.indexer_paged_fp8_topk(q_fp8, weights, cache, page_size, context_lens, block_table, topk,
+                                       K.fused_scratch_cached(n_rows, q_fp8.device), max_cols=max_cols, sorted=True)
+        return idx, head_idx
     logits = K.indexer_paged_fp8_logits(q_fp8, weights, cache, page_size, context_lens, block_table,
                                         max_cols=max_cols, fill=False)
     if logits.shape[0] <= 148 and logits.shape[1] >= 32768 and topk <= 4096:
