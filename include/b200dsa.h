@@ -530,7 +530,9 @@ int b200dsa_paged_mean_pool_fp8_update(const void* cache, int32_t num_pages, int
  *  linear     : logits = x[t,:] @ W_r (bf16 inputs, fp32 accumulate), top-n heads, weights =
  *               softmax over the kept logits.  No counterpart in the reference: a learned
  *               router reading the token's hidden state (hidden = 7168, n = 8 of 64 heads in the
- *               DeepSeek-V3.2 shape) instead of the query norms; logits_out optional.
+ *               DeepSeek-V3.2 shape) instead of the query norms; logits_out optional; out_scale
+ *               (optional fp32 [n_tokens, 64]) multiplies the weights written, e.g. the folded
+ *               per-head scales of the FP8 queries.
  * ------------------------------------------------------------------------------------- */
 int b200dsa_router_qnorm_topk(const void* q_bf16, const float* w, int32_t n_tokens, int32_t n_keep,
                               float* weights_out, int32_t* head_idx, void* stream);
@@ -540,8 +542,9 @@ int b200dsa_router_block_score_topk(const void* q_bf16, const float* w, const fl
                                     int32_t n_keep, float* weights_out, int32_t* head_idx,
                                     float* scores_out, void* stream);
 int b200dsa_router_linear_topk_softmax(const void* x_bf16, const void* w_r_bf16, int32_t n_tokens,
-                                       int32_t hidden, int32_t n_keep, float* weights_out,
-                                       int32_t* head_idx, float* logits_out, void* stream);
+                                       int32_t hidden, int32_t n_keep, const float* out_scale,
+                                       float* weights_out, int32_t* head_idx, float* logits_out,
+                                       void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Insert new index keys into the paged FP8 cache: per-token e4m3 quantisation

@@ -68,7 +68,7 @@ SIGNATURES = {
                                            _vp, _vp],
     "b200dsa_router_qnorm_topk": [_vp, _vp, _i32, _i32, _vp, _vp, _vp],
     "b200dsa_router_block_score_topk": [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp],
-    "b200dsa_router_linear_topk_softmax": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp],
+    "b200dsa_router_linear_topk_softmax": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp],
     "b200dsa_indexer_k_quant_and_cache": [_vp, _vp, _i64, _vp, _i64, _i32, _i32, _vp, _vp],
 }
 

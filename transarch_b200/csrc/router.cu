@@ -46,31 +46,35 @@ __device__ void select_top_heads(const float* score, int n, int* sel, int* keep)
   __syncwarp();
 }
 
-__global__ void __launch_bounds__(256) router_linear_kernel(const __nv_bfloat16* __restrict__ x,
+constexpr int kLinThreads = 1024;          // 128 row groups x 8 threads (8 heads each)
+constexpr int kLinGroups = kLinThreads / 8;
+__global__ void __launch_bounds__(kLinThreads) router_linear_kernel(const __nv_bfloat16* __restrict__ x,
                                                             const __nv_bfloat16* __restrict__ w_r, int hidden, int n_keep,
+                                                            const float* __restrict__ out_scale,
                                                             float* __restrict__ weights_out,
                                                             int32_t* __restrict__ head_idx,
                                                             float* __restrict__ logits_out) {
-  // Thread (grp, h8): rows grp, grp+32, ... of W_r, heads 8*h8 .. 8*h8+7 (one 16-byte load per row),
-  // four rows in flight; x is staged in shared memory once.
+  // Thread (grp, h8): rows grp, grp+128, ... of W_r, heads 8*h8 .. 8*h8+7 (one 16-byte load per row),
+  // eight rows in flight per thread (the kernel is bound by the latency of these loads: one CTA per
+  // token, a few tokens per step); x is staged in shared memory once.
   extern __shared__ __nv_bfloat16 xs[];
-  __shared__ float part[32][kRouterHeads + 1];
+  __shared__ float part[kLinGroups][kRouterHeads + 1];
   __shared__ float logit[kRouterHeads];
   __shared__ int sel[kRouterHeads], keep[kRouterHeads];
   const int t = blockIdx.x, tid = threadIdx.x, h8 = tid & 7, grp = tid >> 3;
   const __nv_bfloat16* xr = x + static_cast<int64_t>(t) * hidden;
-  for (int i = tid; i < hidden; i += 256) xs[i] = xr[i];
+  for (int i = tid; i < hidden; i += kLinThreads) xs[i] = xr[i];
   __syncthreads();
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   const uint4* wv = reinterpret_cast<const uint4*>(w_r) + h8;   // row i: 8 uint4 (64 bf16)
   int i = grp;
-  for (; i + 96 < hidden; i += 128) {
-    uint4 r[4];
+  for (; i + 7 * kLinGroups < hidden; i += 8 * kLinGroups) {
+    uint4 r[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) r[u] = __ldg(wv + static_cast<int64_t>(i + 32 * u) * 8);
+    for (int u = 0; u < 8; ++u) r[u] = __ldg(wv + static_cast<int64_t>(i + kLinGroups * u) * 8);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const float xv = __bfloat162float(xs[i + 32 * u]);
+    for (int u = 0; u < 8; ++u) {
+      const float xv = __bfloat162float(xs[i + kLinGroups * u]);
       const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&r[u]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -79,7 +83,7 @@ __global__ void __launch_bounds__(256) router_linear_kernel(const __nv_bfloat16*
       }
     }
   }
-  for (; i < hidden; i += 32) {
+  for (; i < hidden; i += kLinGroups) {
     const uint4 r = __ldg(wv + static_cast<int64_t>(i) * 8);
     const float xv = __bfloat162float(xs[i]);
     const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&r);
@@ -92,11 +96,16 @@ __global__ void __launch_bounds__(256) router_linear_kernel(const __nv_bfloat16*
 #pragma unroll
   for (int j = 0; j < 8; ++j) part[grp][8 * h8 + j] = acc[j];
   __syncthreads();
-  if (tid < 64) {
+  if (tid < 256) {     // four partial sums per head, then one add tree through the warp
+    const int h = tid >> 2, q4 = tid & 3;
     float sum = 0.f;
-    for (int g = 0; g < 32; ++g) sum += part[g][tid];
-    logit[tid] = sum;
-    if (logits_out) logits_out[static_cast<int64_t>(t) * 64 + tid] = sum;
+    for (int g = q4; g < kLinGroups; g += 4) sum += part[g][h];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (q4 == 0) {
+      logit[h] = sum;
+      if (logits_out) logits_out[static_cast<int64_t>(t) * 64 + h] = sum;
+    }
   }
   __syncthreads();
   select_top_heads(logit, n_keep, sel, keep);
@@ -107,7 +116,8 @@ __global__ void __launch_bounds__(256) router_linear_kernel(const __nv_bfloat16*
     const float mx = logit[sel[0]];
     float den = 0.f;
     for (int j = 0; j < n_keep; ++j) den += expf(logit[sel[j]] - mx);
-    weights_out[static_cast<int64_t>(t) * 64 + h] = keep[h] ? expf(logit[h] - mx) / den : 0.f;
+    const float sc = out_scale ? out_scale[static_cast<int64_t>(t) * 64 + h] : 1.0f;
+    weights_out[static_cast<int64_t>(t) * 64 + h] = keep[h] ? expf(logit[h] - mx) / den * sc : 0.f;
     if (h < n_keep) head_idx[static_cast<int64_t>(t) * n_keep + h] = sel[h];
   }
 }
@@ -208,8 +218,9 @@ static int finish_launch() {
 using namespace b200dsa;
 
 extern "C" int b200dsa_router_linear_topk_softmax(const void* x_bf16, const void* w_r_bf16, int32_t n_tokens,
-                                                  int32_t hidden, int32_t n_keep, float* weights_out,
-                                                  int32_t* head_idx, float* logits_out, void* stream) {
+                                                  int32_t hidden, int32_t n_keep, const float* out_scale,
+                                                  float* weights_out, int32_t* head_idx, float* logits_out,
+                                                  void* stream) {
   if (n_tokens == 0) return B200DSA_OK;
   if (!x_bf16 || !w_r_bf16 || !weights_out || !head_idx || n_tokens < 0 || hidden < 1 || n_keep < 1 || n_keep > 64) {
     set_last_error("b200dsa_router_linear_topk_softmax: bad argument (1 <= n_keep <= 64)");
@@ -219,9 +230,9 @@ extern "C" int b200dsa_router_linear_topk_softmax(const void* x_bf16, const void
     set_last_error("b200dsa_router_linear_topk_softmax: hidden must be <= 24576 and W_r 16-byte aligned");
     return B200DSA_EINVAL;
   }
-  router_linear_kernel<<<n_tokens, 256, static_cast<size_t>(hidden) * 2, static_cast<cudaStream_t>(stream)>>>(
+  router_linear_kernel<<<n_tokens, kLinThreads, static_cast<size_t>(hidden) * 2, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x_bf16), static_cast<const __nv_bfloat16*>(w_r_bf16), hidden, n_keep,
-      weights_out, head_idx, logits_out);
+      out_scale, weights_out, head_idx, logits_out);
   return finish_launch();
 }
 

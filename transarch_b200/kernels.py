@@ -635,17 +635,22 @@ def router_block_score_topk(q: torch.Tensor, w: torch.Tensor, pooled: torch.Tens
     return (wo, hi, sc) if return_scores else (wo, hi)
 
 
-def router_linear_topk_softmax(x: torch.Tensor, w_r: torch.Tensor, n_keep: int, *, return_logits: bool = False):
-    """Linear router: top-n of x @ W_r with softmax weights over the kept heads."""
-    require_cuda(x, w_r)
+def router_linear_topk_softmax(x: torch.Tensor, w_r: torch.Tensor, n_keep: int, *, return_logits: bool = False,
+                               out_scale: Optional[torch.Tensor] = None):
+    """Linear router: top-n of x @ W_r with softmax weights over the kept heads; out_scale fp32 [T, 64]
+    multiplies the weights written (the folded per-head query scales of the FP8 indexer)."""
+    require_cuda(x, w_r, out_scale)
+    if out_scale is not None and (out_scale.dtype != torch.float32 or not out_scale.is_contiguous() or
+                                  out_scale.shape != (x.shape[0], 64)):
+        raise _lib.B200DSAError("out_scale must be contiguous fp32 [T, 64]")
     if x.dtype != torch.bfloat16 or w_r.dtype != torch.bfloat16 or not x.is_contiguous() or \
             not w_r.is_contiguous() or w_r.shape != (x.shape[1], 64):
         raise _lib.B200DSAError("x must be bf16 [T, hidden] and W_r bf16 [hidden, 64], both contiguous")
     T, hidden = x.shape
     wo, hi = _router_out(T, n_keep, x.device)
     lg = torch.empty(T, 64, dtype=torch.float32, device=x.device) if return_logits else None
-    check(_lib.load().b200dsa_router_linear_topk_softmax(ptr(x), ptr(w_r), T, hidden, n_keep, ptr(wo), ptr(hi),
-                                                        ptr(lg), stream_ptr()),
+    check(_lib.load().b200dsa_router_linear_topk_softmax(ptr(x), ptr(w_r), T, hidden, n_keep, ptr(out_scale), ptr(wo),
+                                                        ptr(hi), ptr(lg), stream_ptr()),
           "b200dsa_router_linear_topk_softmax")
     return (wo, hi, lg) if return_logits else (wo, hi)
 

@@ -163,8 +163,8 @@ def misa_linear_router_decode(x: torch.Tensor, w_r: torch.Tensor, q_fp8: torch.T
     """Linear-router variant: logits = x @ W_r, keep the top-n heads, their softmax weights
     replace the head weights (times q_scale_fold [B,64], the per-head FP8 scale and softmax scale
     of the quantised queries), then indexer + top-k.  Returns (indices int32 [B, topk], head_idx)."""
-    gate, head_idx = K.router_linear_topk_softmax(x.contiguous(), w_r.contiguous(), n_keep)
-    weights = (gate * q_scale_fold).contiguous()
+    weights, head_idx = K.router_linear_topk_softmax(x.contiguous(), w_r.contiguous(), n_keep,
+                                                     out_scale=q_scale_fold.to(torch.float32).contiguous())
     n_rows = q_fp8.numel() // (64 * 128)
     if topk <= 2048:
         # candidates collected by the indexer's own epilogue, one selection launch, logits kept only as the
