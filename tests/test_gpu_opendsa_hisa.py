@@ -80,9 +80,41 @@ def test_attend_golden_through_dropin():
                                            sm_scale=Dl ** -0.5).cpu()
     ref = torch.from_numpy(g["out"])
     assert (out - ref).abs().max() / ref.abs().max() < 2e-2
-    with pytest.raises(Exception):
-        D.sparse_attend_absorbed_chunked(q.cuda().requires_grad_(), lat.cuda(), W_UV.cuda(), idx.cuda(), d_c=d_c,
-                                         sm_scale=1.0)
+
+
+def test_attend_gradients_match_reference_autograd():
+    """Under autograd the drop-in is differentiable: d q_lat, d latent and d W_UV against autograd through
+    the reference's own op (its files under oracle/_ref when present, else the oracle restatement) on the
+    golden MLA-shaped case, which has -1 padding, future positions and an empty row.  2e-2 of the largest
+    entry: the forward context is bf16."""
+    from transarch_b200 import opendsa_ops as D
+    from oracle import make_ref
+    name, seed, L, H, Dl, d_c, Kk = ATTEND_CASES[1]
+    q, lat, W_UV, idx = golden_inputs_attend(seed, L, H, Dl, d_c, Kk)
+    q, lat = q.bfloat16().float(), lat.bfloat16().float()
+    gen = torch.Generator().manual_seed(5)
+    G = torch.randn(L, H, W_UV.shape[1], generator=gen)
+    ref_ops = make_ref.reference_ops()
+
+    def ref_fn(a, b, c):
+        if ref_ops is not None:
+            return ref_ops.sparse_attend_absorbed_chunked(a, b, c, idx, d_c=d_c, sm_scale=Dl ** -0.5, q_chunk=7)
+        return O.sparse_attend_absorbed(a, b, c, idx, d_c=d_c, sm_scale=Dl ** -0.5)
+
+    a, b, c = (t.clone().requires_grad_() for t in (q, lat, W_UV))
+    (ref_fn(a, b, c) * G).sum().backward()
+    x, y, z = (t.clone().cuda().requires_grad_() for t in (q, lat, W_UV))
+    out = D.sparse_attend_absorbed_chunked(x, y, z, idx.cuda(), d_c=d_c, sm_scale=Dl ** -0.5, q_chunk=7)
+    assert out.requires_grad
+    (out * G.cuda()).sum().backward()
+    for got, ref, what in ((x.grad, a.grad, "q_lat"), (y.grad, b.grad, "latent"), (z.grad, c.grad, "W_UV")):
+        err = (got.cpu() - ref).abs().max() / ref.abs().max()
+        assert err < 2e-2, (what, float(err))
+    # only some inputs need gradients
+    x2 = q.clone().cuda().requires_grad_()
+    out = D.sparse_attend_absorbed_chunked(x2, lat.cuda(), W_UV.cuda(), idx.cuda(), d_c=d_c, sm_scale=Dl ** -0.5)
+    (out * G.cuda()).sum().backward()
+    assert (x2.grad.cpu() - a.grad).abs().max() / a.grad.abs().max() < 2e-2
 
 
 def test_hisa_two_stage_vs_oracle():

@@ -47,12 +47,16 @@ def hisa_block_logits(q: torch.Tensor, k_pooled: torch.Tensor, w: torch.Tensor, 
     nb = k_pooled.shape[0]
     nb128 = (nb + 127) // 128
     dev = q.device
-    lists = torch.arange(nb128, dtype=torch.int32, device=dev).view(1, -1).expand(T, -1).contiguous()
-    row_cols = torch.full((T,), nb128 * 128, dtype=torch.int32, device=dev)
     bks = (ks // P).to(torch.int32).contiguous()
     bke = ((ke + P - 1) // P).to(torch.int32).clamp(max=nb).contiguous()
-    logits = K.indexer_blocklist_bf16_logits(q, w, k_pooled, lists, row_cols, pos_lo=bks, pos_hi=bke,
-                                             out_scale=sm_scale)
+    # the pooled keys are a flat key tensor: the prefill kernel shares every tile of them between four
+    # queries.  Its columns start at the tile of the lower bound, so the walk starts at block 0 (column =
+    # block id) and the lower bound is masked afterwards.
+    row_cols = (((bke + 127) >> 7) << 7).contiguous()
+    logits = K.indexer_flat_bf16_logits(q, w, k_pooled, torch.zeros_like(bks), bke, row_cols, nb128 * 128,
+                                        out_scale=sm_scale)
+    cols = torch.arange(nb128 * 128, dtype=torch.int32, device=dev).view(1, -1)
+    logits.masked_fill_(cols < bks.view(-1, 1), float("-inf"))
     # force-keep by a +inf score; rows without any valid block keep what they have (no host
     # synchronisation: a scatter of either +inf or the value already there)
     has = (bke > bks).view(-1, 1)

@@ -4,9 +4,10 @@
     sparse_attend_absorbed_chunked OpenDSA/opendsa/ops/sparse_mla.py:51-103
     prepare_ks_ke / prepare_ks_ke_cp  OpenDSA/opendsa/ops/flashkl_warmup.py:41-56, :235-248
 
-Both ops are forward-only (the reference's selection is under torch.no_grad; the sparse
-training backward stays with the reference).  Tensors must live on a CUDA device; there is no
-CPU path.  `patch_opendsa()` rebinds the names the reference imported at module load
+The selection is forward-only (the reference's is under torch.no_grad).  The sparse attention is
+differentiable in q_lat, latent and W_UV: its forward is the attention and up-projection kernels, its
+backward rebuilds the probabilities from the saved log-sum-exp per query chunk and runs as library
+GEMMs.  Tensors must live on a CUDA device; there is no CPU path.  `patch_opendsa()` rebinds the names the reference imported at module load
 (OpenDSA/opendsa/modeling/dsa_attention.py:31-38).
 
 Numerics: scores are computed from bf16-rounded q and k with fp32 accumulation on tcgen05
@@ -139,13 +140,77 @@ def sparse_attend_latent(q_lat, latent, indices, *, sm_scale: float, q_pos: Opti
                                q_pos=None if q_pos is None else q_pos.to(torch.int32).contiguous(), ctx=ctx)
 
 
+def _up_project(ctx: torch.Tensor, W_UV: torch.Tensor) -> torch.Tensor:
+    """[L,H,512] latent context -> [L,H,Dv] through the per-head W_UV (tcgen05 kernel up to Dv = 256)."""
+    if W_UV.shape[1] > 256:
+        return torch.einsum("thl,hvl->thv", ctx.to(W_UV.dtype), W_UV)
+    out_dtype = W_UV.dtype if W_UV.dtype in (torch.bfloat16, torch.float32) else torch.float32
+    out = K.wuv_up_project(ctx, W_UV.to(torch.bfloat16).contiguous(), out_dtype=out_dtype)
+    return out.to(W_UV.dtype)
+
+
+class _SparseAttendAbsorbed(torch.autograd.Function):
+    """Training form of the op.  Forward: the attention kernel (bf16 latent context + fp32 log-sum-exp)
+    and the W_UV kernel; only (q, latent, W_UV, indices, q_pos, ctx, lse) are kept.  Backward: per chunk
+    of queries the probabilities are rebuilt from the saved log-sum-exp (p = exp(s - lse), no second
+    softmax pass) and the five products of the attention backward run as library GEMMs in fp32;
+    d_latent is accumulated with index_add_.  The reference reaches the same gradients by
+    checkpointing _attend_absorbed_chunk and letting autograd replay it
+    (OpenDSA/opendsa/ops/sparse_mla.py:26-48, :96-104)."""
+
+    @staticmethod
+    def forward(fctx, q_lat, latent, W_UV, indices, q_pos, sm_scale, q_chunk):
+        ctx, lse = sparse_attend_latent(q_lat, latent, indices, sm_scale=sm_scale, q_pos=q_pos,
+                                        ctx_dtype=torch.bfloat16)
+        fctx.save_for_backward(q_lat, latent, W_UV, indices, q_pos, ctx, lse)
+        fctx.sm_scale, fctx.q_chunk = sm_scale, q_chunk
+        return _up_project(ctx, W_UV.detach())
+
+    @staticmethod
+    def backward(fctx, d_out):
+        q_lat, latent, W_UV, indices, q_pos, ctx, lse = fctx.saved_tensors
+        scale, L = fctx.sm_scale, q_lat.shape[0]
+        lat = latent.detach().float()
+        Wf = W_UV.detach().float()
+        need_q, need_l, need_w = fctx.needs_input_grad[0], fctx.needs_input_grad[1], fctx.needs_input_grad[2]
+        d_q = torch.empty_like(q_lat, dtype=torch.float32) if need_q else None
+        d_lat = torch.zeros_like(lat) if need_l else None
+        d_W = torch.zeros_like(Wf) if need_w else None
+        for t0 in range(0, L, fctx.q_chunk):
+            t1 = min(t0 + fctx.q_chunk, L)
+            idx = indices[t0:t1].long()
+            valid = (idx >= 0) & (idx <= q_pos[t0:t1].long().view(-1, 1))
+            idx = idx.clamp(min=0)
+            qc = q_lat[t0:t1].detach().float()
+            g = d_out[t0:t1].float()
+            cc = ctx[t0:t1].float()
+            sel = lat[idx]                                                   # [c,K,576]
+            s = torch.einsum("thd,tkd->thk", qc, sel) * scale
+            lse_c = lse[t0:t1].unsqueeze(-1)
+            p = torch.exp(s - lse_c)
+            p = torch.where(valid.unsqueeze(1) & torch.isfinite(lse_c), p, torch.zeros_like(p))
+            if need_w:
+                d_W += torch.einsum("thv,thl->hvl", g, cc)
+            d_ctx = torch.einsum("thv,hvl->thl", g, Wf)                      # [c,H,512]
+            d_p = torch.einsum("thl,tkl->thk", d_ctx, sel[..., :512])
+            delta = (d_ctx * cc).sum(-1, keepdim=True)
+            d_s = p * (d_p - delta) * scale
+            if need_q:
+                d_q[t0:t1] = torch.einsum("thk,tkd->thd", d_s, sel)
+            if need_l:
+                d_sel = torch.einsum("thk,thd->tkd", d_s, qc)
+                d_sel[..., :512] += torch.einsum("thk,thl->tkl", p, d_ctx)
+                d_lat.index_add_(0, idx.reshape(-1), d_sel.reshape(-1, d_sel.shape[-1]))
+        return (None if d_q is None else d_q.to(q_lat.dtype), None if d_lat is None else d_lat.to(latent.dtype),
+                None if d_W is None else d_W.to(W_UV.dtype), None, None, None, None)
+
+
 def sparse_attend_absorbed_chunked(q_lat, latent, W_UV, indices, *, d_c: int, sm_scale: float, cu_seqlens=None,
                                    q_chunk: int = 512, checkpoint: bool = True, q_global_pos=None) -> torch.Tensor:
     """Sparse MLA attention in the absorbed latent space followed by the W_UV up-projection;
-    [Lq, H, Dv].  q_chunk and checkpoint are accepted for signature compatibility and ignored
-    (nothing of size [chunk, K, 576] is ever materialised).  Forward only."""
-    if torch.is_grad_enabled() and (q_lat.requires_grad or latent.requires_grad or W_UV.requires_grad):
-        raise B200DSAError("sparse_attend_absorbed_chunked is forward-only; run the reference op for training")
+    [Lq, H, Dv].  Nothing of size [chunk, K, 576] is materialised in the forward pass, so checkpoint is
+    accepted and ignored; under autograd the op is differentiable in q_lat, latent and W_UV, and q_chunk
+    bounds the [chunk, K, 576] gather of the backward pass (see _SparseAttendAbsorbed)."""
     if d_c != 512:
         raise B200DSAError("d_c must be 512")
     L = q_lat.shape[0]
@@ -155,13 +220,11 @@ def sparse_attend_absorbed_chunked(q_lat, latent, W_UV, indices, *, d_c: int, sm
         q_pos = prepare_ks_ke(cu_seqlens)[1] - 1
     else:
         q_pos = torch.arange(L, device=q_lat.device)
+    if torch.is_grad_enabled() and (q_lat.requires_grad or latent.requires_grad or W_UV.requires_grad):
+        return _SparseAttendAbsorbed.apply(q_lat, latent, W_UV, indices, q_pos, float(sm_scale), int(q_chunk))
     # bf16 context straight from the attention kernel, then the per-head up-projection on tensor cores
     ctx, _ = sparse_attend_latent(q_lat, latent, indices, sm_scale=sm_scale, q_pos=q_pos, ctx_dtype=torch.bfloat16)
-    if W_UV.shape[1] > 256:
-        return torch.einsum("thl,hvl->thv", ctx.to(W_UV.dtype), W_UV)
-    out_dtype = W_UV.dtype if W_UV.dtype in (torch.bfloat16, torch.float32) else torch.float32
-    out = K.wuv_up_project(ctx, W_UV.to(torch.bfloat16).contiguous(), out_dtype=out_dtype)
-    return out.to(W_UV.dtype)
+    return _up_project(ctx, W_UV)
 
 
 def patch_opendsa() -> None:
