@@ -764,13 +764,30 @@ def main():
                                     "sample": f"{n_req} requests of the {B}-request batch shape at context {ctx}, "
                                               f"all stages (quantise, score, top-k, attention), {dt:.1f} s"}
         if world == 1 and not args.skip_configs:
-            # tensor-pipe denominators from the library's own probe kernel, then the other configurations;
-            # the decode state is released first (the configurations build their own)
+            # the rate at which the indexer's own bytes can be read at all: the pages of the cache in
+            # block-table order through bare bulk copies (two pages per ring slot, as the kernel loads them)
+            pages = state.block_table[:, :(shard_len + state.page_size - 1) // state.page_size].reshape(-1).long()
+            offs = (pages * (state.page_size * 132)).contiguous()
+            gbs = step.K.hbm_read_gbs(state.k_cache, offs, state.page_size * 132, chunks_per_stage=2)
+            line["roofline"]["read_probe"] = {
+                "gbs": round(gbs, 1), "frac_of_probe": round(line["roofline"]["achieved"] / gbs, 4),
+                "how": "the same pages in block-table order pulled into a five-slot shared-memory ring by bare "
+                       "bulk copies, two CTAs per SM, nothing computed and nothing written"}
+            # tensor-pipe denominators from the library's own probe kernel, then the other configurations
+            # (the decode state is released first: the configurations build their own)
             fp8_peak = step.K.mma_peak_tflops(True, device=dev)
             bf16_peak = step.K.mma_peak_tflops(False, device=dev)
             line["tensor_peaks"] = {"fp8_tflops_probe": round(fp8_peak, 1), "bf16_tflops_probe": round(bf16_peak, 1),
                                     "how": "back-to-back M=128 N=256 tcgen05 MMAs on shared-memory operands, one CTA "
                                            "per SM, best of 5 launches of about 2 ms"}
+            # which bf16 instruction shapes run at the full rate of the pipe (SM clocks per instruction, counted
+            # inside the kernel): the table the attention kernel's tile choice rests on
+            shapes = {}
+            for m_, n_, ts_ in ((128, 256, False), (128, 64, False), (128, 64, True), (64, 256, False), (64, 64, True)):
+                clk = step.K.mma_shape_clocks(m_, n_, ts_, device=dev)
+                shapes[f"M{m_} N{n_} K16 A-{'tmem' if ts_ else 'smem'}"] = {
+                    "clocks": round(clk, 1), "flops_per_sm_clock": round(2.0 * m_ * n_ * 16 / clk)}
+            line["tensor_peaks"]["bf16_shapes"] = shapes
             graphed = None
             del state, step, dev_q, in_dev, out_dev
             torch.cuda.empty_cache()

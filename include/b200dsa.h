@@ -54,6 +54,20 @@ typedef struct b200dsa_peer_link {
  * roofline denominator of this GPU under its own clocks and power cap.  No counterpart in the
  * reference. */
 int b200dsa_mma_peak_probe(int32_t fp8, int32_t ctas, int32_t iters, int32_t* status, void* stream);
+/* The same loop for one bf16 instruction shape: m = 64 or 128, n = 32, 64, 128 or 256, the A operand from
+ * shared memory (a_from_tmem = 0) or from tensor memory.  One launch issues ctas * iters * 4 MMAs of
+ * 2*m*n*16 flops; clocks_out (optional, int64 [ctas]) receives each CTA's SM clock count from its first
+ * issue to the retirement of its last MMA, so clocks per instruction do not depend on the clock rate.
+ * Used to decide tile shapes (which shapes run at the full rate of the pipe). */
+int b200dsa_mma_shape_probe(int32_t m, int32_t n, int32_t a_from_tmem, int32_t ctas, int32_t iters,
+                            int64_t* clocks_out, int32_t* status, void* stream);
+/* HBM read probe: `ctas` CTAs (two per SM is what the decode indexer runs) pull the chunks
+ * base + offsets[i] (chunk_bytes each, a multiple of 16; chunks_per_stage of them, 1 to 4, share a ring slot
+ * of at most 16896 bytes) into a five-stage shared-memory ring with bulk copies and drop them.  Timed by the
+ * caller: the rate at which that list of chunks can be read at all, e.g. the pages of a paged cache in
+ * block-table order. */
+int b200dsa_hbm_read_probe(const void* base, const int64_t* offsets, int32_t n_chunks, int32_t chunk_bytes,
+                           int32_t chunks_per_stage, int32_t ctas, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Row-wise top-k selection over fp32 scores.

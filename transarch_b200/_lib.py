@@ -21,6 +21,8 @@ SIGNATURES = {
     "b200dsa_abi_version": [],
     "b200dsa_last_error": [],
     "b200dsa_mma_peak_probe": [_i32, _i32, _i32, _vp, _vp],
+    "b200dsa_mma_shape_probe": [_i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
+    "b200dsa_hbm_read_probe": [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp],
     "b200dsa_topk_select": [_vp, _i64, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _i32, _vp,
                             _i32, _i64, _vp, _vp, _vp, _i64, _vp],
     "b200dsa_topk_select_split": [_vp, _i64, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _i32, _vp, _vp,

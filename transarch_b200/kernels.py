@@ -722,6 +722,44 @@ def mma_peak_tflops(fp8: bool = True, *, iters: int = 4096, reps: int = 5, devic
     return best
 
 
+def mma_shape_clocks(m: int, n: int, a_from_tmem: bool, *, iters: int = 2048, device=None) -> float:
+    """SM clocks per bf16 tcgen05 MMA of shape m x n x 16 issued back to back, the A operand in shared or
+    tensor memory (one CTA per SM, counted inside the kernel); see b200dsa_mma_shape_probe.  Synchronises."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    ctas = torch.cuda.get_device_properties(dev).multi_processor_count
+    clocks = torch.zeros(ctas, dtype=torch.int64, device=dev)
+    for _ in range(2):
+        check(_lib.load().b200dsa_mma_shape_probe(m, n, int(a_from_tmem), ctas, iters, ptr(clocks),
+                                                  ptr(status_word(dev)), stream_ptr()), "b200dsa_mma_shape_probe")
+    torch.cuda.synchronize()
+    return float(clocks.float().median()) / (iters * 4)
+
+
+def hbm_read_gbs(buf: torch.Tensor, offsets: torch.Tensor, chunk_bytes: int, *, chunks_per_stage: int = 1,
+                 ctas_per_sm: int = 2, reps: int = 10) -> float:
+    """GB/s at which the chunks buf + offsets[i] (int64 byte offsets, chunk_bytes each) are read by bare bulk
+    copies into a shared-memory ring; see b200dsa_hbm_read_probe.  Synchronises."""
+    require_cuda(buf, offsets)
+    if offsets.dtype != torch.int64 or not offsets.is_contiguous():
+        raise _lib.B200DSAError("offsets must be contiguous int64")
+    ctas = torch.cuda.get_device_properties(buf.device).multi_processor_count * ctas_per_sm
+    n = offsets.numel() // chunks_per_stage * chunks_per_stage
+    st = status_word(buf.device)
+
+    def run():
+        check(_lib.load().b200dsa_hbm_read_probe(ptr(buf), ptr(offsets), n, chunk_bytes, chunks_per_stage, ctas,
+                                                 ptr(st), stream_ptr()), "b200dsa_hbm_read_probe")
+    for _ in range(2):
+        run()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    return n * chunk_bytes * reps / (e0.elapsed_time(e1) * 1e-3) / 1e9
+
+
 def _f32c(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     return None if t is None else t.to(torch.float32).contiguous()
 
