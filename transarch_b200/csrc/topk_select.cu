@@ -270,6 +270,99 @@ __device__ void sort_desc(uint64_t* a, int n) {
   else bitonic_sort_desc(a, n);
 }
 
+// Descending sort of the n winners in `a` by counting: 4096 buckets that are linear in the score between the
+// smallest and the largest finite winner (monotone in the key, so buckets never interleave), an exclusive
+// scan of the bucket sizes from the top, a scatter into `tmp`, and an exact rank inside each bucket by
+// comparing the full 64-bit keys.  Five passes over the keys instead of the 66 compare-exchange stages of a
+// 2048-key bitonic sort.  Returns false, with `a` untouched, when a bucket would hold more than kBucketMax keys
+// (long runs of equal scores): the caller then sorts by compare-exchange.  All threads call it.
+constexpr int kBucketMax = 48;
+__device__ bool bucket_sort_desc(uint64_t* a, int n, uint64_t* tmp, uint32_t* hist, uint32_t* s_seg) {
+  const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
+  __shared__ uint32_t s_lo, s_hi, s_big;
+  if (tid == 0) {
+    s_lo = 0xffffffffu;
+    s_hi = 0u;
+    s_big = 0u;
+  }
+  for (int i = tid; i < kHistBins; i += nthr) hist[i] = 0;
+  __syncthreads();
+  // range of the finite scores (ordered bits compare like the floats)
+  constexpr uint32_t kPosInf = 0xff800000u;   // float_to_ordered(+inf)
+  uint32_t lo = 0xffffffffu, hi = 0u;
+  for (int i = tid; i < n; i += nthr) {
+    const uint32_t o = static_cast<uint32_t>(a[i] >> 32);
+    lo = min(lo, o);
+    if (o < kPosInf) hi = max(hi, o);
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+    hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+  }
+  if (lane == 0) {
+    atomicMin(&s_lo, lo);
+    atomicMax(&s_hi, hi);
+  }
+  __syncthreads();
+  const float vmin = ordered_to_float(s_lo);
+  const float vmax = ordered_to_float(max(s_hi, s_lo));
+  const float span = vmax - vmin;
+  const float scale = (span > 0.f && span <= 3.0e38f) ? 4094.0f / span : 0.f;
+  auto bucket = [&](uint64_t key) -> int {
+    const uint32_t o = static_cast<uint32_t>(key >> 32);
+    if (o >= kPosInf) return kHistBins - 1;
+    const float x = (ordered_to_float(o) - vmin) * scale;      // monotone in the score
+    return min(kHistBins - 2, max(0, static_cast<int>(x)));
+  };
+  for (int i = tid; i < n; i += nthr) atomicAdd(&hist[bucket(a[i])], 1u);
+  __syncthreads();
+  // exclusive scan from the top: thread t owns the kHistBins / nthr bins below bin (kHistBins - t * per)
+  const int per = kHistBins / nthr;           // 4, 8 or 16
+  uint32_t sum = 0, big = 0;
+  const int top = kHistBins - 1 - tid * per;  // highest bin of this thread
+  for (int j = 0; j < per; ++j) {
+    const uint32_t c = hist[top - j];
+    sum += c;
+    big = max(big, c);
+  }
+  uint32_t incl = sum;
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  for (int o = 16; o > 0; o >>= 1) big = max(big, __shfl_xor_sync(0xffffffffu, big, o));
+  if (lane == 31) s_seg[warp] = incl;
+  if (lane == 0 && big > static_cast<uint32_t>(kBucketMax)) atomicMax(&s_big, big);
+  __syncthreads();
+  if (s_big != 0u) return false;   // uniform: every thread reads the same word
+  uint32_t before = incl - sum;
+  for (int w = 0; w < warp; ++w) before += s_seg[w];
+  // hist[b] <- first output slot of bucket b
+  for (int j = 0; j < per; ++j) {
+    const uint32_t c = hist[top - j];
+    hist[top - j] = before;
+    before += c;
+  }
+  __syncthreads();
+  for (int i = tid; i < n; i += nthr) {
+    const uint64_t key = a[i];
+    tmp[atomicAdd(&hist[bucket(key)], 1u)] = key;   // afterwards hist[b] = one past the last slot of bucket b
+  }
+  __syncthreads();
+  for (int i = tid; i < n; i += nthr) {
+    const uint64_t key = tmp[i];
+    const int b = bucket(key);
+    const int end = static_cast<int>(hist[b]);
+    const int start = (b == kHistBins - 1) ? 0 : static_cast<int>(hist[b + 1]);
+    int rank = 0;
+    for (int j = start; j < end; ++j) rank += tmp[j] > key;
+    a[start + rank] = key;
+  }
+  __syncthreads();
+  (void)nwarps;
+  return true;
+}
+
 // Find the highest bin d such that (#elements in bins >= d) >= need.  All threads call it
 // (it contains block barriers).  Writes res[0]=d (or -1 when the whole histogram holds fewer
 // than need), res[1]=count in bins above d, res[2]=hist[d].  Segment s (128 bins) covers bins
@@ -712,10 +805,14 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
 
   // ------------------------------------------------------------------ order + write
   if (p.sorted) {
-    int n_pow2 = 32;
-    while (n_pow2 < n_sel) n_pow2 <<= 1;
-    for (int i = n_sel + tid; i < n_pow2; i += nthr) sel[i] = 0;
-    sort_desc(sel, n_pow2);
+    // counting sort into score buckets; compare-exchange only for short lists and for rows whose scores
+    // crowd into a few buckets (the candidate list is free to serve as the scratch array by now)
+    if (n_sel <= 64 || !bucket_sort_desc(sel, n_sel, cand, hist, s_seg)) {
+      int n_pow2 = 32;
+      while (n_pow2 < n_sel) n_pow2 <<= 1;
+      for (int i = n_sel + tid; i < n_pow2; i += nthr) sel[i] = 0;
+      sort_desc(sel, n_pow2);
+    }
   }
   write_row(sel, min(n_sel, k));
 }
