@@ -286,6 +286,21 @@ int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const float* weigh
                                           float* logits_gated, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Token logits of every query on its OWN list of key positions (MISA stage 2 in prefill: all 64 heads on the
+ * stage-1 candidates, MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/misa_ops.py:517-650, T2):
+ *   logits[r, c] = out_scale * sum_h weights[r,h]*relu(<q[r,h,:], keys[cand[r,c],:]>) for c < row_cols[r];
+ *   -inf where cand[r,c] is negative, not below n_keys or outside [pos_lo[r], pos_hi[r]) (intervals optional).
+ * A tile's 128 key rows are gathered by 16-byte asynchronous copies into the tensor core's swizzled layout;
+ * one N = 64 pass per (query, 128 candidates).  q_bf16 [n_rows, 64, 128], keys_bf16 [n_keys, 128],
+ * cand int32 [n_rows, cand_stride], weights fp32 [n_rows, 64].
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_indexer_gather_bf16_logits(const void* q_bf16, const float* weights, const void* keys_bf16,
+                                       int32_t n_keys, const int32_t* cand, int64_t cand_stride,
+                                       const int32_t* row_cols, const int32_t* pos_lo, const int32_t* pos_hi,
+                                       int32_t n_rows, int32_t max_cols, float out_scale, float* logits,
+                                       int64_t logits_stride, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Prefill token logits over flat bf16 keys with per-query intervals (tcgen05, four queries per key tile):
  *   column c of row r is key position col0[r] + c, col0[r] = 128 * (pos_lo[r] / 128);
  *   logits[r, c] = out_scale * sum_h weights[r,h]*relu(<q[r,h,:], keys[pos,:]>) for pos_lo[r] <= pos <
@@ -297,6 +312,15 @@ int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const float* weigh
  *   q_bf16 [n_rows, 64, 128], keys_bf16 [n_keys, 128] (16-byte aligned), weights [n_rows, 64] fp32,
  *   row_cols [n_rows] = 128 * ceil(pos_hi/128) - col0 (a multiple of 128).
  * ------------------------------------------------------------------------------------- */
+/* The routed form (MISA stage 1 in prefill, misa_ops.py:415-515 with its block_Q = 128 / H query tiling):
+ * q8_bf16 [n_rows, 8, 128] holds the 8 heads the router kept for each query, weights8 [n_rows, 8] their
+ * weights; 32 queries share each key tile (N = 256 = 32 x 8), so the contraction costs an eighth of the
+ * all-head form. */
+int b200dsa_indexer_flat_bf16_logits_routed(const void* q8_bf16, const float* weights8, const void* keys_bf16,
+                                            int32_t n_keys, const int32_t* pos_lo, const int32_t* pos_hi,
+                                            const int32_t* row_cols, int32_t n_rows, int32_t max_cols,
+                                            float out_scale, float* logits, int64_t logits_stride,
+                                            int32_t* status, void* stream);
 int b200dsa_indexer_flat_bf16_logits(const void* q_bf16, const float* weights, const void* keys_bf16,
                                      int32_t n_keys, const int32_t* pos_lo, const int32_t* pos_hi,
                                      const int32_t* row_cols, int32_t n_rows, int32_t max_cols,

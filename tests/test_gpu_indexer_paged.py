@@ -120,3 +120,52 @@ def test_flat_prefill_groups_of_four_queries_match_the_per_query_kernel():
         a, b = int(lo[r]), int(hi[r])
         c0 = int(col0[r])
         assert O.rel_err(got[r, a - c0:b - c0].cpu().view(1, -1), sc[a:b].view(1, -1)) < 2e-3
+
+
+def test_routed_flat_kernel_and_gather_kernel():
+    """The two kernels of the routed prefill by themselves: eight gathered heads with 32 queries per key tile
+    (row count not a multiple of 32, two documents, a query without keys), and all-head scores on per-query
+    candidate lists with missing (-1), out-of-range and masked entries."""
+    from transarch_b200 import _lib, kernels as K
+    g = torch.Generator().manual_seed(77)
+    T, N = 75, 1500
+    k = torch.randn(N, 128, generator=g).bfloat16()
+    q8 = torch.randn(T, 8, 128, generator=g).bfloat16()
+    w8 = torch.randn(T, 8, generator=g) / 4
+    ke = torch.randint(1, N + 1, (T,), generator=g, dtype=torch.int32)
+    ks = torch.zeros(T, dtype=torch.int32)
+    ks[40:] = torch.minimum(torch.full((T - 40,), 700, dtype=torch.int32), ke[40:] - 1)
+    ke[7] = ks[7]                                                     # no visible key at all
+    col0 = (ks >> 7) << 7
+    row_cols = ((((ke + 127) >> 7) << 7) - col0).clamp(min=0)
+    cols = ((N + 127) // 128) * 128
+    out = K.indexer_flat_bf16_logits_routed(q8.cuda(), w8.cuda(), k.cuda(), ks.cuda(), ke.cuda(), row_cols.cuda(), cols,
+                                            out_scale=0.25).cpu()
+    ref = O.mask_interval(O.indexer_scores(q8.float(), k.float(), w8, 0.25), ks.long(), ke.long())
+    for t in range(T):
+        n = int(row_cols[t])
+        got = out[t, :n]
+        want = ref[t, int(col0[t]):int(col0[t]) + n]
+        want = torch.cat([want, torch.full((n - want.numel(),), float("-inf"))])
+        fin = torch.isfinite(want)
+        assert torch.equal(torch.isfinite(got), fin), t
+        if fin.any():
+            assert O.rel_err(got[fin], want[fin]) < 2e-3, t
+    # gather kernel
+    q = torch.randn(T, 64, 128, generator=g).bfloat16()
+    w = torch.randn(T, 64, generator=g) / 8
+    n_cand = 300
+    cand = torch.randint(0, N, (T, n_cand), generator=g, dtype=torch.int32)
+    cand[:, 17] = -1
+    cand[3, 40] = N + 5                                               # beyond the keys: dropped, not read
+    cand[5, 200:] = -1
+    got = K.indexer_gather_bf16_logits(q.cuda(), w.cuda(), k.cuda(), cand.cuda(), pos_lo=ks.cuda(), pos_hi=ke.cuda(),
+                                       out_scale=0.5).cpu()
+    full = O.mask_interval(O.indexer_scores(q.float(), k.float(), w, 0.5), ks.long(), ke.long())
+    okc = (cand >= 0) & (cand < N)
+    want = torch.gather(full, 1, cand.clamp(0, N - 1).long())
+    want = torch.where(okc, want, torch.full_like(want, float("-inf")))
+    fin = torch.isfinite(want)
+    assert torch.equal(torch.isfinite(got), fin)
+    assert O.rel_err(got[fin], want[fin]) < 2e-3
+    assert _lib.read_status(torch.device("cuda")) == 0

@@ -104,11 +104,15 @@ def test_pooled_key_cache_follows_the_cache_bit_exactly():
         assert torch.equal(torch.gather(x[0], 1, ox), torch.gather(y[0], 1, oy))
 
 
-@pytest.mark.parametrize("use_qnorm", [True, False])
-def test_misa_mqa_logits_prefill(use_qnorm):
+@pytest.mark.parametrize("use_qnorm,s1,two_docs", [(True, 512, False), (False, 512, False), (True, 2048, False),
+                                                   (True, 384, True)])
+def test_misa_mqa_logits_prefill(use_qnorm, s1, two_docs):
+    """s1 = 512 / 384 of 3000 keys: the two-stage form (eight gathered heads, 32 queries per key tile, then
+    all heads on the gathered candidates); s1 = 2048: the one-pass form.  two_docs: the later queries belong
+    to a second document that starts inside a key tile."""
     from transarch_b200 import misa as M
     g = torch.Generator().manual_seed(33)
-    Mq, N, s1 = 24, 3000, 512
+    Mq, N = 40 if two_docs else 24, 3000
     k = torch.randn(N, 128, generator=g)
     kq, sc = O.quant_fp8_rows(k)
     q = torch.randn(Mq, 64, 128, generator=g)
@@ -116,6 +120,8 @@ def test_misa_mqa_logits_prefill(use_qnorm):
     q_fp8, wf = O.quant_q_fold_weights(q, w, 128 ** -0.5, 64 ** -0.5)
     ke = torch.arange(N - Mq, N, dtype=torch.int32) + 1
     ks = torch.zeros(Mq, dtype=torch.int32)
+    if two_docs:
+        ks[Mq // 2:] = 1111
     hidx = O.qnorm_head_topk(q, 8) if use_qnorm else None
     logits, cand = M.misa_mqa_logits(q_fp8.cuda(), (kq.cuda(), sc.cuda()), wf.cuda(),
                                      None if hidx is None else hidx.cuda(), ks.cuda(), ke.cuda(), use_qnorm, 8, s1,

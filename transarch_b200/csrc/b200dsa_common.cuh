@@ -106,6 +106,19 @@ __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_
                : "memory");
 }
 
+// 16-byte asynchronous copies issued by ordinary threads (row gathers).  A thread's arrival on `bar` is
+// delivered once all its earlier copies have landed; the barrier's count must include these arrivals
+// ("noinc").  Data written this way is read by the tensor core only after fence_proxy_async().
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+  const uint32_t sz = valid ? 16u : 0u;  // 0 -> the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_mbar_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------------------
 // tcgen05: TMEM allocation, MMA, commit, load
 // ---------------------------------------------------------------------------------------

@@ -26,18 +26,23 @@
 namespace b200dsa {
 
 constexpr int kFlatTile = 128;
-constexpr int kFlatGroup = 4;                     // queries per MMA
+constexpr int kFlatGroup = 4;                     // queries per MMA with all 64 heads
 constexpr int kFlatHeads = 64;
+// Routed form (MISA stage 1): the router kept kRoutedHeads of a query's heads and they were gathered into
+// q [n_rows, 8, 128]; an MMA then serves 32 queries (N = 256 = 32 x 8), which is where the routing saves
+// flops: the key tile is contracted with 8 heads per query instead of 64.
+constexpr int kRoutedHeads = 8;
 constexpr int kFlatThreads = 320;
 constexpr int kFlatStages = 4;
 constexpr int kFlatStageBytes = kFlatTile * 128 * 2;          // 32 KB
 constexpr int kFlatQBytes = kFlatGroup * kFlatHeads * 128 * 2;  // 64 KB
-constexpr int kFlatMaxGroups = 1024;              // groups per launch (4096 rows)
-constexpr int kFlatWBytes = 8 * 128 * 4;                      // per epilogue warp: the weights of its two queries
-constexpr int kFlatSmem = kFlatStages * kFlatStageBytes + kFlatQBytes + 1024 + 256 + kFlatWBytes;
+constexpr int kFlatMaxGroups = 1024;              // groups per launch (4096 rows; 32768 in the routed form)
+constexpr int kFlatWBytes = 8 * 128 * 4;                      // per epilogue warp: the weights of its queries
+constexpr int kFlatRowParamBytes = 8 * 16 * 16;               // routed form, per epilogue warp: lo, hi, col0, ncol of 16 queries
+constexpr int kFlatSmem = kFlatStages * kFlatStageBytes + kFlatQBytes + 1024 + 256 + kFlatWBytes + kFlatRowParamBytes;
 
 struct FlatParams {
-  const float* weights;      // [n_rows, 64]
+  const float* weights;      // [n_rows, heads per query]
   const int32_t* pos_lo;     // [n_rows]
   const int32_t* pos_hi;     // [n_rows]
   const int32_t* row_cols;   // [n_rows] columns of the row's range (a multiple of 128)
@@ -49,9 +54,12 @@ struct FlatParams {
   int32_t* status;
 };
 
+template <int kHq>   // heads per query: 64 (all heads) or 8 (routed)
 __global__ void __launch_bounds__(kFlatThreads, 1)
 indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
                     const FlatParams p) {
+  constexpr int kGroup = 256 / kHq;     // queries per MMA (4 or 32)
+  constexpr int kQW = 128 / kHq;        // queries per epilogue warp (2 or 16)
   pdl_launch_dependents();
   pdl_wait_prior();
   extern __shared__ uint8_t smem_dyn[];
@@ -71,13 +79,13 @@ indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   uint64_t* acc_empty = acc_full + 2;           // [2]
   float* w_mem = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);   // [8 warps][2 queries][64]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n_groups = (p.n_rows + kFlatGroup - 1) / kFlatGroup;
+  const int n_groups = (p.n_rows + kGroup - 1) / kGroup;
 
   if (tid == 0) s_abort = 0;
   for (int g = tid; g < n_groups; g += kFlatThreads) {
     int b0 = 0x7fffffff, b1 = 0;
-    for (int j = 0; j < kFlatGroup; ++j) {
-      const int r = g * kFlatGroup + j;
+    for (int j = 0; j < kGroup; ++j) {
+      const int r = g * kGroup + j;
       if (r >= p.n_rows) break;
       const int lo = p.pos_lo[r], hi = min(p.pos_hi[r], p.n_blocks * kFlatTile);
       if (hi > lo && p.row_cols[r] > 0) {
@@ -145,8 +153,8 @@ indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         if (!__all_sync(0xffffffffu, okq)) break;
         if (elect_one()) {
           mbar_arrive_expect_tx(q_full, kFlatQBytes);   // rows beyond the last query are zero-filled
-          tma_load_2d(q_mem, &tmap_q, q_full, 0, grp * kFlatGroup * kFlatHeads);
-          tma_load_2d(q_mem + kFlatQBytes / 2, &tmap_q, q_full, 64, grp * kFlatGroup * kFlatHeads);
+          tma_load_2d(q_mem, &tmap_q, q_full, 0, grp * 256);
+          tma_load_2d(q_mem + kFlatQBytes / 2, &tmap_q, q_full, 64, grp * 256);
         }
         ++qit;
         prev = grp;
@@ -166,7 +174,7 @@ indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     issued = it;
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    constexpr uint32_t idesc = make_idesc(kFmtBF16, kFmtBF16, 128, kFlatGroup * kFlatHeads);
+    constexpr uint32_t idesc = make_idesc(kFmtBF16, kFmtBF16, 128, 256);
     int grp = grp0, prev = -1, it = 0, qit = 0;
     for (int g = g0; g < g1; ++g) {
       while (g >= s_prefix[grp + 1]) ++grp;
@@ -202,9 +210,78 @@ indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int lane_base = (warp & 3) * 32;          // TMEM lanes this warp may read
-    const int qh = (warp >= 6) ? 2 : 0;             // first of the two queries of the group this warp reduces
+    const int qh = (warp >= 6) ? kQW : 0;           // first query of the group this warp reduces
     float* wq = w_mem + (warp - 2) * 128;
     int grp = grp0, prev = -1, it = 0;
+    if constexpr (kHq == kRoutedHeads) {
+      // ---- routed form: 16 queries x 8 heads per warp; the queries' intervals live in shared memory
+      int4* rp = reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(w_mem) + kFlatWBytes) + (warp - 2) * 16;
+      for (int g = g0; g < g1; ++g) {
+        while (g >= s_prefix[grp + 1]) ++grp;
+        if (grp != prev) {
+          __syncwarp();
+          const int r0 = grp * kGroup + qh;
+          if (lane < kQW) {
+            const int r = r0 + lane;
+            int4 v = make_int4(0, 0, 0, 0);
+            if (r < p.n_rows) {
+              v.x = p.pos_lo[r];
+              v.y = p.pos_hi[r];
+              v.z = (v.x >> 7) << 7;
+              v.w = max(0, min(p.row_cols[r], p.logits_cols));
+            }
+            rp[lane] = v;
+          }
+          // 128 weights = 32 lanes x float4 = 16 queries x 8 heads, contiguous in the weight matrix
+          float4 wv = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (r0 + (lane >> 1) < p.n_rows)
+            wv = __ldg(reinterpret_cast<const float4*>(p.weights + static_cast<int64_t>(r0) * kHq) + lane);
+          reinterpret_cast<float4*>(wq)[lane] = wv;
+          __syncwarp();
+          prev = grp;
+        }
+        const int blk = s_b0[grp] + (g - s_prefix[grp]);
+        const int pos = blk * kFlatTile + lane_base + lane;
+        const int as = it & 1;
+        const bool ready = mbar_wait(&acc_full[as], (it >> 1) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, ready)) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + as * 256 + (warp >= 6 ? 128 : 0);
+        uint32_t va[64], vb[64];
+        tmem_ld_32x32(taddr, *reinterpret_cast<uint32_t(*)[32]>(va));
+        tmem_ld_32x32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(va + 32));
+        tc_wait_ld();
+        tmem_ld_32x32(taddr + 64, *reinterpret_cast<uint32_t(*)[32]>(vb));       // lands while queries 0-7 are reduced
+        tmem_ld_32x32(taddr + 96, *reinterpret_cast<uint32_t(*)[32]>(vb + 32));
+        const int r0 = grp * kGroup + qh;
+#pragma unroll
+        for (int jq = 0; jq < kQW; ++jq) {
+          if (jq == 8) {
+            tc_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&acc_empty[as]);       // both halves are in registers
+          }
+          const uint32_t* v = (jq < 8 ? va : vb) + (jq & 7) * 8;
+          const float4 w0 = reinterpret_cast<const float4*>(wq + jq * 8)[0];     // same address in every lane
+          const float4 w1 = reinterpret_cast<const float4*>(wq + jq * 8)[1];
+          float a0 = fmaxf(__uint_as_float(v[0]), 0.f) * w0.x, a1 = fmaxf(__uint_as_float(v[1]), 0.f) * w0.y;
+          a0 = fmaf(fmaxf(__uint_as_float(v[2]), 0.f), w0.z, a0);
+          a1 = fmaf(fmaxf(__uint_as_float(v[3]), 0.f), w0.w, a1);
+          a0 = fmaf(fmaxf(__uint_as_float(v[4]), 0.f), w1.x, a0);
+          a1 = fmaf(fmaxf(__uint_as_float(v[5]), 0.f), w1.y, a1);
+          a0 = fmaf(fmaxf(__uint_as_float(v[6]), 0.f), w1.z, a0);
+          a1 = fmaf(fmaxf(__uint_as_float(v[7]), 0.f), w1.w, a1);
+          const int4 q = rp[jq];
+          const int c = pos - q.z;
+          if (r0 + jq < p.n_rows && c >= 0 && c < q.w) {            // inside the row's column range
+            const bool keep = pos >= q.x && pos < q.y;
+            p.logits[static_cast<int64_t>(r0 + jq) * p.logits_stride + c] = keep ? (a0 + a1) * p.out_scale : -INFINITY;
+          }
+        }
+        ++it;
+      }
+    } else {
+      // ---- all heads: two queries x 64 heads per warp
     int lo[2], hi[2], col0[2], ncol[2];
     for (int g = g0; g < g1; ++g) {
       while (g >= s_prefix[grp + 1]) ++grp;
@@ -212,7 +289,7 @@ indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         __syncwarp();
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          const int r = grp * kFlatGroup + qh + j;
+          const int r = grp * kGroup + qh + j;
           lo[j] = hi[j] = col0[j] = ncol[j] = 0;
           if (r < p.n_rows) {
             lo[j] = p.pos_lo[r];
@@ -222,7 +299,7 @@ indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
           }
         }
         // 128 weights = 32 lanes x float4: rows r0, r0+1 are contiguous in the weight matrix
-        const int r0 = grp * kFlatGroup + qh;
+        const int r0 = grp * kGroup + qh;
         float4 wv = make_float4(0.f, 0.f, 0.f, 0.f);
         if (r0 + (lane >> 4) < p.n_rows)
           wv = __ldg(reinterpret_cast<const float4*>(p.weights + static_cast<int64_t>(r0) * kFlatHeads) + lane);
@@ -264,7 +341,7 @@ indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       mbar_arrive(&acc_empty[as]);
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const int r = grp * kFlatGroup + qh + j;
+        const int r = grp * kGroup + qh + j;
         const int c = pos - col0[j];
         if (r < p.n_rows && c >= 0 && c < ncol[j]) {          // inside the row's column range
           const bool keep = pos >= lo[j] && pos < hi[j];
@@ -272,6 +349,7 @@ indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         }
       }
       ++it;
+    }
     }
   }
 
@@ -299,11 +377,12 @@ void set_last_error(const char* msg);
 
 using namespace b200dsa;
 
-extern "C" int b200dsa_indexer_flat_bf16_logits(const void* q_bf16, const float* weights, const void* keys_bf16,
-                                                int32_t n_keys, const int32_t* pos_lo, const int32_t* pos_hi,
-                                                const int32_t* row_cols, int32_t n_rows, int32_t max_cols,
-                                                float out_scale, float* logits, int64_t logits_stride,
-                                                int32_t* status, void* stream) {
+template <int kHq>
+static int flat_launch(const void* q_bf16, const float* weights, const void* keys_bf16, int32_t n_keys,
+                       const int32_t* pos_lo, const int32_t* pos_hi, const int32_t* row_cols, int32_t n_rows,
+                       int32_t max_cols, float out_scale, float* logits, int64_t logits_stride, int32_t* status,
+                       void* stream) {
+  constexpr int kGroup = 256 / kHq;
   if (n_rows == 0) return B200DSA_OK;
   if (!q_bf16 || !weights || !keys_bf16 || !pos_lo || !pos_hi || !row_cols || !logits || !status || n_rows < 0 ||
       n_keys < 1 || max_cols < 0 || logits_stride < max_cols) {
@@ -330,7 +409,7 @@ extern "C" int b200dsa_indexer_flat_bf16_logits(const void* q_bf16, const float*
       return B200DSA_ECUDA;
     }
   }
-  cudaError_t e = cudaFuncSetAttribute(indexer_flat_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFlatSmem);
+  cudaError_t e = cudaFuncSetAttribute(indexer_flat_kernel<kHq>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFlatSmem);
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;
@@ -338,13 +417,13 @@ extern "C" int b200dsa_indexer_flat_bf16_logits(const void* q_bf16, const float*
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int rows_per_launch = kFlatMaxGroups * kFlatGroup;
+  const int rows_per_launch = kFlatMaxGroups * kGroup;
   for (int r0 = 0; r0 < n_rows; r0 += rows_per_launch) {
     const int nr = n_rows - r0 < rows_per_launch ? n_rows - r0 : rows_per_launch;
-    const uint8_t* qbase = static_cast<const uint8_t*>(q_bf16) + static_cast<int64_t>(r0) * kFlatHeads * 256;
-    cuuint64_t dims[2] = {128, static_cast<cuuint64_t>(nr) * kFlatHeads};
+    const uint8_t* qbase = static_cast<const uint8_t*>(q_bf16) + static_cast<int64_t>(r0) * kHq * 256;
+    cuuint64_t dims[2] = {128, static_cast<cuuint64_t>(nr) * kHq};
     cuuint64_t strides[1] = {256};
-    cuuint32_t box[2] = {64, kFlatGroup * kFlatHeads};
+    cuuint32_t box[2] = {64, 256};
     if (enc(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint8_t*>(qbase), dims, strides, box, es,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
@@ -352,7 +431,7 @@ extern "C" int b200dsa_indexer_flat_bf16_logits(const void* q_bf16, const float*
       return B200DSA_ECUDA;
     }
     FlatParams p{};
-    p.weights = weights + static_cast<int64_t>(r0) * kFlatHeads;
+    p.weights = weights + static_cast<int64_t>(r0) * kHq;
     p.pos_lo = pos_lo + r0;
     p.pos_hi = pos_hi + r0;
     p.row_cols = row_cols + r0;
@@ -363,7 +442,7 @@ extern "C" int b200dsa_indexer_flat_bf16_logits(const void* q_bf16, const float*
     p.logits_stride = logits_stride;
     p.logits_cols = max_cols;
     p.status = status;
-    e = launch_chained(indexer_flat_kernel, dim3(sms), dim3(kFlatThreads), kFlatSmem, static_cast<cudaStream_t>(stream),
+    e = launch_chained(indexer_flat_kernel<kHq>, dim3(sms), dim3(kFlatThreads), kFlatSmem, static_cast<cudaStream_t>(stream),
                        mk, mq, p);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) {
@@ -372,4 +451,23 @@ extern "C" int b200dsa_indexer_flat_bf16_logits(const void* q_bf16, const float*
     }
   }
   return B200DSA_OK;
+}
+
+extern "C" int b200dsa_indexer_flat_bf16_logits(const void* q_bf16, const float* weights, const void* keys_bf16,
+                                                int32_t n_keys, const int32_t* pos_lo, const int32_t* pos_hi,
+                                                const int32_t* row_cols, int32_t n_rows, int32_t max_cols,
+                                                float out_scale, float* logits, int64_t logits_stride,
+                                                int32_t* status, void* stream) {
+  return flat_launch<kFlatHeads>(q_bf16, weights, keys_bf16, n_keys, pos_lo, pos_hi, row_cols, n_rows, max_cols,
+                                 out_scale, logits, logits_stride, status, stream);
+}
+
+extern "C" int b200dsa_indexer_flat_bf16_logits_routed(const void* q8_bf16, const float* weights8,
+                                                       const void* keys_bf16, int32_t n_keys, const int32_t* pos_lo,
+                                                       const int32_t* pos_hi, const int32_t* row_cols,
+                                                       int32_t n_rows, int32_t max_cols, float out_scale,
+                                                       float* logits, int64_t logits_stride, int32_t* status,
+                                                       void* stream) {
+  return flat_launch<kRoutedHeads>(q8_bf16, weights8, keys_bf16, n_keys, pos_lo, pos_hi, row_cols, n_rows, max_cols,
+                                   out_scale, logits, logits_stride, status, stream);
 }

@@ -111,7 +111,10 @@ struct PagedIndexerParams {
 // kList (fp8 only): rows address the cache through per-row lists of logical 128-key blocks.  A template
 // parameter, not a run-time test: the plain decode kernel is bound by HBM closely enough that two extra
 // branches per tile in its producer and epilogue cost 4 % of its time.
-template <bool kFp8, bool kEmit = false, bool kList = false>
+// kGather (bf16 only): the "table" row of a query is a list of arbitrary key positions (MISA stage 2: the
+// stage-1 candidates); a tile's 128 rows are gathered with 16-byte asynchronous copies into the swizzled
+// layout, column c of the row is candidate c.
+template <bool kFp8, bool kEmit = false, bool kList = false, bool kGather = false>
 __global__ void __launch_bounds__(kThreads, PagedCfg<kFp8, kEmit>::kCtasPerSm)
 indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
                      const PagedIndexerParams p) {
@@ -166,7 +169,7 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       s_prefix[r + 1] = acc;
     }
     for (int s = 0; s < Cfg::kStages; ++s) {
-      mbar_init(&full[s], 1);
+      mbar_init(&full[s], kGather ? 32 : 1);   // gather: the producer warp's 32 lanes, each after its copies
       mbar_init(&empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -263,7 +266,7 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
         tbl_entry = (lane < 4 && e < p.table_cols) ? trow[e] : -1;
       }
       const int npages = (nkeys + P - 1) >> p_shift;
-      if (!listed && (tbl_base < 0 || first < tbl_base || first + npages > tbl_base + 32)) {
+      if (!listed && !kGather && (tbl_base < 0 || first < tbl_base || first + npages > tbl_base + 32)) {
         tbl_base = first;
         const int e = tbl_base + lane;
         tbl_entry = (e < tbl_len) ? (p.table ? trow[e] : ident0 + e) : -1;
@@ -299,6 +302,28 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
           }
           if (nvalid != npages) atomicMax(p.status, kDevBadIndex);
         }
+      } else if constexpr (kGather) {
+        // candidate positions of the tile: four per lane; a row is 16 copies of 16 bytes, two rows per instruction
+        int idx4[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = key0 + u * 32 + lane;
+          const int v = (i < cols) ? __ldg(trow + i) : -1;
+          idx4[u] = (v >= 0 && v < p.num_pages) ? v : -1;
+        }
+        const int c16 = lane & 15, half = lane >> 4;
+        const uint32_t dst0 = smem_u32(dst) + (c16 >> 3) * (Cfg::kStageBytes / 2);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int h = 0; h < 16; ++h) {
+            const int r = u * 32 + 2 * h + half;
+            const int idx = __shfl_sync(0xffffffffu, idx4[u], 2 * h + half);
+            const uint8_t* src = p.cache + static_cast<int64_t>(idx < 0 ? 0 : idx) * (kDim * 2) + c16 * 16;
+            cp_async_16(dst0 + r * 128 + (((c16 & 7) ^ (r & 7)) << 4), src, idx >= 0);   // missing rows are zero-filled
+          }
+        }
+        cp_async_mbar_arrive(&full[s]);
       } else {
         const int blk = __shfl_sync(0xffffffffu, tbl_entry, (first - tbl_base) & 31);
         if (elect_one()) {
@@ -315,6 +340,7 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       ++it;
     }
     issued = it;
+    if constexpr (kGather) cp_async_wait_all();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     // Whole warp in the loop; one elected lane issues the MMAs and their commits.
@@ -337,6 +363,7 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       const bool okf = mbar_wait(&full[s], (it / Cfg::kStages) & 1, abort_flag) &&
                        mbar_wait(&acc_empty[as], ((ait >> 1) & 1) ^ 1, abort_flag);
       if (!__all_sync(0xffffffffu, okf)) break;
+      if constexpr (kGather) fence_proxy_async();   // gathered rows were written through the generic proxy
       tc_fence_after();
       if (elect_one()) {
         const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
@@ -454,6 +481,11 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
           const int b = p.klist[static_cast<int64_t>(row) * p.klist_stride + t];
           const int pos = b * kTileKeys + lane_base + lane;
           keep = keep && b >= 0 && pos >= lo && pos < hi;
+        }
+      } else if constexpr (kGather) {
+        if (keep) {
+          const int pos = __ldg(trow + key);
+          keep = pos >= 0 && pos < p.num_pages && pos >= lo && pos < hi;
         }
       } else {
         if (keep) {
@@ -686,11 +718,11 @@ static int sm_count() {
   return n;
 }
 
-template <bool kFp8, bool kEmit = false, bool kList = false>
+template <bool kFp8, bool kEmit = false, bool kList = false, bool kGather = false>
 static int launch_paged(const CUtensorMap& mk, const CUtensorMap& mq, PagedIndexerParams p, int64_t est_tiles,
                         cudaStream_t stream) {
   using Cfg = PagedCfg<kFp8, kEmit>;
-  cudaError_t e = cudaFuncSetAttribute(indexer_paged_kernel<kFp8, kEmit, kList>,
+  cudaError_t e = cudaFuncSetAttribute(indexer_paged_kernel<kFp8, kEmit, kList, kGather>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
@@ -698,7 +730,7 @@ static int launch_paged(const CUtensorMap& mk, const CUtensorMap& mq, PagedIndex
   }
   int grid = sm_count() * Cfg::kCtasPerSm;
   if (est_tiles > 0 && est_tiles < grid) grid = static_cast<int>(est_tiles);
-  e = launch_chained(indexer_paged_kernel<kFp8, kEmit, kList>, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, mk,
+  e = launch_chained(indexer_paged_kernel<kFp8, kEmit, kList, kGather>, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, mk,
                      mq, p);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -998,6 +1030,65 @@ extern "C" int b200dsa_indexer_blocklist_bf16_logits(const void* q_bf16, const f
     p.logits_gated = logits_gated ? logits_gated + static_cast<int64_t>(r0) * logits_stride : nullptr;
     p.status = status;
     rc = launch_paged<false, false>(mk, mq, p, 0, static_cast<cudaStream_t>(stream));
+    if (rc) return rc;
+  }
+  return B200DSA_OK;
+}
+
+extern "C" int b200dsa_indexer_gather_bf16_logits(const void* q_bf16, const float* weights, const void* keys_bf16,
+                                                  int32_t n_keys, const int32_t* cand, int64_t cand_stride,
+                                                  const int32_t* row_cols, const int32_t* pos_lo,
+                                                  const int32_t* pos_hi, int32_t n_rows, int32_t max_cols,
+                                                  float out_scale, float* logits, int64_t logits_stride,
+                                                  int32_t* status, void* stream) {
+  if (n_rows == 0) return B200DSA_OK;
+  if (!q_bf16 || !weights || !keys_bf16 || !cand || !row_cols || !logits || !status || n_rows < 0 || n_keys < 1 ||
+      max_cols < 0 || logits_stride < max_cols || cand_stride < max_cols ||
+      ((pos_lo == nullptr) != (pos_hi == nullptr))) {
+    set_last_error("b200dsa_indexer_gather_bf16_logits: bad argument (cand_stride and logits_stride >= max_cols)");
+    return B200DSA_EINVAL;
+  }
+  if ((reinterpret_cast<uintptr_t>(q_bf16) & 15) || (reinterpret_cast<uintptr_t>(keys_bf16) & 15) ||
+      (reinterpret_cast<uintptr_t>(weights) & 15)) {
+    set_last_error("b200dsa_indexer_gather_bf16_logits: q, weights and keys must be 16-byte aligned");
+    return B200DSA_EALIGN;
+  }
+  CUtensorMap mk, mq;
+  {
+    cuuint64_t dims[2] = {kDim, static_cast<cuuint64_t>(n_keys)};
+    cuuint64_t strides[1] = {kDim * 2};
+    cuuint32_t box[2] = {64, kTileKeys};
+    int rc = encode_map(&mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, keys_bf16, dims, strides, box);   // not loaded through
+    if (rc) return rc;
+  }
+  for (int r0 = 0; r0 < n_rows; r0 += kMaxRows) {
+    const int nr = n_rows - r0 < kMaxRows ? n_rows - r0 : kMaxRows;
+    const uint8_t* qbase = static_cast<const uint8_t*>(q_bf16) + static_cast<int64_t>(r0) * kHeads * kDim * 2;
+    cuuint64_t dims[2] = {kDim, static_cast<cuuint64_t>(nr) * kHeads};
+    cuuint64_t strides[1] = {kDim * 2};
+    cuuint32_t box[2] = {64, kHeads};
+    int rc = encode_map(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, qbase, dims, strides, box);
+    if (rc) return rc;
+    PagedIndexerParams p{};
+    p.cache = static_cast<const uint8_t*>(keys_bf16);   // gather source
+    p.page_bytes = 0;
+    p.page_size = kTileKeys;
+    p.num_pages = n_keys;                               // valid positions are [0, n_keys)
+    p.weights = weights + static_cast<int64_t>(r0) * kHeads;
+    p.row_cols = row_cols + r0;
+    p.table = cand + static_cast<int64_t>(r0) * cand_stride;
+    p.table_stride = cand_stride;
+    p.table_cols = static_cast<int32_t>(cand_stride < 0x7fffffff ? cand_stride : 0x7fffffff);
+    p.table_row_div = 1;
+    p.pos_lo = pos_lo ? pos_lo + r0 : nullptr;
+    p.pos_hi = pos_hi ? pos_hi + r0 : nullptr;
+    p.n_rows = nr;
+    p.out_scale = out_scale;
+    p.logits = logits + static_cast<int64_t>(r0) * logits_stride;
+    p.logits_stride = logits_stride;
+    p.logits_cols = max_cols;
+    p.status = status;
+    rc = launch_paged<false, false, false, true>(mk, mq, p, 0, static_cast<cudaStream_t>(stream));
     if (rc) return rc;
   }
   return B200DSA_OK;

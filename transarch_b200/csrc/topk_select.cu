@@ -435,7 +435,8 @@ __device__ void find_threshold_bin(const uint32_t* hist, int need, int* res, uin
 // wanted quantile (4x the wanted tail mass), and the main pass only counts scores at or above it.
 template <class Off>
 __device__ bool sample_bin_floor(const TopkParams& p, const float* __restrict__ src, int begin, int n, int k,
-                                 Off&& coff, uint32_t* hist, int* s_res, uint32_t* s_seg, uint32_t* bin_floor) {
+                                 Off&& coff, uint32_t* hist, int* s_res, uint32_t* s_seg, uint32_t* bin_floor,
+                                 int list_cap = kCandCap) {
   const int tid = threadIdx.x, nthr = blockDim.x;
   const bool exact = n <= kSampleMax;
   const int m = exact ? n : kSampleMax;
@@ -443,7 +444,7 @@ __device__ bool sample_bin_floor(const TopkParams& p, const float* __restrict__ 
   const int64_t step = exact ? kSampleChunk : n / n_chunks;
   const float ratio = static_cast<float>(n) / static_cast<float>(m);
   const float want_full = exact ? static_cast<float>(k) : k + 6.0f * sqrtf(2.0f * k * ratio) + 32.0f;
-  if (want_full > 0.8f * kCandCap) return false;
+  if (want_full > 0.8f * list_cap) return false;
   const int want_sample = static_cast<int>(ceilf(want_full / ratio));
 
   // pass 1: 8 samples from the head of every chunk
@@ -689,7 +690,8 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   }
   uint32_t bin_floor = 0;
   bool try_fast = !have_pre;
-  if (try_fast && n > cand_cap) try_fast = sample_bin_floor(p, src, begin, n, k, coff, hist, s_res, s_seg, &bin_floor);
+  if (try_fast && n > cand_cap)
+    try_fast = sample_bin_floor(p, src, begin, n, k, coff, hist, s_res, s_seg, &bin_floor, cand_cap);
 
   // Each warp compacts its takes into its own segment of the candidate list with votes
   // only (no atomics); a full segment raises the overflow flag and the row falls back.
@@ -955,6 +957,10 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
   if (n_cols <= kCandCap) {
     cand_cap = 1024;
     while (cand_cap < n_cols) cand_cap <<= 1;
+  } else if (k > kCandCap / 2) {
+    // a large k (MISA's stage-1 top-8192) needs room for k plus the sampling margin: the long list, which
+    // together with 8192 winners is the largest shared-memory configuration
+    cand_cap = kListCap;
   }
   const size_t smem = kHistBins * sizeof(uint32_t) + (static_cast<size_t>(cand_cap) + kEqCap + k_pow2) * sizeof(uint64_t);
   cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -404,6 +404,66 @@ def indexer_flat_bf16_logits(q: torch.Tensor, weights: torch.Tensor, keys: torch
     return out
 
 
+def indexer_flat_bf16_logits_routed(q8: torch.Tensor, weights8: torch.Tensor, keys: torch.Tensor, pos_lo: torch.Tensor,
+                                    pos_hi: torch.Tensor, row_cols: torch.Tensor, max_cols: int, *,
+                                    out_scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Routed prefill logits [n_rows, max_cols]: q8 [n_rows, 8, 128] are the eight heads kept for each query,
+    32 queries per key tile; see b200dsa_indexer_flat_bf16_logits_routed (columns as in the all-head form)."""
+    require_cuda(q8, weights8, keys, pos_lo, pos_hi, row_cols, out)
+    if q8.dtype != torch.bfloat16 or not q8.is_contiguous() or q8.shape[-2:] != (8, 128):
+        raise _lib.B200DSAError("q8 must be contiguous bf16 [n_rows, 8, 128]")
+    if keys.dtype != torch.bfloat16 or not keys.is_contiguous() or keys.shape[-1] != 128:
+        raise _lib.B200DSAError("keys must be contiguous bf16 [n_keys, 128]")
+    n_rows = q8.shape[0]
+    if weights8.dtype != torch.float32 or not weights8.is_contiguous() or weights8.numel() != n_rows * 8:
+        raise _lib.B200DSAError("weights8 must be contiguous fp32 [n_rows, 8]")
+    for t_, nm in ((pos_lo, "pos_lo"), (pos_hi, "pos_hi"), (row_cols, "row_cols")):
+        if _i32(t_, nm).numel() != n_rows:
+            raise _lib.B200DSAError(f"{nm} must have one entry per row")
+    if out is None:
+        out = torch.full((n_rows, max_cols), NEG_INF, dtype=torch.float32, device=q8.device)
+    elif out.dtype != torch.float32 or out.stride(1) != 1 or out.shape[0] < n_rows or out.shape[1] < max_cols:
+        raise _lib.B200DSAError("out must be fp32 [>=n_rows, >=max_cols] with unit column stride")
+    rc = _lib.load().b200dsa_indexer_flat_bf16_logits_routed(
+        ptr(q8), ptr(weights8), ptr(keys), keys.shape[0], ptr(pos_lo), ptr(pos_hi), ptr(row_cols), n_rows, max_cols,
+        out_scale, ptr(out), out.stride(0), ptr(status_word(q8.device)), stream_ptr())
+    check(rc, "b200dsa_indexer_flat_bf16_logits_routed")
+    return out
+
+
+def indexer_gather_bf16_logits(q: torch.Tensor, weights: torch.Tensor, keys: torch.Tensor, cand: torch.Tensor, *,
+                               row_cols: Optional[torch.Tensor] = None, pos_lo: Optional[torch.Tensor] = None,
+                               pos_hi: Optional[torch.Tensor] = None, out_scale: float = 1.0,
+                               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """All-head logits [n_rows, n_cand] of every query on its own candidate positions cand int32
+    [n_rows, n_cand] (-1 = none -> -inf); see b200dsa_indexer_gather_bf16_logits."""
+    require_cuda(q, weights, keys, cand, row_cols, pos_lo, pos_hi, out)
+    if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.shape[-2:] != (64, 128):
+        raise _lib.B200DSAError("q must be contiguous bf16 [n_rows, 64, 128]")
+    if keys.dtype != torch.bfloat16 or not keys.is_contiguous() or keys.shape[-1] != 128:
+        raise _lib.B200DSAError("keys must be contiguous bf16 [n_keys, 128]")
+    n_rows = q.shape[0]
+    if weights.dtype != torch.float32 or not weights.is_contiguous() or weights.numel() != n_rows * 64:
+        raise _lib.B200DSAError("weights must be contiguous fp32 [n_rows, 64]")
+    if _i32(cand, "cand").dim() != 2 or cand.shape[0] != n_rows or cand.stride(1) != 1:
+        raise _lib.B200DSAError("cand must be int32 [n_rows, n_cand] with unit column stride")
+    n_cand = cand.shape[1]
+    if row_cols is None:
+        row_cols = torch.full((n_rows,), n_cand, dtype=torch.int32, device=q.device)
+    for t_, nm in ((row_cols, "row_cols"), (pos_lo, "pos_lo"), (pos_hi, "pos_hi")):
+        if t_ is not None and _i32(t_, nm).numel() != n_rows:
+            raise _lib.B200DSAError(f"{nm} must have one entry per row")
+    if out is None:
+        out = torch.full((n_rows, n_cand), NEG_INF, dtype=torch.float32, device=q.device)
+    elif out.dtype != torch.float32 or out.stride(1) != 1 or out.shape[0] < n_rows or out.shape[1] < n_cand:
+        raise _lib.B200DSAError("out must be fp32 [>=n_rows, >=n_cand] with unit column stride")
+    rc = _lib.load().b200dsa_indexer_gather_bf16_logits(
+        ptr(q), ptr(weights), ptr(keys), keys.shape[0], ptr(cand), cand.stride(0), ptr(row_cols), ptr(pos_lo),
+        ptr(pos_hi), n_rows, n_cand, out_scale, ptr(out), out.stride(0), ptr(status_word(q.device)), stream_ptr())
+    check(rc, "b200dsa_indexer_gather_bf16_logits")
+    return out
+
+
 def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: float, *,
                       kv_row_base: Optional[torch.Tensor] = None, q_pos: Optional[torch.Tensor] = None,
                       pos_lo: int = 0, pos_hi: int = 2 ** 31 - 1, n_idx_item: Optional[torch.Tensor] = None,

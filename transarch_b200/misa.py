@@ -82,8 +82,11 @@ def misa_mqa_logits(q: torch.Tensor, kv: Tuple[torch.Tensor, torch.Tensor], weig
         pooled = pooled.to(torch.bfloat16).float().contiguous()            # the reference pools to bf16
         _, head_idx = K.router_block_score_topk(qb, w, pooled, (ks // k_block_size).contiguous(),
                                                 ((ke + k_block_size - 1) // k_block_size).contiguous(), topk_heads)
-    bl, row_cols = identity_block_lists(ks.long(), ke.long(), N)
     s1 = min(stage1_topk, N)
+    if head_idx.shape[1] <= 8 and N >= 2 * s1:
+        return _misa_prefill_two_stage(qb, w, k, head_idx, ks, ke, s1)
+    # short key ranges: one pass writes the routed and the all-head score of every key, stage 2 is a gather
+    bl, row_cols = identity_block_lists(ks.long(), ke.long(), N)
     full, stage1 = K.indexer_blocklist_bf16_logits(qb, w, k, bl, row_cols, pos_lo=ks, pos_hi=ke,
                                                    head_mask=K.head_mask_from_indices(head_idx))
     cand = K.topk_select(stage1, s1, col_end=row_cols, page_table=bl, page_size=128, sorted=False)
@@ -92,6 +95,37 @@ def misa_mqa_logits(q: torch.Tensor, kv: Tuple[torch.Tensor, torch.Tensor], weig
     cols = (cand - col0).clamp(min=0).long()
     logits = torch.gather(full, 1, cols)
     logits = torch.where(cand >= 0, logits, torch.full_like(logits, float("-inf")))
+    return logits, cand
+
+
+_STAGE1_BYTES = 1 << 30     # bound on the routed score matrix of one query chunk
+
+
+def _misa_prefill_two_stage(qb, w, k, head_idx, ks, ke, s1):
+    """Long key ranges, where the routing saves work (misa_ops.py:415-515 stage 1 on the kept heads with
+    block_Q = 128 / H queries per tile, :517-650 stage 2 on all heads over the candidates): the kept heads
+    of every query are gathered into [M, 8, 128] and scored 32 queries per key tile; the top-s1 positions
+    of that score are then re-scored with all 64 heads by the gathering kernel, 128 candidates per pass.
+    Fewer than eight kept heads are padded with zero-weight copies."""
+    M, N = qb.shape[0], k.shape[0]
+    idx = head_idx.long()
+    w8 = torch.gather(w, 1, idx)
+    if idx.shape[1] < 8:
+        pad = 8 - idx.shape[1]
+        idx = torch.cat([idx, idx[:, :1].expand(-1, pad)], dim=1)
+        w8 = torch.cat([w8, w8.new_zeros(M, pad)], dim=1)
+    q8 = torch.gather(qb, 1, idx.view(M, 8, 1).expand(-1, -1, 128)).contiguous()
+    w8 = w8.contiguous()
+    col0 = ((ks >> 7) << 7).contiguous()
+    row_cols = ((((ke + 127) >> 7) << 7) - col0).clamp_(min=0).contiguous()
+    cols = ((N + 127) // 128) * 128
+    cand = torch.empty(M, s1, dtype=torch.int32, device=qb.device)
+    chunk = max(32, min(M, (_STAGE1_BYTES // (4 * cols)) // 32 * 32))
+    for t0 in range(0, M, chunk):
+        t1 = min(M, t0 + chunk)
+        stage1 = K.indexer_flat_bf16_logits_routed(q8[t0:t1], w8[t0:t1], k, ks[t0:t1], ke[t0:t1], row_cols[t0:t1], cols)
+        K.topk_select(stage1, s1, row_pos_offset=col0[t0:t1], sorted=False, out=cand[t0:t1])
+    logits = K.indexer_gather_bf16_logits(qb, w, k, cand, pos_lo=ks, pos_hi=ke)
     return logits, cand
 
 
