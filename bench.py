@@ -178,11 +178,11 @@ def run_reference(args, rank: int):
 CFG_REPS, CFG_WARM = 50, 10
 
 
-def _time_call(fn, flush):
-    for _ in range(CFG_WARM):
+def _time_call(fn, flush, reps=None, warm=None):
+    for _ in range(CFG_WARM if warm is None else warm):
         fn()
     ts = []
-    for _ in range(CFG_REPS):
+    for _ in range(CFG_REPS if reps is None else reps):
         flush.add_(1)                                      # evict L2 (256 MB > 126 MB)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(); fn(); e1.record()
@@ -316,7 +316,29 @@ def bench_configs(dev, peaks, threads: int, fp8_peak: float, only=None, with_cpu
             "cpu_kind": "port (no reference code for the linear router)",
             "cpu_sample": f"{sample} of 32 requests, 8 routed heads only, scaled"}
 
-    for tag, fn in (("C1", c1), ("C2", c2), ("C3", c3), ("C4", c4)):
+    def m1():
+        """MISA routed prefill (not a BASELINE configuration): 4096 queries at the tail of 65536 keys, q-norm
+        router 8 of 64 heads, stage-1 top-8192, seed 5"""
+        g = torch.Generator(device=dev).manual_seed(5)
+        N, M, s1 = 65536, 4096, 8192
+        kq = torch.randn(N, 128, generator=g, device=dev).to(torch.float8_e4m3fn)
+        sc = torch.ones(N, device=dev)
+        q = torch.randn(M, 64, 128, generator=g, device=dev).to(torch.float8_e4m3fn)
+        w = torch.randn(M, 64, generator=g, device=dev) / 8
+        ke = torch.arange(N - M, N, device=dev, dtype=torch.int32) + 1
+        ks = torch.zeros(M, dtype=torch.int32, device=dev)
+        hidx = torch.topk(q.float().norm(dim=-1), 8, dim=-1).indices.int()
+        med, mn = _time_call(lambda: misa.misa_mqa_logits(q, (kq, sc), w, hidx, ks, ke, True, 8, s1), flush, reps=10,
+                             warm=3)
+        pairs = float((ke.long() - ks.long()).sum())            # (query, key) pairs in range
+        flops = int(pairs * 8 * 256 + M * s1 * 64 * 256)
+        out["M1 MISA routed prefill, 4096 queries at the tail of 65536 keys, 8 of 64 heads, stage-1 top-8192 (bf16)"] = {
+            "call": "misa.misa_mqa_logits", "us_median": med, "us_min": mn, "flops": flops,
+            "flops_without_routing": int(pairs * 64 * 256), "bound": "tensor",
+            "achieved_tflops": flops / med / 1e6, "frac_of_bf16_sustained": flops / med / 1e6 / bf16,
+            "cpu_seconds": None, "cpu_kind": "not timed"}
+
+    for tag, fn in (("C1", c1), ("C2", c2), ("C3", c3), ("C4", c4), ("M1", m1)):
         if want(tag):
             fn()
             torch.cuda.empty_cache()
@@ -360,7 +382,7 @@ def main():
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-configs", action="store_true", help="do not time the other configurations of the path")
     ap.add_argument("--skip-parity", action="store_true", help="do not compare sampled requests with the oracle")
-    ap.add_argument("--configs-only", default="", help="comma-separated subset of C1,C2,C3,C4: time only these "
+    ap.add_argument("--configs-only", default="", help="comma-separated subset of C1,C2,C3,C4,M1: time only these "
                     "configurations (no decode step) and print them; for profiling single kernels")
     ap.add_argument("--config-reps", type=int, default=0, help="timed repetitions per configuration (default 50)")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")

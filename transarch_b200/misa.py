@@ -121,10 +121,13 @@ def _misa_prefill_two_stage(qb, w, k, head_idx, ks, ke, s1):
     cols = ((N + 127) // 128) * 128
     cand = torch.empty(M, s1, dtype=torch.int32, device=qb.device)
     chunk = max(32, min(M, (_STAGE1_BYTES // (4 * cols)) // 32 * 32))
+    buf = torch.empty(min(chunk, M), cols, dtype=torch.float32, device=qb.device)   # only columns < row_cols are read
     for t0 in range(0, M, chunk):
         t1 = min(M, t0 + chunk)
-        stage1 = K.indexer_flat_bf16_logits_routed(q8[t0:t1], w8[t0:t1], k, ks[t0:t1], ke[t0:t1], row_cols[t0:t1], cols)
-        K.topk_select(stage1, s1, row_pos_offset=col0[t0:t1], sorted=False, out=cand[t0:t1])
+        stage1 = K.indexer_flat_bf16_logits_routed(q8[t0:t1], w8[t0:t1], k, ks[t0:t1], ke[t0:t1], row_cols[t0:t1], cols,
+                                                   out=buf[:t1 - t0])
+        K.topk_select(stage1[:t1 - t0], s1, col_end=row_cols[t0:t1], row_pos_offset=col0[t0:t1], sorted=False,
+                      out=cand[t0:t1])
     logits = K.indexer_gather_bf16_logits(qb, w, k, cand, pos_lo=ks, pos_hi=ke)
     return logits, cand
 
