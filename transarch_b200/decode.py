@@ -282,6 +282,37 @@ class SparseDecodeStep:
         return idx, ctx, lse
 
 
+def input_layout(batch: int, n_heads: int) -> dict:
+    """Byte offsets of (q_idx bf16 [B,64,128], w fp32 [B,64], q_lat bf16 [B,H,576]) inside one packed buffer
+    (each part starts on a 256-byte boundary)."""
+    sizes = (batch * 64 * 128 * 2, batch * 64 * 4, batch * n_heads * 576 * 2)
+    offs, o = [], 0
+    for n in sizes:
+        offs.append(o)
+        o += (n + 255) // 256 * 256
+    return {"offsets": tuple(offs), "sizes": sizes, "bytes": o}
+
+
+def unpack_inputs(buf: torch.Tensor, batch: int, n_heads: int):
+    """(q_idx, w, q_lat) as views of a packed uint8 buffer (input_layout)."""
+    lay = input_layout(batch, n_heads)
+    (o0, o1, o2), (n0, n1, n2) = lay["offsets"], lay["sizes"]
+    return (buf[o0:o0 + n0].view(torch.bfloat16).view(batch, 64, 128),
+            buf[o1:o1 + n1].view(torch.float32).view(batch, 64),
+            buf[o2:o2 + n2].view(torch.bfloat16).view(batch, n_heads, 576))
+
+
+def pack_inputs(q_idx: torch.Tensor, w: torch.Tensor, q_lat: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+    """Copy the three inputs into one uint8 buffer (allocated on q_idx's device when not given)."""
+    B, H = q_idx.shape[0], q_lat.shape[1]
+    lay = input_layout(B, H)
+    if out is None:
+        out = torch.empty(lay["bytes"], dtype=torch.uint8, device=q_idx.device)
+    for dst, src in zip(unpack_inputs(out, B, H), (q_idx, w, q_lat)):
+        dst.copy_(src)
+    return out
+
+
 class GraphedDecodeStep:
     """The whole step captured once into a CUDA graph and replayed: per-step host work drops to
     one graph launch (the kernels' host calls, tensor-map encodes and NCCL enqueues are recorded
@@ -294,9 +325,11 @@ class GraphedDecodeStep:
         self.step = step
         dev = step.dev
         B, H = step.B, step.H
-        self.q_idx = torch.empty(B, 64, 128, dtype=torch.bfloat16, device=dev)
-        self.w = torch.empty(B, 64, dtype=torch.float32, device=dev)
-        self.q_lat = torch.empty(B, H, 576, dtype=torch.bfloat16, device=dev)
+        # the three inputs are views of one byte buffer, so that a serving loop can stage a step's inputs in one
+        # pinned arena and bring them in with one copy (replay_packed)
+        self.layout = input_layout(B, H)
+        self.inputs = torch.empty(self.layout["bytes"], dtype=torch.uint8, device=dev)
+        self.q_idx, self.w, self.q_lat = unpack_inputs(self.inputs, B, H)
         self._state = (k_cache, context_lens, block_table, kv, kv_row_base, context_lens_local)
         self.graph = None
         self.out = None
@@ -317,6 +350,12 @@ class GraphedDecodeStep:
             self.out = self.step.run(self.q_idx, self.w, self.q_lat, k_cache, context_lens, block_table, kv,
                                      kv_row_base, local)
         return self
+
+    def replay_packed(self, packed: torch.Tensor):
+        """One copy of a packed input buffer (pack_inputs layout; device or pinned host), then replay."""
+        self.inputs.copy_(packed, non_blocking=True)
+        self.graph.replay()
+        return self.out
 
     def replay(self, q_idx=None, w=None, q_lat=None):
         """Copy the given inputs (device or pinned host tensors) into the static buffers and replay."""
