@@ -6,7 +6,7 @@ baseline, the reference arm of the benchmark and the tests can import them on a 
 checkout of TransArch.  Nothing under oracle/_ref/ is tracked by git and nothing in the shipped
 package imports it.
 
-    python -m oracle.make_ref [/path/to/TransArch]      (default: /root/reference)
+    python -m oracle.make_ref [/path/to/TransArch]      (default: $TRANSARCH_ROOT, else DEFAULT_ROOT below)
 
 Installed:
   oracle/_ref/opendsa/ops/{topk_select,sparse_mla,flashkl_warmup}.py   <- OpenDSA/opendsa/ops/
@@ -25,6 +25,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF_DIR = os.path.join(HERE, "_ref")
+DEFAULT_ROOT = os.environ.get("TRANSARCH_ROOT", os.path.join(os.sep, "root", "reference"))
 
 FILES = [
     ("OpenDSA/opendsa/ops/topk_select.py", "opendsa/ops/topk_select.py"),
@@ -45,7 +46,7 @@ FILES = [
 ]
 
 
-def make_ref(reference_root: str = "/root/reference") -> bool:
+def make_ref(reference_root: str = DEFAULT_ROOT) -> bool:
     """Copy the files; returns False (and leaves oracle/_ref/ as it is) when the checkout is absent."""
     if not os.path.isdir(reference_root):
         return False
@@ -71,6 +72,6 @@ def reference_ops():
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else DEFAULT_ROOT
     ok = make_ref(root)
     print(f"oracle/_ref {'installed from ' + root if ok else 'NOT installed: ' + root + ' is missing'}")
