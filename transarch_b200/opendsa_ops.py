@@ -74,19 +74,20 @@ def identity_block_lists(ks: torch.Tensor, ke: torch.Tensor, n_keys: int):
 
 
 def indexer_logits_flat(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, ks: torch.Tensor, ke: torch.Tensor,
-                        sm_scale: float):
+                        sm_scale: float, out: Optional[torch.Tensor] = None):
     """Token logits of every row over the 128-key blocks covering its interval [ks, ke):
     (logits fp32 [T, cols] with -inf outside the interval, col0 int32 [T] = position of column 0 of
     each row, row_cols int32 [T]).  No block list is built: the kernel walks consecutive blocks, and four
-    consecutive queries share every key tile."""
+    consecutive queries share every key tile.  With `out` (fp32 [>= T, >= cols]) nothing is allocated or
+    pre-filled: only the columns below row_cols of each row are then defined."""
     lo = ks.to(torch.int32).contiguous()
     hi = ke.to(torch.int32).contiguous()
     col0 = (lo >> 7) << 7
     row_cols = (((hi + (_BLOCK - 1)) >> 7) << 7) - col0
     row_cols.clamp_(min=0)
     cols = ((k.shape[0] + _BLOCK - 1) // _BLOCK) * _BLOCK
-    logits = K.indexer_flat_bf16_logits(q, w, k, lo, hi, row_cols.contiguous(), cols, out_scale=sm_scale)
-    return logits, col0, row_cols
+    logits = K.indexer_flat_bf16_logits(q, w, k, lo, hi, row_cols.contiguous(), cols, out_scale=sm_scale, out=out)
+    return logits[:q.shape[0]], col0, row_cols
 
 
 @torch.no_grad()
@@ -119,9 +120,10 @@ def indexer_select_topk(index_q, index_k, index_w, cu_seqlens, topk, *, sm_scale
     k_eff = min(topk, 8192)
     if topk > 8192:
         raise B200DSAError("topk above 8192 is not supported")
+    buf = torch.empty(min(rows_per, Lq), cols, dtype=torch.float32, device=index_q.device)   # read below row_cols only
     for t0 in range(0, Lq, rows_per):
         t1 = min(t0 + rows_per, Lq)
-        logits, col0, row_cols = indexer_logits_flat(q[t0:t1], k, w[t0:t1], ks[t0:t1], ke[t0:t1], sf)
+        logits, col0, row_cols = indexer_logits_flat(q[t0:t1], k, w[t0:t1], ks[t0:t1], ke[t0:t1], sf, out=buf)
         K.topk_select(logits, k_eff, col_end=row_cols, row_pos_offset=col0, sorted=sorted, out=out[t0:t1])
     return out
 
