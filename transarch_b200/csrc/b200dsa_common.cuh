@@ -256,6 +256,29 @@ inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// In-place inclusive prefix sum of counts[1..n] (counts[0] stays 0), run by ONE full warp: every lane adds up a
+// run of consecutive entries, a shuffle scan joins the runs.  The run length is odd so that the lanes walk
+// different shared-memory banks.  (A single thread adding 1024 entries one after the other takes about 30 us,
+// which every CTA of a persistent kernel would spend before its first load.)
+__device__ __forceinline__ void warp_prefix_inplace(int* counts, int n) {
+  const int lane = threadIdx.x & 31;
+  const int per = ((n + 31) / 32) | 1;
+  const int lo = min(n, lane * per), hi = min(n, lo + per);
+  int sum = 0;
+  for (int i = lo; i < hi; ++i) sum += counts[i + 1];
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  int acc = incl - sum;
+  for (int i = lo; i < hi; ++i) {
+    acc += counts[i + 1];
+    counts[i + 1] = acc;
+  }
+}
+
 // Order-preserving map fp32 -> u32 (larger float <=> larger unsigned).
 __device__ __forceinline__ uint32_t float_to_ordered(float f) {
   uint32_t u = __float_as_uint(f);

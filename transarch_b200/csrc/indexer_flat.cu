@@ -98,12 +98,8 @@ indexer_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   }
   if (tid == 0) s_prefix[0] = 0;
   __syncthreads();
+  if (warp == 0) warp_prefix_inplace(s_prefix, n_groups);
   if (tid == 0) {
-    int acc = 0;
-    for (int g = 0; g < n_groups; ++g) {
-      acc += s_prefix[g + 1];
-      s_prefix[g + 1] = acc;
-    }
     for (int s = 0; s < kFlatStages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);

@@ -162,12 +162,8 @@ indexer_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
   }
   if (tid == 0) s_prefix[0] = 0;
   __syncthreads();
+  if (warp == 0) warp_prefix_inplace(s_prefix, p.n_rows);
   if (tid == 0) {
-    int acc = 0;
-    for (int r = 0; r < p.n_rows; ++r) {
-      acc += s_prefix[r + 1];
-      s_prefix[r + 1] = acc;
-    }
     for (int s = 0; s < Cfg::kStages; ++s) {
       mbar_init(&full[s], kGather ? 32 : 1);   // gather: the producer warp's 32 lanes, each after its copies
       mbar_init(&empty[s], 1);
