@@ -417,6 +417,10 @@ def main():
     group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # NCCL only carries set-up traffic and barriers here (the exchanges of the step are this library's own
+        # peer-memory kernels): it needs no NVLink multicast objects, and without them a rank that leaves
+        # early cannot disturb its peers
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
     B, ctx = args.batch, args.context
     assert ctx % (world * PAGE) == 0
