@@ -484,6 +484,7 @@ def main():
     # an NVLink all-gather (posted peer stores, one kernel) replicates them inside the node.  Each rank
     # returns its 1/world of the result rows to its host.
     ag = None
+    ag_packed = False
     if world > 1 and step.peer is not None:
         from transarch_b200.peer import PeerAllGather
         sizes = [t.numel() * t.element_size() for t in host_q[0]]
@@ -497,7 +498,22 @@ def main():
                 cat[o:o + t.numel() * t.element_size()] = t.contiguous().view(torch.uint8).reshape(-1)
             host_cat.append(cat)
         recv_views = [ag.recv[o:o + n].view(t.dtype).view(t.shape) for t, o, n in zip(host_q[0], offs, sizes)]
+        ag_packed = tuple(offs) == lay["offsets"] and total_in == lay["bytes"]
         rows_lo, rows_hi = rank * B // world, (rank + 1) * B // world
+
+    # everything an iteration touches is bound once: views of the per-slot buffers (the sharded form moves only this
+    # rank's rows), so that the loop itself is a handful of copy, event and launch calls
+    if ag is not None:
+        send_src = [hc[rank * ag.chunk:(rank + 1) * ag.chunk] for hc in host_cat]
+        recv_packed = ag.recv[:lay["bytes"]] if ag_packed else None
+        od = [(o[0][rows_lo:rows_hi], o[1][rows_lo:rows_hi]) for o in out_dev]
+        oh = [(o[0][rows_lo:rows_hi], o[1][rows_lo:rows_hi]) for o in out_host]
+    else:
+        od, oh = out_dev, out_host
+    res_rows = None
+    if graphed is not None and graphed.out is not None:
+        r_idx, r_ctx = graphed.out[0], graphed.out[1]
+        res_rows = (r_idx[rows_lo:rows_hi], r_ctx[rows_lo:rows_hi]) if ag is not None else (r_idx, r_ctx)
 
     def run_e2e(i):
         sl = i % slots
@@ -507,7 +523,7 @@ def main():
             s_in.wait_event(ev_in_free[sl])
         with torch.cuda.stream(s_in):
             if ag is not None:
-                ag.send[sl].copy_(host_cat[i % n_sets][rank * ag.chunk:(rank + 1) * ag.chunk], non_blocking=True)
+                ag.send[sl].copy_(send_src[i % n_sets], non_blocking=True)
             else:
                 in_pack[sl].copy_(host_pack[i % n_sets], non_blocking=True)
             ev_in[sl].record(s_in)
@@ -520,26 +536,23 @@ def main():
         if graphed is None:
             idx, c, _ = step.run(ins[0], ins[1], ins[2], state.k_cache, state.context_lens,
                                  state.block_table, state.kv, state.kv_row_base, state.context_lens_local)
-        elif ag is None:
-            idx, c, _ = graphed.replay_packed(in_pack[sl])
+            src = (idx[rows_lo:rows_hi], c[rows_lo:rows_hi]) if ag is not None else (idx, c)
         else:
-            idx, c, _ = graphed.replay(*ins)
+            if ag is None:
+                graphed.replay_packed(in_pack[sl])
+            elif ag_packed:
+                graphed.replay_packed(recv_packed)       # the gathered bytes already have the layout
+            else:
+                graphed.replay(*ins)
+            src = res_rows
         ev_in_free[sl].record(main)
-        if ag is not None:
-            out_dev[sl][0][rows_lo:rows_hi].copy_(idx[rows_lo:rows_hi], non_blocking=True)
-            out_dev[sl][1][rows_lo:rows_hi].copy_(c[rows_lo:rows_hi], non_blocking=True)
-        else:
-            out_dev[sl][0].copy_(idx, non_blocking=True)
-            out_dev[sl][1].copy_(c, non_blocking=True)
+        od[sl][0].copy_(src[0], non_blocking=True)
+        od[sl][1].copy_(src[1], non_blocking=True)
         ev_done[sl].record(main)
         s_out.wait_event(ev_done[sl])
         with torch.cuda.stream(s_out):
-            if ag is not None:
-                out_host[sl][0][rows_lo:rows_hi].copy_(out_dev[sl][0][rows_lo:rows_hi], non_blocking=True)
-                out_host[sl][1][rows_lo:rows_hi].copy_(out_dev[sl][1][rows_lo:rows_hi], non_blocking=True)
-            else:
-                out_host[sl][0].copy_(out_dev[sl][0], non_blocking=True)
-                out_host[sl][1].copy_(out_dev[sl][1], non_blocking=True)
+            oh[sl][0].copy_(od[sl][0], non_blocking=True)
+            oh[sl][1].copy_(od[sl][1], non_blocking=True)
             ev_out[sl].record(s_out)
         e2e_started[sl] = True
 
