@@ -110,6 +110,14 @@ def test_attend_gradients_match_reference_autograd():
     for got, ref, what in ((x.grad, a.grad, "q_lat"), (y.grad, b.grad, "latent"), (z.grad, c.grad, "W_UV")):
         err = (got.cpu() - ref).abs().max() / ref.abs().max()
         assert err < 2e-2, (what, float(err))
+    # bf16 inputs: the backward's products run in bf16 (fp32 accumulation); same gradients within bf16 accuracy
+    xb, yb, zb = (t.clone().cuda().bfloat16().requires_grad_() for t in (q, lat, W_UV))
+    outb = D.sparse_attend_absorbed_chunked(xb, yb, zb, idx.cuda(), d_c=d_c, sm_scale=Dl ** -0.5, q_chunk=7)
+    (outb.float() * G.cuda()).sum().backward()
+    for got, ref, what in ((xb.grad, a.grad, "q_lat"), (yb.grad, b.grad, "latent"), (zb.grad, c.grad, "W_UV")):
+        assert got.dtype == torch.bfloat16
+        err = (got.float().cpu() - ref).abs().max() / ref.abs().max()
+        assert err < 4e-2, (what, float(err))
     # only some inputs need gradients
     x2 = q.clone().cuda().requires_grad_()
     out = D.sparse_attend_absorbed_chunked(x2, lat.cuda(), W_UV.cuda(), idx.cuda(), d_c=d_c, sm_scale=Dl ** -0.5)

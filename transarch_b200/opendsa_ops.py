@@ -172,36 +172,39 @@ class _SparseAttendAbsorbed(torch.autograd.Function):
     def backward(fctx, d_out):
         q_lat, latent, W_UV, indices, q_pos, ctx, lse = fctx.saved_tensors
         scale, L = fctx.sm_scale, q_lat.shape[0]
-        lat = latent.detach().float()
-        Wf = W_UV.detach().float()
+        # the five products run in the dtype of the inputs (bf16 inputs: bf16 operands on the tensor cores, fp32
+        # accumulation, as the reference's own backward under bf16); the softmax algebra stays fp32
+        cdt = torch.bfloat16 if q_lat.dtype == torch.bfloat16 and latent.dtype == torch.bfloat16 else torch.float32
+        lat = latent.detach().to(cdt)
+        Wc = W_UV.detach().to(cdt)
         need_q, need_l, need_w = fctx.needs_input_grad[0], fctx.needs_input_grad[1], fctx.needs_input_grad[2]
-        d_q = torch.empty_like(q_lat, dtype=torch.float32) if need_q else None
-        d_lat = torch.zeros_like(lat) if need_l else None
-        d_W = torch.zeros_like(Wf) if need_w else None
+        d_q = torch.empty(q_lat.shape, dtype=torch.float32, device=q_lat.device) if need_q else None
+        d_lat = torch.zeros(latent.shape, dtype=torch.float32, device=latent.device) if need_l else None
+        d_W = torch.zeros(W_UV.shape, dtype=torch.float32, device=W_UV.device) if need_w else None
         for t0 in range(0, L, fctx.q_chunk):
             t1 = min(t0 + fctx.q_chunk, L)
             idx = indices[t0:t1].long()
             valid = (idx >= 0) & (idx <= q_pos[t0:t1].long().view(-1, 1))
             idx = idx.clamp(min=0)
-            qc = q_lat[t0:t1].detach().float()
-            g = d_out[t0:t1].float()
-            cc = ctx[t0:t1].float()
+            qc = q_lat[t0:t1].detach().to(cdt)
+            g = d_out[t0:t1].to(cdt)
+            cc = ctx[t0:t1]
             sel = lat[idx]                                                   # [c,K,576]
-            s = torch.einsum("thd,tkd->thk", qc, sel) * scale
+            s = torch.einsum("thd,tkd->thk", qc, sel).float() * scale
             lse_c = lse[t0:t1].unsqueeze(-1)
             p = torch.exp(s - lse_c)
             p = torch.where(valid.unsqueeze(1) & torch.isfinite(lse_c), p, torch.zeros_like(p))
             if need_w:
-                d_W += torch.einsum("thv,thl->hvl", g, cc)
-            d_ctx = torch.einsum("thv,hvl->thl", g, Wf)                      # [c,H,512]
-            d_p = torch.einsum("thl,tkl->thk", d_ctx, sel[..., :512])
-            delta = (d_ctx * cc).sum(-1, keepdim=True)
-            d_s = p * (d_p - delta) * scale
+                d_W += torch.einsum("thv,thl->hvl", g, cc.to(cdt)).float()
+            d_ctx = torch.einsum("thv,hvl->thl", g, Wc)                      # [c,H,512]
+            d_p = torch.einsum("thl,tkl->thk", d_ctx, sel[..., :512]).float()
+            delta = (d_ctx.float() * cc.float()).sum(-1, keepdim=True)
+            d_s = (p * (d_p - delta) * scale).to(cdt)
             if need_q:
-                d_q[t0:t1] = torch.einsum("thk,tkd->thd", d_s, sel)
+                d_q[t0:t1] = torch.einsum("thk,tkd->thd", d_s, sel).float()
             if need_l:
-                d_sel = torch.einsum("thk,thd->tkd", d_s, qc)
-                d_sel[..., :512] += torch.einsum("thk,thl->tkl", p, d_ctx)
+                d_sel = torch.einsum("thk,thd->tkd", d_s, qc).float()
+                d_sel[..., :512] += torch.einsum("thk,thl->tkl", p.to(cdt), d_ctx).float()
                 d_lat.index_add_(0, idx.reshape(-1), d_sel.reshape(-1, d_sel.shape[-1]))
         return (None if d_q is None else d_q.to(q_lat.dtype), None if d_lat is None else d_lat.to(latent.dtype),
                 None if d_W is None else d_W.to(W_UV.dtype), None, None, None, None)
