@@ -524,6 +524,26 @@ int b200dsa_indexer_q_rope(const void* q_proj, int32_t in_f32, int64_t n_tokens,
                            void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Backward of the sparse MLA attention (the training form of sparse_attend_absorbed_chunked,
+ * OpenDSA/opendsa/ops/sparse_mla.py:26-48 under autograd): the two memory-bound steps around the dense
+ * products, per chunk of queries.
+ *   pointwise: p = exp(scale*s - lse) on valid entries (index >= 0 and <= q_pos), else 0;
+ *              ds = p * (dp - delta) * scale.   s, dp, p, ds: [n_queries, n_heads, n_idx] bf16 or fp32
+ *              (is_bf16), lse / delta fp32 [n_queries, n_heads], indices int32 [n_queries, n_idx] (a multiple
+ *              of 8 columns), q_pos int32 [n_queries].
+ *   scatter:   d_latent[indices[t,j], :] += rows_qk[t,j,0:576] + rows_v[t,j,0:512] (rows_v may be NULL) for
+ *              valid entries; d_latent fp32 [n_latent_rows, 576], accumulated with 16-byte vector reductions.
+ * ------------------------------------------------------------------------------------- */
+int b200dsa_sparse_attn_bwd_pointwise(const void* s, const void* dp, int32_t is_bf16, const float* lse,
+                                      const float* delta, const int32_t* indices, const int32_t* q_pos,
+                                      int32_t n_queries, int32_t n_heads, int32_t n_idx, float scale,
+                                      void* p_out, void* ds_out, void* stream);
+int b200dsa_scatter_add_latent_rows(float* d_latent, int64_t n_latent_rows, const void* rows_qk,
+                                    const void* rows_v, int32_t is_bf16, const int32_t* indices,
+                                    const int32_t* q_pos, int32_t n_queries, int32_t n_idx, int32_t* status,
+                                    void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Block mean pooling of index keys: pooled[j] = mean(keys[j*block : min((j+1)*block, n)]),
  * fp32 accumulation, the tail block divided by its true length.
  * Replaces MISA_preprint/misa_vllm_patch_2stage/misa_vllm_patch/block_ops.py:685-754

@@ -144,3 +144,49 @@ def test_wuv_up_projection_matches_einsum(T, H, dv):
     assert _lib.read_status(out32.device) == 0
     assert (out32.cpu() - ref).abs().max() < 1e-4 * ref.abs().max()        # bf16 products are exact in fp32
     assert (out16.float().cpu() - ref).abs().max() < 1e-2 * ref.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_backward_support_kernels(dtype):
+    """The two kernels of the attention backward against the same arithmetic in framework operations:
+    p / ds from raw scores (padding, future positions, a query without keys), and the fp32 scatter-add of the
+    per-(query, key) row gradients into d_latent (duplicates, skipped entries, an index beyond the rows)."""
+    from transarch_b200 import _lib, kernels as K
+    g = torch.Generator().manual_seed(9)
+    T, H, Kk, N = 13, 5, 40, 50
+    s = torch.randn(T, H, Kk, generator=g).to(dtype)
+    dp = torch.randn(T, H, Kk, generator=g).to(dtype)
+    idx = torch.randint(0, N, (T, Kk), generator=g, dtype=torch.int32)
+    idx[torch.rand(T, Kk, generator=g) < 0.2] = -1
+    q_pos = torch.randint(10, N, (T,), generator=g, dtype=torch.int32)
+    lse = torch.randn(T, H, generator=g) + 2.0
+    lse[3] = float("-inf")                                    # a query that saw no key
+    delta = torch.randn(T, H, generator=g)
+    scale = 0.37
+    p, ds = K.sparse_attn_bwd_pointwise(s.cuda(), dp.cuda(), lse.cuda(), delta.cuda(), idx.cuda(), q_pos.cuda(), scale)
+    valid = ((idx >= 0) & (idx <= q_pos.view(-1, 1))).unsqueeze(1) & torch.isfinite(lse).unsqueeze(-1)
+    p_ref = torch.where(valid, torch.exp(s.float() * scale - lse.unsqueeze(-1)), torch.zeros(T, H, Kk))
+    ds_ref = p_ref * (dp.float() - delta.unsqueeze(-1)) * scale
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert p.dtype == dtype and torch.allclose(p.float().cpu(), p_ref, rtol=tol, atol=tol)
+    assert torch.allclose(ds.float().cpu(), ds_ref, rtol=tol, atol=tol)
+    # scatter-add
+    a = torch.randn(T, Kk, 576, generator=g).to(dtype)
+    b = torch.randn(T, Kk, 512, generator=g).to(dtype)
+    d_lat = torch.zeros(N, 576, device="cuda")
+    K.scatter_add_latent_rows(d_lat, a.cuda(), b.cuda(), idx.cuda(), q_pos.cuda())
+    ok = (idx >= 0) & (idx <= q_pos.view(-1, 1))
+    rows = a.float().clone()
+    rows[..., :512] += b.float()
+    ref = torch.zeros(N, 576).index_add_(0, idx[ok].long(), rows[ok])
+    assert torch.allclose(d_lat.cpu(), ref, rtol=1e-5, atol=1e-4)
+    K.scatter_add_latent_rows(d_lat, a.cuda(), None, idx.cuda(), q_pos.cuda())          # without the value part
+    ref2 = ref + torch.zeros(N, 576).index_add_(0, idx[ok].long(), a.float()[ok])
+    assert torch.allclose(d_lat.cpu(), ref2, rtol=1e-5, atol=1e-4)
+    assert _lib.read_status(torch.device("cuda")) == 0
+    # an index past the destination is skipped and reported
+    small = torch.zeros(20, 576, device="cuda")
+    K.scatter_add_latent_rows(small, a.cuda(), None, idx.cuda(), torch.full((T,), N, dtype=torch.int32).cuda())
+    assert _lib.read_status(torch.device("cuda")) == 2
+    ok2 = (idx >= 0) & (idx < 20)
+    assert torch.allclose(small.cpu(), torch.zeros(20, 576).index_add_(0, idx[ok2].long(), a.float()[ok2]), rtol=1e-5, atol=1e-4)

@@ -69,6 +69,8 @@ SIGNATURES = {
     "b200dsa_indexer_q_rope": [_vp, _i32, _i64, _i32, _vp, _vp, _i32, _vp, _vp, _f32, _i32, _vp, _vp, _vp],
     "b200dsa_block_mean_pool_bf16": [_vp, _i32, _i32, _vp, _vp, _vp],
     "b200dsa_paged_mean_pool_fp8": [_vp, _i32, _i32, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp],
+    "b200dsa_sparse_attn_bwd_pointwise": [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _vp, _vp, _vp],
+    "b200dsa_scatter_add_latent_rows": [_vp, _i64, _vp, _vp, _i32, _vp, _vp, _i32, _i32, _vp, _vp],
     "b200dsa_paged_mean_pool_fp8_update": [_vp, _i32, _i32, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _vp,
                                            _vp, _vp],
     "b200dsa_router_qnorm_topk": [_vp, _vp, _i32, _i32, _vp, _vp, _vp],

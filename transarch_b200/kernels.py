@@ -782,6 +782,49 @@ def mma_peak_tflops(fp8: bool = True, *, iters: int = 4096, reps: int = 5, devic
     return best
 
 
+def sparse_attn_bwd_pointwise(s: torch.Tensor, dp: torch.Tensor, lse: torch.Tensor, delta: torch.Tensor,
+                              indices: torch.Tensor, q_pos: torch.Tensor, scale: float):
+    """(p, ds) of the attention backward from raw scores s and dp [T, H, K] (bf16 or fp32, same dtype out);
+    see b200dsa_sparse_attn_bwd_pointwise."""
+    require_cuda(s, dp, lse, delta, indices, q_pos)
+    if s.dtype not in (torch.bfloat16, torch.float32) or dp.dtype != s.dtype or s.shape != dp.shape or s.dim() != 3 or \
+            not s.is_contiguous() or not dp.is_contiguous():
+        raise _lib.B200DSAError("s and dp must be contiguous [T, H, K] of the same dtype (bf16 or fp32)")
+    T, H, Kk = s.shape
+    for t_, nm, shape in ((lse, "lse", (T, H)), (delta, "delta", (T, H))):
+        if t_.dtype != torch.float32 or not t_.is_contiguous() or tuple(t_.shape) != shape:
+            raise _lib.B200DSAError(f"{nm} must be contiguous fp32 [T, H]")
+    if _i32(indices, "indices").shape != (T, Kk) or _i32(q_pos, "q_pos").numel() != T:
+        raise _lib.B200DSAError("indices must be int32 [T, K] and q_pos int32 [T]")
+    p, ds = torch.empty_like(s), torch.empty_like(s)
+    check(_lib.load().b200dsa_sparse_attn_bwd_pointwise(ptr(s), ptr(dp), int(s.dtype == torch.bfloat16), ptr(lse),
+                                                       ptr(delta), ptr(indices), ptr(q_pos), T, H, Kk, scale, ptr(p),
+                                                       ptr(ds), stream_ptr()), "b200dsa_sparse_attn_bwd_pointwise")
+    return p, ds
+
+
+def scatter_add_latent_rows(d_latent: torch.Tensor, rows_qk: torch.Tensor, rows_v: Optional[torch.Tensor],
+                            indices: torch.Tensor, q_pos: torch.Tensor) -> None:
+    """d_latent[indices[t,j]] += rows_qk[t,j] (+ rows_v[t,j] on the first 512 columns) over the valid entries;
+    see b200dsa_scatter_add_latent_rows."""
+    require_cuda(d_latent, rows_qk, rows_v, indices, q_pos)
+    if d_latent.dtype != torch.float32 or not d_latent.is_contiguous() or d_latent.shape[-1] != 576:
+        raise _lib.B200DSAError("d_latent must be contiguous fp32 [rows, 576]")
+    if rows_qk.dtype not in (torch.bfloat16, torch.float32) or not rows_qk.is_contiguous() or rows_qk.dim() != 3 or \
+            rows_qk.shape[-1] != 576:
+        raise _lib.B200DSAError("rows_qk must be contiguous [T, K, 576] bf16 or fp32")
+    T, Kk = rows_qk.shape[:2]
+    if rows_v is not None and (rows_v.dtype != rows_qk.dtype or not rows_v.is_contiguous() or
+                               tuple(rows_v.shape) != (T, Kk, 512)):
+        raise _lib.B200DSAError("rows_v must be contiguous [T, K, 512] of the dtype of rows_qk")
+    if _i32(indices, "indices").shape != (T, Kk) or _i32(q_pos, "q_pos").numel() != T:
+        raise _lib.B200DSAError("indices must be int32 [T, K] and q_pos int32 [T]")
+    check(_lib.load().b200dsa_scatter_add_latent_rows(ptr(d_latent), d_latent.shape[0], ptr(rows_qk), ptr(rows_v),
+                                                     int(rows_qk.dtype == torch.bfloat16), ptr(indices), ptr(q_pos), T,
+                                                     Kk, ptr(status_word(d_latent.device)), stream_ptr()),
+          "b200dsa_scatter_add_latent_rows")
+
+
 def mma_shape_clocks(m: int, n: int, a_from_tmem: bool, *, iters: int = 2048, device=None) -> float:
     """SM clocks per bf16 tcgen05 MMA of shape m x n x 16 issued back to back, the A operand in shared or
     tensor memory (one CTA per SM, counted inside the kernel); see b200dsa_mma_shape_probe.  Synchronises."""

@@ -155,8 +155,9 @@ class _SparseAttendAbsorbed(torch.autograd.Function):
     """Training form of the op.  Forward: the attention kernel (bf16 latent context + fp32 log-sum-exp)
     and the W_UV kernel; only (q, latent, W_UV, indices, q_pos, ctx, lse) are kept.  Backward: per chunk
     of queries the probabilities are rebuilt from the saved log-sum-exp (p = exp(s - lse), no second
-    softmax pass) and the five products of the attention backward run as library GEMMs in fp32;
-    d_latent is accumulated with index_add_.  The reference reaches the same gradients by
+    softmax pass: b200dsa_sparse_attn_bwd_pointwise), the five products of the attention backward run as
+    library GEMMs on the gathered rows, and d_latent is accumulated in fp32 by
+    b200dsa_scatter_add_latent_rows.  The reference reaches the same gradients by
     checkpointing _attend_absorbed_chunk and letting autograd replay it
     (OpenDSA/opendsa/ops/sparse_mla.py:26-48, :96-104)."""
 
@@ -181,6 +182,11 @@ class _SparseAttendAbsorbed(torch.autograd.Function):
         d_q = torch.empty(q_lat.shape, dtype=torch.float32, device=q_lat.device) if need_q else None
         d_lat = torch.zeros(latent.shape, dtype=torch.float32, device=latent.device) if need_l else None
         d_W = torch.zeros(W_UV.shape, dtype=torch.float32, device=W_UV.device) if need_w else None
+        # on the GPU the element-wise step and the scatter-add are this library's kernels (one pass each); the
+        # same arithmetic in framework operations serves the host-side test of this function
+        fused = q_lat.is_cuda and indices.shape[1] % 8 == 0
+        idx32 = indices.to(torch.int32).contiguous()
+        qp32 = q_pos.to(torch.int32).contiguous()
         for t0 in range(0, L, fctx.q_chunk):
             t1 = min(t0 + fctx.q_chunk, L)
             idx = indices[t0:t1].long()
@@ -190,22 +196,32 @@ class _SparseAttendAbsorbed(torch.autograd.Function):
             g = d_out[t0:t1].to(cdt)
             cc = ctx[t0:t1]
             sel = lat[idx]                                                   # [c,K,576]
-            s = torch.einsum("thd,tkd->thk", qc, sel).float() * scale
-            lse_c = lse[t0:t1].unsqueeze(-1)
-            p = torch.exp(s - lse_c)
-            p = torch.where(valid.unsqueeze(1) & torch.isfinite(lse_c), p, torch.zeros_like(p))
+            s = torch.einsum("thd,tkd->thk", qc, sel)                        # raw scores
             if need_w:
                 d_W += torch.einsum("thv,thl->hvl", g, cc.to(cdt)).float()
             d_ctx = torch.einsum("thv,hvl->thl", g, Wc)                      # [c,H,512]
-            d_p = torch.einsum("thl,tkl->thk", d_ctx, sel[..., :512]).float()
-            delta = (d_ctx.float() * cc.float()).sum(-1, keepdim=True)
-            d_s = (p * (d_p - delta) * scale).to(cdt)
+            d_p = torch.einsum("thl,tkl->thk", d_ctx, sel[..., :512])
+            delta = (d_ctx.float() * cc.float()).sum(-1)
+            if fused:
+                p, d_s = K.sparse_attn_bwd_pointwise(s.contiguous(), d_p.contiguous(), lse[t0:t1].contiguous(),
+                                                     delta.contiguous(), idx32[t0:t1], qp32[t0:t1], scale)
+            else:
+                lse_c = lse[t0:t1].unsqueeze(-1)
+                p = torch.exp(s.float() * scale - lse_c)
+                p = torch.where(valid.unsqueeze(1) & torch.isfinite(lse_c), p, torch.zeros_like(p))
+                d_s = (p * (d_p.float() - delta.unsqueeze(-1)) * scale).to(cdt)
+                p = p.to(cdt)
             if need_q:
                 d_q[t0:t1] = torch.einsum("thk,tkd->thd", d_s, sel).float()
             if need_l:
-                d_sel = torch.einsum("thk,thd->tkd", d_s, qc).float()
-                d_sel[..., :512] += torch.einsum("thk,thl->tkl", p.to(cdt), d_ctx).float()
-                d_lat.index_add_(0, idx.reshape(-1), d_sel.reshape(-1, d_sel.shape[-1]))
+                d_sel = torch.einsum("thk,thd->tkd", d_s, qc)
+                d_sel_v = torch.einsum("thk,thl->tkl", p, d_ctx)
+                if fused:
+                    K.scatter_add_latent_rows(d_lat, d_sel.contiguous(), d_sel_v.contiguous(), idx32[t0:t1], qp32[t0:t1])
+                else:
+                    d_sel = d_sel.float()
+                    d_sel[..., :512] += d_sel_v.float()
+                    d_lat.index_add_(0, idx.reshape(-1), d_sel.reshape(-1, d_sel.shape[-1]))
         return (None if d_q is None else d_q.to(q_lat.dtype), None if d_lat is None else d_lat.to(latent.dtype),
                 None if d_W is None else d_W.to(W_UV.dtype), None, None, None, None)
 
