@@ -338,7 +338,34 @@ def bench_configs(dev, peaks, threads: int, fp8_peak: float, only=None, with_cpu
             "achieved_tflops": flops / med / 1e6, "frac_of_bf16_sustained": flops / med / 1e6 / bf16,
             "cpu_seconds": None, "cpu_kind": "not timed"}
 
-    for tag, fn in (("C1", c1), ("C2", c2), ("C3", c3), ("C4", c4), ("M1", m1)):
+    def t1():
+        """training form of the sparse attention (not a BASELINE configuration): forward + backward of
+        sparse_attend_absorbed_chunked, 2048 queries x 128 heads x top-2048, bf16, seed 6; beside it the reference's
+        own torch op on the same GPU"""
+        g = torch.Generator(device=dev).manual_seed(6)
+        L, H, Kk, Dv = 2048, 128, 2048, 128
+        q = (torch.randn(L, H, 576, generator=g, device=dev) * 0.3).bfloat16()
+        lat = (torch.randn(L, 576, generator=g, device=dev) * 0.3).bfloat16()
+        W = (torch.randn(H, Dv, 512, generator=g, device=dev) / 512 ** 0.5).bfloat16()
+        idx = (torch.rand(L, Kk, generator=g, device=dev) * (torch.arange(L, device=dev).view(-1, 1) + 1)).int()
+        G = torch.randn(L, H, Dv, generator=g, device=dev).bfloat16()
+
+        def fwd_bwd(fn):
+            x, y, z = (t.clone().requires_grad_() for t in (q, lat, W))
+            (fn(x, y, z, idx, d_c=512, sm_scale=576 ** -0.5, q_chunk=512).float() * G.float()).sum().backward()
+
+        med, mn = _time_call(lambda: fwd_bwd(opendsa_ops.sparse_attend_absorbed_chunked), flush, reps=5, warm=2)
+        ref_us = None
+        if ref is not None:
+            ref_us, _ = _time_call(lambda: fwd_bwd(ref.sparse_attend_absorbed_chunked), flush, reps=3, warm=1)
+        flops = int(L * H * Kk * (576 * 6 + 512 * 4))        # forward 2 products, backward 2 + 3 products
+        out["T1 sparse attention forward + backward, 2048 queries x 128 heads x top-2048 (bf16)"] = {
+            "call": "opendsa_ops.sparse_attend_absorbed_chunked under autograd", "us_median": med, "us_min": mn,
+            "flops": flops, "bound": "tensor", "achieved_tflops": flops / med / 1e6,
+            "frac_of_bf16_sustained": flops / med / 1e6 / bf16,
+            "reference_torch_op_same_gpu_us": ref_us, "cpu_seconds": None, "cpu_kind": "not timed"}
+
+    for tag, fn in (("C1", c1), ("C2", c2), ("C3", c3), ("C4", c4), ("M1", m1), ("T1", t1)):
         if want(tag):
             fn()
             torch.cuda.empty_cache()
@@ -382,7 +409,7 @@ def main():
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-configs", action="store_true", help="do not time the other configurations of the path")
     ap.add_argument("--skip-parity", action="store_true", help="do not compare sampled requests with the oracle")
-    ap.add_argument("--configs-only", default="", help="comma-separated subset of C1,C2,C3,C4,M1: time only these "
+    ap.add_argument("--configs-only", default="", help="comma-separated subset of C1,C2,C3,C4,M1,T1: time only these "
                     "configurations (no decode step) and print them; for profiling single kernels")
     ap.add_argument("--config-reps", type=int, default=0, help="timed repetitions per configuration (default 50)")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
