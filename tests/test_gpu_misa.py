@@ -275,3 +275,37 @@ def test_single_pass_gated_and_full_scores():
     g2_ref = K.indexer_blocklist_bf16_logits(qb, gate_weights_by_heads(wb, hb), k, bl, row_cols, pos_lo=ks, pos_hi=ke)
     assert torch.equal(f2, f2_ref) and torch.equal(g2, g2_ref)
     assert _lib.read_status(full.device) == 0
+
+
+def test_misa_prefill_two_stage_edge_cases():
+    """Two-stage routed prefill where the pieces do not line up: five kept heads (padded to eight with zero
+    weights), a stage-1 budget that is no multiple of 128, queries that see fewer keys than the budget (their
+    candidate rows end in -1 / -inf), and a query count that is no multiple of 32."""
+    from transarch_b200 import misa as M
+    g = torch.Generator().manual_seed(41)
+    Mq, N, s1 = 45, 2600, 1000
+    k = torch.randn(N, 128, generator=g)
+    kq, sc = O.quant_fp8_rows(k)
+    q = torch.randn(Mq, 64, 128, generator=g)
+    w = torch.randn(Mq, 64, generator=g) / 8
+    q_fp8, wf = O.quant_q_fold_weights(q, w, 128 ** -0.5, 64 ** -0.5)
+    ke = torch.randint(1, N + 1, (Mq,), generator=g, dtype=torch.int32)
+    ke[:5] = torch.tensor([1, 7, 130, 999, 1001], dtype=torch.int32)      # fewer keys than the budget
+    ks = torch.zeros(Mq, dtype=torch.int32)
+    hidx = O.qnorm_head_topk(q, 5)
+    logits, cand = M.misa_mqa_logits(q_fp8.cuda(), (kq.cuda(), sc.cuda()), wf.cuda(), hidx.cuda(), ks.cuda(), ke.cuda(),
+                                     True, 5, s1)
+    assert logits.shape == (Mq, s1) and cand.shape == (Mq, s1)
+    kb = (kq.float() * sc.unsqueeze(-1)).bfloat16().float()
+    qf = q_fp8.float()
+    q8, w8 = O.gather_heads(qf, wf, hidx)
+    s1_scores = O.mask_interval(O.indexer_scores(q8, kb, w8, 1.0), ks.long(), ke.long())
+    ref_cand = O.topk_rows(s1_scores, s1)
+    O.assert_selection_parity(cand.cpu(), ref_cand, s1_scores, 2e-3, what="stage-1 candidates, five heads")
+    n_valid = (cand.cpu() >= 0).sum(1)
+    assert torch.equal(n_valid, torch.minimum(ke.long(), torch.tensor(s1)))
+    full = O.mask_interval(O.indexer_scores(qf, kb, wf, 1.0), ks.long(), ke.long())
+    got = torch.gather(full, 1, cand.cpu().clamp(min=0).long())
+    ok = cand.cpu() >= 0
+    assert O.rel_err(logits.cpu()[ok], got[ok]) < 2e-3
+    assert torch.isinf(logits.cpu()[~ok]).all() and (logits.cpu()[~ok] < 0).all()
