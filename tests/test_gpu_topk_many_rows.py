@@ -1,6 +1,7 @@
 """The one-warp-per-row selection that b200dsa_topk_select uses for many short rows (unordered results, and
-ordered ones of up to 256 winners), against a stable sort and against the one-CTA-per-row kernel (reached
-through a row count below the switch or an ordered result of many winners): same sets, same order."""
+ordered ones of up to 256 winners; at least 1024 rows, at least as many rows as columns, at most 4096 columns),
+against a stable sort and against the one-CTA-per-row kernel (reached through a row count below the switch or
+an ordered result of many winners): same sets, same order."""
 import pytest
 import torch
 
@@ -30,8 +31,8 @@ def _ref_sorted(scores, k, begin=None, end=None, keep_inf=False):
     return out
 
 
-@pytest.mark.parametrize("n_rows,n_cols,k", [(300, 4096, 2048), (257, 1024, 64), (512, 8192, 2048), (260, 700, 1000),
-                                             (256, 16384, 4096), (400, 3000, 256), (300, 90, 200)])
+@pytest.mark.parametrize("n_rows,n_cols,k", [(4100, 4096, 2048), (1100, 1024, 64), (1030, 700, 1000), (3100, 3000, 256),
+                                             (1024, 90, 200), (1500, 1024, 4096)])
 def test_many_rows_match_the_oracle(n_rows, n_cols, k):
     from transarch_b200 import kernels as K
     g = torch.Generator().manual_seed(n_cols + k)
@@ -59,7 +60,7 @@ def test_many_rows_massive_ties_and_position_maps(k):
     they do not grow with the column; thousands of exactly equal scores (zeros) around the threshold."""
     from transarch_b200 import kernels as K
     g = torch.Generator().manual_seed(5)
-    n_rows, n_cols = 300, 2048
+    n_rows, n_cols = 2100, 2048
     s = torch.zeros(n_rows, n_cols)
     hot = torch.rand(n_rows, n_cols, generator=g) < 0.2
     s[hot] = torch.randn(int(hot.sum()), generator=g).abs()      # about 400 positive scores, the rest exact zeros
@@ -71,7 +72,7 @@ def test_many_rows_massive_ties_and_position_maps(k):
     col = torch.arange(n_cols)
     pos = pages.long()[:, col // 128] * 128 + (col % 128)
     # reference: sort by (score desc, position asc)
-    for r in (0, 17, 299):
+    for r in (0, 17, 2099):
         order = sorted(range(n_cols), key=lambda c: (-float(s[r, c]), int(pos[r, c])))[:k]
         assert got[r].tolist() == [int(pos[r, c]) for c in order]
     un = K.topk_select(s.cuda(), k, page_table=pages.cuda(), page_size=128, sorted=False).cpu()   # one warp per row

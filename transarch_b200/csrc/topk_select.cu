@@ -1142,11 +1142,12 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
   }
   int k_pow2 = 32;
   while (k_pow2 < k) k_pow2 <<= 1;
-  // many short rows: one warp per row; an ordered result of a few winners is sorted by a second pass (which
-  // needs the scores next to the positions), an ordered result of thousands stays with the kernel below, whose
-  // sort runs on the winners while they are still in shared memory (533 against 562 us for 4096 rows of 8192
-  // columns and k = 2048; unordered 383 against 419 us, top-64 of 1024 columns 65 against 97 us)
-  if (n_rows >= 256 && n_cols <= 16384 && k <= 4096 && seg_cols == 0 &&
+  // many short rows: one warp per row.  A warp needs about 19 us per 1024 columns of its row, so this pays once
+  // there are enough rows to hide that (4096 rows: 1024 columns 41 against 76 us, 4096 columns 138 against 199 us;
+  // 1024 rows of 4096 columns 79 against 55 us, rows of 8192 columns never).  An ordered result of a few winners
+  // is sorted by a second pass (which needs the scores next to the positions); an ordered result of thousands
+  // stays with the kernel below, whose sort runs on the winners while they are still in shared memory.
+  if (n_rows >= 1024 && n_cols <= 4096 && n_rows >= n_cols && k <= 4096 && seg_cols == 0 &&
       (!sorted || (k <= 256 && out_val != nullptr))) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e2 = launch_chained(topk_warp_select_kernel, dim3((n_rows + kWselWarps - 1) / kWselWarps),
