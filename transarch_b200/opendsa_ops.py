@@ -112,14 +112,14 @@ def indexer_select_topk(index_q, index_k, index_w, cu_seqlens, topk, *, sm_scale
     q, w = _pad_heads(index_q.to(torch.bfloat16), index_w.to(torch.float32))
     k = index_k.to(torch.bfloat16).contiguous()
     Lk = k.shape[0]
-    out = torch.full((Lq, topk), -1, dtype=torch.int32, device=index_q.device)
-    if Lq == 0 or Lk == 0:
-        return out
-    cols = ((Lk + _BLOCK - 1) // _BLOCK) * _BLOCK
-    rows_per = max(1, min(q_chunk, _MAX_LOGIT_BYTES // (cols * 4)))
-    k_eff = min(topk, 8192)
     if topk > 8192:
         raise B200DSAError("topk above 8192 is not supported")
+    if Lq == 0 or Lk == 0:
+        return torch.full((Lq, topk), -1, dtype=torch.int32, device=index_q.device)
+    out = torch.empty(Lq, topk, dtype=torch.int32, device=index_q.device)     # the selection writes every column
+    cols = ((Lk + _BLOCK - 1) // _BLOCK) * _BLOCK
+    rows_per = max(1, min(q_chunk, _MAX_LOGIT_BYTES // (cols * 4)))
+    k_eff = topk
     buf = torch.empty(min(rows_per, Lq), cols, dtype=torch.float32, device=index_q.device)   # read below row_cols only
     for t0 in range(0, Lq, rows_per):
         t1 = min(t0 + rows_per, Lq)
