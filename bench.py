@@ -663,6 +663,7 @@ def main():
     # "indexer + top-k per step" figure without the host's launch gaps of the eager stage split above.
     select_us = None
     partial_us = {}
+    attention_kernels_us = None
 
     def graph_time(fn):
         """us per replay of fn captured into its own CUDA graph (max over ranks)."""
@@ -697,6 +698,21 @@ def main():
             return step.select(sel_q, sel_w, state.k_cache, state.context_lens_local, state.block_table)
 
         select_us = graph_time(do_select)
+        if world == 1:
+            # the two attention kernels by themselves, each from a graph of its own: the head-split kernel the step
+            # uses (M = 64) and the cluster-of-two kernel that reaches M = 128 by exchanging partial scores
+            att_idx = do_select().clone()
+            att_ctx = torch.empty(B, sel_lat.shape[1], 512, dtype=torch.bfloat16, device=dev)
+            att_lse = torch.empty(B, sel_lat.shape[1], dtype=torch.float32, device=dev)
+
+            def attend_with(pair):
+                return lambda: step.K.sparse_mla_decode(sel_lat, state.kv, att_idx, step.attn_scale,
+                                                        kv_row_base=state.kv_row_base, q_pos=state.context_lens,
+                                                        q_pos_bias=-1, ctx=att_ctx, lse=att_lse, pair=pair)
+
+            attention_kernels_us = {"heads_split_m64": round(graph_time(attend_with(False)), 2),
+                                    "cluster_pair_m128": round(graph_time(attend_with(True)), 2)}
+            del att_idx, att_ctx, att_lse
         if world > 1:
             # prefixes of the sharded step, each from its own graph: the differences are the exchange stages
             # Every prefix ends with a node barrier (its own kernel) so that no rank starts the next replay
@@ -815,6 +831,7 @@ def main():
                                       (B * shard_len * (132 + 8)) / (select_us * 1e-6) / 1e9 / peaks["hbm_gbs"]),
             "stage_us": {k_: round(1e3 * v, 2) for k_, v in stage_ms.items()},
             "graph_stage_us": partial_us,
+            "attention_kernels_us": attention_kernels_us,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps, "note": e2e_note, "h2d_copy_alone_ms": h2d_only_ms,
                     "h2d_copy_alone_gbs": h2d / (h2d_only_ms * 1e-3) / 1e9},

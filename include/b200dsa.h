@@ -354,6 +354,19 @@ int b200dsa_sparse_mla_decode(const void* q_bf16, const void* kv_bf16, int64_t k
                               int32_t n_items, int32_t n_heads, float sm_scale, void* ctx, int32_t ctx_bf16,
                               float* lse, int32_t* status, void* stream);
 
+/* Same arguments and results as b200dsa_sparse_mla_decode, computed by the cluster-of-two kernel: the two
+ * CTAs of an item split the latent dimensions instead of the heads, so that all 128 heads form one UMMA
+ * M = 128 tile (full tensor rate) and every selected row is fetched once; partial scores and probabilities
+ * cross the cluster through shared memory (bulk copies to one CTA, no multicast).  Measured slower than the
+ * default kernel on B200 (86 against 63 us at 64 items x 128 heads x 2048 keys: the exchange is bound by
+ * the bandwidth between the two CTAs' shared memories), so nothing in the library selects it by itself. */
+int b200dsa_sparse_mla_decode_pair(const void* q_bf16, const void* kv_bf16, int64_t kv_rows,
+                                   const int64_t* kv_row_base, const int32_t* indices, int64_t idx_stride,
+                                   int32_t n_idx, const int32_t* n_idx_item, const int32_t* q_pos,
+                                   int32_t q_pos_bias, int32_t pos_lo, int32_t pos_hi,
+                                   int32_t n_items, int32_t n_heads, float sm_scale, void* ctx, int32_t ctx_bf16,
+                                   float* lse, int32_t* status, void* stream);
+
 /* b200dsa_sparse_mla_decode for a rank of the key-sharded step: after the last CTA has written (and
  * fenced) its part of ctx / lse, which the caller placed in this rank's exchange buffer, the kernel raises
  * this rank's "partial ready" flag on every rank, so that b200dsa_peer_lse_combine(pre_signalled = 1)

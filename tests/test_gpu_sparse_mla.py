@@ -42,7 +42,8 @@ def test_golden_mla_shape_matches_reference_output():
 
 @pytest.mark.parametrize("n_items,H,n_idx,ctx_len", [(3, 128, 2048, 5000), (2, 16, 64, 300), (4, 128, 100, 4000),
                                                       (1, 128, 33, 50)])
-def test_decode_vs_oracle(n_items, H, n_idx, ctx_len):
+@pytest.mark.parametrize("pair", [False, True], ids=["heads_split", "cluster_pair"])
+def test_decode_vs_oracle(n_items, H, n_idx, ctx_len, pair):
     from transarch_b200 import _lib, kernels as K
     g = torch.Generator().manual_seed(n_idx + H)
     q = torch.randn(n_items, H, 576, generator=g).bfloat16()
@@ -54,7 +55,7 @@ def test_decode_vs_oracle(n_items, H, n_idx, ctx_len):
     qpos[0] = ctx_len // 2                                  # masks about half of item 0's picks
     scale = 192 ** -0.5
     ctx, lse = K.sparse_mla_decode(q.cuda(), kv.cuda(), idx.cuda(), scale, kv_row_base=base.cuda(),
-                                   q_pos=qpos.cuda())
+                                   q_pos=qpos.cuda(), pair=pair)
     assert _lib.read_status(ctx.device) == 0
     for b in range(n_items):
         rc, rl = O.sparse_attend_latent(q[b:b + 1], kv[b * ctx_len:(b + 1) * ctx_len], idx[b:b + 1],
@@ -63,11 +64,12 @@ def test_decode_vs_oracle(n_items, H, n_idx, ctx_len):
     # bf16 result buffer (the dtype the reference op returns): the fp32 result rounded once
     out16 = torch.empty(n_items, H, 512, dtype=torch.bfloat16, device="cuda")
     ctx16, lse16 = K.sparse_mla_decode(q.cuda(), kv.cuda(), idx.cuda(), scale, kv_row_base=base.cuda(),
-                                       q_pos=qpos.cuda(), ctx=out16)
+                                       q_pos=qpos.cuda(), ctx=out16, pair=pair)
     assert ctx16.dtype == torch.bfloat16 and torch.equal(ctx16, ctx.bfloat16()) and torch.equal(lse16, lse)
 
 
-def test_shard_partials_merge_to_full():
+@pytest.mark.parametrize("pair", [False, True], ids=["heads_split", "cluster_pair"])
+def test_shard_partials_merge_to_full(pair):
     """Two position shards attended separately and merged by log-sum-exp equal the full result."""
     from transarch_b200 import kernels as K
     g = torch.Generator().manual_seed(77)
@@ -81,14 +83,16 @@ def test_shard_partials_merge_to_full():
     parts, lses = [], []
     for lo, hi in [(0, 1400), (1400, ctx_len)]:
         c, l = K.sparse_mla_decode(q.cuda(), kv[lo:hi].contiguous().cuda(), idx.cuda(), scale,
-                                   pos_lo=lo, pos_hi=hi)
+                                   pos_lo=lo, pos_hi=hi, pair=pair)
         parts.append(c.cpu()); lses.append(l.cpu())
     out, lse = O.lse_combine(parts, lses)
     _check(out, lse, full_ctx, full_lse)
 
 
-def test_large_scores_trigger_rescale():
-    """Keys ordered so that the running maximum keeps growing: exercises the O rescale path."""
+@pytest.mark.parametrize("pair", [False, True], ids=["heads_split", "cluster_pair"])
+def test_large_scores_trigger_rescale(pair):
+    """Keys ordered so that the running maximum keeps growing: exercises the O rescale path (in the
+    cluster-of-two kernel also the factors that travel to the partner CTA)."""
     from transarch_b200 import kernels as K
     g = torch.Generator().manual_seed(78)
     H, n_idx = 128, 256
@@ -97,12 +101,13 @@ def test_large_scores_trigger_rescale():
     kv = (kv * torch.linspace(0.2, 6.0, n_idx).view(-1, 1)).bfloat16()   # later keys: far larger scores
     idx = torch.arange(n_idx, dtype=torch.int32).view(1, -1)
     scale = 0.3
-    ctx, lse = K.sparse_mla_decode(q.cuda(), kv.cuda(), idx.cuda(), scale)
+    ctx, lse = K.sparse_mla_decode(q.cuda(), kv.cuda(), idx.cuda(), scale, pair=pair)
     rc, rl = O.sparse_attend_latent(q, kv, idx, d_c=512, sm_scale=scale, q_pos=torch.tensor([n_idx]))
     _check(ctx.cpu(), lse.cpu(), rc, rl)
 
 
-def test_out_of_range_row_is_skipped_and_reported():
+@pytest.mark.parametrize("pair", [False, True], ids=["heads_split", "cluster_pair"])
+def test_out_of_range_row_is_skipped_and_reported(pair):
     """An index that points past the latent cache is not read: the kernel drops that key, raises the
     status word to 2 (a skipped index) and the result equals attention over the remaining keys."""
     from transarch_b200 import _lib, kernels as K
@@ -116,7 +121,7 @@ def test_out_of_range_row_is_skipped_and_reported():
     scale = 192 ** -0.5
     dev = torch.device("cuda")
     assert _lib.read_status(dev) == 0
-    ctx, lse = K.sparse_mla_decode(q.cuda(), kv.cuda(), bad.cuda(), scale)
+    ctx, lse = K.sparse_mla_decode(q.cuda(), kv.cuda(), bad.cuda(), scale, pair=pair)
     torch.cuda.synchronize()
     assert _lib.read_status(dev) == 2
     good = idx.clone()
@@ -126,9 +131,30 @@ def test_out_of_range_row_is_skipped_and_reported():
                                         q_pos=torch.tensor([rows]))
         _check(ctx[b:b + 1].cpu(), lse[b:b + 1].cpu(), rc, rl)
     # the word was cleared by the read; a clean call leaves it at 0
-    K.sparse_mla_decode(q.cuda(), kv.cuda(), good.cuda(), scale)
+    K.sparse_mla_decode(q.cuda(), kv.cuda(), good.cuda(), scale, pair=pair)
     torch.cuda.synchronize()
     assert _lib.read_status(dev) == 0
+
+
+def test_cluster_pair_kernel_agrees_with_heads_split_kernel():
+    """Same inputs through both attention kernels (64 items, 96 heads: the pair kernel pads to 128 rows)."""
+    from transarch_b200 import _lib, kernels as K
+    g = torch.Generator().manual_seed(31)
+    n, H, n_idx, rows = 64, 96, 700, 20000
+    q = torch.randn(n, H, 576, generator=g).bfloat16().cuda()
+    kv = (0.5 * torch.randn(rows, 576, generator=g)).bfloat16().cuda()
+    idx = torch.randint(0, rows, (n, n_idx), generator=g).to(torch.int32).cuda()
+    idx[:, 5::11] = -1
+    lens = torch.randint(0, n_idx + 1, (n,), generator=g).to(torch.int32).cuda()
+    lens[0] = 0                                                     # an item without keys
+    a, la = K.sparse_mla_decode(q, kv, idx, 0.07, n_idx_item=lens)
+    b, lb = K.sparse_mla_decode(q, kv, idx, 0.07, n_idx_item=lens, pair=True)
+    assert _lib.read_status(q.device) == 0
+    assert (a[0] == 0).all() and (b[0] == 0).all() and torch.isinf(lb[0]).all()
+    assert torch.equal(torch.isfinite(la), torch.isfinite(lb))
+    fin = torch.isfinite(la)
+    assert (la[fin] - lb[fin]).abs().max() < 1e-3
+    assert (a - b).abs().max() / a.abs().max() < 5e-3
 
 
 @pytest.mark.parametrize("T,H,dv", [(64, 128, 128), (200, 16, 96), (5, 8, 8), (129, 3, 256)])

@@ -44,6 +44,8 @@ SIGNATURES = {
     "b200dsa_compact_owned": [_vp, _i64, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _vp],
     "b200dsa_sparse_mla_decode": [_vp, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32,
                                   _vp, _i32, _vp, _vp, _vp],
+    "b200dsa_sparse_mla_decode_pair": [_vp, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32,
+                                       _f32, _vp, _i32, _vp, _vp, _vp],
     "b200dsa_wuv_up_project": [_vp, _vp, _i32, _i32, _i32, _vp, _i32, _vp, _vp],
     "b200dsa_lse_combine": [_vp, _vp, _i32, _i64, _vp, _vp, _vp],
     "b200dsa_peer_lse_combine": [_vp, _i32, _i32, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _i32, _i32, _i32, _vp, _vp],

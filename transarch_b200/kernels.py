@@ -472,11 +472,12 @@ def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, 
                       kv_row_base: Optional[torch.Tensor] = None, q_pos: Optional[torch.Tensor] = None,
                       pos_lo: int = 0, pos_hi: int = 2 ** 31 - 1, n_idx_item: Optional[torch.Tensor] = None,
                       ctx: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
-                      q_pos_bias: int = 0, signal=None) -> Tuple[torch.Tensor, torch.Tensor]:
+                      q_pos_bias: int = 0, signal=None, pair: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """Latent-space sparse attention: (ctx [n, H, 512], lse [n, H] fp32); see
     b200dsa_sparse_mla_decode.  ctx is fp32 unless a bf16 buffer is passed in; q_pos_bias is added to
     q_pos (-1: q_pos holds context lengths).  signal=(link, ticket): the kernel's last CTA raises this
-    rank's "partial ready" flag on every rank (b200dsa_sparse_mla_decode_signal)."""
+    rank's "partial ready" flag on every rank (b200dsa_sparse_mla_decode_signal).  pair=True runs the
+    cluster-of-two kernel (b200dsa_sparse_mla_decode_pair: same results, measured slower)."""
     require_cuda(q, kv, indices, kv_row_base, q_pos)
     if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.dim() != 3 or q.shape[2] != 576:
         raise _lib.B200DSAError("q must be contiguous bf16 [n_items, n_heads, 576]")
@@ -498,7 +499,11 @@ def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, 
     args = (ptr(q), ptr(kv), kv.shape[0], ptr(kv_row_base), ptr(indices), indices.stride(0), indices.shape[1],
             ptr(_i32(n_idx_item, "n_idx_item")), ptr(q_pos), q_pos_bias, pos_lo, pos_hi, n, H, sm_scale, ptr(ctx),
             int(ctx.dtype == torch.bfloat16), ptr(lse))
-    if signal is None:
+    if pair:
+        if signal is not None:
+            raise _lib.B200DSAError("the cluster-of-two kernel has no signalling form")
+        rc = lib.b200dsa_sparse_mla_decode_pair(*args, ptr(status_word(q.device)), stream_ptr())
+    elif signal is None:
         rc = lib.b200dsa_sparse_mla_decode(*args, ptr(status_word(q.device)), stream_ptr())
     else:
         link, ticket = signal
