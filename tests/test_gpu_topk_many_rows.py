@@ -1,7 +1,6 @@
-"""The one-warp-per-row selection that b200dsa_topk_select uses for many short rows (unordered results, and
-ordered ones of up to 256 winners; at least 1024 rows, at least as many rows as columns, at most 4096 columns),
-against a stable sort and against the one-CTA-per-row kernel (reached through a row count below the switch or
-an ordered result of many winners): same sets, same order."""
+"""The row-in-shared-memory selection that b200dsa_topk_select uses for many rows (at least 256 rows of at most
+8192 columns, k up to 4096), against a stable sort and against the large one-CTA-per-row kernel (reached through
+a row count below the switch): same sets, same order."""
 import pytest
 import torch
 
@@ -32,7 +31,7 @@ def _ref_sorted(scores, k, begin=None, end=None, keep_inf=False):
 
 
 @pytest.mark.parametrize("n_rows,n_cols,k", [(4100, 4096, 2048), (1100, 1024, 64), (1030, 700, 1000), (3100, 3000, 256),
-                                             (1024, 90, 200), (1500, 1024, 4096)])
+                                             (1024, 90, 200), (1500, 1024, 4096), (300, 8192, 2048), (256, 8190, 4096)])
 def test_many_rows_match_the_oracle(n_rows, n_cols, k):
     from transarch_b200 import kernels as K
     g = torch.Generator().manual_seed(n_cols + k)
@@ -67,7 +66,7 @@ def test_many_rows_massive_ties_and_position_maps(k):
     s[:, 100:140] = 0.5                                           # a run of equal positive scores as well
     pages = torch.stack([torch.randperm(64, generator=g)[:16] for _ in range(n_rows)]).int()   # 16 pages of 128
     got = K.topk_select(s.cuda(), k, page_table=pages.cuda(), page_size=128, sorted=True).cpu()
-    few = K.topk_select(s[:40].cuda(), k, page_table=pages[:40].cuda(), page_size=128, sorted=True).cpu()  # CTA-per-row
+    few = K.topk_select(s[:40].cuda(), k, page_table=pages[:40].cuda(), page_size=128, sorted=True).cpu()  # large CTA per row
     assert torch.equal(got[:40], few)
     col = torch.arange(n_cols)
     pos = pages.long()[:, col // 128] * 128 + (col % 128)
@@ -75,7 +74,7 @@ def test_many_rows_massive_ties_and_position_maps(k):
     for r in (0, 17, 2099):
         order = sorted(range(n_cols), key=lambda c: (-float(s[r, c]), int(pos[r, c])))[:k]
         assert got[r].tolist() == [int(pos[r, c]) for c in order]
-    un = K.topk_select(s.cuda(), k, page_table=pages.cuda(), page_size=128, sorted=False).cpu()   # one warp per row
+    un = K.topk_select(s.cuda(), k, page_table=pages.cuda(), page_size=128, sorted=False).cpu()
     assert torch.equal(torch.sort(un, dim=1).values, torch.sort(got, dim=1).values)
     # plain columns
     a = K.topk_select(s.cuda(), k, sorted=True).cpu()

@@ -915,194 +915,160 @@ topk_collect_kernel(const TopkParams p, int splits, const int32_t* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------------------------
-// Many short rows (causal prefill, HISA block and token selections: thousands of rows of a few thousand
-// columns): one WARP per row, eight rows per CTA, 64 rows in flight per SM.  The one-CTA-per-row kernel above
-// spends such rows in block barriers and shared-memory passes; here a row is never staged: the warp re-reads
-// it (from L2) once per radix digit and once to emit.
-//
-// Exact MSD radix select on the 64-bit composite (ordered score ‖ ~position), eight bits per pass, into a
-// warp-private 256-bin histogram (lanes that hold the same digit are merged with match.any, so no atomics).
-// A pass ends the search as soon as the bin that holds the k-th key holds exactly as many keys as are still
-// wanted: every key at or above the decided prefix then wins.  Composites are unique, so this happens at the
-// latest after the eighth pass; distinct scores need two to four.  Positions are only computed for passes
-// beyond the 32 score bits (ties) and for the winners.  Output order is the scan order (unsorted).
+// Many rows of at most 8192 columns: a 256-thread CTA per row with the whole row in shared memory as
+// 32-bit order-preserving keys (0 marks an invalid score), several CTAs per SM so that the block-wide
+// steps of one row hide behind those of the others.  Exact most-significant-digit radix select with 12 /
+// 12 / 8-bit digits over the score key; only when more keys tie at the k-th score than are still wanted
+// does it go on over the bit-inverted positions of the tied keys (12 / 12 / 8 bits again), so positions
+// are computed for tied keys and for winners only.  The level-0 histogram is filled while the row is
+// loaded.  Winners leave in scan order, or through the counting sort when an ordered result is asked for.
 // ---------------------------------------------------------------------------------------------
-constexpr int kWselWarps = 8;
+constexpr int kRowsThreads = 256;
+constexpr int kRowsMaxCols = 8192;
+constexpr int kRowsMinRows = 256;
 
-__global__ void __launch_bounds__(kWselWarps * 32) topk_warp_select_kernel(const TopkParams p) {
-  __shared__ uint32_t s_hist[kWselWarps][256];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.x * kWselWarps + warp;
-  if (row >= p.n_rows) return;
-  uint32_t* hist = s_hist[warp];
+__global__ void __launch_bounds__(kRowsThreads) topk_rows_kernel(const TopkParams p, int key_words, int k_pow2) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw);                 // 4096 bins
+  uint32_t* keys = hist + kHistBins;                                      // the row; later the sort's scratch
+  uint64_t* sel = reinterpret_cast<uint64_t*>(keys + key_words);          // ordered result only: the winners
+  __shared__ int s_res[3], s_cnt;
+  __shared__ uint32_t s_seg[32];
+
+  const int row = blockIdx.x;
+  const int tid = threadIdx.x;
   int begin = p.col_begin ? p.col_begin[row] : 0;
   int end = p.col_end ? p.col_end[row] : p.n_cols;
   begin = max(begin, 0);
   end = min(end, p.n_cols);
-  const float* src = p.scores + row * p.row_stride;
+  const int n = max(0, end - begin);
+  const float* src = p.scores + row * p.row_stride + begin;
   int32_t* out_idx = p.out_idx + row * p.out_stride;
   float* out_val = p.out_val ? p.out_val + row * p.out_stride : nullptr;
   const int k = p.k;
-  const unsigned below = (1u << lane) - 1u;
 
-  uint64_t prefix = 0;
-  int pbits = 0, need = k;
-  bool take_all = end <= begin;
-  for (int pass = 0; pass < 8 && !take_all; ++pass) {
-    const bool need_pos = pass >= 4;
+  for (int i = tid; i < kHistBins; i += kRowsThreads) hist[i] = 0;
+  if (tid == 0) s_cnt = 0;
+  __syncthreads();
+  // ---- load: keys to shared memory, level-0 histogram (top 12 bits) on the way
+  for (int base = 0; base < n; base += kRowsThreads * 8) {
+    float v[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) hist[lane * 8 + i] = 0;
-    __syncwarp();
-    for (int base = begin; base < end; base += 128) {
-      float v[4];
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + u * kRowsThreads + tid;
+      v[u] = i < n ? __ldg(src + i) : 0.f;
+    }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int col = base + u * 32 + lane;
-        v[u] = col < end ? __ldg(src + col) : 0.f;
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + u * kRowsThreads + tid;
+      if (i < n) {
+        const bool ok = score_valid(v[u], p.keep_pos_inf);
+        const uint32_t key = ok ? float_to_ordered(v[u]) : 0u;
+        keys[i] = key;
+        if (ok) atomicAdd(&hist[key >> 20], 1u);
       }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int col = base + u * 32 + lane;
-        bool ok = col < end && score_valid(v[u], p.keep_pos_inf);
-        uint64_t key = static_cast<uint64_t>(float_to_ordered(v[u])) << 32;
-        if (ok && pbits > 0) ok = (key >> (64 - min(pbits, 32))) == (pbits <= 32 ? prefix : (prefix >> (pbits - 32)));
-        if (ok && need_pos) {
-          key |= static_cast<uint32_t>(~static_cast<uint32_t>(out_position(p, row, col)));
-          ok = (key >> (64 - pbits)) == prefix;
+    }
+  }
+  __syncthreads();
+
+  // ---- radix select.  Decided so far: the top kbits of the score key (tkey), then the top nbits of ~position
+  uint32_t tkey = 0, tnpos = 0;
+  int kbits = 0, nbits = 0, need = k;
+  bool take_all = false;
+  auto npos_of = [&](int i) { return ~static_cast<uint32_t>(out_position(p, row, begin + i)); };
+#pragma unroll 1
+  for (int level = 0; level < 6; ++level) {
+    const int width = (level % 3 == 2) ? 8 : 12;
+    if (level > 0) {
+      for (int i = tid; i < kHistBins; i += kRowsThreads) hist[i] = 0;
+      __syncthreads();
+      for (int i = tid; i < n; i += kRowsThreads) {
+        const uint32_t key = keys[i];
+        if (key == 0u) continue;
+        if (level < 3) {
+          if ((key >> (32 - kbits)) != (tkey >> (32 - kbits))) continue;
+          atomicAdd(&hist[(key >> (32 - kbits - width)) & ((1u << width) - 1u)], 1u);
+        } else {
+          if (key != tkey) continue;
+          const uint32_t np = npos_of(i);
+          if (nbits > 0 && (np >> (32 - nbits)) != (tnpos >> (32 - nbits))) continue;
+          atomicAdd(&hist[(np >> (32 - nbits - width)) & ((1u << width) - 1u)], 1u);
         }
-        const uint32_t digit = static_cast<uint32_t>(key >> (56 - pbits)) & 255u;
-        if (ok) atomicAdd(&hist[digit], 1u);
       }
+      __syncthreads();
     }
-    // lane l owns bins 8l .. 8l+7; higher lanes hold higher digits
-    uint32_t mine[8], sum = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      mine[i] = hist[lane * 8 + i];
-      sum += mine[i];
-    }
-    uint32_t suf = sum;          // inclusive suffix over the lanes
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t u = __shfl_down_sync(0xffffffffu, suf, o);
-      if (lane + o < 32) suf += u;
-    }
-    const uint32_t total = __shfl_sync(0xffffffffu, suf, 0);
-    if (pass == 0 && total <= static_cast<uint32_t>(need)) {   // fewer valid keys than wanted: all of them win
+    find_threshold_bin(hist, need, s_res, s_seg);
+    const int d = s_res[0], above = s_res[1], in_bin = s_res[2];
+    __syncthreads();   // s_res is rewritten by the next level
+    if (d < 0) {       // fewer valid keys than wanted (level 0 only): all of them win
       take_all = true;
       break;
     }
-    const uint32_t above_lane = suf - sum;
-    const bool own = above_lane < static_cast<uint32_t>(need) && suf >= static_cast<uint32_t>(need);
-    int d = 0, above = 0, in_bin = 0;
-    if (own) {
-      uint32_t a = above_lane;
-#pragma unroll
-      for (int i = 7; i >= 0; --i) {
-        if (a < static_cast<uint32_t>(need) && a + mine[i] >= static_cast<uint32_t>(need)) {
-          d = lane * 8 + i;
-          above = static_cast<int>(a);
-          in_bin = static_cast<int>(mine[i]);
-        }
-        a += mine[i];
-      }
+    if (level < 3) {
+      tkey |= static_cast<uint32_t>(d) << (32 - kbits - width);
+      kbits += width;
+    } else {
+      tnpos |= static_cast<uint32_t>(d) << (32 - nbits - width);
+      nbits += width;
     }
-    const int who = max(0, __ffs(__ballot_sync(0xffffffffu, own)) - 1);
-    d = __shfl_sync(0xffffffffu, d, who);
-    above = __shfl_sync(0xffffffffu, above, who);
-    in_bin = __shfl_sync(0xffffffffu, in_bin, who);
-    prefix = (prefix << 8) | static_cast<uint64_t>(d);
-    pbits += 8;
     need -= above;
-    __syncwarp();
-    if (in_bin == need) break;      // every key with these leading bits, and everything above, wins
+    if (in_bin == need) break;   // everything with these leading bits wins
   }
 
-  // ---- emit in scan order
-  int cnt = 0;
-  const bool cmp_pos = !take_all && pbits > 32;
-  for (int base = begin; base < end; base += 128) {
-    float v[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int col = base + u * 32 + lane;
-      v[u] = col < end ? __ldg(src + col) : 0.f;
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int col = base + u * 32 + lane;
-      bool win = col < end && score_valid(v[u], p.keep_pos_inf);
-      int32_t pos = 0;
-      if (win && !take_all) {
-        const uint64_t hi = static_cast<uint64_t>(float_to_ordered(v[u])) << 32;
-        if (!cmp_pos) {
-          win = (hi >> (64 - pbits)) >= prefix;
-        } else {
-          const uint64_t top = prefix >> (pbits - 32);                 // the 32 score bits of the threshold
-          const uint64_t sc = hi >> 32;
-          if (sc != top) {
-            win = sc > top;
-          } else {
-            pos = out_position(p, row, col);
-            const uint64_t key = hi | static_cast<uint32_t>(~static_cast<uint32_t>(pos));
-            win = (key >> (64 - pbits)) >= prefix;
-          }
-        }
+  // ---- emit
+  auto wins = [&](uint32_t key, int i) -> bool {
+    if (key == 0u) return false;
+    if (take_all) return true;
+    if (kbits < 32) return (key >> (32 - kbits)) >= (tkey >> (32 - kbits));
+    if (key != tkey) return key > tkey;
+    if (nbits == 0) return true;
+    return (npos_of(i) >> (32 - nbits)) >= (tnpos >> (32 - nbits));
+  };
+  const int lane = tid & 31;
+  for (int base = 0; base < n; base += kRowsThreads) {
+    const int i = base + tid;
+    const uint32_t key = i < n ? keys[i] : 0u;
+    const bool win = i < n && wins(key, i);
+    const unsigned m = __ballot_sync(0xffffffffu, win);
+    if (m == 0) continue;
+    const int leader = __ffs(m) - 1;
+    int slot = 0;
+    if (lane == leader) slot = atomicAdd(&s_cnt, __popc(m));
+    slot = __shfl_sync(0xffffffffu, slot, leader) + __popc(m & ((1u << lane) - 1u));
+    if (win && slot < k) {
+      const int32_t pos = out_position(p, row, begin + i);
+      if (p.sorted) {
+        sel[slot] = (static_cast<uint64_t>(key) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(pos));
+      } else {
+        out_idx[slot] = pos;
+        if (out_val) out_val[slot] = ordered_to_float(key);
       }
-      const unsigned m = __ballot_sync(0xffffffffu, win);
-      if (win) {
-        const int slot = cnt + __popc(m & below);
-        if (slot < k) {
-          out_idx[slot] = out_position(p, row, col);
-          if (out_val) out_val[slot] = v[u];
-        }
-      }
-      cnt += __popc(m);
     }
   }
-  for (int j = min(cnt, k) + lane; j < k; j += 32) {
+  __syncthreads();
+  const int n_sel = min(s_cnt, k);
+  if (p.sorted) {
+    uint64_t* tmp = reinterpret_cast<uint64_t*>(keys);
+    if (n_sel > 1 && (n_sel <= 64 || !bucket_sort_desc(sel, n_sel, tmp, hist, s_seg))) {
+      int n_pow2 = 64;
+      while (n_pow2 < n_sel) n_pow2 <<= 1;
+      for (int i = n_sel + tid; i < n_pow2; i += kRowsThreads) sel[i] = 0;
+      __syncthreads();
+      sort_desc(sel, n_pow2);
+    }
+    for (int j = tid; j < n_sel; j += kRowsThreads) {
+      const uint64_t key = sel[j];
+      out_idx[j] = static_cast<int32_t>(~static_cast<uint32_t>(key & 0xffffffffu));
+      if (out_val) out_val[j] = ordered_to_float(static_cast<uint32_t>(key >> 32));
+    }
+  }
+  for (int j = n_sel + tid; j < k; j += kRowsThreads) {
     out_idx[j] = -1;
     if (out_val) out_val[j] = -INFINITY;
   }
-}
-
-// Orders rows of (position, score) pairs that a selection wrote unsorted: descending score, ascending position.
-__global__ void __launch_bounds__(512) topk_sort_rows_kernel(int32_t* __restrict__ idx, float* __restrict__ val,
-                                                            int64_t stride, int k, int k_pow2) {
-  extern __shared__ __align__(16) uint8_t smem_raw[];
-  uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw);
-  uint64_t* a = reinterpret_cast<uint64_t*>(smem_raw + kHistBins * sizeof(uint32_t));
-  uint64_t* tmp = a + k_pow2;
-  __shared__ uint32_t s_seg[32];
-  __shared__ int s_n;
-  int32_t* ri = idx + blockIdx.x * stride;
-  float* rv = val + blockIdx.x * stride;
-  if (threadIdx.x == 0) s_n = 0;
-  __syncthreads();
-  // the selection wrote its winners first and the padding behind them
-  int mine = 0;
-  for (int j = threadIdx.x; j < k; j += blockDim.x) {
-    const int32_t pos = ri[j];
-    if (pos >= 0) {
-      a[j] = make_composite(rv[j], pos);
-      ++mine;
-    }
-  }
-  if (mine) atomicAdd(&s_n, mine);
-  __syncthreads();
-  const int n = s_n;
-  if (n <= 1) return;
-  if (n <= 64 || !bucket_sort_desc(a, n, tmp, hist, s_seg)) {
-    int n_pow2 = 32;
-    while (n_pow2 < n) n_pow2 <<= 1;
-    for (int i = n + threadIdx.x; i < n_pow2; i += blockDim.x) a[i] = 0;
-    sort_desc(a, n_pow2);
-  }
-  for (int j = threadIdx.x; j < n; j += blockDim.x) {
-    const uint64_t key = a[j];
-    ri[j] = static_cast<int32_t>(~static_cast<uint32_t>(key & 0xffffffffu));
-    rv[j] = ordered_to_float(static_cast<uint32_t>(key >> 32));
-  }
+  (void)k_pow2;
 }
 
 void set_last_error(const char* msg);
@@ -1142,27 +1108,20 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
   }
   int k_pow2 = 32;
   while (k_pow2 < k) k_pow2 <<= 1;
-  // many short rows: one warp per row.  A warp needs about 19 us per 1024 columns of its row, so this pays once
-  // there are enough rows to hide that (4096 rows: 1024 columns 41 against 76 us, 4096 columns 138 against 199 us;
-  // 1024 rows of 4096 columns 79 against 55 us, rows of 8192 columns never).  An ordered result of a few winners
-  // is sorted by a second pass (which needs the scores next to the positions); an ordered result of thousands
-  // stays with the kernel below, whose sort runs on the winners while they are still in shared memory.
-  if (n_rows >= 1024 && n_cols <= 4096 && n_rows >= n_cols && k <= 4096 && seg_cols == 0 &&
-      (!sorted || (k <= 256 && out_val != nullptr))) {
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    cudaError_t e2 = launch_chained(topk_warp_select_kernel, dim3((n_rows + kWselWarps - 1) / kWselWarps),
-                                    dim3(kWselWarps * 32), 0, st, p);
-    if (e2 == cudaSuccess && sorted && k > 1) {
-      const size_t smem_sort = kHistBins * sizeof(uint32_t) + 2 * static_cast<size_t>(k_pow2) * sizeof(uint64_t);
-      e2 = cudaFuncSetAttribute(topk_sort_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                static_cast<int>(smem_sort));
-      if (e2 == cudaSuccess)
-        e2 = launch_chained(topk_sort_rows_kernel, dim3(n_rows), dim3(k_pow2 >= 1024 ? 512 : 256), smem_sort, st, out_idx, out_val,
-                            out_stride, static_cast<int>(k), k_pow2);
-    }
-    if (e2 == cudaSuccess) e2 = cudaGetLastError();
-    if (e2 != cudaSuccess) {
-      set_last_error(cudaGetErrorString(e2));
+  // many rows that fit shared memory: a small CTA per row, several per SM
+  if (n_rows >= kRowsMinRows && n_cols <= kRowsMaxCols && k <= 4096 && seg_cols == 0) {
+    const int sel_entries = sorted ? max(k_pow2, 64) : 0;
+    const int key_words = max((n_cols + 3) & ~3, 2 * sel_entries);
+    const size_t smem_rows = kHistBins * sizeof(uint32_t) + static_cast<size_t>(key_words) * 4 +
+                             static_cast<size_t>(sel_entries) * 8;
+    cudaError_t e3 = cudaFuncSetAttribute(topk_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          kHistBins * 4 + kRowsMaxCols * 4 + 4096 * 8);
+    if (e3 == cudaSuccess)
+      e3 = launch_chained(topk_rows_kernel, dim3(n_rows), dim3(kRowsThreads), smem_rows,
+                          static_cast<cudaStream_t>(stream), p, key_words, k_pow2);
+    if (e3 == cudaSuccess) e3 = cudaGetLastError();
+    if (e3 != cudaSuccess) {
+      set_last_error(cudaGetErrorString(e3));
       return B200DSA_ECUDA;
     }
     return B200DSA_OK;

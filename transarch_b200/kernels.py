@@ -51,10 +51,6 @@ def topk_select(scores: torch.Tensor, k: int, *, col_begin: Optional[torch.Tenso
         vals = torch.empty(n_rows, out.stride(0), dtype=torch.float32, device=scores.device)
     if vals is not None and (vals.dtype != torch.float32 or vals.stride(0) != out.stride(0)):
         raise _lib.B200DSAError("out_values must be fp32 with the row stride of out")
-    if vals is None and sorted and n_rows >= 1024 and n_rows >= n_cols and n_cols <= 4096 and k <= 256 and seg_cols == 0:
-        # many short rows with few winners are selected by one warp each and ordered by a second pass, which
-        # reads the scores of the winners next to their positions
-        vals = torch.empty(n_rows, out.stride(0), dtype=torch.float32, device=scores.device)
     seg_arr = (ctypes.c_int64 * len(seg_offsets))(*seg_offsets) if seg_offsets is not None else None
     lib = _lib.load()
     rc = lib.b200dsa_topk_select(
