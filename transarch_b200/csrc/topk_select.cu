@@ -495,14 +495,19 @@ struct SelectResult {
   uint64_t full;     // decided leading bits of the threshold composite
   int full_bits;
   int need_eq;       // winners still to be taken from the keys whose leading bits equal `full`
+  bool eq_all_win;   // exactly need_eq keys have those leading bits: they all win, nothing is left to order
 };
 
 // Most-significant-digit radix select.  for_each(need_pos, f) must call f(key, active) the same
 // number of times on every thread of a warp; keys are 64-bit composites (position bits may be
 // zero while need_pos is false).
+// to_the_end: keep refining until the threshold bin holds exactly the keys still wanted (cheap passes over keys
+// in shared memory: two or three levels for distinct scores) instead of stopping at a bin of up to kEqCap keys
+// that the caller then has to sort.
 template <class ForEach>
-__device__ SelectResult radix_select(ForEach&& for_each, int need, uint32_t* hist, int* s_res, uint32_t* s_seg) {
-  SelectResult r{false, 0, 0, 0};
+__device__ SelectResult radix_select(ForEach&& for_each, int need, uint32_t* hist, int* s_res, uint32_t* s_seg,
+                                     bool to_the_end = false) {
+  SelectResult r{false, 0, 0, 0, false};
   uint64_t prefix = 0;
   int prefix_bits = 0;
   for (int level = 0; level < 6; ++level) {
@@ -528,7 +533,8 @@ __device__ SelectResult radix_select(ForEach&& for_each, int need, uint32_t* his
     r.full = (prefix << digit_bits) | static_cast<uint64_t>(d);
     r.full_bits = prefix_bits + digit_bits;
     r.need_eq = need - above;
-    if (in_bin <= kEqCap || level == 5) return r;
+    r.eq_all_win = in_bin == r.need_eq;
+    if (r.eq_all_win || level == 5 || (!to_the_end && in_bin <= kEqCap)) return r;
     prefix = r.full;
     prefix_bits = r.full_bits;
     need = r.need_eq;
@@ -750,8 +756,8 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
           direct = true;
         } else {
           const uint64_t top = key >> (64 - r.full_bits);
-          direct = top > r.full;
-          tie = top == r.full;
+          direct = top > r.full || (r.eq_all_win && top == r.full);
+          tie = !r.eq_all_win && top == r.full;
         }
       }
       list_append(sel, &s_sel_cnt, k_pow2, key, direct);
@@ -762,9 +768,9 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   SelectResult r;
   if (from_smem) {
     if (cnt <= k) {
-      r = SelectResult{true, 0, 0, 0};
+      r = SelectResult{true, 0, 0, 0, false};
     } else {
-      r = radix_select(each_cand, k, hist, s_res, s_seg);
+      r = radix_select(each_cand, k, hist, s_res, s_seg, /*to_the_end=*/true);
     }
     each_cand(true, emit(r));
   } else {
@@ -773,7 +779,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   }
   __syncthreads();
   int n_sel = min(s_sel_cnt, k_pow2);
-  if (!r.take_all) {
+  if (!r.take_all && !r.eq_all_win) {
     const int n_eq = min(s_eq_cnt, kEqCap);
     int n_eq_pow2 = 32;
     while (n_eq_pow2 < n_eq) n_eq_pow2 <<= 1;
