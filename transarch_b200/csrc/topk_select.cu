@@ -130,6 +130,22 @@ __device__ __forceinline__ void list_append(uint64_t* list, int* counter, int ca
   }
 }
 
+// Totals of the warps of a block (at most 32, in shared memory) -> sum of the totals of the warps before `warp`,
+// and the sum of all of them.  One load and a shuffle scan per thread instead of a dependent chain of up to 32
+// shared-memory loads.
+template <class T>
+__device__ __forceinline__ void warp_totals_scan(const T* totals, int nwarps, int warp, int& before, int& total) {
+  const int lane = threadIdx.x & 31;
+  const int mine = lane < nwarps ? static_cast<int>(totals[lane]) : 0;
+  int incl = mine;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  before = __shfl_sync(0xffffffffu, incl - mine, warp);
+  total = __shfl_sync(0xffffffffu, incl, 31);
+}
+
 // Stream row elements [begin, begin+n) through f(value, column, in_range) with many loads in
 // flight per thread.  Every thread calls f the same number of times (f may use warp votes).
 // The 16-byte path needs src 16-byte aligned.
@@ -335,8 +351,10 @@ __device__ bool bucket_sort_desc(uint64_t* a, int n, uint64_t* tmp, uint32_t* hi
   if (lane == 0 && big > static_cast<uint32_t>(kBucketMax)) atomicMax(&s_big, big);
   __syncthreads();
   if (s_big != 0u) return false;   // uniform: every thread reads the same word
-  uint32_t before = incl - sum;
-  for (int w = 0; w < warp; ++w) before += s_seg[w];
+  int before_w, total_w;
+  warp_totals_scan(s_seg, nwarps, warp, before_w, total_w);
+  (void)total_w;
+  uint32_t before = incl - sum + static_cast<uint32_t>(before_w);
   // hist[b] <- first output slot of bucket b
   for (int j = 0; j < per; ++j) {
     const uint32_t c = hist[top - j];
@@ -425,6 +443,63 @@ __device__ void find_threshold_bin(const uint32_t* hist, int need, int* res, uin
   __syncthreads();
 }
 
+// find_threshold_bin with one barrier: every warp repeats the search over the 32 segment sums and the
+// owning segment itself, so the answer sits in registers of every thread and nothing goes through shared memory
+// a second time.  d = -1 when the histogram holds fewer than `need`.
+__device__ __forceinline__ void find_threshold_bin_bcast(const uint32_t* hist, int need, uint32_t* seg_sum, int& d,
+                                                         int& above, int& in_bin) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int sgm = warp; sgm < 32; sgm += nwarps) {
+    const uint4 v = reinterpret_cast<const uint4*>(hist + kHistBins - 128 * (sgm + 1))[lane];
+    uint32_t t = v.x + v.y + v.z + v.w;
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) seg_sum[sgm] = t;
+  }
+  __syncthreads();
+  const uint32_t mine = seg_sum[lane];
+  uint32_t incl = mine;
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  const bool owner = (incl - mine < static_cast<uint32_t>(need)) && (incl >= static_cast<uint32_t>(need));
+  const unsigned who = __ballot_sync(0xffffffffu, owner);
+  d = -1;
+  above = 0;
+  in_bin = 0;
+  if (who == 0) return;
+  const int sgm = __ffs(who) - 1;
+  const uint32_t above_seg = __shfl_sync(0xffffffffu, incl - mine, sgm);
+  const int base = kHistBins - 128 * (sgm + 1);
+  const uint4 v = reinterpret_cast<const uint4*>(hist + base)[lane];   // lane l: bins base+4l .. base+4l+3
+  const uint32_t t = v.x + v.y + v.z + v.w;
+  uint32_t suf = t;  // inclusive suffix over lanes (lane 31 first)
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t u = __shfl_down_sync(0xffffffffu, suf, o);
+    if (lane + o < 32) suf += u;
+  }
+  const uint32_t above_lane = above_seg + suf - t;
+  const bool own = (above_lane < static_cast<uint32_t>(need)) && (above_lane + t >= static_cast<uint32_t>(need));
+  int dd = 0, aa = 0, ib = 0;
+  if (own) {
+    uint32_t a = above_lane;
+    const uint32_t h[4] = {v.w, v.z, v.y, v.x};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (a < static_cast<uint32_t>(need) && a + h[j] >= static_cast<uint32_t>(need)) {
+        dd = base + 4 * lane + 3 - j;
+        aa = static_cast<int>(a);
+        ib = static_cast<int>(h[j]);
+      }
+      a += h[j];
+    }
+  }
+  const int src = __ffs(__ballot_sync(0xffffffffu, own)) - 1;
+  d = __shfl_sync(0xffffffffu, dd, src);
+  above = __shfl_sync(0xffffffffu, aa, src);
+  in_bin = __shfl_sync(0xffffffffu, ib, src);
+}
+
 // Sample the row into the 4096-bin histogram and choose the bin floor: with a 6-sigma margin at
 // least k elements of the row lie at or above it.  Returns false when the fast path does not
 // apply (margin too wide for the candidate list, or a sample with too few valid scores).  All
@@ -504,14 +579,18 @@ struct SelectResult {
 // to_the_end: keep refining until the threshold bin holds exactly the keys still wanted (cheap passes over keys
 // in shared memory: two or three levels for distinct scores) instead of stopping at a bin of up to kEqCap keys
 // that the caller then has to sort.
+// In that mode the caller may pass the leading bits that all keys share (lead_bits of them, value `lead`): the
+// first digit then starts right below them and spreads the keys over the whole histogram (candidates above a
+// floor share sign, exponent and often more: the top 12 bits alone put them into a handful of bins, on which the
+// shared-memory atomics serialise).
 template <class ForEach>
 __device__ SelectResult radix_select(ForEach&& for_each, int need, uint32_t* hist, int* s_res, uint32_t* s_seg,
-                                     bool to_the_end = false) {
+                                     bool to_the_end = false, uint64_t lead = 0, int lead_bits = 0) {
   SelectResult r{false, 0, 0, 0, false};
-  uint64_t prefix = 0;
-  int prefix_bits = 0;
+  uint64_t prefix = lead;
+  int prefix_bits = lead_bits;
   for (int level = 0; level < 6; ++level) {
-    const int digit_bits = (level % 3 == 2) ? 8 : 12;
+    const int digit_bits = to_the_end ? min(12, 64 - prefix_bits) : ((level % 3 == 2) ? 8 : 12);
     const int shift = 64 - prefix_bits - digit_bits;
     const bool need_pos = (prefix_bits + digit_bits) > 32;
     for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) hist[i] = 0;
@@ -534,7 +613,7 @@ __device__ SelectResult radix_select(ForEach&& for_each, int need, uint32_t* his
     r.full_bits = prefix_bits + digit_bits;
     r.need_eq = need - above;
     r.eq_all_win = in_bin == r.need_eq;
-    if (r.eq_all_win || level == 5 || (!to_the_end && in_bin <= kEqCap)) return r;
+    if (r.eq_all_win || level == 5 || r.full_bits == 64 || (!to_the_end && in_bin <= kEqCap)) return r;
     prefix = r.full;
     prefix_bits = r.full_bits;
     need = r.need_eq;
@@ -551,6 +630,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   uint64_t* eq = cand + cand_cap;   // cand_cap <= kCandCap: rows that fit entirely get a smaller list
   uint64_t* sel = eq + kEqCap;  // k_pow2 entries
   __shared__ int s_eq_cnt, s_sel_cnt, s_res[3], s_warp_cnt[32], s_overflow, s_own_cnt, s_last;
+  __shared__ uint32_t s_kmin, s_kmax;   // range of the score keys of the candidates in shared memory
   __shared__ uint32_t s_seg[32];
 
   const int row = blockIdx.x;
@@ -577,6 +657,9 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     s_eq_cnt = 0;
     s_sel_cnt = 0;
     s_own_cnt = 0;
+    s_res[0] = 0;
+    s_kmin = 0xffffffffu;
+    s_kmax = 0u;
   }
   if (p.wait_on) {
     // the rows of this launch were pushed by the peers' selections: wait for every rank's flag
@@ -650,8 +733,129 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   bool have_pre = false;
   if (p.pre_cand) {
     // split / fused mode: the candidates of this row were collected by an earlier kernel
+    // the first eight entries per thread of the row's list are fetched before its length is known (the slots
+    // exist whatever the length; what lies beyond it is dropped below): one memory round trip instead of two
+    constexpr int kFastPer = 8;
+    uint64_t t[kFastPer];
+    {
+      const uint64_t* g = p.pre_cand + static_cast<int64_t>(row) * cand_cap;
+#pragma unroll
+      for (int j = 0; j < kFastPer; ++j) t[j] = (tid + j * nthr < cand_cap) ? g[tid + j * nthr] : 0ull;
+    }
     const int c = p.pre_count[row];
     const uint32_t fl = p.pre_floor ? p.pre_floor[row] : 0u;
+    // ---- fast path: a list of at most eight candidates per thread stays in registers.  The score keys are
+    // taken relative to the smallest one, so that the first digit starts at the highest bit in which the
+    // candidates differ and spreads them over the whole histogram (above a floor they share sign, exponent
+    // and more, and the top key bits alone would put them into a handful of bins); two histograms alternate,
+    // so a level costs two barriers; winners are placed by a scan of per-thread counts.
+    if (c > k && c <= kFastPer * nthr && c <= cand_cap) {
+      uint32_t* hist2 = reinterpret_cast<uint32_t*>(cand);   // the candidate area is not used on this path
+      for (int i = tid; i < kHistBins; i += nthr) {
+        hist[i] = 0;
+        hist2[i] = 0;
+      }
+#pragma unroll
+      for (int j = 0; j < kFastPer; ++j) {
+        if (tid + j * nthr >= c) t[j] = 0ull;
+      }
+      int n_ge = 0;
+      uint32_t lo = 0xffffffffu, hi = 0u;
+#pragma unroll
+      for (int j = 0; j < kFastPer; ++j) {
+        if (tid + j * nthr < c) {
+          const uint32_t sk = static_cast<uint32_t>(t[j] >> 32);
+          n_ge += sk >= fl;
+          lo = min(lo, sk);
+          hi = max(hi, sk);
+        }
+      }
+      for (int o = 16; o > 0; o >>= 1) {
+        n_ge += __shfl_xor_sync(0xffffffffu, n_ge, o);
+        lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+        hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+      }
+      if (lane_id == 0 && lo <= hi) {
+        atomicAdd(&s_res[0], n_ge);
+        atomicMin(&s_kmin, lo);
+        atomicMax(&s_kmax, hi);
+      }
+      __syncthreads();
+      const bool fast_ok = !p.pre_floor || s_res[0] >= k || fl == 0x00800000u;
+      if (fast_ok) {
+        if (tid == 0) {          // re-arm for the next call (every thread has read the count by now)
+          p.pre_count[row] = 0;
+          if (p.pre_floor) p.pre_floor[row] = 0u;
+        }
+        const uint32_t kmin = s_kmin, kmax = s_kmax;
+        const int score_bits = kmax > kmin ? 32 - __clz(kmax - kmin) : 0;
+        const int width = score_bits + 32;
+        const uint64_t sub = static_cast<uint64_t>(kmin) << 32;
+#pragma unroll
+        for (int j = 0; j < kFastPer; ++j) t[j] -= sub;   // absent entries are never looked at
+        uint64_t prefix = 0;
+        int pbits = 0, need = k;
+        uint32_t* cur = hist;
+        uint32_t* other = hist2;
+#pragma unroll 1
+        for (int level = 0; level < 6; ++level) {
+          const int dbits = min(12, width - pbits);
+          const int shift = width - pbits - dbits;
+          const uint32_t mask = (1u << dbits) - 1u;
+#pragma unroll
+          for (int j = 0; j < kFastPer; ++j) {
+            if (tid + j * nthr < c && (pbits == 0 || (t[j] >> (width - pbits)) == prefix))
+              atomicAdd(&cur[static_cast<uint32_t>(t[j] >> shift) & mask], 1u);
+          }
+          __syncthreads();
+          if (level > 0) {   // the histogram of the previous level has been read by every warp: clear it for the next
+            for (int i = tid; i < kHistBins; i += nthr) other[i] = 0;
+          }
+          int d, above, in_bin;
+          find_threshold_bin_bcast(cur, need, s_seg, d, above, in_bin);
+          if (d < 0) break;      // cannot happen: more candidates than wanted share the prefix
+          prefix = (prefix << dbits) | static_cast<uint64_t>(d);
+          pbits += dbits;
+          need -= above;
+          if (in_bin == need || pbits == width) break;
+          uint32_t* sw = cur;
+          cur = other;
+          other = sw;
+        }
+        // winners: everything at or above the decided prefix
+        auto wins = [&](uint64_t x) { return pbits == 0 || (x >> (width - pbits)) >= prefix; };
+        int mine = 0;
+#pragma unroll
+        for (int j = 0; j < kFastPer; ++j) mine += (tid + j * nthr < c && wins(t[j])) ? 1 : 0;
+        int incl = mine;
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane_id >= o) incl += v;
+        }
+        if (lane_id == 31) s_warp_cnt[warp_id] = incl;
+        __syncthreads();
+        int before, total;
+        warp_totals_scan(s_warp_cnt, n_warps, warp_id, before, total);
+        before += incl - mine;
+#pragma unroll
+        for (int j = 0; j < kFastPer; ++j) {
+          if (tid + j * nthr < c && wins(t[j])) {
+            if (before < k_pow2) sel[before] = t[j] + sub;
+            ++before;
+          }
+        }
+        __syncthreads();
+        const int n_fast = min(total, k);
+        if (p.sorted && (n_fast <= 64 || !bucket_sort_desc(sel, n_fast, cand, hist, s_seg))) {
+          int n_pow2 = 32;
+          while (n_pow2 < n_fast) n_pow2 <<= 1;
+          for (int i = n_fast + tid; i < n_pow2; i += nthr) sel[i] = 0;
+          sort_desc(sel, n_pow2);
+        }
+        write_row(sel, n_fast);
+        return;
+      }
+    }
     __syncthreads();
     if (tid == 0) {          // re-arm for the next call
       p.pre_count[row] = 0;
@@ -662,10 +866,22 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     if (usable) {
       const uint64_t* g = p.pre_cand + static_cast<int64_t>(row) * cand_cap;
       int n_ge = 0;
+      uint32_t lo = 0xffffffffu, hi = 0u;
       for (int i = tid; i < c; i += nthr) {
         const uint64_t e = g[i];
         cand[i] = e;
-        n_ge += static_cast<uint32_t>(e >> 32) >= fl;
+        const uint32_t sk = static_cast<uint32_t>(e >> 32);
+        n_ge += sk >= fl;
+        lo = min(lo, sk);
+        hi = max(hi, sk);
+      }
+      for (int o = 16; o > 0; o >>= 1) {
+        lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+        hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+      }
+      if (lane_id == 0 && lo <= hi) {
+        atomicMin(&s_kmin, lo);
+        atomicMax(&s_kmax, hi);
       }
       if (p.pre_floor) {
         // the list is complete at and above the floor; a floor of -FLT_MAX means the whole row is in it
@@ -703,21 +919,37 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
   // only (no atomics); a full segment raises the overflow flag and the row falls back.
   if (try_fast) {
     int wcnt = 0;  // warp-uniform
+    uint32_t lo = 0xffffffffu, hi = 0u;
     stream_row(src, begin, n, vec_ok, coff, [&](float v, int col, bool in_range) {
-      const bool take = in_range && score_valid(v, p.keep_pos_inf) && (float_to_ordered(v) >> 20) >= bin_floor;
+      const uint32_t sk = float_to_ordered(v);
+      const bool take = in_range && score_valid(v, p.keep_pos_inf) && (sk >> 20) >= bin_floor;
       const unsigned act = __ballot_sync(0xffffffffu, take);
       if (take) {
         const int slot = wcnt + __popc(act & ((1u << lane_id) - 1));
         if (slot < seg_cap) my_seg[slot] = make_composite(v, out_position(p, row, col));
+        lo = min(lo, sk);
+        hi = max(hi, sk);
       }
       wcnt += __popc(act);
     });
+    for (int o = 16; o > 0; o >>= 1) {
+      lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+      hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    }
     if (lane_id == 0) {
       s_warp_cnt[warp_id] = min(wcnt, seg_cap);
       if (wcnt > seg_cap) s_overflow = 1;
+      if (lo <= hi) {
+        atomicMin(&s_kmin, lo);
+        atomicMax(&s_kmax, hi);
+      }
     }
     __syncthreads();
-    for (int w = 0; w < n_warps; ++w) cnt += s_warp_cnt[w];
+    {
+      int before_unused, total;
+      warp_totals_scan(s_warp_cnt, n_warps, warp_id, before_unused, total);
+      cnt += total;
+    }
     from_smem = (s_overflow == 0) && (cnt >= k || n <= cand_cap);
   }
 
@@ -770,9 +1002,42 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     if (cnt <= k) {
       r = SelectResult{true, 0, 0, 0, false};
     } else {
-      r = radix_select(each_cand, k, hist, s_res, s_seg, /*to_the_end=*/true);
+      // leading bits that every candidate's score key shares
+      const uint32_t kmin = s_kmin, kmax = s_kmax;
+      const int lead_bits = kmin > kmax ? 0 : ((kmin ^ kmax) ? __clz(kmin ^ kmax) : 32);
+      const uint64_t lead = lead_bits ? static_cast<uint64_t>(kmax >> (32 - lead_bits)) : 0ull;
+      r = radix_select(each_cand, k, hist, s_res, s_seg, /*to_the_end=*/true, lead, lead_bits);
     }
-    each_cand(true, emit(r));
+    if (have_pre && (r.take_all || r.eq_all_win)) {
+      // contiguous list, exact threshold: count this thread's winners, scan the counts over the block, place
+      // them (one pass of votes and an atomic per warp and 32 candidates costs more than both passes here)
+      auto wins = [&](uint64_t key) {
+        if (r.take_all) return true;
+        return (key >> (64 - r.full_bits)) >= r.full;
+      };
+      int mine = 0;
+      for (int i = tid; i < cnt; i += nthr) mine += wins(cand[i]) ? 1 : 0;
+      int incl = mine;
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane_id >= o) incl += v;
+      }
+      if (lane_id == 31) s_seg[warp_id] = static_cast<uint32_t>(incl);
+      __syncthreads();
+      int before, total;
+      warp_totals_scan(s_seg, n_warps, warp_id, before, total);
+      before += incl - mine;
+      if (tid == 0) s_sel_cnt = total;
+      for (int i = tid; i < cnt; i += nthr) {
+        const uint64_t key = cand[i];
+        if (wins(key)) {
+          if (before < k_pow2) sel[before] = key;
+          ++before;
+        }
+      }
+    } else {
+      each_cand(true, emit(r));
+    }
   } else {
     r = radix_select(each_row, k, hist, s_res, s_seg);
     each_row(true, emit(r));
