@@ -724,8 +724,93 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     return;
   }
 
-  // ------------------------------------------------------------------ candidate collection
+  // ---- selection from at most eight candidates per thread held in registers (composites; bit j of `pres` says
+  // that t[j] holds one; n_present of them in the block; s_kmin / s_kmax hold the range of their score keys and
+  // both histograms are clear).  The score keys are taken relative to the smallest one, so that the first digit
+  // starts at the highest bit in which the candidates differ and spreads them over the whole histogram (above a
+  // floor they share sign, exponent and more: the top key bits alone would put them into a handful of bins, on
+  // which the shared-memory atomics serialise); two histograms alternate, so a level costs two barriers; the
+  // winners are placed by a scan of per-thread counts.  Writes the row's result.
+  constexpr int kFastPer = 8;
   const int warp_id = tid >> 5, lane_id = tid & 31, n_warps = nthr >> 5;
+  uint32_t* hist2 = reinterpret_cast<uint32_t*>(cand);   // the candidate area is not used on these paths
+  auto pres_of_count = [&](int c) {
+    uint32_t m = 0;
+#pragma unroll
+    for (int j = 0; j < kFastPer; ++j) m |= (tid + j * nthr < c) ? (1u << j) : 0u;
+    return m;
+  };
+  auto select_from_registers = [&](uint64_t (&t)[kFastPer], uint32_t pres, int n_present) {
+    const uint32_t kmin = s_kmin, kmax = s_kmax;
+    const int score_bits = kmax > kmin ? 32 - __clz(kmax - kmin) : 0;
+    const int width = score_bits + 32;
+    const uint64_t sub = static_cast<uint64_t>(kmin) << 32;
+#pragma unroll
+    for (int j = 0; j < kFastPer; ++j) t[j] -= sub;   // absent entries are never looked at
+    uint64_t prefix = 0;
+    int pbits = 0, need = k;
+    const int max_levels = n_present > k ? 6 : 0;   // no more candidates than wanted: all of them win
+    uint32_t* cur = hist;
+    uint32_t* other = hist2;
+#pragma unroll 1
+    for (int level = 0; level < max_levels; ++level) {
+      const int dbits = min(12, width - pbits);
+      const int shift = width - pbits - dbits;
+      const uint32_t mask = (1u << dbits) - 1u;
+#pragma unroll
+      for (int j = 0; j < kFastPer; ++j) {
+        if (((pres >> j) & 1u) && (pbits == 0 || (t[j] >> (width - pbits)) == prefix))
+          atomicAdd(&cur[static_cast<uint32_t>(t[j] >> shift) & mask], 1u);
+      }
+      __syncthreads();
+      if (level > 0) {   // the histogram of the previous level has been read by every warp: clear it for the next
+        for (int i = tid; i < kHistBins; i += nthr) other[i] = 0;
+      }
+      int d, above, in_bin;
+      find_threshold_bin_bcast(cur, need, s_seg, d, above, in_bin);
+      if (d < 0) break;      // cannot happen: more candidates than wanted share the prefix
+      prefix = (prefix << dbits) | static_cast<uint64_t>(d);
+      pbits += dbits;
+      need -= above;
+      if (in_bin == need || pbits == width) break;
+      uint32_t* sw = cur;
+      cur = other;
+      other = sw;
+    }
+    // winners: everything at or above the decided prefix
+    auto wins = [&](uint64_t x) { return pbits == 0 || (x >> (width - pbits)) >= prefix; };
+    int mine = 0;
+#pragma unroll
+    for (int j = 0; j < kFastPer; ++j) mine += (((pres >> j) & 1u) && wins(t[j])) ? 1 : 0;
+    int incl = mine;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane_id >= o) incl += v;
+    }
+    if (lane_id == 31) s_warp_cnt[warp_id] = incl;
+    __syncthreads();
+    int before, total;
+    warp_totals_scan(s_warp_cnt, n_warps, warp_id, before, total);
+    before += incl - mine;
+#pragma unroll
+    for (int j = 0; j < kFastPer; ++j) {
+      if (((pres >> j) & 1u) && wins(t[j])) {
+        if (before < k_pow2) sel[before] = t[j] + sub;
+        ++before;
+      }
+    }
+    __syncthreads();
+    const int n_fast = min(total, k);
+    if (p.sorted && (n_fast <= 64 || !bucket_sort_desc(sel, n_fast, cand, hist, s_seg))) {
+      int n_pow2 = 32;
+      while (n_pow2 < n_fast) n_pow2 <<= 1;
+      for (int i = n_fast + tid; i < n_pow2; i += nthr) sel[i] = 0;
+      sort_desc(sel, n_pow2);
+    }
+    write_row(sel, n_fast);
+  };
+
+  // ------------------------------------------------------------------ candidate collection
   const int seg_cap = cand_cap / n_warps;
   uint64_t* my_seg = cand + warp_id * seg_cap;
   bool from_smem = false;
@@ -735,7 +820,6 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     // split / fused mode: the candidates of this row were collected by an earlier kernel
     // the first eight entries per thread of the row's list are fetched before its length is known (the slots
     // exist whatever the length; what lies beyond it is dropped below): one memory round trip instead of two
-    constexpr int kFastPer = 8;
     uint64_t t[kFastPer];
     {
       const uint64_t* g = p.pre_cand + static_cast<int64_t>(row) * cand_cap;
@@ -750,7 +834,6 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     // and more, and the top key bits alone would put them into a handful of bins); two histograms alternate,
     // so a level costs two barriers; winners are placed by a scan of per-thread counts.
     if (c > k && c <= kFastPer * nthr && c <= cand_cap) {
-      uint32_t* hist2 = reinterpret_cast<uint32_t*>(cand);   // the candidate area is not used on this path
       for (int i = tid; i < kHistBins; i += nthr) {
         hist[i] = 0;
         hist2[i] = 0;
@@ -787,72 +870,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
           p.pre_count[row] = 0;
           if (p.pre_floor) p.pre_floor[row] = 0u;
         }
-        const uint32_t kmin = s_kmin, kmax = s_kmax;
-        const int score_bits = kmax > kmin ? 32 - __clz(kmax - kmin) : 0;
-        const int width = score_bits + 32;
-        const uint64_t sub = static_cast<uint64_t>(kmin) << 32;
-#pragma unroll
-        for (int j = 0; j < kFastPer; ++j) t[j] -= sub;   // absent entries are never looked at
-        uint64_t prefix = 0;
-        int pbits = 0, need = k;
-        uint32_t* cur = hist;
-        uint32_t* other = hist2;
-#pragma unroll 1
-        for (int level = 0; level < 6; ++level) {
-          const int dbits = min(12, width - pbits);
-          const int shift = width - pbits - dbits;
-          const uint32_t mask = (1u << dbits) - 1u;
-#pragma unroll
-          for (int j = 0; j < kFastPer; ++j) {
-            if (tid + j * nthr < c && (pbits == 0 || (t[j] >> (width - pbits)) == prefix))
-              atomicAdd(&cur[static_cast<uint32_t>(t[j] >> shift) & mask], 1u);
-          }
-          __syncthreads();
-          if (level > 0) {   // the histogram of the previous level has been read by every warp: clear it for the next
-            for (int i = tid; i < kHistBins; i += nthr) other[i] = 0;
-          }
-          int d, above, in_bin;
-          find_threshold_bin_bcast(cur, need, s_seg, d, above, in_bin);
-          if (d < 0) break;      // cannot happen: more candidates than wanted share the prefix
-          prefix = (prefix << dbits) | static_cast<uint64_t>(d);
-          pbits += dbits;
-          need -= above;
-          if (in_bin == need || pbits == width) break;
-          uint32_t* sw = cur;
-          cur = other;
-          other = sw;
-        }
-        // winners: everything at or above the decided prefix
-        auto wins = [&](uint64_t x) { return pbits == 0 || (x >> (width - pbits)) >= prefix; };
-        int mine = 0;
-#pragma unroll
-        for (int j = 0; j < kFastPer; ++j) mine += (tid + j * nthr < c && wins(t[j])) ? 1 : 0;
-        int incl = mine;
-        for (int o = 1; o < 32; o <<= 1) {
-          const int v = __shfl_up_sync(0xffffffffu, incl, o);
-          if (lane_id >= o) incl += v;
-        }
-        if (lane_id == 31) s_warp_cnt[warp_id] = incl;
-        __syncthreads();
-        int before, total;
-        warp_totals_scan(s_warp_cnt, n_warps, warp_id, before, total);
-        before += incl - mine;
-#pragma unroll
-        for (int j = 0; j < kFastPer; ++j) {
-          if (tid + j * nthr < c && wins(t[j])) {
-            if (before < k_pow2) sel[before] = t[j] + sub;
-            ++before;
-          }
-        }
-        __syncthreads();
-        const int n_fast = min(total, k);
-        if (p.sorted && (n_fast <= 64 || !bucket_sort_desc(sel, n_fast, cand, hist, s_seg))) {
-          int n_pow2 = 32;
-          while (n_pow2 < n_fast) n_pow2 <<= 1;
-          for (int i = n_fast + tid; i < n_pow2; i += nthr) sel[i] = 0;
-          sort_desc(sel, n_pow2);
-        }
-        write_row(sel, n_fast);
+        select_from_registers(t, c <= 0 ? 0u : pres_of_count(c), c);
         return;
       }
     }
@@ -909,6 +927,48 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
       from_smem = true;
       cnt = c;
     }
+  }
+  if (!p.pre_cand && n <= kFastPer * nthr && cand_cap >= 2048) {
+    // short rows, and the merge of the ranks' candidates: straight from global memory into registers
+    for (int i = tid; i < kHistBins; i += nthr) {
+      hist[i] = 0;
+      hist2[i] = 0;
+    }
+    float v[kFastPer];
+#pragma unroll
+    for (int j = 0; j < kFastPer; ++j) {
+      const int i = tid + j * nthr;
+      v[j] = i < n ? __ldg(src + coff(begin + i)) : 0.f;
+    }
+    uint64_t t[kFastPer];
+    uint32_t pres = 0, lo = 0xffffffffu, hi = 0u;
+    int n_pres = 0;
+#pragma unroll
+    for (int j = 0; j < kFastPer; ++j) {
+      const int i = tid + j * nthr;
+      t[j] = 0ull;
+      if (i < n && score_valid(v[j], p.keep_pos_inf)) {
+        t[j] = make_composite(v[j], out_position(p, row, begin + i));
+        pres |= 1u << j;
+        const uint32_t sk = static_cast<uint32_t>(t[j] >> 32);
+        lo = min(lo, sk);
+        hi = max(hi, sk);
+        ++n_pres;
+      }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      n_pres += __shfl_xor_sync(0xffffffffu, n_pres, o);
+      lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+      hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    }
+    if (lane_id == 0 && lo <= hi) {
+      atomicAdd(&s_res[0], n_pres);
+      atomicMin(&s_kmin, lo);
+      atomicMax(&s_kmax, hi);
+    }
+    __syncthreads();
+    select_from_registers(t, pres, s_res[0]);
+    return;
   }
   uint32_t bin_floor = 0;
   bool try_fast = !have_pre;
@@ -1401,7 +1461,7 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
   // them per SM (block top-m, causal prefill)
   int cand_cap = kCandCap;
   if (n_cols <= kCandCap) {
-    cand_cap = 1024;
+    cand_cap = 2048;   // at least 16 KB: the register path keeps its second histogram there
     while (cand_cap < n_cols) cand_cap <<= 1;
   } else if (k > kCandCap / 2) {
     // a large k (MISA's stage-1 top-8192) needs room for k plus the sampling margin: the long list, which
@@ -1415,7 +1475,7 @@ extern "C" int b200dsa_topk_select(const float* scores, int64_t row_stride, int3
     set_last_error(cudaGetErrorString(e));
     return B200DSA_ECUDA;
   }
-  const int threads = n_cols > 8192 ? 1024 : (n_cols > 2048 ? 512 : 256);
+  const int threads = n_cols > 4096 ? 1024 : (n_cols > 2048 ? 512 : 256);   // at most eight columns per thread up to 8192
   e = launch_chained(topk_select_kernel, dim3(n_rows), dim3(threads), smem, static_cast<cudaStream_t>(stream), p, k_pow2,
                      cand_cap);
   if (e == cudaSuccess) e = cudaGetLastError();
@@ -1537,13 +1597,13 @@ extern "C" int b200dsa_topk_merge_owned(const int32_t* recv, int32_t world, int3
   while (k_pow2 < k) k_pow2 <<= 1;
   int cand_cap = kCandCap;
   if (world * k <= kCandCap) {
-    cand_cap = 1024;
+    cand_cap = 2048;
     while (cand_cap < world * k) cand_cap <<= 1;
   }
   const size_t smem = kHistBins * sizeof(uint32_t) + (static_cast<size_t>(cand_cap) + kEqCap + k_pow2) * sizeof(uint64_t);
   cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kMaxSelectSmem);
-  const int threads = world * k > 8192 ? 1024 : (world * k > 2048 ? 512 : 256);
+  const int threads = world * k > 4096 ? 1024 : (world * k > 2048 ? 512 : 256);
   if (e == cudaSuccess)
     e = launch_chained(topk_select_kernel, dim3(n_rows), dim3(threads), smem, static_cast<cudaStream_t>(stream), p,
                        k_pow2, cand_cap);
