@@ -17,6 +17,8 @@
 // Exact fallback (any distribution, massive ties): the same radix select with the row in
 // global memory as its source, re-reading it once per digit.
 // The k winners are optionally bitonic-sorted (descending score, ascending position).
+#include <type_traits>
+
 #include "b200dsa_common.cuh"
 
 namespace b200dsa {
@@ -740,13 +742,14 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     for (int j = 0; j < kFastPer; ++j) m |= (tid + j * nthr < c) ? (1u << j) : 0u;
     return m;
   };
-  auto select_from_registers = [&](uint64_t (&t)[kFastPer], uint32_t pres, int n_present) {
+  auto select_from_registers = [&](auto& t, uint32_t pres, int n_present) {
+    constexpr int kPer = static_cast<int>(sizeof(t) / sizeof(t[0]));
     const uint32_t kmin = s_kmin, kmax = s_kmax;
     const int score_bits = kmax > kmin ? 32 - __clz(kmax - kmin) : 0;
     const int width = score_bits + 32;
     const uint64_t sub = static_cast<uint64_t>(kmin) << 32;
 #pragma unroll
-    for (int j = 0; j < kFastPer; ++j) t[j] -= sub;   // absent entries are never looked at
+    for (int j = 0; j < kPer; ++j) t[j] -= sub;   // absent entries are never looked at
     uint64_t prefix = 0;
     int pbits = 0, need = k;
     const int max_levels = n_present > k ? 6 : 0;   // no more candidates than wanted: all of them win
@@ -758,7 +761,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
       const int shift = width - pbits - dbits;
       const uint32_t mask = (1u << dbits) - 1u;
 #pragma unroll
-      for (int j = 0; j < kFastPer; ++j) {
+      for (int j = 0; j < kPer; ++j) {
         if (((pres >> j) & 1u) && (pbits == 0 || (t[j] >> (width - pbits)) == prefix))
           atomicAdd(&cur[static_cast<uint32_t>(t[j] >> shift) & mask], 1u);
       }
@@ -781,7 +784,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     auto wins = [&](uint64_t x) { return pbits == 0 || (x >> (width - pbits)) >= prefix; };
     int mine = 0;
 #pragma unroll
-    for (int j = 0; j < kFastPer; ++j) mine += (((pres >> j) & 1u) && wins(t[j])) ? 1 : 0;
+    for (int j = 0; j < kPer; ++j) mine += (((pres >> j) & 1u) && wins(t[j])) ? 1 : 0;
     int incl = mine;
     for (int o = 1; o < 32; o <<= 1) {
       const int v = __shfl_up_sync(0xffffffffu, incl, o);
@@ -793,7 +796,7 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     warp_totals_scan(s_warp_cnt, n_warps, warp_id, before, total);
     before += incl - mine;
 #pragma unroll
-    for (int j = 0; j < kFastPer; ++j) {
+    for (int j = 0; j < kPer; ++j) {
       if (((pres >> j) & 1u) && wins(t[j])) {
         if (before < k_pow2) sel[before] = t[j] + sub;
         ++before;
@@ -928,23 +931,26 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
       cnt = c;
     }
   }
-  if (!p.pre_cand && n <= kFastPer * nthr && cand_cap >= 2048) {
+  // short rows, and the merge of the ranks' candidates: straight from global memory into registers, eight
+  // columns per thread (sixteen for the 16384 candidates of an eight-rank merge)
+  auto direct_from_global = [&](auto per_tag) {
+    constexpr int kPer = decltype(per_tag)::value;
     // short rows, and the merge of the ranks' candidates: straight from global memory into registers
     for (int i = tid; i < kHistBins; i += nthr) {
       hist[i] = 0;
       hist2[i] = 0;
     }
-    float v[kFastPer];
+    float v[kPer];
 #pragma unroll
-    for (int j = 0; j < kFastPer; ++j) {
+    for (int j = 0; j < kPer; ++j) {
       const int i = tid + j * nthr;
       v[j] = i < n ? __ldg(src + coff(begin + i)) : 0.f;
     }
-    uint64_t t[kFastPer];
+    uint64_t t[kPer];
     uint32_t pres = 0, lo = 0xffffffffu, hi = 0u;
     int n_pres = 0;
 #pragma unroll
-    for (int j = 0; j < kFastPer; ++j) {
+    for (int j = 0; j < kPer; ++j) {
       const int i = tid + j * nthr;
       t[j] = 0ull;
       if (i < n && score_valid(v[j], p.keep_pos_inf)) {
@@ -968,7 +974,16 @@ __global__ void __launch_bounds__(1024, 1) topk_select_kernel(const TopkParams p
     }
     __syncthreads();
     select_from_registers(t, pres, s_res[0]);
-    return;
+  };
+  if (!p.pre_cand && cand_cap >= 2048) {
+    if (n <= kFastPer * nthr) {
+      direct_from_global(std::integral_constant<int, kFastPer>{});
+      return;
+    }
+    if (n <= 2 * kFastPer * nthr) {
+      direct_from_global(std::integral_constant<int, 2 * kFastPer>{});
+      return;
+    }
   }
   uint32_t bin_floor = 0;
   bool try_fast = !have_pre;
