@@ -211,3 +211,43 @@ def test_topk_split_private_list_overflow_falls_back():
         assert torch.equal(out, ref)
         assert (scratch[1][:n_rows] == 0).all()
     assert set(cols.tolist()) <= set(out[1].cpu().tolist())
+
+
+@pytest.mark.parametrize("n_cols", [700, 3000, 8192, 12000, 16384])
+def test_topk_short_rows_ties_and_specials(n_cols):
+    """Rows of at most sixteen columns per thread are selected from registers (score keys relative to the
+    smallest, then the bit-inverted positions of tied keys): all-equal rows, two-valued rows, coarse values with
+    long runs of ties, NaN / -inf / +inf entries, fewer valid scores than k, positions that do not grow with
+    the column."""
+    from transarch_b200 import kernels as K
+    g = torch.Generator().manual_seed(n_cols)
+    k = min(2048, n_cols // 2)
+    s = torch.zeros(6, n_cols)
+    s[1, torch.arange(0, n_cols, 11)] = 1.0                              # two-valued
+    s[2] = (torch.randn(n_cols, generator=g) * 3).round() / 2 + 0.0      # coarse: long runs of ties (+ 0.0 turns
+                                                                          # -0.0 into +0.0: the keys order the two)
+    s[3] = torch.randn(n_cols, generator=g)
+    s[3, ::5] = float("nan"); s[3, 1::5] = float("-inf"); s[3, 7] = float("inf")
+    s[4] = float("-inf"); s[4, 5:5 + k // 3] = torch.randn(k // 3, generator=g)   # fewer valid scores than k
+    s[5] = -torch.arange(n_cols).float()                                  # strictly decreasing
+    idx = K.topk_select(s.cuda(), k, sorted=True).cpu()
+    un = K.topk_select(s.cuda(), k, sorted=False).cpu()
+    for r in range(6):
+        row = s[r].clone()
+        row[torch.isnan(row) | (row == float("inf"))] = float("-inf")
+        n_valid = int(torch.isfinite(row).sum())
+        exp = torch.sort(row, descending=True, stable=True).indices[:min(k, n_valid)]
+        assert torch.equal(idx[r, :exp.numel()].long(), exp), r
+        assert (idx[r, exp.numel():] == -1).all()
+        assert torch.equal(torch.sort(un[r]).values, torch.sort(idx[r]).values)
+    with_inf = K.topk_select(s.cuda(), 8, keep_pos_inf=True).cpu()
+    assert with_inf[3, 0] == 7
+    # ties broken by POSITION when positions come from a page table in which they do not grow with the column
+    if n_cols % 128 == 0:
+        pages = torch.stack([torch.randperm(4 * n_cols // 128, generator=g)[: n_cols // 128] for _ in range(6)]).int()
+        got = K.topk_select(s.cuda(), k, page_table=pages.cuda(), page_size=128, sorted=True).cpu()
+        col = torch.arange(n_cols)
+        pos = pages.long()[:, col // 128] * 128 + (col % 128)
+        for r in (0, 1, 2):
+            order = sorted(range(n_cols), key=lambda c: (-float(s[r, c]), int(pos[r, c])))[:k]
+            assert got[r].tolist() == [int(pos[r, c]) for c in order]
