@@ -479,11 +479,14 @@ def main():
         graphed = GraphedDecodeStep(step, state.k_cache, state.context_lens, state.block_table, state.kv,
                                     state.kv_row_base, state.context_lens_local).capture()
 
+    from transarch_b200.decode import PipelinedDecode, input_layout, pack_inputs, unpack_inputs
+    dev_pack = [pack_inputs(*dq) for dq in dev_q]       # the query sets, resident in HBM in the packed layout
+
     def run_device(i):
-        # inputs already resident in HBM: a device-to-device copy into the graph's static buffers
+        # inputs already resident in HBM: one device-to-device copy into the graph's static buffer
         if graphed is None:
             return run_eager(i)
-        return graphed.replay(*dev_q[i % n_sets])
+        return graphed.replay_packed(dev_pack[i % n_sets])
 
     # End to end with HOST buffers, as a serving loop would run it: three streams and four slots, so the
     # pinned-host -> device copy of step i+1 and the device -> host copy of step i-1 overlap the
@@ -492,7 +495,6 @@ def main():
     slots = 4
     # a step's three inputs travel as one packed byte buffer: one pinned arena per query set on the host, one
     # staging buffer per slot on the device (the views below are what an eager step reads)
-    from transarch_b200.decode import input_layout, pack_inputs, unpack_inputs
     lay = input_layout(B, HEADS)
     host_pack = [pack_inputs(*hq, out=torch.empty(lay["bytes"], dtype=torch.uint8).pin_memory()) for hq in host_q]
     in_pack = [torch.empty(lay["bytes"], dtype=torch.uint8, device=dev) for _ in range(slots)]
@@ -542,7 +544,29 @@ def main():
         r_idx, r_ctx = graphed.out[0], graphed.out[1]
         res_rows = (r_idx[rows_lo:rows_hi], r_ctx[rows_lo:rows_hi]) if ag is not None else (r_idx, r_ctx)
 
+    # Single GPU: three captured steps with buffers of their own (PipelinedDecode), so that the copies from and to
+    # the host use the graphs' own buffers and no device-side staging copy is left in the loop.  (Two would stall:
+    # a slot's input copy can only start once its previous result has reached the host, 160 us after its kernels,
+    # and takes 190 us itself, more than the one step in between.)
+    pipe = None
+    if world == 1 and graphed is not None:
+        captured = [graphed]
+        for _ in range(2):
+            step_n = SparseDecodeStep(B, shard_len, page_size=PAGE, topk=TOPK, n_heads=HEADS, index_scale=INDEX_SCALE,
+                                      attn_scale=ATTN_SCALE, device=dev, shard=shard, ctx_dtype=torch.bfloat16,
+                                      result=args.result)
+            step_n.run(*dev_q[0], state.k_cache, state.context_lens, state.block_table, state.kv, state.kv_row_base,
+                       state.context_lens_local)
+            torch.cuda.synchronize()
+            captured.append(GraphedDecodeStep(step_n, state.k_cache, state.context_lens, state.block_table, state.kv,
+                                              state.kv_row_base, state.context_lens_local).capture())
+        pipe = PipelinedDecode(captured)
+        out_host = pipe.host_out              # what the byte counts below and the parity check read
+
     def run_e2e(i):
+        if pipe is not None:
+            pipe.submit(host_pack[i % n_sets])
+            return
         sl = i % slots
         main = torch.cuda.current_stream()
         if e2e_started[sl]:

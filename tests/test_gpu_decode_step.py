@@ -178,3 +178,43 @@ def test_many_shards_through_peer_buffers_emulated(world):
             assert (lse_out.view(B, H) - lse1).abs().max() < 1e-3
     finally:
         pc.close()
+
+
+def test_pipelined_decode_returns_each_steps_own_result():
+    """Two captured steps used in turn with host buffers: every submitted input set comes back with the result
+    the eager step gives for it (no slot hands out another step's data, inputs are not overwritten early)."""
+    from transarch_b200 import _lib
+    from transarch_b200.decode import GraphedDecodeStep, PipelinedDecode, SparseDecodeStep, pack_inputs
+    ctxs = [6000, 9000, 3000]
+    prob = make_global_problem(43, ctxs)
+    st = shard_state(prob, 0, 1, max(ctxs), "cuda")
+    args = (st["cache"], st["lens"], st["table"], st["kv"], st["base"])
+    mk = lambda: SparseDecodeStep(len(ctxs), st["table"].shape[1] * 64, topk=512, sorted_topk=True,
+                                  ctx_dtype=torch.bfloat16)
+    eager = mk()
+    graphs = []
+    for _ in range(2):
+        stp = mk()
+        stp.run(*_cuda(prob), *args)
+        torch.cuda.synchronize()
+        graphs.append(GraphedDecodeStep(stp, *args).capture())
+    pipe = PipelinedDecode(graphs)
+    g = torch.Generator().manual_seed(7)
+    sets, want = [], []
+    for i in range(5):
+        q_idx = torch.randn(prob["q_idx"].shape, generator=g).bfloat16()
+        w = (torch.randn(prob["w"].shape, generator=g) / 8).float()
+        q_lat = torch.randn(prob["q_lat"].shape, generator=g).bfloat16()
+        sets.append(pack_inputs(q_idx, w, q_lat).pin_memory())
+        idx, ctx, _ = eager.run(q_idx.cuda(), w.cuda(), q_lat.cuda(), *args)
+        want.append((idx.cpu().clone(), ctx.cpu().clone()))
+    slots = []
+    for i in range(5):
+        sl = pipe.submit(sets[i])
+        slots.append(sl)
+        if i >= 1:                                # read step i-1 while step i is in flight
+            idx, ctx = pipe.result(slots[i - 1])
+            assert torch.equal(idx, want[i - 1][0]) and torch.equal(ctx, want[i - 1][1])
+    idx, ctx = pipe.result(slots[4])
+    assert torch.equal(idx, want[4][0]) and torch.equal(ctx, want[4][1])
+    assert _lib.read_status(torch.device("cuda")) == 0

@@ -22,7 +22,7 @@ Host-logic tests on CPU ranks pass a stand-in with the same function names.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -365,3 +365,63 @@ class GraphedDecodeStep:
             self.q_lat.copy_(q_lat, non_blocking=True)
         self.graph.replay()
         return self.out
+
+
+class PipelinedDecode:
+    """A serving loop over host buffers without device-side staging copies: several captured steps, each with its
+    own input and result buffers, are used in turn, so that the host-to-device copy of step i+1 lands straight
+    in the static input buffer of its graph while the kernels of step i run, and the device-to-host copy of step
+    i-1 reads the result buffers of its graph.  (With a single graph the inputs and results have to pass through
+    per-slot device buffers: three device-to-device copies per step.)  Single-GPU steps only: the captured steps
+    of a key-sharded run share one exchange buffer and its step counters.
+
+        pipe = PipelinedDecode([GraphedDecodeStep(step_a, ...).capture(), GraphedDecodeStep(step_b, ...).capture()])
+        slot = pipe.submit(packed_pinned)       # inputs in pack_inputs layout, page-locked host memory
+        idx, ctx = pipe.result(slot)            # page-locked host tensors, valid until the slot is submitted again
+    """
+
+    def __init__(self, graphs: Sequence["GraphedDecodeStep"]):
+        if len(graphs) < 2:
+            raise ValueError("PipelinedDecode needs at least two captured steps")
+        for g in graphs:
+            if g.graph is None or g.step.shard.world_size != 1:
+                raise ValueError("PipelinedDecode takes captured single-GPU steps")
+        self.graphs = list(graphs)
+        dev = graphs[0].step.dev
+        n = len(graphs)
+        self.s_in, self.s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        self.ev_in = [torch.cuda.Event() for _ in range(n)]
+        self.ev_done = [torch.cuda.Event() for _ in range(n)]
+        self.ev_out = [torch.cuda.Event() for _ in range(n)]
+        self.started = [False] * n
+        self.host_out = [(torch.empty(g.out[0].shape, dtype=g.out[0].dtype).pin_memory(),
+                          torch.empty(g.out[1].shape, dtype=g.out[1].dtype).pin_memory()) for g in graphs]
+        self.count = 0
+
+    def submit(self, packed_host: torch.Tensor) -> int:
+        """Enqueue one step on the next slot; returns the slot.  Blocks only until that slot's previous result
+        has reached the host (its graph's buffers are free then)."""
+        sl = self.count % len(self.graphs)
+        self.count += 1
+        g = self.graphs[sl]
+        main = torch.cuda.current_stream()
+        if self.started[sl]:
+            self.ev_out[sl].synchronize()
+        with torch.cuda.stream(self.s_in):
+            g.inputs.copy_(packed_host, non_blocking=True)
+            self.ev_in[sl].record(self.s_in)
+        main.wait_event(self.ev_in[sl])
+        g.graph.replay()
+        self.ev_done[sl].record(main)
+        self.s_out.wait_event(self.ev_done[sl])
+        with torch.cuda.stream(self.s_out):
+            self.host_out[sl][0].copy_(g.out[0], non_blocking=True)
+            self.host_out[sl][1].copy_(g.out[1], non_blocking=True)
+            self.ev_out[sl].record(self.s_out)
+        self.started[sl] = True
+        return sl
+
+    def result(self, slot: int):
+        """(indices, ctx) of the last step submitted on `slot`, on the host."""
+        self.ev_out[slot].synchronize()
+        return self.host_out[slot]
