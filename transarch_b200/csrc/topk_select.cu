@@ -4,19 +4,23 @@
 // position into a unique 64-bit composite, so "k largest composites" is a total order:
 // descending score, ties towards the lowest position.
 //
-// Fast path (reads the row about once):
-//   1. contiguous chunks spread over the row are sampled into a 4096-bin histogram of the
-//      top 12 key bits (warp-aggregated shared-memory atomics) and a bin is chosen so that,
-//      with a 6-sigma margin, at least k row elements lie at or above it;
-//   2. one streaming pass appends every element at or above that bin to a shared-memory
-//      candidate list (warp-aggregated append);
-//   3. an exact most-significant-digit radix select (12/12/8-bit digits over the 64-bit
-//      composite) runs on the candidates in shared memory; the undecided bin, once small,
-//      is bitonic-sorted to pick the last few winners.
-// Rows that fit the candidate list entirely skip step 1.
-// Exact fallback (any distribution, massive ties): the same radix select with the row in
-// global memory as its source, re-reading it once per digit.
-// The k winners are optionally bitonic-sorted (descending score, ascending position).
+// topk_select_kernel (few rows; 256 to 1024 threads per row), by where the candidates of a row come from:
+//   * a list collected by an earlier kernel (the indexer's epilogue, or topk_collect_kernel), a row of at most
+//     sixteen columns per thread, or the merged candidates of the ranks: the candidates stay in REGISTERS; the
+//     score keys are taken relative to the smallest one, an exact most-significant-digit radix select with 12-bit
+//     digits runs over them with two alternating histograms until the threshold bin holds exactly the keys still
+//     wanted, and the winners are placed by a scan of per-thread counts;
+//   * a long row: contiguous chunks spread over the row are sampled into a 4096-bin histogram of the top 12 key
+//     bits and a bin is chosen so that, with a 6-sigma margin, at least k row elements lie at or above it; one
+//     streaming pass appends every element at or above that bin to a shared-memory candidate list; the same
+//     radix select then runs on the list in shared memory;
+//   * exact fallback (any distribution, massive ties, overflowing lists): the radix select (12/12/8-bit digits)
+//     with the row in global memory as its source, re-reading it once per digit; the undecided bin, once small,
+//     is sorted to pick the last few winners.
+// topk_rows_kernel (many rows of at most 8192 columns): a 256-thread CTA per row, the row in shared memory as
+// 32-bit keys, positions computed for tied keys and winners only.
+// The k winners are optionally ordered (descending score, ascending position) by a counting sort into buckets that
+// are linear in the score, with a bitonic sort as the fallback for rows whose scores crowd into one bucket.
 #include <type_traits>
 
 #include "b200dsa_common.cuh"
