@@ -327,6 +327,14 @@ int b200dsa_indexer_flat_bf16_logits(const void* q_bf16, const float* weights, c
                                      float out_scale, float* logits, int64_t logits_stride,
                                      int32_t* status, void* stream);
 
+/* Causal intervals of packed queries, one launch: for row t at position p = q_pos[t] (t when q_pos is NULL),
+ * lo[t] = start of the last document of cu_seqlens [n_cu] that begins at or before p, hi[t] = p + 1
+ * (OpenDSA/opendsa/ops/flashkl_warmup.py:41-56 prepare_ks_ke, :235-248 prepare_ks_ke_cp), and the column frame the
+ * flat logits kernels and the selection use: col0[t] = lo rounded down to a multiple of 128, row_cols[t] = the
+ * multiple of 128 that covers [col0, hi).  All arrays int32 [n_rows]. */
+int b200dsa_causal_row_intervals(const int32_t* cu_seqlens, int32_t n_cu, const int32_t* q_pos, int32_t n_rows,
+                                 int32_t* lo, int32_t* hi, int32_t* col0, int32_t* row_cols, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Sparse MLA attention over selected keys in the absorbed latent space (tcgen05), one query
  * token per item; emits the latent-space context and the log-sum-exp so that partial results

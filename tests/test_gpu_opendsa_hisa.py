@@ -257,3 +257,21 @@ def test_patch_opendsa_rebinds_the_reference_names():
     mq, mk, mw = mine.cuda()(h.cuda(), h.cuda(), cos.cuda(), sin.cuda())
     for a, b in ((mq, rq), (mk, rk), (mw, rw)):
         assert (a.cpu() - b).abs().max() < 2e-4 * b.abs().max()
+
+
+def test_causal_row_intervals_equal_the_torch_helpers():
+    """One launch gives what prepare_ks_ke / prepare_ks_ke_cp and the column-frame arithmetic give."""
+    from transarch_b200 import kernels as K
+    from transarch_b200.opendsa_ops import prepare_ks_ke, prepare_ks_ke_cp
+    cu = torch.tensor([0, 5, 5, 700, 701, 4096], dtype=torch.int32, device="cuda")      # an empty document too
+    lo, hi, col0, rc = K.causal_row_intervals(cu, 4096)
+    ks, ke = prepare_ks_ke(cu, total=4096)
+    assert torch.equal(lo.long(), ks) and torch.equal(hi.long(), ke)
+    assert torch.equal(col0, (lo >> 7) << 7)
+    assert torch.equal(rc, ((((hi + 127) >> 7) << 7) - col0).clamp(min=0))
+    g = torch.Generator().manual_seed(1)
+    pos = torch.randint(0, 4096, (333,), generator=g).cuda()
+    lo, hi, col0, rc = K.causal_row_intervals(cu, 333, pos)
+    ks, ke = prepare_ks_ke_cp(cu, pos)
+    assert torch.equal(lo.long(), ks) and torch.equal(hi.long(), ke)
+    assert torch.equal(rc, ((((hi + 127) >> 7) << 7) - ((lo >> 7) << 7)).clamp(min=0))

@@ -41,6 +41,7 @@ SIGNATURES = {
     "b200dsa_indexer_flat_bf16_logits_routed": [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _f32, _vp, _i64, _vp, _vp],
     "b200dsa_indexer_gather_bf16_logits": [_vp, _vp, _vp, _i32, _vp, _i64, _vp, _vp, _vp, _i32, _i32, _f32, _vp, _i64,
                                            _vp, _vp],
+    "b200dsa_causal_row_intervals": [_vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp],
     "b200dsa_compact_owned": [_vp, _i64, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _vp],
     "b200dsa_sparse_mla_decode": [_vp, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32,
                                   _vp, _i32, _vp, _vp, _vp],

@@ -467,3 +467,56 @@ extern "C" int b200dsa_indexer_flat_bf16_logits_routed(const void* q8_bf16, cons
   return flat_launch<kRoutedHeads>(q8_bf16, weights8, keys_bf16, n_keys, pos_lo, pos_hi, row_cols, n_rows, max_cols,
                                    out_scale, logits, logits_stride, status, stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Causal intervals of packed queries in one launch (the reference builds them with a Python loop over the
+// documents, OpenDSA/opendsa/ops/flashkl_warmup.py:41-56, or a searchsorted, :235-248; as separate torch
+// operations they cost about fifteen launches in front of the logits kernel): for row t at position
+// p = q_pos[t] (or t), doc = the last document whose start is <= p, lo = its start, hi = p + 1, and the
+// column frame of the logits kernels: col0 = lo rounded down to a 128-key block, row_cols = blocks covering
+// [col0, hi) in keys.
+// ---------------------------------------------------------------------------------------------
+namespace b200dsa {
+__global__ void __launch_bounds__(256) causal_row_intervals_kernel(const int32_t* __restrict__ cu, int n_cu,
+                                                                   const int32_t* __restrict__ q_pos, int n_rows,
+                                                                   int32_t* __restrict__ lo, int32_t* __restrict__ hi,
+                                                                   int32_t* __restrict__ col0,
+                                                                   int32_t* __restrict__ row_cols) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_rows) return;
+  const int p = q_pos ? q_pos[t] : t;
+  // first index whose start is > p (searchsorted right), minus one, kept inside the documents
+  int a = 0, b = n_cu;
+  while (a < b) {
+    const int m = (a + b) >> 1;
+    if (__ldg(cu + m) <= p) a = m + 1; else b = m;
+  }
+  int d = a - 1;
+  d = max(0, min(d, n_cu - 2));
+  const int s = __ldg(cu + d);
+  const int e = p + 1;
+  const int c0 = (s >> 7) << 7;
+  lo[t] = s;
+  hi[t] = e;
+  col0[t] = c0;
+  row_cols[t] = max(0, (((e + 127) >> 7) << 7) - c0);
+}
+}  // namespace b200dsa
+
+extern "C" int b200dsa_causal_row_intervals(const int32_t* cu_seqlens, int32_t n_cu, const int32_t* q_pos,
+                                            int32_t n_rows, int32_t* lo, int32_t* hi, int32_t* col0,
+                                            int32_t* row_cols, void* stream) {
+  if (n_rows == 0) return B200DSA_OK;
+  if (!cu_seqlens || n_cu < 2 || n_rows < 0 || !lo || !hi || !col0 || !row_cols) {
+    set_last_error("b200dsa_causal_row_intervals: bad argument (cu_seqlens needs at least two entries)");
+    return B200DSA_EINVAL;
+  }
+  causal_row_intervals_kernel<<<(n_rows + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      cu_seqlens, n_cu, q_pos, n_rows, lo, hi, col0, row_cols);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return B200DSA_ECUDA;
+  }
+  return B200DSA_OK;
+}

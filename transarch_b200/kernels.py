@@ -404,6 +404,21 @@ def indexer_flat_bf16_logits(q: torch.Tensor, weights: torch.Tensor, keys: torch
     return out
 
 
+def causal_row_intervals(cu_seqlens: torch.Tensor, n_rows: int, q_pos: Optional[torch.Tensor] = None):
+    """(lo, hi, col0, row_cols) int32 [n_rows] of packed causal queries in one launch; see
+    b200dsa_causal_row_intervals."""
+    require_cuda(cu_seqlens, q_pos)
+    cu = cu_seqlens.to(torch.int32).contiguous()
+    qp = None if q_pos is None else q_pos.to(torch.int32).contiguous()
+    if qp is not None and qp.numel() != n_rows:
+        raise _lib.B200DSAError("q_pos must have one entry per row")
+    out = torch.empty(4, max(n_rows, 1), dtype=torch.int32, device=cu.device)
+    rc = _lib.load().b200dsa_causal_row_intervals(ptr(cu), cu.numel(), ptr(qp), n_rows, ptr(out[0]), ptr(out[1]),
+                                                   ptr(out[2]), ptr(out[3]), stream_ptr())
+    check(rc, "b200dsa_causal_row_intervals")
+    return out[0, :n_rows], out[1, :n_rows], out[2, :n_rows], out[3, :n_rows]
+
+
 def indexer_flat_bf16_logits_routed(q8: torch.Tensor, weights8: torch.Tensor, keys: torch.Tensor, pos_lo: torch.Tensor,
                                     pos_hi: torch.Tensor, row_cols: torch.Tensor, max_cols: int, *,
                                     out_scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:

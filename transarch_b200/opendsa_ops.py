@@ -105,10 +105,6 @@ def indexer_select_topk(index_q, index_k, index_w, cu_seqlens, topk, *, sm_scale
     if d != 128:
         raise B200DSAError("index head dim must be 128")
     sf = sm_scale_index if sm_scale_index is not None else d ** -0.5
-    if q_global_pos is None:
-        ks, ke = prepare_ks_ke(cu_seqlens, total=Lq)
-    else:
-        ks, ke = prepare_ks_ke_cp(cu_seqlens, q_global_pos)
     q, w = _pad_heads(index_q.to(torch.bfloat16), index_w.to(torch.float32))
     k = index_k.to(torch.bfloat16).contiguous()
     Lk = k.shape[0]
@@ -121,10 +117,14 @@ def indexer_select_topk(index_q, index_k, index_w, cu_seqlens, topk, *, sm_scale
     rows_per = max(1, min(q_chunk, _MAX_LOGIT_BYTES // (cols * 4)))
     k_eff = topk
     buf = torch.empty(min(rows_per, Lq), cols, dtype=torch.float32, device=index_q.device)   # read below row_cols only
+    # the causal intervals of all queries and the column frame of their logits rows: one launch
+    lo, hi, col0, row_cols = K.causal_row_intervals(cu_seqlens, Lq, q_global_pos)
     for t0 in range(0, Lq, rows_per):
         t1 = min(t0 + rows_per, Lq)
-        logits, col0, row_cols = indexer_logits_flat(q[t0:t1], k, w[t0:t1], ks[t0:t1], ke[t0:t1], sf, out=buf)
-        K.topk_select(logits, k_eff, col_end=row_cols, row_pos_offset=col0, sorted=sorted, out=out[t0:t1])
+        logits = K.indexer_flat_bf16_logits(q[t0:t1], w[t0:t1], k, lo[t0:t1], hi[t0:t1], row_cols[t0:t1], cols,
+                                            out_scale=sf, out=buf)
+        K.topk_select(logits[:t1 - t0], k_eff, col_end=row_cols[t0:t1], row_pos_offset=col0[t0:t1], sorted=sorted,
+                      out=out[t0:t1])
     return out
 
 
