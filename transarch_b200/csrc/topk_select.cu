@@ -1285,7 +1285,7 @@ __global__ void __launch_bounds__(kRowsThreads) topk_rows_kernel(const TopkParam
   uint32_t* keys = hist + kHistBins;                                      // the row; later the sort's scratch
   uint64_t* sel = reinterpret_cast<uint64_t*>(keys + key_words);          // ordered result only: the winners
   __shared__ int s_res[3], s_cnt;
-  __shared__ uint32_t s_seg[32];
+  __shared__ uint32_t s_seg[32], s_kmin, s_kmax, s_big;
 
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
@@ -1300,9 +1300,16 @@ __global__ void __launch_bounds__(kRowsThreads) topk_rows_kernel(const TopkParam
   const int k = p.k;
 
   for (int i = tid; i < kHistBins; i += kRowsThreads) hist[i] = 0;
-  if (tid == 0) s_cnt = 0;
+  if (tid == 0) {
+    s_cnt = 0;
+    s_kmin = 0xffffffffu;
+    s_kmax = 0u;
+    s_big = 0u;
+  }
   __syncthreads();
-  // ---- load: keys to shared memory, level-0 histogram (top 12 bits) on the way
+  // ---- load: keys to shared memory, level-0 histogram (top 12 bits) on the way; for an ordered result also
+  // the range of the valid keys
+  uint32_t klo = 0xffffffffu, khi = 0u;
   for (int base = 0; base < n; base += kRowsThreads * 8) {
     float v[8];
 #pragma unroll
@@ -1317,8 +1324,22 @@ __global__ void __launch_bounds__(kRowsThreads) topk_rows_kernel(const TopkParam
         const bool ok = score_valid(v[u], p.keep_pos_inf);
         const uint32_t key = ok ? float_to_ordered(v[u]) : 0u;
         keys[i] = key;
-        if (ok) atomicAdd(&hist[key >> 20], 1u);
+        if (ok) {
+          atomicAdd(&hist[key >> 20], 1u);
+          klo = min(klo, key);
+          khi = max(khi, key);
+        }
       }
+    }
+  }
+  if (p.sorted) {
+    for (int o = 16; o > 0; o >>= 1) {
+      klo = min(klo, __shfl_xor_sync(0xffffffffu, klo, o));
+      khi = max(khi, __shfl_xor_sync(0xffffffffu, khi, o));
+    }
+    if ((tid & 31) == 0 && klo <= khi) {
+      atomicMin(&s_kmin, klo);
+      atomicMax(&s_kmax, khi);
     }
   }
   __syncthreads();
@@ -1377,6 +1398,19 @@ __global__ void __launch_bounds__(kRowsThreads) topk_rows_kernel(const TopkParam
     return (npos_of(i) >> (32 - nbits)) >= (tnpos >> (32 - nbits));
   };
   const int lane = tid & 31;
+  // Ordered result: the winners are counted into 4096 buckets of equal width in KEY space, bucket 0 holding the
+  // largest keys (the smallest winner key is the decided threshold prefix, or the row minimum when everything
+  // wins; integer arithmetic only), while they are emitted.
+  uint32_t win_lo = s_kmin;
+  if (!take_all) win_lo = max(win_lo, kbits >= 32 ? tkey : (tkey & ~((1u << (32 - kbits)) - 1u)));
+  const uint32_t win_hi = max(s_kmax, win_lo);
+  const int span_bits = win_hi > win_lo ? 32 - __clz(win_hi - win_lo) : 0;
+  const int bshift = max(0, span_bits - 12);
+  auto bucket_of = [&](uint32_t key) { return static_cast<int>((win_hi - key) >> bshift); };   // 0 .. 4095
+  if (p.sorted) {
+    for (int i = tid; i < kHistBins; i += kRowsThreads) hist[i] = 0;   // the radix levels are done with it
+    __syncthreads();
+  }
   for (int base = 0; base < n; base += kRowsThreads) {
     const int i = base + tid;
     const uint32_t key = i < n ? keys[i] : 0u;
@@ -1391,6 +1425,7 @@ __global__ void __launch_bounds__(kRowsThreads) topk_rows_kernel(const TopkParam
       const int32_t pos = out_position(p, row, begin + i);
       if (p.sorted) {
         sel[slot] = (static_cast<uint64_t>(key) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(pos));
+        atomicAdd(&hist[bucket_of(key)], 1u);
       } else {
         out_idx[slot] = pos;
         if (out_val) out_val[slot] = ordered_to_float(key);
@@ -1401,17 +1436,69 @@ __global__ void __launch_bounds__(kRowsThreads) topk_rows_kernel(const TopkParam
   const int n_sel = min(s_cnt, k);
   if (p.sorted) {
     uint64_t* tmp = reinterpret_cast<uint64_t*>(keys);
-    if (n_sel > 1 && (n_sel <= 64 || !bucket_sort_desc(sel, n_sel, tmp, hist, s_seg))) {
-      int n_pow2 = 64;
-      while (n_pow2 < n_sel) n_pow2 <<= 1;
-      for (int i = n_sel + tid; i < n_pow2; i += kRowsThreads) sel[i] = 0;
+    bool done = false;
+    if (n_sel > 64) {
+      // exclusive scan of the bucket counts (thread t owns buckets 16t .. 16t+15); hist[b] <- first slot of bucket b
+      constexpr int kPer = kHistBins / kRowsThreads;
+      uint32_t sum = 0, big = 0;
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) {
+        const uint32_t c = hist[tid * kPer + j];
+        sum += c;
+        big = max(big, c);
+      }
+      uint32_t incl = sum;
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      for (int o = 16; o > 0; o >>= 1) big = max(big, __shfl_xor_sync(0xffffffffu, big, o));
+      if (lane == 31) s_seg[tid >> 5] = incl;
+      if (lane == 0 && big > static_cast<uint32_t>(kBucketMax)) atomicMax(&s_big, big);
       __syncthreads();
-      sort_desc(sel, n_pow2);
+      if (s_big == 0u) {     // uniform; otherwise long runs of equal-ish keys: the general sort below
+        int before_w, total_w;
+        warp_totals_scan(s_seg, kRowsThreads / 32, tid >> 5, before_w, total_w);
+        uint32_t before = incl - sum + static_cast<uint32_t>(before_w);
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+          const uint32_t c = hist[tid * kPer + j];
+          hist[tid * kPer + j] = before;
+          before += c;
+        }
+        __syncthreads();
+        for (int i = tid; i < n_sel; i += kRowsThreads) {
+          const uint64_t key = sel[i];
+          tmp[atomicAdd(&hist[bucket_of(static_cast<uint32_t>(key >> 32))], 1u)] = key;   // hist[b] ends as one past bucket b
+        }
+        __syncthreads();
+        // exact rank inside the bucket by the full composite, then straight to the result
+        for (int i = tid; i < n_sel; i += kRowsThreads) {
+          const uint64_t key = tmp[i];
+          const int b = bucket_of(static_cast<uint32_t>(key >> 32));
+          const int e = static_cast<int>(hist[b]);
+          const int s0 = b == 0 ? 0 : static_cast<int>(hist[b - 1]);
+          int rank = 0;
+          for (int j = s0; j < e; ++j) rank += tmp[j] > key;
+          out_idx[s0 + rank] = static_cast<int32_t>(~static_cast<uint32_t>(key & 0xffffffffu));
+          if (out_val) out_val[s0 + rank] = ordered_to_float(static_cast<uint32_t>(key >> 32));
+        }
+        done = true;
+      }
     }
-    for (int j = tid; j < n_sel; j += kRowsThreads) {
-      const uint64_t key = sel[j];
-      out_idx[j] = static_cast<int32_t>(~static_cast<uint32_t>(key & 0xffffffffu));
-      if (out_val) out_val[j] = ordered_to_float(static_cast<uint32_t>(key >> 32));
+    if (!done) {
+      if (n_sel > 1 && (n_sel <= 64 || !bucket_sort_desc(sel, n_sel, tmp, hist, s_seg))) {
+        int n_pow2 = 64;
+        while (n_pow2 < n_sel) n_pow2 <<= 1;
+        for (int i = n_sel + tid; i < n_pow2; i += kRowsThreads) sel[i] = 0;
+        __syncthreads();
+        sort_desc(sel, n_pow2);
+      }
+      for (int j = tid; j < n_sel; j += kRowsThreads) {
+        const uint64_t key = sel[j];
+        out_idx[j] = static_cast<int32_t>(~static_cast<uint32_t>(key & 0xffffffffu));
+        if (out_val) out_val[j] = ordered_to_float(static_cast<uint32_t>(key >> 32));
+      }
     }
   }
   for (int j = n_sel + tid; j < k; j += kRowsThreads) {
