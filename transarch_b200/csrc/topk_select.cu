@@ -1407,7 +1407,8 @@ __global__ void __launch_bounds__(kRowsThreads) topk_rows_kernel(const TopkParam
   const int span_bits = win_hi > win_lo ? 32 - __clz(win_hi - win_lo) : 0;
   const int bshift = max(0, span_bits - 12);
   auto bucket_of = [&](uint32_t key) { return static_cast<int>((win_hi - key) >> bshift); };   // 0 .. 4095
-  if (p.sorted) {
+  const bool use_buckets = p.sorted && k > 64;   // up to 64 winners are ordered by compare-exchange
+  if (use_buckets) {
     for (int i = tid; i < kHistBins; i += kRowsThreads) hist[i] = 0;   // the radix levels are done with it
     __syncthreads();
   }
@@ -1425,7 +1426,7 @@ __global__ void __launch_bounds__(kRowsThreads) topk_rows_kernel(const TopkParam
       const int32_t pos = out_position(p, row, begin + i);
       if (p.sorted) {
         sel[slot] = (static_cast<uint64_t>(key) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(pos));
-        atomicAdd(&hist[bucket_of(key)], 1u);
+        if (use_buckets) atomicAdd(&hist[bucket_of(key)], 1u);
       } else {
         out_idx[slot] = pos;
         if (out_val) out_val[slot] = ordered_to_float(key);
@@ -1437,7 +1438,7 @@ __global__ void __launch_bounds__(kRowsThreads) topk_rows_kernel(const TopkParam
   if (p.sorted) {
     uint64_t* tmp = reinterpret_cast<uint64_t*>(keys);
     bool done = false;
-    if (n_sel > 64) {
+    if (use_buckets && n_sel > 64) {
       // exclusive scan of the bucket counts (thread t owns buckets 16t .. 16t+15); hist[b] <- first slot of bucket b
       constexpr int kPer = kHistBins / kRowsThreads;
       uint32_t sum = 0, big = 0;
